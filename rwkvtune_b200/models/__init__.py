@@ -1,0 +1,5 @@
+from .configuration import GenerationConfig, RWKVConfig
+from .auto_model import AutoModel
+from .rwkv7 import RWKV7Config, RWKV7Model
+
+__all__ = ["RWKVConfig", "GenerationConfig", "AutoModel", "RWKV7Model", "RWKV7Config"]

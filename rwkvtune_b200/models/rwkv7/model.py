@@ -1,0 +1,386 @@
+"""RWKV-7 ("x070") network built from fused operator calls.
+
+The parameter tree and names are those of the reference
+(``rwkvtune/models/rwkv7/model.py:34-654``) so a ``model.pth`` written by either
+project loads in the other.  The forward pass is *not* the reference's chain of
+~45 framework ops per layer: each block is eight fused operator calls
+(``rwkvtune_b200.ops``) that map one-to-one onto sm_100a kernels on a GPU and
+onto plain PyTorch on the CPU.  One code path serves the three modes the
+reference implements separately: training from a zero state
+(``model.py:435-466``), stateful inference (``:468-497``) and infinite-context
+training with the state carried between chunks
+(``rwkvtune/models/rwkv7/model_infctx.py:200-255``).
+"""
+from __future__ import annotations
+
+import math
+from typing import Any, Dict, List, Optional, Sequence, Tuple
+
+import torch
+import torch.nn as nn
+from torch.utils.checkpoint import checkpoint as _checkpoint
+
+from ... import ops
+from ..generation_mixin import GenerationMixin
+
+
+class Linear(nn.Linear):
+    """Bias-free ``nn.Linear`` whose matmul goes through the framework GEMM."""
+
+    def __init__(self, in_features: int, out_features: int, device=None, dtype=None):
+        super().__init__(in_features, out_features, bias=False, device=device, dtype=dtype)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:  # noqa: D401
+        return ops.linear(x, self.weight)
+
+
+def _ortho(rows: int, cols: int, scale: float, generator: Optional[torch.Generator] = None) -> torch.Tensor:
+    gain = math.sqrt(rows / cols) if rows > cols else 1.0
+    w = torch.empty(rows, cols)
+    nn.init.orthogonal_(w, gain=gain * scale, generator=generator)
+    return w
+
+
+def _low_rank_width(cfg_value: int, coeff: float, C: int) -> int:
+    if cfg_value and cfg_value > 0:
+        return int(cfg_value)
+    return max(32, int(round((coeff * (C ** 0.5)) / 32) * 32))
+
+
+class RWKV7TimeMix(nn.Module):
+    """Time-mix ("attention") half of a block; init formulas follow ``model.py:48-117``."""
+
+    def __init__(self, config, layer_id: int):
+        super().__init__()
+        self.config = config
+        self.layer_id = layer_id
+        self.head_size = config.head_size_a
+        C = config.n_embd
+        self.n_head = H = config.dim_att // self.head_size
+        N = self.head_size
+        L = config.n_layer
+
+        r01 = layer_id / max(L - 1, 1)
+        r10 = 1.0 - layer_id / L
+        idx = torch.arange(C, dtype=torch.float32)
+        ddd = (idx / C).reshape(1, 1, C)
+        linear = idx / max(C - 1, 1) - 0.5
+        zz = ((idx % N) - (N - 1) / 2) / ((N - 1) / 2)
+        zigzag = zz * zz.abs()
+        www = -6 + 6 * (idx / max(C - 1, 1)) ** (1 + r01 ** 0.3)
+
+        P = nn.Parameter
+        self.x_r = P(1.0 - ddd.pow(0.2 * r10))
+        self.x_w = P(1.0 - ddd.pow(0.9 * r10))
+        self.x_k = P(1.0 - ddd.pow(0.7 * r10))
+        self.x_v = P(1.0 - ddd.pow(0.7 * r10))
+        self.x_a = P(1.0 - ddd.pow(0.9 * r10))
+        self.x_g = P(1.0 - ddd.pow(0.2 * r10))
+
+        Dw = _low_rank_width(getattr(config, "dim_att_lora", 0), 2.0, C)
+        self.w1 = P(torch.zeros(C, Dw))
+        self.w2 = P(_ortho(Dw, C, 0.1))
+        self.w0 = P((www + 0.5 + zigzag * 2.5).reshape(1, 1, C))
+
+        self.a1 = P(torch.zeros(C, Dw))
+        self.a2 = P(_ortho(Dw, C, 0.1))
+        self.a0 = P((-0.19 + zigzag * 0.3 + linear * 0.4).reshape(1, 1, C))
+
+        if layer_id > 0:
+            Dv = _low_rank_width(getattr(config, "dim_mv_lora", 0), 1.4, C)
+            self.v1 = P(torch.zeros(C, Dv))
+            self.v2 = P(_ortho(Dv, C, 0.1))
+            self.v0 = P((0.73 - linear * 0.4).reshape(1, 1, C))
+
+        Dg = _low_rank_width(getattr(config, "dim_gate_lora", 0), 5.6, C)
+        self.g1 = P(torch.zeros(C, Dg))
+        self.g2 = P(_ortho(Dg, C, 0.1))
+
+        self.k_k = P((0.71 - linear * 0.1).reshape(1, 1, C))
+        self.k_a = P(torch.full((1, 1, C), 1.02))
+        self.r_k = P(torch.full((H, N), -0.04))
+
+        self.receptance = Linear(C, C)
+        self.key = Linear(C, C)
+        self.value = Linear(C, C)
+        self.output = Linear(C, C)
+        self.ln_x = nn.GroupNorm(H, C, eps=ops.GROUPNORM_EPS)
+        with torch.no_grad():
+            s = C ** -0.5
+            self.receptance.weight.uniform_(-0.5 * s, 0.5 * s)
+            self.key.weight.uniform_(-0.05 * s, 0.05 * s)
+            self.value.weight.uniform_(-0.5 * s, 0.5 * s)
+            self.output.weight.zero_()
+
+    def mix_matrix(self) -> torch.Tensor:
+        C = self.x_r.shape[-1]
+        return torch.cat([self.x_r, self.x_w, self.x_k, self.x_v, self.x_a, self.x_g], dim=0).reshape(6, C)
+
+    def forward(self, x, ln_w, ln_b, v_first, x_prev=None, wkv_state=None, want_state: bool = False):
+        """``x`` is the *pre-LayerNorm* residual stream ``[B, T, C]``.
+
+        Returns ``(out, v_first, last_ln_row, new_wkv_state)``; the last two are
+        ``None`` unless ``want_state``.
+        """
+        mixed, last = ops.ln_shift_mix(x, ln_w, ln_b, self.mix_matrix(), x_prev)
+        xr, xw, xk, xv, xa, xg = mixed.unbind(0)
+
+        r = self.receptance(xr)
+        k = self.key(xk)
+        v = self.value(xv)
+        w_lin = ops.matmul(torch.tanh(ops.matmul(xw, self.w1)), self.w2)
+        a_lin = ops.matmul(ops.matmul(xa, self.a1), self.a2)
+        g = ops.matmul(torch.sigmoid(ops.matmul(xg, self.g1)), self.g2)
+        if self.layer_id == 0:
+            v_lin = None
+            w, k, v, a_, b_ = ops.timemix_prep(k, v, None, w_lin, a_lin, None, self.w0, self.a0, None,
+                                               self.k_k, self.k_a, self.head_size)
+            v_first = v
+        else:
+            v_lin = ops.matmul(ops.matmul(xv, self.v1), self.v2)
+            w, k, v, a_, b_ = ops.timemix_prep(k, v, v_first, w_lin, a_lin, v_lin, self.w0, self.a0, self.v0,
+                                               self.k_k, self.k_a, self.head_size)
+
+        y, new_state = ops.wkv7(r, w, k, v, a_, b_, self.head_size, state=wkv_state, return_state=want_state)
+        z = ops.gn_bonus_gate(y, r, k, v, g, self.ln_x.weight, self.ln_x.bias, self.r_k, self.head_size)
+        out = self.output(z)
+        return out, v_first, (last if want_state else None), new_state
+
+
+class RWKV7ChannelMix(nn.Module):
+    """Squared-ReLU feed-forward half of a block (``model.py:281-343``); width is ``4 * n_embd``."""
+
+    def __init__(self, config, layer_id: int):
+        super().__init__()
+        self.config = config
+        self.layer_id = layer_id
+        C = config.n_embd
+        r10 = 1.0 - layer_id / config.n_layer
+        ddd = (torch.arange(C, dtype=torch.float32) / C).reshape(1, 1, C)
+        self.x_k = nn.Parameter(1.0 - ddd.pow(r10 ** 4))
+        self.key = Linear(C, 4 * C)
+        self.value = Linear(4 * C, C)
+        with torch.no_grad():
+            s = C ** -0.5
+            self.key.weight.uniform_(-0.5 * s, 0.5 * s)
+            self.value.weight.zero_()
+
+    def forward(self, x, ln_w, ln_b, x_prev=None, want_state: bool = False):
+        mixed, last = ops.ln_shift_mix(x, ln_w, ln_b, self.x_k.reshape(1, -1), x_prev)
+        hidden = ops.relu_squared(self.key(mixed[0]))
+        return self.value(hidden), (last if want_state else None)
+
+
+class RWKV7Block(nn.Module):
+    def __init__(self, config, layer_id: int):
+        super().__init__()
+        self.config = config
+        self.layer_id = layer_id
+        self.ln1 = nn.LayerNorm(config.n_embd)
+        self.ln2 = nn.LayerNorm(config.n_embd)
+        self.skip_ln0 = False
+        if layer_id == 0:
+            self.ln0 = nn.LayerNorm(config.n_embd)
+        self.att = RWKV7TimeMix(config, layer_id)
+        self.ffn = RWKV7ChannelMix(config, layer_id)
+
+    def forward(self, x, v_first, att_prev=None, wkv_state=None, ffn_prev=None, want_state: bool = False):
+        if self.layer_id == 0 and not self.skip_ln0:
+            x = ops.layer_norm(x, self.ln0.weight, self.ln0.bias)
+        att, v_first, att_last, new_wkv = self.att(x, self.ln1.weight, self.ln1.bias, v_first,
+                                                   att_prev, wkv_state, want_state)
+        x = x + att
+        ffn, ffn_last = self.ffn(x, self.ln2.weight, self.ln2.bias, ffn_prev, want_state)
+        x = x + ffn
+        return x, v_first, att_last, new_wkv, ffn_last
+
+
+def _block_plain(block, x, v_first):
+    x, v_first, _, _, _ = block(x, v_first)
+    return x, v_first
+
+
+def _block_stateful(block, x, v_first, att_prev, wkv_state, ffn_prev):
+    return block(x, v_first, att_prev, wkv_state, ffn_prev, True)
+
+
+class RWKV7Model(GenerationMixin, nn.Module):
+    """Full model: embedding, ``n_layer`` blocks, final LayerNorm and the vocabulary head."""
+
+    def __init__(self, config):
+        super().__init__()
+        self.config = config
+        self.emb = nn.Embedding(config.vocab_size, config.n_embd)
+        self.blocks = nn.ModuleList([RWKV7Block(config, i) for i in range(config.n_layer)])
+        self.ln_out = nn.LayerNorm(config.n_embd)
+        self.head = Linear(config.n_embd, config.vocab_size)
+        self._emb_preprocessed = False
+
+    # ------------------------------------------------------------------ helpers
+    @property
+    def device(self) -> torch.device:
+        return self.emb.weight.device
+
+    @property
+    def dtype(self) -> torch.dtype:
+        return self.emb.weight.dtype
+
+    def _use_checkpoint(self) -> bool:
+        return bool(getattr(self.config, "grad_cp", 0) == 1 and self.training and torch.is_grad_enabled())
+
+    # ------------------------------------------------------------------ hidden states
+    def forward_hidden(self, idx: torch.Tensor) -> torch.Tensor:
+        """Run embedding and all blocks from a zero state; returns ``ln_out`` output ``[B, T, C]``."""
+        B, T = idx.shape
+        if T > self.config.ctx_len:
+            raise ValueError(f"sequence length {T} exceeds ctx_len {self.config.ctx_len}")
+        x = self.emb(idx)
+        v_first = torch.empty_like(x)
+        cp = self._use_checkpoint()
+        for block in self.blocks:
+            if cp:
+                x, v_first = _checkpoint(_block_plain, block, x, v_first, use_reentrant=False)
+            else:
+                x, v_first = _block_plain(block, x, v_first)
+        return ops.layer_norm(x, self.ln_out.weight, self.ln_out.bias)
+
+    def forward(self, idx: torch.Tensor, logits_to_keep: Optional[int] = None) -> torch.Tensor:
+        """Logits ``[B, T, V]`` (or the last ``logits_to_keep`` positions), ``model.py:435-466``."""
+        x = self.forward_hidden(idx)
+        if logits_to_keep is not None and logits_to_keep < x.shape[1]:
+            x = x[:, -logits_to_keep:, :]
+        return self.head(x)
+
+    def loss(self, idx: torch.Tensor, labels: torch.Tensor, l2wrap: bool = True) -> torch.Tensor:
+        """Mean cross-entropy over targets ``!= -100`` plus L2Wrap, without materialising the logits.
+
+        Equivalent to ``CrossEntropyLoss(ignore_index=-100)(model(idx).view(-1, V), labels.view(-1))``
+        followed by ``L2Wrap`` (``rwkvtune/training/lightning_module.py:175-206``).
+        """
+        x = self.forward_hidden(idx)
+        B, T, C = x.shape
+        return ops.linear_cross_entropy(x.reshape(B * T, C), self._head_weight(), labels.reshape(-1),
+                                        l2wrap=l2wrap, l2wrap_tokens=B * T)
+
+    def _head_weight(self) -> torch.Tensor:
+        head = self.head
+        if hasattr(head, "base_layer"):  # LoRA-wrapped heads are merged on the fly
+            return head.effective_weight()
+        return head.weight
+
+    # ------------------------------------------------------------------ stateful paths
+    def init_state(self, batch_size: int) -> List[Dict[str, torch.Tensor]]:
+        """One dict per layer: ``att_x_prev [B,C]``, ``att_kv [B,H,N,N]`` fp32, ``ffn_x_prev [B,C]``."""
+        cfg = self.config
+        H, N = cfg.dim_att // cfg.head_size_a, cfg.head_size_a
+        dev, dt = self.device, self.dtype
+        return [
+            {
+                "att_x_prev": torch.zeros(batch_size, cfg.n_embd, dtype=dt, device=dev),
+                "att_kv": torch.zeros(batch_size, H, N, N, dtype=torch.float32, device=dev),
+                "ffn_x_prev": torch.zeros(batch_size, cfg.n_embd, dtype=dt, device=dev),
+            }
+            for _ in range(cfg.n_layer)
+        ]
+
+    def forward_states(self, idx, att_prev: Sequence[torch.Tensor], wkv: Sequence[torch.Tensor],
+                       ffn_prev: Sequence[torch.Tensor], checkpoint: bool = False):
+        """Blocks with state in and out.  Returns ``(hidden, att_last[L], wkv[L], ffn_last[L])``.
+
+        Gradients flow through the incoming states, which is what full
+        back-propagation through time across chunks needs.
+        """
+        x = self.emb(idx)
+        v_first = torch.empty_like(x)
+        new_att, new_wkv, new_ffn = [], [], []
+        for i, block in enumerate(self.blocks):
+            if checkpoint:
+                x, v_first, a_l, s_l, f_l = _checkpoint(_block_stateful, block, x, v_first, att_prev[i], wkv[i],
+                                                        ffn_prev[i], use_reentrant=False)
+            else:
+                x, v_first, a_l, s_l, f_l = _block_stateful(block, x, v_first, att_prev[i], wkv[i], ffn_prev[i])
+            new_att.append(a_l)
+            new_wkv.append(s_l)
+            new_ffn.append(f_l)
+        x = ops.layer_norm(x, self.ln_out.weight, self.ln_out.bias)
+        return x, new_att, new_wkv, new_ffn
+
+    def forward_with_state(self, idx: torch.Tensor, states: Optional[List[Dict[str, torch.Tensor]]] = None,
+                           last_only: bool = False):
+        """Stateful inference step (prefill chunk or decode); ``model.py:468-497``.
+
+        Returns ``(logits, new_states)``.  ``logits`` covers every position unless
+        ``last_only`` (then ``[B, 1, V]``).  Carried rows are the post-LayerNorm
+        activations of the last token, stored in fp32 like the reference does.
+        """
+        B, T = idx.shape
+        if states is None:
+            states = self.init_state(B)
+        x, a_l, s_l, f_l = self.forward_states(
+            idx, [s["att_x_prev"] for s in states], [s["att_kv"] for s in states],
+            [s["ffn_x_prev"] for s in states])
+        if last_only:
+            x = x[:, -1:, :]
+        logits = self.head(x)
+        new_states = [
+            {"att_x_prev": a.float(), "att_kv": s.float(), "ffn_x_prev": f.float()}
+            for a, s, f in zip(a_l, s_l, f_l)
+        ]
+        return logits, new_states
+
+    def forward_batch_dynamic(self, tokens_list: List[List[int]], states=None, full_output: bool = False):
+        """Ragged batch forward (``model.py:522-585``): sequences advance in lock-step by the
+        shortest remaining length until all are consumed."""
+        n = len(tokens_list)
+        lengths = [len(t) for t in tokens_list]
+        if states is None:
+            states = self.init_state(n)
+        pos = [0] * n
+        outs: List[Any] = [[] for _ in range(n)] if full_output else [None] * n
+        while True:
+            active = [i for i in range(n) if pos[i] < lengths[i]]
+            if not active:
+                break
+            step = min(lengths[i] - pos[i] for i in active)
+            ids = torch.tensor([tokens_list[i][pos[i]:pos[i] + step] for i in active], dtype=torch.long,
+                               device=self.device)
+            sub = [{k: v[active] for k, v in layer.items()} for layer in states]
+            logits, new_sub = self.forward_with_state(ids, sub)
+            for j, i in enumerate(active):
+                if full_output:
+                    outs[i].append(logits[j])
+                else:
+                    outs[i] = logits[j, -1]
+                pos[i] += step
+            for layer, new_layer in zip(states, new_sub):
+                for key in layer:
+                    layer[key][active] = new_layer[key].to(layer[key].dtype)
+        if full_output:
+            V = self.config.vocab_size
+            outs = [torch.cat(o, dim=0) if o else torch.empty(0, V, dtype=self.dtype, device=self.device) for o in outs]
+        return outs, states
+
+    # ------------------------------------------------------------------ checkpoints
+    def load_state_dict(self, state_dict, strict: bool = True, assign: bool = False):
+        """Accepts official RWKV-LM checkpoints (``model.py:607-654``): flat ``r_k`` is reshaped,
+        layer-0 ``v0/v1/v2`` are dropped, the load is never strict, and a checkpoint without
+        ``blocks.0.ln0.*`` marks the embedding as already normalised (``ln0`` is then skipped)."""
+        sd = dict(state_dict)
+        if "model" in sd and isinstance(sd["model"], dict) and "emb.weight" not in sd:
+            sd = dict(sd["model"])
+        has_ln0 = "blocks.0.ln0.weight" in sd and "blocks.0.ln0.bias" in sd
+        H, N = self.config.dim_att // self.config.head_size_a, self.config.head_size_a
+        for key in list(sd.keys()):
+            if key.endswith("att.r_k") and sd[key].ndim == 1:
+                sd[key] = sd[key].reshape(H, N)
+        if len(self.blocks) and not hasattr(self.blocks[0].att, "v1"):
+            for sfx in ("0", "1", "2"):
+                sd.pop(f"blocks.0.att.v{sfx}", None)
+        result = super().load_state_dict(sd, strict=False, assign=assign)
+        self._emb_preprocessed = not has_ln0
+        if len(self.blocks):
+            self.blocks[0].skip_ln0 = not has_ln0
+        return result
+
+    def num_parameters(self, trainable_only: bool = False) -> int:
+        return sum(p.numel() for p in self.parameters() if p.requires_grad or not trainable_only)

@@ -1,0 +1,124 @@
+"""Fused operator entry points.
+
+Every function here has two implementations with one contract:
+
+* CUDA tensors run the hand-written sm_100a kernels from ``rwkvtune_b200/csrc``
+  (loaded through :mod:`rwkvtune_b200.ops._ext`).  If the native library is
+  missing, a CUDA call raises instead of silently running something else.
+* CPU tensors run the plain-PyTorch statements in :mod:`rwkvtune_b200.ops.reference`,
+  which are also the oracles of the kernel tests.
+
+``set_kernel_enabled(name, False)`` routes one operator family to the PyTorch
+statement on the GPU as well; it exists for A/B measurements and for bisecting
+numerical differences, not as a production mode.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from . import reference
+from .reference import GROUPNORM_EPS, LAYERNORM_EPS, L2WRAP_FACTOR
+
+_KERNELS: Dict[str, bool] = {
+    "wkv7": True,
+    "ln_shift_mix": True,
+    "layer_norm": True,
+    "timemix_prep": True,
+    "gn_bonus_gate": True,
+    "relu_squared": True,
+    "linear_cross_entropy": True,
+    "linear_logprob_entropy": True,
+    "gemm": True,
+}
+
+
+def set_kernel_enabled(name: str, enabled: bool) -> None:
+    if name not in _KERNELS:
+        raise KeyError(f"unknown kernel family {name!r}; known: {sorted(_KERNELS)}")
+    _KERNELS[name] = bool(enabled)
+
+
+def kernel_enabled(name: str) -> bool:
+    return _KERNELS[name]
+
+
+def _native(t: torch.Tensor, name: str) -> bool:
+    return t.is_cuda and _KERNELS[name]
+
+
+def _cuda():
+    from . import cuda_ops  # imported lazily: needs the native library
+
+    return cuda_ops
+
+
+# ------------------------------------------------------------------------------- GEMMs
+def linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """``x @ weight^T`` for an ``nn.Linear`` weight ``[out, in]``."""
+    if _native(x, "gemm"):
+        return _cuda().linear(x, weight)
+    return torch.nn.functional.linear(x, weight)
+
+
+def matmul(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``x @ w`` for a right-multiplied ``[in, out]`` matrix (the low-rank adapters)."""
+    if _native(x, "gemm"):
+        return _cuda().matmul(x, w)
+    return x @ w
+
+
+# ------------------------------------------------------------------------------- fused element-wise
+def layer_norm(x, weight, bias, eps: float = LAYERNORM_EPS):
+    if _native(x, "layer_norm"):
+        return _cuda().layer_norm(x, weight, bias, eps)
+    return reference.layer_norm(x, weight, bias, eps)
+
+
+def ln_shift_mix(x, ln_w, ln_b, mix, prev=None, eps: float = LAYERNORM_EPS):
+    if _native(x, "ln_shift_mix"):
+        return _cuda().ln_shift_mix(x, ln_w, ln_b, mix, prev, eps)
+    return reference.ln_shift_mix(x, ln_w, ln_b, mix, prev, eps)
+
+
+def timemix_prep(k, v, v_first, w_lin, a_lin, v_lin, w0, a0, v0, k_k, k_a, head_size: int = 64):
+    if _native(k, "timemix_prep"):
+        return _cuda().timemix_prep(k, v, v_first, w_lin, a_lin, v_lin, w0, a0, v0, k_k, k_a, head_size)
+    return reference.timemix_prep(k, v, v_first, w_lin, a_lin, v_lin, w0, a0, v0, k_k, k_a, head_size)
+
+
+def gn_bonus_gate(y, r, k, v, g, gn_w, gn_b, r_k, head_size: int = 64, eps: float = GROUPNORM_EPS):
+    if _native(y, "gn_bonus_gate"):
+        return _cuda().gn_bonus_gate(y, r, k, v, g, gn_w, gn_b, r_k, head_size, eps)
+    return reference.gn_bonus_gate(y, r, k, v, g, gn_w, gn_b, r_k, head_size, eps)
+
+
+def relu_squared(x):
+    if _native(x, "relu_squared"):
+        return _cuda().relu_squared(x)
+    return reference.relu_squared(x)
+
+
+# ------------------------------------------------------------------------------- recurrence
+def wkv7(r, w, k, v, a, b, head_size: int = 64, state: Optional[torch.Tensor] = None,
+         return_state: bool = False):
+    """WKV7 recurrence.  Returns ``(y, final_state or None)``; ``y`` has the dtype of ``r``."""
+    if _native(r, "wkv7"):
+        return _cuda().wkv7(r, w, k, v, a, b, head_size, state, return_state)
+    y, s = reference.wkv7(r, w, k, v, a, b, head_size, state)
+    return y.to(r.dtype), (s if return_state else None)
+
+
+# ------------------------------------------------------------------------------- losses
+def linear_cross_entropy(x, weight, labels, l2wrap: bool = True, ignore_index: int = -100,
+                         l2wrap_tokens: Optional[int] = None):
+    if _native(x, "linear_cross_entropy"):
+        return _cuda().linear_cross_entropy(x, weight, labels, l2wrap, ignore_index, l2wrap_tokens)
+    return reference.linear_cross_entropy(x, weight, labels, l2wrap, ignore_index, l2wrap_tokens)
+
+
+def linear_logprob_entropy(x, weight, targets, temperature: float = 1.0, with_entropy: bool = True):
+    if _native(x, "linear_logprob_entropy"):
+        return _cuda().linear_logprob_entropy(x, weight, targets, temperature, with_entropy)
+    return reference.linear_logprob_entropy(x, weight, targets, temperature, with_entropy)
