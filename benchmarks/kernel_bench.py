@@ -1,0 +1,152 @@
+"""Per-kernel micro-benchmarks: CUDA-event timing, achieved GB/s or TFLOP/s, fraction of the measured peak.
+
+    python benchmarks/kernel_bench.py [--only wkv7,ln_shift_mix,...] [--B 8 --T 4096 --C 2048] [--json out.json]
+
+Peaks come from MEASURED_PEAKS.json at the repository root when present (copy bandwidth and
+cuBLAS bf16 throughput measured on the same pool), otherwise from the documented fallback
+(6650 GB/s, 1590 TFLOP/s).  Inputs are larger than the 126 MB L2 at the default shape.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+from rwkvtune_b200 import ops  # noqa: E402
+
+BF = torch.bfloat16
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d["hbm_gbs"], d["bf16_tflops"], "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def timeit(fn, warmup=3, iters=10):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        ts.append(s.elapsed_time(e))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def bench_wkv7(B, T, C, out):
+    H = C // 64
+    r, k, v = (torch.randn(B, T, C, device="cuda").to(BF) for _ in range(3))
+    w = (-torch.nn.functional.softplus(-(torch.randn(B, T, C, device="cuda") * 2 - 1)) - 0.5).to(BF)
+    kk = torch.nn.functional.normalize(torch.randn(B, T, H, 64, device="cuda"), dim=-1).view(B, T, C)
+    a = (-kk).to(BF)
+    b = (kk * torch.rand_like(kk)).to(BF)
+    ins = [t.requires_grad_(True) for t in (r, w, k, v, a, b)]
+    with torch.no_grad():
+        ms_inf = timeit(lambda: ops.wkv7(*ins, 64))
+    ms_fwd = timeit(lambda: ops.wkv7(*ins, 64))
+    y, _ = ops.wkv7(*ins, 64)
+    gy = torch.randn_like(y)
+    ms_bwd = timeit(lambda: torch.autograd.grad(y, ins, gy, retain_graph=True))
+    out["wkv7_fwd_nograd_ms"] = ms_inf
+    out["wkv7_fwd_train_ms"] = ms_fwd
+    out["wkv7_bwd_ms"] = ms_bwd
+    flop = 4 * 2 * B * T * H * 64 * 64
+    out["wkv7_fwd_fp32_tflops"] = flop / ms_inf / 1e9
+
+
+def bench_elementwise(B, T, C, out, hbm):
+    x = torch.randn(B, T, C, device="cuda").to(BF).requires_grad_(True)
+    w = torch.ones(C, device="cuda", requires_grad=True)
+    b = torch.zeros(C, device="cuda", requires_grad=True)
+    nbytes = B * T * C * 2
+    for K in (6, 1):
+        mix = torch.rand(K, C, device="cuda", requires_grad=True)
+        ms = timeit(lambda: ops.ln_shift_mix(x, w, b, mix))
+        o, _ = ops.ln_shift_mix(x, w, b, mix)
+        go = torch.randn_like(o)
+        msb = timeit(lambda: torch.autograd.grad(o, [x, w, b, mix], go, retain_graph=True))
+        out[f"ln_shift_mix{K}_fwd_ms"] = ms
+        out[f"ln_shift_mix{K}_fwd_frac_hbm"] = (1 + K) * nbytes / ms / 1e6 / hbm
+        out[f"ln_shift_mix{K}_bwd_ms"] = msb
+        out[f"ln_shift_mix{K}_bwd_frac_hbm"] = (2 + K) * nbytes / msb / 1e6 / hbm
+    big = lambda: torch.randn(B, T, C, device="cuda").to(BF).requires_grad_(True)
+    par = lambda: torch.randn(1, 1, C, device="cuda", requires_grad=True)
+    args = [big(), big(), big(), big(), big(), big(), par(), par(), par(), par(), par()]
+    ms = timeit(lambda: ops.timemix_prep(*args, 64))
+    outs = ops.timemix_prep(*args, 64)
+    gs = [torch.randn_like(o) for o in outs]
+    msb = timeit(lambda: torch.autograd.grad(outs, args, gs, retain_graph=True))
+    out["timemix_prep_fwd_ms"] = ms
+    out["timemix_prep_fwd_frac_hbm"] = 11 * nbytes / ms / 1e6 / hbm
+    out["timemix_prep_bwd_ms"] = msb
+    out["timemix_prep_bwd_frac_hbm"] = 17 * nbytes / msb / 1e6 / hbm
+    args = [big(), big(), big(), big(), big(), torch.ones(C, device="cuda", requires_grad=True),
+            torch.zeros(C, device="cuda", requires_grad=True), torch.randn(C // 64, 64, device="cuda", requires_grad=True)]
+    ms = timeit(lambda: ops.gn_bonus_gate(*args, 64))
+    z = ops.gn_bonus_gate(*args, 64)
+    gz = torch.randn_like(z)
+    msb = timeit(lambda: torch.autograd.grad(z, args, gz, retain_graph=True))
+    out["gn_bonus_gate_fwd_ms"] = ms
+    out["gn_bonus_gate_fwd_frac_hbm"] = 6 * nbytes / ms / 1e6 / hbm
+    out["gn_bonus_gate_bwd_ms"] = msb
+    out["gn_bonus_gate_bwd_frac_hbm"] = 11 * nbytes / msb / 1e6 / hbm
+
+
+def bench_gemm(B, T, C, out, tf):
+    from rwkvtune_b200.ops import gemm
+    M = B * T
+    for name, (K, N) in {"CxC": (C, C), "Cx4C": (C, 4 * C), "4CxC": (4 * C, C)}.items():
+        x = torch.randn(M, K, device="cuda").to(BF)
+        w = torch.randn(N, K, device="cuda").to(BF)
+        for native in (False, True):
+            gemm.set_native(native)
+            try:
+                ms = timeit(lambda: gemm.mm_nt(x, w))
+            finally:
+                gemm.set_native(True)
+            tag = "native" if native else "cublas"
+            out[f"gemm_nt_{name}_{tag}_ms"] = ms
+            out[f"gemm_nt_{name}_{tag}_tflops"] = 2 * M * K * N / ms / 1e9
+            out[f"gemm_nt_{name}_{tag}_frac_peak"] = 2 * M * K * N / ms / 1e9 / tf
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--only", default="")
+    ap.add_argument("--B", type=int, default=8)
+    ap.add_argument("--T", type=int, default=4096)
+    ap.add_argument("--C", type=int, default=2048)
+    ap.add_argument("--json", default="")
+    a = ap.parse_args()
+    hbm, tf, src = peaks()
+    out = {"shape": [a.B, a.T, a.C], "peaks": {"hbm_gbs": hbm, "bf16_tflops": tf, "source": src}}
+    only = set(filter(None, a.only.split(",")))
+    if not only or "wkv7" in only:
+        bench_wkv7(a.B, a.T, a.C, out)
+    if not only or "elementwise" in only:
+        bench_elementwise(a.B, a.T, a.C, out, hbm)
+    if not only or "gemm" in only:
+        bench_gemm(a.B, a.T, a.C, out, tf)
+    for k, v in out.items():
+        print(f"{k}: {v:.4g}" if isinstance(v, float) else f"{k}: {v}")
+    if a.json:
+        os.makedirs(os.path.dirname(a.json) or ".", exist_ok=True)
+        json.dump(out, open(a.json, "w"), indent=1)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,91 @@
+"""Ahead-of-time build of the native library for sm_100a.
+
+``python -m rwkvtune_b200.csrc.build`` compiles every ``*.cu`` in this directory with
+``nvcc -gencode arch=compute_100a,code=sm_100a`` and links them into
+``librwkvtune_b200.so`` next to the sources.  The kernels depend on the CUDA runtime
+only (no libtorch), so nvcc cross-compiles them on a machine without a GPU in a few
+seconds per file.  The reference instead JIT-compiles its kernels on the user's
+machine at first use (``rwkvtune/models/rwkv7/operators/wkv_loader.py:260-307``).
+"""
+from __future__ import annotations
+
+import concurrent.futures as cf
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+from typing import List
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_NAME = "librwkvtune_b200.so"
+ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
+COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--use_fast_math", "-Xcompiler", "-fPIC",
+                "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr"]
+
+
+def nvcc_path() -> str:
+    cand = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc")
+    if os.path.exists(cand):
+        return cand
+    found = shutil.which("nvcc")
+    if not found:
+        raise RuntimeError("nvcc not found; set CUDA_HOME")
+    return found
+
+
+def sources() -> List[str]:
+    return sorted(f for f in os.listdir(HERE) if f.endswith(".cu"))
+
+
+def _digest(path: str) -> str:
+    h = hashlib.sha256()
+    for dep in [path] + sorted(os.path.join(HERE, f) for f in os.listdir(HERE) if f.endswith(".cuh")):
+        with open(dep, "rb") as fh:
+            h.update(fh.read())
+    h.update(" ".join(ARCH_FLAGS + COMMON_FLAGS).encode())
+    return h.hexdigest()
+
+
+def _compile_one(src: str, verbose: bool) -> str:
+    obj_dir = os.path.join(HERE, "build")
+    os.makedirs(obj_dir, exist_ok=True)
+    obj = os.path.join(obj_dir, src[:-3] + ".o")
+    stamp = obj + ".sha"
+    digest = _digest(os.path.join(HERE, src))
+    if os.path.exists(obj) and os.path.exists(stamp) and open(stamp).read() == digest:
+        return obj
+    cmd = [nvcc_path()] + ARCH_FLAGS + COMMON_FLAGS + ["-Xptxas", "-v", "-c", os.path.join(HERE, src), "-o", obj]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"nvcc failed for {src}:\n{res.stdout}\n{res.stderr}")
+    with open(os.path.join(obj_dir, src[:-3] + ".ptxas.txt"), "w") as fh:
+        fh.write(res.stderr)
+    if verbose:
+        print(f"[build] {src} ok")
+    with open(stamp, "w") as fh:
+        fh.write(digest)
+    return obj
+
+
+def build(verbose: bool = True, force: bool = False) -> str:
+    """Compile and link; returns the path of the shared library."""
+    if force:
+        shutil.rmtree(os.path.join(HERE, "build"), ignore_errors=True)
+    srcs = sources()
+    with cf.ThreadPoolExecutor(max_workers=min(8, len(srcs) or 1)) as pool:
+        objs = list(pool.map(lambda s: _compile_one(s, verbose), srcs))
+    lib = os.path.join(HERE, LIB_NAME)
+    newest = max(os.path.getmtime(o) for o in objs)
+    if force or not os.path.exists(lib) or os.path.getmtime(lib) < newest:
+        cmd = [nvcc_path(), "-shared", "-o", lib] + objs
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
+        if verbose:
+            print(f"[build] linked {lib}")
+    return lib
+
+
+if __name__ == "__main__":
+    build(verbose=True, force="--force" in sys.argv)

@@ -1,0 +1,67 @@
+// Shared device helpers for the sm_100a kernels of rwkvtune_b200.
+// Everything here is header-only; kernels are exported with C linkage and take raw
+// device pointers plus a cudaStream_t so the library has no dependency on libtorch.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define RWKV_EXPORT extern "C" __attribute__((visibility("default")))
+
+typedef __nv_bfloat16 bf16;
+
+// Error codes returned by the C entry points (0 = ok).  Launch failures return the
+// cudaError_t value offset by 1000 so the Python side can print cudaGetErrorString.
+enum RwkvStatus : int {
+  RWKV_OK = 0,
+  RWKV_ERR_BAD_SHAPE = 1,
+  RWKV_ERR_BAD_ALIGNMENT = 2,
+  RWKV_ERR_TOO_LARGE = 3,
+  RWKV_ERR_NOT_INITIALISED = 4,
+  RWKV_ERR_WAIT_TIMEOUT = 5,
+  RWKV_ERR_CUDA_BASE = 1000,
+};
+
+static inline int rwkv_launch_status() {
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? RWKV_OK : RWKV_ERR_CUDA_BASE + (int)e;
+}
+
+__device__ __forceinline__ float bf16_lo(uint32_t packed) { return __uint_as_float(packed << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t packed) { return __uint_as_float(packed & 0xffff0000u); }
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&t);
+}
+
+// 8 bf16 values (one 16-byte vector) -> 8 floats
+__device__ __forceinline__ void unpack8(const uint4& p, float* f) {
+  f[0] = bf16_lo(p.x); f[1] = bf16_hi(p.x);
+  f[2] = bf16_lo(p.y); f[3] = bf16_hi(p.y);
+  f[4] = bf16_lo(p.z); f[5] = bf16_hi(p.z);
+  f[6] = bf16_lo(p.w); f[7] = bf16_hi(p.w);
+}
+
+__device__ __forceinline__ uint4 pack8(const float* f) {
+  uint4 p;
+  p.x = pack_bf16(f[0], f[1]);
+  p.y = pack_bf16(f[2], f[3]);
+  p.z = pack_bf16(f[4], f[5]);
+  p.w = pack_bf16(f[6], f[7]);
+  return p;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }

@@ -1,0 +1,390 @@
+// LayerNorm + token shift + K-way lerp in one pass over the residual stream (forward and
+// backward), and a plain LayerNorm built from the same pieces.
+//
+//   h = LN(x);  out_k[t] = h[t] + (h[t-1] - h[t]) * mix_k     (h[-1] = carried row or 0)
+//
+// The reference runs this as LayerNorm, ZeroPad2d, a subtraction and six multiply-adds,
+// each a separate pass over [B,T,C] (model.py:138-144, :305-306, :373).  Here x is read once
+// and the K outputs are written once.  h is rounded to bf16 before it is mixed, so a
+// sequence processed in chunks with the carried row gives bit-identical results.
+#include "elementwise.cuh"
+
+namespace {
+
+template <int K>
+__global__ void __launch_bounds__(512)
+ln_shift_mix_fwd_kernel(const bf16* __restrict__ x, const float* __restrict__ ln_w, const float* __restrict__ ln_b,
+                        const float* __restrict__ mix, const bf16* __restrict__ prev, bf16* __restrict__ outs,
+                        bf16* __restrict__ last, float* __restrict__ mean_out, float* __restrict__ rstd_out,
+                        int B, int T, int C, int strip, float eps) {
+  __shared__ float red[2 * EW_MAX_WARPS * 4];
+  int phase = 0;
+  const RowCtx rc = make_row_ctx(T, C, strip);
+  const size_t row0 = (size_t)rc.b * T;
+  const size_t plane = (size_t)B * T * C;
+  const float invC = 1.f / C;
+
+  float w[8], bb[8], mu[K][8], hprev[8];
+  if (rc.active) {
+    load8f(ln_w + rc.col, w);
+    load8f(ln_b + rc.col, bb);
+#pragma unroll
+    for (int k = 0; k < K; ++k) load8f(mix + (size_t)k * C + rc.col, mu[k]);
+  }
+#pragma unroll
+  for (int e = 0; e < 8; ++e) hprev[e] = 0.f;
+
+  // halo: h of the row before the strip
+  if (rc.t0 == 0) {
+    if (prev && rc.active) unpack8(ldg16(prev + (size_t)rc.b * C + rc.col), hprev);
+  } else {
+    float xf[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (rc.active) unpack8(ldg16(x + (row0 + rc.t0 - 1) * C + rc.col), xf);
+    float s[1] = {0.f};
+#pragma unroll
+    for (int e = 0; e < 8; ++e) s[0] += xf[e];
+    block_sum<1>(s, red, phase);
+    const float mean = s[0] * invC;
+    float q[1] = {0.f};
+    if (rc.active) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) q[0] += (xf[e] - mean) * (xf[e] - mean);
+    }
+    block_sum<1>(q, red, phase);
+    const float rstd = rsqrtf(q[0] * invC + eps);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) hprev[e] = round_bf16((xf[e] - mean) * rstd * w[e] + bb[e]);
+  }
+
+  for (int tg = rc.t0; tg < rc.t1; tg += 4) {
+    float xf[4][8];
+    float s[4], q[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      s[i] = 0.f;
+      const int t = tg + i;
+      if (t < rc.t1 && rc.active) {
+        unpack8(ldg16(x + (row0 + t) * C + rc.col), xf[i]);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) s[i] += xf[i][e];
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) xf[i][e] = 0.f;
+      }
+    }
+    block_sum<4>(s, red, phase);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      s[i] *= invC;
+      q[i] = 0.f;
+      if (rc.active) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) q[i] += (xf[i][e] - s[i]) * (xf[i][e] - s[i]);
+      }
+    }
+    block_sum<4>(q, red, phase);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int t = tg + i;
+      if (t >= rc.t1) break;
+      const float rstd = rsqrtf(q[i] * invC + eps);
+      if (threadIdx.x == 0 && mean_out) {
+        mean_out[row0 + t] = s[i];
+        rstd_out[row0 + t] = rstd;
+      }
+      if (rc.active) {
+        float hcur[8], o[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) hcur[e] = round_bf16((xf[i][e] - s[i]) * rstd * w[e] + bb[e]);
+#pragma unroll
+        for (int k = 0; k < K; ++k) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) o[e] = hcur[e] + (hprev[e] - hcur[e]) * mu[k][e];
+          stg16(outs + (size_t)k * plane + (row0 + t) * C + rc.col, pack8(o));
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) hprev[e] = hcur[e];
+      }
+    }
+  }
+  if (last && rc.t1 == T && rc.active) stg16(last + (size_t)rc.b * C + rc.col, pack8(hprev));
+}
+
+// Backward.  Walks the strip in reverse; `carry` holds sum_k dO_k[t+1]*mix_k.  Emits dx, the
+// gradient of the carried row (dprev) and per-CTA partial sums of the parameter gradients in
+// `partials` [gridDim.y*gridDim.x][K+2][C]: rows 0..K-1 = dmix, K = dln_w, K+1 = dln_b.
+template <int K>
+__global__ void __launch_bounds__(512)
+ln_shift_mix_bwd_kernel(const bf16* __restrict__ dO, const bf16* __restrict__ dlast, const bf16* __restrict__ x,
+                        const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
+                        const float* __restrict__ ln_w, const float* __restrict__ ln_b,
+                        const float* __restrict__ mix, const bf16* __restrict__ prev, bf16* __restrict__ dx,
+                        float* __restrict__ dprev, float* __restrict__ partials, int B, int T, int C, int strip) {
+  __shared__ float red[2 * EW_MAX_WARPS * 2];
+  int phase = 0;
+  const RowCtx rc = make_row_ctx(T, C, strip);
+  const size_t row0 = (size_t)rc.b * T;
+  const size_t plane = (size_t)B * T * C;
+  const float invC = 1.f / C;
+
+  float w[8], bb[8], mu[K][8];
+  float acc_mu[K][8], acc_w[8], acc_b[8], carry[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    w[e] = bb[e] = 0.f;
+    acc_w[e] = acc_b[e] = carry[e] = 0.f;
+#pragma unroll
+    for (int k = 0; k < K; ++k) { acc_mu[k][e] = 0.f; mu[k][e] = 0.f; }
+  }
+  if (rc.active) {
+    load8f(ln_w + rc.col, w);
+    load8f(ln_b + rc.col, bb);
+#pragma unroll
+    for (int k = 0; k < K; ++k) load8f(mix + (size_t)k * C + rc.col, mu[k]);
+    if (rc.t1 < T) {   // halo: contribution of the row after the strip
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+        float g[8];
+        unpack8(ldg16(dO + (size_t)k * plane + (row0 + rc.t1) * C + rc.col), g);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) carry[e] += g[e] * mu[k][e];
+      }
+    } else if (dlast) {
+      float g[8];
+      unpack8(ldg16(dlast + (size_t)rc.b * C + rc.col), g);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) carry[e] += g[e];
+    }
+  }
+
+  // h of row t (recomputed exactly as the forward rounded it)
+  auto h_of_row = [&](int t, float* xh, float* h) {
+    if (t < 0) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) { xh[e] = 0.f; h[e] = 0.f; }
+      if (prev && rc.active) unpack8(ldg16(prev + (size_t)rc.b * C + rc.col), h);
+      return;
+    }
+    float xf[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (rc.active) unpack8(ldg16(x + (row0 + t) * C + rc.col), xf);
+    const float m = mean_in[row0 + t], r = rstd_in[row0 + t];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      xh[e] = (xf[e] - m) * r;
+      h[e] = round_bf16(xh[e] * w[e] + bb[e]);
+    }
+  };
+
+  float xh_cur[8], h_cur[8], xh_prev[8], h_prev[8];
+  h_of_row(rc.t1 - 1, xh_cur, h_cur);
+  for (int t = rc.t1 - 1; t >= rc.t0; --t) {
+    h_of_row(t - 1, xh_prev, h_prev);
+    float dh[8], ncarry[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { dh[e] = carry[e]; ncarry[e] = 0.f; }
+    if (rc.active) {
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+        float g[8];
+        unpack8(ldg16(dO + (size_t)k * plane + (row0 + t) * C + rc.col), g);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          dh[e] += g[e] * (1.f - mu[k][e]);
+          ncarry[e] += g[e] * mu[k][e];
+          acc_mu[k][e] += g[e] * (h_prev[e] - h_cur[e]);
+        }
+      }
+    }
+    float c[2] = {0.f, 0.f};
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float g = dh[e] * w[e];
+      c[0] += g;
+      c[1] += g * xh_cur[e];
+      acc_w[e] += dh[e] * xh_cur[e];
+      acc_b[e] += dh[e];
+    }
+    block_sum<2>(c, red, phase);
+    if (rc.active) {
+      const float r = rstd_in[row0 + t];
+      float o[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = r * (dh[e] * w[e] - c[0] * invC - xh_cur[e] * c[1] * invC);
+      stg16(dx + (row0 + t) * C + rc.col, pack8(o));
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      carry[e] = ncarry[e];
+      xh_cur[e] = xh_prev[e];
+      h_cur[e] = h_prev[e];
+    }
+  }
+  if (rc.active) {
+    if (dprev && rc.t0 == 0) store8f(dprev + (size_t)rc.b * C + rc.col, carry);
+    float* p = partials + ((size_t)(blockIdx.y * gridDim.x + blockIdx.x) * (K + 2)) * C + rc.col;
+#pragma unroll
+    for (int k = 0; k < K; ++k) store8f(p + (size_t)k * C, acc_mu[k]);
+    store8f(p + (size_t)K * C, acc_w);
+    store8f(p + (size_t)(K + 1) * C, acc_b);
+  }
+}
+
+// Plain LayerNorm over the last dimension of a [rows, C] tensor, `strip` rows per CTA.
+__global__ void __launch_bounds__(512)
+layer_norm_fwd_kernel(const bf16* __restrict__ x, const float* __restrict__ ln_w, const float* __restrict__ ln_b,
+                      bf16* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows,
+                      int C, int strip, float eps) {
+  __shared__ float red[2 * EW_MAX_WARPS * 4];
+  int phase = 0;
+  const int col = threadIdx.x * 8;
+  const bool active = col < C;
+  const int r0 = blockIdx.x * strip, r1 = min(rows, r0 + strip);
+  const float invC = 1.f / C;
+  float w[8] = {0, 0, 0, 0, 0, 0, 0, 0}, bb[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (active) { load8f(ln_w + col, w); load8f(ln_b + col, bb); }
+  for (int rg = r0; rg < r1; rg += 4) {
+    float xf[4][8], s[4], q[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      s[i] = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) xf[i][e] = 0.f;
+      if (rg + i < r1 && active) {
+        unpack8(ldg16(x + (size_t)(rg + i) * C + col), xf[i]);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) s[i] += xf[i][e];
+      }
+    }
+    block_sum<4>(s, red, phase);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      s[i] *= invC;
+      q[i] = 0.f;
+      if (active) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) q[i] += (xf[i][e] - s[i]) * (xf[i][e] - s[i]);
+      }
+    }
+    block_sum<4>(q, red, phase);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = rg + i;
+      if (r >= r1) break;
+      const float rstd = rsqrtf(q[i] * invC + eps);
+      if (threadIdx.x == 0 && mean_out) { mean_out[r] = s[i]; rstd_out[r] = rstd; }
+      if (active) {
+        float o[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = (xf[i][e] - s[i]) * rstd * w[e] + bb[e];
+        stg16(y + (size_t)r * C + col, pack8(o));
+      }
+    }
+  }
+}
+
+// partials: [gridDim.x][2][C] (dln_w, dln_b)
+__global__ void __launch_bounds__(512)
+layer_norm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const float* __restrict__ mean_in,
+                      const float* __restrict__ rstd_in, const float* __restrict__ ln_w, bf16* __restrict__ dx,
+                      float* __restrict__ partials, int rows, int C, int strip) {
+  __shared__ float red[2 * EW_MAX_WARPS * 2];
+  int phase = 0;
+  const int col = threadIdx.x * 8;
+  const bool active = col < C;
+  const int r0 = blockIdx.x * strip, r1 = min(rows, r0 + strip);
+  const float invC = 1.f / C;
+  float w[8] = {0, 0, 0, 0, 0, 0, 0, 0}, acc_w[8] = {0, 0, 0, 0, 0, 0, 0, 0}, acc_b[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (active) load8f(ln_w + col, w);
+  for (int r = r0; r < r1; ++r) {
+    float g[8] = {0, 0, 0, 0, 0, 0, 0, 0}, xh[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    const float m = mean_in[r], rs = rstd_in[r];
+    if (active) {
+      float xf[8];
+      unpack8(ldg16(dy + (size_t)r * C + col), g);
+      unpack8(ldg16(x + (size_t)r * C + col), xf);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) xh[e] = (xf[e] - m) * rs;
+    }
+    float c[2] = {0.f, 0.f};
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      c[0] += g[e] * w[e];
+      c[1] += g[e] * w[e] * xh[e];
+      acc_w[e] += g[e] * xh[e];
+      acc_b[e] += g[e];
+    }
+    block_sum<2>(c, red, phase);
+    if (active) {
+      float o[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = rs * (g[e] * w[e] - c[0] * invC - xh[e] * c[1] * invC);
+      stg16(dx + (size_t)r * C + col, pack8(o));
+    }
+  }
+  if (active) {
+    float* p = partials + (size_t)blockIdx.x * 2 * C + col;
+    store8f(p, acc_w);
+    store8f(p + C, acc_b);
+  }
+}
+
+inline int threads_for(int C) { return ((C / 8 + 31) / 32) * 32; }
+
+}  // namespace
+
+RWKV_EXPORT int rwkv_ln_shift_mix_forward(const void* x, const void* ln_w, const void* ln_b, const void* mix,
+                                          const void* prev, void* outs, void* last, void* mean, void* rstd, int K,
+                                          int B, int T, int C, int strip, float eps, void* stream) {
+  if (C % 8 || C > 8 * 512 * 2 || C / 8 > 512 || strip <= 0 || B > 65535) return RWKV_ERR_BAD_SHAPE;
+  dim3 grid((T + strip - 1) / strip, B);
+  const int nt = threads_for(C);
+  cudaStream_t st = (cudaStream_t)stream;
+#define LAUNCH(KK)                                                                                              \
+  ln_shift_mix_fwd_kernel<KK><<<grid, nt, 0, st>>>((const bf16*)x, (const float*)ln_w, (const float*)ln_b,      \
+                                                   (const float*)mix, (const bf16*)prev, (bf16*)outs,           \
+                                                   (bf16*)last, (float*)mean, (float*)rstd, B, T, C, strip, eps)
+  if (K == 6) LAUNCH(6);
+  else if (K == 1) LAUNCH(1);
+  else return RWKV_ERR_BAD_SHAPE;
+#undef LAUNCH
+  return rwkv_launch_status();
+}
+
+RWKV_EXPORT int rwkv_ln_shift_mix_backward(const void* dO, const void* dlast, const void* x, const void* mean,
+                                           const void* rstd, const void* ln_w, const void* ln_b, const void* mix,
+                                           const void* prev, void* dx, void* dprev, void* partials, int K, int B,
+                                           int T, int C, int strip, void* stream) {
+  if (C % 8 || C / 8 > 512 || strip <= 0 || B > 65535) return RWKV_ERR_BAD_SHAPE;
+  dim3 grid((T + strip - 1) / strip, B);
+  const int nt = threads_for(C);
+  cudaStream_t st = (cudaStream_t)stream;
+#define LAUNCH(KK)                                                                                             \
+  ln_shift_mix_bwd_kernel<KK><<<grid, nt, 0, st>>>((const bf16*)dO, (const bf16*)dlast, (const bf16*)x,        \
+                                                   (const float*)mean, (const float*)rstd, (const float*)ln_w, \
+                                                   (const float*)ln_b, (const float*)mix, (const bf16*)prev,   \
+                                                   (bf16*)dx, (float*)dprev, (float*)partials, B, T, C, strip)
+  if (K == 6) LAUNCH(6);
+  else if (K == 1) LAUNCH(1);
+  else return RWKV_ERR_BAD_SHAPE;
+#undef LAUNCH
+  return rwkv_launch_status();
+}
+
+RWKV_EXPORT int rwkv_layer_norm_forward(const void* x, const void* ln_w, const void* ln_b, void* y, void* mean,
+                                        void* rstd, int rows, int C, int strip, float eps, void* stream) {
+  if (C % 8 || C / 8 > 512 || strip <= 0) return RWKV_ERR_BAD_SHAPE;
+  layer_norm_fwd_kernel<<<(rows + strip - 1) / strip, threads_for(C), 0, (cudaStream_t)stream>>>(
+      (const bf16*)x, (const float*)ln_w, (const float*)ln_b, (bf16*)y, (float*)mean, (float*)rstd, rows, C, strip,
+      eps);
+  return rwkv_launch_status();
+}
+
+RWKV_EXPORT int rwkv_layer_norm_backward(const void* dy, const void* x, const void* mean, const void* rstd,
+                                         const void* ln_w, void* dx, void* partials, int rows, int C, int strip,
+                                         void* stream) {
+  if (C % 8 || C / 8 > 512 || strip <= 0) return RWKV_ERR_BAD_SHAPE;
+  layer_norm_bwd_kernel<<<(rows + strip - 1) / strip, threads_for(C), 0, (cudaStream_t)stream>>>(
+      (const bf16*)dy, (const bf16*)x, (const float*)mean, (const float*)rstd, (const float*)ln_w, (bf16*)dx,
+      (float*)partials, rows, C, strip);
+  return rwkv_launch_status();
+}

@@ -1,0 +1,89 @@
+"""ctypes binding of ``librwkvtune_b200.so``.
+
+The library exports plain C functions taking device pointers and a stream handle;
+this module loads it once, checks return codes and offers small helpers for passing
+``torch.Tensor`` storage.  Nothing here falls back to another implementation: if the
+library is absent a CUDA call raises ``NativeLibraryMissing``.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Optional
+
+import torch
+
+_LIB: Optional[ctypes.CDLL] = None
+_LIB_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "csrc", "librwkvtune_b200.so")
+
+
+class NativeLibraryMissing(RuntimeError):
+    pass
+
+
+class NativeCallError(RuntimeError):
+    pass
+
+
+_STATUS = {1: "bad shape", 2: "bad alignment", 3: "size beyond the supported maximum", 4: "not initialised",
+           5: "device-side wait timed out"}
+
+
+def lib_path() -> str:
+    return _LIB_PATH
+
+
+def available() -> bool:
+    return os.path.exists(_LIB_PATH)
+
+
+def lib() -> ctypes.CDLL:
+    global _LIB
+    if _LIB is None:
+        if not os.path.exists(_LIB_PATH):
+            raise NativeLibraryMissing(
+                f"{_LIB_PATH} not found: build it with `python -m rwkvtune_b200.csrc.build` "
+                "(CUDA tensors never fall back to a PyTorch implementation)")
+        _LIB = ctypes.CDLL(_LIB_PATH)
+    return _LIB
+
+
+def check(status: int, what: str) -> None:
+    if status == 0:
+        return
+    if status >= 1000:
+        code = status - 1000
+        try:
+            msg = torch.cuda.cudart().cudaGetErrorString(code)  # type: ignore[attr-defined]
+        except Exception:
+            msg = f"cudaError {code}"
+        raise NativeCallError(f"{what}: CUDA error {code} ({msg})")
+    raise NativeCallError(f"{what}: {_STATUS.get(status, f'status {status}')}")
+
+
+def ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
+    if t is None:
+        return ctypes.c_void_p(0)
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def call(name: str, *args) -> None:
+    fn = getattr(lib(), name)
+    fn.restype = ctypes.c_int
+    check(fn(*args), name)
+
+
+def i32(v: int) -> ctypes.c_int:
+    return ctypes.c_int(int(v))
+
+
+def i64(v: int) -> ctypes.c_longlong:
+    return ctypes.c_longlong(int(v))
+
+
+def f32(v: float) -> ctypes.c_float:
+    return ctypes.c_float(float(v))

@@ -1,0 +1,383 @@
+"""Autograd wrappers around the native sm_100a kernels.
+
+Each public function mirrors a function of :mod:`rwkvtune_b200.ops.reference`.
+Tensors handed to a kernel are made contiguous and bf16 where the kernel is bf16
+only; shapes are validated here so the kernels themselves stay branch-free.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _ext
+from . import reference as ref
+from ._ext import call, f32, i32, i64, ptr, stream
+
+BF16 = torch.bfloat16
+
+
+def _c(t: torch.Tensor, dtype=None) -> torch.Tensor:
+    if dtype is not None and t.dtype != dtype:
+        t = t.to(dtype)
+    return t if t.is_contiguous() else t.contiguous()
+
+
+# =============================================================================== WKV7
+class _WKV7(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, r, w, k, v, a, b, state, return_state: bool):
+        B, T, C = r.shape
+        H = C // 64
+        out_dtype = r.dtype
+        r, w, k, v, a, b = (_c(t, BF16) for t in (r, w, k, v, a, b))
+        s0 = None if state is None else _c(state, torch.float32)
+        need_grad = any(ctx.needs_input_grad[:7])
+        y = torch.empty(B, T, C, dtype=BF16, device=r.device)
+        NC = (T + 15) // 16
+        sa = torch.empty(B, T, C, dtype=torch.float32, device=r.device) if need_grad else None
+        ckpt = torch.empty(B, H, NC, 64, 64, dtype=torch.float32, device=r.device) if need_grad else None
+        s_final = torch.empty(B, H, 64, 64, dtype=torch.float32, device=r.device) if return_state else None
+        call("rwkv_wkv7_forward", ptr(r), ptr(w), ptr(k), ptr(v), ptr(a), ptr(b), ptr(s0), ptr(y), ptr(sa),
+             ptr(ckpt), ptr(s_final), i32(B), i32(T), i32(H), stream())
+        if need_grad:
+            ctx.save_for_backward(r, w, k, v, a, b, sa, ckpt)
+        ctx.has_state = state is not None
+        ctx.out_dtype = out_dtype
+        ctx.shape = (B, T, H)
+        y = y if out_dtype == BF16 else y.to(out_dtype)
+        if return_state:
+            return y, s_final
+        ctx.mark_non_differentiable()
+        return y, None
+
+    @staticmethod
+    def backward(ctx, dy, ds_final):
+        r, w, k, v, a, b, sa, ckpt = ctx.saved_tensors
+        B, T, H = ctx.shape
+        dy = _c(dy, BF16)
+        ds_T = None if ds_final is None else _c(ds_final, torch.float32)
+        grads = [torch.empty_like(r) for _ in range(6)]
+        ds0 = torch.empty(B, H, 64, 64, dtype=torch.float32, device=r.device) if ctx.has_state else None
+        call("rwkv_wkv7_backward", ptr(r), ptr(w), ptr(k), ptr(v), ptr(a), ptr(b), ptr(dy), ptr(sa), ptr(ckpt),
+             ptr(ds_T), *(ptr(g) for g in grads), ptr(ds0), i32(B), i32(T), i32(H), stream())
+        if ctx.out_dtype != BF16:
+            grads = [g.to(ctx.out_dtype) for g in grads]
+        return (*grads, ds0, None)
+
+
+def wkv7(r, w, k, v, a, b, head_size: int = 64, state: Optional[torch.Tensor] = None, return_state: bool = False):
+    if head_size != 64:
+        raise ValueError("the sm_100a WKV7 kernels are built for head_size 64")
+    if r.shape[-1] % 64:
+        raise ValueError("channel count must be a multiple of 64")
+    y, s = _WKV7.apply(r, w, k, v, a, b, state, return_state)
+    return y, s
+
+
+# =============================================================================== helpers
+def _strip_for(rows_per_batch: int, batch: int, target_ctas: int = 592) -> int:
+    """Time steps per CTA: enough CTAs to fill 148 SMs several times, at least 4 steps each."""
+    total = rows_per_batch * batch
+    strip = max(4, min(64, -(-total // target_ctas)))
+    return (strip + 3) // 4 * 4
+
+
+def _f32(t: torch.Tensor) -> torch.Tensor:
+    return _c(t.detach().reshape(-1), torch.float32)
+
+
+def _param_grad(partials: torch.Tensor, index: int, like: torch.Tensor) -> torch.Tensor:
+    return partials[:, index].sum(0).reshape(like.shape).to(like.dtype)
+
+
+# =============================================================================== LayerNorm / shift / mix
+class _LnShiftMix(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, ln_w, ln_b, mix, prev, eps):
+        B, T, C = x.shape
+        K = mix.shape[0]
+        xb = _c(x, BF16)
+        w32, b32, m32 = _f32(ln_w), _f32(ln_b), _c(mix.detach().reshape(K, C), torch.float32)
+        pv = None if prev is None else _c(prev, BF16)
+        outs = torch.empty(K, B, T, C, dtype=BF16, device=x.device)
+        last = torch.empty(B, C, dtype=BF16, device=x.device)
+        mean = torch.empty(B * T, dtype=torch.float32, device=x.device)
+        rstd = torch.empty_like(mean)
+        strip = _strip_for(T, B)
+        call("rwkv_ln_shift_mix_forward", ptr(xb), ptr(w32), ptr(b32), ptr(m32), ptr(pv), ptr(outs), ptr(last),
+             ptr(mean), ptr(rstd), i32(K), i32(B), i32(T), i32(C), i32(strip), f32(eps), stream())
+        ctx.save_for_backward(xb, mean, rstd, w32, b32, m32, pv)
+        ctx.meta = (B, T, C, K, strip, x.dtype, ln_w, ln_b, mix, prev is not None)
+        if x.dtype != BF16:
+            outs, last = outs.to(x.dtype), last.to(x.dtype)
+        return outs, last
+
+    @staticmethod
+    def backward(ctx, d_outs, d_last):
+        xb, mean, rstd, w32, b32, m32, pv = ctx.saved_tensors
+        B, T, C, K, strip, xdt, ln_w, ln_b, mix, has_prev = ctx.meta
+        dO = _c(d_outs, BF16)
+        dl = None if d_last is None else _c(d_last, BF16)
+        dx = torch.empty(B, T, C, dtype=BF16, device=xb.device)
+        dprev = torch.empty(B, C, dtype=torch.float32, device=xb.device) if has_prev else None
+        n_cta = B * (-(-T // strip))
+        partials = torch.empty(n_cta, K + 2, C, dtype=torch.float32, device=xb.device)
+        call("rwkv_ln_shift_mix_backward", ptr(dO), ptr(dl), ptr(xb), ptr(mean), ptr(rstd), ptr(w32), ptr(b32),
+             ptr(m32), ptr(pv), ptr(dx), ptr(dprev), ptr(partials), i32(K), i32(B), i32(T), i32(C), i32(strip),
+             stream())
+        sums = partials.sum(0)
+        dmix = sums[:K].reshape(mix.shape).to(mix.dtype)
+        dw = sums[K].reshape(ln_w.shape).to(ln_w.dtype)
+        db = sums[K + 1].reshape(ln_b.shape).to(ln_b.dtype)
+        return dx.to(xdt), dw, db, dmix, (dprev.to(xdt) if has_prev else None), None
+
+
+def ln_shift_mix(x, ln_w, ln_b, mix, prev=None, eps: float = ref.LAYERNORM_EPS):
+    K = mix.shape[0]
+    if K not in (1, 6) or x.shape[-1] % 64:
+        return ref.ln_shift_mix(x, ln_w, ln_b, mix, prev, eps)
+    return _LnShiftMix.apply(x, ln_w, ln_b, mix, prev, eps)
+
+
+class _LayerNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, b, eps):
+        C = x.shape[-1]
+        xb = _c(x, BF16).reshape(-1, C)
+        rows = xb.shape[0]
+        w32, b32 = _f32(w), _f32(b)
+        y = torch.empty_like(xb)
+        mean = torch.empty(rows, dtype=torch.float32, device=x.device)
+        rstd = torch.empty_like(mean)
+        strip = _strip_for(rows, 1)
+        call("rwkv_layer_norm_forward", ptr(xb), ptr(w32), ptr(b32), ptr(y), ptr(mean), ptr(rstd), i32(rows), i32(C),
+             i32(strip), f32(eps), stream())
+        ctx.save_for_backward(xb, mean, rstd, w32)
+        ctx.meta = (x.shape, x.dtype, strip, w, b)
+        return y.reshape(x.shape).to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, dy):
+        xb, mean, rstd, w32 = ctx.saved_tensors
+        shape, xdt, strip, w, b = ctx.meta
+        rows, C = xb.shape
+        dyb = _c(dy, BF16).reshape(rows, C)
+        dx = torch.empty_like(xb)
+        partials = torch.empty(-(-rows // strip), 2, C, dtype=torch.float32, device=xb.device)
+        call("rwkv_layer_norm_backward", ptr(dyb), ptr(xb), ptr(mean), ptr(rstd), ptr(w32), ptr(dx), ptr(partials),
+             i32(rows), i32(C), i32(strip), stream())
+        sums = partials.sum(0)
+        return dx.reshape(shape).to(xdt), sums[0].reshape(w.shape).to(w.dtype), sums[1].reshape(b.shape).to(b.dtype), None
+
+
+def layer_norm(x, weight, bias, eps: float = ref.LAYERNORM_EPS):
+    if x.shape[-1] % 8:
+        return ref.layer_norm(x, weight, bias, eps)
+    return _LayerNorm.apply(x, weight, bias, eps)
+
+
+# =============================================================================== time-mix prep / post
+class _TimemixPrep(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, k, v, v_first, w_lin, a_lin, v_lin, w0, a0, v0, k_k, k_a):
+        B, T, C = k.shape
+        dt = k.dtype
+        layer0 = v_first is None
+        kb, vb, wl, al = (_c(t, BF16) for t in (k, v, w_lin, a_lin))
+        vf = None if layer0 else _c(v_first, BF16)
+        vl = None if layer0 else _c(v_lin, BF16)
+        p = [_f32(w0), _f32(a0), None if layer0 else _f32(v0), _f32(k_k), _f32(k_a)]
+        outs = [torch.empty(B, T, C, dtype=BF16, device=k.device) for _ in range(5)]
+        w_o, k_o, v_o, an_o, b_o = outs
+        strip = _strip_for(T, B)
+        call("rwkv_timemix_prep_forward", ptr(kb), ptr(vb), ptr(vf), ptr(wl), ptr(al), ptr(vl), *(ptr(t) for t in p),
+             ptr(w_o), ptr(k_o), ptr(v_o), ptr(an_o), ptr(b_o), i32(B), i32(T), i32(C), i32(strip), stream())
+        if layer0:
+            v_o = vb
+        ctx.save_for_backward(kb, vb, vf, wl, al, vl, *p)
+        ctx.meta = (B, T, C, strip, dt, layer0, [t.shape for t in (w0, a0, k_k, k_a)], [t.dtype for t in (w0, a0, k_k, k_a)])
+        res = (w_o, k_o, v_o, an_o, b_o)
+        return tuple(t.to(dt) for t in res) if dt != BF16 else res
+
+    @staticmethod
+    def backward(ctx, gw, gk, gv, gan, gb):
+        kb, vb, vf, wl, al, vl, w0, a0, v0, k_k, k_a = ctx.saved_tensors
+        B, T, C, strip, dt, layer0, pshapes, pdtypes = ctx.meta
+        dev = kb.device
+        zero = None
+
+        def g_(t):
+            nonlocal zero
+            if t is None:
+                if zero is None:
+                    zero = torch.zeros(B, T, C, dtype=BF16, device=dev)
+                return zero
+            return _c(t, BF16)
+
+        gw, gk, gv, gan, gb = (g_(t) for t in (gw, gk, gv, gan, gb))
+        dk, dv, dwl, dal = (torch.empty(B, T, C, dtype=BF16, device=dev) for _ in range(4))
+        dvf = None if layer0 else torch.empty(B, T, C, dtype=BF16, device=dev)
+        dvl = None if layer0 else torch.empty(B, T, C, dtype=BF16, device=dev)
+        n_cta = B * (-(-T // strip))
+        partials = torch.empty(n_cta, 5, C, dtype=torch.float32, device=dev)
+        call("rwkv_timemix_prep_backward", ptr(gw), ptr(gk), ptr(gv), ptr(gan), ptr(gb), ptr(kb), ptr(vb), ptr(vf),
+             ptr(wl), ptr(al), ptr(vl), ptr(w0), ptr(a0), ptr(v0), ptr(k_k), ptr(k_a), ptr(dk), ptr(dv), ptr(dvf),
+             ptr(dwl), ptr(dal), ptr(dvl), ptr(partials), i32(B), i32(T), i32(C), i32(strip), stream())
+        s = partials.sum(0)
+        cast = (lambda t: t.to(dt)) if dt != BF16 else (lambda t: t)
+        dw0 = s[0].reshape(pshapes[0]).to(pdtypes[0])
+        da0 = s[1].reshape(pshapes[1]).to(pdtypes[1])
+        dv0 = None if layer0 else s[2].reshape(pshapes[0]).to(pdtypes[0])
+        dkk = s[3].reshape(pshapes[2]).to(pdtypes[2])
+        dka = s[4].reshape(pshapes[3]).to(pdtypes[3])
+        return (cast(dk), cast(dv), None if layer0 else cast(dvf), cast(dwl), cast(dal),
+                None if layer0 else cast(dvl), dw0, da0, dv0, dkk, dka)
+
+
+def timemix_prep(k, v, v_first, w_lin, a_lin, v_lin, w0, a0, v0, k_k, k_a, head_size: int = 64):
+    if head_size != 64 or k.shape[-1] % 64:
+        return ref.timemix_prep(k, v, v_first, w_lin, a_lin, v_lin, w0, a0, v0, k_k, k_a, head_size)
+    return _TimemixPrep.apply(k, v, v_first, w_lin, a_lin, v_lin, w0, a0, v0, k_k, k_a)
+
+
+class _GnBonusGate(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, y, r, k, v, g, gn_w, gn_b, r_k, eps):
+        B, T, C = y.shape
+        dt = y.dtype
+        yb, rb, kb, vb, gb_ = (_c(t, BF16) for t in (y, r, k, v, g))
+        p = [_f32(gn_w), _f32(gn_b), _f32(r_k)]
+        z = torch.empty(B, T, C, dtype=BF16, device=y.device)
+        strip = _strip_for(T, B)
+        call("rwkv_gn_bonus_gate_forward", ptr(yb), ptr(rb), ptr(kb), ptr(vb), ptr(gb_), *(ptr(t) for t in p), ptr(z),
+             i32(B), i32(T), i32(C), i32(strip), f32(eps), stream())
+        ctx.save_for_backward(yb, rb, kb, vb, gb_, *p)
+        ctx.meta = (B, T, C, strip, dt, eps, (gn_w.shape, gn_b.shape, r_k.shape), (gn_w.dtype, gn_b.dtype, r_k.dtype))
+        return z.to(dt)
+
+    @staticmethod
+    def backward(ctx, dz):
+        yb, rb, kb, vb, gb_, gw, gb, rk = ctx.saved_tensors
+        B, T, C, strip, dt, eps, shp, dts = ctx.meta
+        dev = yb.device
+        dzb = _c(dz, BF16)
+        dy, dr, dk, dv, dg = (torch.empty(B, T, C, dtype=BF16, device=dev) for _ in range(5))
+        n_cta = B * (-(-T // strip))
+        partials = torch.empty(n_cta, 3, C, dtype=torch.float32, device=dev)
+        call("rwkv_gn_bonus_gate_backward", ptr(dzb), ptr(yb), ptr(rb), ptr(kb), ptr(vb), ptr(gb_), ptr(gw), ptr(gb),
+             ptr(rk), ptr(dy), ptr(dr), ptr(dk), ptr(dv), ptr(dg), ptr(partials), i32(B), i32(T), i32(C), i32(strip),
+             f32(eps), stream())
+        s = partials.sum(0)
+        cast = (lambda t: t.to(dt)) if dt != BF16 else (lambda t: t)
+        return (cast(dy), cast(dr), cast(dk), cast(dv), cast(dg), s[0].reshape(shp[0]).to(dts[0]),
+                s[1].reshape(shp[1]).to(dts[1]), s[2].reshape(shp[2]).to(dts[2]), None)
+
+
+def gn_bonus_gate(y, r, k, v, g, gn_w, gn_b, r_k, head_size: int = 64, eps: float = ref.GROUPNORM_EPS):
+    if head_size != 64 or y.shape[-1] % 64:
+        return ref.gn_bonus_gate(y, r, k, v, g, gn_w, gn_b, r_k, head_size, eps)
+    return _GnBonusGate.apply(y, r, k, v, g, gn_w, gn_b, r_k, eps)
+
+
+class _ReluSq(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        xb = _c(x, BF16)
+        y = torch.empty_like(xb)
+        call("rwkv_relu_sq_forward", ptr(xb), ptr(y), i64(xb.numel()), stream())
+        ctx.save_for_backward(xb)
+        ctx.dt = x.dtype
+        return y.to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (xb,) = ctx.saved_tensors
+        dyb = _c(dy, BF16)
+        dx = torch.empty_like(xb)
+        call("rwkv_relu_sq_backward", ptr(xb), ptr(dyb), ptr(dx), i64(xb.numel()), stream())
+        return dx.to(ctx.dt)
+
+
+def relu_squared(x):
+    if x.numel() % 8:
+        return ref.relu_squared(x)
+    return _ReluSq.apply(x)
+
+
+# =============================================================================== GEMMs
+def linear(x, weight):
+    from . import gemm
+
+    return gemm.linear(x, weight)
+
+
+def matmul(x, w):
+    from . import gemm
+
+    return gemm.matmul(x, w)
+
+
+# =============================================================================== head + loss
+class _LinearCrossEntropy(torch.autograd.Function):
+    """Vocabulary head, cross-entropy (mean over targets != ignore_index) and L2Wrap without ever
+    holding the ``[M, V]`` logits: rows are processed in slabs, and because the loss is a scalar the
+    gradients w.r.t. ``x`` and ``weight`` are produced during the forward sweep."""
+
+    SLAB = 4096
+
+    @staticmethod
+    def forward(ctx, x, weight, labels, l2wrap, ignore_index, l2wrap_tokens):
+        from . import gemm
+
+        M, C = x.shape
+        V = weight.shape[0]
+        valid = labels != ignore_index
+        n_valid = valid.sum().clamp(min=1).float()
+        factor = ref.L2WRAP_FACTOR / float(l2wrap_tokens if l2wrap_tokens is not None else M)
+        need_x, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        dx = torch.empty_like(x) if need_x else None
+        dw = torch.zeros(V, C, dtype=torch.float32, device=x.device) if need_w else None
+        loss_sum = torch.zeros((), dtype=torch.float32, device=x.device)
+        safe_labels = labels.clamp(min=0)
+        for s in range(0, M, _LinearCrossEntropy.SLAB):
+            e = min(M, s + _LinearCrossEntropy.SLAB)
+            xs = x[s:e]
+            logits = gemm.mm_nt(xs, weight).float()
+            mx, am = logits.max(dim=-1, keepdim=True)
+            ex = torch.exp(logits - mx)
+            den = ex.sum(-1, keepdim=True)
+            lse = (mx + den.log()).squeeze(-1)
+            tgt = logits.gather(-1, safe_labels[s:e, None]).squeeze(-1)
+            vs = valid[s:e]
+            loss_sum += ((lse - tgt) * vs).sum()
+            if need_x or need_w:
+                scale = (vs.float() / n_valid)[:, None]
+                grad = ex / den * scale
+                grad.scatter_add_(-1, safe_labels[s:e, None], -scale)
+                if l2wrap:
+                    grad.scatter_add_(-1, am, mx * factor)
+                grad = grad.to(x.dtype)
+                if need_x:
+                    dx[s:e] = gemm.mm_nn(grad, weight)
+                if need_w:
+                    dw += gemm.mm_tn(grad, xs).float()
+        ctx.save_for_backward(dx, dw)
+        ctx.wdtype = weight.dtype
+        return loss_sum / n_valid
+
+    @staticmethod
+    def backward(ctx, g):
+        dx, dw = ctx.saved_tensors
+        return (None if dx is None else dx * g.to(dx.dtype), None if dw is None else (dw * g).to(ctx.wdtype),
+                None, None, None, None)
+
+
+def linear_cross_entropy(x, weight, labels, l2wrap=True, ignore_index=-100, l2wrap_tokens=None):
+    return _LinearCrossEntropy.apply(x, weight, labels, l2wrap, ignore_index, l2wrap_tokens)
+
+
+def linear_logprob_entropy(x, weight, targets, temperature: float = 1.0, with_entropy: bool = True):
+    from . import loss_kernels
+
+    return loss_kernels.linear_logprob_entropy(x, weight, targets, temperature, with_entropy)

@@ -1,0 +1,99 @@
+"""bf16 GEMM front-end.
+
+Three layouts cover everything the network needs (``x`` is always ``[M, K]`` row-major):
+
+* ``mm_nt(x, w)``  = ``x @ w^T``  with ``w [N, K]``  (``nn.Linear`` forward, dgrad of the low-rank maps)
+* ``mm_nn(x, w)``  = ``x @ w``    with ``w [K, N]``  (low-rank maps forward, ``nn.Linear`` dgrad)
+* ``mm_tn(a, b)``  = ``a^T @ b``  with ``a [M, N1]``, ``b [M, N2]``  (every weight gradient)
+
+``linear`` / ``matmul`` wrap them in autograd.  The tcgen05 kernels of
+``rwkvtune_b200/csrc/gemm_tcgen05.cu`` serve the shapes they support (see ``native_ok``);
+other shapes go to the library GEMM.
+"""
+from __future__ import annotations
+
+import torch
+
+_USE_NATIVE = True
+
+
+def set_native(enabled: bool) -> None:
+    global _USE_NATIVE
+    _USE_NATIVE = bool(enabled)
+
+
+def _native():
+    if not _USE_NATIVE:
+        return None
+    try:
+        from . import gemm_native
+    except ImportError:
+        return None
+    return gemm_native
+
+
+def mm_nt(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    n = _native()
+    if n is not None and n.native_ok(x, w, "nt"):
+        return n.mm_nt(x, w)
+    return x @ w.t()
+
+
+def mm_nn(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    n = _native()
+    if n is not None and n.native_ok(x, w, "nn"):
+        return n.mm_nn(x, w)
+    return x @ w
+
+
+def mm_tn(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    n = _native()
+    if n is not None and n.native_ok(a, b, "tn"):
+        return n.mm_tn(a, b)
+    return a.t() @ b
+
+
+class _Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w):
+        ctx.save_for_backward(x, w)
+        x2 = x.reshape(-1, x.shape[-1])
+        return mm_nt(x2, w).reshape(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = mm_nn(dy2, w).reshape(x.shape)
+        if ctx.needs_input_grad[1]:
+            dw = mm_tn(dy2, x.reshape(-1, x.shape[-1]))
+        return dx, dw
+
+
+class _MatMul(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w):
+        ctx.save_for_backward(x, w)
+        x2 = x.reshape(-1, x.shape[-1])
+        return mm_nn(x2, w).reshape(*x.shape[:-1], w.shape[1])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = mm_nt(dy2, w).reshape(x.shape)
+        if ctx.needs_input_grad[1]:
+            dw = mm_tn(x.reshape(-1, x.shape[-1]), dy2)
+        return dx, dw
+
+
+def linear(x, weight):
+    return _Linear.apply(x, weight)
+
+
+def matmul(x, w):
+    return _MatMul.apply(x, w)

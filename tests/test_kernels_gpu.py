@@ -1,0 +1,207 @@
+"""Each sm_100a kernel against the fp32 PyTorch statement of the same operator."""
+import pytest
+import torch
+
+from rwkvtune_b200 import ops
+from rwkvtune_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+BF = torch.bfloat16
+
+
+def _close(a, b, rtol, atol, name=""):
+    a, b = a.float(), b.float()
+    err = (a - b).abs()
+    tol = atol + rtol * b.abs()
+    frac_bad = (err > tol).float().mean().item()
+    assert frac_bad < 2e-3, f"{name}: {frac_bad:.4f} of elements off, max err {err.max().item():.4g}, ref max {b.abs().max().item():.4g}"
+
+
+def _wkv_inputs(B, T, H, seed=0, dev="cuda"):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    C = H * 64
+    rnd = lambda s=1.0: (torch.randn(B, T, C, generator=g) * s)
+    r, k, v = rnd(), rnd(), rnd()
+    w = -torch.nn.functional.softplus(-(rnd(2.0) - 1.0)) - 0.5
+    kk = torch.nn.functional.normalize(rnd().view(B, T, H, 64), dim=-1).view(B, T, C)
+    a = torch.sigmoid(rnd())
+    return [t.to(dev).to(BF) for t in (r, w, k, v, -kk, kk * a)]
+
+
+@pytest.mark.parametrize("B,T,H,with_state", [(2, 64, 2, False), (1, 37, 3, True), (2, 128, 1, True)])
+def test_wkv7_forward_backward(B, T, H, with_state):
+    ins = _wkv_inputs(B, T, H)
+    s0 = (torch.randn(B, H, 64, 64, device="cuda") * 0.1) if with_state else None
+    ins_k = [t.clone().requires_grad_(True) for t in ins]
+    ins_r = [t.float().clone().requires_grad_(True) for t in ins]
+    s0_k = s0.clone().requires_grad_(True) if with_state else None
+    s0_r = s0.clone().requires_grad_(True) if with_state else None
+    y, sT = ops.wkv7(*ins_k, 64, state=s0_k, return_state=True)
+    y_ref, sT_ref = ref.wkv7(*ins_r, 64, s0_r)
+    _close(y, y_ref, 2e-2, 2e-2, "y")
+    _close(sT, sT_ref, 1e-3, 1e-3, "final state")
+    gy = torch.randn_like(y_ref)
+    gs = torch.randn_like(sT_ref) * 0.1
+    (y.float() * gy).sum().add((sT * gs).sum()).backward()
+    (y_ref * gy).sum().add((sT_ref * gs).sum()).backward()
+    for name, a, b in zip("rwkvab", ins_k, ins_r):
+        _close(a.grad, b.grad, 3e-2, 3e-2 * b.grad.abs().mean().item() + 1e-3, f"d{name}")
+    if with_state:
+        _close(s0_k.grad, s0_r.grad, 3e-2, 3e-2 * s0_r.grad.abs().mean().item() + 1e-3, "ds0")
+
+
+def test_wkv7_chunk_carry_equals_full():
+    ins = _wkv_inputs(1, 96, 2, seed=3)
+    y_full, s_full = ops.wkv7(*ins, 64, return_state=True)
+    y1, s1 = ops.wkv7(*[t[:, :40] for t in ins], 64, return_state=True)
+    y2, s2 = ops.wkv7(*[t[:, 40:] for t in ins], 64, state=s1, return_state=True)
+    assert torch.equal(torch.cat([y1, y2], 1), y_full)
+    assert torch.allclose(s2, s_full, atol=1e-6)
+
+
+@pytest.mark.parametrize("K,B,T,C,with_prev", [(6, 2, 50, 256, False), (1, 3, 17, 512, True), (6, 1, 130, 768, True)])
+def test_ln_shift_mix(K, B, T, C, with_prev):
+    torch.manual_seed(0)
+    x = torch.randn(B, T, C, device="cuda").to(BF)
+    w = (1 + 0.1 * torch.randn(C, device="cuda"))
+    b = 0.1 * torch.randn(C, device="cuda")
+    mix = torch.rand(K, C, device="cuda")
+    prev = torch.randn(B, C, device="cuda").to(BF) if with_prev else None
+    leaves_k = [t.clone().requires_grad_(True) for t in (x, w, b, mix)] + ([prev.clone().requires_grad_(True)] if with_prev else [None])
+    leaves_r = [t.float().clone().requires_grad_(True) for t in (x, w, b, mix)] + ([prev.float().clone().requires_grad_(True)] if with_prev else [None])
+    o, last = ops.ln_shift_mix(*leaves_k)
+    o_r, last_r = ref.ln_shift_mix(*leaves_r)
+    _close(o, o_r, 1e-2, 2e-2, "outs")
+    _close(last, last_r, 1e-2, 2e-2, "last")
+    go = torch.randn_like(o_r)
+    gl = torch.randn_like(last_r)
+    (o.float() * go).sum().add((last.float() * gl).sum()).backward()
+    (o_r * go).sum().add((last_r * gl).sum()).backward()
+    names = ["dx", "dln_w", "dln_b", "dmix", "dprev"]
+    for n, a, r_ in zip(names, leaves_k, leaves_r):
+        if a is None:
+            continue
+        scale = r_.grad.abs().mean().item()
+        _close(a.grad, r_.grad, 3e-2, 3e-2 * scale + 1e-3, n)
+
+
+def test_layer_norm():
+    torch.manual_seed(0)
+    x = torch.randn(70, 512, device="cuda").to(BF)
+    w = 1 + 0.1 * torch.randn(512, device="cuda")
+    b = 0.1 * torch.randn(512, device="cuda")
+    lk = [t.clone().requires_grad_(True) for t in (x, w, b)]
+    lr = [t.float().clone().requires_grad_(True) for t in (x, w, b)]
+    y = ops.layer_norm(*lk)
+    y_r = ref.layer_norm(*lr)
+    _close(y, y_r, 1e-2, 1e-2, "y")
+    g = torch.randn_like(y_r)
+    (y.float() * g).sum().backward()
+    (y_r * g).sum().backward()
+    for n, a, r_ in zip(["dx", "dw", "db"], lk, lr):
+        _close(a.grad, r_.grad, 3e-2, 3e-2 * r_.grad.abs().mean().item() + 1e-3, n)
+
+
+@pytest.mark.parametrize("layer0", [True, False])
+def test_timemix_prep(layer0):
+    torch.manual_seed(1)
+    B, T, C = 2, 33, 256
+    big = lambda: torch.randn(B, T, C, device="cuda").to(BF)
+    par = lambda s=1.0: (torch.randn(1, 1, C, device="cuda") * s)
+    k, v, vf, wl, al, vl = big(), big(), big(), big(), big(), big()
+    w0, a0, v0, kk, ka = par(), par(), par(), par(0.3) + 0.7, par(0.1) + 1.0
+    args = [k, v, None if layer0 else vf, wl, al, None if layer0 else vl, w0, a0, None if layer0 else v0, kk, ka]
+    mk = lambda f: [None if t is None else f(t).clone().requires_grad_(True) for t in args]
+    ak, ar = mk(lambda t: t), mk(lambda t: t.float())
+    outs = ops.timemix_prep(*ak, 64)
+    outs_r = ref.timemix_prep(*ar, 64)
+    gs = [torch.randn_like(o) for o in outs_r]
+    for n, o, o_r in zip(["w", "k", "v", "an", "b"], outs, outs_r):
+        _close(o, o_r, 1e-2, 1e-2, n)
+    sum((o.float() * g).sum() for o, g in zip(outs, gs)).backward()
+    sum((o * g).sum() for o, g in zip(outs_r, gs)).backward()
+    names = ["dk", "dv", "dvfirst", "dwlin", "dalin", "dvlin", "dw0", "da0", "dv0", "dk_k", "dk_a"]
+    for n, a, r_ in zip(names, ak, ar):
+        if a is None:
+            continue
+        _close(a.grad, r_.grad, 3e-2, 3e-2 * r_.grad.abs().mean().item() + 1e-3, n)
+
+
+def test_gn_bonus_gate():
+    torch.manual_seed(2)
+    B, T, C = 2, 21, 256
+    big = lambda: torch.randn(B, T, C, device="cuda").to(BF)
+    y, r, k, v, g = big(), big(), big(), big(), big()
+    gw = 1 + 0.1 * torch.randn(C, device="cuda")
+    gb = 0.1 * torch.randn(C, device="cuda")
+    rk = 0.1 * torch.randn(C // 64, 64, device="cuda")
+    args = [y, r, k, v, g, gw, gb, rk]
+    ak = [t.clone().requires_grad_(True) for t in args]
+    ar = [t.float().clone().requires_grad_(True) for t in args]
+    z = ops.gn_bonus_gate(*ak, 64)
+    z_r = ref.gn_bonus_gate(*ar, 64)
+    _close(z, z_r, 1e-2, 2e-2, "z")
+    gz = torch.randn_like(z_r)
+    (z.float() * gz).sum().backward()
+    (z_r * gz).sum().backward()
+    for n, a, r_ in zip(["dy", "dr", "dk", "dv", "dg", "dgn_w", "dgn_b", "dr_k"], ak, ar):
+        _close(a.grad, r_.grad, 3e-2, 3e-2 * r_.grad.abs().mean().item() + 1e-3, n)
+
+
+def test_relu_squared():
+    x = torch.randn(4, 33, 256, device="cuda").to(BF).requires_grad_(True)
+    y = ops.relu_squared(x)
+    xr = x.detach().float().requires_grad_(True)
+    yr = ref.relu_squared(xr)
+    _close(y, yr, 1e-2, 1e-3)
+    g = torch.randn_like(yr)
+    (y.float() * g).sum().backward()
+    (yr * g).sum().backward()
+    _close(x.grad, xr.grad, 2e-2, 1e-2)
+
+
+def test_linear_cross_entropy_matches_reference():
+    torch.manual_seed(0)
+    M, C, V = 300, 128, 1024
+    x = (torch.randn(M, C, device="cuda") * 0.5).to(BF)
+    w = (torch.randn(V, C, device="cuda") * 0.1).to(BF)
+    labels = torch.randint(0, V, (M,), device="cuda")
+    labels[:40] = -100
+    xk, wk = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    xr, wr = x.float().clone().requires_grad_(True), w.float().clone().requires_grad_(True)
+    loss = ops.linear_cross_entropy(xk, wk, labels, True, -100, M)
+    loss_r = ref.linear_cross_entropy(xr, wr, labels, True, -100, M)
+    assert abs(loss.item() - loss_r.item()) < 2e-2
+    loss.backward(); loss_r.backward()
+    _close(xk.grad, xr.grad, 5e-2, 5e-2 * xr.grad.abs().mean().item() + 1e-5, "dx")
+    _close(wk.grad, wr.grad, 5e-2, 5e-2 * wr.grad.abs().mean().item() + 1e-5, "dw")
+
+
+def test_model_step_on_gpu_matches_cpu_reference():
+    from rwkvtune_b200.models import RWKVConfig, RWKV7Model
+    torch.manual_seed(0)
+    cfg = RWKVConfig(n_layer=2, n_embd=256, vocab_size=1024, dim_att_lora=32, dim_gate_lora=64, dim_mv_lora=32)
+    m = RWKV7Model(cfg)
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            if n.endswith(("output.weight", "ffn.value.weight", "w1", "a1", "v1", "g1")):
+                p.copy_(torch.randn_like(p) * 0.05)
+    idx = torch.randint(0, 1024, (2, 48))
+    labels = torch.randint(0, 1024, (2, 48))
+    loss_cpu = m.loss(idx, labels)
+    loss_cpu.backward()
+    g_cpu = {n: p.grad.clone() for n, p in m.named_parameters()}
+    m.zero_grad()
+    mg = RWKV7Model(cfg)
+    mg.load_state_dict(m.state_dict())
+    mg = mg.cuda().to(BF)
+    loss_gpu = mg.loss(idx.cuda(), labels.cuda())
+    loss_gpu.backward()
+    assert abs(loss_gpu.item() - loss_cpu.item()) < 5e-2, (loss_gpu.item(), loss_cpu.item())
+    bad = []
+    for n, p in mg.named_parameters():
+        a, b = p.grad.float().cpu(), g_cpu[n]
+        cos = torch.nn.functional.cosine_similarity(a.flatten(), b.flatten(), dim=0).item()
+        if cos < 0.98 and b.abs().max() > 1e-6:
+            bad.append((n, cos))
+    assert not bad, bad
