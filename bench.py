@@ -1,0 +1,181 @@
+"""Headline benchmark: RWKV-7 pretraining throughput (tokens/s over the whole job).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--model 1.5b]
+
+N > 1 is launched by ``python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N``;
+one rank per GPU, ZeRO-2.  Synthetic uniform-random tokens, random-init weights, bf16.
+Timing: W untimed steps, then K steps between barrier + synchronize, CUDA events on the
+launching stream, maximum over ranks.  The ``e2e`` figure repeats the measurement through the
+host-side call a trainer makes per batch (pinned host tensors in, loss read back each step).
+Rank 0 prints one JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+MODELS = {
+    "0.1b": dict(n_layer=12, n_embd=768, dim_att_lora=64, dim_gate_lora=128, dim_mv_lora=32),
+    "0.4b": dict(n_layer=24, n_embd=1024, dim_att_lora=64, dim_gate_lora=128, dim_mv_lora=32),
+    "1.5b": dict(n_layer=24, n_embd=2048, dim_att_lora=96, dim_gate_lora=256, dim_mv_lora=64),
+    "2.9b": dict(n_layer=32, n_embd=2560, dim_att_lora=96, dim_gate_lora=320, dim_mv_lora=64),
+}
+# published by the reference for 1.5B SFT on two unnamed GPUs: 2.3 it/s x 2 samples x 1024 tokens x 2 GPUs
+PUBLISHED_TOK_S = {"1.5b": 9420.8, "0.1b": 68812.8, "0.4b": 28672.0, "2.9b": 3072.0}
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of this rank's GPU with nvidia-smi while the timed region runs."""
+
+    def __init__(self, index: int):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
+        self._stop_evt = threading.Event()
+
+    def run(self):
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        while not self._stop_evt.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-i",
+                                      str(self.index)], capture_output=True, text=True, timeout=5).stdout.strip()
+                f = [x.strip() for x in out.split(",")]
+                self.samples.append(float(f[0]))
+                self.max_mhz = float(f[1])
+                for n, v in zip(names, f[2:]):
+                    if v.lower().startswith("active"):
+                        self.reasons.add(n)
+            except Exception:
+                pass
+            self._stop_evt.wait(0.2)
+
+    def stop(self):
+        self._stop_evt.set()
+        self.join(timeout=6)
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s)}
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=8)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="1.5b", choices=sorted(MODELS))
+    ap.add_argument("--ctx-len", type=int, default=4096)
+    ap.add_argument("--micro-bsz", type=int, default=8)
+    ap.add_argument("--grad-cp", type=int, default=1)
+    ap.add_argument("--transport", default=os.environ.get("RWKVTUNE_TRANSPORT", "nccl"))
+    return ap.parse_args()
+
+
+def run_ours(a):
+    import torch
+    import torch.distributed as dist
+
+    from rwkvtune_b200.engine import EngineConfig, TrainEngine
+    from rwkvtune_b200.models import RWKVConfig, RWKV7Model
+    from rwkvtune_b200.ops import _ext
+    from rwkvtune_b200.parallel import init_distributed
+
+    ctx = init_distributed("gpu")
+    if ctx.world_size != a.gpus:
+        raise SystemExit(f"--gpus {a.gpus} but WORLD_SIZE={ctx.world_size}: launch with torch.distributed.run")
+    torch.manual_seed(1234 + ctx.rank)
+    cfg = RWKVConfig(vocab_size=65536, ctx_len=a.ctx_len, **MODELS[a.model])
+    torch.manual_seed(1234)   # identical weights on every rank
+    with torch.device(ctx.device):
+        model = RWKV7Model(cfg)
+    strategy = "deepspeed_stage_2" if ctx.world_size > 1 else "auto"
+    eng = TrainEngine(model, EngineConfig(lr_init=3e-4, weight_decay=0.01, grad_clip=1.0, strategy=strategy,
+                                          precision="bf16", grad_cp=a.grad_cp, transport=a.transport), ctx)
+    B, T, V = a.micro_bsz, a.ctx_len, cfg.vocab_size
+    g = torch.Generator().manual_seed(99 + ctx.rank)
+    n_batches = a.warmup + a.steps
+    host_ids = [torch.randint(0, V, (B, T), generator=g).pin_memory() for _ in range(n_batches)]
+    host_lab = [torch.randint(0, V, (B, T), generator=g).pin_memory() for _ in range(n_batches)]
+    dev_ids = [t.to(ctx.device) for t in host_ids]
+    dev_lab = [t.to(ctx.device) for t in host_lab]
+
+    def sync():
+        if ctx.world_size > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-timed arm: inputs already resident
+    for i in range(a.warmup):
+        eng.train_step(dev_ids[i], dev_lab[i], 3e-4)
+    sampler = ClockSampler(ctx.local_rank)
+    sync()
+    sampler.start()
+    launches0 = _ext.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(a.warmup, n_batches):
+        loss = eng.train_step(dev_ids[i], dev_lab[i], 3e-4)
+    e1.record()
+    sync()
+    clocks = sampler.stop()
+    launches = _ext.launch_count() - launches0
+    ms = e0.elapsed_time(e1)
+    final_loss = float(loss)
+
+    # ---- end-to-end arm: pinned host inputs copied every step, loss read back every step
+    sync()
+    t0 = time.perf_counter()
+    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2.record()
+    for i in range(a.warmup, n_batches):
+        eng.train_step_from_host(host_ids[i], host_lab[i], 3e-4)
+    e3.record()
+    sync()
+    ms_e2e = max(e2.elapsed_time(e3), (time.perf_counter() - t0) * 1e3)
+
+    t = torch.tensor([ms, ms_e2e], device=ctx.device, dtype=torch.float64)
+    if ctx.world_size > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, ms_e2e = float(t[0]), float(t[1])
+    tokens = B * T * a.steps * ctx.world_size
+    value = tokens / (ms / 1e3)
+    if ctx.is_main:
+        print(json.dumps({
+            "metric": "train_tokens_per_sec", "value": value, "unit": "tokens/s", "n_gpus": ctx.world_size,
+            "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms / a.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": value / PUBLISHED_TOK_S[a.model], "dtype": "bf16", "data": "synthetic",
+            "impl": "ours", "final_loss": final_loss,
+            "config": {"model": f"rwkv7-{a.model}", "global_batch": B * ctx.world_size, "seq_len": T,
+                       "parallelism": f"zero2-dp{ctx.world_size}" if ctx.world_size > 1 else "single",
+                       "grad_cp": a.grad_cp, "transport": a.transport, "optimizer": "AdamW fp32 master, clip 1.0",
+                       "l2_flush": "per-step activations and weights (>3 GB) exceed the 126 MB L2"},
+            "clocks": clocks,
+            "e2e": {"value": tokens / (ms_e2e / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": 2 * B * T * 8,
+                    "d2h_bytes_per_step": 4},
+            "gpu_launches": launches,
+        }))
+    if ctx.world_size > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    a = parse()
+    if a.impl == "reference":
+        from baseline.run_reference import run_reference
+
+        run_reference(a)
+    else:
+        run_ours(a)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,139 @@
+"""Training engine: owns the device copy of the model, the flat parameter space, the sharded
+optimiser and one training step (forward, fused loss, backward, reduce, clip, AdamW, publish).
+
+It replaces ``lightning.Trainer`` + the DeepSpeed/DDP strategy objects that the reference's
+trainers construct (``rwkvtune/training/sft_trainer.py:369-485``) and the ``training_step`` bodies
+of its Lightning modules (``rwkvtune/training/lightning_module.py:175-206``,
+``rwkvtune/training/lightning_module_infctx.py:213-417``).
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass
+from typing import Callable, Dict, Optional, Sequence
+
+import torch
+
+from ..models.rwkv7.model_infctx import as_infctx
+from ..parallel.bootstrap import DistContext
+from ..parallel.flat import FlatParamSpace, build_param_groups
+from ..parallel.zero import ZeroOptimizer
+
+STRATEGY_STAGE = {"auto": 0, "ddp": 0, "single": 0, "deepspeed_stage_1": 1, "deepspeed_stage_2": 2,
+                  "deepspeed_stage_2_offload": 2, "deepspeed_stage_3": 3, "deepspeed_stage_3_offload": 3}
+
+
+def resolve_stage(strategy: str) -> int:
+    if strategy not in STRATEGY_STAGE:
+        raise ValueError(f"unknown strategy {strategy!r}; expected one of {sorted(STRATEGY_STAGE)}")
+    return STRATEGY_STAGE[strategy]
+
+
+@dataclass
+class EngineConfig:
+    lr_init: float = 3e-4
+    beta1: float = 0.9
+    beta2: float = 0.99
+    adam_eps: float = 1e-8
+    weight_decay: float = 0.0
+    grad_clip: float = 1.0
+    accumulate_grad_batches: int = 1
+    strategy: str = "auto"
+    precision: str = "bf16"
+    grad_cp: int = 0
+    lr_2x_patterns: Sequence[str] = ()
+    train_type: str = "normal"
+    chunk_ctx: int = 512
+    truncated_bptt: bool = True
+    transport: str = "nccl"
+    l2wrap: bool = True
+
+
+class TrainEngine:
+    def __init__(self, model: torch.nn.Module, cfg: EngineConfig, ctx: DistContext):
+        self.cfg, self.ctx = cfg, ctx
+        dtype = {"bf16": torch.bfloat16, "fp16": torch.bfloat16, "fp32": torch.float32}[cfg.precision]
+        if ctx.device.type == "cpu":
+            dtype = torch.float32
+        self.model = model.to(device=ctx.device, dtype=dtype)
+        self.model.config.grad_cp = cfg.grad_cp
+        if cfg.train_type == "infctx":
+            as_infctx(self.model)
+        self.model.train()
+        stage = resolve_stage(cfg.strategy)
+        groups = build_param_groups(self.model.named_parameters(), cfg.weight_decay, cfg.lr_2x_patterns)
+        if not groups:
+            raise RuntimeError("the model has no trainable parameters")
+        self.space = FlatParamSpace(groups, ctx.world_size, dtype, ctx.device)
+        self.stage = stage
+        self.opt = ZeroOptimizer(self.space, ctx, min(stage, 2), (cfg.beta1, cfg.beta2), cfg.adam_eps, cfg.grad_clip,
+                                 cfg.transport)
+        self.micro_step = 0
+        self.optimizer_steps = 0
+        self.tokens_seen = 0
+
+    # ------------------------------------------------------------------ losses
+    def _loss_normal(self, idx: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
+        return self.model.loss(idx, labels, l2wrap=self.cfg.l2wrap)
+
+    def _step_infctx(self, idx: torch.Tensor, labels: torch.Tensor, scale: float) -> torch.Tensor:
+        """Chunked back-propagation through time.  Truncated mode back-propagates each chunk and
+        detaches the carried state; full mode keeps the graph and back-propagates once
+        (``rwkvtune/training/lightning_module_infctx.py:213-417``)."""
+        cfg, m = self.cfg, self.model
+        B, T = idx.shape
+        C, L = m.config.n_embd, m.config.n_layer
+        H, N = m.config.dim_att // m.config.head_size_a, m.config.head_size_a
+        chunk = cfg.chunk_ctx
+        n_chunks = (T + chunk - 1) // chunk
+        shift = torch.zeros(L, 2, B, C, device=idx.device, dtype=m.dtype)
+        wkv = torch.zeros(L, B, H, N, N, device=idx.device, dtype=torch.float32)
+        total = torch.zeros((), device=idx.device, dtype=torch.float32)
+        pending = []
+        for i in range(n_chunks):
+            ids_c, lab_c = idx[:, i * chunk:(i + 1) * chunk], labels[:, i * chunk:(i + 1) * chunk]
+            x, shift, wkv = m.forward_hidden_infctx(ids_c, shift, wkv, checkpoint=bool(cfg.grad_cp))
+            Bc, Tc, _ = x.shape
+            from .. import ops
+
+            loss_c = ops.linear_cross_entropy(x.reshape(Bc * Tc, C), m._head_weight(), lab_c.reshape(-1),
+                                              l2wrap=cfg.l2wrap, l2wrap_tokens=Bc * Tc)
+            has_valid = bool((lab_c != -100).any()) if cfg.truncated_bptt else True
+            if cfg.truncated_bptt:
+                if has_valid:
+                    (loss_c * (scale / n_chunks)).backward()
+                    total += loss_c.detach()
+                shift, wkv = shift.detach(), wkv.detach()
+            else:
+                pending.append(loss_c)
+        if not cfg.truncated_bptt:
+            loss = torch.stack(pending).mean()
+            (loss * scale).backward()
+            return loss.detach()
+        return total / n_chunks
+
+    # ------------------------------------------------------------------ one micro-batch
+    def train_step(self, idx: torch.Tensor, labels: torch.Tensor, lr: float) -> torch.Tensor:
+        """Forward + backward for one micro-batch; runs the optimiser every
+        ``accumulate_grad_batches`` calls.  Returns the detached loss (device tensor)."""
+        acc = self.cfg.accumulate_grad_batches
+        scale = 1.0 / acc
+        if self.cfg.train_type == "infctx":
+            loss = self._step_infctx(idx, labels, scale)
+        else:
+            loss = self._loss_normal(idx, labels)
+            (loss * scale if acc > 1 else loss).backward()
+            loss = loss.detach()
+        self.micro_step += 1
+        self.tokens_seen += idx.numel()
+        if self.micro_step % acc == 0:
+            self.opt.step(lr)
+            self.opt.zero_grad()
+            self.optimizer_steps += 1
+        return loss
+
+    def train_step_from_host(self, idx_cpu: torch.Tensor, labels_cpu: torch.Tensor, lr: float) -> float:
+        """The call a trainer makes per batch: pinned host tensors in, Python float out."""
+        idx = idx_cpu.to(self.ctx.device, non_blocking=True)
+        labels = labels_cpu.to(self.ctx.device, non_blocking=True)
+        return float(self.train_step(idx, labels, lr))

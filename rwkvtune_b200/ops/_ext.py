@@ -71,10 +71,19 @@ def stream() -> ctypes.c_void_p:
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+LAUNCH_COUNT = 0   # native entry-point calls since import (each issues at least one kernel)
+
+
 def call(name: str, *args) -> None:
+    global LAUNCH_COUNT
     fn = getattr(lib(), name)
     fn.restype = ctypes.c_int
+    LAUNCH_COUNT += 1
     check(fn(*args), name)
+
+
+def launch_count() -> int:
+    return LAUNCH_COUNT
 
 
 def i32(v: int) -> ctypes.c_int:
