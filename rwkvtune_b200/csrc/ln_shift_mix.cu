@@ -388,3 +388,67 @@ RWKV_EXPORT int rwkv_layer_norm_backward(const void* dy, const void* x, const vo
       (float*)partials, rows, C, strip);
   return rwkv_launch_status();
 }
+
+
+// ------------------------------------------------------------------------------------------
+// Allocation-free variant of the LayerNorm backward (see no_alloc.h for who needs it and the
+// rules).  Same kernel as above; the per-block partial sums land in a library-owned device
+// array and a second small kernel folds them into dw / db.
+// ------------------------------------------------------------------------------------------
+#include "no_alloc.h"
+
+static __device__ __align__(256) float g_ln_bwd_scratch[RWKV_NOALLOC_LN_SCRATCH_FLOATS];
+
+namespace {
+
+__global__ void __launch_bounds__(256)
+ln_partials_reduce_kernel(const float* __restrict__ partials, int nblocks, int C, float* __restrict__ dw,
+                          float* __restrict__ db) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  float sw = 0.f, sb = 0.f;
+  for (int b = 0; b < nblocks; ++b) {
+    sw += partials[(size_t)b * 2 * C + c];
+    sb += partials[(size_t)b * 2 * C + C + c];
+  }
+  dw[c] = sw;
+  db[c] = sb;
+}
+
+constexpr int kMaxDevices = 64;
+float* g_scratch_ptr[kMaxDevices] = {nullptr};
+
+// Device address of the scratch array on the current device, resolved once per device.
+int noalloc_scratch(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return RWKV_ERR_CUDA_BASE + (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return RWKV_ERR_BAD_SHAPE;
+  if (g_scratch_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_ln_bwd_scratch);
+    if (e != cudaSuccess) return RWKV_ERR_CUDA_BASE + (int)e;
+    g_scratch_ptr[dev] = static_cast<float*>(p);
+  }
+  *out = g_scratch_ptr[dev];
+  return RWKV_OK;
+}
+
+}  // namespace
+
+RWKV_EXPORT int rwkv_layer_norm_backward_noalloc(const void* dy, const void* x, const void* mean, const void* rstd,
+                                                 const void* ln_w, void* dx, void* dw, void* db, int rows, int C,
+                                                 int strip, void* stream) {
+  if (rows <= 0 || C <= 0 || C % 8 || C / 8 > 512 || strip <= 0) return RWKV_ERR_BAD_SHAPE;
+  const long long nblocks = ((long long)rows + strip - 1) / strip;
+  if (nblocks * 2 * C > (long long)RWKV_NOALLOC_LN_SCRATCH_FLOATS) return RWKV_ERR_TOO_LARGE;
+  float* scratch = nullptr;
+  const int st = noalloc_scratch(&scratch);
+  if (st != RWKV_OK) return st;
+  cudaStream_t s = (cudaStream_t)stream;
+  layer_norm_bwd_kernel<<<(int)nblocks, threads_for(C), 0, s>>>(
+      (const bf16*)dy, (const bf16*)x, (const float*)mean, (const float*)rstd, (const float*)ln_w, (bf16*)dx, scratch,
+      rows, C, strip);
+  ln_partials_reduce_kernel<<<(C + 255) / 256, 256, 0, s>>>(scratch, (int)nblocks, C, (float*)dw, (float*)db);
+  return rwkv_launch_status();
+}
