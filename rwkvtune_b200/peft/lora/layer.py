@@ -1,0 +1,124 @@
+"""LoRA-wrapped linear layer with a fused forward/backward.
+
+``y = x W^T + s (x A^T) B^T`` with the base weight frozen.  The reference evaluates this as three
+``F.linear`` calls and lets autograd also differentiate through the base layer
+(``rwkvtune/peft/lora/layer.py:92-130``).  Here one autograd node does it: the backward produces
+``dx = dy W + s (dy B) A``, ``dA`` and ``dB`` and never forms the (unused) base weight gradient.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn as nn
+
+from ...ops import gemm
+
+
+class _LoraLinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, a, b, scaling: float, w_needs_grad: bool):
+        x2 = x.reshape(-1, x.shape[-1])
+        xa = gemm.mm_nt(x2, a)                       # [M, r]
+        y = gemm.mm_nt(x2, w) + gemm.mm_nt(xa, b) * scaling
+        ctx.save_for_backward(x2, w, a, b, xa)
+        ctx.scaling, ctx.shape = scaling, x.shape
+        return y.reshape(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w, a, b, xa = ctx.saved_tensors
+        s = ctx.scaling
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        dyb = gemm.mm_nn(dy2, b)                     # [M, r]
+        dx = dw = da = db = None
+        if ctx.needs_input_grad[0]:
+            dx = (gemm.mm_nn(dy2, w) + gemm.mm_nn(dyb, a) * s).reshape(ctx.shape)
+        if ctx.needs_input_grad[1]:
+            dw = gemm.mm_tn(dy2, x2)
+        if ctx.needs_input_grad[2]:
+            da = gemm.mm_tn(dyb, x2) * s
+        if ctx.needs_input_grad[3]:
+            db = gemm.mm_tn(dy2, xa) * s
+        return dx, dw, da, db, None, None
+
+
+class LoraLinear(nn.Module):
+    def __init__(self, base_layer: nn.Linear, r: int = 64, lora_alpha: int = 128, lora_dropout: float = 0.0,
+                 use_rslora: bool = False, init_lora_weights=True):
+        super().__init__()
+        if not isinstance(base_layer, nn.Linear):
+            raise TypeError("LoraLinear wraps nn.Linear modules only")
+        self.base_layer = base_layer
+        self.in_features, self.out_features = base_layer.in_features, base_layer.out_features
+        self.r, self.lora_alpha = r, lora_alpha
+        self.scaling = lora_alpha / math.sqrt(r) if use_rslora else lora_alpha / r
+        dev, dt = base_layer.weight.device, base_layer.weight.dtype
+        self.lora_A = nn.Parameter(torch.zeros(r, self.in_features, device=dev, dtype=dt))
+        self.lora_B = nn.Parameter(torch.zeros(self.out_features, r, device=dev, dtype=dt))
+        self.lora_dropout = nn.Dropout(lora_dropout) if lora_dropout > 0 else nn.Identity()
+        if init_lora_weights:
+            self.reset_lora_parameters(init_lora_weights)
+        self.merged = False
+        self.disabled = False
+
+    @property
+    def weight(self) -> torch.Tensor:
+        return self.base_layer.weight
+
+    def reset_lora_parameters(self, mode=True) -> None:
+        if mode == "gaussian":
+            nn.init.normal_(self.lora_A, std=1.0 / self.r)
+        else:
+            a = torch.empty(self.lora_A.shape, dtype=torch.float32, device=self.lora_A.device)
+            nn.init.kaiming_uniform_(a, a=math.sqrt(5))
+            with torch.no_grad():
+                self.lora_A.copy_(a)
+        nn.init.zeros_(self.lora_B)
+
+    def effective_weight(self) -> torch.Tensor:
+        if self.merged or self.disabled:
+            return self.base_layer.weight
+        return self.base_layer.weight + (self.lora_B @ self.lora_A) * self.scaling
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self.disabled or self.merged:
+            return self.base_layer(x)
+        if isinstance(self.lora_dropout, nn.Dropout) and self.training:
+            base = self.base_layer(x)
+            xd = self.lora_dropout(x)
+            return base + gemm.linear(gemm.linear(xd, self.lora_A), self.lora_B) * self.scaling
+        return _LoraLinearFn.apply(x, self.base_layer.weight, self.lora_A, self.lora_B, self.scaling,
+                                   self.base_layer.weight.requires_grad)
+
+    @torch.no_grad()
+    def merge(self) -> None:
+        if not self.merged:
+            self.base_layer.weight.add_(((self.lora_B.float() @ self.lora_A.float()) * self.scaling).to(self.base_layer.weight.dtype))
+            self.merged = True
+
+    @torch.no_grad()
+    def unmerge(self) -> None:
+        if self.merged:
+            self.base_layer.weight.sub_(((self.lora_B.float() @ self.lora_A.float()) * self.scaling).to(self.base_layer.weight.dtype))
+            self.merged = False
+
+    def disable_adapter(self) -> None:
+        self.disabled = True
+
+    def enable_adapter(self) -> None:
+        self.disabled = False
+
+    def get_lora_state_dict(self) -> dict:
+        return {"lora_A": self.lora_A.detach().clone(), "lora_B": self.lora_B.detach().clone()}
+
+    def load_lora_state_dict(self, state_dict: dict) -> None:
+        with torch.no_grad():
+            if "lora_A" in state_dict:
+                self.lora_A.copy_(state_dict["lora_A"])
+            if "lora_B" in state_dict:
+                self.lora_B.copy_(state_dict["lora_B"])
+
+    def extra_repr(self) -> str:
+        return (f"in_features={self.in_features}, out_features={self.out_features}, r={self.r}, "
+                f"scaling={self.scaling:.4f}, merged={self.merged}, disabled={self.disabled}")
