@@ -19,9 +19,9 @@ TOKENIZER_FILES = ("tokenizer.json", "tokenizer_config.json", "special_tokens_ma
 
 def build_parser() -> argparse.ArgumentParser:
     p = argparse.ArgumentParser(prog="rwkvtune-merge-lora", description="Merge LoRA weights into a base RWKV-7 model")
-    p.add_argument("--base-model", required=True, help="base model directory (config.json + weights)")
-    p.add_argument("--lora-model", required=True, help="adapter directory (adapter_config.json + adapter_model.bin)")
-    p.add_argument("--output", required=True, help="output directory for the merged model")
+    p.add_argument("--base-model", "-b", required=True, help="base model directory (config.json + weights)")
+    p.add_argument("--lora-model", "-l", required=True, help="adapter directory (adapter_config.json + adapter_model.bin)")
+    p.add_argument("--output", "-o", required=True, help="output directory for the merged model")
     p.add_argument("--device", default="cpu", choices=["cuda", "cpu"])
     p.add_argument("--precision", default="bf16", choices=["fp32", "fp16", "bf16"])
     p.add_argument("--save-format", default="pth", choices=["pth", "safetensors"])
