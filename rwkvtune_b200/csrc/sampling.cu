@@ -1,0 +1,200 @@
+// Temperature + top-p sampling over a full vocabulary row without sorting it.
+//
+// One 1024-thread CTA per row; each thread keeps up to 64 probabilities in registers
+// (V <= 65536).  The nucleus is "the sorted prefix whose cumulative mass is <= top_p, plus
+// always the most likely token" -- i.e. token i is kept iff the mass of all tokens at least as
+// likely as i is <= top_p.  That set is {p >= theta*} for a threshold found by bisection on
+// theta (each probe is one register pass + one block reduction), so no sort, no cumsum and no
+// scatter is needed.  The draw is an inverse-CDF walk over the kept tokens in index order with a
+// Philox4x32-10 uniform keyed by (seed, row).  Replaces the full 65536-way sort + cumsum +
+// unsort + softmax + multinomial sequence of the reference
+// (rwkvtune/inference/core.py:165-238).
+#include "common.cuh"
+
+namespace {
+
+constexpr int ST = 1024;       // threads per row
+constexpr int SPT = 64;        // values per thread
+
+__device__ __forceinline__ uint2 mulhilo(uint32_t a, uint32_t b) {
+  const unsigned long long p = (unsigned long long)a * b;
+  return make_uint2((uint32_t)p, (uint32_t)(p >> 32));
+}
+
+// Philox4x32-10; returns a uniform in (0, 1)
+__device__ float philox_uniform(unsigned long long seed, unsigned long long ctr) {
+  uint32_t c0 = (uint32_t)ctr, c1 = (uint32_t)(ctr >> 32), c2 = 0x243F6A88u, c3 = 0x85A308D3u;
+  uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const uint2 m0 = mulhilo(0xD2511F53u, c0), m1 = mulhilo(0xCD9E8D57u, c2);
+    const uint32_t n0 = m1.y ^ c1 ^ k0, n1 = m1.x, n2 = m0.y ^ c3 ^ k1, n3 = m0.x;
+    c0 = n0; c1 = n1; c2 = n2; c3 = n3;
+    k0 += 0x9E3779B9u; k1 += 0xBB67AE85u;
+  }
+  return ((c0 >> 8) + 0.5f) * (1.0f / 16777216.0f);
+}
+
+__device__ __forceinline__ float block_reduce_sum(float v, float* red) {
+  v = warp_sum(v);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float s = (threadIdx.x < 32) ? red[threadIdx.x] : 0.f;
+  if (threadIdx.x < 32) s = warp_sum(s);
+  if (threadIdx.x == 0) red[32] = s;
+  __syncthreads();
+  return red[32];
+}
+
+__device__ __forceinline__ float block_reduce_max(float v, float* red) {
+  v = warp_max(v);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float s = (threadIdx.x < 32) ? red[threadIdx.x] : -INFINITY;
+  if (threadIdx.x < 32) s = warp_max(s);
+  if (threadIdx.x == 0) red[32] = s;
+  __syncthreads();
+  return red[32];
+}
+
+template <typename T>
+__global__ void __launch_bounds__(ST)
+sample_top_p_kernel(const T* __restrict__ logits, int V, int n_valid, float inv_temp, float top_p,
+                    unsigned long long seed, long long* __restrict__ tokens, float* __restrict__ logps) {
+  __shared__ float red[33];
+  __shared__ float scan[ST / 32];
+  __shared__ int winner;
+  __shared__ int amax;
+  const int row = blockIdx.x, tid = threadIdx.x;
+  const T* x = logits + (size_t)row * V;
+
+  float p[SPT];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < SPT; ++j) {
+    const int i = tid + j * ST;
+    float v = -INFINITY;
+    if (i < n_valid) {
+      if constexpr (sizeof(T) == 2) v = __bfloat162float(x[i]) * inv_temp;
+      else v = x[i] * inv_temp;
+      if (!(v == v)) v = -INFINITY;   // NaN logits are never sampled
+    }
+    p[j] = v;
+    mx = fmaxf(mx, v);
+  }
+  mx = block_reduce_max(mx, red);
+  float z = 0.f;
+#pragma unroll
+  for (int j = 0; j < SPT; ++j) {
+    p[j] = (p[j] == -INFINITY) ? 0.f : __expf(p[j] - mx);
+    z += p[j];
+  }
+  z = block_reduce_sum(z, red);
+  const float inv_z = 1.f / z;
+  float pmax = 0.f;
+#pragma unroll
+  for (int j = 0; j < SPT; ++j) {
+    p[j] *= inv_z;
+    pmax = fmaxf(pmax, p[j]);
+  }
+  if (tid == 0) amax = 0x7fffffff;
+  pmax = block_reduce_max(pmax, red);
+#pragma unroll
+  for (int j = 0; j < SPT; ++j)
+    if (p[j] == pmax) atomicMin(&amax, tid + j * ST);
+
+  // bisection for the smallest theta with mass({p >= theta}) <= top_p
+  float theta = 0.f;
+  if (top_p < 1.f) {
+    float lo = 0.f, hi = pmax;          // mass(lo) > top_p (or lo == 0), mass(hi) may or may not qualify
+    float m_hi = 0.f;
+#pragma unroll
+    for (int j = 0; j < SPT; ++j) m_hi += (p[j] >= hi) ? p[j] : 0.f;
+    m_hi = block_reduce_sum(m_hi, red);
+    if (m_hi > top_p) {
+      theta = pmax;                      // even the top token alone exceeds top_p: keep just it
+    } else {
+      for (int it = 0; it < 30; ++it) {
+        const float mid = 0.5f * (lo + hi);
+        float m = 0.f;
+#pragma unroll
+        for (int j = 0; j < SPT; ++j) m += (p[j] >= mid) ? p[j] : 0.f;
+        m = block_reduce_sum(m, red);
+        if (m <= top_p) hi = mid; else lo = mid;
+      }
+      theta = hi;
+    }
+  }
+
+  float kept = 0.f;
+#pragma unroll
+  for (int j = 0; j < SPT; ++j) kept += (p[j] >= theta && p[j] > 0.f) ? p[j] : 0.f;
+  // block-wide exclusive scan of the per-thread kept mass
+  const int lane = tid & 31, warp = tid >> 5;
+  float incl = kept;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const float t = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += t;
+  }
+  if (lane == 31) scan[warp] = incl;
+  if (tid == 0) winner = -1;
+  __syncthreads();
+  if (warp == 0) {
+    float w = scan[lane];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float t = __shfl_up_sync(0xffffffffu, w, o);
+      if (lane >= o) w += t;
+    }
+    scan[lane] = w;   // inclusive over warps
+  }
+  __syncthreads();
+  const float total = scan[ST / 32 - 1];
+  const float excl = (warp ? scan[warp - 1] : 0.f) + incl - kept;
+  const float u = philox_uniform(seed, (unsigned long long)row) * total;
+  if (kept > 0.f && u >= excl && u < excl + kept) {
+    float acc = excl;
+    int pick = -1;
+#pragma unroll
+    for (int j = 0; j < SPT; ++j) {
+      if (p[j] >= theta && p[j] > 0.f) {
+        if (pick < 0) pick = j;          // first kept value as a floor
+        if (u >= acc) pick = j;
+        acc += p[j];
+      }
+    }
+    atomicMax(&winner, tid + pick * ST);
+    // the token's log-probability under the renormalised nucleus
+    float pv = 0.f;
+#pragma unroll
+    for (int j = 0; j < SPT; ++j) if (j == pick) pv = p[j];
+    logps[row] = __logf(pv / total);
+  }
+  __syncthreads();
+  if (tid == 0) {
+    if (winner < 0) {   // rounding left u at the very end of the CDF: take the most likely token
+      winner = amax;
+      logps[row] = __logf(pmax / total);
+    }
+    tokens[row] = winner;
+  }
+}
+
+}  // namespace
+
+// logits: [n, V] fp32 (is_bf16 = 0) or bf16 (1); ids >= n_valid are banned; tokens int64 [n], logps fp32 [n]
+RWKV_EXPORT int rwkv_sample_top_p(const void* logits, int is_bf16, int n, int V, int n_valid, float inv_temp,
+                                  float top_p, long long seed, void* tokens, void* logps, void* stream) {
+  if (n <= 0 || V <= 0 || V > ST * SPT || n_valid <= 0 || n_valid > V) return RWKV_ERR_BAD_SHAPE;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (is_bf16)
+    sample_top_p_kernel<bf16><<<n, ST, 0, st>>>((const bf16*)logits, V, n_valid, inv_temp, top_p,
+                                                (unsigned long long)seed, (long long*)tokens, (float*)logps);
+  else
+    sample_top_p_kernel<float><<<n, ST, 0, st>>>((const float*)logits, V, n_valid, inv_temp, top_p,
+                                                 (unsigned long long)seed, (long long*)tokens, (float*)logps);
+  return rwkv_launch_status();
+}

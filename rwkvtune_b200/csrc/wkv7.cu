@@ -168,8 +168,9 @@ wkv7_fwd_kernel(const bf16* __restrict__ q_, const bf16* __restrict__ w_, const 
       __syncwarp();
     }
 
+    const int nsteps = min(CH, T - c * CH);   // the last chunk may be short (decode runs one step)
 #pragma unroll 1
-    for (int t = 0; t < CH; ++t) {
+    for (int t = 0; t < nsteps; ++t) {
       float2 d0, d1, b0, b1, k0, k1, q0, q1, a0, a1;
       ld4_as2(&sm.in[ID][t][c0], d0, d1);
       ld4_as2(&sm.in[IB][t][c0], b0, b1);

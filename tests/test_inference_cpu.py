@@ -1,0 +1,131 @@
+"""Sampler rules, rollout generator, scheduler, state cache on a tiny CPU model."""
+import pytest
+import torch
+
+from rwkvtune_b200.data.tokenizers import RWKVTokenizer, get_vocab_path
+from rwkvtune_b200.inference import (BatchGenerator, GenerationConfig, GRPOBatchGenerator, SchedulerCore, SequenceState,
+                                     TokenSampler, create_state_cache)
+from rwkvtune_b200.models import RWKVConfig, RWKV7Model
+
+
+@pytest.fixture(scope="module")
+def model():
+    torch.manual_seed(0)
+    m = RWKV7Model(RWKVConfig(n_layer=2, n_embd=64, vocab_size=256, eos_token_id=7))
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            if n.endswith(("output.weight", "ffn.value.weight")):
+                p.normal_(0, 0.05)
+    return m.eval()
+
+
+class _Tok:
+    eos_token_id = 7
+    vocab_size = 250
+    idx2token = {i: bytes([65 + i % 26]) for i in range(1, 250)}
+
+    def decode(self, ids, **kw):
+        return "".join(chr(65 + int(i) % 26) for i in ids)
+
+    def encode(self, s):
+        return [ord(c) - 64 for c in s]
+
+
+def test_top_p_rule_keeps_prefix_and_bans_oov():
+    logits = torch.log(torch.tensor([[0.5, 0.3, 0.15, 0.05, 0.0001]]))
+    f = TokenSampler.filter_logits(logits, 1.0, 0.8, 0, max_valid_token_id=3)
+    assert torch.isfinite(f[0, :2]).all() and torch.isinf(f[0, 2:]).all()
+    f = TokenSampler.filter_logits(logits, 1.0, 0.3, 0)      # top token alone exceeds p: still kept
+    assert torch.isfinite(f[0, 0]) and torch.isinf(f[0, 1:]).all()
+    tok, lp = TokenSampler.sample_batch(logits.repeat(8, 1), temperature=0.0)
+    assert (tok == 0).all()
+    g = torch.Generator().manual_seed(1)
+    tok, lp = TokenSampler.sample_batch(logits.repeat(4000, 1), 1.0, 0.8, generator=g)
+    frac = (tok == 0).float().mean().item()
+    assert set(tok.tolist()) <= {0, 1} and abs(frac - 0.625) < 0.03
+    assert torch.allclose(lp[tok == 0], torch.log(torch.tensor(0.625)), atol=1e-4)
+
+
+def test_grpo_generator_matches_stepwise_greedy(model):
+    gen = GRPOBatchGenerator(model, _Tok(), sync_every=2)
+    prompts = [[3, 4, 5, 6], [9, 8], [3, 4, 5, 6]]
+    out = gen.generate(prompts, max_new_tokens=6, num_generations=2, temperature=0.0)
+    assert out["completion_ids"].shape[0] == 6 and gen.last_stats["unique_prompts"] == 2
+    ref = model.generate(torch.tensor([[3, 4, 5, 6]]), max_new_tokens=6, do_sample=False, eos_token_id=7)[0, 4:]
+    ids, mask = out["completion_ids"][0], out["masks"][0]
+    n = int(mask.sum())
+    assert torch.equal(ids[:n], ref[:n])
+    assert torch.equal(out["completion_ids"][0], out["completion_ids"][1])      # greedy paths agree
+    assert torch.equal(out["completion_ids"][0], out["completion_ids"][4])      # duplicated prompt
+    assert (out["completion_ids"][~out["masks"]] == 0).all()
+    assert len(out["completions"]) == 6
+
+
+def test_grpo_generator_sampling_stops_at_eos(model):
+    gen = GRPOBatchGenerator(model, _Tok())
+    out = gen.generate([[1, 2, 3]] * 2, max_new_tokens=40, num_generations=4, temperature=1.0, top_p=0.95,
+                       repetition_penalty=1.1, seed=5)
+    ids, masks = out["completion_ids"], out["masks"]
+    for row, m in zip(ids, masks):
+        n = int(m.sum())
+        assert 1 <= n <= 40
+        body = row[:n - 1]
+        assert (body != 7).all()                   # EOS only ever as the last kept token
+        assert row[:n].max() <= 249                # ids beyond the tokenizer are banned
+    out2 = gen.generate([[1, 2, 3]] * 2, max_new_tokens=40, num_generations=4, temperature=1.0, top_p=0.95,
+                        repetition_penalty=1.1, seed=5)
+    assert torch.equal(out2["completion_ids"], ids)
+
+
+def test_scheduler_equals_plain_generate(model):
+    tok = _Tok()
+    sched = SchedulerCore(model, tok, max_batch_size=2, max_batch_tokens=8, prefill_chunk_size=3)
+    seqs = [SequenceState(i, p, max_new_tokens=5, temperature=0.0, eos_token_id=7)
+            for i, p in enumerate([[3, 4, 5, 6, 7, 8, 9], [9, 8], [20, 21, 22]])]
+    sched.add_sequences(seqs)
+    for _ in sched.run_to_completion_sync():
+        pass
+    for s in seqs:
+        ref = model.generate(torch.tensor([s.prompt_tokens]), max_new_tokens=5, do_sample=False, eos_token_id=7)
+        assert s.generated_tokens == ref[0, len(s.prompt_tokens):].tolist()[:len(s.generated_tokens)]
+        assert s.is_finished and s.finish_reason in ("eos", "length")
+    assert sched.get_stats()["free_slots"] == 2
+
+
+def test_state_cache_prefix_hit_gives_same_tokens(model):
+    tok = _Tok()
+    cache = create_state_cache(model, max_cache_memory_gb=0.01, max_cache_entries=2)
+    sys_prompt = [3, 4, 5, 6, 10, 11]
+    assert cache.create_checkpoints(sys_prompt + [20, 21], system_prompt_len=6) == 2
+    pos, state, out = cache.lookup(sys_prompt + [30, 31, 32])
+    assert pos == 6 and state is not None
+    bg = BatchGenerator(model, tok, GenerationConfig(max_length=4, temperature=0.0), max_batch_size=2)
+    bg.scheduler.state_cache = cache
+    a = bg.generate(input_ids=[sys_prompt + [30, 31, 32]])["completion_ids"]
+    bg.scheduler.state_cache = None
+    b = bg.generate(input_ids=[sys_prompt + [30, 31, 32]])["completion_ids"]
+    assert torch.equal(a, b)
+    cache.create_checkpoints([40, 41, 42])
+    assert cache.get_stats()["entries"] <= 2 and cache.get_stats()["evictions"] >= 1
+
+
+def test_structured_output_masks_to_json():
+    from rwkvtune_b200.inference import create_enforcer, is_structured_output_available
+    if not is_structured_output_available():
+        pytest.skip("lm-format-enforcer not installed")
+    tok = RWKVTokenizer(get_vocab_path())
+    enf = create_enforcer(tok, {"type": "json_schema", "json_schema": {"schema": {
+        "type": "object", "properties": {"ok": {"type": "boolean"}}, "required": ["ok"]}}})
+    text = ""
+    for _ in range(40):
+        logits = torch.zeros(65536)
+        masked = enf.mask_logits(logits)
+        if enf.is_finished():
+            break
+        allowed = torch.isfinite(masked).nonzero().flatten().tolist()
+        pick = max(allowed, key=lambda t: len(tok.idx2token.get(t, b"")))
+        text += tok.decode([pick])
+        if enf.update(pick):
+            break
+    import json
+    assert json.loads(text)["ok"] in (True, False)

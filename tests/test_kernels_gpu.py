@@ -205,3 +205,28 @@ def test_model_step_on_gpu_matches_cpu_reference():
         if cos < 0.98 and b.abs().max() > 1e-6:
             bad.append((n, cos))
     assert not bad, bad
+
+
+def test_sampler_kernel_matches_filtered_distribution():
+    from rwkvtune_b200.inference.core import TokenSampler
+    from rwkvtune_b200.inference import sampling_native
+    torch.manual_seed(0)
+    V, n = 1000, 4096
+    base = torch.randn(1, V, device="cuda") * 2.0
+    logits = base.expand(n, V).contiguous()
+    temp, top_p = 0.8, 0.7
+    filt = TokenSampler.filter_logits(base, temp, top_p, 0, max_valid_token_id=989)
+    probs = torch.softmax(filt, -1)[0]
+    toks, lps = sampling_native.sample_top_p(logits, temp, top_p, 989, seed=7)
+    assert toks.max() <= 989 and (probs[toks] > 0).all(), "sampled a token outside the nucleus"
+    counts = torch.bincount(toks, minlength=V).float()
+    kept = probs > 0
+    expected = probs[kept] * n
+    chi2 = ((counts[kept] - expected) ** 2 / expected.clamp(min=1e-9)).sum().item()
+    dof = int(kept.sum()) - 1
+    assert chi2 < dof + 6 * (2 * dof) ** 0.5 + 10, (chi2, dof)
+    assert torch.allclose(lps, torch.log(probs[toks]), atol=2e-3)
+    toks2, _ = sampling_native.sample_top_p(logits, temp, top_p, 989, seed=7)
+    assert torch.equal(toks, toks2), "same seed must give the same draws"
+    bf = sampling_native.sample_top_p(logits.to(torch.bfloat16), temp, 1.0, None, seed=3)[0]
+    assert bf.min() >= 0 and bf.max() < V
