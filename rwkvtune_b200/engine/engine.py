@@ -132,6 +132,19 @@ class TrainEngine:
             self.optimizer_steps += 1
         return loss
 
+    def backward_and_step(self, loss: torch.Tensor, lr: float) -> bool:
+        """Back-propagate an externally computed loss (already a mean over the micro-batch) and run the
+        optimiser on accumulation boundaries.  Returns True when an optimiser step happened."""
+        acc = self.cfg.accumulate_grad_batches
+        (loss / acc if acc > 1 else loss).backward()
+        self.micro_step += 1
+        if self.micro_step % acc == 0:
+            self.opt.step(lr)
+            self.opt.zero_grad()
+            self.optimizer_steps += 1
+            return True
+        return False
+
     def train_step_from_host(self, idx_cpu: torch.Tensor, labels_cpu: torch.Tensor, lr: float) -> float:
         """The call a trainer makes per batch: pinned host tensors in, Python float out."""
         idx = idx_cpu.to(self.ctx.device, non_blocking=True)

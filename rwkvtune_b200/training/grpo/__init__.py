@@ -1,0 +1,7 @@
+from .advantage import AdvantageCalculator
+from .dataset import GRPODataBuffer, RepeatBatchSampler, create_grpo_dataloader
+from .loss import BNPOLoss, DAPOLoss, DrGRPOLoss, GRPOLossBase, get_loss_function
+from .utils import entropy_from_logits, selective_log_softmax
+
+__all__ = ["AdvantageCalculator", "GRPODataBuffer", "RepeatBatchSampler", "create_grpo_dataloader", "GRPOLossBase",
+           "DAPOLoss", "DrGRPOLoss", "BNPOLoss", "get_loss_function", "selective_log_softmax", "entropy_from_logits"]

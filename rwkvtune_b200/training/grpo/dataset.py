@@ -1,0 +1,102 @@
+"""Prompt batching for GRPO (``rwkvtune/training/grpo/dataset.py:17-212``).
+
+Each prompt batch is yielded ``repeat_batch_count = steps_per_generation * num_iterations`` times:
+the first occurrence triggers a rollout, the following ones consume the buffered slices.  Unlike the
+reference, which hands ``rank=0`` to every process so that all ranks read the same shard, each rank
+here reads its own shard (``world_size = devices``) and draws with a rank-specific seed.
+"""
+from __future__ import annotations
+
+from typing import Any, Dict, Iterator, List, Optional
+
+import torch
+
+
+class RepeatBatchSampler:
+    """Yields each batch of indices ``repeat_count`` times in a row."""
+
+    def __init__(self, n: int, batch_size: int, repeat_count: int = 1, shuffle: bool = True, seed: int = 42,
+                 rank: int = 0, world_size: int = 1, drop_last: bool = True):
+        self.n, self.batch_size, self.repeat_count = n, batch_size, max(1, repeat_count)
+        self.shuffle, self.seed, self.rank, self.world_size, self.drop_last = shuffle, seed, rank, world_size, drop_last
+        self.epoch = 0
+
+    def set_epoch(self, epoch: int) -> None:
+        self.epoch = epoch
+
+    def _indices(self) -> List[int]:
+        if self.shuffle:
+            g = torch.Generator().manual_seed(self.seed + self.epoch)
+            order = torch.randperm(self.n, generator=g).tolist()
+        else:
+            order = list(range(self.n))
+        total = (self.n + self.world_size - 1) // self.world_size * self.world_size
+        order += order[: total - self.n]
+        return order[self.rank:total:self.world_size]
+
+    def num_batches(self) -> int:
+        per_rank = (self.n + self.world_size - 1) // self.world_size
+        return per_rank // self.batch_size if self.drop_last else -(-per_rank // self.batch_size)
+
+    def __len__(self) -> int:
+        return self.num_batches() * self.repeat_count
+
+    def __iter__(self) -> Iterator[List[int]]:
+        idx = self._indices()
+        for b in range(self.num_batches()):
+            batch = idx[b * self.batch_size:(b + 1) * self.batch_size]
+            for _ in range(self.repeat_count):
+                yield batch
+
+
+def grpo_collate(samples: List[Dict[str, Any]]) -> Dict[str, Any]:
+    """``{"prompts": [...], "input_ids": [[...], ...], <every other column>: [...]}``."""
+    out: Dict[str, Any] = {"prompts": [s["prompt"] for s in samples],
+                           "input_ids": [list(s["input_ids"]) for s in samples]}
+    for key in samples[0]:
+        if key not in ("prompt", "input_ids"):
+            out[key] = [s[key] for s in samples]
+    return out
+
+
+class GRPODataLoader:
+    def __init__(self, dataset, sampler: RepeatBatchSampler):
+        self.dataset, self.sampler = dataset, sampler
+
+    def __len__(self) -> int:
+        return len(self.sampler)
+
+    def __iter__(self):
+        for idx in self.sampler:
+            yield grpo_collate([self.dataset[i] for i in idx])
+
+
+def create_grpo_dataloader(dataset, batch_size: int, repeat_batch_count: int = 1, shuffle: bool = True, seed: int = 42,
+                           rank: int = 0, world_size: int = 1, num_workers: int = 0) -> GRPODataLoader:
+    first = dataset[0]
+    for col in ("prompt", "input_ids"):
+        if col not in first:
+            raise ValueError(f"GRPO dataset samples need a {col!r} field")
+    return GRPODataLoader(dataset, RepeatBatchSampler(len(dataset), batch_size, repeat_batch_count, shuffle, seed, rank,
+                                                      world_size))
+
+
+class GRPODataBuffer:
+    """FIFO of rollout slices (kept for API parity; the trainer holds its slices in a plain list)."""
+
+    def __init__(self, capacity: int = 16):
+        self.capacity, self.items = capacity, []
+
+    def add(self, item) -> None:
+        self.items.append(item)
+        if len(self.items) > self.capacity:
+            self.items.pop(0)
+
+    def pop(self):
+        return self.items.pop(0) if self.items else None
+
+    def __len__(self) -> int:
+        return len(self.items)
+
+    def clear(self) -> None:
+        self.items.clear()
