@@ -1,0 +1,381 @@
+// bf16 GEMM on the 5th-generation tensor cores: C[M,N] = op(A) * op(B), fp32 accumulation in
+// tensor memory, operands streamed by TMA.
+//
+// One persistent CTA per SM, six warps with fixed roles:
+//   warp 0    TMA producer: fills a 4-stage ring of {A 128x64, B 256x64} bf16 tiles (128-byte
+//             swizzle), one mbarrier transaction per stage
+//   warp 1    allocates the 512 tensor-memory columns and issues tcgen05.mma (128x256x16 per
+//             instruction, one elected thread); tcgen05.commit releases ring stages and signals
+//             a finished accumulator
+//   warps 2-5 epilogue: tcgen05.ld the 128x256 fp32 accumulator quarter by quarter, optional
+//             fused relu(x)^2, convert to bf16, stage in swizzled shared memory, TMA store
+// Two accumulators (2 x 256 columns) let the epilogue of tile i overlap the MMAs of tile i+1.
+//
+// Operand layouts: an operand is "K-major" when the contraction index is contiguous in memory
+// and "MN-major" when the M (or N) index is.  Both are expressed through the shared-memory and
+// instruction descriptors, so x@W^T (NT), x@W (NN) and dy^T@x (TN) run in the same kernel without
+// transposing anything in memory.
+//
+// Every mbarrier wait is bounded: on expiry the waiter records a code in `status`, all roles
+// leave their loops, tensor memory is released and the kernel returns.
+//
+// Replaces the cuBLAS calls behind every nn.Linear / matmul of the reference
+// (rwkvtune/models/rwkv7/model.py:146-170, :307-308).
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64;
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;          // 16 KiB
+constexpr int B_BYTES = BN * BK * 2;          // 32 KiB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int C_CHUNK_BYTES = BM * 64 * 2;    // 128 rows x 64 bf16
+constexpr int NUM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr uint32_t WAIT_LIMIT = 1u << 28;
+
+struct Barriers {
+  uint64_t full[STAGES];
+  uint64_t empty[STAGES];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 2 * C_CHUNK_BYTES + 1024 + 256;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.b32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false (after recording `code`) when the limit is hit or another role aborted.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Barriers* bars, int* status, int code) {
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 0xffff) == 0xffff && *reinterpret_cast<volatile int*>(&bars->abort_flag)) return false;
+  }
+  *reinterpret_cast<volatile int*>(&bars->abort_flag) = 1;
+  if (status) atomicCAS(status, 0, code);
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(src), "r"(x), "r"(y)
+               : "memory");
+}
+
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_16, uint32_t sbo_16) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr >> 4) & 0x3fff);
+  d |= (uint64_t)(lbo_16 & 0x3fff) << 16;
+  d |= (uint64_t)(sbo_16 & 0x3fff) << 32;
+  d |= (uint64_t)1 << 46;   // descriptor version for sm_100
+  d |= (uint64_t)2 << 61;   // 128-byte swizzle
+  return d;
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// EPI: 0 = plain store, 1 = relu(x)^2
+template <bool A_MN, bool B_MN, int EPI>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const __grid_constant__ CUtensorMap map_c, int M, int N, int K, int* status) {
+  extern __shared__ unsigned char smem_dyn[];
+  const uint32_t raw = smem_u32(smem_dyn);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  unsigned char* base_ptr = smem_dyn + (base - raw);
+  const uint32_t c_stage = base + STAGES * STAGE_BYTES;
+  Barriers* bars = reinterpret_cast<Barriers*>(base_ptr + STAGES * STAGE_BYTES + 2 * C_CHUNK_BYTES);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&bars->full[s], 1); mbar_init(&bars->empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&bars->acc_full[a], 1); mbar_init(&bars->acc_empty[a], 4); }
+    bars->abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)),
+                 "r"(TMEM_COLS));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&bars->empty[stage], phase ^ 1, bars, status, 101)) { ok = false; break; }
+          mbar_expect_tx(&bars->full[stage], STAGE_BYTES);
+          const uint32_t sa = base + stage * STAGE_BYTES, sb = sa + A_BYTES;
+          const int k0 = kb * BK;
+          if (A_MN) {
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c) tma_load_2d(sa + c * (BK * 128), &map_a, &bars->full[stage], m0 + c * 64, k0);
+          } else {
+            tma_load_2d(sa, &map_a, &bars->full[stage], k0, m0);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c) tma_load_2d(sb + c * (BK * 128), &map_b, &bars->full[stage], n0 + c * 64, k0);
+          } else {
+            tma_load_2d(sb, &map_b, &bars->full[stage], k0, n0);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((A_MN ? 1u : 0u) << 15) |
+                                 ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+      constexpr uint32_t a_lbo = A_MN ? (BK * 128) >> 4 : 1, b_lbo = B_MN ? (BK * 128) >> 4 : 1;
+      constexpr uint32_t a_adv = A_MN ? (2 * 1024) >> 4 : 32 >> 4, b_adv = B_MN ? (2 * 1024) >> 4 : 32 >> 4;
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+        const int acc = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1;
+        if (!mbar_wait(&bars->acc_empty[acc], acc_phase ^ 1, bars, status, 102)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&bars->full[stage], phase, bars, status, 103)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = base + stage * STAGE_BYTES, sb = sa + A_BYTES;
+          const uint64_t adesc = make_smem_desc(sa, a_lbo, 1024 >> 4);
+          const uint64_t bdesc = make_smem_desc(sb, b_lbo, 1024 >> 4);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k)
+            umma_f16(d_tmem, adesc + (uint64_t)(k * a_adv), bdesc + (uint64_t)(k * b_adv), idesc, (kb | k) ? 1u : 0u);
+          umma_commit(&bars->empty[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit(&bars->acc_full[acc]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int quarter = warp & 3;                 // tensor-memory lanes [32q, 32q+32)
+    const int row = quarter * 32 + lane;          // row of the tile owned by this thread
+    int local = 0;
+    int cbuf = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+      const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+      const int acc = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      mbar_wait(&bars->acc_full[acc], acc_phase, bars, status, 104);
+      // the four epilogue warps must take the same branch: a timeout is published in abort_flag before
+      // this barrier and read by everyone after it
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (*reinterpret_cast<volatile int*>(&bars->abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int chunk = 0; chunk < BN / 64; ++chunk) {
+        uint32_t v0[32], v1[32];
+        tmem_ld32(t_row + chunk * 64, v0);
+        tmem_ld32(t_row + chunk * 64 + 32, v1);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        // the staging buffer we are about to overwrite must have been read by its TMA store
+        if (threadIdx.x == 64) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const uint32_t cs = c_stage + cbuf * C_CHUNK_BYTES + row * 128;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {   // eight 16-byte pieces of this row, XOR-swizzled by (row % 8)
+          float f[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const int col = j * 8 + e;
+            float x = __uint_as_float(col < 32 ? v0[col] : v1[col - 32]);
+            if (EPI == 1) { x = fmaxf(x, 0.f); x = x * x; }
+            f[e] = x;
+          }
+          const uint4 packed = pack8(f);
+          const uint32_t dst = cs + ((j ^ (row & 7)) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(packed.x), "r"(packed.y),
+                       "r"(packed.z), "r"(packed.w)
+                       : "memory");
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (threadIdx.x == 64) {
+          tma_store_2d(&map_c, c_stage + cbuf * C_CHUNK_BYTES, n0 + chunk * 64, m0);
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+        cbuf ^= 1;
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->acc_empty[acc]);
+    }
+    if (threadIdx.x == 64) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS));
+  }
+}
+
+// ------------------------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// 2-D bf16 tensor map over a row-major [rows, cols] matrix with leading dimension `ld` (elements),
+// box = {box_cols, box_rows}, 128-byte swizzle.
+int make_map(CUtensorMap* map, const void* ptr, long long rows, long long cols, long long ld, int box_cols,
+             int box_rows) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return RWKV_ERR_NOT_INITIALISED;
+  if (((uintptr_t)ptr & 15) || (ld * 2) % 16) return RWKV_ERR_BAD_ALIGNMENT;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? RWKV_OK : RWKV_ERR_CUDA_BASE + 900 + (int)r;
+}
+
+template <bool A_MN, bool B_MN, int EPI>
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, int M, int N, int K, int* status,
+           int sms, cudaStream_t st) {
+  auto kern = gemm_tcgen05_kernel<A_MN, B_MN, EPI>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return RWKV_ERR_CUDA_BASE + (int)e;
+    configured = true;
+  }
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int grid = tiles < sms ? tiles : sms;
+  kern<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(ma, mb, mc, M, N, K, status);
+  return rwkv_launch_status();
+}
+
+}  // namespace
+
+// C[M,N] (row-major, ldc) = op(A) op(B) in bf16 with fp32 accumulation.
+//   a_mn = 0: A is [M,K] row-major (lda);  a_mn = 1: A is stored [K,M] row-major (lda)
+//   b_mn = 0: B is [N,K] row-major (ldb);  b_mn = 1: B is stored [K,N] row-major (ldb)
+//   epilogue: 0 none, 1 relu(x)^2.   status: device int, set non-zero if a device-side wait timed out.
+RWKV_EXPORT int rwkv_gemm_bf16_tcgen05(const void* a, const void* b, void* c, int M, int N, int K, long long lda,
+                                       long long ldb, long long ldc, int a_mn, int b_mn, int epilogue, void* status,
+                                       void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return RWKV_ERR_BAD_SHAPE;
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  CUtensorMap ma, mb, mc;
+  int r;
+  r = a_mn ? make_map(&ma, a, K, M, lda, 64, BK) : make_map(&ma, a, M, K, lda, BK, BM);
+  if (r) return r;
+  r = b_mn ? make_map(&mb, b, K, N, ldb, 64, BK) : make_map(&mb, b, N, K, ldb, BK, BN);
+  if (r) return r;
+  r = make_map(&mc, c, M, N, ldc, 64, BM);
+  if (r) return r;
+  cudaStream_t st = (cudaStream_t)stream;
+  int* sp = (int*)status;
+#define DISPATCH(AM, BMN)                                                              \
+  (epilogue == 1 ? launch<AM, BMN, 1>(ma, mb, mc, M, N, K, sp, sms, st)                \
+                 : launch<AM, BMN, 0>(ma, mb, mc, M, N, K, sp, sms, st))
+  if (!a_mn && !b_mn) return DISPATCH(false, false);
+  if (!a_mn && b_mn) return DISPATCH(false, true);
+  if (a_mn && b_mn) return DISPATCH(true, true);
+  return DISPATCH(true, false);
+#undef DISPATCH
+}

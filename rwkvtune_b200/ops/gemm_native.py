@@ -1,0 +1,71 @@
+"""Binding of the tcgen05 GEMM (``rwkvtune_b200/csrc/gemm_tcgen05.cu``).
+
+``native_ok`` states which problems the kernel takes: bf16 CUDA tensors, 16-byte aligned rows
+(every leading dimension a multiple of 8 elements) and sizes large enough that a 128x256 tile is
+not mostly padding.  Everything else goes to the library GEMM.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _ext
+
+_STATUS = {}
+MIN_M, MIN_N, MIN_K = 128, 64, 32
+
+
+def _status(device: torch.device) -> torch.Tensor:
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    if key not in _STATUS:
+        _STATUS[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _STATUS[key]
+
+
+def check_status(device=None) -> int:
+    """Host-side read of the device status word (non-zero = a bounded wait inside the kernel expired)."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    return int(_status(dev).item())
+
+
+def available() -> bool:
+    return _ext.available() and hasattr(_ext.lib(), "rwkv_gemm_bf16_tcgen05")
+
+
+def _rows_ok(t: torch.Tensor) -> bool:
+    return (t.dim() == 2 and t.dtype == torch.bfloat16 and t.is_cuda and t.stride(1) == 1 and t.stride(0) % 8 == 0
+            and t.data_ptr() % 16 == 0)
+
+
+def native_ok(x: torch.Tensor, w: torch.Tensor, layout: str) -> bool:
+    if not (_rows_ok(x) and _rows_ok(w)) or not available():
+        return False
+    if layout == "nt":
+        M, K, N = x.shape[0], x.shape[1], w.shape[0]
+    elif layout == "nn":
+        M, K, N = x.shape[0], x.shape[1], w.shape[1]
+    else:
+        M, K, N = x.shape[1], x.shape[0], w.shape[1]
+    return M >= MIN_M and N >= MIN_N and K >= MIN_K and N % 8 == 0
+
+
+def _run(a, b, M, N, K, a_mn: int, b_mn: int, epilogue: int = 0) -> torch.Tensor:
+    c = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+    _ext.call("rwkv_gemm_bf16_tcgen05", _ext.ptr(a), _ext.ptr(b), _ext.ptr(c), _ext.i32(M), _ext.i32(N), _ext.i32(K),
+              _ext.i64(a.stride(0)), _ext.i64(b.stride(0)), _ext.i64(c.stride(0)), _ext.i32(a_mn), _ext.i32(b_mn),
+              _ext.i32(epilogue), _ext.ptr(_status(a.device)), _ext.stream())
+    return c
+
+
+def mm_nt(x: torch.Tensor, w: torch.Tensor, epilogue: int = 0) -> torch.Tensor:
+    """``x [M,K] @ w[N,K]^T``"""
+    return _run(x, w, x.shape[0], w.shape[0], x.shape[1], 0, 0, epilogue)
+
+
+def mm_nn(x: torch.Tensor, w: torch.Tensor, epilogue: int = 0) -> torch.Tensor:
+    """``x [M,K] @ w[K,N]``"""
+    return _run(x, w, x.shape[0], w.shape[1], x.shape[1], 0, 1, epilogue)
+
+
+def mm_tn(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """``a[Kc,M]^T @ b[Kc,N]`` (weight gradients: contraction over the token dimension)"""
+    return _run(a, b, a.shape[1], b.shape[1], a.shape[0], 1, 1)

@@ -230,3 +230,39 @@ def test_sampler_kernel_matches_filtered_distribution():
     assert torch.equal(toks, toks2), "same seed must give the same draws"
     bf = sampling_native.sample_top_p(logits.to(torch.bfloat16), temp, 1.0, None, seed=3)[0]
     assert bf.min() >= 0 and bf.max() < V
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 512, 128), (200, 320, 96), (1024, 2048, 2048), (384, 64, 32)])
+@pytest.mark.parametrize("layout", ["nt", "nn", "tn"])
+def test_tcgen05_gemm_layouts(M, N, K, layout):
+    from rwkvtune_b200.ops import gemm_native
+    if not gemm_native.available():
+        pytest.fail("native GEMM missing from the library")
+    torch.manual_seed(M + N + K)
+    if layout == "nt":
+        a = torch.randn(M, K, device="cuda").to(BF); b = torch.randn(N, K, device="cuda").to(BF)
+        ref_out = a.float() @ b.float().t()
+        assert gemm_native.native_ok(a, b, "nt")
+        out = gemm_native.mm_nt(a, b)
+    elif layout == "nn":
+        a = torch.randn(M, K, device="cuda").to(BF); b = torch.randn(K, N, device="cuda").to(BF)
+        ref_out = a.float() @ b.float()
+        out = gemm_native.mm_nn(a, b)
+    else:
+        a = torch.randn(K, M, device="cuda").to(BF); b = torch.randn(K, N, device="cuda").to(BF)
+        ref_out = a.float().t() @ b.float()
+        out = gemm_native.mm_tn(a, b)
+    torch.cuda.synchronize()
+    assert gemm_native.check_status() == 0, "a device-side wait in the GEMM kernel timed out"
+    err = (out.float() - ref_out).abs().max().item()
+    assert err <= 2e-2 * ref_out.abs().max().item() + 1e-2, (layout, err, ref_out.abs().max().item())
+
+
+def test_tcgen05_gemm_relu_sq_epilogue():
+    from rwkvtune_b200.ops import gemm_native
+    torch.manual_seed(0)
+    a = torch.randn(512, 256, device="cuda").to(BF); b = torch.randn(768, 256, device="cuda").to(BF)
+    out = gemm_native.mm_nt(a, b, epilogue=1)
+    ref_out = torch.relu(a.float() @ b.float().t()) ** 2
+    assert gemm_native.check_status() == 0
+    assert (out.float() - ref_out).abs().max().item() <= 2e-2 * ref_out.abs().max().item() + 1e-2
