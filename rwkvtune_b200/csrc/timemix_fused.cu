@@ -313,14 +313,15 @@ __global__ void relu_sq_fwd_kernel(const bf16* __restrict__ x, bf16* __restrict_
     stg16(y + i * 8, pack8(f));
   }
 }
+// from_output = 1: the first argument is y = relu(x)^2 (what the fused GEMM epilogue stored) and relu(x) = sqrt(y)
 __global__ void relu_sq_bwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, bf16* __restrict__ dx,
-                                   size_t n8) {
+                                   size_t n8, int from_output) {
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
     float f[8], g[8];
     unpack8(ldg16(x + i * 8), f);
     unpack8(ldg16(dy + i * 8), g);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) f[e] = 2.f * fmaxf(f[e], 0.f) * g[e];
+    for (int e = 0; e < 8; ++e) f[e] = 2.f * (from_output ? sqrtf(fmaxf(f[e], 0.f)) : fmaxf(f[e], 0.f)) * g[e];
     stg16(dx + i * 8, pack8(f));
   }
 }
@@ -395,11 +396,12 @@ RWKV_EXPORT int rwkv_relu_sq_forward(const void* x, void* y, long long n, void* 
   return rwkv_launch_status();
 }
 
-RWKV_EXPORT int rwkv_relu_sq_backward(const void* x, const void* dy, void* dx, long long n, void* stream) {
+RWKV_EXPORT int rwkv_relu_sq_backward(const void* x, const void* dy, void* dx, long long n, int from_output,
+                                      void* stream) {
   if (n % 8) return RWKV_ERR_BAD_SHAPE;
   const size_t n8 = (size_t)n / 8;
   const int blocks = (int)((n8 + 255) / 256 < 148 * 16 ? (n8 + 255) / 256 : 148 * 16);
   relu_sq_bwd_kernel<<<blocks > 0 ? blocks : 1, 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (const bf16*)dy,
-                                                                               (bf16*)dx, n8);
+                                                                               (bf16*)dx, n8, from_output);
   return rwkv_launch_status();
 }

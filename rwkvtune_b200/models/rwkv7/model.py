@@ -167,7 +167,10 @@ class RWKV7ChannelMix(nn.Module):
 
     def forward(self, x, ln_w, ln_b, x_prev=None, want_state: bool = False):
         mixed, last = ops.ln_shift_mix(x, ln_w, ln_b, self.x_k.reshape(1, -1), x_prev)
-        hidden = ops.relu_squared(self.key(mixed[0]))
+        if type(self.key) is Linear:
+            hidden = ops.linear_relu_sq(mixed[0], self.key.weight)
+        else:   # wrapped (e.g. LoRA): activation applied separately
+            hidden = ops.relu_squared(self.key(mixed[0]))
         return self.value(hidden), (last if want_state else None)
 
 

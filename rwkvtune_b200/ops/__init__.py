@@ -69,6 +69,13 @@ def matmul(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     return x @ w
 
 
+def linear_relu_sq(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """``relu(x @ weight^T) ** 2`` (channel-mix key projection); fused into the GEMM epilogue on CUDA."""
+    if _native(x, "gemm") and _native(x, "relu_squared"):
+        return _cuda().linear_relu_sq(x, weight)
+    return reference.relu_squared(torch.nn.functional.linear(x, weight))
+
+
 # ------------------------------------------------------------------------------- fused element-wise
 def layer_norm(x, weight, bias, eps: float = LAYERNORM_EPS):
     if _native(x, "layer_norm"):

@@ -295,7 +295,7 @@ class _ReluSq(torch.autograd.Function):
         (xb,) = ctx.saved_tensors
         dyb = _c(dy, BF16)
         dx = torch.empty_like(xb)
-        call("rwkv_relu_sq_backward", ptr(xb), ptr(dyb), ptr(dx), i64(xb.numel()), stream())
+        call("rwkv_relu_sq_backward", ptr(xb), ptr(dyb), ptr(dx), i64(xb.numel()), i32(0), stream())
         return dx.to(ctx.dt)
 
 
@@ -381,3 +381,39 @@ def linear_logprob_entropy(x, weight, targets, temperature: float = 1.0, with_en
     from . import loss_kernels
 
     return loss_kernels.linear_logprob_entropy(x, weight, targets, temperature, with_entropy)
+
+
+class _LinearReluSq(torch.autograd.Function):
+    """``relu(x @ W^T)^2`` with the activation applied in the GEMM epilogue.  Only the output is kept:
+    the backward recovers ``relu(pre) = sqrt(y)`` instead of re-reading a saved pre-activation."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        from . import gemm_native
+
+        x2 = _c(x.reshape(-1, x.shape[-1]), BF16)
+        y = gemm_native.mm_nt(x2, w, epilogue=1)
+        ctx.save_for_backward(x2, w, y)
+        ctx.shape = x.shape
+        return y.reshape(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        from . import gemm
+
+        x2, w, y = ctx.saved_tensors
+        dyb = _c(dy.reshape(-1, dy.shape[-1]), BF16)
+        dpre = torch.empty_like(y)
+        call("rwkv_relu_sq_backward", ptr(y), ptr(dyb), ptr(dpre), i64(y.numel()), i32(1), stream())
+        dx = gemm.mm_nn(dpre, w).reshape(ctx.shape) if ctx.needs_input_grad[0] else None
+        dw = gemm.mm_tn(dpre, x2) if ctx.needs_input_grad[1] else None
+        return dx, dw
+
+
+def linear_relu_sq(x, weight):
+    from . import gemm_native
+
+    x2 = x.reshape(-1, x.shape[-1])
+    if x.dtype == BF16 and weight.dtype == BF16 and gemm_native.native_ok(x2 if x2.is_contiguous() else x2.contiguous(), weight, "nt"):
+        return _LinearReluSq.apply(x, weight)
+    return relu_squared(linear(x, weight))

@@ -45,7 +45,11 @@ def native_ok(x: torch.Tensor, w: torch.Tensor, layout: str) -> bool:
         M, K, N = x.shape[0], x.shape[1], w.shape[1]
     else:
         M, K, N = x.shape[1], x.shape[0], w.shape[1]
-    return M >= MIN_M and N >= MIN_N and K >= MIN_K and N % 8 == 0
+    if not (M >= MIN_M and N >= MIN_N and K >= MIN_K and N % 8 == 0):
+        return False
+    tiles = -(-M // 128) * -(-N // 256)
+    # a long contraction spread over few output tiles needs split-K, which this kernel does not do
+    return tiles >= 64 or K <= 4096
 
 
 def _run(a, b, M, N, K, a_mn: int, b_mn: int, epilogue: int = 0) -> torch.Tensor:
