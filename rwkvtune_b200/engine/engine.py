@@ -64,7 +64,12 @@ class TrainEngine:
         groups = build_param_groups(self.model.named_parameters(), cfg.weight_decay, cfg.lr_2x_patterns)
         if not groups:
             raise RuntimeError("the model has no trainable parameters")
-        self.space = FlatParamSpace(groups, ctx.world_size, dtype, ctx.device)
+        allocator = None
+        if cfg.transport == "p2p" and ctx.world_size > 1 and ctx.device.type == "cuda" and 1 <= stage <= 2:
+            from ..parallel.p2p import symmetric_allocator
+
+            allocator = symmetric_allocator()
+        self.space = FlatParamSpace(groups, ctx.world_size, dtype, ctx.device, allocator)
         self.stage = stage
         self.opt = ZeroOptimizer(self.space, ctx, min(stage, 2), (cfg.beta1, cfg.beta2), cfg.adam_eps, cfg.grad_clip,
                                  cfg.transport)

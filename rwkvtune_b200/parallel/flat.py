@@ -37,7 +37,7 @@ class Segment:
 
 class FlatParamSpace:
     def __init__(self, groups: Sequence[ParamGroupSpec], world_size: int = 1, dtype: torch.dtype = None,
-                 device: torch.device = None):
+                 device: torch.device = None, allocator: Optional[Callable[[int, torch.dtype, torch.device], torch.Tensor]] = None):
         params = [p for g in groups for _, p in g.params]
         if not params:
             raise ValueError("no trainable parameters")
@@ -58,8 +58,11 @@ class FlatParamSpace:
         quantum = ALIGN * world_size
         self.padded = (off + quantum - 1) // quantum * quantum
         self.shard_numel = self.padded // world_size
-        self.params = torch.zeros(self.padded, dtype=self.dtype, device=self.device)
-        self.grads = torch.zeros(self.padded, dtype=self.dtype, device=self.device)
+        alloc = allocator or (lambda n, dt, dev: torch.zeros(n, dtype=dt, device=dev))
+        self.params = alloc(self.padded, self.dtype, self.device)
+        self.grads = alloc(self.padded, self.dtype, self.device)
+        self.params.zero_()
+        self.grads.zero_()
         with torch.no_grad():
             for seg, p in zip(self.segments, params):
                 view = self.params[seg.start:seg.start + seg.numel].view(seg.shape)

@@ -48,7 +48,7 @@ class ZeroOptimizer:
         self._shard_grad = (torch.empty(self.hi - self.lo, dtype=space.dtype, device=dev)
                             if self.stage >= 1 else None)
         self._p2p = None
-        if transport == "p2p" and ctx.world_size > 1:
+        if transport == "p2p" and ctx.world_size > 1 and self.stage >= 1 and space.device.type == "cuda":
             from . import p2p
 
             self._p2p = p2p.FusedZero2(space, ctx, self)
