@@ -76,7 +76,8 @@ def parse():
     ap.add_argument("--ctx-len", type=int, default=4096)
     ap.add_argument("--micro-bsz", type=int, default=8)
     ap.add_argument("--grad-cp", type=int, default=1)
-    ap.add_argument("--transport", default=os.environ.get("RWKVTUNE_TRANSPORT", "nccl"))
+    ap.add_argument("--transport", default=os.environ.get("RWKVTUNE_TRANSPORT", "p2p"),
+                    help="multi-GPU gradient/parameter transport: p2p (fused peer-memory kernels) or nccl")
     return ap.parse_args()
 
 

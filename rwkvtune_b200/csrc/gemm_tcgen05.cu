@@ -133,11 +133,66 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
+constexpr int MAX_RANKS = 16;
+
+// All-gather fused into the GEMM (ZeRO-3): the weight is stored as K-panels, rank p owning columns
+// [p*Kp, (p+1)*Kp) as a contiguous [N, Kp] matrix.  A few CTAs of the same grid copy the panels from
+// the owners' memory (plain peer loads over NVLink) into a local [N, K] staging matrix and raise one
+// flag per panel; the GEMM CTAs walk the contraction panel by panel in arrival order (own panel first)
+// and TMA-load B from the staging matrix as soon as the panel's flag is up.  Each remote byte crosses
+// NVLink once; the transfer of panel p+1 overlaps the MMAs on panel p.
+struct AgParams {
+  const bf16* shard[MAX_RANKS];
+  bf16* staged;
+  int* panel_flag;     // [world], equals `epoch` once the panel has landed
+  int* panel_count;    // [world], monotonically increasing arrival counters
+  int rank, world, epoch, n_copy, Kp;
+};
+
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_gpu(int* p, int v) {
+  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__device__ void ag_copy_role(const AgParams& ag, int N, int K) {
+  const int vec_per_row = ag.Kp / 8;
+  const long long total = (long long)N * vec_per_row;
+  const long long stride = (long long)ag.n_copy * blockDim.x;
+  for (int s = 0; s < ag.world; ++s) {
+    const int p = (ag.rank + s) % ag.world;
+    const uint4* src = reinterpret_cast<const uint4*>(ag.shard[p]);
+    for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < total; v += stride) {
+      const long long row = v / vec_per_row;
+      const int c = (int)(v - row * vec_per_row);
+      const uint4 val = __ldcg(src + v);
+      *reinterpret_cast<uint4*>(ag.staged + row * K + (long long)p * ag.Kp + c * 8) = val;
+    }
+    __threadfence();
+    asm volatile("fence.proxy.async;" ::: "memory");
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const int old = atomicAdd(&ag.panel_count[p], 1);
+      if (old + 1 == ag.epoch * ag.n_copy) st_release_gpu(&ag.panel_flag[p], ag.epoch);
+    }
+  }
+}
+
 // EPI: 0 = plain store, 1 = relu(x)^2
-template <bool A_MN, bool B_MN, int EPI>
+template <bool A_MN, bool B_MN, int EPI, bool AG>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                    const __grid_constant__ CUtensorMap map_c, int M, int N, int K, int* status) {
+                    const __grid_constant__ CUtensorMap map_c, int M, int N, int K, int* status,
+                    const __grid_constant__ AgParams ag) {
+  if (AG && (int)blockIdx.x < ag.n_copy) {   // copy CTAs never touch barriers or tensor memory
+    ag_copy_role(ag, N, K);
+    return;
+  }
+  const int cta = AG ? (int)blockIdx.x - ag.n_copy : (int)blockIdx.x;
+  const int n_cta = AG ? (int)gridDim.x - ag.n_copy : (int)gridDim.x;
   extern __shared__ unsigned char smem_dyn[];
   const uint32_t raw = smem_u32(smem_dyn);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -172,13 +227,33 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int tile = cta; tile < num_tiles && ok; tile += n_cta) {
         const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
         for (int kb = 0; kb < num_kb; ++kb) {
+          int k0 = kb * BK;
+          if (AG) {   // contraction walked panel by panel, starting with the locally owned one
+            const int kb_per_panel = ag.Kp / BK;
+            const int s_idx = kb / kb_per_panel;
+            const int p = (ag.rank + s_idx) % ag.world;
+            k0 = p * ag.Kp + (kb - s_idx * kb_per_panel) * BK;
+            if (kb % kb_per_panel == 0) {
+              bool landed = false;
+              for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
+                if (ld_acquire_gpu(&ag.panel_flag[p]) >= ag.epoch) { landed = true; break; }
+                if ((it & 0xfff) == 0xfff && *reinterpret_cast<volatile int*>(&bars->abort_flag)) break;
+              }
+              if (!landed) {
+                *reinterpret_cast<volatile int*>(&bars->abort_flag) = 1;
+                if (status) atomicCAS(status, 0, 105);
+                ok = false;
+                break;
+              }
+              asm volatile("fence.proxy.async;" ::: "memory");
+            }
+          }
           if (!mbar_wait(&bars->empty[stage], phase ^ 1, bars, status, 101)) { ok = false; break; }
           mbar_expect_tx(&bars->full[stage], STAGE_BYTES);
           const uint32_t sa = base + stage * STAGE_BYTES, sb = sa + A_BYTES;
-          const int k0 = kb * BK;
           if (A_MN) {
 #pragma unroll
             for (int c = 0; c < BM / 64; ++c) tma_load_2d(sa + c * (BK * 128), &map_a, &bars->full[stage], m0 + c * 64, k0);
@@ -206,7 +281,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       uint32_t phase = 0;
       int local = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+      for (int tile = cta; tile < num_tiles && ok; tile += n_cta, ++local) {
         const int acc = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1;
         if (!mbar_wait(&bars->acc_empty[acc], acc_phase ^ 1, bars, status, 102)) { ok = false; break; }
@@ -234,7 +309,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     int local = 0;
     int cbuf = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+    for (int tile = cta; tile < num_tiles && ok; tile += n_cta, ++local) {
       const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
@@ -331,7 +406,7 @@ int make_map(CUtensorMap* map, const void* ptr, long long rows, long long cols, 
 template <bool A_MN, bool B_MN, int EPI>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, int M, int N, int K, int* status,
            int sms, cudaStream_t st) {
-  auto kern = gemm_tcgen05_kernel<A_MN, B_MN, EPI>;
+  auto kern = gemm_tcgen05_kernel<A_MN, B_MN, EPI, false>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
@@ -340,8 +415,28 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, 
   }
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int grid = tiles < sms ? tiles : sms;
-  kern<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(ma, mb, mc, M, N, K, status);
+  AgParams none = {};
+  kern<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(ma, mb, mc, M, N, K, status, none);
   return rwkv_launch_status();
+}
+
+int launch_ag(CUtensorMap ma, CUtensorMap mb, CUtensorMap mc, int M, int N, int K, int* status, int sms,
+              AgParams ag, cudaStream_t st) {
+  auto kern = gemm_tcgen05_kernel<false, false, 0, true>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return RWKV_ERR_CUDA_BASE + (int)e;
+    configured = true;
+  }
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  int n_gemm = sms - ag.n_copy;
+  if (tiles < n_gemm) n_gemm = tiles;
+  const int grid = n_gemm + ag.n_copy;
+  // GEMM CTAs wait for copy CTAs of the same grid: a cooperative launch guarantees they are co-resident
+  void* args[] = {&ma, &mb, &mc, &M, &N, &K, &status, &ag};
+  cudaError_t e = cudaLaunchCooperativeKernel((void*)kern, dim3(grid), dim3(NUM_THREADS), args, SMEM_BYTES, st);
+  return e == cudaSuccess ? rwkv_launch_status() : RWKV_ERR_CUDA_BASE + (int)e;
 }
 
 }  // namespace
@@ -378,4 +473,36 @@ RWKV_EXPORT int rwkv_gemm_bf16_tcgen05(const void* a, const void* b, void* c, in
   if (a_mn && b_mn) return DISPATCH(true, true);
   return DISPATCH(true, false);
 #undef DISPATCH
+}
+
+// y[M,N] = x[M,K] @ W[N,K]^T where W is stored as `world` K-panels, panel p ([N, K/world], row-major) living at
+// shard_ptrs[p] (peer-mapped addresses; shard_ptrs[rank] is local).  `staged` ([N,K] bf16, local) receives the
+// gathered weight and can be reused afterwards (e.g. by the backward pass).  panel_flag / panel_count: `world`
+// device ints each, zero-initialised once; `epoch` must increase by one per call on the same buffers.
+RWKV_EXPORT int rwkv_ag_gemm_bf16_tcgen05(const void* x, const unsigned long long* shard_ptrs, void* staged, void* y,
+                                          int M, int N, int K, int rank, int world, void* panel_flag,
+                                          void* panel_count, int epoch, int n_copy, void* status, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || world <= 0 || world > MAX_RANKS || rank < 0 || rank >= world) return RWKV_ERR_BAD_SHAPE;
+  if (K % world || (K / world) % BK || n_copy <= 0 || epoch <= 0) return RWKV_ERR_BAD_SHAPE;
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  if (n_copy >= sms) return RWKV_ERR_BAD_SHAPE;
+  CUtensorMap ma, mb, mc;
+  int r = make_map(&ma, x, M, K, K, BK, BM);
+  if (r) return r;
+  r = make_map(&mb, staged, N, K, K, BK, BN);
+  if (r) return r;
+  r = make_map(&mc, y, M, N, N, 64, BM);
+  if (r) return r;
+  AgParams ag = {};
+  for (int i = 0; i < world; ++i) ag.shard[i] = reinterpret_cast<const bf16*>(shard_ptrs[i]);
+  ag.staged = (bf16*)staged;
+  ag.panel_flag = (int*)panel_flag;
+  ag.panel_count = (int*)panel_count;
+  ag.rank = rank; ag.world = world; ag.epoch = epoch; ag.n_copy = n_copy; ag.Kp = K / world;
+  return launch_ag(ma, mb, mc, M, N, K, (int*)status, sms, ag, (cudaStream_t)stream);
 }

@@ -61,11 +61,16 @@ class TrainEngine:
             as_infctx(self.model)
         self.model.train()
         stage = resolve_stage(cfg.strategy)
+        self.zero3 = None
+        if stage == 3 and ctx.world_size > 1 and ctx.device.type == "cuda" and dtype == torch.bfloat16:
+            from ..parallel.zero3 import Zero3ShardedLinears
+
+            self.zero3 = Zero3ShardedLinears(self.model, ctx)
         groups = build_param_groups(self.model.named_parameters(), cfg.weight_decay, cfg.lr_2x_patterns)
         if not groups:
             raise RuntimeError("the model has no trainable parameters")
         allocator = None
-        if cfg.transport == "p2p" and ctx.world_size > 1 and ctx.device.type == "cuda" and 1 <= stage <= 2:
+        if cfg.transport == "p2p" and ctx.world_size > 1 and ctx.device.type == "cuda" and stage >= 1:
             from ..parallel.p2p import symmetric_allocator
 
             allocator = symmetric_allocator()

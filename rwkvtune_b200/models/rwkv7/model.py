@@ -31,6 +31,11 @@ class Linear(nn.Linear):
         super().__init__(in_features, out_features, bias=False, device=device, dtype=dtype)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:  # noqa: D401
+        sw = getattr(self, "_sharded", None)
+        if sw is not None:   # ZeRO-3: weight lives as K-panels across ranks, gathered inside the GEMM
+            from ...parallel.zero3 import ag_linear
+
+            return ag_linear(x, sw)
         return ops.linear(x, self.weight)
 
 

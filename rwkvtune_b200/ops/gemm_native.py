@@ -73,3 +73,31 @@ def mm_nn(x: torch.Tensor, w: torch.Tensor, epilogue: int = 0) -> torch.Tensor:
 def mm_tn(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     """``a[Kc,M]^T @ b[Kc,N]`` (weight gradients: contraction over the token dimension)"""
     return _run(a, b, a.shape[1], b.shape[1], a.shape[0], 1, 1)
+
+
+class GatheredWeight:
+    """A ``[N, K]`` weight stored as ``world`` K-panels (one per rank) plus the local staging matrix the
+    all-gather-fused GEMM fills.  ``shard_ptrs`` are device addresses of every rank's ``[N, K/world]`` panel as
+    mapped in this process (symmetric memory); on one GPU they can be plain local tensors (used by tests)."""
+
+    def __init__(self, shard_ptrs, rank: int, world: int, N: int, K: int, device, n_copy: int = 16):
+        import ctypes
+
+        self.rank, self.world, self.N, self.K = rank, world, N, K
+        self.ptrs = (ctypes.c_ulonglong * world)(*[int(p) for p in shard_ptrs])
+        self.staged = torch.empty(N, K, dtype=torch.bfloat16, device=device)
+        self.flags = torch.zeros(world, dtype=torch.int32, device=device)
+        self.counts = torch.zeros(world, dtype=torch.int32, device=device)
+        self.epoch = 0
+        self.n_copy = n_copy
+
+
+def ag_mm_nt(x: torch.Tensor, gw: GatheredWeight) -> torch.Tensor:
+    """``x [M,K] @ W^T`` with the all-gather of ``W`` fused into the GEMM; afterwards ``gw.staged`` holds ``W``."""
+    M = x.shape[0]
+    y = torch.empty(M, gw.N, dtype=torch.bfloat16, device=x.device)
+    gw.epoch += 1
+    _ext.call("rwkv_ag_gemm_bf16_tcgen05", _ext.ptr(x), gw.ptrs, _ext.ptr(gw.staged), _ext.ptr(y), _ext.i32(M),
+              _ext.i32(gw.N), _ext.i32(gw.K), _ext.i32(gw.rank), _ext.i32(gw.world), _ext.ptr(gw.flags),
+              _ext.ptr(gw.counts), _ext.i32(gw.epoch), _ext.i32(gw.n_copy), _ext.ptr(_status(x.device)), _ext.stream())
+    return y

@@ -82,6 +82,13 @@ class LoraLinear(nn.Module):
         return self.base_layer.weight + (self.lora_B @ self.lora_A) * self.scaling
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        sw = getattr(self, "_sharded", None)
+        if sw is not None:   # ZeRO-3 sharded frozen base weight
+            from ...parallel.zero3 import ag_linear, lora_ag_linear
+
+            if self.disabled:
+                return ag_linear(x, sw)
+            return lora_ag_linear(x, sw, self.lora_A, self.lora_B, self.scaling)
         if self.disabled or self.merged:
             return self.base_layer(x)
         if isinstance(self.lora_dropout, nn.Dropout) and self.training:

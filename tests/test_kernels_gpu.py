@@ -266,3 +266,24 @@ def test_tcgen05_gemm_relu_sq_epilogue():
     ref_out = torch.relu(a.float() @ b.float().t()) ** 2
     assert gemm_native.check_status() == 0
     assert (out.float() - ref_out).abs().max().item() <= 2e-2 * ref_out.abs().max().item() + 1e-2
+
+
+@pytest.mark.parametrize("M,N,K,W,rank", [(512, 512, 512, 4, 1), (1024, 2560, 2560, 8, 5), (384, 320, 256, 2, 0)])
+def test_ag_fused_gemm_emulated_panels(M, N, K, W, rank):
+    """K-panels of the weight held in separate buffers (as if on W ranks); the fused kernel must gather them into
+    the staging matrix and produce x @ W^T.  Called twice to check the epoch-based panel flags."""
+    from rwkvtune_b200.ops import gemm_native
+    torch.manual_seed(K)
+    x = torch.randn(M, K, device="cuda").to(BF)
+    w = (torch.randn(N, K, device="cuda") * 0.1).to(BF)
+    Kp = K // W
+    shards = [w[:, p * Kp:(p + 1) * Kp].contiguous() for p in range(W)]
+    gw = gemm_native.GatheredWeight([s.data_ptr() for s in shards], rank, W, N, K, x.device, n_copy=8)
+    ref_out = x.float() @ w.float().t()
+    for _ in range(2):
+        gw.staged.zero_()
+        y = gemm_native.ag_mm_nt(x, gw)
+        torch.cuda.synchronize()
+        assert gemm_native.check_status() == 0
+        assert torch.equal(gw.staged, w)
+        assert (y.float() - ref_out).abs().max().item() <= 2e-2 * ref_out.abs().max().item() + 1e-2

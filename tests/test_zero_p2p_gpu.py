@@ -128,3 +128,56 @@ def test_p2p_transport_matches_nccl_two_ranks(tmp_path):
     assert rec["max_param_diff"] <= 2e-2 * rec["param_scale"] + 1e-3, rec
     for x, y in zip(rec["losses_nccl"], rec["losses_p2p"]):
         assert abs(x - y) < 5e-2, rec
+
+
+_WORKER_Z3 = r'''
+import os, sys, json, torch
+sys.path.insert(0, os.environ["RWKV_ROOT"])
+from rwkvtune_b200.engine import EngineConfig, TrainEngine
+from rwkvtune_b200.models import RWKVConfig, RWKV7Model
+from rwkvtune_b200.parallel import init_distributed
+from rwkvtune_b200.peft import LoraConfig, get_peft_model
+from rwkvtune_b200.ops import gemm_native
+ctx = init_distributed("gpu")
+out = {}
+for strategy in ("deepspeed_stage_2", "deepspeed_stage_3"):
+    torch.manual_seed(0)
+    cfg = RWKVConfig(n_layer=2, n_embd=256, vocab_size=1024, dim_att_lora=32, dim_gate_lora=64, dim_mv_lora=32)
+    model = RWKV7Model(cfg)
+    with torch.no_grad():
+        for n, p in model.named_parameters():
+            if n.endswith(("output.weight", "ffn.value.weight")):
+                p.normal_(0, 0.05)
+    model = get_peft_model(model, LoraConfig(r=16, lora_alpha=32))
+    eng = TrainEngine(model, EngineConfig(lr_init=2e-3, strategy=strategy, precision="bf16", grad_cp=1, transport="p2p"), ctx)
+    if strategy.endswith("3"):
+        assert eng.zero3 is not None and len(eng.zero3.sharded) == 12, "stage 3 did not shard the projection weights"
+    g = torch.Generator().manual_seed(100 + ctx.rank)
+    losses = []
+    for step in range(4):
+        idx = torch.randint(0, 1024, (2, 128), generator=g).to(ctx.device)
+        losses.append(float(eng.train_step(idx, idx.roll(-1, 1), 2e-3)))
+    torch.cuda.synchronize()
+    out[strategy] = losses
+    assert gemm_native.check_status() == 0
+torch.distributed.barrier()
+if ctx.rank == 0:
+    print(json.dumps(out))
+torch.distributed.destroy_process_group()
+'''
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_zero3_lora_fused_allgather_gemm_matches_stage2(tmp_path):
+    script = tmp_path / "worker_z3.py"
+    script.write_text(_WORKER_Z3)
+    env = dict(os.environ, RWKV_ROOT=ROOT, NCCL_NVLS_ENABLE="0")
+    res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                          "--master-addr", "127.0.0.1", "--master-port", "29534", str(script)],
+                         capture_output=True, text=True, env=env, timeout=300)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-3000:]
+    import json
+    rec = json.loads([l for l in res.stdout.splitlines() if l.startswith("{")][-1])
+    for x, y in zip(rec["deepspeed_stage_2"], rec["deepspeed_stage_3"]):
+        assert abs(x - y) < 5e-2, rec
+    assert rec["deepspeed_stage_3"][-1] < rec["deepspeed_stage_3"][0]
