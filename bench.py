@@ -76,6 +76,9 @@ def parse():
     ap.add_argument("--ctx-len", type=int, default=4096)
     ap.add_argument("--micro-bsz", type=int, default=8)
     ap.add_argument("--grad-cp", type=int, default=1)
+    ap.add_argument("--grad-cp-layers", default="auto",
+                    help="with --grad-cp 1: 'all' (recompute every block, the reference behaviour), an integer k "
+                         "(recompute only the first k blocks) or 'auto' (as few as fit in HBM)")
     ap.add_argument("--transport", default=os.environ.get("RWKVTUNE_TRANSPORT", "p2p"),
                     help="multi-GPU gradient/parameter transport: p2p (fused peer-memory kernels) or nccl")
     return ap.parse_args()
@@ -115,8 +118,15 @@ def run_ours(a):
         torch.cuda.synchronize()
 
     # ---- device-timed arm: inputs already resident
+    cp_layers = cfg.n_layer if a.grad_cp else 0
     for i in range(a.warmup):
         eng.train_step(dev_ids[i], dev_lab[i], 3e-4)
+        if i == 0 and a.grad_cp and a.grad_cp_layers != "all":
+            torch.cuda.synchronize()
+            if a.grad_cp_layers == "auto":
+                cp_layers = eng.autotune_checkpointing(B, T)
+            else:
+                cp_layers = model.config.grad_cp_layers = int(a.grad_cp_layers)
     sampler = ClockSampler(ctx.local_rank)
     sync()
     sampler.start()
@@ -157,7 +167,8 @@ def run_ours(a):
             "impl": "ours", "final_loss": final_loss,
             "config": {"model": f"rwkv7-{a.model}", "global_batch": B * ctx.world_size, "seq_len": T,
                        "parallelism": f"zero2-dp{ctx.world_size}" if ctx.world_size > 1 else "single",
-                       "grad_cp": a.grad_cp, "transport": a.transport, "optimizer": "AdamW fp32 master, clip 1.0",
+                       "grad_cp": a.grad_cp, "checkpointed_layers": cp_layers,
+                       "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2**30, 1), "transport": a.transport, "optimizer": "AdamW fp32 master, clip 1.0",
                        "l2_flush": "per-step activations and weights (>3 GB) exceed the 126 MB L2"},
             "clocks": clocks,
             "e2e": {"value": tokens / (ms_e2e / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": 2 * B * T * 8,

@@ -47,6 +47,7 @@ class EngineConfig:
     truncated_bptt: bool = True
     transport: str = "nccl"
     l2wrap: bool = True
+    grad_cp_layers: Optional[object] = None   # None = all layers when grad_cp=1; int k = first k layers; "auto"
 
 
 class TrainEngine:
@@ -57,6 +58,8 @@ class TrainEngine:
             dtype = torch.float32
         self.model = model.to(device=ctx.device, dtype=dtype)
         self.model.config.grad_cp = cfg.grad_cp
+        if isinstance(cfg.grad_cp_layers, int):
+            self.model.config.grad_cp_layers = cfg.grad_cp_layers
         if cfg.train_type == "infctx":
             as_infctx(self.model)
         self.model.train()
@@ -81,6 +84,31 @@ class TrainEngine:
         self.micro_step = 0
         self.optimizer_steps = 0
         self.tokens_seen = 0
+
+    # ------------------------------------------------------------------ memory-aware checkpointing
+    SAVED_UNITS_PER_LAYER = 38.0   # [tokens, n_embd] bf16 tensors a block keeps for backward without checkpointing
+
+    def autotune_checkpointing(self, batch: int, seq_len: int, reserve_fraction: float = 0.10) -> int:
+        """With ``grad_cp=1`` the reference recomputes every block in backward.  180 GB of HBM usually has
+        room to keep the activations of most blocks instead; this picks how many blocks still need
+        checkpointing.  Call it after one full-checkpointing step so the peak of that step is known.
+        Returns the number of checkpointed layers (also stored in ``model.config.grad_cp_layers``)."""
+        cfg = self.model.config
+        L = cfg.n_layer
+        if self.ctx.device.type != "cuda" or not self.cfg.grad_cp:
+            return L
+        total = torch.cuda.get_device_properties(self.ctx.device).total_memory
+        peak = torch.cuda.max_memory_allocated(self.ctx.device)
+        per_layer = self.SAVED_UNITS_PER_LAYER * batch * seq_len * cfg.n_embd * 2
+        budget = total * (1.0 - reserve_fraction) - peak
+        free_layers = int(max(0, budget) // per_layer)
+        n_cp = max(0, L - free_layers)
+        if self.ctx.world_size > 1:   # every rank must make the same choice
+            t = torch.tensor([n_cp], device=self.ctx.device)
+            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+            n_cp = int(t)
+        cfg.grad_cp_layers = n_cp
+        return n_cp
 
     # ------------------------------------------------------------------ losses
     def _loss_normal(self, idx: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:

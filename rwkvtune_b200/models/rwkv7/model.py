@@ -245,8 +245,9 @@ class RWKV7Model(GenerationMixin, nn.Module):
         x = self.emb(idx)
         v_first = torch.empty_like(x)
         cp = self._use_checkpoint()
-        for block in self.blocks:
-            if cp:
+        n_cp = getattr(self.config, "grad_cp_layers", None)   # None: every layer; k: only the first k layers
+        for i, block in enumerate(self.blocks):
+            if cp and (n_cp is None or i < n_cp):
                 x, v_first = _checkpoint(_block_plain, block, x, v_first, use_reentrant=False)
             else:
                 x, v_first = _block_plain(block, x, v_first)
