@@ -14,6 +14,7 @@ from typing import Callable, Dict, Optional, Sequence
 
 import torch
 
+from .. import ops
 from ..models.rwkv7.model_infctx import as_infctx
 from ..parallel.bootstrap import DistContext
 from ..parallel.flat import FlatParamSpace, build_param_groups
@@ -168,6 +169,7 @@ class TrainEngine:
             self.opt.step(lr)
             self.opt.zero_grad()
             self.optimizer_steps += 1
+            ops.bump_param_epoch()
         return loss
 
     def backward_and_step(self, loss: torch.Tensor, lr: float) -> bool:
@@ -180,6 +182,7 @@ class TrainEngine:
             self.opt.step(lr)
             self.opt.zero_grad()
             self.optimizer_steps += 1
+            ops.bump_param_epoch()
             return True
         return False
 

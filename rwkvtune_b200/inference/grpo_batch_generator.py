@@ -22,10 +22,58 @@ import torch
 from .core import TokenSampler, apply_repetition_penalty
 
 
+class _DecodeGraph:
+    """One decode step (all layers + head) for a fixed number of sequences, captured as a CUDA graph.
+    The recurrent state lives in static buffers that the captured step updates in place, so a replay
+    costs one launch instead of several hundred."""
+
+    def __init__(self, gen: "GRPOBatchGenerator", n: int):
+        from ..ops import cuda_ops
+
+        self.gen, self.n = gen, n
+        dev = gen.device
+        self.tok = torch.zeros(n, 1, dtype=torch.long, device=dev)
+        self.state = gen._zero_state(n)
+        cuda_ops.INPLACE_STATE = True
+        try:
+            side = torch.cuda.Stream(device=dev)
+            side.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(side):
+                for _ in range(2):
+                    self._body()
+            torch.cuda.current_stream(dev).wait_stream(side)
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph):
+                self.logits = self._body()
+        finally:
+            cuda_ops.INPLACE_STATE = False
+
+    def _body(self) -> torch.Tensor:
+        logits, (a, s, f) = self.gen._forward(self.tok, self.state)
+        for dst, src in zip(self.state[0], a):
+            dst.copy_(src)
+        for dst, src in zip(self.state[1], s):
+            if dst.data_ptr() != src.data_ptr():
+                dst.copy_(src)
+        for dst, src in zip(self.state[2], f):
+            dst.copy_(src)
+        return logits
+
+    def load_state(self, state) -> None:
+        for part_dst, part_src in zip(self.state, state):
+            for dst, src in zip(part_dst, part_src):
+                dst.copy_(src)
+
+    def step(self, tok: torch.Tensor) -> torch.Tensor:
+        self.tok.copy_(tok[:, None])
+        self.graph.replay()
+        return self.logits
+
+
 class GRPOBatchGenerator:
     def __init__(self, model, tokenizer=None, device=None, eos_token_id=None, prefill_chunk_size: int = 2048,
                  max_prefill_batch_size: int = -1, max_decode_batch_size: int = -1, sync_every: int = 8,
-                 verbose: bool = False):
+                 verbose: bool = False, use_cuda_graph: Optional[bool] = None):
         self.model = model
         self.tokenizer = tokenizer
         self.device = torch.device(device) if device is not None else next(model.parameters()).device
@@ -44,6 +92,16 @@ class GRPOBatchGenerator:
         if tokenizer is not None and hasattr(tokenizer, "vocab_size"):
             self.max_valid_token_id = int(tokenizer.vocab_size) - 1
         self.last_stats: Dict[str, float] = {}
+        sharded = any(getattr(m, "_sharded", None) is not None for m in model.modules())
+        self.use_cuda_graph = (self.device.type == "cuda" and not sharded) if use_cuda_graph is None else use_cuda_graph
+        self._graphs: Dict[int, _DecodeGraph] = {}
+
+    def _graph_for(self, n: int) -> "_DecodeGraph":
+        if n not in self._graphs:
+            if len(self._graphs) >= 6:
+                self._graphs.pop(next(iter(self._graphs)))
+            self._graphs[n] = _DecodeGraph(self, n)
+        return self._graphs[n]
 
     # ------------------------------------------------------------------ state helpers
     def _zero_state(self, n: int):
@@ -133,6 +191,10 @@ class GRPOBatchGenerator:
         finished = torch.zeros(n, dtype=torch.bool, device=dev)
         rows = torch.arange(n, device=dev)          # original row of each live path
         steps = 0
+        graph = None
+        if self.use_cuda_graph:
+            graph = self._graph_for(n)
+            graph.load_state(state)
         try:
             for step in range(max_new_tokens):
                 lg = logits.float()
@@ -161,9 +223,15 @@ class GRPOBatchGenerator:
                     if n_done * 2 >= rows.numel():   # compact: drop finished paths from the decode batch
                         keep = (~fin_live).nonzero(as_tuple=True)[0]
                         rows = rows.index_select(0, keep)
-                        state = self._select(state, keep)
+                        state = self._select(graph.state if graph is not None else state, keep)
                         tok = tok.index_select(0, keep)
-                logits, state = self._forward(tok[:, None], state)
+                        if graph is not None:
+                            graph = self._graph_for(int(keep.numel()))
+                            graph.load_state(state)
+                if graph is not None:
+                    logits = graph.step(tok)
+                else:
+                    logits, state = self._forward(tok[:, None], state)
         finally:
             TokenSampler.set_max_valid_token_id(prev_max)
             if was_training:

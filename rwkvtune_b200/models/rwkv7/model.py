@@ -119,6 +119,14 @@ class RWKV7TimeMix(nn.Module):
 
     def mix_matrix(self) -> torch.Tensor:
         C = self.x_r.shape[-1]
+        if not torch.is_grad_enabled():   # inference: one cached [6, C] parameter-like tensor, rebuilt when weights change
+            key = tuple(p._version for p in (self.x_r, self.x_w, self.x_k, self.x_v, self.x_a, self.x_g)) + (ops.param_epoch(),)
+            cached = getattr(self, "_mix_cache", None)
+            if cached is None or cached[0] != key or cached[1].device != self.x_r.device:
+                m = torch.cat([self.x_r, self.x_w, self.x_k, self.x_v, self.x_a, self.x_g], dim=0).reshape(6, C)
+                cached = (key, torch.nn.Parameter(m.detach().clone(), requires_grad=False))
+                object.__setattr__(self, "_mix_cache", cached)
+            return cached[1]
         return torch.cat([self.x_r, self.x_w, self.x_k, self.x_v, self.x_a, self.x_g], dim=0).reshape(6, C)
 
     def forward(self, x, ln_w, ln_b, v_first, x_prev=None, wkv_state=None, want_state: bool = False):
@@ -171,7 +179,7 @@ class RWKV7ChannelMix(nn.Module):
             self.value.weight.zero_()
 
     def forward(self, x, ln_w, ln_b, x_prev=None, want_state: bool = False):
-        mixed, last = ops.ln_shift_mix(x, ln_w, ln_b, self.x_k.reshape(1, -1), x_prev)
+        mixed, last = ops.ln_shift_mix(x, ln_w, ln_b, self.x_k, x_prev)
         if type(self.key) is Linear:
             hidden = ops.linear_relu_sq(mixed[0], self.key.weight)
         else:   # wrapped (e.g. LoRA): activation applied separately

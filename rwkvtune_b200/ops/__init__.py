@@ -34,6 +34,25 @@ _KERNELS: Dict[str, bool] = {
 }
 
 
+def param_epoch() -> int:
+    """Counter bumped whenever parameters are rewritten by the optimiser kernels."""
+    from . import cuda_ops_epoch
+
+    return cuda_ops_epoch.EPOCH[0]
+
+
+def bump_param_epoch() -> None:
+    from . import cuda_ops_epoch
+
+    cuda_ops_epoch.EPOCH[0] += 1
+    try:
+        from . import cuda_ops
+
+        cuda_ops.bump_param_epoch()
+    except Exception:
+        pass
+
+
 def set_kernel_enabled(name: str, enabled: bool) -> None:
     if name not in _KERNELS:
         raise KeyError(f"unknown kernel family {name!r}; known: {sorted(_KERNELS)}")

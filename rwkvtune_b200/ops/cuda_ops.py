@@ -15,6 +15,7 @@ from . import reference as ref
 from ._ext import call, f32, i32, i64, ptr, stream
 
 BF16 = torch.bfloat16
+INPLACE_STATE = False   # set by the rollout engine while decoding: WKV state tensors are updated in place
 
 
 def _c(t: torch.Tensor, dtype=None) -> torch.Tensor:
@@ -37,7 +38,10 @@ class _WKV7(torch.autograd.Function):
         NC = (T + 15) // 16
         sa = torch.empty(B, T, C, dtype=torch.float32, device=r.device) if need_grad else None
         ckpt = torch.empty(B, H, NC, 64, 64, dtype=torch.float32, device=r.device) if need_grad else None
-        s_final = torch.empty(B, H, 64, 64, dtype=torch.float32, device=r.device) if return_state else None
+        if return_state and INPLACE_STATE and s0 is not None and not need_grad and s0.data_ptr() == state.data_ptr():
+            s_final = s0        # decode: the kernel reads a head's state before it writes it, so in/out may alias
+        else:
+            s_final = torch.empty(B, H, 64, 64, dtype=torch.float32, device=r.device) if return_state else None
         call("rwkv_wkv7_forward", ptr(r), ptr(w), ptr(k), ptr(v), ptr(a), ptr(b), ptr(s0), ptr(y), ptr(sa),
              ptr(ckpt), ptr(s_final), i32(B), i32(T), i32(H), stream())
         if need_grad:
@@ -48,7 +52,6 @@ class _WKV7(torch.autograd.Function):
         y = y if out_dtype == BF16 else y.to(out_dtype)
         if return_state:
             return y, s_final
-        ctx.mark_non_differentiable()
         return y, None
 
     @staticmethod
@@ -83,8 +86,35 @@ def _strip_for(rows_per_batch: int, batch: int, target_ctas: int = 592) -> int:
     return (strip + 3) // 4 * 4
 
 
+_PARAM_EPOCH = 0
+_F32_CACHE = {}
+
+
+def bump_param_epoch() -> None:
+    """Called after parameters were rewritten behind autograd's back (the optimiser kernels write through raw
+    pointers): cached fp32 copies of small parameters are refreshed on next use."""
+    global _PARAM_EPOCH
+    _PARAM_EPOCH += 1
+
+
 def _f32(t: torch.Tensor) -> torch.Tensor:
-    return _c(t.detach().reshape(-1), torch.float32)
+    """Flat fp32 copy of a small per-channel parameter.  Copies of ``nn.Parameter`` objects are cached (same
+    storage for the life of the parameter, refreshed in place after each optimiser step), which removes a
+    dozen tiny conversion kernels per layer and keeps addresses stable for CUDA-graph replay."""
+    if not isinstance(t, torch.nn.Parameter):
+        return _c(t.detach().reshape(-1), torch.float32)
+    key = (t.data_ptr(), t.numel(), t.dtype)
+    stamp = (_PARAM_EPOCH, t._version)
+    hit = _F32_CACHE.get(key)
+    if hit is not None and hit[0] == stamp:
+        return hit[1]
+    if hit is not None:
+        hit[1].copy_(t.detach().reshape(-1))
+        _F32_CACHE[key] = (stamp, hit[1])
+        return hit[1]
+    out = t.detach().reshape(-1).float().contiguous()
+    _F32_CACHE[key] = (stamp, out)
+    return out
 
 
 def _param_grad(partials: torch.Tensor, index: int, like: torch.Tensor) -> torch.Tensor:
@@ -96,9 +126,9 @@ class _LnShiftMix(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, ln_w, ln_b, mix, prev, eps):
         B, T, C = x.shape
-        K = mix.shape[0]
+        K = mix.numel() // C
         xb = _c(x, BF16)
-        w32, b32, m32 = _f32(ln_w), _f32(ln_b), _c(mix.detach().reshape(K, C), torch.float32)
+        w32, b32, m32 = _f32(ln_w), _f32(ln_b), _f32(mix).reshape(K, C)
         pv = None if prev is None else _c(prev, BF16)
         outs = torch.empty(K, B, T, C, dtype=BF16, device=x.device)
         last = torch.empty(B, C, dtype=BF16, device=x.device)
@@ -134,9 +164,9 @@ class _LnShiftMix(torch.autograd.Function):
 
 
 def ln_shift_mix(x, ln_w, ln_b, mix, prev=None, eps: float = ref.LAYERNORM_EPS):
-    K = mix.shape[0]
+    K = mix.numel() // x.shape[-1]
     if K not in (1, 6) or x.shape[-1] % 64:
-        return ref.ln_shift_mix(x, ln_w, ln_b, mix, prev, eps)
+        return ref.ln_shift_mix(x, ln_w, ln_b, mix.reshape(K, -1), prev, eps)
     return _LnShiftMix.apply(x, ln_w, ln_b, mix, prev, eps)
 
 

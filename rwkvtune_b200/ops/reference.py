@@ -68,6 +68,7 @@ def ln_shift_mix(x, ln_w, ln_b, mix, prev: Optional[torch.Tensor] = None, eps: f
     """
     h = F.layer_norm(x.float(), (x.shape[-1],), ln_w.float(), ln_b.float(), eps)
     delta = token_shift(h, None if prev is None else prev.float()) - h
+    mix = mix.reshape(-1, x.shape[-1])
     outs = h.unsqueeze(0) + delta.unsqueeze(0) * mix.float().reshape(mix.shape[0], 1, 1, -1)
     return outs.to(x.dtype), h[:, -1].to(x.dtype)
 
