@@ -61,6 +61,10 @@ def bench_wkv7(B, T, C, out):
     y, _ = ops.wkv7(*ins, 64)
     gy = torch.randn_like(y)
     ms_bwd = timeit(lambda: torch.autograd.grad(y, ins, gy, retain_graph=True))
+    from rwkvtune_b200.ops import cuda_ops
+    if hasattr(cuda_ops, "wkv7_tc_forward"):
+        with torch.no_grad():
+            out["wkv7_tc_fwd_ms"] = timeit(lambda: cuda_ops.wkv7_tc_forward(*ins, save_chunk_states=True))
     out["wkv7_fwd_nograd_ms"] = ms_inf
     out["wkv7_fwd_train_ms"] = ms_fwd
     out["wkv7_bwd_ms"] = ms_bwd

@@ -447,3 +447,19 @@ def linear_relu_sq(x, weight):
     if x.dtype == BF16 and weight.dtype == BF16 and gemm_native.native_ok(x2 if x2.is_contiguous() else x2.contiguous(), weight, "nt"):
         return _LinearReluSq.apply(x, weight)
     return relu_squared(linear(x, weight))
+
+
+# =============================================================================== WKV7, chunked tensor-core form
+def wkv7_tc_forward(r, w, k, v, a, b, state=None, return_state=False, save_chunk_states=False):
+    """Forward only (no autograd): returns ``(y, final_state or None, chunk_start_states or None)``."""
+    B, T, C = r.shape
+    H = C // 64
+    r, w, k, v, a, b = (_c(t, BF16) for t in (r, w, k, v, a, b))
+    s0 = None if state is None else _c(state, torch.float32)
+    y = torch.empty(B, T, C, dtype=BF16, device=r.device)
+    NC = (T + 15) // 16
+    cs = torch.empty(B, H, NC, 64, 64, dtype=BF16, device=r.device) if save_chunk_states else None
+    sf = torch.empty(B, H, 64, 64, dtype=torch.float32, device=r.device) if return_state else None
+    call("rwkv_wkv7_tc_forward", ptr(r), ptr(w), ptr(k), ptr(v), ptr(a), ptr(b), ptr(s0), ptr(y), ptr(cs), ptr(sf),
+         i32(B), i32(T), i32(H), stream())
+    return y, sf, cs

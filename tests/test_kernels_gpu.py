@@ -287,3 +287,18 @@ def test_ag_fused_gemm_emulated_panels(M, N, K, W, rank):
         assert gemm_native.check_status() == 0
         assert torch.equal(gw.staged, w)
         assert (y.float() - ref_out).abs().max().item() <= 2e-2 * ref_out.abs().max().item() + 1e-2
+
+
+@pytest.mark.parametrize("B,T,H,with_state", [(2, 64, 2, False), (1, 37, 3, True), (2, 256, 1, True)])
+def test_wkv7_tensor_core_forward(B, T, H, with_state):
+    from rwkvtune_b200.ops import cuda_ops
+    ins = _wkv_inputs(B, T, H, seed=5)
+    s0 = (torch.randn(B, H, 64, 64, device="cuda") * 0.1) if with_state else None
+    y, sT, cs = cuda_ops.wkv7_tc_forward(*ins, state=s0, return_state=True, save_chunk_states=True)
+    y_ref, sT_ref = ref.wkv7(*[t.float() for t in ins], 64, s0)
+    rel = ((y.float() - y_ref).norm() / y_ref.norm()).item()
+    assert rel < 1.5e-2, rel
+    rel_s = ((sT - sT_ref).norm() / sT_ref.norm()).item()
+    assert rel_s < 1.5e-2, rel_s
+    if with_state:
+        assert torch.allclose(cs[:, :, 0].float(), s0, atol=2e-2, rtol=2e-2)
