@@ -48,6 +48,7 @@ def timeit(fn, warmup=3, iters=10):
 
 
 def bench_wkv7(B, T, C, out):
+    from rwkvtune_b200.ops import cuda_ops
     H = C // 64
     r, k, v = (torch.randn(B, T, C, device="cuda").to(BF) for _ in range(3))
     w = (-torch.nn.functional.softplus(-(torch.randn(B, T, C, device="cuda") * 2 - 1)) - 0.5).to(BF)
@@ -55,21 +56,24 @@ def bench_wkv7(B, T, C, out):
     a = (-kk).to(BF)
     b = (kk * torch.rand_like(kk)).to(BF)
     ins = [t.requires_grad_(True) for t in (r, w, k, v, a, b)]
-    with torch.no_grad():
-        ms_inf = timeit(lambda: ops.wkv7(*ins, 64))
-    ms_fwd = timeit(lambda: ops.wkv7(*ins, 64))
-    y, _ = ops.wkv7(*ins, 64)
-    gy = torch.randn_like(y)
-    ms_bwd = timeit(lambda: torch.autograd.grad(y, ins, gy, retain_graph=True))
-    from rwkvtune_b200.ops import cuda_ops
-    if hasattr(cuda_ops, "wkv7_tc_forward"):
-        with torch.no_grad():
-            out["wkv7_tc_fwd_ms"] = timeit(lambda: cuda_ops.wkv7_tc_forward(*ins, save_chunk_states=True))
-    out["wkv7_fwd_nograd_ms"] = ms_inf
-    out["wkv7_fwd_train_ms"] = ms_fwd
-    out["wkv7_bwd_ms"] = ms_bwd
+    prev = cuda_ops.WKV7_IMPL
     flop = 4 * 2 * B * T * H * 64 * 64
-    out["wkv7_fwd_fp32_tflops"] = flop / ms_inf / 1e9
+    try:
+        for impl in ("simt", "tc"):
+            cuda_ops.WKV7_IMPL = impl
+            with torch.no_grad():
+                ms_inf = timeit(lambda: ops.wkv7(*ins, 64))
+            ms_fwd = timeit(lambda: ops.wkv7(*ins, 64))
+            y, _ = ops.wkv7(*ins, 64)
+            gy = torch.randn_like(y)
+            ms_bwd = timeit(lambda: torch.autograd.grad(y, ins, gy, retain_graph=True))
+            out[f"wkv7_{impl}_fwd_nograd_ms"] = ms_inf
+            out[f"wkv7_{impl}_fwd_train_ms"] = ms_fwd
+            out[f"wkv7_{impl}_bwd_ms"] = ms_bwd
+            out[f"wkv7_{impl}_fwd_recurrence_tflops"] = flop / ms_inf / 1e9
+            del y
+    finally:
+        cuda_ops.WKV7_IMPL = prev
 
 
 def bench_elementwise(B, T, C, out, hbm):

@@ -69,12 +69,69 @@ class _WKV7(torch.autograd.Function):
         return (*grads, ds0, None)
 
 
+def _tc_ws(B, T, H, mode, device):
+    n = B * H * ((T + 15) // 16) * (10496 if mode == 0 else 7424)
+    return torch.empty(n, dtype=torch.uint8, device=device)
+
+
+class _WKV7TC(torch.autograd.Function):
+    """Chunked tensor-core WKV7 (16-step chunks).  Saves the bf16 state at the start of every chunk; the
+    backward recomputes the intra-chunk quantities from the inputs and those states."""
+
+    @staticmethod
+    def forward(ctx, r, w, k, v, a, b, state, return_state: bool):
+        B, T, C = r.shape
+        H = C // 64
+        out_dtype = r.dtype
+        r, w, k, v, a, b = (_c(t, BF16) for t in (r, w, k, v, a, b))
+        s0 = None if state is None else _c(state, torch.float32)
+        need_grad = any(ctx.needs_input_grad[:7])
+        NC = (T + 15) // 16
+        y = torch.empty(B, T, C, dtype=BF16, device=r.device)
+        cs = torch.empty(B, H, NC, 64, 64, dtype=BF16, device=r.device) if need_grad else None
+        s_final = torch.empty(B, H, 64, 64, dtype=torch.float32, device=r.device) if return_state else None
+        ws = _tc_ws(B, T, H, 0, r.device)
+        call("rwkv_wkv7_tc_forward", ptr(r), ptr(w), ptr(k), ptr(v), ptr(a), ptr(b), ptr(s0), ptr(y), ptr(cs),
+             ptr(s_final), ptr(ws), i32(B), i32(T), i32(H), stream())
+        if need_grad:
+            ctx.save_for_backward(r, w, k, v, a, b, cs)
+        ctx.has_state = state is not None
+        ctx.out_dtype = out_dtype
+        ctx.shape = (B, T, H)
+        y = y if out_dtype == BF16 else y.to(out_dtype)
+        return y, s_final
+
+    @staticmethod
+    def backward(ctx, dy, ds_final):
+        r, w, k, v, a, b, cs = ctx.saved_tensors
+        B, T, H = ctx.shape
+        dy = _c(dy, BF16)
+        ds_T = None if ds_final is None else _c(ds_final, torch.float32)
+        grads = [torch.empty_like(r) for _ in range(6)]
+        ds0 = torch.empty(B, H, 64, 64, dtype=torch.float32, device=r.device) if ctx.has_state else None
+        dstates = torch.empty_like(cs)
+        ws = _tc_ws(B, T, H, 1, r.device)
+        call("rwkv_wkv7_tc_backward", ptr(r), ptr(w), ptr(k), ptr(v), ptr(a), ptr(b), ptr(dy), ptr(cs), ptr(ds_T),
+             ptr(dstates), ptr(ws), *(ptr(g) for g in grads), ptr(ds0), i32(B), i32(T), i32(H), stream())
+        if ctx.out_dtype != BF16:
+            grads = [g.to(ctx.out_dtype) for g in grads]
+        return (*grads, ds0, None)
+
+
+# "auto": tensor-core chunked kernels from TC_MIN_T steps up, the step-by-step kernels below (decode, short
+# chunks).  "simt" / "tc" force one implementation (A/B measurements and tests).
+WKV7_IMPL = "auto"
+TC_MIN_T = 32
+
+
 def wkv7(r, w, k, v, a, b, head_size: int = 64, state: Optional[torch.Tensor] = None, return_state: bool = False):
     if head_size != 64:
         raise ValueError("the sm_100a WKV7 kernels are built for head_size 64")
     if r.shape[-1] % 64:
         raise ValueError("channel count must be a multiple of 64")
-    y, s = _WKV7.apply(r, w, k, v, a, b, state, return_state)
+    use_tc = WKV7_IMPL == "tc" or (WKV7_IMPL == "auto" and r.shape[1] >= TC_MIN_T)
+    fn = _WKV7TC if use_tc else _WKV7
+    y, s = fn.apply(r, w, k, v, a, b, state, return_state)
     return y, s
 
 
@@ -460,6 +517,7 @@ def wkv7_tc_forward(r, w, k, v, a, b, state=None, return_state=False, save_chunk
     NC = (T + 15) // 16
     cs = torch.empty(B, H, NC, 64, 64, dtype=BF16, device=r.device) if save_chunk_states else None
     sf = torch.empty(B, H, 64, 64, dtype=torch.float32, device=r.device) if return_state else None
+    ws = _tc_ws(B, T, H, 0, r.device)
     call("rwkv_wkv7_tc_forward", ptr(r), ptr(w), ptr(k), ptr(v), ptr(a), ptr(b), ptr(s0), ptr(y), ptr(cs), ptr(sf),
-         i32(B), i32(T), i32(H), stream())
+         ptr(ws), i32(B), i32(T), i32(H), stream())
     return y, sf, cs
