@@ -427,28 +427,42 @@ class _LinearCrossEntropy(torch.autograd.Function):
         dw = torch.zeros(V, C, dtype=torch.float32, device=x.device) if need_w else None
         loss_sum = torch.zeros((), dtype=torch.float32, device=x.device)
         safe_labels = labels.clamp(min=0)
+        fused_rows = x.dtype == BF16 and weight.dtype == BF16 and V % 8 == 0
+        if fused_rows:
+            labels_c = _c(labels, torch.int64)
+            inv_n = (1.0 / n_valid).reshape(1)
+            loss_rows = torch.empty(M, dtype=torch.float32, device=x.device)
+            write_grad = 1 if (need_x or need_w) else 0
         for s in range(0, M, _LinearCrossEntropy.SLAB):
             e = min(M, s + _LinearCrossEntropy.SLAB)
             xs = x[s:e]
-            logits = gemm.mm_nt(xs, weight).float()
-            mx, am = logits.max(dim=-1, keepdim=True)
-            ex = torch.exp(logits - mx)
-            den = ex.sum(-1, keepdim=True)
-            lse = (mx + den.log()).squeeze(-1)
-            tgt = logits.gather(-1, safe_labels[s:e, None]).squeeze(-1)
-            vs = valid[s:e]
-            loss_sum += ((lse - tgt) * vs).sum()
-            if need_x or need_w:
-                scale = (vs.float() / n_valid)[:, None]
-                grad = ex / den * scale
-                grad.scatter_add_(-1, safe_labels[s:e, None], -scale)
-                if l2wrap:
-                    grad.scatter_add_(-1, am, mx * factor)
-                grad = grad.to(x.dtype)
-                if need_x:
-                    dx[s:e] = gemm.mm_nn(grad, weight)
-                if need_w:
-                    dw += gemm.mm_tn(grad, xs).float()
+            if fused_rows:
+                # one statistics sweep + one in-place rewrite of the bf16 slab (logits -> d logits)
+                grad = _c(gemm.mm_nt(xs, weight))
+                call("rwkv_ce_rows", ptr(grad), ptr(labels_c[s:e]), ptr(inv_n), f32(factor if l2wrap else 0.0),
+                     i64(ignore_index), ptr(loss_rows[s:e]), i32(write_grad), i64(e - s), i32(V), stream())
+            else:
+                logits = gemm.mm_nt(xs, weight).float()
+                mx, am = logits.max(dim=-1, keepdim=True)
+                ex = torch.exp(logits - mx)
+                den = ex.sum(-1, keepdim=True)
+                lse = (mx + den.log()).squeeze(-1)
+                tgt = logits.gather(-1, safe_labels[s:e, None]).squeeze(-1)
+                vs = valid[s:e]
+                loss_sum += ((lse - tgt) * vs).sum()
+                if need_x or need_w:
+                    scale = (vs.float() / n_valid)[:, None]
+                    grad = ex / den * scale
+                    grad.scatter_add_(-1, safe_labels[s:e, None], -scale)
+                    if l2wrap:
+                        grad.scatter_add_(-1, am, mx * factor)
+                    grad = grad.to(x.dtype)
+            if need_x:
+                dx[s:e] = gemm.mm_nn(grad, weight)
+            if need_w:
+                dw += gemm.mm_tn(grad, xs).float()
+        if fused_rows:
+            loss_sum = loss_rows.sum()
         ctx.save_for_backward(dx, dw)
         ctx.wdtype = weight.dtype
         return loss_sum / n_valid

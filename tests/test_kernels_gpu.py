@@ -215,6 +215,29 @@ def test_linear_cross_entropy_matches_reference():
     _close(wk.grad, wr.grad, 5e-2, 5e-2 * wr.grad.abs().mean().item() + 1e-5, "dw")
 
 
+@pytest.mark.parametrize("temperature,with_entropy", [(1.0, True), (0.7, True), (1.3, False)])
+def test_linear_logprob_entropy_matches_reference(temperature, with_entropy):
+    torch.manual_seed(1)
+    M, C, V = 200, 128, 1024
+    x = (torch.randn(M, C, device="cuda") * 0.5).to(BF)
+    w = (torch.randn(V, C, device="cuda") * 0.1).to(BF)
+    targets = torch.randint(0, V, (M,), device="cuda")
+    xk, wk = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    xr, wr = x.float().clone().requires_grad_(True), w.float().clone().requires_grad_(True)
+    lp, ent = ops.linear_logprob_entropy(xk, wk, targets, temperature, with_entropy)
+    lp_r, ent_r = ref.linear_logprob_entropy(xr, wr, targets, temperature, with_entropy)
+    _close(lp, lp_r, 2e-2, 3e-2, "logp")
+    g1 = torch.randn(M, device="cuda")
+    total, total_r = (lp * g1).sum(), (lp_r * g1).sum()
+    if with_entropy:
+        _close(ent, ent_r, 2e-2, 3e-2, "entropy")
+        g2 = torch.randn(M, device="cuda")
+        total, total_r = total + (ent * g2).sum(), total_r + (ent_r * g2).sum()
+    total.backward(); total_r.backward()
+    _close(xk.grad, xr.grad, 5e-2, 5e-2 * xr.grad.abs().mean().item() + 1e-4, "dx")
+    _close(wk.grad, wr.grad, 5e-2, 5e-2 * wr.grad.abs().mean().item() + 1e-4, "dw")
+
+
 def test_model_step_on_gpu_matches_cpu_reference():
     from rwkvtune_b200.models import RWKVConfig, RWKV7Model
     torch.manual_seed(0)
