@@ -328,6 +328,162 @@ layer_norm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, c
   }
 }
 
+__device__ __forceinline__ void unpack4(const uint2& p, float* f) {
+  f[0] = bf16_lo(p.x); f[1] = bf16_hi(p.x); f[2] = bf16_lo(p.y); f[3] = bf16_hi(p.y);
+}
+__device__ __forceinline__ uint2 pack4(const float* f) { return make_uint2(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3])); }
+__device__ __forceinline__ void load4f(const float* p, float* f) {
+  const float4 a = *reinterpret_cast<const float4*>(p);
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w;
+}
+__device__ __forceinline__ void store4f(float* p, const float* f) {
+  *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+}
+
+// Same backward with four channels per thread (C/4 threads): the K mix coefficients and the K+2 parameter-gradient
+// accumulators then take half the registers, which leaves room to fetch the next row's K gradient tiles before
+// the block reduction of the current row.  Same `partials` layout as the kernel above.
+template <int K>
+__global__ void __launch_bounds__(512)
+ln_shift_mix_bwd_v4_kernel(const bf16* __restrict__ dO, const bf16* __restrict__ dlast, const bf16* __restrict__ x,
+                           const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
+                           const float* __restrict__ ln_w, const float* __restrict__ ln_b,
+                           const float* __restrict__ mix, const bf16* __restrict__ prev, bf16* __restrict__ dx,
+                           float* __restrict__ dprev, float* __restrict__ partials, int B, int T, int C, int strip) {
+  __shared__ float red[2 * EW_MAX_WARPS * 2];
+  int phase = 0;
+  const int b = blockIdx.y, t0 = blockIdx.x * strip, t1 = min(T, t0 + strip);
+  const int col = threadIdx.x * 4;
+  const bool active = col < C;
+  const size_t row0 = (size_t)b * T;
+  const size_t plane = (size_t)B * T * C;
+  const float invC = 1.f / C;
+  auto ld4 = [](const bf16* p) { return *reinterpret_cast<const uint2*>(p); };
+
+  float w[4], bb[4], mu[K][4];
+  float acc_mu[K][4], acc_w[4], acc_b[4], carry[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    w[e] = bb[e] = 0.f;
+    acc_w[e] = acc_b[e] = carry[e] = 0.f;
+#pragma unroll
+    for (int k = 0; k < K; ++k) { acc_mu[k][e] = 0.f; mu[k][e] = 0.f; }
+  }
+  if (active) {
+    load4f(ln_w + col, w);
+    load4f(ln_b + col, bb);
+#pragma unroll
+    for (int k = 0; k < K; ++k) load4f(mix + (size_t)k * C + col, mu[k]);
+    if (t1 < T) {   // halo: contribution of the row after the strip
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+        float g[4];
+        unpack4(ld4(dO + (size_t)k * plane + (row0 + t1) * C + col), g);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) carry[e] += g[e] * mu[k][e];
+      }
+    } else if (dlast) {
+      float g[4];
+      unpack4(ld4(dlast + (size_t)b * C + col), g);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) carry[e] += g[e];
+    }
+  }
+  // raw row t (x tile, mean, rstd), fetched one iteration before it is turned into h / xhat
+  uint2 xq = make_uint2(0u, 0u);
+  float mq = 0.f, rq = 0.f;
+  auto fetch_x = [&](int t) {
+    if (t >= 0) {
+      xq = active ? ld4(x + (row0 + t) * C + col) : make_uint2(0u, 0u);
+      mq = mean_in[row0 + t];
+      rq = rstd_in[row0 + t];
+    } else {
+      xq = (prev && active) ? ld4(prev + (size_t)b * C + col) : make_uint2(0u, 0u);
+    }
+  };
+  auto h_from_fetched = [&](int t, float* xh, float* h) {
+    float xf[4];
+    unpack4(xq, xf);
+    if (t < 0) {   // carried row: already h
+#pragma unroll
+      for (int e = 0; e < 4; ++e) { xh[e] = 0.f; h[e] = xf[e]; }
+      return;
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      xh[e] = (xf[e] - mq) * rq;
+      h[e] = round_bf16(xh[e] * w[e] + bb[e]);
+    }
+  };
+  uint2 gq[K];
+  auto fetch = [&](int t) {
+#pragma unroll
+    for (int k = 0; k < K; ++k)
+      gq[k] = (active && t >= t0) ? ld4(dO + (size_t)k * plane + (row0 + t) * C + col) : make_uint2(0u, 0u);
+  };
+
+  float xh_cur[4], h_cur[4], xh_prev[4], h_prev[4];
+  fetch_x(t1 - 1);
+  h_from_fetched(t1 - 1, xh_cur, h_cur);
+  fetch(t1 - 1);
+  fetch_x(t1 - 2);
+  for (int t = t1 - 1; t >= t0; --t) {
+    uint2 gc[K];
+#pragma unroll
+    for (int k = 0; k < K; ++k) gc[k] = gq[k];
+    h_from_fetched(t - 1, xh_prev, h_prev);
+    if (t - 1 >= t0) {   // next row's tiles are in flight during this row's reduction
+      fetch(t - 1);
+      fetch_x(t - 2);
+    }
+    float dh[4], ncarry[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) { dh[e] = carry[e]; ncarry[e] = 0.f; }
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      float g[4];
+      unpack4(gc[k], g);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        dh[e] += g[e] * (1.f - mu[k][e]);
+        ncarry[e] += g[e] * mu[k][e];
+        acc_mu[k][e] += g[e] * (h_prev[e] - h_cur[e]);
+      }
+    }
+    float c[2] = {0.f, 0.f};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float g = dh[e] * w[e];
+      c[0] += g;
+      c[1] += g * xh_cur[e];
+      acc_w[e] += dh[e] * xh_cur[e];
+      acc_b[e] += dh[e];
+    }
+    block_sum<2>(c, red, phase);
+    if (active) {
+      const float r = rstd_in[row0 + t];
+      float o[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) o[e] = r * (dh[e] * w[e] - c[0] * invC - xh_cur[e] * c[1] * invC);
+      *reinterpret_cast<uint2*>(dx + (row0 + t) * C + col) = pack4(o);
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      carry[e] = ncarry[e];
+      xh_cur[e] = xh_prev[e];
+      h_cur[e] = h_prev[e];
+    }
+  }
+  if (active) {
+    if (dprev && t0 == 0) store4f(dprev + (size_t)b * C + col, carry);
+    float* p = partials + ((size_t)(blockIdx.y * gridDim.x + blockIdx.x) * (K + 2)) * C + col;
+#pragma unroll
+    for (int k = 0; k < K; ++k) store4f(p + (size_t)k * C, acc_mu[k]);
+    store4f(p + (size_t)K * C, acc_w);
+    store4f(p + (size_t)(K + 1) * C, acc_b);
+  }
+}
+
 inline int threads_for(int C) { return ((C / 8 + 31) / 32) * 32; }
 
 }  // namespace
@@ -363,7 +519,12 @@ RWKV_EXPORT int rwkv_ln_shift_mix_backward(const void* dO, const void* dlast, co
                                                    (const float*)mean, (const float*)rstd, (const float*)ln_w, \
                                                    (const float*)ln_b, (const float*)mix, (const bf16*)prev,   \
                                                    (bf16*)dx, (float*)dprev, (float*)partials, B, T, C, strip)
-  if (K == 6) LAUNCH(6);
+  if (K == 6 && C / 4 <= 512) {
+    ln_shift_mix_bwd_v4_kernel<6><<<grid, ((C / 4 + 31) / 32) * 32, 0, st>>>(
+        (const bf16*)dO, (const bf16*)dlast, (const bf16*)x, (const float*)mean, (const float*)rstd,
+        (const float*)ln_w, (const float*)ln_b, (const float*)mix, (const bf16*)prev, (bf16*)dx, (float*)dprev,
+        (float*)partials, B, T, C, strip);
+  } else if (K == 6) LAUNCH(6);
   else if (K == 1) LAUNCH(1);
   else return RWKV_ERR_BAD_SHAPE;
 #undef LAUNCH

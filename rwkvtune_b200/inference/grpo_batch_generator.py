@@ -19,6 +19,7 @@ from typing import Any, Dict, List, Optional, Sequence
 
 import torch
 
+from .. import ops
 from .core import TokenSampler, apply_repetition_penalty
 
 
@@ -115,7 +116,7 @@ class GRPOBatchGenerator:
 
     @staticmethod
     def _select(state, index: torch.Tensor):
-        return tuple([t.index_select(0, index) for t in part] for part in state)
+        return tuple([ops.gather_rows(t, index) for t in part] for part in state)
 
     def _forward(self, ids: torch.Tensor, state):
         att, wkv, ffn = state

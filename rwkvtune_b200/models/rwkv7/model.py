@@ -117,6 +117,11 @@ class RWKV7TimeMix(nn.Module):
             self.value.weight.uniform_(-0.5 * s, 0.5 * s)
             self.output.weight.zero_()
 
+    def _plain_projections(self) -> bool:
+        """True when r/k/v are unwrapped, unsharded ``Linear`` layers (no adapter, no ZeRO-3 panels)."""
+        return all(type(m) is Linear and getattr(m, "_sharded", None) is None
+                   for m in (self.receptance, self.key, self.value))
+
     def mix_matrix(self) -> torch.Tensor:
         C = self.x_r.shape[-1]
         if not torch.is_grad_enabled():   # inference: one cached [6, C] parameter-like tensor, rebuilt when weights change
@@ -138,9 +143,12 @@ class RWKV7TimeMix(nn.Module):
         mixed, last = ops.ln_shift_mix(x, ln_w, ln_b, self.mix_matrix(), x_prev)
         xr, xw, xk, xv, xa, xg = mixed.unbind(0)
 
-        r = self.receptance(xr)
-        k = self.key(xk)
-        v = self.value(xv)
+        if self._plain_projections() and x.is_cuda and not torch.is_grad_enabled():
+            r, k, v = ops.linear_group([xr, xk, xv], [self.receptance.weight, self.key.weight, self.value.weight])
+        else:
+            r = self.receptance(xr)
+            k = self.key(xk)
+            v = self.value(xv)
         w_lin = ops.matmul(torch.tanh(ops.matmul(xw, self.w1)), self.w2)
         a_lin = ops.matmul(ops.matmul(xa, self.a1), self.a2)
         g = ops.matmul(torch.sigmoid(ops.matmul(xg, self.g1)), self.g2)
@@ -250,7 +258,7 @@ class RWKV7Model(GenerationMixin, nn.Module):
         B, T = idx.shape
         if T > self.config.ctx_len:
             raise ValueError(f"sequence length {T} exceeds ctx_len {self.config.ctx_len}")
-        x = self.emb(idx)
+        x = ops.embedding(idx, self.emb.weight)
         v_first = torch.empty_like(x)
         cp = self._use_checkpoint()
         n_cp = getattr(self.config, "grad_cp_layers", None)   # None: every layer; k: only the first k layers
@@ -307,7 +315,7 @@ class RWKV7Model(GenerationMixin, nn.Module):
         Gradients flow through the incoming states, which is what full
         back-propagation through time across chunks needs.
         """
-        x = self.emb(idx)
+        x = ops.embedding(idx, self.emb.weight)
         v_first = torch.empty_like(x)
         new_att, new_wkv, new_ffn = [], [], []
         for i, block in enumerate(self.blocks):

@@ -31,6 +31,7 @@ _KERNELS: Dict[str, bool] = {
     "linear_cross_entropy": True,
     "linear_logprob_entropy": True,
     "gemm": True,
+    "gather": True,
 }
 
 
@@ -86,6 +87,15 @@ def matmul(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     if _native(x, "gemm"):
         return _cuda().matmul(x, w)
     return x @ w
+
+
+def linear_group(xs, weights):
+    """Several independent ``x_i @ W_i^T`` with the same leading shape; one grouped launch while decoding."""
+    if _native(xs[0], "gemm"):
+        from . import gemm
+
+        return gemm.linear_group(list(xs), list(weights))
+    return [torch.nn.functional.linear(x, w) for x, w in zip(xs, weights)]
 
 
 def linear_relu_sq(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
@@ -148,3 +158,18 @@ def linear_logprob_entropy(x, weight, targets, temperature: float = 1.0, with_en
     if _native(x, "linear_logprob_entropy"):
         return _cuda().linear_logprob_entropy(x, weight, targets, temperature, with_entropy)
     return reference.linear_logprob_entropy(x, weight, targets, temperature, with_entropy)
+
+
+# ------------------------------------------------------------------------------- gathers
+def embedding(idx: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """Embedding lookup; the gradient accumulates repeated tokens in fp32 in a fixed order."""
+    if _native(weight, "gather"):
+        return _cuda().embedding(idx, weight)
+    return torch.nn.functional.embedding(idx, weight)
+
+
+def gather_rows(src: torch.Tensor, index: torch.Tensor) -> torch.Tensor:
+    """``src.index_select(0, index)``: state fan-out to sampling paths and compaction of live rows."""
+    if _native(src, "gather"):
+        return _cuda().gather_rows(src, index)
+    return src.index_select(0, index)

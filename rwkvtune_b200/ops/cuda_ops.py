@@ -535,3 +535,42 @@ def wkv7_tc_forward(r, w, k, v, a, b, state=None, return_state=False, save_chunk
     call("rwkv_wkv7_tc_forward", ptr(r), ptr(w), ptr(k), ptr(v), ptr(a), ptr(b), ptr(s0), ptr(y), ptr(cs), ptr(sf),
          ptr(ws), i32(B), i32(T), i32(H), stream())
     return y, sf, cs
+
+
+# =============================================================================== gathers
+def gather_rows(src: torch.Tensor, index: torch.Tensor) -> torch.Tensor:
+    """``src.index_select(0, index)`` for a contiguous tensor whose rows are a multiple of 16 bytes."""
+    src = _c(src)
+    index = _c(index, torch.int64)
+    row_bytes = (src.numel() // max(src.shape[0], 1)) * src.element_size()
+    if row_bytes % 16 or src.data_ptr() % 16:
+        return src.index_select(0, index)
+    out = torch.empty((index.numel(),) + tuple(src.shape[1:]), dtype=src.dtype, device=src.device)
+    call("rwkv_gather_rows", ptr(src), ptr(index), ptr(out), i64(index.numel()), i64(src.shape[0]), i64(row_bytes),
+         stream())
+    return out
+
+
+class _Embedding(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, idx, weight):
+        ctx.save_for_backward(idx)
+        ctx.wshape = weight.shape
+        return gather_rows(weight, idx.reshape(-1)).reshape(*idx.shape, weight.shape[1])
+
+    @staticmethod
+    def backward(ctx, dy):
+        (idx,) = ctx.saved_tensors
+        V, C = ctx.wshape
+        dyb = _c(dy.reshape(-1, C), BF16)
+        sorted_idx, order = torch.sort(idx.reshape(-1).to(torch.int64), stable=True)
+        dW = torch.zeros(V, C, dtype=BF16, device=dy.device)
+        call("rwkv_embedding_backward", ptr(dyb), ptr(sorted_idx), ptr(order), ptr(dW), i64(dyb.shape[0]), i64(V),
+             i32(C), stream())
+        return None, dW
+
+
+def embedding(idx, weight):
+    if weight.dtype != BF16 or weight.shape[1] % 8:
+        return torch.nn.functional.embedding(idx, weight)
+    return _Embedding.apply(idx, weight)

@@ -34,9 +34,25 @@ def _native():
 
 def mm_nt(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     n = _native()
-    if n is not None and n.native_ok(x, w, "nt"):
-        return n.mm_nt(x, w)
+    if n is not None:
+        if n.SMALL_M_DISPATCH and n.small_m_ok(x, w):
+            return n.small_m_group([x], [w])[0]
+        if n.native_ok(x, w, "nt"):
+            return n.mm_nt(x, w)
     return x @ w.t()
+
+
+def linear_group(xs, ws):
+    """``[x_i @ w_i^T]`` for several independent projections with the same row count.  During decoding
+    (few rows, no autograd) they go out as one grouped launch; otherwise one ``linear`` each."""
+    n = _native()
+    if (n is not None and n.SMALL_M_DISPATCH and not torch.is_grad_enabled() and len(xs) <= 8
+            and all(x.shape[:-1] == xs[0].shape[:-1] for x in xs)):
+        x2 = [x.reshape(-1, x.shape[-1]) for x in xs]
+        if all(n.small_m_ok(a, w) for a, w in zip(x2, ws)):
+            ys = n.small_m_group(x2, list(ws))
+            return [y.reshape(*x.shape[:-1], w.shape[0]) for y, x, w in zip(ys, xs, ws)]
+    return [linear(x, w) for x, w in zip(xs, ws)]
 
 
 def mm_nn(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
