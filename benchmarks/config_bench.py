@@ -1,0 +1,273 @@
+"""Throughput of the other training configurations (the headline pretrain config lives in ``bench.py``).
+
+    python benchmarks/config_bench.py --config lora_zero3   # 2.9B SFT, LoRA r=64, ZeRO-3 when launched on >1 GPU
+    python benchmarks/config_bench.py --config infctx       # 0.4B, 65536-token sequences in 4096-token chunks
+    python benchmarks/config_bench.py --config grpo         # 1.5B GRPO (dapo, beta 0.04), LoRA r=64, G=8
+    python benchmarks/config_bench.py --config collectives  # fused reduce-scatter / AdamW+broadcast vs NVLink roofline
+
+Multi-GPU: ``python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 benchmarks/config_bench.py ...``.
+Synthetic uniform-random tokens, random-init weights, bf16; timed on the device with CUDA events after warm-up,
+max over ranks; prints one JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+from bench import MODELS  # noqa: E402
+
+NVLINK_GBS = 770.0    # measured peer copy bandwidth per direction per GPU on this machine class
+
+
+def _ctx():
+    from rwkvtune_b200.parallel import init_distributed
+
+    return init_distributed("gpu")
+
+
+def _max_over_ranks(ctx, value: float) -> float:
+    if ctx.world_size == 1:
+        return value
+    t = torch.tensor([value], device=ctx.device, dtype=torch.float64)
+    torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    return float(t)
+
+
+def _time_steps(ctx, step, warmup: int, steps: int) -> float:
+    for i in range(warmup):
+        step(i)
+    if ctx.world_size > 1:
+        torch.distributed.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        step(warmup + i)
+    e1.record()
+    torch.cuda.synchronize()
+    return _max_over_ranks(ctx, e0.elapsed_time(e1) / steps)
+
+
+def bench_lora_zero3(a):
+    from rwkvtune_b200 import LoraConfig, get_peft_model
+    from rwkvtune_b200.engine import EngineConfig, TrainEngine
+    from rwkvtune_b200.models import RWKVConfig, RWKV7Model
+
+    ctx = _ctx()
+    B, T = a.micro_bsz or 2, a.ctx_len or 8192
+    cfg = RWKVConfig(vocab_size=65536, ctx_len=T, **MODELS["2.9b"])
+    torch.manual_seed(7)
+    with torch.device(ctx.device):
+        model = RWKV7Model(cfg)
+    model = get_peft_model(model, LoraConfig(r=64, lora_alpha=128))
+    strategy = "deepspeed_stage_3" if ctx.world_size > 1 else "auto"
+    eng = TrainEngine(model, EngineConfig(lr_init=2e-5, grad_clip=1.0, strategy=strategy, precision="bf16", grad_cp=1,
+                                          transport="auto"), ctx)
+    g = torch.Generator().manual_seed(100 + ctx.rank)
+    n = a.warmup + a.steps
+    ids = [torch.randint(0, 65536, (B, T), generator=g).to(ctx.device) for _ in range(n)]
+    labels = []
+    for i in range(n):
+        lab = torch.randint(0, 65536, (B, T), generator=g)
+        for b in range(B):
+            lab[b, :int(torch.randint(128, 2049, (1,), generator=g))] = -100
+        labels.append(lab.to(ctx.device))
+    state = {"cp": None}
+
+    def step(i):
+        eng.train_step(ids[i], labels[i], 2e-5)
+        if i == 0:
+            torch.cuda.synchronize()
+            state["cp"] = eng.autotune_checkpointing(B, T)
+
+    ms = _time_steps(ctx, step, a.warmup, a.steps)
+    tokens = B * T * ctx.world_size
+    return ctx, {"metric": "train_tokens_per_sec", "value": tokens / ms * 1e3, "ms_per_step": ms,
+                 "config": {"model": "rwkv7-2.9b", "lora_r": 64, "seq_len": T, "micro_bsz": B,
+                            "parallelism": f"zero3-dp{ctx.world_size}" if ctx.world_size > 1 else "single",
+                            "fused_allgather_gemm": eng.zero3 is not None, "checkpointed_layers": state["cp"],
+                            "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2**30, 1)}}
+
+
+def bench_infctx(a):
+    from rwkvtune_b200.engine import EngineConfig, TrainEngine
+    from rwkvtune_b200.models import RWKVConfig, RWKV7Model
+
+    ctx = _ctx()
+    B, T, chunk = a.micro_bsz or 1, a.ctx_len or 65536, 4096
+    cfg = RWKVConfig(vocab_size=65536, ctx_len=T, **MODELS["0.4b"])
+    torch.manual_seed(7)
+    with torch.device(ctx.device):
+        model = RWKV7Model(cfg)
+    strategy = "deepspeed_stage_2" if ctx.world_size > 1 else "auto"
+    eng = TrainEngine(model, EngineConfig(lr_init=1e-4, grad_clip=1.0, strategy=strategy, precision="bf16", grad_cp=1,
+                                          train_type="infctx", chunk_ctx=chunk, transport="auto"), ctx)
+    g = torch.Generator().manual_seed(100 + ctx.rank)
+    n = a.warmup + a.steps
+    ids = [torch.randint(0, 65536, (B, T), generator=g).to(ctx.device) for _ in range(n)]
+    labels = [torch.randint(0, 65536, (B, T), generator=g).to(ctx.device) for _ in range(n)]
+    ms = _time_steps(ctx, lambda i: eng.train_step(ids[i], labels[i], 1e-4), a.warmup, a.steps)
+    tokens = B * T * ctx.world_size
+    return ctx, {"metric": "train_tokens_per_sec", "value": tokens / ms * 1e3, "ms_per_step": ms,
+                 "config": {"model": "rwkv7-0.4b", "seq_len": T, "chunk_ctx": chunk, "micro_bsz": B, "bptt": "truncated",
+                            "parallelism": f"zero2-dp{ctx.world_size}" if ctx.world_size > 1 else "single",
+                            "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2**30, 1)}}
+
+
+class _IdTokenizer:
+    """Text is the space-separated token ids, so a reward function can see ids."""
+    eos_token_id = None
+    vocab_size = 65536
+
+    def encode(self, text):
+        return [int(t) for t in text.split()]
+
+    def decode(self, ids):
+        return " ".join(str(int(i)) for i in ids)
+
+
+def _low_id_fraction(prompts, completions, **extra):
+    out = []
+    for c in completions:
+        ids = [int(t) for t in c.split()] if c else []
+        out.append(sum(i < 32768 for i in ids) / max(1, len(ids)))
+    return out
+
+
+def bench_grpo(a):
+    import tempfile
+
+    from rwkvtune_b200 import GRPOConfig, GRPOTrainer, LoraConfig
+    from rwkvtune_b200.models import RWKVConfig, RWKV7Model
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    prompts_per_gpu, G, S, P, Cn = a.micro_bsz or 8, 8, 8, 512, a.new_tokens
+    cfg = RWKVConfig(vocab_size=65536, ctx_len=4096, eos_token_id=None, **MODELS["1.5b"])
+    torch.manual_seed(7)
+    model = RWKV7Model(cfg)
+    g = torch.Generator().manual_seed(5)
+    cycles = 2     # the first rollout + 8 steps warm up (graph capture, allocator); the second is reported
+    data = [{"prompt": f"p{i}", "input_ids": torch.randint(1, 65000, (P,), generator=g).tolist()}
+            for i in range(prompts_per_gpu * world * cycles)]
+    times, rollouts = [], []
+
+    class Clock:
+        def on_step_end(self, trainer, metrics):
+            torch.cuda.synchronize()
+            times.append(time.perf_counter())
+            rollouts.append((metrics["rollout/tokens_per_sec"], metrics["rollout/seconds"], metrics["completions/mean_length"]))
+
+    with tempfile.TemporaryDirectory() as tmp:
+        args = GRPOConfig(num_generations=G, num_iterations=1, micro_bsz=prompts_per_gpu, steps_per_generation=S,
+                          max_prompt_length=P, max_completion_length=Cn, temperature=1.0, top_p=0.95, top_k=0,
+                          loss_type="dapo", beta=0.04, lr_init=1e-6, lr_final=1e-7, warmup_steps=0, accelerator="gpu",
+                          devices=1, precision="bf16", proj_dir=tmp, epoch_count=1, epoch_steps=S * cycles, use_lora=True,
+                          save_total_limit=1, log_steps=1000)
+        tr = GRPOTrainer(model=model, reward_funcs=[_low_id_fraction], args=args, train_dataset=data,
+                         processing_class=_IdTokenizer(), peft_config=LoraConfig(r=64, lora_alpha=128), callbacks=[Clock()])
+        tr.train()
+        ctx = tr.ctx
+    # second cycle: steps S .. 2S-1; step S includes the rollout, so train time is measured over steps S+1 .. 2S-1
+    step_s = (times[2 * S - 1] - times[S]) / (S - 1)
+    roll_tps, roll_s, mean_len = rollouts[2 * S - 1]
+    seqs_per_step = prompts_per_gpu * G // S
+    train_tokens = seqs_per_step * (P + mean_len) * ctx.world_size
+    step_s = _max_over_ranks(ctx, step_s)
+    roll_s = _max_over_ranks(ctx, roll_s)
+    gen_tokens = prompts_per_gpu * G * mean_len * ctx.world_size
+    return ctx, {"metric": "grpo_rollout_tokens_per_sec", "value": gen_tokens / roll_s, "rollout_seconds": roll_s,
+                 "train_tokens_per_sec": train_tokens / step_s, "train_ms_per_step": step_s * 1e3,
+                 "config": {"model": "rwkv7-1.5b", "lora_r": 64, "loss_type": "dapo", "beta": 0.04,
+                            "prompts_per_gpu": prompts_per_gpu, "prompt_len": P, "num_generations": G,
+                            "max_completion_length": Cn, "steps_per_generation": S, "mean_completion_length": mean_len,
+                            "timing": "host clock around device-synchronised steps (through GRPOTrainer.train())",
+                            "parallelism": f"dp{ctx.world_size}"}}
+
+
+def bench_collectives(a):
+    """Fused ZeRO-2 kernels on the 1.5B flat parameter space: bytes that must cross NVLink / time vs 770 GB/s."""
+    from rwkvtune_b200.engine import EngineConfig, TrainEngine
+    from rwkvtune_b200.models import RWKVConfig, RWKV7Model
+    from rwkvtune_b200.ops import _ext
+
+    ctx = _ctx()
+    if ctx.world_size < 2:
+        raise SystemExit("--config collectives needs at least 2 ranks")
+    cfg = RWKVConfig(vocab_size=65536, ctx_len=4096, **MODELS["1.5b"])
+    torch.manual_seed(7)
+    with torch.device(ctx.device):
+        model = RWKV7Model(cfg)
+    eng = TrainEngine(model, EngineConfig(lr_init=1e-4, strategy="deepspeed_stage_2", precision="bf16", transport="p2p"), ctx)
+    fz, opt, sp = eng.opt._p2p, eng.opt, eng.space
+    sp.grads.normal_(0, 1e-3)
+    W = ctx.world_size
+    shard = opt.hi - opt.lo
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+    acc = [0.0, 0.0, 0.0]
+    iters = a.warmup + a.steps
+    for it in range(iters):
+        opt.step_count += 1
+        fz._barrier()
+        ev[0].record()
+        _ext.call("rwkv_zero2_reduce_scatter", fz.grad_ptrs, fz.ctrl_ptrs, _ext.i32(fz.rank), _ext.i32(W), _ext.i64(opt.lo),
+                  _ext.i64(shard), _ext.f32(1.0 / W), _ext.ptr(fz.gred), _ext.ptr(fz.scratch), _ext.stream())
+        ev[1].record()
+        fz._barrier()
+        ev[2].record()
+        for gi, s, e in sp.group_segments_in(opt.lo, opt.hi):
+            grp = sp.groups[gi]
+            lo, hi = s - opt.lo, e - opt.lo
+            _ext.call("rwkv_zero2_adam_broadcast", fz.param_ptrs, fz.ctrl_ptrs, _ext.i32(fz.rank), _ext.i32(W), _ext.i64(s),
+                      _ext.i64(e - s), _ext.ptr(opt.master[lo:hi]), _ext.ptr(opt.exp_avg[lo:hi]),
+                      _ext.ptr(opt.exp_avg_sq[lo:hi]), _ext.ptr(fz.gred[lo:hi]), _ext.f32(1e-6 * grp.lr_scale),
+                      _ext.f32(opt.beta1), _ext.f32(opt.beta2), _ext.f32(opt.eps), _ext.f32(grp.weight_decay),
+                      _ext.i32(opt.step_count), _ext.f32(opt.grad_clip), _ext.stream())
+        ev[3].record()
+        fz._barrier()
+        torch.cuda.synchronize()
+        if it >= a.warmup:
+            acc[0] += ev[0].elapsed_time(ev[1])
+            acc[1] += ev[2].elapsed_time(ev[3])
+            acc[2] += ev[0].elapsed_time(ev[3])
+    fz.check()
+    rs_ms, ab_ms, all_ms = (_max_over_ranks(ctx, x / a.steps) for x in acc)
+    link_bytes = (W - 1) * shard * 2          # bf16 shard pulled from / pushed to each of W-1 peers
+    hbm_adam = shard * (3 * 4 * 2 + 4 + 2)     # master, m, v read+write (fp32), reduced grad read, bf16 param write
+    return ctx, {"metric": "fused_zero2_fraction_of_nvlink_roofline", "value": link_bytes / (rs_ms * 1e-3) / 1e9 / NVLINK_GBS,
+                 "reduce_scatter_ms": rs_ms, "reduce_scatter_gbs_in": link_bytes / (rs_ms * 1e-3) / 1e9,
+                 "reduce_scatter_frac_of_770": link_bytes / (rs_ms * 1e-3) / 1e9 / NVLINK_GBS,
+                 "adam_broadcast_ms": ab_ms, "adam_broadcast_gbs_out": link_bytes / (ab_ms * 1e-3) / 1e9,
+                 "adam_broadcast_frac_of_770": link_bytes / (ab_ms * 1e-3) / 1e9 / NVLINK_GBS,
+                 "whole_step_ms": all_ms, "link_bytes_per_phase": link_bytes, "adam_hbm_bytes": hbm_adam,
+                 "config": {"model": "rwkv7-1.5b", "elements": int(sp.padded), "shard_elements": int(shard),
+                            "parallelism": f"zero2-dp{W}", "roofline": "bytes over NVLink per direction / 770 GB/s measured"}}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--config", required=True, choices=["lora_zero3", "infctx", "grpo", "collectives"])
+    ap.add_argument("--steps", type=int, default=4)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--micro-bsz", type=int, default=0)
+    ap.add_argument("--ctx-len", type=int, default=0)
+    ap.add_argument("--new-tokens", type=int, default=512)
+    a = ap.parse_args()
+    ctx, out = {"lora_zero3": bench_lora_zero3, "infctx": bench_infctx, "grpo": bench_grpo,
+                "collectives": bench_collectives}[a.config](a)
+    out.update({"n_gpus": ctx.world_size, "steps": a.steps, "warmup": a.warmup, "dtype": "bf16", "data": "synthetic"})
+    if ctx.is_main:
+        print(json.dumps(out))
+    if ctx.world_size > 1 and torch.distributed.is_initialized():
+        torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

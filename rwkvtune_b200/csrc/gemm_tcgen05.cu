@@ -159,17 +159,32 @@ __device__ __forceinline__ void st_release_gpu(int* p, int v) {
 }
 
 __device__ void ag_copy_role(const AgParams& ag, int N, int K) {
+  // A peer load takes a couple of microseconds to come back, so throughput is bytes in flight / latency:
+  // every thread keeps AG_UNROLL independent 16-byte loads outstanding before it stores any of them.
+  constexpr int AG_UNROLL = 8;
   const int vec_per_row = ag.Kp / 8;
   const long long total = (long long)N * vec_per_row;
   const long long stride = (long long)ag.n_copy * blockDim.x;
   for (int s = 0; s < ag.world; ++s) {
     const int p = (ag.rank + s) % ag.world;
     const uint4* src = reinterpret_cast<const uint4*>(ag.shard[p]);
-    for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < total; v += stride) {
-      const long long row = v / vec_per_row;
-      const int c = (int)(v - row * vec_per_row);
-      const uint4 val = __ldcg(src + v);
-      *reinterpret_cast<uint4*>(ag.staged + row * K + (long long)p * ag.Kp + c * 8) = val;
+    bf16* dst = ag.staged + (long long)p * ag.Kp;
+    for (long long v0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; v0 < total; v0 += stride * AG_UNROLL) {
+      uint4 val[AG_UNROLL];
+#pragma unroll
+      for (int u = 0; u < AG_UNROLL; ++u) {
+        const long long v = v0 + u * stride;
+        if (v < total) val[u] = __ldcg(src + v);
+      }
+#pragma unroll
+      for (int u = 0; u < AG_UNROLL; ++u) {
+        const long long v = v0 + u * stride;
+        if (v < total) {
+          const long long row = v / vec_per_row;
+          const int c = (int)(v - row * vec_per_row);
+          *reinterpret_cast<uint4*>(dst + row * K + c * 8) = val[u];
+        }
+      }
     }
     __threadfence();
     asm volatile("fence.proxy.async;" ::: "memory");
@@ -181,12 +196,12 @@ __device__ void ag_copy_role(const AgParams& ag, int N, int K) {
   }
 }
 
-// EPI: 0 = plain store, 1 = relu(x)^2
+// EPI: 0 = plain store, 1 = relu(x)^2, 2 = add to the bf16 values already in C (in place: C += A B)
 template <bool A_MN, bool B_MN, int EPI, bool AG>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const __grid_constant__ CUtensorMap map_c, int M, int N, int K, int* status,
-                    const __grid_constant__ AgParams ag) {
+                    const bf16* __restrict__ c_in, long long ldc, const __grid_constant__ AgParams ag) {
   if (AG && (int)blockIdx.x < ag.n_copy) {   // copy CTAs never touch barriers or tensor memory
     ag_copy_role(ag, N, K);
     return;
@@ -325,6 +340,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         uint32_t v0[32], v1[32];
         tmem_ld32(t_row + chunk * 64, v0);
         tmem_ld32(t_row + chunk * 64 + 32, v1);
+        uint4 cin[EPI == 2 ? 8 : 1];
+        if (EPI == 2) {   // this thread's 64 output columns of the existing C, fetched while the TMEM load is in flight
+          const long long gm = m0 + row;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int gn = n0 + chunk * 64 + j * 8;
+            cin[j] = (gm < M && gn < N) ? __ldcg(reinterpret_cast<const uint4*>(c_in + gm * ldc + gn))
+                                        : make_uint4(0u, 0u, 0u, 0u);
+          }
+        }
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         // the staging buffer we are about to overwrite must have been read by its TMA store
         if (threadIdx.x == 64) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
@@ -332,12 +357,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const uint32_t cs = c_stage + cbuf * C_CHUNK_BYTES + row * 128;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {   // eight 16-byte pieces of this row, XOR-swizzled by (row % 8)
-          float f[8];
+          float f[8], prev[8];
+          if (EPI == 2) unpack8(cin[j], prev);
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
             const int col = j * 8 + e;
             float x = __uint_as_float(col < 32 ? v0[col] : v1[col - 32]);
             if (EPI == 1) { x = fmaxf(x, 0.f); x = x * x; }
+            if (EPI == 2) x += prev[e];
             f[e] = x;
           }
           const uint4 packed = pack8(f);
@@ -405,7 +432,7 @@ int make_map(CUtensorMap* map, const void* ptr, long long rows, long long cols, 
 
 template <bool A_MN, bool B_MN, int EPI>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, int M, int N, int K, int* status,
-           int sms, cudaStream_t st) {
+           int sms, const bf16* c_in, long long ldc, cudaStream_t st) {
   auto kern = gemm_tcgen05_kernel<A_MN, B_MN, EPI, false>;
   static bool configured = false;
   if (!configured) {
@@ -416,7 +443,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, 
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int grid = tiles < sms ? tiles : sms;
   AgParams none = {};
-  kern<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(ma, mb, mc, M, N, K, status, none);
+  kern<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(ma, mb, mc, M, N, K, status, c_in, ldc, none);
   return rwkv_launch_status();
 }
 
@@ -434,7 +461,9 @@ int launch_ag(CUtensorMap ma, CUtensorMap mb, CUtensorMap mc, int M, int N, int 
   if (tiles < n_gemm) n_gemm = tiles;
   const int grid = n_gemm + ag.n_copy;
   // GEMM CTAs wait for copy CTAs of the same grid: a cooperative launch guarantees they are co-resident
-  void* args[] = {&ma, &mb, &mc, &M, &N, &K, &status, &ag};
+  const bf16* c_in = nullptr;
+  long long ldc = 0;
+  void* args[] = {&ma, &mb, &mc, &M, &N, &K, &status, &c_in, &ldc, &ag};
   cudaError_t e = cudaLaunchCooperativeKernel((void*)kern, dim3(grid), dim3(NUM_THREADS), args, SMEM_BYTES, st);
   return e == cudaSuccess ? rwkv_launch_status() : RWKV_ERR_CUDA_BASE + (int)e;
 }
@@ -444,7 +473,7 @@ int launch_ag(CUtensorMap ma, CUtensorMap mb, CUtensorMap mc, int M, int N, int 
 // C[M,N] (row-major, ldc) = op(A) op(B) in bf16 with fp32 accumulation.
 //   a_mn = 0: A is [M,K] row-major (lda);  a_mn = 1: A is stored [K,M] row-major (lda)
 //   b_mn = 0: B is [N,K] row-major (ldb);  b_mn = 1: B is stored [K,N] row-major (ldb)
-//   epilogue: 0 none, 1 relu(x)^2.   status: device int, set non-zero if a device-side wait timed out.
+//   epilogue: 0 none, 1 relu(x)^2, 2 accumulate into the values already in C.   status: device int, set non-zero if a device-side wait timed out.
 RWKV_EXPORT int rwkv_gemm_bf16_tcgen05(const void* a, const void* b, void* c, int M, int N, int K, long long lda,
                                        long long ldb, long long ldc, int a_mn, int b_mn, int epilogue, void* status,
                                        void* stream) {
@@ -465,9 +494,11 @@ RWKV_EXPORT int rwkv_gemm_bf16_tcgen05(const void* a, const void* b, void* c, in
   if (r) return r;
   cudaStream_t st = (cudaStream_t)stream;
   int* sp = (int*)status;
-#define DISPATCH(AM, BMN)                                                              \
-  (epilogue == 1 ? launch<AM, BMN, 1>(ma, mb, mc, M, N, K, sp, sms, st)                \
-                 : launch<AM, BMN, 0>(ma, mb, mc, M, N, K, sp, sms, st))
+  const bf16* cp = (const bf16*)c;
+#define DISPATCH(AM, BMN)                                                                        \
+  (epilogue == 1   ? launch<AM, BMN, 1>(ma, mb, mc, M, N, K, sp, sms, cp, ldc, st)                \
+   : epilogue == 2 ? launch<AM, BMN, 2>(ma, mb, mc, M, N, K, sp, sms, cp, ldc, st)                \
+                   : launch<AM, BMN, 0>(ma, mb, mc, M, N, K, sp, sms, cp, ldc, st))
   if (!a_mn && !b_mn) return DISPATCH(false, false);
   if (!a_mn && b_mn) return DISPATCH(false, true);
   if (a_mn && b_mn) return DISPATCH(true, true);

@@ -46,7 +46,7 @@ class EngineConfig:
     train_type: str = "normal"
     chunk_ctx: int = 512
     truncated_bptt: bool = True
-    transport: str = "nccl"
+    transport: str = "auto"   # "p2p": fused kernels over symmetric memory; "nccl": library collectives; "auto": p2p on multi-GPU CUDA when symmetric memory can be set up
     l2wrap: bool = True
     grad_cp_layers: Optional[object] = None   # None = all layers when grad_cp=1; int k = first k layers; "auto"
 
@@ -74,14 +74,29 @@ class TrainEngine:
         if not groups:
             raise RuntimeError("the model has no trainable parameters")
         allocator = None
-        if cfg.transport == "p2p" and ctx.world_size > 1 and ctx.device.type == "cuda" and stage >= 1:
-            from ..parallel.p2p import symmetric_allocator
+        transport = cfg.transport
+        p2p_capable = ctx.world_size > 1 and ctx.device.type == "cuda" and stage >= 1 and dtype == torch.bfloat16
+        if transport == "p2p" and ctx.world_size > 1 and not p2p_capable:
+            raise ValueError("transport 'p2p' needs CUDA, bf16 and a ZeRO stage >= 1")
+        if transport in ("p2p", "auto") and p2p_capable:
+            try:
+                from ..parallel.p2p import symmetric_allocator
 
-            allocator = symmetric_allocator()
+                allocator = symmetric_allocator()
+                transport = "p2p"
+            except Exception as exc:   # no symmetric memory on this system: library collectives do the same job
+                if cfg.transport == "p2p":
+                    raise
+                if ctx.is_main:
+                    print(f"[engine] symmetric memory unavailable ({exc}); using NCCL collectives")
+                transport = "nccl"
+        elif transport == "auto":
+            transport = "nccl"
+        self.transport = transport
         self.space = FlatParamSpace(groups, ctx.world_size, dtype, ctx.device, allocator)
         self.stage = stage
         self.opt = ZeroOptimizer(self.space, ctx, min(stage, 2), (cfg.beta1, cfg.beta2), cfg.adam_eps, cfg.grad_clip,
-                                 cfg.transport)
+                                 transport)
         self.micro_step = 0
         self.optimizer_steps = 0
         self.tokens_seen = 0

@@ -62,6 +62,27 @@ def mm_nn(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     return x @ w
 
 
+def _acc_ok(n, y: torch.Tensor) -> bool:
+    return (n is not None and y.is_cuda and y.dtype == torch.bfloat16 and y.dim() == 2 and y.stride(1) == 1
+            and y.data_ptr() % 16 == 0 and (y.stride(0) * 2) % 16 == 0)
+
+
+def addmm_nt_(y: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``y += x @ w^T`` in place; on the native path the sum happens in the GEMM epilogue (no temporary)."""
+    n = _native()
+    if _acc_ok(n, y) and n.native_ok(x, w, "nt"):
+        return n.mm_nt(x, w, out=y)
+    return y.add_(x @ w.t())
+
+
+def addmm_nn_(y: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``y += x @ w`` in place (see :func:`addmm_nt_`)."""
+    n = _native()
+    if _acc_ok(n, y) and n.native_ok(x, w, "nn"):
+        return n.mm_nn(x, w, out=y)
+    return y.add_(x @ w)
+
+
 def mm_tn(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     n = _native()
     if n is not None and n.native_ok(a, b, "tn"):

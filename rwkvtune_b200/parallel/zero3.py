@@ -91,7 +91,7 @@ class _LoraAGLinearFn(torch.autograd.Function):
         base = gemm_native.ag_mm_nt(x2, gw)
         gw.current_owner = sw
         xa = gemm.mm_nt(x2, a)
-        y = base + gemm.mm_nt(xa, b) * scaling
+        y = gemm.addmm_nt_(base, xa * scaling, b)
         ctx.save_for_backward(x2, a, b, xa)
         ctx.sw, ctx.shape, ctx.scaling = sw, x.shape, scaling
         return y.reshape(*x.shape[:-1], sw.N)
@@ -105,7 +105,7 @@ class _LoraAGLinearFn(torch.autograd.Function):
         dyb = gemm.mm_nn(dy2, b)
         dx = None
         if ctx.needs_input_grad[0]:
-            dx = (gemm.mm_nn(dy2, sw.full_weight()) + gemm.mm_nn(dyb, a) * s).reshape(ctx.shape)
+            dx = gemm.addmm_nn_(gemm.mm_nn(dy2, sw.full_weight()), dyb * s, a).reshape(ctx.shape)
         da = gemm.mm_tn(dyb, x2) * s if ctx.needs_input_grad[2] else None
         db = gemm.mm_tn(dy2, xa) * s if ctx.needs_input_grad[3] else None
         return dx, None, da, db, None

@@ -20,7 +20,7 @@ class _LoraLinearFn(torch.autograd.Function):
     def forward(ctx, x, w, a, b, scaling: float, w_needs_grad: bool):
         x2 = x.reshape(-1, x.shape[-1])
         xa = gemm.mm_nt(x2, a)                       # [M, r]
-        y = gemm.mm_nt(x2, w) + gemm.mm_nt(xa, b) * scaling
+        y = gemm.addmm_nt_(gemm.mm_nt(x2, w), xa * scaling, b)     # scale the [M, r] factor, add in the GEMM epilogue
         ctx.save_for_backward(x2, w, a, b, xa)
         ctx.scaling, ctx.shape = scaling, x.shape
         return y.reshape(*x.shape[:-1], w.shape[0])
@@ -33,7 +33,7 @@ class _LoraLinearFn(torch.autograd.Function):
         dyb = gemm.mm_nn(dy2, b)                     # [M, r]
         dx = dw = da = db = None
         if ctx.needs_input_grad[0]:
-            dx = (gemm.mm_nn(dy2, w) + gemm.mm_nn(dyb, a) * s).reshape(ctx.shape)
+            dx = gemm.addmm_nn_(gemm.mm_nn(dy2, w), dyb * s, a).reshape(ctx.shape)
         if ctx.needs_input_grad[1]:
             dw = gemm.mm_tn(dy2, x2)
         if ctx.needs_input_grad[2]:

@@ -407,3 +407,21 @@ def test_small_m_grouped_gemm(M):
         outs = ops.linear_group([xs[0], xs[1]], [ws[0], ws[1]])
     for o, y in zip(outs, ys):
         assert torch.allclose(o.float(), y.float(), atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("layout", ["nt", "nn"])
+def test_gemm_accumulate_epilogue(layout):
+    from rwkvtune_b200.ops import gemm
+    torch.manual_seed(3)
+    M, K, N = 1000, 64, 520            # ragged M and N tiles, LoRA-like short contraction
+    x = (torch.randn(M, K, device="cuda") * 0.5).to(BF)
+    w = (torch.randn(N, K, device="cuda") * 0.2).to(BF)
+    y0 = torch.randn(M, N, device="cuda").to(BF)
+    y = y0.clone()
+    if layout == "nt":
+        out = gemm.addmm_nt_(y, x, w)
+    else:
+        out = gemm.addmm_nn_(y, x, w.t().contiguous())
+    assert out.data_ptr() == y.data_ptr()
+    ref_y = y0.float() + x.float() @ w.float().t()
+    assert (y.float() - ref_y).abs().max().item() <= 2e-2 * ref_y.abs().max().item() + 1e-2
