@@ -473,11 +473,13 @@ int launch_ag(CUtensorMap ma, CUtensorMap mb, CUtensorMap mc, int M, int N, int 
 // C[M,N] (row-major, ldc) = op(A) op(B) in bf16 with fp32 accumulation.
 //   a_mn = 0: A is [M,K] row-major (lda);  a_mn = 1: A is stored [K,M] row-major (lda)
 //   b_mn = 0: B is [N,K] row-major (ldb);  b_mn = 1: B is stored [K,N] row-major (ldb)
-//   epilogue: 0 none, 1 relu(x)^2, 2 accumulate into the values already in C.   status: device int, set non-zero if a device-side wait timed out.
+//   epilogue: 0 none, 1 relu(x)^2, 2 add a bf16 [M,N] matrix: `residual` (row stride ldr) or, when that is null,
+//   the values already in C (in place).   status: device int, set non-zero if a device-side wait timed out.
 RWKV_EXPORT int rwkv_gemm_bf16_tcgen05(const void* a, const void* b, void* c, int M, int N, int K, long long lda,
                                        long long ldb, long long ldc, int a_mn, int b_mn, int epilogue, void* status,
-                                       void* stream) {
+                                       const void* residual, long long ldr, void* stream) {
   if (M <= 0 || N <= 0 || K <= 0) return RWKV_ERR_BAD_SHAPE;
+  if (epilogue == 2 && residual && (((uintptr_t)residual & 15) || (ldr * 2) % 16)) return RWKV_ERR_BAD_ALIGNMENT;
   static int sms = 0;
   if (!sms) {
     int dev = 0;
@@ -494,7 +496,8 @@ RWKV_EXPORT int rwkv_gemm_bf16_tcgen05(const void* a, const void* b, void* c, in
   if (r) return r;
   cudaStream_t st = (cudaStream_t)stream;
   int* sp = (int*)status;
-  const bf16* cp = (const bf16*)c;
+  const bf16* cp = residual ? (const bf16*)residual : (const bf16*)c;
+  if (residual) ldc = ldr;      // from here on ldc is only the row stride of the matrix added in the epilogue
 #define DISPATCH(AM, BMN)                                                                        \
   (epilogue == 1   ? launch<AM, BMN, 1>(ma, mb, mc, M, N, K, sp, sms, cp, ldc, st)                \
    : epilogue == 2 ? launch<AM, BMN, 2>(ma, mb, mc, M, N, K, sp, sms, cp, ldc, st)                \

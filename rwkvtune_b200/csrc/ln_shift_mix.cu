@@ -113,9 +113,12 @@ ln_shift_mix_fwd_kernel(const bf16* __restrict__ x, const float* __restrict__ ln
 // Backward.  Walks the strip in reverse; `carry` holds sum_k dO_k[t+1]*mix_k.  Emits dx, the
 // gradient of the carried row (dprev) and per-CTA partial sums of the parameter gradients in
 // `partials` [gridDim.y*gridDim.x][K+2][C]: rows 0..K-1 = dmix, K = dln_w, K+1 = dln_b.
+struct DOutPtrs { const bf16* p[6]; };   // the K output gradients may live in separate allocations
+
 template <int K>
 __global__ void __launch_bounds__(512)
-ln_shift_mix_bwd_kernel(const bf16* __restrict__ dO, const bf16* __restrict__ dlast, const bf16* __restrict__ x,
+ln_shift_mix_bwd_kernel(const DOutPtrs dO, const bf16* __restrict__ dlast, const bf16* __restrict__ dres,
+                        const bf16* __restrict__ x,
                         const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
                         const float* __restrict__ ln_w, const float* __restrict__ ln_b,
                         const float* __restrict__ mix, const bf16* __restrict__ prev, bf16* __restrict__ dx,
@@ -124,7 +127,6 @@ ln_shift_mix_bwd_kernel(const bf16* __restrict__ dO, const bf16* __restrict__ dl
   int phase = 0;
   const RowCtx rc = make_row_ctx(T, C, strip);
   const size_t row0 = (size_t)rc.b * T;
-  const size_t plane = (size_t)B * T * C;
   const float invC = 1.f / C;
 
   float w[8], bb[8], mu[K][8];
@@ -145,7 +147,7 @@ ln_shift_mix_bwd_kernel(const bf16* __restrict__ dO, const bf16* __restrict__ dl
 #pragma unroll
       for (int k = 0; k < K; ++k) {
         float g[8];
-        unpack8(ldg16(dO + (size_t)k * plane + (row0 + rc.t1) * C + rc.col), g);
+        unpack8(ldg16(dO.p[k] + (row0 + rc.t1) * C + rc.col), g);
 #pragma unroll
         for (int e = 0; e < 8; ++e) carry[e] += g[e] * mu[k][e];
       }
@@ -186,7 +188,7 @@ ln_shift_mix_bwd_kernel(const bf16* __restrict__ dO, const bf16* __restrict__ dl
 #pragma unroll
       for (int k = 0; k < K; ++k) {
         float g[8];
-        unpack8(ldg16(dO + (size_t)k * plane + (row0 + t) * C + rc.col), g);
+        unpack8(ldg16(dO.p[k] + (row0 + t) * C + rc.col), g);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           dh[e] += g[e] * (1.f - mu[k][e]);
@@ -210,6 +212,12 @@ ln_shift_mix_bwd_kernel(const bf16* __restrict__ dO, const bf16* __restrict__ dl
       float o[8];
 #pragma unroll
       for (int e = 0; e < 8; ++e) o[e] = r * (dh[e] * w[e] - c[0] * invC - xh_cur[e] * c[1] * invC);
+      if (dres) {   // gradient arriving through the residual connection around this LayerNorm
+        float rr[8];
+        unpack8(ldg16(dres + (row0 + t) * C + rc.col), rr);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] += rr[e];
+      }
       stg16(dx + (row0 + t) * C + rc.col, pack8(o));
     }
 #pragma unroll
@@ -345,7 +353,8 @@ __device__ __forceinline__ void store4f(float* p, const float* f) {
 // the block reduction of the current row.  Same `partials` layout as the kernel above.
 template <int K>
 __global__ void __launch_bounds__(512)
-ln_shift_mix_bwd_v4_kernel(const bf16* __restrict__ dO, const bf16* __restrict__ dlast, const bf16* __restrict__ x,
+ln_shift_mix_bwd_v4_kernel(const DOutPtrs dO, const bf16* __restrict__ dlast, const bf16* __restrict__ dres,
+                           const bf16* __restrict__ x,
                            const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
                            const float* __restrict__ ln_w, const float* __restrict__ ln_b,
                            const float* __restrict__ mix, const bf16* __restrict__ prev, bf16* __restrict__ dx,
@@ -356,7 +365,6 @@ ln_shift_mix_bwd_v4_kernel(const bf16* __restrict__ dO, const bf16* __restrict__
   const int col = threadIdx.x * 4;
   const bool active = col < C;
   const size_t row0 = (size_t)b * T;
-  const size_t plane = (size_t)B * T * C;
   const float invC = 1.f / C;
   auto ld4 = [](const bf16* p) { return *reinterpret_cast<const uint2*>(p); };
 
@@ -378,7 +386,7 @@ ln_shift_mix_bwd_v4_kernel(const bf16* __restrict__ dO, const bf16* __restrict__
 #pragma unroll
       for (int k = 0; k < K; ++k) {
         float g[4];
-        unpack4(ld4(dO + (size_t)k * plane + (row0 + t1) * C + col), g);
+        unpack4(ld4(dO.p[k] + (row0 + t1) * C + col), g);
 #pragma unroll
         for (int e = 0; e < 4; ++e) carry[e] += g[e] * mu[k][e];
       }
@@ -419,7 +427,7 @@ ln_shift_mix_bwd_v4_kernel(const bf16* __restrict__ dO, const bf16* __restrict__
   auto fetch = [&](int t) {
 #pragma unroll
     for (int k = 0; k < K; ++k)
-      gq[k] = (active && t >= t0) ? ld4(dO + (size_t)k * plane + (row0 + t) * C + col) : make_uint2(0u, 0u);
+      gq[k] = (active && t >= t0) ? ld4(dO.p[k] + (row0 + t) * C + col) : make_uint2(0u, 0u);
   };
 
   float xh_cur[4], h_cur[4], xh_prev[4], h_prev[4];
@@ -465,6 +473,12 @@ ln_shift_mix_bwd_v4_kernel(const bf16* __restrict__ dO, const bf16* __restrict__
       float o[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) o[e] = r * (dh[e] * w[e] - c[0] * invC - xh_cur[e] * c[1] * invC);
+      if (dres) {
+        float rr[4];
+        unpack4(ld4(dres + (row0 + t) * C + col), rr);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[e] += rr[e];
+      }
       *reinterpret_cast<uint2*>(dx + (row0 + t) * C + col) = pack4(o);
     }
 #pragma unroll
@@ -506,7 +520,10 @@ RWKV_EXPORT int rwkv_ln_shift_mix_forward(const void* x, const void* ln_w, const
   return rwkv_launch_status();
 }
 
-RWKV_EXPORT int rwkv_ln_shift_mix_backward(const void* dO, const void* dlast, const void* x, const void* mean,
+// dO: host array of K device pointers, each a bf16 [B, T, C] gradient of one mixed output.
+// dres: optional bf16 [B, T, C] added to dx (the gradient of a residual connection that bypasses this operator).
+RWKV_EXPORT int rwkv_ln_shift_mix_backward(const void* const* dO, const void* dlast, const void* dres, const void* x,
+                                           const void* mean,
                                            const void* rstd, const void* ln_w, const void* ln_b, const void* mix,
                                            const void* prev, void* dx, void* dprev, void* partials, int K, int B,
                                            int T, int C, int strip, void* stream) {
@@ -514,14 +531,20 @@ RWKV_EXPORT int rwkv_ln_shift_mix_backward(const void* dO, const void* dlast, co
   dim3 grid((T + strip - 1) / strip, B);
   const int nt = threads_for(C);
   cudaStream_t st = (cudaStream_t)stream;
+  if (K != 1 && K != 6) return RWKV_ERR_BAD_SHAPE;
+  DOutPtrs dptrs = {};
+  for (int k = 0; k < K; ++k) {
+    if (!dO[k] || ((uintptr_t)dO[k] & 15)) return RWKV_ERR_BAD_ALIGNMENT;
+    dptrs.p[k] = (const bf16*)dO[k];
+  }
 #define LAUNCH(KK)                                                                                             \
-  ln_shift_mix_bwd_kernel<KK><<<grid, nt, 0, st>>>((const bf16*)dO, (const bf16*)dlast, (const bf16*)x,        \
+  ln_shift_mix_bwd_kernel<KK><<<grid, nt, 0, st>>>(dptrs, (const bf16*)dlast, (const bf16*)dres, (const bf16*)x, \
                                                    (const float*)mean, (const float*)rstd, (const float*)ln_w, \
                                                    (const float*)ln_b, (const float*)mix, (const bf16*)prev,   \
                                                    (bf16*)dx, (float*)dprev, (float*)partials, B, T, C, strip)
   if (K == 6 && C / 4 <= 512) {
     ln_shift_mix_bwd_v4_kernel<6><<<grid, ((C / 4 + 31) / 32) * 32, 0, st>>>(
-        (const bf16*)dO, (const bf16*)dlast, (const bf16*)x, (const float*)mean, (const float*)rstd,
+        dptrs, (const bf16*)dlast, (const bf16*)dres, (const bf16*)x, (const float*)mean, (const float*)rstd,
         (const float*)ln_w, (const float*)ln_b, (const float*)mix, (const bf16*)prev, (bf16*)dx, (float*)dprev,
         (float*)partials, B, T, C, strip);
   } else if (K == 6) LAUNCH(6);

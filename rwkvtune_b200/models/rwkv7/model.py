@@ -39,6 +39,13 @@ class Linear(nn.Linear):
         return ops.linear(x, self.weight)
 
 
+def _project_add(layer: nn.Module, h: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
+    """``residual + layer(h)``; a plain, unsharded :class:`Linear` adds the residual in its GEMM epilogue."""
+    if type(layer) is Linear and getattr(layer, "_sharded", None) is None:
+        return ops.linear_add(h, layer.weight, residual)
+    return residual + layer(h)
+
+
 def _ortho(rows: int, cols: int, scale: float, generator: Optional[torch.Generator] = None) -> torch.Tensor:
     gain = math.sqrt(rows / cols) if rows > cols else 1.0
     w = torch.empty(rows, cols)
@@ -137,11 +144,10 @@ class RWKV7TimeMix(nn.Module):
     def forward(self, x, ln_w, ln_b, v_first, x_prev=None, wkv_state=None, want_state: bool = False):
         """``x`` is the *pre-LayerNorm* residual stream ``[B, T, C]``.
 
-        Returns ``(out, v_first, last_ln_row, new_wkv_state)``; the last two are
-        ``None`` unless ``want_state``.
+        Returns ``(x + out, v_first, last_ln_row, new_wkv_state)`` - the updated residual stream, not the
+        bare projection; the last two are ``None`` unless ``want_state``.
         """
-        mixed, last = ops.ln_shift_mix(x, ln_w, ln_b, self.mix_matrix(), x_prev)
-        xr, xw, xk, xv, xa, xg = mixed.unbind(0)
+        (xr, xw, xk, xv, xa, xg), last, x = ops.ln_shift_mix_unbound(x, ln_w, ln_b, self.mix_matrix(), x_prev)
 
         if self._plain_projections() and x.is_cuda and not torch.is_grad_enabled():
             r, k, v = ops.linear_group([xr, xk, xv], [self.receptance.weight, self.key.weight, self.value.weight])
@@ -164,7 +170,7 @@ class RWKV7TimeMix(nn.Module):
 
         y, new_state = ops.wkv7(r, w, k, v, a_, b_, self.head_size, state=wkv_state, return_state=want_state)
         z = ops.gn_bonus_gate(y, r, k, v, g, self.ln_x.weight, self.ln_x.bias, self.r_k, self.head_size)
-        out = self.output(z)
+        out = _project_add(self.output, z, x)      # x + output(z): the residual sum rides in the GEMM epilogue
         return out, v_first, (last if want_state else None), new_state
 
 
@@ -187,12 +193,12 @@ class RWKV7ChannelMix(nn.Module):
             self.value.weight.zero_()
 
     def forward(self, x, ln_w, ln_b, x_prev=None, want_state: bool = False):
-        mixed, last = ops.ln_shift_mix(x, ln_w, ln_b, self.x_k, x_prev)
+        (xk,), last, x = ops.ln_shift_mix_unbound(x, ln_w, ln_b, self.x_k, x_prev)
         if type(self.key) is Linear:
-            hidden = ops.linear_relu_sq(mixed[0], self.key.weight)
+            hidden = ops.linear_relu_sq(xk, self.key.weight)
         else:   # wrapped (e.g. LoRA): activation applied separately
-            hidden = ops.relu_squared(self.key(mixed[0]))
-        return self.value(hidden), (last if want_state else None)
+            hidden = ops.relu_squared(self.key(xk))
+        return _project_add(self.value, hidden, x), (last if want_state else None)
 
 
 class RWKV7Block(nn.Module):
@@ -211,11 +217,10 @@ class RWKV7Block(nn.Module):
     def forward(self, x, v_first, att_prev=None, wkv_state=None, ffn_prev=None, want_state: bool = False):
         if self.layer_id == 0 and not self.skip_ln0:
             x = ops.layer_norm(x, self.ln0.weight, self.ln0.bias)
-        att, v_first, att_last, new_wkv = self.att(x, self.ln1.weight, self.ln1.bias, v_first,
-                                                   att_prev, wkv_state, want_state)
-        x = x + att
-        ffn, ffn_last = self.ffn(x, self.ln2.weight, self.ln2.bias, ffn_prev, want_state)
-        x = x + ffn
+        # both halves return the updated residual stream
+        x, v_first, att_last, new_wkv = self.att(x, self.ln1.weight, self.ln1.bias, v_first,
+                                                 att_prev, wkv_state, want_state)
+        x, ffn_last = self.ffn(x, self.ln2.weight, self.ln2.bias, ffn_prev, want_state)
         return x, v_first, att_last, new_wkv, ffn_last
 
 

@@ -89,6 +89,15 @@ def matmul(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     return x @ w
 
 
+def linear_add(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
+    """``residual + x @ weight^T``; on CUDA the residual is added in the GEMM epilogue."""
+    if _native(x, "gemm") and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16:
+        from . import gemm
+
+        return gemm.linear_add(x, weight, residual)
+    return residual + torch.nn.functional.linear(x, weight)
+
+
 def linear_group(xs, weights):
     """Several independent ``x_i @ W_i^T`` with the same leading shape; one grouped launch while decoding."""
     if _native(xs[0], "gemm"):
@@ -116,6 +125,17 @@ def ln_shift_mix(x, ln_w, ln_b, mix, prev=None, eps: float = LAYERNORM_EPS):
     if _native(x, "ln_shift_mix"):
         return _cuda().ln_shift_mix(x, ln_w, ln_b, mix, prev, eps)
     return reference.ln_shift_mix(x, ln_w, ln_b, mix, prev, eps)
+
+
+def ln_shift_mix_unbound(x, ln_w, ln_b, mix, prev=None, eps: float = LAYERNORM_EPS):
+    """:func:`ln_shift_mix` with the mixed outputs as a tuple of ``K`` tensors (no stacked gradient in backward).
+
+    Returns ``(outs, last_row, x)``.  The third item is ``x`` again; a residual connection that adds to *it*
+    sends its gradient through this operator's backward kernel, which sums it into ``dx`` for free."""
+    if _native(x, "ln_shift_mix"):
+        return _cuda().ln_shift_mix_unbound(x, ln_w, ln_b, mix, prev, eps)
+    outs, last = reference.ln_shift_mix(x, ln_w, ln_b, mix.reshape(-1, x.shape[-1]), prev, eps)
+    return outs.unbind(0), last, x
 
 
 def timemix_prep(k, v, v_first, w_lin, a_lin, v_lin, w0, a0, v0, k_k, k_a, head_size: int = 64):

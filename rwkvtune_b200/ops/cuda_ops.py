@@ -202,22 +202,67 @@ class _LnShiftMix(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, d_outs, d_last):
-        xb, mean, rstd, w32, b32, m32, pv = ctx.saved_tensors
-        B, T, C, K, strip, xdt, ln_w, ln_b, mix, has_prev = ctx.meta
-        dO = _c(d_outs, BF16)
-        dl = None if d_last is None else _c(d_last, BF16)
-        dx = torch.empty(B, T, C, dtype=BF16, device=xb.device)
-        dprev = torch.empty(B, C, dtype=torch.float32, device=xb.device) if has_prev else None
-        n_cta = B * (-(-T // strip))
-        partials = torch.empty(n_cta, K + 2, C, dtype=torch.float32, device=xb.device)
-        call("rwkv_ln_shift_mix_backward", ptr(dO), ptr(dl), ptr(xb), ptr(mean), ptr(rstd), ptr(w32), ptr(b32),
-             ptr(m32), ptr(pv), ptr(dx), ptr(dprev), ptr(partials), i32(K), i32(B), i32(T), i32(C), i32(strip),
-             stream())
-        sums = partials.sum(0)
-        dmix = sums[:K].reshape(mix.shape).to(mix.dtype)
-        dw = sums[K].reshape(ln_w.shape).to(ln_w.dtype)
-        db = sums[K + 1].reshape(ln_b.shape).to(ln_b.dtype)
-        return dx.to(xdt), dw, db, dmix, (dprev.to(xdt) if has_prev else None), None
+        return _ln_shift_mix_backward(ctx, list(_c(d_outs, BF16).unbind(0)), d_last)
+
+
+def _ln_shift_mix_backward(ctx, d_list, d_last, d_res=None):
+    """``d_list``: K contiguous bf16 ``[B, T, C]`` gradients (separate allocations are fine: the kernel takes K
+    pointers); ``d_res``: gradient of the residual connection around the operator, summed into ``dx`` by the kernel."""
+    import ctypes
+
+    xb, mean, rstd, w32, b32, m32, pv = ctx.saved_tensors
+    B, T, C, K, strip, xdt, ln_w, ln_b, mix, has_prev = ctx.meta
+    dl = None if d_last is None else _c(d_last, BF16)
+    dx = torch.empty(B, T, C, dtype=BF16, device=xb.device)
+    dprev = torch.empty(B, C, dtype=torch.float32, device=xb.device) if has_prev else None
+    n_cta = B * (-(-T // strip))
+    partials = torch.empty(n_cta, K + 2, C, dtype=torch.float32, device=xb.device)
+    dptrs = (ctypes.c_void_p * K)(*[t.data_ptr() for t in d_list])
+    dr = None if d_res is None else _c(d_res, BF16)
+    call("rwkv_ln_shift_mix_backward", dptrs, ptr(dl), ptr(dr), ptr(xb), ptr(mean), ptr(rstd), ptr(w32), ptr(b32),
+         ptr(m32), ptr(pv), ptr(dx), ptr(dprev), ptr(partials), i32(K), i32(B), i32(T), i32(C), i32(strip),
+         stream())
+    sums = partials.sum(0)
+    dmix = sums[:K].reshape(mix.shape).to(mix.dtype)
+    dw = sums[K].reshape(ln_w.shape).to(ln_w.dtype)
+    db = sums[K + 1].reshape(ln_b.shape).to(ln_b.dtype)
+    return dx.to(xdt), dw, db, dmix, (dprev.to(xdt) if has_prev else None), None
+
+
+class _LnShiftMixUnbound(torch.autograd.Function):
+    """Same operator with the K mixed outputs returned as K tensors: their gradients then reach the backward
+    kernel as K pointers and are never stacked into one buffer."""
+
+    @staticmethod
+    def forward(ctx, x, ln_w, ln_b, mix, prev, eps):
+        outs, last = _LnShiftMix.forward(ctx, x, ln_w, ln_b, mix, prev, eps)
+        # x is handed back as an output: a residual connection that uses this copy routes its gradient through
+        # this node, where the kernel adds it to dx instead of a separate accumulation pass
+        return (*outs.unbind(0), last, x.view_as(x))
+
+    @staticmethod
+    def backward(ctx, *grads):
+        *d_outs, d_last, d_res = grads
+        B, T, C = ctx.meta[0], ctx.meta[1], ctx.meta[2]
+        zero = None
+        d_list = []
+        for g in d_outs:
+            if g is None:
+                if zero is None:
+                    zero = torch.zeros(B, T, C, dtype=BF16, device=ctx.saved_tensors[0].device)
+                g = zero
+            d_list.append(_c(g, BF16))
+        return _ln_shift_mix_backward(ctx, d_list, d_last, d_res)
+
+
+def ln_shift_mix_unbound(x, ln_w, ln_b, mix, prev=None, eps: float = ref.LAYERNORM_EPS):
+    """Returns ``((out_0, ..., out_{K-1}), last_row, x)``; use the returned ``x`` for the residual connection."""
+    K = mix.numel() // x.shape[-1]
+    if K not in (1, 6) or x.shape[-1] % 64:
+        outs, last = ref.ln_shift_mix(x, ln_w, ln_b, mix.reshape(K, -1), prev, eps)
+        return outs.unbind(0), last, x
+    res = _LnShiftMixUnbound.apply(x, ln_w, ln_b, mix, prev, eps)
+    return res[:-2], res[-2], res[-1]
 
 
 def ln_shift_mix(x, ln_w, ln_b, mix, prev=None, eps: float = ref.LAYERNORM_EPS):

@@ -109,6 +109,37 @@ class _Linear(torch.autograd.Function):
         return dx, dw
 
 
+class _LinearAdd(torch.autograd.Function):
+    """``residual + x @ w^T`` with the sum formed in the GEMM epilogue (residual stream update of a block)."""
+
+    @staticmethod
+    def forward(ctx, x, w, residual):
+        ctx.save_for_backward(x, w)
+        x2 = x.reshape(-1, x.shape[-1])
+        r2 = residual.reshape(-1, residual.shape[-1])
+        n = _native()
+        if _acc_ok(n, r2) and n.native_ok(x2, w, "nt"):
+            y = n.mm_nt(x2, w, residual=r2)
+        else:
+            y = r2 + mm_nt(x2, w)
+        return y.reshape(residual.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = mm_nn(dy2, w).reshape(x.shape)
+        if ctx.needs_input_grad[1]:
+            dw = mm_tn(dy2, x.reshape(-1, x.shape[-1]))
+        return dx, dw, (dy if ctx.needs_input_grad[2] else None)
+
+
+def linear_add(x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
+    return _LinearAdd.apply(x, w, residual)
+
+
 class _MatMul(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w):

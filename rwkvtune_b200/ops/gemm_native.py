@@ -52,21 +52,27 @@ def native_ok(x: torch.Tensor, w: torch.Tensor, layout: str) -> bool:
     return tiles >= 64 or K <= 4096
 
 
-def _run(a, b, M, N, K, a_mn: int, b_mn: int, epilogue: int = 0, out: torch.Tensor = None) -> torch.Tensor:
-    """``out`` given: accumulate into it (epilogue 2, ``out += op(a) op(b)``); it must be bf16 ``[M, N]`` with unit inner stride."""
+def _run(a, b, M, N, K, a_mn: int, b_mn: int, epilogue: int = 0, out: torch.Tensor = None,
+         residual: torch.Tensor = None) -> torch.Tensor:
+    """``out`` given: accumulate into it (epilogue 2, ``out += op(a) op(b)``).  ``residual`` given: return
+    ``residual + op(a) op(b)`` in a new tensor.  Both must be bf16 ``[M, N]`` with unit inner stride."""
     if out is not None:
         c, epilogue = out, 2
     else:
         c = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+        if residual is not None:
+            epilogue = 2
     _ext.call("rwkv_gemm_bf16_tcgen05", _ext.ptr(a), _ext.ptr(b), _ext.ptr(c), _ext.i32(M), _ext.i32(N), _ext.i32(K),
               _ext.i64(a.stride(0)), _ext.i64(b.stride(0)), _ext.i64(c.stride(0)), _ext.i32(a_mn), _ext.i32(b_mn),
-              _ext.i32(epilogue), _ext.ptr(_status(a.device)), _ext.stream())
+              _ext.i32(epilogue), _ext.ptr(_status(a.device)), _ext.ptr(residual),
+              _ext.i64(0 if residual is None else residual.stride(0)), _ext.stream())
     return c
 
 
-def mm_nt(x: torch.Tensor, w: torch.Tensor, epilogue: int = 0, out: torch.Tensor = None) -> torch.Tensor:
+def mm_nt(x: torch.Tensor, w: torch.Tensor, epilogue: int = 0, out: torch.Tensor = None,
+          residual: torch.Tensor = None) -> torch.Tensor:
     """``x [M,K] @ w[N,K]^T``"""
-    return _run(x, w, x.shape[0], w.shape[0], x.shape[1], 0, 0, epilogue, out)
+    return _run(x, w, x.shape[0], w.shape[0], x.shape[1], 0, 0, epilogue, out, residual)
 
 
 def mm_nn(x: torch.Tensor, w: torch.Tensor, epilogue: int = 0, out: torch.Tensor = None) -> torch.Tensor:
