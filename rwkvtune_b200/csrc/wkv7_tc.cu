@@ -28,6 +28,8 @@
 // These small dependent products are issued with mma.sync from registers: tcgen05 needs operands in
 // shared memory and results read back from tensor memory between every dependent product, which costs
 // more than the 16x16x64 products themselves.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace {
@@ -106,16 +108,27 @@ __device__ __forceinline__ void ld8f(float (&f)[8], const float* p) {
 template <class SM>
 __device__ __forceinline__ void build_operands(SM& sm, int chunk, int T) {
   const int tid = threadIdx.x;
-  if (tid < N) {
+  {
+    // log-decay prefix sums over the 16 steps: thread (channel j, half h) scans steps 8h .. 8h+7, the second half
+    // then adds the first half's total (one shared-memory exchange)
+    const int j = tid & (N - 1), hf = tid >> 6;
     const bf16* wrow = reinterpret_cast<const bf16*>(&sm.raw[RW][0][0]);
+    float c[8];
     float acc = 0.f;
 #pragma unroll
-    for (int t = 0; t < L; ++t) {
+    for (int i = 0; i < 8; ++i) {
+      const int t = hf * 8 + i;
       const bool live = chunk * L + t < T;
-      acc += live ? -__expf(__bfloat162float(wrow[t * (RAWLD * 8) + tid])) : 0.f;
-      sm.E[t][tid] = __expf(acc);
+      acc += live ? -__expf(__bfloat162float(wrow[t * (RAWLD * 8) + j])) : 0.f;
+      c[i] = acc;
     }
-    sm.gL[tid] = __expf(acc);
+    float* half_total = &sm.Mab[0][0];   // scratch (Mab itself is produced later, after barriers)
+    if (hf == 0) half_total[j] = acc;
+    __syncthreads();
+    const float base = hf ? half_total[j] : 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sm.E[hf * 8 + i][j] = __expf(c[i] + base);
+    if (hf) sm.gL[j] = __expf(c[7] + base);
   }
   __syncthreads();
   const int row = tid >> 3, part = tid & 7, j0 = part * 8;
@@ -193,17 +206,21 @@ __device__ __forceinline__ void build_small_matrices(SM& sm) {
     }
   }
   __syncthreads();
-  if (warp == 0 && lane < L) {   // row `lane` of (I - Mab)^-1 by forward substitution
-    float x[L];
+  if (warp == 0 && lane < L) {
+    // Row `lane` of X = (I - Mab)^-1:  x[t] = [t == lane] + sum_{s<t} x[s] Mab[s][t].  Column-oriented: as soon as
+    // x[s] is known it is pushed into every later accumulator, so the dependent chain is one FMA per step and the
+    // other 15 - s FMAs of the step are independent.
+    float acc[L];
 #pragma unroll
-    for (int t = 0; t < L; ++t) {
-      float acc = (lane == t) ? 1.f : 0.f;
+    for (int t = 0; t < L; ++t) acc[t] = (lane == t) ? 1.f : 0.f;
 #pragma unroll
-      for (int s = 0; s < t; ++s) acc += x[s] * sm.Mab[s][t];
-      x[t] = acc;
-      const bf16 hv = __float2bfloat16_rn(acc);
-      sm.TinvT[t][lane] = hv;
-      if (WITH_N) sm.TinvN[lane][t] = hv;
+    for (int s_ = 0; s_ < L; ++s_) {
+      const float xs = acc[s_];
+#pragma unroll
+      for (int t = s_ + 1; t < L; ++t) acc[t] += xs * sm.Mab[s_][t];
+      const bf16 hv = __float2bfloat16_rn(xs);
+      sm.TinvT[s_][lane] = hv;
+      if (WITH_N) sm.TinvN[lane][s_] = hv;
     }
   }
   __syncthreads();
@@ -468,6 +485,9 @@ struct BScanSm {
 };
 
 // Reverse walk.  dstates[c] = dS at the END of chunk c (bf16); ds0 = dS at the start of the sequence.
+// FROM_FWD: `ws` is the forward pass's workspace (WsFwd, kept by the caller), whose Pb and Tinv are stored
+// transposed; otherwise it is the WsBwd written by the prep kernel in mode 1.
+template <bool FROM_FWD>
 __global__ void __launch_bounds__(NT)
 wkv7_tc_bwd_scan_kernel(const bf16* __restrict__ dy_, const unsigned char* __restrict__ ws,
                         const float* __restrict__ ds_final, bf16* __restrict__ dstates, float* __restrict__ ds0,
@@ -488,16 +508,22 @@ wkv7_tc_bwd_scan_kernel(const bf16* __restrict__ dy_, const unsigned char* __res
     if (i < NC) {
       const int c = NC - 1 - i;
       BScanStage& s = sm.st[i % STAGES];
-      const WsBwd* w = reinterpret_cast<const WsBwd*>(ws + (((size_t)bb * H + h) * NC + c) * sizeof(WsBwd));
+      using Ws = typename std::conditional<FROM_FWD, WsFwd, WsBwd>::type;
+      const Ws* w = reinterpret_cast<const Ws*>(ws + (((size_t)bb * H + h) * NC + c) * sizeof(Ws));
       cp16(&s.At[row][part * 8], &w->At[row][part * 8], true);
       cp16(&s.Qt[row][part * 8], &w->Qt[row][part * 8], true);
       cp16(&s.Bb[row][part * 8], &w->Bb[row][part * 8], true);
       const int t = c * L + row;
       const bool live = t < T;
       cp16(&s.dYs[row][part * 8], dy_ + base + (size_t)(live ? t : 0) * tok_stride + part * 8, live);
-      if (part < 2) {
-        cp16(&s.PbN[row][part * 8], &w->PbN[row][part * 8], true);
-        cp16(&s.TinvN[row][part * 8], &w->TinvN[row][part * 8], true);
+      if (part < 2) {   // PbN / TinvN hold the transposed matrices when the source is the forward workspace
+        if constexpr (FROM_FWD) {
+          cp16(&s.PbN[row][part * 8], &w->PbT[row][part * 8], true);
+          cp16(&s.TinvN[row][part * 8], &w->TinvT[row][part * 8], true);
+        } else {
+          cp16(&s.PbN[row][part * 8], &w->PbN[row][part * 8], true);
+          cp16(&s.TinvN[row][part * 8], &w->TinvN[row][part * 8], true);
+        }
       }
       if (tid < 16) cp16(&s.gL[tid * 4], &w->gL[tid * 4], true);
     }
@@ -526,8 +552,13 @@ wkv7_tc_bwd_scan_kernel(const bf16* __restrict__ dy_, const unsigned char* __res
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk) load_b(bBb[kk], &s.Bb[0][0], LDS_, 0, kk * 16, lane);
     load_a_t(dya, &s.dYs[0][0], LDS_, 0, m0, lane);
-    load_b(bPb, &s.PbN[0][0], LDM, 0, 0, lane);
-    load_b(bTinv, &s.TinvN[0][0], LDM, 0, 0, lane);
+    if constexpr (FROM_FWD) {   // stored [t][s]: B[k=t][n=s] is a transposed load
+      load_b_t(bPb, &s.PbN[0][0], LDM, 0, 0, lane);
+      load_b_t(bTinv, &s.TinvN[0][0], LDM, 0, 0, lane);
+    } else {
+      load_b(bPb, &s.PbN[0][0], LDM, 0, 0, lane);
+      load_b(bTinv, &s.TinvN[0][0], LDM, 0, 0, lane);
+    }
 #pragma unroll
     for (int n2 = 0; n2 < 4; ++n2) {
       load_b_t(bQt[n2], &s.Qt[0][0], LDS_, 0, n2 * 16, lane);
@@ -877,7 +908,8 @@ int configure_once() {
   if (status >= 0) return status;
   cudaError_t e = set_smem(wkv7_tc_prep_kernel, sizeof(PrepSm));
   if (e == cudaSuccess) e = set_smem(wkv7_tc_scan_kernel, sizeof(ScanSm));
-  if (e == cudaSuccess) e = set_smem(wkv7_tc_bwd_scan_kernel, sizeof(BScanSm));
+  if (e == cudaSuccess) e = set_smem(wkv7_tc_bwd_scan_kernel<false>, sizeof(BScanSm));
+  if (e == cudaSuccess) e = set_smem(wkv7_tc_bwd_scan_kernel<true>, sizeof(BScanSm));
   if (e == cudaSuccess) e = set_smem(wkv7_tc_bwd_chunk_kernel, sizeof(BwdSm));
   if (e != cudaSuccess) return RWKV_ERR_CUDA_BASE + (int)e;
   status = 0;
@@ -910,21 +942,28 @@ RWKV_EXPORT int rwkv_wkv7_tc_forward(const void* q, const void* w, const void* k
 }
 
 // dy and the six gradients: bf16 [B,T,H,64]; chunk_states from the forward; ds_final (in) / ds0 (out): fp32
-// [B,H,64,64] or null; dstates: scratch bf16 [B,H,ceil(T/16),64,64]; ws: rwkv_wkv7_tc_ws_bytes(..., 1) bytes.
+// [B,H,64,64] or null; dstates: scratch bf16 [B,H,ceil(T/16),64,64].
+// ws_is_forward = 0: ws is scratch of rwkv_wkv7_tc_ws_bytes(..., 1) bytes, filled here by the prep kernel;
+// ws_is_forward = 1: ws is the workspace the forward call of the SAME inputs filled (kept by the caller), and
+// the prep kernel is skipped.
 RWKV_EXPORT int rwkv_wkv7_tc_backward(const void* q, const void* w, const void* k, const void* v, const void* a,
                                       const void* b, const void* dy, const void* chunk_states, const void* ds_final,
-                                      void* dstates, void* ws, void* dq, void* dw, void* dk, void* dv, void* da,
-                                      void* db, void* ds0, int B, int T, int H, void* stream) {
+                                      void* dstates, void* ws, int ws_is_forward, void* dq, void* dw, void* dk,
+                                      void* dv, void* da, void* db, void* ds0, int B, int T, int H, void* stream) {
   if (B <= 0 || T <= 0 || H <= 0 || B > 65535 || H > 65535) return RWKV_ERR_BAD_SHAPE;
   if (int rc = configure_once()) return rc;
   const int NC = (T + L - 1) / L;
   cudaStream_t st = (cudaStream_t)stream;
-  wkv7_tc_prep_kernel<<<dim3(NC, H, B), NT, sizeof(PrepSm), st>>>((const bf16*)q, (const bf16*)w, (const bf16*)k,
-                                                                  (const bf16*)v, (const bf16*)a, (const bf16*)b,
-                                                                  (unsigned char*)ws, T, H, 1);
-  wkv7_tc_bwd_scan_kernel<<<dim3(H, B), NT, sizeof(BScanSm), st>>>((const bf16*)dy, (const unsigned char*)ws,
-                                                                   (const float*)ds_final, (bf16*)dstates, (float*)ds0,
-                                                                   T, H);
+  if (ws_is_forward) {
+    wkv7_tc_bwd_scan_kernel<true><<<dim3(H, B), NT, sizeof(BScanSm), st>>>(
+        (const bf16*)dy, (const unsigned char*)ws, (const float*)ds_final, (bf16*)dstates, (float*)ds0, T, H);
+  } else {
+    wkv7_tc_prep_kernel<<<dim3(NC, H, B), NT, sizeof(PrepSm), st>>>((const bf16*)q, (const bf16*)w, (const bf16*)k,
+                                                                    (const bf16*)v, (const bf16*)a, (const bf16*)b,
+                                                                    (unsigned char*)ws, T, H, 1);
+    wkv7_tc_bwd_scan_kernel<false><<<dim3(H, B), NT, sizeof(BScanSm), st>>>(
+        (const bf16*)dy, (const unsigned char*)ws, (const float*)ds_final, (bf16*)dstates, (float*)ds0, T, H);
+  }
   wkv7_tc_bwd_chunk_kernel<<<dim3(NC, H, B), NT, sizeof(BwdSm), st>>>(
       (const bf16*)q, (const bf16*)w, (const bf16*)k, (const bf16*)v, (const bf16*)a, (const bf16*)b, (const bf16*)dy,
       (const bf16*)chunk_states, (const bf16*)dstates, (bf16*)dq, (bf16*)dw, (bf16*)dk, (bf16*)dv, (bf16*)da,

@@ -102,7 +102,7 @@ class TrainEngine:
         self.tokens_seen = 0
 
     # ------------------------------------------------------------------ memory-aware checkpointing
-    SAVED_UNITS_PER_LAYER = 32.0   # [tokens, n_embd] bf16 tensors a block keeps for backward without checkpointing
+    SAVED_UNITS_PER_LAYER = 37.0   # [tokens, n_embd] bf16 tensors a block keeps for backward without checkpointing
 
     def autotune_checkpointing(self, batch: int, seq_len: int, reserve_fraction: float = 0.10) -> int:
         """With ``grad_cp=1`` the reference recomputes every block in backward.  180 GB of HBM usually has

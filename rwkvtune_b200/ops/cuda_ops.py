@@ -94,7 +94,9 @@ class _WKV7TC(torch.autograd.Function):
         call("rwkv_wkv7_tc_forward", ptr(r), ptr(w), ptr(k), ptr(v), ptr(a), ptr(b), ptr(s0), ptr(y), ptr(cs),
              ptr(s_final), ptr(ws), i32(B), i32(T), i32(H), stream())
         if need_grad:
-            ctx.save_for_backward(r, w, k, v, a, b, cs)
+            # the chunk-parallel products of the forward (10.5 KB per chunk) serve the reverse scan as they are;
+            # keeping them costs memory (5 [tokens, C] bf16 units per layer) and saves a prep pass in backward
+            ctx.save_for_backward(r, w, k, v, a, b, cs, *((ws,) if WKV7_KEEP_WORKSPACE else ()))
         ctx.has_state = state is not None
         ctx.out_dtype = out_dtype
         ctx.shape = (B, T, H)
@@ -103,16 +105,17 @@ class _WKV7TC(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy, ds_final):
-        r, w, k, v, a, b, cs = ctx.saved_tensors
+        r, w, k, v, a, b, cs, *kept = ctx.saved_tensors
         B, T, H = ctx.shape
         dy = _c(dy, BF16)
         ds_T = None if ds_final is None else _c(ds_final, torch.float32)
         grads = [torch.empty_like(r) for _ in range(6)]
         ds0 = torch.empty(B, H, 64, 64, dtype=torch.float32, device=r.device) if ctx.has_state else None
         dstates = torch.empty_like(cs)
-        ws = _tc_ws(B, T, H, 1, r.device)
+        ws = kept[0] if kept else _tc_ws(B, T, H, 1, r.device)
         call("rwkv_wkv7_tc_backward", ptr(r), ptr(w), ptr(k), ptr(v), ptr(a), ptr(b), ptr(dy), ptr(cs), ptr(ds_T),
-             ptr(dstates), ptr(ws), *(ptr(g) for g in grads), ptr(ds0), i32(B), i32(T), i32(H), stream())
+             ptr(dstates), ptr(ws), i32(1 if kept else 0), *(ptr(g) for g in grads), ptr(ds0), i32(B), i32(T), i32(H),
+             stream())
         if ctx.out_dtype != BF16:
             grads = [g.to(ctx.out_dtype) for g in grads]
         return (*grads, ds0, None)
@@ -122,6 +125,7 @@ class _WKV7TC(torch.autograd.Function):
 # chunks).  "simt" / "tc" force one implementation (A/B measurements and tests).
 WKV7_IMPL = "auto"
 TC_MIN_T = 32
+WKV7_KEEP_WORKSPACE = True    # keep the forward's chunk products for the backward (memory for time)
 
 
 def wkv7(r, w, k, v, a, b, head_size: int = 64, state: Optional[torch.Tensor] = None, return_state: bool = False):

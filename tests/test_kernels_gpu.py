@@ -44,8 +44,11 @@ def _relnorm(a, b):
 
 
 @pytest.mark.parametrize("B,T,H,with_state", [(2, 64, 2, False), (1, 37, 3, True), (2, 128, 1, True), (1, 272, 2, True)])
-@pytest.mark.parametrize("impl", ["simt", "tc"])
-def test_wkv7_forward_backward(B, T, H, with_state, impl, wkv_impl):
+@pytest.mark.parametrize("impl", ["simt", "tc", "tc-recompute"])
+def test_wkv7_forward_backward(B, T, H, with_state, impl, wkv_impl, monkeypatch):
+    from rwkvtune_b200.ops import cuda_ops
+    monkeypatch.setattr(cuda_ops, "WKV7_KEEP_WORKSPACE", impl == "tc")   # "tc-recompute": backward runs its own prep pass
+    impl = impl.split("-")[0]
     wkv_impl(impl)
     ins = _wkv_inputs(B, T, H)
     s0 = (torch.randn(B, H, 64, 64, device="cuda") * 0.1) if with_state else None
