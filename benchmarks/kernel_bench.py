@@ -132,6 +132,25 @@ def bench_gemm(B, T, C, out, tf):
             out[f"gemm_nt_{name}_{tag}_frac_peak"] = 2 * M * K * N / ms / 1e9 / tf
 
 
+def bench_loss(C, out, hbm, M=8192, V=65536):
+    """Head + cross-entropy + L2Wrap, forward and backward in one sweep (two 4096-row slabs)."""
+    x = (torch.randn(M, C, device="cuda") * 0.5).to(BF).requires_grad_(True)
+    w = (torch.randn(V, C, device="cuda") * 0.02).to(BF).requires_grad_(True)
+    labels = torch.randint(0, V, (M,), device="cuda")
+    ms = timeit(lambda: ops.linear_cross_entropy(x, w, labels, True, -100, M))
+    out["linear_ce_fwd_bwd_ms"] = ms
+    out["linear_ce_fwd_bwd_tflops"] = 3 * 2 * M * V * C / ms / 1e9
+    logits = torch.randn(4096, V, device="cuda").to(BF)
+    from rwkvtune_b200.ops._ext import call, f32, i32, i64, ptr, stream
+    inv_n = torch.full((1,), 1.0 / 4096, device="cuda")
+    rows = torch.empty(4096, device="cuda")
+    lab = labels[:4096].contiguous()
+    ms = timeit(lambda: call("rwkv_ce_rows", ptr(logits), ptr(lab), ptr(inv_n), f32(1e-8), i64(-100), ptr(rows), i32(1),
+                             i64(4096), i32(V), stream()))
+    out["ce_rows_slab_ms"] = ms
+    out["ce_rows_frac_hbm"] = 2 * logits.numel() * 2 / ms / 1e6 / hbm     # one read (the re-read hits L2) + one write
+
+
 def _graph_time(fn):
     """Device time of ``fn`` replayed from a CUDA graph (decode steps run from graphs; eager timing of
     microsecond kernels would measure the host)."""
@@ -182,6 +201,8 @@ def main():
         bench_elementwise(a.B, a.T, a.C, out, hbm)
     if not only or "gemm" in only:
         bench_gemm(a.B, a.T, a.C, out, tf)
+    if not only or "loss" in only:
+        bench_loss(a.C, out, hbm)
     if not only or "decode" in only:
         bench_decode_gemm(a.C, out, hbm)
     for k, v in out.items():

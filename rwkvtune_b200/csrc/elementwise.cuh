@@ -56,12 +56,9 @@ __device__ __forceinline__ void block_sum(float (&v)[NV], float* buf, int& phase
     for (int i = 0; i < NV; ++i) slot[warp * NV + i] = v[i];
   }
   __syncthreads();
+  // every warp folds the per-warp partials itself: lane w reads warp w's value, then one shuffle tree
 #pragma unroll
-  for (int i = 0; i < NV; ++i) {
-    float s = 0.f;
-    for (int w = 0; w < nw; ++w) s += slot[w * NV + i];
-    v[i] = s;
-  }
+  for (int i = 0; i < NV; ++i) v[i] = warp_sum(lane < nw ? slot[lane * NV + i] : 0.f);
   phase ^= 1;
 }
 

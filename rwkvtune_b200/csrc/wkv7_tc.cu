@@ -28,8 +28,6 @@
 // These small dependent products are issued with mma.sync from registers: tcgen05 needs operands in
 // shared memory and results read back from tensor memory between every dependent product, which costs
 // more than the 16x16x64 products themselves.
-#include <type_traits>
-
 #include "common.cuh"
 
 namespace {
@@ -102,35 +100,39 @@ __device__ __forceinline__ void ld8f(float (&f)[8], const float* p) {
   f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
 }
 
+// Prefix products of the decay over the 16 steps of a chunk: E[t][j] = exp(sum_{i<=t} -exp(w_i[j])) (fp32) and,
+// with WRITE_GL, gL[j] = E[15][j].  Thread (channel j, half h) scans steps 8h .. 8h+7, the second half then adds
+// the first half's total (`scratch`: 64 floats).  All NT threads; ends with a block barrier.
+template <bool WRITE_GL>
+__device__ __forceinline__ void decay_scan(const bf16* wrow, int ld, float (*E)[NP], float* gL, float* scratch,
+                                           int chunk, int T) {
+  const int tid = threadIdx.x;
+  const int j = tid & (N - 1), hf = tid >> 6;
+  float c[8];
+  float acc = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int t = hf * 8 + i;
+    const bool live = chunk * L + t < T;
+    acc += live ? -__expf(__bfloat162float(wrow[t * ld + j])) : 0.f;
+    c[i] = acc;
+  }
+  if (hf == 0) scratch[j] = acc;
+  __syncthreads();
+  const float base = hf ? scratch[j] : 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) E[hf * 8 + i][j] = __expf(c[i] + base);
+  if (WRITE_GL && hf) gL[j] = __expf(c[7] + base);
+  __syncthreads();
+}
+
 // From sm.raw (q w k v a b of one chunk, bf16, rows past the sequence end zero-filled) builds
 //   E[t][j] = gamma_t (fp32), gL = gamma_L, and the bf16 operand arrays At Bt Kt Qt Bb Kb Vs.
 // All NT threads; thread (row, part) handles 8 consecutive channels of one step.
 template <class SM>
 __device__ __forceinline__ void build_operands(SM& sm, int chunk, int T) {
   const int tid = threadIdx.x;
-  {
-    // log-decay prefix sums over the 16 steps: thread (channel j, half h) scans steps 8h .. 8h+7, the second half
-    // then adds the first half's total (one shared-memory exchange)
-    const int j = tid & (N - 1), hf = tid >> 6;
-    const bf16* wrow = reinterpret_cast<const bf16*>(&sm.raw[RW][0][0]);
-    float c[8];
-    float acc = 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int t = hf * 8 + i;
-      const bool live = chunk * L + t < T;
-      acc += live ? -__expf(__bfloat162float(wrow[t * (RAWLD * 8) + j])) : 0.f;
-      c[i] = acc;
-    }
-    float* half_total = &sm.Mab[0][0];   // scratch (Mab itself is produced later, after barriers)
-    if (hf == 0) half_total[j] = acc;
-    __syncthreads();
-    const float base = hf ? half_total[j] : 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) sm.E[hf * 8 + i][j] = __expf(c[i] + base);
-    if (hf) sm.gL[j] = __expf(c[7] + base);
-  }
-  __syncthreads();
+  decay_scan<true>(reinterpret_cast<const bf16*>(&sm.raw[RW][0][0]), RAWLD * 8, sm.E, sm.gL, &sm.Mab[0][0], chunk, T);
   const int row = tid >> 3, part = tid & 7, j0 = part * 8;
   float e[8], ep[8], gl[8], qv[8], kv[8], av[8], bv[8];
   ld8f(e, &sm.E[row][j0]);
@@ -180,9 +182,8 @@ __device__ __forceinline__ void small_xzt(float (&c0)[4], float (&c1)[4], const 
 }
 
 // Intra-chunk matrices (independent of the state): Mab (fp32), Mka, Pb, Pk and Tinv = (I - Mab)^-1 in bf16,
-// stored transposed (xT[t][s] = x[s][t]) and, with WITH_N, also untransposed (xN[s][t]).
-// Ends with a block barrier: all outputs are visible on return.
-template <bool WITH_N, class SM>
+// stored transposed (xT[t][s] = x[s][t]).  Ends with a block barrier: all outputs are visible on return.
+template <class SM>
 __device__ __forceinline__ void build_small_matrices(SM& sm) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, tq = lane & 3;
@@ -200,9 +201,9 @@ __device__ __forceinline__ void build_small_matrices(SM& sm) {
       if (strict ? (s >= t) : (s > t)) val = 0.f;
       const bf16 hv = __float2bfloat16_rn(val);
       if (warp == 0) sm.Mab[s][t] = val;
-      else if (warp == 1) { sm.MkaT[t][s] = hv; if (WITH_N) sm.MkaN[s][t] = hv; }
-      else if (warp == 2) { sm.PbT[t][s] = hv; if (WITH_N) sm.PbN[s][t] = hv; }
-      else { sm.PkT[t][s] = hv; if (WITH_N) sm.PkN[s][t] = hv; }
+      else if (warp == 1) sm.MkaT[t][s] = hv;
+      else if (warp == 2) sm.PbT[t][s] = hv;
+      else sm.PkT[t][s] = hv;
     }
   }
   __syncthreads();
@@ -218,9 +219,7 @@ __device__ __forceinline__ void build_small_matrices(SM& sm) {
       const float xs = acc[s_];
 #pragma unroll
       for (int t = s_ + 1; t < L; ++t) acc[t] += xs * sm.Mab[s_][t];
-      const bf16 hv = __float2bfloat16_rn(xs);
-      sm.TinvT[s_][lane] = hv;
-      if (WITH_N) sm.TinvN[lane][s_] = hv;
+      sm.TinvT[s_][lane] = __float2bfloat16_rn(xs);
     }
   }
   __syncthreads();
@@ -232,12 +231,6 @@ struct WsFwd {          // per chunk, 10496 bytes
   bf16 MkaT[L][L], PbT[L][L], PkT[L][L], TinvT[L][L];
   float gL[N];
 };
-struct WsBwd {          // per chunk, 7424 bytes: what the reverse scan needs
-  bf16 At[L][N], Qt[L][N], Bb[L][N];
-  bf16 PbN[L][L], TinvN[L][L];
-  float gL[N];
-};
-
 struct PrepSm {
   uint4 raw[6][L][RAWLD];
   float E[L][NP];
@@ -245,7 +238,6 @@ struct PrepSm {
   bf16 At[L][LDS_], Bt[L][LDS_], Kt[L][LDS_], Qt[L][LDS_], Bb[L][LDS_], Kb[L][LDS_], Vs[L][LDS_];
   float Mab[L][L + 1];
   bf16 MkaT[L][LDM], PbT[L][LDM], PkT[L][LDM], TinvT[L][LDM];
-  bf16 MkaN[L][LDM], PbN[L][LDM], PkN[L][LDM], TinvN[L][LDM];
 };
 
 // Loads the six raw input tiles of chunk c (rows past T zero-filled) with cp.async; caller waits.
@@ -260,11 +252,11 @@ __device__ __forceinline__ void load_raw_chunk(SM& sm, const bf16* const (&src)[
   for (int u = 0; u < 6; ++u) cp16(&sm.raw[u][row][part], src[u] + off, live);
 }
 
-// grid (NC, H, B).  mode 0: write WsFwd; mode 1: write WsBwd.
+// grid (NC, H, B): one chunk per CTA, writes that chunk's WsFwd.
 __global__ void __launch_bounds__(NT)
 wkv7_tc_prep_kernel(const bf16* __restrict__ q_, const bf16* __restrict__ w_, const bf16* __restrict__ k_,
                     const bf16* __restrict__ v_, const bf16* __restrict__ a_, const bf16* __restrict__ b_,
-                    unsigned char* __restrict__ ws, int T, int H, int mode) {
+                    unsigned char* __restrict__ ws, int T, int H) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   PrepSm& sm = *reinterpret_cast<PrepSm*>(smem_raw);
   const int c = blockIdx.x, h = blockIdx.y, bb = blockIdx.z;
@@ -276,35 +268,22 @@ wkv7_tc_prep_kernel(const bf16* __restrict__ q_, const bf16* __restrict__ w_, co
   cp_wait<0>();
   __syncthreads();
   build_operands(sm, c, T);
-  if (mode == 0) build_small_matrices<false>(sm);
-  else build_small_matrices<true>(sm);
+  build_small_matrices(sm);
   const size_t chunk_id = ((size_t)bb * H + h) * NC + c;
   const int row = tid >> 3, part = tid & 7, j0 = part * 8;
   auto cpy = [](bf16* dst, const bf16* src_) { *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src_); };
-  if (mode == 0) {
-    WsFwd* o = reinterpret_cast<WsFwd*>(ws + chunk_id * sizeof(WsFwd));
-    cpy(&o->At[row][j0], &sm.At[row][j0]);
-    cpy(&o->Qt[row][j0], &sm.Qt[row][j0]);
-    cpy(&o->Bb[row][j0], &sm.Bb[row][j0]);
-    cpy(&o->Kb[row][j0], &sm.Kb[row][j0]);
-    if (part < 2) {
-      cpy(&o->MkaT[row][j0], &sm.MkaT[row][j0]);
-      cpy(&o->PbT[row][j0], &sm.PbT[row][j0]);
-      cpy(&o->PkT[row][j0], &sm.PkT[row][j0]);
-      cpy(&o->TinvT[row][j0], &sm.TinvT[row][j0]);
-    }
-    if (tid < N) o->gL[tid] = sm.gL[tid];
-  } else {
-    WsBwd* o = reinterpret_cast<WsBwd*>(ws + chunk_id * sizeof(WsBwd));
-    cpy(&o->At[row][j0], &sm.At[row][j0]);
-    cpy(&o->Qt[row][j0], &sm.Qt[row][j0]);
-    cpy(&o->Bb[row][j0], &sm.Bb[row][j0]);
-    if (part < 2) {
-      cpy(&o->PbN[row][j0], &sm.PbN[row][j0]);
-      cpy(&o->TinvN[row][j0], &sm.TinvN[row][j0]);
-    }
-    if (tid < N) o->gL[tid] = sm.gL[tid];
+  WsFwd* o = reinterpret_cast<WsFwd*>(ws + chunk_id * sizeof(WsFwd));
+  cpy(&o->At[row][j0], &sm.At[row][j0]);
+  cpy(&o->Qt[row][j0], &sm.Qt[row][j0]);
+  cpy(&o->Bb[row][j0], &sm.Bb[row][j0]);
+  cpy(&o->Kb[row][j0], &sm.Kb[row][j0]);
+  if (part < 2) {
+    cpy(&o->MkaT[row][j0], &sm.MkaT[row][j0]);
+    cpy(&o->PbT[row][j0], &sm.PbT[row][j0]);
+    cpy(&o->PkT[row][j0], &sm.PkT[row][j0]);
+    cpy(&o->TinvT[row][j0], &sm.TinvT[row][j0]);
   }
+  if (tid < N) o->gL[tid] = sm.gL[tid];
 }
 
 // ------------------------------------------------------------------------------------------ scans
@@ -477,7 +456,7 @@ wkv7_tc_scan_kernel(const bf16* __restrict__ v_, const unsigned char* __restrict
 
 struct BScanStage {
   bf16 At[L][LDS_], Qt[L][LDS_], Bb[L][LDS_], dYs[L][LDS_];
-  bf16 PbN[L][LDM], TinvN[L][LDM];
+  bf16 PbT[L][LDM], TinvT[L][LDM];
   float gL[N];
 };
 struct BScanSm {
@@ -485,9 +464,7 @@ struct BScanSm {
 };
 
 // Reverse walk.  dstates[c] = dS at the END of chunk c (bf16); ds0 = dS at the start of the sequence.
-// FROM_FWD: `ws` is the forward pass's workspace (WsFwd, kept by the caller), whose Pb and Tinv are stored
-// transposed; otherwise it is the WsBwd written by the prep kernel in mode 1.
-template <bool FROM_FWD>
+// `ws` is a forward workspace (WsFwd): Pb and Tinv are stored transposed.
 __global__ void __launch_bounds__(NT)
 wkv7_tc_bwd_scan_kernel(const bf16* __restrict__ dy_, const unsigned char* __restrict__ ws,
                         const float* __restrict__ ds_final, bf16* __restrict__ dstates, float* __restrict__ ds0,
@@ -508,22 +485,16 @@ wkv7_tc_bwd_scan_kernel(const bf16* __restrict__ dy_, const unsigned char* __res
     if (i < NC) {
       const int c = NC - 1 - i;
       BScanStage& s = sm.st[i % STAGES];
-      using Ws = typename std::conditional<FROM_FWD, WsFwd, WsBwd>::type;
-      const Ws* w = reinterpret_cast<const Ws*>(ws + (((size_t)bb * H + h) * NC + c) * sizeof(Ws));
+      const WsFwd* w = reinterpret_cast<const WsFwd*>(ws + (((size_t)bb * H + h) * NC + c) * sizeof(WsFwd));
       cp16(&s.At[row][part * 8], &w->At[row][part * 8], true);
       cp16(&s.Qt[row][part * 8], &w->Qt[row][part * 8], true);
       cp16(&s.Bb[row][part * 8], &w->Bb[row][part * 8], true);
       const int t = c * L + row;
       const bool live = t < T;
       cp16(&s.dYs[row][part * 8], dy_ + base + (size_t)(live ? t : 0) * tok_stride + part * 8, live);
-      if (part < 2) {   // PbN / TinvN hold the transposed matrices when the source is the forward workspace
-        if constexpr (FROM_FWD) {
-          cp16(&s.PbN[row][part * 8], &w->PbT[row][part * 8], true);
-          cp16(&s.TinvN[row][part * 8], &w->TinvT[row][part * 8], true);
-        } else {
-          cp16(&s.PbN[row][part * 8], &w->PbN[row][part * 8], true);
-          cp16(&s.TinvN[row][part * 8], &w->TinvN[row][part * 8], true);
-        }
+      if (part < 2) {
+        cp16(&s.PbT[row][part * 8], &w->PbT[row][part * 8], true);
+        cp16(&s.TinvT[row][part * 8], &w->TinvT[row][part * 8], true);
       }
       if (tid < 16) cp16(&s.gL[tid * 4], &w->gL[tid * 4], true);
     }
@@ -552,13 +523,8 @@ wkv7_tc_bwd_scan_kernel(const bf16* __restrict__ dy_, const unsigned char* __res
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk) load_b(bBb[kk], &s.Bb[0][0], LDS_, 0, kk * 16, lane);
     load_a_t(dya, &s.dYs[0][0], LDS_, 0, m0, lane);
-    if constexpr (FROM_FWD) {   // stored [t][s]: B[k=t][n=s] is a transposed load
-      load_b_t(bPb, &s.PbN[0][0], LDM, 0, 0, lane);
-      load_b_t(bTinv, &s.TinvN[0][0], LDM, 0, 0, lane);
-    } else {
-      load_b(bPb, &s.PbN[0][0], LDM, 0, 0, lane);
-      load_b(bTinv, &s.TinvN[0][0], LDM, 0, 0, lane);
-    }
+    load_b_t(bPb, &s.PbT[0][0], LDM, 0, 0, lane);      // stored [t][s]: B[k=t][n=s] is a transposed load
+    load_b_t(bTinv, &s.TinvT[0][0], LDM, 0, 0, lane);
 #pragma unroll
     for (int n2 = 0; n2 < 4; ++n2) {
       load_b_t(bQt[n2], &s.Qt[0][0], LDS_, 0, n2 * 16, lane);
@@ -600,25 +566,23 @@ wkv7_tc_bwd_scan_kernel(const bf16* __restrict__ dy_, const unsigned char* __res
 
 // ------------------------------------------------------------------------------------------ bwd chunk
 struct BwdSm {
-  uint4 raw[6][L][RAWLD];
+  bf16 wraw[L][N];                                 // log-decay inputs of the chunk
   float E[L][NP];
   float gL[N];
   bf16 At[L][LDS_], Bt[L][LDS_], Kt[L][LDS_], Qt[L][LDS_], Bb[L][LDS_], Kb[L][LDS_], Vs[L][LDS_];
   bf16 dYs[L][LDS_];
   bf16 S0s[N][LDS_], dSs[N][LDS_];
-  float Mab[L][L + 1];
-  bf16 MkaT[L][LDM], PbT[L][LDM], PkT[L][LDM], TinvT[L][LDM];
-  bf16 MkaN[L][LDM], PbN[L][LDM], PkN[L][LDM], TinvN[L][LDM];
-  bf16 dPbT[L][LDM], dPbN[L][LDM], dPkT[L][LDM], dPkN[L][LDM];
-  bf16 dMkaT[L][LDM], dMkaN[L][LDM], dMabT[L][LDM], dMabN[L][LDM];
+  bf16 MkaT[L][LDM], PbT[L][LDM], PkT[L][LDM], TinvT[L][LDM];       // from the forward workspace
+  bf16 dPbN[L][LDM], dPkN[L][LDM], dMkaN[L][LDM], dMabN[L][LDM];
   bf16 Us[4][L][LDM], dRs[4][L][LDM];              // per warp: [v_local][s]
   bf16 dVs[L][LDS_];
-  float sds[4][N], extra[N];
+  float sds[4][N], extra[N], scratch[N];
   union {
-    float part4[4][4][L][L + 1];                   // per warp: partial dPb dPk dMka dMab over its value rows
+    float part2[2][4][L][L + 1];                   // partial dPb dPk dMka dMab: warps 0,1 store, warps 2,3 add
     struct { float Gs[L][NP], ada[L][NP], xs[L][NP]; } fin;
   } u;
 };
+static_assert(sizeof(BwdSm) <= 74 * 1024, "three CTAs of the chunk backward must fit one SM");
 enum { A_DPB = 0, A_DPK, A_DMKA, A_DMAB };
 
 __device__ __forceinline__ void store_tile(float (*dst)[L + 1], const float (&c0)[4], const float (&c1)[4], int g, int tq) {
@@ -635,7 +599,7 @@ __global__ void __launch_bounds__(NT)
 wkv7_tc_bwd_chunk_kernel(const bf16* __restrict__ q_, const bf16* __restrict__ w_, const bf16* __restrict__ k_,
                          const bf16* __restrict__ v_, const bf16* __restrict__ a_, const bf16* __restrict__ b_,
                          const bf16* __restrict__ dy_, const bf16* __restrict__ chunk_states,
-                         const bf16* __restrict__ dstates, bf16* __restrict__ dq_, bf16* __restrict__ dw_,
+                         const bf16* __restrict__ dstates, const unsigned char* __restrict__ ws, bf16* __restrict__ dq_, bf16* __restrict__ dw_,
                          bf16* __restrict__ dk_, bf16* __restrict__ dv_, bf16* __restrict__ da_, bf16* __restrict__ db_,
                          int T, int H) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -651,11 +615,26 @@ wkv7_tc_bwd_chunk_kernel(const bf16* __restrict__ q_, const bf16* __restrict__ w
   const size_t chunk_id = ((size_t)bb * H + h) * NC + c;
 
   {
-    const bf16* const src[6] = {q_, w_, k_, v_, a_, b_};
-    load_raw_chunk(sm, src, base, tok_stride, c, T);
+    // scaled operands and the four 16x16 matrices come from the forward pass's workspace; raw v, dy, w and the
+    // two 64x64 states from their own tensors
+    const WsFwd* w = reinterpret_cast<const WsFwd*>(ws + chunk_id * sizeof(WsFwd));
+    cp16(&sm.At[row][j0], &w->At[row][j0], true);
+    cp16(&sm.Qt[row][j0], &w->Qt[row][j0], true);
+    cp16(&sm.Bb[row][j0], &w->Bb[row][j0], true);
+    cp16(&sm.Kb[row][j0], &w->Kb[row][j0], true);
+    if (part < 2) {
+      cp16(&sm.MkaT[row][j0], &w->MkaT[row][j0], true);
+      cp16(&sm.PbT[row][j0], &w->PbT[row][j0], true);
+      cp16(&sm.PkT[row][j0], &w->PkT[row][j0], true);
+      cp16(&sm.TinvT[row][j0], &w->TinvT[row][j0], true);
+    }
+    if (tid < 16) cp16(&sm.gL[tid * 4], &w->gL[tid * 4], true);
     const int t = c * L + row;
     const bool live = t < T;
-    cp16(&sm.dYs[row][j0], dy_ + base + (size_t)(live ? t : 0) * tok_stride + j0, live);
+    const size_t off = base + (size_t)(live ? t : 0) * tok_stride + j0;
+    cp16(&sm.Vs[row][j0], v_ + off, live);
+    cp16(&sm.dYs[row][j0], dy_ + off, live);
+    cp16(&sm.wraw[row][j0], w_ + off, live);
     const bf16* s0p = chunk_states + chunk_id * N * N;
     const bf16* dsp = dstates + chunk_id * N * N;
 #pragma unroll
@@ -668,8 +647,22 @@ wkv7_tc_bwd_chunk_kernel(const bf16* __restrict__ q_, const bf16* __restrict__ w
   }
   cp_wait<0>();
   __syncthreads();
-  build_operands(sm, c, T);
-  build_small_matrices<true>(sm);
+  decay_scan<false>(&sm.wraw[0][0], N, sm.E, nullptr, sm.scratch, c, T);
+  {  // Bt = b / gamma_t = Bb / gamma_L, Kt likewise (thread (row, part): 8 channels of one step)
+    float bbv[8], kbv[8], gl[8];
+    unpack8(*reinterpret_cast<const uint4*>(&sm.Bb[row][j0]), bbv);
+    unpack8(*reinterpret_cast<const uint4*>(&sm.Kb[row][j0]), kbv);
+    ld8f(gl, &sm.gL[j0]);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float inv = __fdividef(1.f, gl[i]);
+      bbv[i] *= inv;
+      kbv[i] *= inv;
+    }
+    *reinterpret_cast<uint4*>(&sm.Bt[row][j0]) = pack8(bbv);
+    *reinterpret_cast<uint4*>(&sm.Kt[row][j0]) = pack8(kbv);
+  }
+  __syncthreads();
 
   {  // sds[q][j] = gamma_L[j] * sum over 16 value rows of S0[v][j] dS[v][j]   (d log gamma_L through the carried state)
     const int jp = tid & 31, qd = tid >> 5;
@@ -712,10 +705,10 @@ wkv7_tc_bwd_chunk_kernel(const bf16* __restrict__ q_, const bf16* __restrict__ w
     load_b(b, &sm.MkaT[0][0], LDM, 0, 0, lane);
     mma16816(r0, va, b[0], b[1]);
     mma16816(r1, va, b[2], b[3]);
-    load_b(b, &sm.PbN[0][0], LDM, 0, 0, lane);
+    load_b_t(b, &sm.PbT[0][0], LDM, 0, 0, lane);
     mma16816(du0, dya, b[0], b[1]);
     mma16816(du1, dya, b[2], b[3]);
-    load_b(b, &sm.PkN[0][0], LDM, 0, 0, lane);
+    load_b_t(b, &sm.PkT[0][0], LDM, 0, 0, lane);
     mma16816(dv0, dya, b[0], b[1]);
     mma16816(dv1, dya, b[2], b[3]);
     uint32_t ra[4], dua[4], dra[4];
@@ -725,11 +718,11 @@ wkv7_tc_bwd_chunk_kernel(const bf16* __restrict__ q_, const bf16* __restrict__ w
     mma16816(u0, ra, b[0], b[1]);
     mma16816(u1, ra, b[2], b[3]);
     acc_to_a(dua, du0, du1);
-    load_b(b, &sm.TinvN[0][0], LDM, 0, 0, lane);
+    load_b_t(b, &sm.TinvT[0][0], LDM, 0, 0, lane);
     mma16816(dr0, dua, b[0], b[1]);
     mma16816(dr1, dua, b[2], b[3]);
     acc_to_a(dra, dr0, dr1);
-    load_b(b, &sm.MkaN[0][0], LDM, 0, 0, lane);
+    load_b_t(b, &sm.MkaT[0][0], LDM, 0, 0, lane);
     mma16816(dv0, dra, b[0], b[1]);
     mma16816(dv1, dra, b[2], b[3]);
 #pragma unroll
@@ -749,29 +742,44 @@ wkv7_tc_bwd_chunk_kernel(const bf16* __restrict__ q_, const bf16* __restrict__ w
     load_a(aV, &sm.Vs[0][0], LDS_, 0, m0, lane);            // A[s][v] = V[s][v]
     load_b(bdY, &sm.dYs[0][0], LDS_, 0, m0, lane);          // B[v][t] = dY[t][v]
     load_b_t(bdR, &sm.dRs[warp][0][0], LDM, 0, 0, lane);    // B[v][t] = dR[v][t]
-    float c0[4], c1[4];
+    float pc[4][2][4];
 #pragma unroll
     for (int m = 0; m < 4; ++m) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) c0[e] = c1[e] = 0.f;
+      for (int e = 0; e < 4; ++e) pc[m][0][e] = pc[m][1][e] = 0.f;
       const uint32_t (&A_)[4] = (m == A_DPB || m == A_DMAB) ? aUt : aV;
       const uint32_t (&B_)[4] = (m == A_DPB || m == A_DPK) ? bdY : bdR;
-      mma16816(c0, A_, B_[0], B_[1]);
-      mma16816(c1, A_, B_[2], B_[3]);
-      store_tile(sm.u.part4[warp][m], c0, c1, g, tq);
+      mma16816(pc[m][0], A_, B_[0], B_[1]);
+      mma16816(pc[m][1], A_, B_[2], B_[3]);
+    }
+    // cross-warp sum in two rounds: warps 0,1 store their fragments, warps 2,3 add theirs at the same positions
+    if (warp < 2) {
+#pragma unroll
+      for (int m = 0; m < 4; ++m) store_tile(sm.u.part2[warp][m], pc[m][0], pc[m][1], g, tq);
+    }
+    __syncthreads();
+    if (warp >= 2) {
+#pragma unroll
+      for (int m = 0; m < 4; ++m) {
+        float (*dst)[L + 1] = sm.u.part2[warp - 2][m];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int s_ = g + (e >> 1) * 8, t_ = tq * 2 + (e & 1);
+          dst[s_][t_] += pc[m][0][e];
+          dst[s_][t_ + 8] += pc[m][1][e];
+        }
+      }
     }
   }
   __syncthreads();
-  // masks (Pb, Pk: s <= t; Mka, Mab: s < t) and bf16 copies in both orientations
+  // masks (Pb, Pk: s <= t; Mka, Mab: s < t), bf16
   for (int e = tid; e < 4 * L * L; e += NT) {
-    const int m = e >> 8, s = (e >> 4) & 15, t = e & 15;
-    const float val = sm.u.part4[0][m][s][t] + sm.u.part4[1][m][s][t] + sm.u.part4[2][m][s][t] + sm.u.part4[3][m][s][t];
-    const bool keep = (m == A_DPB || m == A_DPK) ? (s <= t) : (s < t);
+    const int m = e >> 8, s_ = (e >> 4) & 15, t_ = e & 15;
+    const float val = sm.u.part2[0][m][s_][t_] + sm.u.part2[1][m][s_][t_];
+    const bool keep = (m == A_DPB || m == A_DPK) ? (s_ <= t_) : (s_ < t_);
     const bf16 hv = __float2bfloat16_rn(keep ? val : 0.f);
-    if (m == A_DPB) { sm.dPbN[s][t] = hv; sm.dPbT[t][s] = hv; }
-    else if (m == A_DPK) { sm.dPkN[s][t] = hv; sm.dPkT[t][s] = hv; }
-    else if (m == A_DMKA) { sm.dMkaN[s][t] = hv; sm.dMkaT[t][s] = hv; }
-    else { sm.dMabN[s][t] = hv; sm.dMabT[t][s] = hv; }
+    bf16 (*dst)[LDM] = m == A_DPB ? sm.dPbN : m == A_DPK ? sm.dPkN : m == A_DMKA ? sm.dMkaN : sm.dMabN;
+    dst[s_][t_] = hv;
   }
   __syncthreads();
 
@@ -803,14 +811,14 @@ wkv7_tc_bwd_chunk_kernel(const bf16* __restrict__ q_, const bf16* __restrict__ w
     }
     // contractions over the 16 steps
     load_b_t(b, &sm.Bt[0][0], LDS_, 0, m0, lane);
-    load_a(a, &sm.dPbT[0][0], LDM, 0, 0, lane);
+    load_a_t(a, &sm.dPbN[0][0], LDM, 0, 0, lane);
     mma16816(dQt[0], a, b[0], b[1]); mma16816(dQt[1], a, b[2], b[3]);
-    load_a(a, &sm.dMabT[0][0], LDM, 0, 0, lane);
+    load_a_t(a, &sm.dMabN[0][0], LDM, 0, 0, lane);
     mma16816(dAt[0], a, b[0], b[1]); mma16816(dAt[1], a, b[2], b[3]);
     load_b_t(b, &sm.Kt[0][0], LDS_, 0, m0, lane);
-    load_a(a, &sm.dPkT[0][0], LDM, 0, 0, lane);
+    load_a_t(a, &sm.dPkN[0][0], LDM, 0, 0, lane);
     mma16816(dQt[0], a, b[0], b[1]); mma16816(dQt[1], a, b[2], b[3]);
-    load_a(a, &sm.dMkaT[0][0], LDM, 0, 0, lane);
+    load_a_t(a, &sm.dMkaN[0][0], LDM, 0, 0, lane);
     mma16816(dAt[0], a, b[0], b[1]); mma16816(dAt[1], a, b[2], b[3]);
     load_b_t(b, &sm.At[0][0], LDS_, 0, m0, lane);
     load_a(a, &sm.dMkaN[0][0], LDM, 0, 0, lane);
@@ -827,8 +835,10 @@ wkv7_tc_bwd_chunk_kernel(const bf16* __restrict__ q_, const bf16* __restrict__ w
 
   // ---- undo the decay scaling; G = d loss / d log gamma_t
   bf16 (*odq)[LDS_] = sm.At, (*oda)[LDS_] = sm.Bt, (*odb)[LDS_] = sm.Kt, (*odk)[LDS_] = sm.Qt;
-  auto raw2 = [&](int which, int t, int j) {
-    return __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(&sm.raw[which][t][0])[j >> 1]);
+  auto raw2 = [&](const bf16* src, int t, int j) {   // the chunk's inputs were read moments ago: these hit L2
+    const int tt = c * L + t;
+    if (tt >= T) return make_float2(0.f, 0.f);
+    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + base + (size_t)tt * tok_stride + j));
   };
   auto st2 = [](bf16* p, float x, float y) { *reinterpret_cast<uint32_t*>(p) = pack_bf16(x, y); };
 #pragma unroll
@@ -839,7 +849,7 @@ wkv7_tc_bwd_chunk_kernel(const bf16* __restrict__ q_, const bf16* __restrict__ w
       const float2 E = *reinterpret_cast<const float2*>(&sm.E[t][j]);
       const float2 Ep = t ? *reinterpret_cast<const float2*>(&sm.E[t - 1][j]) : make_float2(1.f, 1.f);
       const float2 gl = *reinterpret_cast<const float2*>(&sm.gL[j]);
-      const float2 qv = raw2(RQ, t, j), kv = raw2(RK, t, j), av = raw2(RA, t, j), bv = raw2(RB, t, j);
+      const float2 qv = raw2(q_, t, j), kv = raw2(k_, t, j), av = raw2(a_, t, j), bv = raw2(b_, t, j);
       const float ix = __fdividef(1.f, E.x), iy = __fdividef(1.f, E.y);
       const float lx = gl.x * ix, ly = gl.y * iy;
       const float dqx = dQt[i][e0] * E.x, dqy = dQt[i][e1] * E.y;
@@ -882,7 +892,7 @@ wkv7_tc_bwd_chunk_kernel(const bf16* __restrict__ q_, const bf16* __restrict__ w
     const int t = c * L + row;
     if (t < T) {
       float wv[8], dw[8];
-      unpack8(sm.raw[RW][row][part], wv);
+      unpack8(*reinterpret_cast<const uint4*>(&sm.wraw[row][j0]), wv);
 #pragma unroll
       for (int i = 0; i < 8; ++i) dw[i] = -__expf(wv[i]) * gsum[i];
       const size_t off = base + (size_t)t * tok_stride + j0;
@@ -908,8 +918,7 @@ int configure_once() {
   if (status >= 0) return status;
   cudaError_t e = set_smem(wkv7_tc_prep_kernel, sizeof(PrepSm));
   if (e == cudaSuccess) e = set_smem(wkv7_tc_scan_kernel, sizeof(ScanSm));
-  if (e == cudaSuccess) e = set_smem(wkv7_tc_bwd_scan_kernel<false>, sizeof(BScanSm));
-  if (e == cudaSuccess) e = set_smem(wkv7_tc_bwd_scan_kernel<true>, sizeof(BScanSm));
+  if (e == cudaSuccess) e = set_smem(wkv7_tc_bwd_scan_kernel, sizeof(BScanSm));
   if (e == cudaSuccess) e = set_smem(wkv7_tc_bwd_chunk_kernel, sizeof(BwdSm));
   if (e != cudaSuccess) return RWKV_ERR_CUDA_BASE + (int)e;
   status = 0;
@@ -917,15 +926,15 @@ int configure_once() {
 }
 }  // namespace
 
-// Workspace bytes for the forward (mode 0) or backward (mode 1) prep output.
-RWKV_EXPORT long long rwkv_wkv7_tc_ws_bytes(int B, int T, int H, int mode) {
+// Bytes of the chunk-product workspace the forward fills and the backward reads.
+RWKV_EXPORT long long rwkv_wkv7_tc_ws_bytes(int B, int T, int H) {
   const long long NC = (T + L - 1) / L;
-  return (long long)B * H * NC * (long long)(mode == 0 ? sizeof(WsFwd) : sizeof(WsBwd));
+  return (long long)B * H * NC * (long long)sizeof(WsFwd);
 }
 
 // q,w,k,v,a,b,y: bf16 [B,T,H,64]; s0/s_final: fp32 [B,H,64,64] or null (row = value channel, column = key
 // channel); chunk_states: bf16 [B,H,ceil(T/16),64,64] or null - the state at the START of each chunk;
-// ws: rwkv_wkv7_tc_ws_bytes(..., 0) bytes, 16-byte aligned.
+// ws: rwkv_wkv7_tc_ws_bytes() bytes, 16-byte aligned; it may be kept for the backward call.
 RWKV_EXPORT int rwkv_wkv7_tc_forward(const void* q, const void* w, const void* k, const void* v, const void* a,
                                      const void* b, const void* s0, void* y, void* chunk_states, void* s_final,
                                      void* ws, int B, int T, int H, void* stream) {
@@ -935,7 +944,7 @@ RWKV_EXPORT int rwkv_wkv7_tc_forward(const void* q, const void* w, const void* k
   cudaStream_t st = (cudaStream_t)stream;
   wkv7_tc_prep_kernel<<<dim3(NC, H, B), NT, sizeof(PrepSm), st>>>((const bf16*)q, (const bf16*)w, (const bf16*)k,
                                                                   (const bf16*)v, (const bf16*)a, (const bf16*)b,
-                                                                  (unsigned char*)ws, T, H, 0);
+                                                                  (unsigned char*)ws, T, H);
   wkv7_tc_scan_kernel<<<dim3(H, B), NT, sizeof(ScanSm), st>>>((const bf16*)v, (const unsigned char*)ws, (const float*)s0,
                                                               (bf16*)y, (bf16*)chunk_states, (float*)s_final, T, H);
   return rwkv_launch_status();
@@ -943,9 +952,8 @@ RWKV_EXPORT int rwkv_wkv7_tc_forward(const void* q, const void* w, const void* k
 
 // dy and the six gradients: bf16 [B,T,H,64]; chunk_states from the forward; ds_final (in) / ds0 (out): fp32
 // [B,H,64,64] or null; dstates: scratch bf16 [B,H,ceil(T/16),64,64].
-// ws_is_forward = 0: ws is scratch of rwkv_wkv7_tc_ws_bytes(..., 1) bytes, filled here by the prep kernel;
-// ws_is_forward = 1: ws is the workspace the forward call of the SAME inputs filled (kept by the caller), and
-// the prep kernel is skipped.
+// ws: rwkv_wkv7_tc_ws_bytes() bytes.  ws_is_forward = 1: it still holds what the forward call on the SAME inputs
+// wrote (kept by the caller); ws_is_forward = 0: scratch, refilled here by the prep kernel.
 RWKV_EXPORT int rwkv_wkv7_tc_backward(const void* q, const void* w, const void* k, const void* v, const void* a,
                                       const void* b, const void* dy, const void* chunk_states, const void* ds_final,
                                       void* dstates, void* ws, int ws_is_forward, void* dq, void* dw, void* dk,
@@ -954,19 +962,16 @@ RWKV_EXPORT int rwkv_wkv7_tc_backward(const void* q, const void* w, const void* 
   if (int rc = configure_once()) return rc;
   const int NC = (T + L - 1) / L;
   cudaStream_t st = (cudaStream_t)stream;
-  if (ws_is_forward) {
-    wkv7_tc_bwd_scan_kernel<true><<<dim3(H, B), NT, sizeof(BScanSm), st>>>(
-        (const bf16*)dy, (const unsigned char*)ws, (const float*)ds_final, (bf16*)dstates, (float*)ds0, T, H);
-  } else {
+  if (!ws_is_forward)
     wkv7_tc_prep_kernel<<<dim3(NC, H, B), NT, sizeof(PrepSm), st>>>((const bf16*)q, (const bf16*)w, (const bf16*)k,
                                                                     (const bf16*)v, (const bf16*)a, (const bf16*)b,
-                                                                    (unsigned char*)ws, T, H, 1);
-    wkv7_tc_bwd_scan_kernel<false><<<dim3(H, B), NT, sizeof(BScanSm), st>>>(
-        (const bf16*)dy, (const unsigned char*)ws, (const float*)ds_final, (bf16*)dstates, (float*)ds0, T, H);
-  }
+                                                                    (unsigned char*)ws, T, H);
+  wkv7_tc_bwd_scan_kernel<<<dim3(H, B), NT, sizeof(BScanSm), st>>>((const bf16*)dy, (const unsigned char*)ws,
+                                                                   (const float*)ds_final, (bf16*)dstates, (float*)ds0,
+                                                                   T, H);
   wkv7_tc_bwd_chunk_kernel<<<dim3(NC, H, B), NT, sizeof(BwdSm), st>>>(
       (const bf16*)q, (const bf16*)w, (const bf16*)k, (const bf16*)v, (const bf16*)a, (const bf16*)b, (const bf16*)dy,
-      (const bf16*)chunk_states, (const bf16*)dstates, (bf16*)dq, (bf16*)dw, (bf16*)dk, (bf16*)dv, (bf16*)da,
+      (const bf16*)chunk_states, (const bf16*)dstates, (const unsigned char*)ws, (bf16*)dq, (bf16*)dw, (bf16*)dk, (bf16*)dv, (bf16*)da,
       (bf16*)db, T, H);
   return rwkv_launch_status();
 }

@@ -69,9 +69,9 @@ class _WKV7(torch.autograd.Function):
         return (*grads, ds0, None)
 
 
-def _tc_ws(B, T, H, mode, device):
-    n = B * H * ((T + 15) // 16) * (10496 if mode == 0 else 7424)
-    return torch.empty(n, dtype=torch.uint8, device=device)
+def _tc_ws(B, T, H, device):
+    """Chunk-product workspace of the tensor-core WKV7 kernels (10 496 bytes per 16-step chunk)."""
+    return torch.empty(B * H * ((T + 15) // 16) * 10496, dtype=torch.uint8, device=device)
 
 
 class _WKV7TC(torch.autograd.Function):
@@ -90,7 +90,7 @@ class _WKV7TC(torch.autograd.Function):
         y = torch.empty(B, T, C, dtype=BF16, device=r.device)
         cs = torch.empty(B, H, NC, 64, 64, dtype=BF16, device=r.device) if need_grad else None
         s_final = torch.empty(B, H, 64, 64, dtype=torch.float32, device=r.device) if return_state else None
-        ws = _tc_ws(B, T, H, 0, r.device)
+        ws = _tc_ws(B, T, H, r.device)
         call("rwkv_wkv7_tc_forward", ptr(r), ptr(w), ptr(k), ptr(v), ptr(a), ptr(b), ptr(s0), ptr(y), ptr(cs),
              ptr(s_final), ptr(ws), i32(B), i32(T), i32(H), stream())
         if need_grad:
@@ -112,7 +112,7 @@ class _WKV7TC(torch.autograd.Function):
         grads = [torch.empty_like(r) for _ in range(6)]
         ds0 = torch.empty(B, H, 64, 64, dtype=torch.float32, device=r.device) if ctx.has_state else None
         dstates = torch.empty_like(cs)
-        ws = kept[0] if kept else _tc_ws(B, T, H, 1, r.device)
+        ws = kept[0] if kept else _tc_ws(B, T, H, r.device)
         call("rwkv_wkv7_tc_backward", ptr(r), ptr(w), ptr(k), ptr(v), ptr(a), ptr(b), ptr(dy), ptr(cs), ptr(ds_T),
              ptr(dstates), ptr(ws), i32(1 if kept else 0), *(ptr(g) for g in grads), ptr(ds0), i32(B), i32(T), i32(H),
              stream())
@@ -580,7 +580,7 @@ def wkv7_tc_forward(r, w, k, v, a, b, state=None, return_state=False, save_chunk
     NC = (T + 15) // 16
     cs = torch.empty(B, H, NC, 64, 64, dtype=BF16, device=r.device) if save_chunk_states else None
     sf = torch.empty(B, H, 64, 64, dtype=torch.float32, device=r.device) if return_state else None
-    ws = _tc_ws(B, T, H, 0, r.device)
+    ws = _tc_ws(B, T, H, r.device)
     call("rwkv_wkv7_tc_forward", ptr(r), ptr(w), ptr(k), ptr(v), ptr(a), ptr(b), ptr(s0), ptr(y), ptr(cs), ptr(sf),
          ptr(ws), i32(B), i32(T), i32(H), stream())
     return y, sf, cs
