@@ -56,22 +56,27 @@ ln_shift_mix_fwd_kernel(const bf16* __restrict__ x, const float* __restrict__ ln
     for (int e = 0; e < 8; ++e) hprev[e] = round_bf16((xf[e] - mean) * rstd * w[e] + bb[e]);
   }
 
+  // raw tiles of the next four rows are fetched before the reductions of the current four
+  uint4 xq[4];
+  auto fetch4 = [&](int tg) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int t = tg + i;
+      xq[i] = (t < rc.t1 && rc.active) ? ldg16(x + (row0 + t) * C + rc.col) : make_uint4(0u, 0u, 0u, 0u);
+    }
+  };
+  fetch4(rc.t0);
   for (int tg = rc.t0; tg < rc.t1; tg += 4) {
     float xf[4][8];
     float s[4], q[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       s[i] = 0.f;
-      const int t = tg + i;
-      if (t < rc.t1 && rc.active) {
-        unpack8(ldg16(x + (row0 + t) * C + rc.col), xf[i]);
+      unpack8(xq[i], xf[i]);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) s[i] += xf[i][e];
-      } else {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) xf[i][e] = 0.f;
-      }
+      for (int e = 0; e < 8; ++e) s[i] += xf[i][e];
     }
+    if (tg + 4 < rc.t1) fetch4(tg + 4);
     block_sum<4>(s, red, phase);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -542,15 +547,19 @@ RWKV_EXPORT int rwkv_ln_shift_mix_backward(const void* const* dO, const void* dl
                                                    (const float*)mean, (const float*)rstd, (const float*)ln_w, \
                                                    (const float*)ln_b, (const float*)mix, (const bf16*)prev,   \
                                                    (bf16*)dx, (float*)dprev, (float*)partials, B, T, C, strip)
-  if (K == 6 && C / 4 <= 512) {
-    ln_shift_mix_bwd_v4_kernel<6><<<grid, ((C / 4 + 31) / 32) * 32, 0, st>>>(
-        dptrs, (const bf16*)dlast, (const bf16*)dres, (const bf16*)x, (const float*)mean, (const float*)rstd,
-        (const float*)ln_w, (const float*)ln_b, (const float*)mix, (const bf16*)prev, (bf16*)dx, (float*)dprev,
-        (float*)partials, B, T, C, strip);
+#define LAUNCH_V4(KK)                                                                                          \
+  ln_shift_mix_bwd_v4_kernel<KK><<<grid, ((C / 4 + 31) / 32) * 32, 0, st>>>(                                    \
+      dptrs, (const bf16*)dlast, (const bf16*)dres, (const bf16*)x, (const float*)mean, (const float*)rstd,      \
+      (const float*)ln_w, (const float*)ln_b, (const float*)mix, (const bf16*)prev, (bf16*)dx, (float*)dprev,    \
+      (float*)partials, B, T, C, strip)
+  if (C / 4 <= 512) {   // four channels per thread with row prefetch
+    if (K == 6) LAUNCH_V4(6);
+    else LAUNCH_V4(1);
   } else if (K == 6) LAUNCH(6);
   else if (K == 1) LAUNCH(1);
   else return RWKV_ERR_BAD_SHAPE;
 #undef LAUNCH
+#undef LAUNCH_V4
   return rwkv_launch_status();
 }
 
