@@ -91,6 +91,11 @@ class LoraLinear(nn.Module):
             return lora_ag_linear(x, sw, self.lora_A, self.lora_B, self.scaling)
         if self.disabled or self.merged:
             return self.base_layer(x)
+        if not torch.is_grad_enabled() and x.is_cuda and x.numel() // x.shape[-1] <= 256:
+            # decode-sized batch: three library GEMMs, the adapter product added by the last one (beta = 1, alpha = scaling)
+            x2 = x.reshape(-1, x.shape[-1])
+            y = torch.addmm(x2 @ self.base_layer.weight.t(), x2 @ self.lora_A.t(), self.lora_B.t(), alpha=self.scaling)
+            return y.reshape(*x.shape[:-1], self.out_features)
         if isinstance(self.lora_dropout, nn.Dropout) and self.training:
             base = self.base_layer(x)
             xd = self.lora_dropout(x)
