@@ -85,15 +85,6 @@ __device__ __forceinline__ void acc_to_a(uint32_t (&a)[4], const float (&c0)[4],
   a[3] = pack_bf16(c1[2], c1[3]);
 }
 
-// Same for a warp that owns only rows 0..7 of the 16-row tile: rows 8..15 of the A operand are zero, so the
-// accumulator elements [2], [3] (rows g + 8) stay zero and are never read.
-__device__ __forceinline__ void acc_to_a8(uint32_t (&a)[4], const float (&c0)[4], const float (&c1)[4]) {
-  a[0] = pack_bf16(c0[0], c0[1]);
-  a[1] = 0u;
-  a[2] = pack_bf16(c1[0], c1[1]);
-  a[3] = 0u;
-}
-
 enum { RQ = 0, RW, RK, RV, RA, RB };
 
 __device__ __forceinline__ void cp16(void* dst, const void* src, bool pred) {
@@ -298,31 +289,28 @@ wkv7_tc_prep_kernel(const bf16* __restrict__ q_, const bf16* __restrict__ w_, co
 // ------------------------------------------------------------------------------------------ scans
 constexpr int STAGES = 3;
 
-// accumulator rows [m0, m0+8) x 64 columns <-> global fp32 / bf16 [64][64]   (the scans give each warp 8 state rows:
-// twice as many warps per SM hide the latency of the dependent chunk steps; accumulator elements [2], [3] unused)
-constexpr int SCAN_NT = 256;
+// accumulator rows [m0, m0+16) x 64 columns <-> global fp32 / bf16 [64][64]
 __device__ __forceinline__ void load_state_f32(float (&S)[8][4], const float* p, int m0, int g, int tq) {
 #pragma unroll
   for (int n = 0; n < 8; ++n)
 #pragma unroll
-    for (int hh = 0; hh < 1; ++hh) {
+    for (int hh = 0; hh < 2; ++hh) {
       const float2 t2 = *reinterpret_cast<const float2*>(p + (m0 + g + hh * 8) * N + n * 8 + tq * 2);
       S[n][hh * 2] = t2.x; S[n][hh * 2 + 1] = t2.y;
-      S[n][2] = S[n][3] = 0.f;
     }
 }
 __device__ __forceinline__ void store_state_f32(const float (&S)[8][4], float* p, int m0, int g, int tq) {
 #pragma unroll
   for (int n = 0; n < 8; ++n)
 #pragma unroll
-    for (int hh = 0; hh < 1; ++hh)
+    for (int hh = 0; hh < 2; ++hh)
       *reinterpret_cast<float2*>(p + (m0 + g + hh * 8) * N + n * 8 + tq * 2) = make_float2(S[n][hh * 2], S[n][hh * 2 + 1]);
 }
 __device__ __forceinline__ void store_state_bf16(const float (&S)[8][4], bf16* p, int m0, int g, int tq) {
 #pragma unroll
   for (int n = 0; n < 8; ++n)
 #pragma unroll
-    for (int hh = 0; hh < 1; ++hh)
+    for (int hh = 0; hh < 2; ++hh)
       *reinterpret_cast<uint32_t*>(p + (m0 + g + hh * 8) * N + n * 8 + tq * 2) = pack_bf16(S[n][hh * 2], S[n][hh * 2 + 1]);
 }
 
@@ -333,10 +321,10 @@ struct ScanStage {
 };
 struct ScanSm {
   ScanStage st[STAGES];
-  float ybuf[8][L][9];       // per warp: [t][v_local]
+  float ybuf[4][L][L + 1];   // per warp: [t][v_local]
 };
 
-__global__ void __launch_bounds__(SCAN_NT)
+__global__ void __launch_bounds__(NT)
 wkv7_tc_scan_kernel(const bf16* __restrict__ v_, const unsigned char* __restrict__ ws, const float* __restrict__ s0,
                     bf16* __restrict__ y_, bf16* __restrict__ chunk_states, float* __restrict__ s_final, int T, int H) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -344,14 +332,14 @@ wkv7_tc_scan_kernel(const bf16* __restrict__ v_, const unsigned char* __restrict
   const int h = blockIdx.x, bb = blockIdx.y;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, tq = lane & 3;
-  const int m0 = warp * 8;
+  const int m0 = warp * 16;
   const int NC = (T + L - 1) / L;
   const size_t tok_stride = (size_t)H * N;
   const size_t base = ((size_t)bb * T * H + h) * N;
   const int row = tid >> 3, part = tid & 7;
 
   auto stage = [&](int c) {
-    if (c < NC && tid < NT) {
+    if (c < NC) {
       ScanStage& s = sm.st[c % STAGES];
       const WsFwd* w = reinterpret_cast<const WsFwd*>(ws + (((size_t)bb * H + h) * NC + c) * sizeof(WsFwd));
       cp16(&s.At[row][part * 8], &w->At[row][part * 8], true);
@@ -409,8 +397,7 @@ wkv7_tc_scan_kernel(const bf16* __restrict__ v_, const unsigned char* __restrict
     }
     uint32_t sa[4][4];
 #pragma unroll
-    for (int kk = 0; kk < 4; ++kk) acc_to_a8(sa[kk], S[2 * kk], S[2 * kk + 1]);
-    va[1] = va[3] = 0u;     // value rows m0+8.. belong to the next warp
+    for (int kk = 0; kk < 4; ++kk) acc_to_a(sa[kk], S[2 * kk], S[2 * kk + 1]);
 
     float r0[4] = {0, 0, 0, 0}, r1[4] = {0, 0, 0, 0};   // R = S0 At^T + V Mka
     float y0[4] = {0, 0, 0, 0}, y1[4] = {0, 0, 0, 0};   // Y = S0 Qt^T + U Pb + V Pk
@@ -427,10 +414,10 @@ wkv7_tc_scan_kernel(const bf16* __restrict__ v_, const unsigned char* __restrict
     mma16816(y1, va, bPk[2], bPk[3]);
     uint32_t ra[4], ua[4];
     float u0[4] = {0, 0, 0, 0}, u1[4] = {0, 0, 0, 0};
-    acc_to_a8(ra, r0, r1);
+    acc_to_a(ra, r0, r1);
     mma16816(u0, ra, bTinv[0], bTinv[1]);
     mma16816(u1, ra, bTinv[2], bTinv[3]);
-    acc_to_a8(ua, u0, u1);
+    acc_to_a(ua, u0, u1);
     mma16816(y0, ua, bPb[0], bPb[1]);
     mma16816(y1, ua, bPb[2], bPb[3]);
     // S <- S diag(gamma_L) + U Bb + V Kb
@@ -439,28 +426,29 @@ wkv7_tc_scan_kernel(const bf16* __restrict__ v_, const unsigned char* __restrict
       const int n = 2 * n2;
       const float2 g0 = *reinterpret_cast<const float2*>(&s.gL[n * 8 + tq * 2]);
       const float2 g1 = *reinterpret_cast<const float2*>(&s.gL[(n + 1) * 8 + tq * 2]);
-      S[n][0] *= g0.x; S[n][1] *= g0.y;
-      S[n + 1][0] *= g1.x; S[n + 1][1] *= g1.y;
+      S[n][0] *= g0.x; S[n][1] *= g0.y; S[n][2] *= g0.x; S[n][3] *= g0.y;
+      S[n + 1][0] *= g1.x; S[n + 1][1] *= g1.y; S[n + 1][2] *= g1.x; S[n + 1][3] *= g1.y;
       mma16816(S[n], ua, bBb[n2][0], bBb[n2][1]);
       mma16816(S[n + 1], ua, bBb[n2][2], bBb[n2][3]);
       mma16816(S[n], va, bKb[n2][0], bKb[n2][1]);
       mma16816(S[n + 1], va, bKb[n2][2], bKb[n2][3]);
     }
-    // y of this warp's 8 value rows: transpose through the warp's own buffer, 8-byte stores
+    // y of this warp's 16 value rows: transpose through the warp's own buffer, 16-byte stores
     __syncwarp();
 #pragma unroll
-    for (int e = 0; e < 2; ++e) {
-      sm.ybuf[warp][tq * 2 + e][g] = y0[e];
-      sm.ybuf[warp][8 + tq * 2 + e][g] = y1[e];
+    for (int e = 0; e < 4; ++e) {
+      const int vl = g + (e >> 1) * 8;
+      sm.ybuf[warp][tq * 2 + (e & 1)][vl] = y0[e];
+      sm.ybuf[warp][8 + tq * 2 + (e & 1)][vl] = y1[e];
     }
     __syncwarp();
     {
       const int tl = lane >> 1, hf = lane & 1;
       const int t = c * L + tl;
-      const float* src = &sm.ybuf[warp][tl][hf * 4];
-      if (t < T)
-        *reinterpret_cast<uint2*>(y_ + base + (size_t)t * tok_stride + m0 + hf * 4) =
-            make_uint2(pack_bf16(src[0], src[1]), pack_bf16(src[2], src[3]));
+      float f[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] = sm.ybuf[warp][tl][hf * 8 + i];
+      if (t < T) *reinterpret_cast<uint4*>(y_ + base + (size_t)t * tok_stride + m0 + hf * 8) = pack8(f);
     }
   }
   if (s_final) store_state_f32(S, s_final + ((size_t)bb * H + h) * N * N, m0, g, tq);
@@ -477,7 +465,7 @@ struct BScanSm {
 
 // Reverse walk.  dstates[c] = dS at the END of chunk c (bf16); ds0 = dS at the start of the sequence.
 // `ws` is a forward workspace (WsFwd): Pb and Tinv are stored transposed.
-__global__ void __launch_bounds__(SCAN_NT)
+__global__ void __launch_bounds__(NT)
 wkv7_tc_bwd_scan_kernel(const bf16* __restrict__ dy_, const unsigned char* __restrict__ ws,
                         const float* __restrict__ ds_final, bf16* __restrict__ dstates, float* __restrict__ ds0,
                         int T, int H) {
@@ -486,7 +474,7 @@ wkv7_tc_bwd_scan_kernel(const bf16* __restrict__ dy_, const unsigned char* __res
   const int h = blockIdx.x, bb = blockIdx.y;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, tq = lane & 3;
-  const int m0 = warp * 8;
+  const int m0 = warp * 16;
   const int NC = (T + L - 1) / L;
   const size_t tok_stride = (size_t)H * N;
   const size_t base = ((size_t)bb * T * H + h) * N;
@@ -494,7 +482,7 @@ wkv7_tc_bwd_scan_kernel(const bf16* __restrict__ dy_, const unsigned char* __res
 
   // i counts walked chunks: chunk index c = NC-1-i
   auto stage = [&](int i) {
-    if (i < NC && tid < NT) {
+    if (i < NC) {
       const int c = NC - 1 - i;
       BScanStage& s = sm.st[i % STAGES];
       const WsFwd* w = reinterpret_cast<const WsFwd*>(ws + (((size_t)bb * H + h) * NC + c) * sizeof(WsFwd));
@@ -544,8 +532,7 @@ wkv7_tc_bwd_scan_kernel(const bf16* __restrict__ dy_, const unsigned char* __res
     }
     uint32_t dsa[4][4];
 #pragma unroll
-    for (int kk = 0; kk < 4; ++kk) acc_to_a8(dsa[kk], S[2 * kk], S[2 * kk + 1]);
-    dya[1] = dya[3] = 0u;
+    for (int kk = 0; kk < 4; ++kk) acc_to_a(dsa[kk], S[2 * kk], S[2 * kk + 1]);
     float u0[4] = {0, 0, 0, 0}, u1[4] = {0, 0, 0, 0};   // dU = dY Pb^T + dS Bb^T
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk) {
@@ -555,19 +542,19 @@ wkv7_tc_bwd_scan_kernel(const bf16* __restrict__ dy_, const unsigned char* __res
     mma16816(u0, dya, bPb[0], bPb[1]);
     mma16816(u1, dya, bPb[2], bPb[3]);
     uint32_t dua[4], dra[4];
-    acc_to_a8(dua, u0, u1);
+    acc_to_a(dua, u0, u1);
     float r0[4] = {0, 0, 0, 0}, r1[4] = {0, 0, 0, 0};   // dR = dU Tinv^T
     mma16816(r0, dua, bTinv[0], bTinv[1]);
     mma16816(r1, dua, bTinv[2], bTinv[3]);
-    acc_to_a8(dra, r0, r1);
+    acc_to_a(dra, r0, r1);
     // dS0 = dS diag(gamma_L) + dY Qt + dR At
 #pragma unroll
     for (int n2 = 0; n2 < 4; ++n2) {
       const int n = 2 * n2;
       const float2 g0 = *reinterpret_cast<const float2*>(&s.gL[n * 8 + tq * 2]);
       const float2 g1 = *reinterpret_cast<const float2*>(&s.gL[(n + 1) * 8 + tq * 2]);
-      S[n][0] *= g0.x; S[n][1] *= g0.y;
-      S[n + 1][0] *= g1.x; S[n + 1][1] *= g1.y;
+      S[n][0] *= g0.x; S[n][1] *= g0.y; S[n][2] *= g0.x; S[n][3] *= g0.y;
+      S[n + 1][0] *= g1.x; S[n + 1][1] *= g1.y; S[n + 1][2] *= g1.x; S[n + 1][3] *= g1.y;
       mma16816(S[n], dya, bQt[n2][0], bQt[n2][1]);
       mma16816(S[n + 1], dya, bQt[n2][2], bQt[n2][3]);
       mma16816(S[n], dra, bAt[n2][0], bAt[n2][1]);
@@ -958,7 +945,7 @@ RWKV_EXPORT int rwkv_wkv7_tc_forward(const void* q, const void* w, const void* k
   wkv7_tc_prep_kernel<<<dim3(NC, H, B), NT, sizeof(PrepSm), st>>>((const bf16*)q, (const bf16*)w, (const bf16*)k,
                                                                   (const bf16*)v, (const bf16*)a, (const bf16*)b,
                                                                   (unsigned char*)ws, T, H);
-  wkv7_tc_scan_kernel<<<dim3(H, B), SCAN_NT, sizeof(ScanSm), st>>>((const bf16*)v, (const unsigned char*)ws, (const float*)s0,
+  wkv7_tc_scan_kernel<<<dim3(H, B), NT, sizeof(ScanSm), st>>>((const bf16*)v, (const unsigned char*)ws, (const float*)s0,
                                                               (bf16*)y, (bf16*)chunk_states, (float*)s_final, T, H);
   return rwkv_launch_status();
 }
@@ -979,7 +966,7 @@ RWKV_EXPORT int rwkv_wkv7_tc_backward(const void* q, const void* w, const void* 
     wkv7_tc_prep_kernel<<<dim3(NC, H, B), NT, sizeof(PrepSm), st>>>((const bf16*)q, (const bf16*)w, (const bf16*)k,
                                                                     (const bf16*)v, (const bf16*)a, (const bf16*)b,
                                                                     (unsigned char*)ws, T, H);
-  wkv7_tc_bwd_scan_kernel<<<dim3(H, B), SCAN_NT, sizeof(BScanSm), st>>>((const bf16*)dy, (const unsigned char*)ws,
+  wkv7_tc_bwd_scan_kernel<<<dim3(H, B), NT, sizeof(BScanSm), st>>>((const bf16*)dy, (const unsigned char*)ws,
                                                                    (const float*)ds_final, (bf16*)dstates, (float*)ds0,
                                                                    T, H);
   wkv7_tc_bwd_chunk_kernel<<<dim3(NC, H, B), NT, sizeof(BwdSm), st>>>(
