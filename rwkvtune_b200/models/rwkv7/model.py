@@ -233,6 +233,49 @@ def _block_stateful(block, x, v_first, att_prev, wkv_state, ffn_prev):
     return block(x, v_first, att_prev, wkv_state, ffn_prev, True)
 
 
+class _Recompute(torch.autograd.Function):
+    """Activation checkpointing of one block: run it without a graph, keep only its inputs, run it again with a
+    graph when the gradient arrives.  Does what ``torch.utils.checkpoint`` does for this model
+    (``rwkvtune/models/rwkv7/model.py:454-455`` wraps every block) without the per-saved-tensor pack/unpack hooks of
+    the non-reentrant implementation, which cost more host time than the kernels of a small block.  ``anchor`` is an
+    empty tensor that requires grad, so the node is part of the graph even when no real input requires grad (frozen
+    embedding under LoRA); parameter gradients accumulate into ``.grad`` during the inner backward."""
+
+    @staticmethod
+    def forward(ctx, fn, block, anchor, *tensors):
+        ctx.fn, ctx.block = fn, block
+        ctx.req = [t is not None and t.requires_grad for t in tensors]
+        ctx.none = [t is None for t in tensors]
+        ctx.save_for_backward(*[t for t in tensors if t is not None])
+        with torch.no_grad():
+            outs = fn(block, *tensors)
+        return tuple(outs)
+
+    @staticmethod
+    def backward(ctx, *grads):
+        saved = iter(ctx.saved_tensors)
+        inputs = [None if is_none else next(saved).detach().requires_grad_(req)
+                  for is_none, req in zip(ctx.none, ctx.req)]
+        with torch.enable_grad():
+            outs = ctx.fn(ctx.block, *inputs)
+        pairs = [(o, g) for o, g in zip(outs, grads) if isinstance(o, torch.Tensor) and o.requires_grad and g is not None]
+        if pairs:
+            torch.autograd.backward([o for o, _ in pairs], [g for _, g in pairs])
+        return (None, None, None) + tuple(t.grad if t is not None and t.requires_grad else None for t in inputs)
+
+
+def _has_active_dropout(block: nn.Module) -> bool:
+    return block.training and any(isinstance(m, nn.Dropout) and m.p > 0 for m in block.modules())
+
+
+def _checkpoint_block(fn, block, *tensors):
+    """Recompute-in-backward wrapper for one block (random-number state is only preserved by the library path)."""
+    if _has_active_dropout(block):
+        return _checkpoint(fn, block, *tensors, use_reentrant=False)
+    anchor = torch.empty(0, device=tensors[0].device, requires_grad=True)
+    return _Recompute.apply(fn, block, anchor, *tensors)
+
+
 class RWKV7Model(GenerationMixin, nn.Module):
     """Full model: embedding, ``n_layer`` blocks, final LayerNorm and the vocabulary head."""
 
@@ -269,7 +312,7 @@ class RWKV7Model(GenerationMixin, nn.Module):
         n_cp = getattr(self.config, "grad_cp_layers", None)   # None: every layer; k: only the first k layers
         for i, block in enumerate(self.blocks):
             if cp and (n_cp is None or i < n_cp):
-                x, v_first = _checkpoint(_block_plain, block, x, v_first, use_reentrant=False)
+                x, v_first = _checkpoint_block(_block_plain, block, x, v_first)
             else:
                 x, v_first = _block_plain(block, x, v_first)
         return ops.layer_norm(x, self.ln_out.weight, self.ln_out.bias)
@@ -325,8 +368,8 @@ class RWKV7Model(GenerationMixin, nn.Module):
         new_att, new_wkv, new_ffn = [], [], []
         for i, block in enumerate(self.blocks):
             if checkpoint:
-                x, v_first, a_l, s_l, f_l = _checkpoint(_block_stateful, block, x, v_first, att_prev[i], wkv[i],
-                                                        ffn_prev[i], use_reentrant=False)
+                x, v_first, a_l, s_l, f_l = _checkpoint_block(_block_stateful, block, x, v_first, att_prev[i], wkv[i],
+                                                              ffn_prev[i])
             else:
                 x, v_first, a_l, s_l, f_l = _block_stateful(block, x, v_first, att_prev[i], wkv[i], ffn_prev[i])
             new_att.append(a_l)

@@ -27,8 +27,14 @@ def check_status(device=None) -> int:
     return int(_status(dev).item())
 
 
+_HAS_GEMM = None
+
+
 def available() -> bool:
-    return _ext.available() and hasattr(_ext.lib(), "rwkv_gemm_bf16_tcgen05")
+    global _HAS_GEMM
+    if _HAS_GEMM is None:
+        _HAS_GEMM = _ext.available() and hasattr(_ext.lib(), "rwkv_gemm_bf16_tcgen05")
+    return _HAS_GEMM
 
 
 def _rows_ok(t: torch.Tensor) -> bool:

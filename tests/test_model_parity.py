@@ -88,3 +88,34 @@ def test_loss_matches_logits_path():
     loss = m.loss(idx, labels, l2wrap=False)
     ref = torch.nn.functional.cross_entropy(m(idx).reshape(-1, 128), labels.reshape(-1), ignore_index=-100)
     assert torch.allclose(loss, ref, atol=1e-6)
+
+
+def test_block_recompute_matches_plain_backward():
+    """Per-block activation checkpointing (own recompute node) gives the same loss and gradients, also when no
+    block input requires grad (frozen embedding) and through the stateful chunked path."""
+    import torch
+    from rwkvtune_b200.models import RWKVConfig, RWKV7Model
+
+    torch.manual_seed(0)
+    cfg = RWKVConfig(n_layer=3, n_embd=64, vocab_size=128, dim_att_lora=8, dim_gate_lora=8, dim_mv_lora=8, ctx_len=64)
+    m = RWKV7Model(cfg).train()
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            if n.endswith(("output.weight", "ffn.value.weight", "w1", "a1", "v1", "g1")):
+                p.normal_(0, 0.05)
+    m.emb.weight.requires_grad_(False)
+    idx = torch.randint(0, 128, (2, 24))
+    labels = torch.randint(0, 128, (2, 24))
+
+    def grads(cp):
+        m.config.grad_cp = cp
+        m.zero_grad()
+        loss = m.loss(idx, labels)
+        loss.backward()
+        return float(loss), {n: p.grad.clone() for n, p in m.named_parameters() if p.grad is not None}
+
+    l0, g0 = grads(0)
+    l1, g1 = grads(1)
+    assert abs(l0 - l1) < 1e-6 and g0.keys() == g1.keys() and len(g0) > 10
+    for n in g0:
+        assert torch.allclose(g0[n], g1[n], atol=1e-6, rtol=1e-5), n
