@@ -196,7 +196,8 @@ __device__ void ag_copy_role(const AgParams& ag, int N, int K) {
   }
 }
 
-// EPI: 0 = plain store, 1 = relu(x)^2, 2 = add to the bf16 values already in C (in place: C += A B)
+// EPI: 0 = plain store, 1 = relu(x)^2, 2 = add to the bf16 values already in C (in place: C += A B),
+//      3 = tanh(x), 4 = sigmoid(x)  (the bottleneck activations of the low-rank decay and gate chains)
 template <bool A_MN, bool B_MN, int EPI, bool AG>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -365,6 +366,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             float x = __uint_as_float(col < 32 ? v0[col] : v1[col - 32]);
             if (EPI == 1) { x = fmaxf(x, 0.f); x = x * x; }
             if (EPI == 2) x += prev[e];
+            if (EPI == 3) x = 1.f - __fdividef(2.f, __expf(2.f * x) + 1.f);     // tanh, saturates cleanly at +-1
+            if (EPI == 4) x = __fdividef(1.f, 1.f + __expf(-x));
             f[e] = x;
           }
           const uint4 packed = pack8(f);
@@ -473,7 +476,7 @@ int launch_ag(CUtensorMap ma, CUtensorMap mb, CUtensorMap mc, int M, int N, int 
 // C[M,N] (row-major, ldc) = op(A) op(B) in bf16 with fp32 accumulation.
 //   a_mn = 0: A is [M,K] row-major (lda);  a_mn = 1: A is stored [K,M] row-major (lda)
 //   b_mn = 0: B is [N,K] row-major (ldb);  b_mn = 1: B is stored [K,N] row-major (ldb)
-//   epilogue: 0 none, 1 relu(x)^2, 2 add a bf16 [M,N] matrix: `residual` (row stride ldr) or, when that is null,
+//   epilogue: 0 none, 1 relu(x)^2, 3 tanh, 4 sigmoid, 2 add a bf16 [M,N] matrix: `residual` (row stride ldr) or, when that is null,
 //   the values already in C (in place).   status: device int, set non-zero if a device-side wait timed out.
 RWKV_EXPORT int rwkv_gemm_bf16_tcgen05(const void* a, const void* b, void* c, int M, int N, int K, long long lda,
                                        long long ldb, long long ldc, int a_mn, int b_mn, int epilogue, void* status,
@@ -501,6 +504,8 @@ RWKV_EXPORT int rwkv_gemm_bf16_tcgen05(const void* a, const void* b, void* c, in
 #define DISPATCH(AM, BMN)                                                                        \
   (epilogue == 1   ? launch<AM, BMN, 1>(ma, mb, mc, M, N, K, sp, sms, cp, ldc, st)                \
    : epilogue == 2 ? launch<AM, BMN, 2>(ma, mb, mc, M, N, K, sp, sms, cp, ldc, st)                \
+   : epilogue == 3 ? launch<AM, BMN, 3>(ma, mb, mc, M, N, K, sp, sms, cp, ldc, st)                \
+   : epilogue == 4 ? launch<AM, BMN, 4>(ma, mb, mc, M, N, K, sp, sms, cp, ldc, st)                \
                    : launch<AM, BMN, 0>(ma, mb, mc, M, N, K, sp, sms, cp, ldc, st))
   if (!a_mn && !b_mn) return DISPATCH(false, false);
   if (!a_mn && b_mn) return DISPATCH(false, true);

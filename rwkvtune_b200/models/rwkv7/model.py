@@ -155,9 +155,9 @@ class RWKV7TimeMix(nn.Module):
             r = self.receptance(xr)
             k = self.key(xk)
             v = self.value(xv)
-        w_lin = ops.matmul(torch.tanh(ops.matmul(xw, self.w1)), self.w2)
+        w_lin = ops.matmul(ops.matmul_act(xw, self.w1, "tanh"), self.w2)
         a_lin = ops.matmul(ops.matmul(xa, self.a1), self.a2)
-        g = ops.matmul(torch.sigmoid(ops.matmul(xg, self.g1)), self.g2)
+        g = ops.matmul(ops.matmul_act(xg, self.g1, "sigmoid"), self.g2)
         if self.layer_id == 0:
             v_lin = None
             w, k, v, a_, b_ = ops.timemix_prep(k, v, None, w_lin, a_lin, None, self.w0, self.a0, None,

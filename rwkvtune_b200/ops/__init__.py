@@ -89,6 +89,17 @@ def matmul(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     return x @ w
 
 
+def matmul_act(x: torch.Tensor, w: torch.Tensor, act: str) -> torch.Tensor:
+    """``tanh(x @ w)`` or ``sigmoid(x @ w)`` (first stage of the low-rank decay / gate chains); the activation runs
+    in the GEMM epilogue on CUDA."""
+    if _native(x, "gemm") and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
+        from . import gemm
+
+        return gemm.matmul_act(x, w, act)
+    pre = x @ w
+    return torch.tanh(pre) if act == "tanh" else torch.sigmoid(pre)
+
+
 def linear_add(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
     """``residual + x @ weight^T``; on CUDA the residual is added in the GEMM epilogue."""
     if _native(x, "gemm") and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16:

@@ -85,12 +85,20 @@ def stream() -> ctypes.c_void_p:
 LAUNCH_COUNT = 0   # native entry-point calls since import (each issues at least one kernel)
 
 
+_FUNCS = {}
+
+
 def call(name: str, *args) -> None:
     global LAUNCH_COUNT
-    fn = getattr(lib(), name)
-    fn.restype = ctypes.c_int
+    fn = _FUNCS.get(name)
+    if fn is None:
+        fn = getattr(lib(), name)
+        fn.restype = ctypes.c_int
+        _FUNCS[name] = fn
     LAUNCH_COUNT += 1
-    check(fn(*args), name)
+    status = fn(*args)
+    if status:
+        check(status, name)
 
 
 def launch_count() -> int:

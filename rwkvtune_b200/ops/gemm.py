@@ -159,6 +159,41 @@ class _MatMul(torch.autograd.Function):
         return dx, dw
 
 
+class _MatMulAct(torch.autograd.Function):
+    """``act(x @ w)`` for ``act`` in tanh / sigmoid, the activation applied in the GEMM epilogue; the backward
+    needs only the output (``tanh' = 1 - y^2``, ``sigmoid' = y (1 - y)``)."""
+
+    @staticmethod
+    def forward(ctx, x, w, act: str):
+        x2 = x.reshape(-1, x.shape[-1])
+        n = _native()
+        if n is not None and n.native_ok(x2, w, "nn"):
+            y = n.mm_nn(x2, w, epilogue=3 if act == "tanh" else 4)
+        else:
+            y = torch.tanh(x2 @ w) if act == "tanh" else torch.sigmoid(x2 @ w)
+        ctx.save_for_backward(x, w, y)
+        ctx.act = act
+        return y.reshape(*x.shape[:-1], w.shape[1])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, y = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        dpre = dy2 * (1 - y * y) if ctx.act == "tanh" else dy2 * (y * (1 - y))
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = mm_nt(dpre, w).reshape(x.shape)
+        if ctx.needs_input_grad[1]:
+            dw = mm_tn(x.reshape(-1, x.shape[-1]), dpre)
+        return dx, dw, None
+
+
+def matmul_act(x, w, act: str):
+    if act not in ("tanh", "sigmoid"):
+        raise ValueError(f"unsupported activation {act!r}")
+    return _MatMulAct.apply(x, w, act)
+
+
 def linear(x, weight):
     return _Linear.apply(x, weight)
 

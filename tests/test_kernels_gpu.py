@@ -428,3 +428,22 @@ def test_gemm_accumulate_epilogue(layout):
     assert out.data_ptr() == y.data_ptr()
     ref_y = y0.float() + x.float() @ w.float().t()
     assert (y.float() - ref_y).abs().max().item() <= 2e-2 * ref_y.abs().max().item() + 1e-2
+
+
+@pytest.mark.parametrize("act", ["tanh", "sigmoid"])
+def test_gemm_activation_epilogue(act):
+    torch.manual_seed(4)
+    M, K, N = 700, 256, 96
+    x = (torch.randn(M, K, device="cuda") * 0.5).to(BF)
+    w = (torch.randn(K, N, device="cuda") * 0.2).to(BF)
+    xk, wk = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    xr, wr = x.float().clone().requires_grad_(True), w.float().clone().requires_grad_(True)
+    y = ops.matmul_act(xk, wk, act)
+    pre = xr @ wr
+    yr = torch.tanh(pre) if act == "tanh" else torch.sigmoid(pre)
+    _close(y, yr, 1e-2, 1e-2, act)
+    g = torch.randn_like(yr)
+    (y.float() * g).sum().backward()
+    (yr * g).sum().backward()
+    _close(xk.grad, xr.grad, 3e-2, 3e-2 * xr.grad.abs().mean().item() + 1e-3, "dx")
+    _close(wk.grad, wr.grad, 3e-2, 3e-2 * wr.grad.abs().mean().item() + 1e-2, "dw")
