@@ -783,6 +783,27 @@ wkv7_tc_bwd_chunk_kernel(const bf16* __restrict__ q_, const bf16* __restrict__ w
   }
   __syncthreads();
 
+  // q, k, a, b at this thread's output positions, requested now so that they arrive during the products below
+  // (the chunk's inputs were read by the prep kernel moments ago: L2 hits)
+  float2 rq[2][2], rk[2][2], ra2[2][2], rb[2][2];
+  {
+    auto raw2 = [&](const bf16* src, int t, int j) {
+      const int tt = c * L + t;
+      if (tt >= T) return make_float2(0.f, 0.f);
+      return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + base + (size_t)tt * tok_stride + j));
+    };
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        const int t = g + hh * 8, j = m0 + i * 8 + tq * 2;
+        rq[i][hh] = raw2(q_, t, j);
+        rk[i][hh] = raw2(k_, t, j);
+        ra2[i][hh] = raw2(a_, t, j);
+        rb[i][hh] = raw2(b_, t, j);
+      }
+  }
+
   // ---- key-channel phase: warp owns channels [m0, m0+16) of the six [16 x 64] gradients
   float dQt[2][4], dAt[2][4], dKt[2][4], dBt[2][4], dBb[2][4], dKb[2][4];
 #pragma unroll
@@ -835,11 +856,6 @@ wkv7_tc_bwd_chunk_kernel(const bf16* __restrict__ q_, const bf16* __restrict__ w
 
   // ---- undo the decay scaling; G = d loss / d log gamma_t
   bf16 (*odq)[LDS_] = sm.At, (*oda)[LDS_] = sm.Bt, (*odb)[LDS_] = sm.Kt, (*odk)[LDS_] = sm.Qt;
-  auto raw2 = [&](const bf16* src, int t, int j) {   // the chunk's inputs were read moments ago: these hit L2
-    const int tt = c * L + t;
-    if (tt >= T) return make_float2(0.f, 0.f);
-    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + base + (size_t)tt * tok_stride + j));
-  };
   auto st2 = [](bf16* p, float x, float y) { *reinterpret_cast<uint32_t*>(p) = pack_bf16(x, y); };
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
@@ -849,7 +865,7 @@ wkv7_tc_bwd_chunk_kernel(const bf16* __restrict__ q_, const bf16* __restrict__ w
       const float2 E = *reinterpret_cast<const float2*>(&sm.E[t][j]);
       const float2 Ep = t ? *reinterpret_cast<const float2*>(&sm.E[t - 1][j]) : make_float2(1.f, 1.f);
       const float2 gl = *reinterpret_cast<const float2*>(&sm.gL[j]);
-      const float2 qv = raw2(q_, t, j), kv = raw2(k_, t, j), av = raw2(a_, t, j), bv = raw2(b_, t, j);
+      const float2 qv = rq[i][hh], kv = rk[i][hh], av = ra2[i][hh], bv = rb[i][hh];
       const float ix = __fdividef(1.f, E.x), iy = __fdividef(1.f, E.y);
       const float lx = gl.x * ix, ly = gl.y * iy;
       const float dqx = dQt[i][e0] * E.x, dqy = dQt[i][e1] * E.y;
@@ -870,33 +886,37 @@ wkv7_tc_bwd_chunk_kernel(const bf16* __restrict__ q_, const bf16* __restrict__ w
     }
   }
   __syncthreads();
-  if (tid < N) {
-    float ex = sm.sds[0][tid] + sm.sds[1][tid] + sm.sds[2][tid] + sm.sds[3][tid];
+  bf16 (*odw)[LDS_] = sm.Bb;      // free since the value-row phase
+  {
+    // d loss / d log-decay: suffix sums over the steps of  G_total[t] = Gs[t] + (a da)[t+1]  (gamma_t scales a_{t+1});
+    // the last step also receives everything that flows through gamma_L.  Thread (channel j, half h) owns steps
+    // 8h .. 8h+7 of one column: scalar, conflict-free shared-memory reads.
+    const int j = tid & (N - 1), hf = tid >> 6;
+    float ex = sm.sds[0][j] + sm.sds[1][j] + sm.sds[2][j] + sm.sds[3][j];
 #pragma unroll
-    for (int t = 0; t < L; ++t) ex += sm.u.fin.xs[t][tid];
-    sm.extra[tid] = ex;
+    for (int t = 0; t < L; ++t) ex += sm.u.fin.xs[t][j];
+    float run = 0.f, r[8];
+#pragma unroll
+    for (int i = 7; i >= 0; --i) {
+      const int t = hf * 8 + i;
+      run += sm.u.fin.Gs[t][j] + (t + 1 < L ? sm.u.fin.ada[t + 1][j] : ex);
+      r[i] = run;
+    }
+    if (hf) sm.scratch[j] = run;
+    __syncthreads();
+    const float later = hf ? 0.f : sm.scratch[j];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int t = hf * 8 + i;
+      odw[t][j] = __float2bfloat16_rn(-__expf(__bfloat162float(sm.wraw[t][j])) * (r[i] + later));
+    }
   }
   __syncthreads();
-  {  // thread (row, part): G_total[t] = Gs[t] + (a da)[t+1]  (gamma_t scales a_{t+1}); the last step gets `extra`
-    float gsum[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) gsum[i] = 0.f;
-    for (int t2 = row; t2 < L; ++t2) {
-      float gv[8], xv[8];
-      ld8f(gv, &sm.u.fin.Gs[t2][j0]);
-      if (t2 + 1 < L) ld8f(xv, &sm.u.fin.ada[t2 + 1][j0]);
-      else ld8f(xv, &sm.extra[j0]);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) gsum[i] += gv[i] + xv[i];
-    }
+  {
     const int t = c * L + row;
     if (t < T) {
-      float wv[8], dw[8];
-      unpack8(*reinterpret_cast<const uint4*>(&sm.wraw[row][j0]), wv);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) dw[i] = -__expf(wv[i]) * gsum[i];
       const size_t off = base + (size_t)t * tok_stride + j0;
-      *reinterpret_cast<uint4*>(dw_ + off) = pack8(dw);
+      *reinterpret_cast<uint4*>(dw_ + off) = *reinterpret_cast<const uint4*>(&odw[row][j0]);
       *reinterpret_cast<uint4*>(dq_ + off) = *reinterpret_cast<const uint4*>(&odq[row][j0]);
       *reinterpret_cast<uint4*>(da_ + off) = *reinterpret_cast<const uint4*>(&oda[row][j0]);
       *reinterpret_cast<uint4*>(db_ + off) = *reinterpret_cast<const uint4*>(&odb[row][j0]);
