@@ -109,14 +109,21 @@ timemix_prep_bwd_kernel(const bf16* __restrict__ gw, const bf16* __restrict__ gk
   }
   for (int t = rc.t0; t < rc.t1; ++t) {
     const size_t off = ((size_t)rc.b * T + t) * C + rc.col;
-    float kf[8] = {0, 0, 0, 0, 0, 0, 0, 0}, al[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    float g_an[8] = {0, 0, 0, 0, 0, 0, 0, 0}, g_b[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    if (rc.active) {
-      unpack8(ldg16(k + off), kf);
-      unpack8(ldg16(alin + off), al);
-      unpack8(ldg16(gan + off), g_an);
-      unpack8(ldg16(gb + off), g_b);
-    }
+    // every tile of this row is requested up front: one memory round trip per row instead of three
+    const uint4 z4 = make_uint4(0u, 0u, 0u, 0u);
+    const bool on = rc.active;
+    const uint4 q_k = on ? ldg16(k + off) : z4, q_al = on ? ldg16(alin + off) : z4;
+    const uint4 q_gan = on ? ldg16(gan + off) : z4, q_gb = on ? ldg16(gb + off) : z4;
+    const uint4 q_gk = on ? ldg16(gk + off) : z4, q_gw = on ? ldg16(gw + off) : z4, q_wl = on ? ldg16(wlin + off) : z4;
+    const uint4 q_gv = on ? ldg16(gv + off) : z4;
+    const bool mixv = on && vfirst != nullptr;
+    const uint4 q_v = mixv ? ldg16(v + off) : z4, q_vf = mixv ? ldg16(vfirst + off) : z4;
+    const uint4 q_vl = mixv ? ldg16(vlin + off) : z4;
+    float kf[8], al[8], g_an[8], g_b[8];
+    unpack8(q_k, kf);
+    unpack8(q_al, al);
+    unpack8(q_gan, g_an);
+    unpack8(q_gb, g_b);
     float a[8], kr[8], dkk[8];
     float nrm2 = 0.f;
 #pragma unroll
@@ -134,9 +141,9 @@ timemix_prep_bwd_kernel(const bf16* __restrict__ gw, const bf16* __restrict__ gk
     dot = head_sum(dot);
     if (!rc.active) continue;
     float g_k[8], g_w[8], wl[8];
-    unpack8(ldg16(gk + off), g_k);
-    unpack8(ldg16(gw + off), g_w);
-    unpack8(ldg16(wlin + off), wl);
+    unpack8(q_gk, g_k);
+    unpack8(q_gw, g_w);
+    unpack8(q_wl, wl);
     float o_dk[8], o_dw[8], o_da[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
@@ -156,12 +163,12 @@ timemix_prep_bwd_kernel(const bf16* __restrict__ gw, const bf16* __restrict__ gk
     stg16(dwlin + off, pack8(o_dw));
     stg16(dalin + off, pack8(o_da));
     float g_v[8];
-    unpack8(ldg16(gv + off), g_v);
+    unpack8(q_gv, g_v);
     if (vfirst) {
       float vf[8], v1[8], vl[8], o_dv[8], o_dvf[8], o_dvl[8];
-      unpack8(ldg16(v + off), vf);
-      unpack8(ldg16(vfirst + off), v1);
-      unpack8(ldg16(vlin + off), vl);
+      unpack8(q_v, vf);
+      unpack8(q_vf, v1);
+      unpack8(q_vl, vl);
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
         const float s = sigmoidf_(p.v0[e] + vl[e]);
