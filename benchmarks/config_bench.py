@@ -109,7 +109,8 @@ def bench_infctx(a):
         model = RWKV7Model(cfg)
     strategy = "deepspeed_stage_2" if ctx.world_size > 1 else "auto"
     eng = TrainEngine(model, EngineConfig(lr_init=1e-4, grad_clip=1.0, strategy=strategy, precision="bf16", grad_cp=1,
-                                          train_type="infctx", chunk_ctx=chunk, transport="auto"), ctx)
+                                          train_type="infctx", chunk_ctx=chunk, transport="auto",
+                                          cuda_graph=not a.no_graph), ctx)
     g = torch.Generator().manual_seed(100 + ctx.rank)
     n = a.warmup + a.steps
     ids = [torch.randint(0, 65536, (B, T), generator=g).to(ctx.device) for _ in range(n)]
@@ -118,6 +119,7 @@ def bench_infctx(a):
     tokens = B * T * ctx.world_size
     return ctx, {"metric": "train_tokens_per_sec", "value": tokens / ms * 1e3, "ms_per_step": ms,
                  "config": {"model": "rwkv7-0.4b", "seq_len": T, "chunk_ctx": chunk, "micro_bsz": B, "bptt": "truncated",
+                            "cuda_graph_chunk_step": not a.no_graph,
                             "parallelism": f"zero2-dp{ctx.world_size}" if ctx.world_size > 1 else "single",
                             "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2**30, 1)}}
 
@@ -259,6 +261,7 @@ def main():
     ap.add_argument("--micro-bsz", type=int, default=0)
     ap.add_argument("--ctx-len", type=int, default=0)
     ap.add_argument("--new-tokens", type=int, default=512)
+    ap.add_argument("--no-graph", action="store_true", help="infctx: issue every chunk eagerly instead of replaying a CUDA graph")
     a = ap.parse_args()
     ctx, out = {"lora_zero3": bench_lora_zero3, "infctx": bench_infctx, "grpo": bench_grpo,
                 "collectives": bench_collectives}[a.config](a)

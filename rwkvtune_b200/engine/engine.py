@@ -49,6 +49,7 @@ class EngineConfig:
     transport: str = "auto"   # "p2p": fused kernels over symmetric memory; "nccl": library collectives; "auto": p2p on multi-GPU CUDA when symmetric memory can be set up
     l2wrap: bool = True
     grad_cp_layers: Optional[object] = None   # None = all layers when grad_cp=1; int k = first k layers; "auto"
+    cuda_graph: bool = False   # replay forward+backward of a micro-batch (or of one infctx chunk) from a CUDA graph
 
 
 class TrainEngine:
@@ -100,6 +101,7 @@ class TrainEngine:
         self.micro_step = 0
         self.optimizer_steps = 0
         self.tokens_seen = 0
+        self._graphs: Dict[tuple, dict] = {}
 
     # ------------------------------------------------------------------ memory-aware checkpointing
     SAVED_UNITS_PER_LAYER = 37.0   # [tokens, n_embd] bf16 tensors a block keeps for backward without checkpointing
@@ -144,15 +146,26 @@ class TrainEngine:
         wkv = torch.zeros(L, B, H, N, N, device=idx.device, dtype=torch.float32)
         total = torch.zeros((), device=idx.device, dtype=torch.float32)
         pending = []
+        if cfg.truncated_bptt:
+            # which chunks have a supervised token: one device-to-host read for the whole sequence, so the chunk loop
+            # below never waits for the GPU and the host can run ahead of it
+            pad = n_chunks * chunk - T
+            lab_p = torch.nn.functional.pad(labels, (0, pad), value=-100) if pad else labels
+            chunk_valid = (lab_p.reshape(B, n_chunks, chunk) != -100).any(dim=2).any(dim=0).tolist()
+        use_graph = cfg.truncated_bptt and self._graph_ok() and T % chunk == 0 and all(chunk_valid)
         for i in range(n_chunks):
             ids_c, lab_c = idx[:, i * chunk:(i + 1) * chunk], labels[:, i * chunk:(i + 1) * chunk]
+            if use_graph:
+                loss_c, shift, wkv = self._graph_chunk(ids_c, lab_c, shift, wkv, scale / n_chunks)
+                total += loss_c
+                continue
             x, shift, wkv = m.forward_hidden_infctx(ids_c, shift, wkv, checkpoint=bool(cfg.grad_cp))
             Bc, Tc, _ = x.shape
             from .. import ops
 
             loss_c = ops.linear_cross_entropy(x.reshape(Bc * Tc, C), m._head_weight(), lab_c.reshape(-1),
                                               l2wrap=cfg.l2wrap, l2wrap_tokens=Bc * Tc)
-            has_valid = bool((lab_c != -100).any()) if cfg.truncated_bptt else True
+            has_valid = chunk_valid[i] if cfg.truncated_bptt else True
             if cfg.truncated_bptt:
                 if has_valid:
                     (loss_c * (scale / n_chunks)).backward()
@@ -166,6 +179,74 @@ class TrainEngine:
             return loss.detach()
         return total / n_chunks
 
+    # ------------------------------------------------------------------ CUDA-graph replay of forward + backward
+    GRAPH_WARMUP_STEPS = 2     # eager steps before a shape is captured (allocator, lazy module state)
+
+    def _graph_ok(self) -> bool:
+        return (self.cfg.cuda_graph and self.ctx.device.type == "cuda" and self.zero3 is None
+                and self.optimizer_steps >= self.GRAPH_WARMUP_STEPS)
+
+    def _capture(self, key: tuple, build) -> dict:
+        """Records ``build()`` (forward, loss, backward on static tensors) into a CUDA graph.  Small batches are bound
+        by host-side launch cost (a few thousand launches per step); a replay issues them in one call.  Parameter
+        gradients accumulate into the flat gradient buffer exactly as in eager mode.  Cached fp32 parameter copies
+        are invalidated first so that their refresh kernels are part of the recording."""
+        ops.bump_param_epoch()
+        torch.cuda.synchronize()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        entry = {"graph": torch.cuda.CUDAGraph()}
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(entry["graph"], stream=side):
+                entry.update(build())
+        torch.cuda.current_stream().wait_stream(side)
+        self._graphs[key] = entry
+        return entry
+
+    def _graph_step_normal(self, idx: torch.Tensor, labels: torch.Tensor, scale: float) -> torch.Tensor:
+        key = ("normal", tuple(idx.shape), scale)
+        entry = self._graphs.get(key)
+        if entry is None:
+            static_idx, static_lab = idx.clone(), labels.clone()
+
+            def build():
+                loss = self._loss_normal(static_idx, static_lab)
+                (loss * scale if scale != 1.0 else loss).backward()
+                return {"idx": static_idx, "labels": static_lab, "loss": loss.detach()}
+
+            entry = self._capture(key, build)
+        entry["idx"].copy_(idx)
+        entry["labels"].copy_(labels)
+        entry["graph"].replay()
+        return entry["loss"].clone()
+
+    def _graph_chunk(self, ids_c, lab_c, shift, wkv, factor: float):
+        """One infctx chunk (forward, loss, backward of ``loss * factor``) replayed from a graph; states in and out
+        are static tensors.  Returns ``(loss, new_shift, new_wkv)`` (the state outputs are overwritten by the next
+        replay, so the caller consumes them before calling again)."""
+        m, cfg = self.model, self.cfg
+        key = ("chunk", tuple(ids_c.shape), factor)
+        entry = self._graphs.get(key)
+        if entry is None:
+            s_ids, s_lab, s_shift, s_wkv = ids_c.clone(), lab_c.clone(), shift.clone(), wkv.clone()
+
+            def build():
+                x, n_shift, n_wkv = m.forward_hidden_infctx(s_ids, s_shift, s_wkv, checkpoint=bool(cfg.grad_cp))
+                Bc, Tc, C = x.shape
+                loss_c = ops.linear_cross_entropy(x.reshape(Bc * Tc, C), m._head_weight(), s_lab.reshape(-1),
+                                                  l2wrap=cfg.l2wrap, l2wrap_tokens=Bc * Tc)
+                (loss_c * factor).backward()
+                return {"ids": s_ids, "labels": s_lab, "shift": s_shift, "wkv": s_wkv, "loss": loss_c.detach(),
+                        "new_shift": n_shift.detach(), "new_wkv": n_wkv.detach()}
+
+            entry = self._capture(key, build)
+        entry["ids"].copy_(ids_c)
+        entry["labels"].copy_(lab_c)
+        entry["shift"].copy_(shift)
+        entry["wkv"].copy_(wkv)
+        entry["graph"].replay()
+        return entry["loss"], entry["new_shift"], entry["new_wkv"]
+
     # ------------------------------------------------------------------ one micro-batch
     def train_step(self, idx: torch.Tensor, labels: torch.Tensor, lr: float) -> torch.Tensor:
         """Forward + backward for one micro-batch; runs the optimiser every
@@ -174,6 +255,8 @@ class TrainEngine:
         scale = 1.0 / acc
         if self.cfg.train_type == "infctx":
             loss = self._step_infctx(idx, labels, scale)
+        elif self._graph_ok():
+            loss = self._graph_step_normal(idx, labels, scale)
         else:
             loss = self._loss_normal(idx, labels)
             (loss * scale if acc > 1 else loss).backward()

@@ -292,7 +292,8 @@ class GRPOTrainer:
         cfg = EngineConfig(lr_init=a.lr_init, beta1=a.beta1, beta2=a.beta2, adam_eps=a.adam_eps, weight_decay=a.weight_decay,
                            grad_clip=a.grad_clip, accumulate_grad_batches=a.accumulate_grad_batches, strategy=a.strategy,
                            precision=a.precision if a.accelerator != "cpu" else "fp32", grad_cp=a.grad_cp,
-                           lr_2x_patterns=("att.w0",), transport=os.environ.get("RWKVTUNE_TRANSPORT", "auto"))
+                           lr_2x_patterns=("att.w0",), transport=os.environ.get("RWKVTUNE_TRANSPORT", "auto"),
+                           cuda_graph=os.environ.get("RWKVTUNE_CUDA_GRAPH", "0") == "1")
         self.engine = eng = TrainEngine(self.model, cfg, ctx)
         self.model = eng.model
         if self.ref_model is not None:

@@ -92,7 +92,8 @@ class SupervisedTrainer:
                             precision=a.precision if a.accelerator != "cpu" else "fp32", grad_cp=a.grad_cp,
                             lr_2x_patterns=("att.w0",) if a.train_type == "infctx" else (),
                             train_type=a.train_type, chunk_ctx=a.chunk_ctx, truncated_bptt=a.truncated_bptt,
-                            transport=os.environ.get("RWKVTUNE_TRANSPORT", "auto"))
+                            transport=os.environ.get("RWKVTUNE_TRANSPORT", "auto"),
+                           cuda_graph=os.environ.get("RWKVTUNE_CUDA_GRAPH", "0") == "1")
 
     # ------------------------------------------------------------------ public
     def train(self) -> None:
