@@ -81,6 +81,7 @@ def parse():
                          "(recompute only the first k blocks) or 'auto' (as few as fit in HBM)")
     ap.add_argument("--transport", default=os.environ.get("RWKVTUNE_TRANSPORT", "p2p"),
                     help="multi-GPU gradient/parameter transport: p2p (fused peer-memory kernels) or nccl")
+    ap.add_argument("--cuda-graph", type=int, default=0, help="replay forward+backward from a CUDA graph")
     return ap.parse_args()
 
 
@@ -103,7 +104,8 @@ def run_ours(a):
         model = RWKV7Model(cfg)
     strategy = "deepspeed_stage_2" if ctx.world_size > 1 else "auto"
     eng = TrainEngine(model, EngineConfig(lr_init=3e-4, weight_decay=0.01, grad_clip=1.0, strategy=strategy,
-                                          precision="bf16", grad_cp=a.grad_cp, transport=a.transport), ctx)
+                                          precision="bf16", grad_cp=a.grad_cp, transport=a.transport,
+                                          cuda_graph=bool(a.cuda_graph)), ctx)
     B, T, V = a.micro_bsz, a.ctx_len, cfg.vocab_size
     g = torch.Generator().manual_seed(99 + ctx.rank)
     n_batches = a.warmup + a.steps
@@ -167,7 +169,7 @@ def run_ours(a):
             "impl": "ours", "final_loss": final_loss,
             "config": {"model": f"rwkv7-{a.model}", "global_batch": B * ctx.world_size, "seq_len": T,
                        "parallelism": f"zero2-dp{ctx.world_size}" if ctx.world_size > 1 else "single",
-                       "grad_cp": a.grad_cp, "checkpointed_layers": cp_layers,
+                       "grad_cp": a.grad_cp, "checkpointed_layers": cp_layers, "cuda_graph": bool(a.cuda_graph),
                        "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2**30, 1), "transport": a.transport, "optimizer": "AdamW fp32 master, clip 1.0",
                        "l2_flush": "per-step activations and weights (>3 GB) exceed the 126 MB L2"},
             "clocks": clocks,
