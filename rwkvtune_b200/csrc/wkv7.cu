@@ -91,11 +91,15 @@ __global__ void __launch_bounds__(NTHREADS)
 wkv7_fwd_kernel(const bf16* __restrict__ q_, const bf16* __restrict__ w_, const bf16* __restrict__ k_,
                 const bf16* __restrict__ v_, const bf16* __restrict__ a_, const bf16* __restrict__ b_,
                 const float* __restrict__ s0, bf16* __restrict__ y_, float* __restrict__ sa_out,
-                float* __restrict__ ckpt, float* __restrict__ s_final, int T, int H) {
+                float* __restrict__ ckpt, float* __restrict__ s_final, const long long* __restrict__ slots,
+                int T, int H) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   FwdSmem& sm = *reinterpret_cast<FwdSmem*>(smem_raw);
 
   const int h = blockIdx.x, bb = blockIdx.y;
+  // state row of this sequence: its batch index, or its slot in a state pool (continuous batching keeps the
+  // states of all admitted sequences in one pool and decodes any subset of them in place)
+  const size_t srow = slots ? (size_t)slots[bb] : (size_t)bb;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int rg = lane >> 4, cg = lane & 15;
   const int r0 = warp * 16 + rg * 8;     // first of this thread's 8 rows
@@ -107,7 +111,7 @@ wkv7_fwd_kernel(const bf16* __restrict__ q_, const bf16* __restrict__ w_, const 
 
   float2 S2[8][2];
   if (s0) {
-    const float* p = s0 + ((size_t)bb * H + h) * N * N;
+    const float* p = s0 + (srow * H + h) * N * N;
 #pragma unroll
     for (int i = 0; i < 8; ++i) ld4_as2(p + (r0 + i) * N + c0, S2[i][0], S2[i][1]);
   } else {
@@ -223,7 +227,7 @@ wkv7_fwd_kernel(const bf16* __restrict__ q_, const bf16* __restrict__ w_, const 
     }
   }
   if (s_final) {
-    float* p = s_final + ((size_t)bb * H + h) * N * N;
+    float* p = s_final + (srow * H + h) * N * N;
 #pragma unroll
     for (int i = 0; i < 8; ++i)
       *reinterpret_cast<float4*>(p + (r0 + i) * N + c0) = make_float4(S2[i][0].x, S2[i][0].y, S2[i][1].x, S2[i][1].y);
@@ -558,7 +562,27 @@ RWKV_EXPORT int rwkv_wkv7_forward(const void* q, const void* w, const void* k, c
   dim3 grid(H, B);
   wkv7_fwd_kernel<<<grid, NTHREADS, sizeof(FwdSmem), (cudaStream_t)stream>>>(
       (const bf16*)q, (const bf16*)w, (const bf16*)k, (const bf16*)v, (const bf16*)a, (const bf16*)b,
-      (const float*)s0, (bf16*)y, (float*)sa, (float*)ckpt, (float*)s_final, T, H);
+      (const float*)s0, (bf16*)y, (float*)sa, (float*)ckpt, (float*)s_final, nullptr, T, H);
+  return rwkv_launch_status();
+}
+
+// Forward on a state pool: sequence i reads and writes pool[slots[i]] ([n_slots, H, 64, 64] fp32) in place; no
+// gather before and no scatter after the step.  q .. b, y: bf16 [B, T, H, 64]; slots: int64 [B], distinct.
+RWKV_EXPORT int rwkv_wkv7_forward_slots(const void* q, const void* w, const void* k, const void* v, const void* a,
+                                        const void* b, void* pool, const void* slots, void* y, int B, int T, int H,
+                                        void* stream) {
+  if (B <= 0 || T <= 0 || H <= 0 || B > 65535 || !pool || !slots) return RWKV_ERR_BAD_SHAPE;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(wkv7_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)sizeof(FwdSmem));
+    if (e != cudaSuccess) return RWKV_ERR_CUDA_BASE + (int)e;
+    configured = true;
+  }
+  dim3 grid(H, B);
+  wkv7_fwd_kernel<<<grid, NTHREADS, sizeof(FwdSmem), (cudaStream_t)stream>>>(
+      (const bf16*)q, (const bf16*)w, (const bf16*)k, (const bf16*)v, (const bf16*)a, (const bf16*)b,
+      (const float*)pool, (bf16*)y, nullptr, nullptr, (float*)pool, (const long long*)slots, T, H);
   return rwkv_launch_status();
 }
 

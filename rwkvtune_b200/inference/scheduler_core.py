@@ -153,20 +153,24 @@ class SchedulerCore:
         return [{k: pool[l, slot:slot + 1].float().clone() for k, pool in self.state_pool.items()}
                 for l in range(self.n_layer)]
 
-    def _gather_states(self, slots: List[int]):
-        idx = torch.tensor(slots, dtype=torch.long, device=self.device)
-        return idx, tuple(self.state_pool[k].index_select(1, idx) for k in ("att_x_prev", "att_kv", "ffn_x_prev"))
-
-    def _scatter_states(self, idx: torch.Tensor, att, wkv, ffn) -> None:
-        self.state_pool["att_x_prev"].index_copy_(1, idx, torch.stack(att).to(self.dtype))
-        self.state_pool["att_kv"].index_copy_(1, idx, torch.stack(wkv).float())
-        self.state_pool["ffn_x_prev"].index_copy_(1, idx, torch.stack(ffn).to(self.dtype))
-
     @torch.no_grad()
     def _model_forward_with_state(self, ids: torch.Tensor, slots: List[int]) -> torch.Tensor:
-        idx, (att, wkv, ffn) = self._gather_states(slots)
-        x, a, s, f = self.model.forward_states(ids, list(att.unbind(0)), list(wkv.unbind(0)), list(ffn.unbind(0)))
-        self._scatter_states(idx, a, s, f)
+        """One model call on the sequences in ``slots``.  The WKV states (16 KB per head and layer, by far the largest
+        part of a sequence's state) are never gathered or scattered: the kernel reads and writes ``pool[slot]`` in
+        place.  The two token-shift rows per layer go through ``index_select`` / ``index_copy_``."""
+        idx = torch.tensor(slots, dtype=torch.long, device=self.device)
+        att = self.state_pool["att_x_prev"].index_select(1, idx)
+        ffn = self.state_pool["ffn_x_prev"].index_select(1, idx)
+        kv_pool = self.state_pool["att_kv"]
+        if kv_pool.dtype == torch.float32 and kv_pool.is_contiguous():
+            wkv = [(kv_pool[l], idx) for l in range(self.n_layer)]
+        else:
+            wkv = list(kv_pool.index_select(1, idx).unbind(0))
+        x, a, s, f = self.model.forward_states(ids, list(att.unbind(0)), wkv, list(ffn.unbind(0)))
+        self.state_pool["att_x_prev"].index_copy_(1, idx, torch.stack(a).to(self.dtype))
+        self.state_pool["ffn_x_prev"].index_copy_(1, idx, torch.stack(f).to(self.dtype))
+        if not isinstance(s[0], tuple):
+            kv_pool.index_copy_(1, idx, torch.stack(s).to(kv_pool.dtype))
         return self.model.head(x[:, -1, :]).float()
 
     def _finish_sequence(self, seq: SequenceState, reason: str) -> None:

@@ -177,6 +177,17 @@ def wkv7(r, w, k, v, a, b, head_size: int = 64, state: Optional[torch.Tensor] = 
     return y.to(r.dtype), (s if return_state else None)
 
 
+def wkv7_pool_step(r, w, k, v, a, b, pool: torch.Tensor, slots: torch.Tensor, head_size: int = 64) -> torch.Tensor:
+    """WKV7 forward without autograd on a state pool ``[n_slots, H, N, N]`` (fp32): sequence ``i`` reads and writes
+    ``pool[slots[i]]`` in place.  ``slots`` must be distinct."""
+    if _native(r, "wkv7") and head_size == 64:
+        return _cuda().wkv7_pool_step(r, w, k, v, a, b, pool, slots)
+    with torch.no_grad():
+        y, s = reference.wkv7(r, w, k, v, a, b, head_size, pool.index_select(0, slots))
+        pool.index_copy_(0, slots, s.to(pool.dtype))
+    return y.to(r.dtype)
+
+
 # ------------------------------------------------------------------------------- losses
 def linear_cross_entropy(x, weight, labels, l2wrap: bool = True, ignore_index: int = -100,
                          l2wrap_tokens: Optional[int] = None):

@@ -586,6 +586,21 @@ def wkv7_tc_forward(r, w, k, v, a, b, state=None, return_state=False, save_chunk
     return y, sf, cs
 
 
+def wkv7_pool_step(r, w, k, v, a, b, pool: torch.Tensor, slots: torch.Tensor) -> torch.Tensor:
+    """WKV7 forward (no autograd) that updates ``pool[slots[i]]`` (fp32 ``[n_slots, H, 64, 64]``) in place for
+    sequence ``i``: decode or prefill of any subset of a state pool without gathering or scattering states."""
+    B, T, C = r.shape
+    H = C // 64
+    if pool.dtype != torch.float32 or not pool.is_contiguous() or tuple(pool.shape[1:]) != (H, 64, 64):
+        raise ValueError("pool must be a contiguous fp32 [n_slots, H, 64, 64] tensor")
+    r, w, k, v, a, b = (_c(t, BF16) for t in (r, w, k, v, a, b))
+    slots = _c(slots, torch.int64)
+    y = torch.empty(B, T, C, dtype=BF16, device=r.device)
+    call("rwkv_wkv7_forward_slots", ptr(r), ptr(w), ptr(k), ptr(v), ptr(a), ptr(b), ptr(pool), ptr(slots), ptr(y),
+         i32(B), i32(T), i32(H), stream())
+    return y
+
+
 # =============================================================================== gathers
 def gather_rows(src: torch.Tensor, index: torch.Tensor) -> torch.Tensor:
     """``src.index_select(0, index)`` for a contiguous tensor whose rows are a multiple of 16 bytes."""

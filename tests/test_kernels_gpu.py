@@ -447,3 +447,18 @@ def test_gemm_activation_epilogue(act):
     (yr * g).sum().backward()
     _close(xk.grad, xr.grad, 3e-2, 3e-2 * xr.grad.abs().mean().item() + 1e-3, "dx")
     _close(wk.grad, wr.grad, 3e-2, 3e-2 * wr.grad.abs().mean().item() + 1e-2, "dw")
+
+
+@pytest.mark.parametrize("T", [1, 5])
+def test_wkv7_pool_step_updates_slots_in_place(T):
+    B, H = 3, 2
+    ins = _wkv_inputs(B, T, H, seed=9)
+    pool = torch.randn(7, H, 64, 64, device="cuda") * 0.1
+    slots = torch.tensor([5, 0, 3], device="cuda")
+    before = pool.clone()
+    y = ops.wkv7_pool_step(*ins, pool, slots)
+    y_ref, s_ref = ref.wkv7(*[t.float() for t in ins], 64, before.index_select(0, slots))
+    _close(y, y_ref, 2e-2, 2e-2, "y")
+    assert torch.allclose(pool.index_select(0, slots), s_ref, atol=1e-3, rtol=1e-3)
+    untouched = torch.tensor([1, 2, 4, 6], device="cuda")
+    assert torch.equal(pool.index_select(0, untouched), before.index_select(0, untouched))
