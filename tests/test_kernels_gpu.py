@@ -462,3 +462,42 @@ def test_wkv7_pool_step_updates_slots_in_place(T):
     assert torch.allclose(pool.index_select(0, slots), s_ref, atol=1e-3, rtol=1e-3)
     untouched = torch.tensor([1, 2, 4, 6], device="cuda")
     assert torch.equal(pool.index_select(0, untouched), before.index_select(0, untouched))
+
+
+def test_scheduler_pool_step_matches_gathered_states():
+    """The scheduler's in-place pool step gives the logits and states of the gather / compute / scatter formulation."""
+    from rwkvtune_b200.inference import SchedulerCore
+    from rwkvtune_b200.models import RWKVConfig, RWKV7Model
+
+    class Tok:
+        eos_token_id = 7
+        vocab_size = 250
+        idx2token = {i: bytes([65 + i % 26]) for i in range(1, 250)}
+
+        def decode(self, ids, **kw):
+            return "".join(chr(65 + int(i) % 26) for i in ids)
+
+    torch.manual_seed(0)
+    m = RWKV7Model(RWKVConfig(n_layer=2, n_embd=128, vocab_size=256, eos_token_id=7, dim_att_lora=16, dim_gate_lora=16,
+                              dim_mv_lora=16))
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            if n.endswith(("output.weight", "ffn.value.weight", "w1", "a1", "v1", "g1")):
+                p.normal_(0, 0.05)
+    m = m.cuda().to(BF).eval()
+    sched = SchedulerCore(m, Tok(), max_batch_size=4, max_batch_tokens=16, prefill_chunk_size=4)
+    for k, pool in sched.state_pool.items():
+        pool.copy_(torch.randn_like(pool.float()).to(pool.dtype) * 0.1)
+    before = {k: v.clone() for k, v in sched.state_pool.items()}
+    slots = [2, 0, 3]
+    idx = torch.tensor(slots, device="cuda")
+    ids = torch.randint(1, 250, (3, 3), device="cuda")
+    logits = sched._model_forward_with_state(ids, slots)
+    with torch.no_grad():
+        x, a, s, f = m.forward_states(ids, list(before["att_x_prev"].index_select(1, idx).unbind(0)),
+                                      list(before["att_kv"].index_select(1, idx).unbind(0)),
+                                      list(before["ffn_x_prev"].index_select(1, idx).unbind(0)))
+        ref_logits = m.head(x[:, -1, :]).float()
+    assert torch.allclose(logits, ref_logits, atol=2e-2, rtol=2e-2)
+    assert torch.allclose(sched.state_pool["att_kv"].index_select(1, idx), torch.stack(s).float(), atol=1e-4, rtol=1e-4)
+    assert torch.equal(sched.state_pool["att_kv"][:, 1], before["att_kv"][:, 1])      # slot 1 was not scheduled
