@@ -473,7 +473,10 @@ class _LinearCrossEntropy(torch.autograd.Function):
         factor = ref.L2WRAP_FACTOR / float(l2wrap_tokens if l2wrap_tokens is not None else M)
         need_x, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
         dx = torch.empty_like(x) if need_x else None
-        dw = torch.zeros(V, C, dtype=torch.float32, device=x.device) if need_w else None
+        # bf16 inputs: the weight gradient is accumulated over the slabs in the GEMM epilogue (bf16 [V, C], no fp32
+        # temporary of half a gigabyte re-read per slab); other dtypes keep an fp32 accumulator
+        dw_in_epilogue = need_w and x.dtype == BF16 and weight.dtype == BF16
+        dw = (torch.zeros(V, C, dtype=BF16 if dw_in_epilogue else torch.float32, device=x.device) if need_w else None)
         loss_sum = torch.zeros((), dtype=torch.float32, device=x.device)
         safe_labels = labels.clamp(min=0)
         fused_rows = x.dtype == BF16 and weight.dtype == BF16 and V % 8 == 0
@@ -509,7 +512,10 @@ class _LinearCrossEntropy(torch.autograd.Function):
             if need_x:
                 dx[s:e] = gemm.mm_nn(grad, weight)
             if need_w:
-                dw += gemm.mm_tn(grad, xs).float()
+                if dw_in_epilogue:
+                    gemm.addmm_tn_(dw, grad, xs)
+                else:
+                    dw += gemm.mm_tn(grad, xs).float()
         if fused_rows:
             loss_sum = loss_rows.sum()
         ctx.save_for_backward(dx, dw)

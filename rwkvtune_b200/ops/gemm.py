@@ -83,6 +83,14 @@ def addmm_nn_(y: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor
     return y.add_(x @ w)
 
 
+def addmm_tn_(y: torch.Tensor, a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """``y += a^T @ b`` in place (a weight gradient accumulated over row slabs; see :func:`addmm_nt_`)."""
+    n = _native()
+    if _acc_ok(n, y) and n.native_ok(a, b, "tn"):
+        return n.mm_tn(a, b, out=y)
+    return y.add_((a.t() @ b).to(y.dtype))
+
+
 def mm_tn(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     n = _native()
     if n is not None and n.native_ok(a, b, "tn"):

@@ -86,9 +86,9 @@ def mm_nn(x: torch.Tensor, w: torch.Tensor, epilogue: int = 0, out: torch.Tensor
     return _run(x, w, x.shape[0], w.shape[1], x.shape[1], 0, 1, epilogue, out)
 
 
-def mm_tn(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+def mm_tn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor = None) -> torch.Tensor:
     """``a[Kc,M]^T @ b[Kc,N]`` (weight gradients: contraction over the token dimension)"""
-    return _run(a, b, a.shape[1], b.shape[1], a.shape[0], 1, 1)
+    return _run(a, b, a.shape[1], b.shape[1], a.shape[0], 1, 1, 0, out)
 
 
 class GatheredWeight:
