@@ -197,7 +197,9 @@ __device__ void ag_copy_role(const AgParams& ag, int N, int K) {
 }
 
 // EPI: 0 = plain store, 1 = relu(x)^2, 2 = add to the bf16 values already in C (in place: C += A B),
-//      3 = tanh(x), 4 = sigmoid(x)  (the bottleneck activations of the low-rank decay and gate chains)
+//      3 = tanh(x), 4 = sigmoid(x)  (the bottleneck activations of the low-rank decay and gate chains),
+//      5 = x * 2 sqrt(Y) with Y a bf16 [M,N] matrix: the derivative of relu(p)^2 expressed through its output Y,
+//          applied to the dgrad of the channel-mix value projection (no separate activation-backward pass)
 template <bool A_MN, bool B_MN, int EPI, bool AG>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -341,8 +343,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         uint32_t v0[32], v1[32];
         tmem_ld32(t_row + chunk * 64, v0);
         tmem_ld32(t_row + chunk * 64 + 32, v1);
-        uint4 cin[EPI == 2 ? 8 : 1];
-        if (EPI == 2) {   // this thread's 64 output columns of the existing C, fetched while the TMEM load is in flight
+        uint4 cin[(EPI == 2 || EPI == 5) ? 8 : 1];
+        if (EPI == 2 || EPI == 5) {   // this thread's 64 output columns of the existing C, fetched while the TMEM load is in flight
           const long long gm = m0 + row;
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
@@ -359,7 +361,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
         for (int j = 0; j < 8; ++j) {   // eight 16-byte pieces of this row, XOR-swizzled by (row % 8)
           float f[8], prev[8];
-          if (EPI == 2) unpack8(cin[j], prev);
+          if (EPI == 2 || EPI == 5) unpack8(cin[j], prev);
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
             const int col = j * 8 + e;
@@ -368,6 +370,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             if (EPI == 2) x += prev[e];
             if (EPI == 3) x = 1.f - __fdividef(2.f, __expf(2.f * x) + 1.f);     // tanh, saturates cleanly at +-1
             if (EPI == 4) x = __fdividef(1.f, 1.f + __expf(-x));
+            if (EPI == 5) x *= 2.f * sqrtf(prev[e]);
             f[e] = x;
           }
           const uint4 packed = pack8(f);
@@ -476,13 +479,15 @@ int launch_ag(CUtensorMap ma, CUtensorMap mb, CUtensorMap mc, int M, int N, int 
 // C[M,N] (row-major, ldc) = op(A) op(B) in bf16 with fp32 accumulation.
 //   a_mn = 0: A is [M,K] row-major (lda);  a_mn = 1: A is stored [K,M] row-major (lda)
 //   b_mn = 0: B is [N,K] row-major (ldb);  b_mn = 1: B is stored [K,N] row-major (ldb)
-//   epilogue: 0 none, 1 relu(x)^2, 3 tanh, 4 sigmoid, 2 add a bf16 [M,N] matrix: `residual` (row stride ldr) or, when that is null,
+//   epilogue: 0 none, 1 relu(x)^2, 3 tanh, 4 sigmoid, 5 multiply by 2 sqrt(residual), 2 add a bf16 [M,N] matrix: `residual` (row stride ldr) or, when that is null,
 //   the values already in C (in place).   status: device int, set non-zero if a device-side wait timed out.
 RWKV_EXPORT int rwkv_gemm_bf16_tcgen05(const void* a, const void* b, void* c, int M, int N, int K, long long lda,
                                        long long ldb, long long ldc, int a_mn, int b_mn, int epilogue, void* status,
                                        const void* residual, long long ldr, void* stream) {
   if (M <= 0 || N <= 0 || K <= 0) return RWKV_ERR_BAD_SHAPE;
-  if (epilogue == 2 && residual && (((uintptr_t)residual & 15) || (ldr * 2) % 16)) return RWKV_ERR_BAD_ALIGNMENT;
+  if ((epilogue == 2 || epilogue == 5) && residual && (((uintptr_t)residual & 15) || (ldr * 2) % 16))
+    return RWKV_ERR_BAD_ALIGNMENT;
+  if (epilogue == 5 && !residual) return RWKV_ERR_BAD_SHAPE;
   static int sms = 0;
   if (!sms) {
     int dev = 0;
@@ -506,6 +511,7 @@ RWKV_EXPORT int rwkv_gemm_bf16_tcgen05(const void* a, const void* b, void* c, in
    : epilogue == 2 ? launch<AM, BMN, 2>(ma, mb, mc, M, N, K, sp, sms, cp, ldc, st)                \
    : epilogue == 3 ? launch<AM, BMN, 3>(ma, mb, mc, M, N, K, sp, sms, cp, ldc, st)                \
    : epilogue == 4 ? launch<AM, BMN, 4>(ma, mb, mc, M, N, K, sp, sms, cp, ldc, st)                \
+   : epilogue == 5 ? launch<AM, BMN, 5>(ma, mb, mc, M, N, K, sp, sms, cp, ldc, st)                \
                    : launch<AM, BMN, 0>(ma, mb, mc, M, N, K, sp, sms, cp, ldc, st))
   if (!a_mn && !b_mn) return DISPATCH(false, false);
   if (!a_mn && b_mn) return DISPATCH(false, true);

@@ -197,6 +197,9 @@ class RWKV7ChannelMix(nn.Module):
 
     def forward(self, x, ln_w, ln_b, x_prev=None, want_state: bool = False):
         (xk,), last, x = ops.ln_shift_mix_unbound(x, ln_w, ln_b, self.x_k, x_prev)
+        plain = all(type(m) is Linear and getattr(m, "_sharded", None) is None for m in (self.key, self.value))
+        if plain:
+            return ops.channel_mix_ffn(xk, self.key.weight, self.value.weight, x), (last if want_state else None)
         if type(self.key) is Linear:
             hidden = ops.linear_relu_sq(xk, self.key.weight)
         else:   # wrapped (e.g. LoRA): activation applied separately

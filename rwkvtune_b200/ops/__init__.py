@@ -109,6 +109,14 @@ def linear_add(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor) ->
     return residual + torch.nn.functional.linear(x, weight)
 
 
+def channel_mix_ffn(xk: torch.Tensor, w_key: torch.Tensor, w_value: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
+    """``residual + relu(xk @ w_key^T)^2 @ w_value^T`` (the feed-forward half of a block) as one autograd node."""
+    if _native(xk, "gemm") and _native(xk, "relu_squared"):
+        return _cuda().channel_mix_ffn(xk, w_key, w_value, residual)
+    hidden = reference.relu_squared(torch.nn.functional.linear(xk, w_key))
+    return residual + torch.nn.functional.linear(hidden, w_value)
+
+
 def linear_group(xs, weights):
     """Several independent ``x_i @ W_i^T`` with the same leading shape; one grouped launch while decoding."""
     if _native(xs[0], "gemm"):

@@ -566,6 +566,54 @@ class _LinearReluSq(torch.autograd.Function):
         return dx, dw
 
 
+class _ChannelMixFFN(torch.autograd.Function):
+    """``residual + relu(xk Wk^T)^2 Wv^T`` as one node: relu^2 in the epilogue of the key GEMM, the residual sum in the
+    epilogue of the value GEMM, and in backward the activation derivative ``2 sqrt(hidden)`` in the epilogue of the
+    value projection's dgrad GEMM (``rwkvtune/models/rwkv7/model.py:304-308`` is the unfused statement)."""
+
+    @staticmethod
+    def forward(ctx, xk, wk, wv, residual):
+        from . import gemm_native
+
+        x2 = _c(xk.reshape(-1, xk.shape[-1]), BF16)
+        r2 = _c(residual.reshape(-1, residual.shape[-1]), BF16)
+        hidden = gemm_native.mm_nt(x2, wk, epilogue=1)
+        out = gemm_native.mm_nt(hidden, wv, residual=r2)
+        ctx.save_for_backward(x2, wk, wv, hidden)
+        ctx.shape = xk.shape
+        return out.reshape(residual.shape)
+
+    @staticmethod
+    def backward(ctx, dout):
+        from . import gemm, gemm_native
+
+        x2, wk, wv, hidden = ctx.saved_tensors
+        d2 = _c(dout.reshape(-1, dout.shape[-1]), BF16)
+        dpre = gemm_native.mm_nn(d2, wv, epilogue=5, residual=hidden)        # (dout Wv) * 2 sqrt(hidden)
+        dwv = gemm.mm_tn(d2, hidden) if ctx.needs_input_grad[2] else None
+        dx = gemm.mm_nn(dpre, wk).reshape(ctx.shape) if ctx.needs_input_grad[0] else None
+        dwk = gemm.mm_tn(dpre, x2) if ctx.needs_input_grad[1] else None
+        return dx, dwk, dwv, (dout if ctx.needs_input_grad[3] else None)
+
+
+def channel_mix_ffn(xk, wk, wv, residual):
+    from . import gemm_native
+
+    x2 = xk.reshape(-1, xk.shape[-1])
+    r2 = residual.reshape(-1, residual.shape[-1])
+    ok = (xk.dtype == BF16 and wk.dtype == BF16 and wv.dtype == BF16 and residual.dtype == BF16
+          and x2.is_contiguous() and r2.is_contiguous() and gemm_native.native_ok(x2, wk, "nt")
+          and x2.shape[0] >= gemm_native.MIN_M and wk.shape[0] % 8 == 0 and wv.shape[0] % 8 == 0)
+    if ok:   # the value projection contracts over 4C: without split-K it needs enough output tiles of its own
+        tiles = -(-x2.shape[0] // 128) * -(-wv.shape[0] // 256)
+        ok = tiles >= 64 or wv.shape[1] <= 4096
+    if ok:
+        return _ChannelMixFFN.apply(xk, wk, wv, residual)
+    from . import gemm
+
+    return gemm.linear_add(linear_relu_sq(xk, wk), wv, residual)
+
+
 def linear_relu_sq(x, weight):
     from . import gemm_native
 

@@ -66,7 +66,7 @@ def _run(a, b, M, N, K, a_mn: int, b_mn: int, epilogue: int = 0, out: torch.Tens
         c, epilogue = out, 2
     else:
         c = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
-        if residual is not None:
+        if residual is not None and epilogue == 0:
             epilogue = 2
     _ext.call("rwkv_gemm_bf16_tcgen05", _ext.ptr(a), _ext.ptr(b), _ext.ptr(c), _ext.i32(M), _ext.i32(N), _ext.i32(K),
               _ext.i64(a.stride(0)), _ext.i64(b.stride(0)), _ext.i64(c.stride(0)), _ext.i32(a_mn), _ext.i32(b_mn),
@@ -81,9 +81,10 @@ def mm_nt(x: torch.Tensor, w: torch.Tensor, epilogue: int = 0, out: torch.Tensor
     return _run(x, w, x.shape[0], w.shape[0], x.shape[1], 0, 0, epilogue, out, residual)
 
 
-def mm_nn(x: torch.Tensor, w: torch.Tensor, epilogue: int = 0, out: torch.Tensor = None) -> torch.Tensor:
-    """``x [M,K] @ w[K,N]``"""
-    return _run(x, w, x.shape[0], w.shape[1], x.shape[1], 0, 1, epilogue, out)
+def mm_nn(x: torch.Tensor, w: torch.Tensor, epilogue: int = 0, out: torch.Tensor = None,
+          residual: torch.Tensor = None) -> torch.Tensor:
+    """``x [M,K] @ w[K,N]``; with ``epilogue=5`` the result is multiplied by ``2 sqrt(residual)``."""
+    return _run(x, w, x.shape[0], w.shape[1], x.shape[1], 0, 1, epilogue, out, residual)
 
 
 def mm_tn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor = None) -> torch.Tensor:

@@ -501,3 +501,22 @@ def test_scheduler_pool_step_matches_gathered_states():
     assert torch.allclose(logits, ref_logits, atol=2e-2, rtol=2e-2)
     assert torch.allclose(sched.state_pool["att_kv"].index_select(1, idx), torch.stack(s).float(), atol=1e-4, rtol=1e-4)
     assert torch.equal(sched.state_pool["att_kv"][:, 1], before["att_kv"][:, 1])      # slot 1 was not scheduled
+
+
+def test_channel_mix_ffn_fused_node():
+    torch.manual_seed(5)
+    M, C = 640, 256
+    xk = (torch.randn(2, M // 2, C, device="cuda") * 0.5).to(BF)
+    res = torch.randn(2, M // 2, C, device="cuda").to(BF)
+    wk = (torch.randn(4 * C, C, device="cuda") * 0.05).to(BF)
+    wv = (torch.randn(C, 4 * C, device="cuda") * 0.05).to(BF)
+    leaves_k = [t.clone().requires_grad_(True) for t in (xk, wk, wv, res)]
+    leaves_r = [t.float().clone().requires_grad_(True) for t in (xk, wk, wv, res)]
+    out = ops.channel_mix_ffn(*leaves_k)
+    out_r = leaves_r[3] + torch.relu(leaves_r[0] @ leaves_r[1].t()) ** 2 @ leaves_r[2].t()
+    _close(out, out_r, 2e-2, 2e-2, "out")
+    g = torch.randn_like(out_r)
+    (out.float() * g).sum().backward()
+    (out_r * g).sum().backward()
+    for name, a, b in zip(["dxk", "dwk", "dwv", "dres"], leaves_k, leaves_r):
+        _close(a.grad, b.grad, 4e-2, 4e-2 * b.grad.abs().mean().item() + 1e-3, name)
