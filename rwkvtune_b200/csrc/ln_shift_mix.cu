@@ -452,17 +452,22 @@ ln_shift_mix_bwd_v4_kernel(const DOutPtrs dO, const bf16* __restrict__ dlast, co
     float dh[4], ncarry[4];
 #pragma unroll
     for (int e = 0; e < 4; ++e) { dh[e] = carry[e]; ncarry[e] = 0.f; }
+    float dlt[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) dlt[e] = h_prev[e] - h_cur[e];
 #pragma unroll
     for (int k = 0; k < K; ++k) {
       float g[4];
       unpack4(gc[k], g);
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        dh[e] += g[e] * (1.f - mu[k][e]);
+        dh[e] += g[e];                       // sum_k g_k (1 - mu_k) = sum_k g_k - ncarry, finished below
         ncarry[e] += g[e] * mu[k][e];
-        acc_mu[k][e] += g[e] * (h_prev[e] - h_cur[e]);
+        acc_mu[k][e] += g[e] * dlt[e];
       }
     }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) dh[e] -= ncarry[e];
     float c[2] = {0.f, 0.f};
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
