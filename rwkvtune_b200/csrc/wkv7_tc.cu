@@ -632,9 +632,10 @@ wkv7_tc_bwd_chunk_kernel(const bf16* __restrict__ q_, const bf16* __restrict__ w
     const int t = c * L + row;
     const bool live = t < T;
     const size_t off = base + (size_t)(live ? t : 0) * tok_stride + j0;
+    cp16(&sm.wraw[row][j0], w_ + off, live);
+    cp_commit();      // group 1: what the decay scan and the Bt / Kt rescaling need
     cp16(&sm.Vs[row][j0], v_ + off, live);
     cp16(&sm.dYs[row][j0], dy_ + off, live);
-    cp16(&sm.wraw[row][j0], w_ + off, live);
     const bf16* s0p = chunk_states + chunk_id * N * N;
     const bf16* dsp = dstates + chunk_id * N * N;
 #pragma unroll
@@ -643,9 +644,9 @@ wkv7_tc_bwd_chunk_kernel(const bf16* __restrict__ q_, const bf16* __restrict__ w
       cp16(&sm.S0s[r][j0], s0p + r * N + j0, true);
       cp16(&sm.dSs[r][j0], dsp + r * N + j0, true);
     }
-    cp_commit();
+    cp_commit();      // group 2: values, output gradient and the two 64x64 states, still in flight during the scan
   }
-  cp_wait<0>();
+  cp_wait<1>();
   __syncthreads();
   decay_scan<false>(&sm.wraw[0][0], N, sm.E, nullptr, sm.scratch, c, T);
   {  // Bt = b / gamma_t = Bb / gamma_L, Kt likewise (thread (row, part): 8 channels of one step)
@@ -662,6 +663,7 @@ wkv7_tc_bwd_chunk_kernel(const bf16* __restrict__ q_, const bf16* __restrict__ w
     *reinterpret_cast<uint4*>(&sm.Bt[row][j0]) = pack8(bbv);
     *reinterpret_cast<uint4*>(&sm.Kt[row][j0]) = pack8(kbv);
   }
+  cp_wait<0>();
   __syncthreads();
 
   {  // sds[q][j] = gamma_L[j] * sum over 16 value rows of S0[v][j] dS[v][j]   (d log gamma_L through the carried state)
