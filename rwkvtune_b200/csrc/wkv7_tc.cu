@@ -601,7 +601,7 @@ wkv7_tc_bwd_chunk_kernel(const bf16* __restrict__ q_, const bf16* __restrict__ w
                          const bf16* __restrict__ dy_, const bf16* __restrict__ chunk_states,
                          const bf16* __restrict__ dstates, const unsigned char* __restrict__ ws, bf16* __restrict__ dq_, bf16* __restrict__ dw_,
                          bf16* __restrict__ dk_, bf16* __restrict__ dv_, bf16* __restrict__ da_, bf16* __restrict__ db_,
-                         int T, int H) {
+                         int acc_qkv, int T, int H) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   BwdSm& sm = *reinterpret_cast<BwdSm*>(smem_raw);
   const int c = blockIdx.x, h = blockIdx.y, bb = blockIdx.z;
@@ -645,6 +645,14 @@ wkv7_tc_bwd_chunk_kernel(const bf16* __restrict__ q_, const bf16* __restrict__ w
       cp16(&sm.dSs[r][j0], dsp + r * N + j0, true);
     }
     cp_commit();      // group 2: values, output gradient and the two 64x64 states, still in flight during the scan
+  }
+  // acc_qkv: this thread's tiles of the gradients already in dq / dk / dv, requested now and added in the output pass
+  uint4 acc_in[3] = {make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u)};
+  if (acc_qkv && c * L + row < T) {
+    const size_t off = base + (size_t)(c * L + row) * tok_stride + j0;
+    acc_in[0] = *reinterpret_cast<const uint4*>(dq_ + off);
+    acc_in[1] = *reinterpret_cast<const uint4*>(dk_ + off);
+    acc_in[2] = *reinterpret_cast<const uint4*>(dv_ + off);
   }
   cp_wait<1>();
   __syncthreads();
@@ -919,11 +927,25 @@ wkv7_tc_bwd_chunk_kernel(const bf16* __restrict__ q_, const bf16* __restrict__ w
     if (t < T) {
       const size_t off = base + (size_t)t * tok_stride + j0;
       *reinterpret_cast<uint4*>(dw_ + off) = *reinterpret_cast<const uint4*>(&odw[row][j0]);
-      *reinterpret_cast<uint4*>(dq_ + off) = *reinterpret_cast<const uint4*>(&odq[row][j0]);
+      // acc_qkv: dq / dk / dv already hold another consumer's gradient of the same tensors (the bonus term of the
+      // output normalisation reads r, k, v too); it is summed here instead of by a separate pass
+      auto put = [&](bf16* dst, const bf16* stage, const uint4& prior) {
+        uint4 val = *reinterpret_cast<const uint4*>(stage);
+        if (acc_qkv) {
+          float fa[8], fb[8];
+          unpack8(val, fa);
+          unpack8(prior, fb);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) fa[i] += fb[i];
+          val = pack8(fa);
+        }
+        *reinterpret_cast<uint4*>(dst) = val;
+      };
+      put(dq_ + off, &odq[row][j0], acc_in[0]);
+      put(dk_ + off, &odk[row][j0], acc_in[1]);
+      put(dv_ + off, &sm.dVs[row][j0], acc_in[2]);
       *reinterpret_cast<uint4*>(da_ + off) = *reinterpret_cast<const uint4*>(&oda[row][j0]);
       *reinterpret_cast<uint4*>(db_ + off) = *reinterpret_cast<const uint4*>(&odb[row][j0]);
-      *reinterpret_cast<uint4*>(dk_ + off) = *reinterpret_cast<const uint4*>(&odk[row][j0]);
-      *reinterpret_cast<uint4*>(dv_ + off) = *reinterpret_cast<const uint4*>(&sm.dVs[row][j0]);
     }
   }
 }
@@ -974,12 +996,14 @@ RWKV_EXPORT int rwkv_wkv7_tc_forward(const void* q, const void* w, const void* k
 
 // dy and the six gradients: bf16 [B,T,H,64]; chunk_states from the forward; ds_final (in) / ds0 (out): fp32
 // [B,H,64,64] or null; dstates: scratch bf16 [B,H,ceil(T/16),64,64].
+// acc_qkv = 1: dq, dk, dv are added to what the three buffers already contain.
 // ws: rwkv_wkv7_tc_ws_bytes() bytes.  ws_is_forward = 1: it still holds what the forward call on the SAME inputs
 // wrote (kept by the caller); ws_is_forward = 0: scratch, refilled here by the prep kernel.
 RWKV_EXPORT int rwkv_wkv7_tc_backward(const void* q, const void* w, const void* k, const void* v, const void* a,
                                       const void* b, const void* dy, const void* chunk_states, const void* ds_final,
                                       void* dstates, void* ws, int ws_is_forward, void* dq, void* dw, void* dk,
-                                      void* dv, void* da, void* db, void* ds0, int B, int T, int H, void* stream) {
+                                      void* dv, void* da, void* db, void* ds0, int acc_qkv, int B, int T, int H,
+                                      void* stream) {
   if (B <= 0 || T <= 0 || H <= 0 || B > 65535 || H > 65535) return RWKV_ERR_BAD_SHAPE;
   if (int rc = configure_once()) return rc;
   const int NC = (T + L - 1) / L;
@@ -994,6 +1018,6 @@ RWKV_EXPORT int rwkv_wkv7_tc_backward(const void* q, const void* w, const void* 
   wkv7_tc_bwd_chunk_kernel<<<dim3(NC, H, B), NT, sizeof(BwdSm), st>>>(
       (const bf16*)q, (const bf16*)w, (const bf16*)k, (const bf16*)v, (const bf16*)a, (const bf16*)b, (const bf16*)dy,
       (const bf16*)chunk_states, (const bf16*)dstates, (const unsigned char*)ws, (bf16*)dq, (bf16*)dw, (bf16*)dk, (bf16*)dv, (bf16*)da,
-      (bf16*)db, T, H);
+      (bf16*)db, acc_qkv, T, H);
   return rwkv_launch_status();
 }

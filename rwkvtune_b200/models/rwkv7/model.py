@@ -168,11 +168,9 @@ class RWKV7TimeMix(nn.Module):
             w, k, v, a_, b_ = ops.timemix_prep(k, v, v_first, w_lin, a_lin, v_lin, self.w0, self.a0, self.v0,
                                                self.k_k, self.k_a, self.head_size)
 
-        if isinstance(wkv_state, tuple):   # (state pool [n_slots, H, N, N], slot index per sequence): updated in place
-            y, new_state = ops.wkv7_pool_step(r, w, k, v, a_, b_, wkv_state[0], wkv_state[1], self.head_size), wkv_state
-        else:
-            y, new_state = ops.wkv7(r, w, k, v, a_, b_, self.head_size, state=wkv_state, return_state=want_state)
-        z = ops.gn_bonus_gate(y, r, k, v, g, self.ln_x.weight, self.ln_x.bias, self.r_k, self.head_size)
+        # wkv_state may be (state pool [n_slots, H, N, N], slot index per sequence): updated in place by the kernel
+        z, new_state = ops.wkv7_gn(r, w, k, v, a_, b_, g, self.ln_x.weight, self.ln_x.bias, self.r_k, self.head_size,
+                                   state=wkv_state, return_state=want_state)
         out = _project_add(self.output, z, x)      # x + output(z): the residual sum rides in the GEMM epilogue
         return out, v_first, (last if want_state else None), new_state
 

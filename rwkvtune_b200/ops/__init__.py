@@ -196,6 +196,19 @@ def wkv7_pool_step(r, w, k, v, a, b, pool: torch.Tensor, slots: torch.Tensor, he
     return y.to(r.dtype)
 
 
+def wkv7_gn(r, w, k, v, a, b, g, gn_w, gn_b, r_k, head_size: int = 64, state: Optional[torch.Tensor] = None,
+            return_state: bool = False, eps: float = GROUPNORM_EPS):
+    """The recurrence followed by GroupNorm + bonus + gate; returns ``(z, final_state or None)``.  On CUDA the two
+    share one autograd node so that the gradients of ``r``, ``k``, ``v`` are summed inside the backward kernel."""
+    if _native(r, "wkv7") and _native(r, "gn_bonus_gate") and not isinstance(state, tuple):
+        return _cuda().wkv7_gn(r, w, k, v, a, b, g, gn_w, gn_b, r_k, head_size, state, return_state, eps)
+    if isinstance(state, tuple):
+        y, s = wkv7_pool_step(r, w, k, v, a, b, state[0], state[1], head_size), state
+    else:
+        y, s = wkv7(r, w, k, v, a, b, head_size, state, return_state)
+    return gn_bonus_gate(y, r, k, v, g, gn_w, gn_b, r_k, head_size, eps), s
+
+
 # ------------------------------------------------------------------------------- losses
 def linear_cross_entropy(x, weight, labels, l2wrap: bool = True, ignore_index: int = -100,
                          l2wrap_tokens: Optional[int] = None):

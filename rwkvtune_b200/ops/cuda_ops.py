@@ -114,8 +114,8 @@ class _WKV7TC(torch.autograd.Function):
         dstates = torch.empty_like(cs)
         ws = kept[0] if kept else _tc_ws(B, T, H, r.device)
         call("rwkv_wkv7_tc_backward", ptr(r), ptr(w), ptr(k), ptr(v), ptr(a), ptr(b), ptr(dy), ptr(cs), ptr(ds_T),
-             ptr(dstates), ptr(ws), i32(1 if kept else 0), *(ptr(g) for g in grads), ptr(ds0), i32(B), i32(T), i32(H),
-             stream())
+             ptr(dstates), ptr(ws), i32(1 if kept else 0), *(ptr(g) for g in grads), ptr(ds0), i32(0), i32(B), i32(T),
+             i32(H), stream())
         if ctx.out_dtype != BF16:
             grads = [g.to(ctx.out_dtype) for g in grads]
         return (*grads, ds0, None)
@@ -414,6 +414,74 @@ def gn_bonus_gate(y, r, k, v, g, gn_w, gn_b, r_k, head_size: int = 64, eps: floa
     if head_size != 64 or y.shape[-1] % 64:
         return ref.gn_bonus_gate(y, r, k, v, g, gn_w, gn_b, r_k, head_size, eps)
     return _GnBonusGate.apply(y, r, k, v, g, gn_w, gn_b, r_k, eps)
+
+
+class _WKV7GN(torch.autograd.Function):
+    """Tensor-core WKV7 followed by GroupNorm + bonus + gate as ONE node.  Both halves read ``r``, ``k`` and ``v``;
+    as separate nodes autograd sums their two gradients with three extra passes over ``[B, T, C]`` per layer.  Here
+    the normalisation backward writes its share first and the WKV7 chunk kernel adds its own in its output pass."""
+
+    @staticmethod
+    def forward(ctx, r, w, k, v, a, b, g, gn_w, gn_b, r_k, state, return_state: bool, eps: float):
+        B, T, C = r.shape
+        H = C // 64
+        r, w, k, v, a, b, g = (_c(t, BF16) for t in (r, w, k, v, a, b, g))
+        s0 = None if state is None else _c(state, torch.float32)
+        need_grad = any(ctx.needs_input_grad[:11])
+        NC = (T + 15) // 16
+        y = torch.empty(B, T, C, dtype=BF16, device=r.device)
+        cs = torch.empty(B, H, NC, 64, 64, dtype=BF16, device=r.device) if need_grad else None
+        s_final = torch.empty(B, H, 64, 64, dtype=torch.float32, device=r.device) if return_state else None
+        ws = _tc_ws(B, T, H, r.device)
+        call("rwkv_wkv7_tc_forward", ptr(r), ptr(w), ptr(k), ptr(v), ptr(a), ptr(b), ptr(s0), ptr(y), ptr(cs),
+             ptr(s_final), ptr(ws), i32(B), i32(T), i32(H), stream())
+        p = [_f32(gn_w), _f32(gn_b), _f32(r_k)]
+        z = torch.empty(B, T, C, dtype=BF16, device=r.device)
+        strip = _strip_for(T, B)
+        call("rwkv_gn_bonus_gate_forward", ptr(y), ptr(r), ptr(k), ptr(v), ptr(g), *(ptr(t) for t in p), ptr(z),
+             i32(B), i32(T), i32(C), i32(strip), f32(eps), stream())
+        if need_grad:
+            ctx.save_for_backward(r, w, k, v, a, b, g, y, cs, *p, *((ws,) if WKV7_KEEP_WORKSPACE else ()))
+        ctx.meta = (B, T, H, strip, eps, state is not None, (gn_w.shape, gn_b.shape, r_k.shape),
+                    (gn_w.dtype, gn_b.dtype, r_k.dtype))
+        return z, s_final
+
+    @staticmethod
+    def backward(ctx, dz, ds_final):
+        r, w, k, v, a, b, g, y, cs, gw, gb, rk, *kept = ctx.saved_tensors
+        B, T, H, strip, eps, has_state, shp, dts = ctx.meta
+        C = H * 64
+        dev = r.device
+        dzb = _c(dz, BF16)
+        dy, dr, dk, dv, dg = (torch.empty(B, T, C, dtype=BF16, device=dev) for _ in range(5))
+        n_cta = B * (-(-T // strip))
+        partials = torch.empty(n_cta, 3, C, dtype=torch.float32, device=dev)
+        call("rwkv_gn_bonus_gate_backward", ptr(dzb), ptr(y), ptr(r), ptr(k), ptr(v), ptr(g), ptr(gw), ptr(gb),
+             ptr(rk), ptr(dy), ptr(dr), ptr(dk), ptr(dv), ptr(dg), ptr(partials), i32(B), i32(T), i32(C), i32(strip),
+             f32(eps), stream())
+        ds_T = None if ds_final is None else _c(ds_final, torch.float32)
+        dw, da, db = (torch.empty(B, T, C, dtype=BF16, device=dev) for _ in range(3))
+        ds0 = torch.empty(B, H, 64, 64, dtype=torch.float32, device=dev) if has_state else None
+        dstates = torch.empty_like(cs)
+        ws = kept[0] if kept else _tc_ws(B, T, H, dev)
+        call("rwkv_wkv7_tc_backward", ptr(r), ptr(w), ptr(k), ptr(v), ptr(a), ptr(b), ptr(dy), ptr(cs), ptr(ds_T),
+             ptr(dstates), ptr(ws), i32(1 if kept else 0), ptr(dr), ptr(dw), ptr(dk), ptr(dv), ptr(da), ptr(db),
+             ptr(ds0), i32(1), i32(B), i32(T), i32(H), stream())
+        s = partials.sum(0)
+        return (dr, dw, dk, dv, da, db, dg, s[0].reshape(shp[0]).to(dts[0]), s[1].reshape(shp[1]).to(dts[1]),
+                s[2].reshape(shp[2]).to(dts[2]), ds0, None, None)
+
+
+def wkv7_gn(r, w, k, v, a, b, g, gn_w, gn_b, r_k, head_size: int = 64, state=None, return_state: bool = False,
+            eps: float = ref.GROUPNORM_EPS):
+    """``gn_bonus_gate(wkv7(r, w, k, v, a, b), r, k, v, g, ...)``; returns ``(z, final_state or None)``."""
+    use_tc = WKV7_IMPL == "tc" or (WKV7_IMPL == "auto" and r.shape[1] >= TC_MIN_T)
+    fusable = (use_tc and head_size == 64 and r.shape[-1] % 64 == 0 and torch.is_grad_enabled()
+               and all(t.dtype == BF16 for t in (r, w, k, v, a, b, g)))
+    if fusable:
+        return _WKV7GN.apply(r, w, k, v, a, b, g, gn_w, gn_b, r_k, state, return_state, eps)
+    y, s = wkv7(r, w, k, v, a, b, head_size, state, return_state)
+    return gn_bonus_gate(y, r, k, v, g, gn_w, gn_b, r_k, head_size, eps), s
 
 
 class _ReluSq(torch.autograd.Function):

@@ -520,3 +520,32 @@ def test_channel_mix_ffn_fused_node():
     (out_r * g).sum().backward()
     for name, a, b in zip(["dxk", "dwk", "dwv", "dres"], leaves_k, leaves_r):
         _close(a.grad, b.grad, 4e-2, 4e-2 * b.grad.abs().mean().item() + 1e-3, name)
+
+
+@pytest.mark.parametrize("with_state", [False, True])
+def test_wkv7_gn_fused_node_matches_reference(with_state):
+    B, T, H = 2, 80, 2
+    C = H * 64
+    ins = _wkv_inputs(B, T, H, seed=11)
+    torch.manual_seed(12)
+    g = torch.sigmoid(torch.randn(B, T, C, device="cuda")).to(BF)
+    gn_w = 1 + 0.1 * torch.randn(C, device="cuda")
+    gn_b = 0.1 * torch.randn(C, device="cuda")
+    r_k = 0.1 * torch.randn(H, 64, device="cuda")
+    s0 = (torch.randn(B, H, 64, 64, device="cuda") * 0.1) if with_state else None
+    lk = [t.clone().requires_grad_(True) for t in (*ins, g, gn_w, gn_b, r_k)]
+    lr = [t.float().clone().requires_grad_(True) for t in (*ins, g, gn_w, gn_b, r_k)]
+    sk = s0.clone().requires_grad_(True) if with_state else None
+    sr = s0.clone().requires_grad_(True) if with_state else None
+    z, sT = ops.wkv7_gn(*lk, 64, state=sk, return_state=True)
+    y_r, sT_r = ref.wkv7(*lr[:6], 64, sr)
+    z_r = ref.gn_bonus_gate(y_r, lr[0], lr[2], lr[3], lr[6], lr[7], lr[8], lr[9], 64)
+    assert _relnorm(z, z_r) < 2e-2 and _relnorm(sT, sT_r) < 1.5e-2
+    gz = torch.randn_like(z_r)
+    gs = torch.randn_like(sT_r) * 0.1
+    (z.float() * gz).sum().add((sT * gs).sum()).backward()
+    (z_r * gz).sum().add((sT_r * gs).sum()).backward()
+    for name, a_, b_ in zip(["dr", "dw", "dk", "dv", "da", "db", "dg", "dgn_w", "dgn_b", "dr_k"], lk, lr):
+        assert _relnorm(a_.grad, b_.grad) < 3e-2, (name, _relnorm(a_.grad, b_.grad))
+    if with_state:
+        assert _relnorm(sk.grad, sr.grad) < 2e-2
