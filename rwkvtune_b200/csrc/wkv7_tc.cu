@@ -399,19 +399,43 @@ wkv7_tc_scan_kernel(const bf16* __restrict__ v_, const unsigned char* __restrict
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk) acc_to_a(sa[kk], S[2 * kk], S[2 * kk + 1]);
 
-    float r0[4] = {0, 0, 0, 0}, r1[4] = {0, 0, 0, 0};   // R = S0 At^T + V Mka
+    // The chunk-to-chunk dependency runs  S -> R -> U -> S.  A dependent mma.sync costs its full latency, so every
+    // product on that path gets its own accumulator (summed with plain adds afterwards) and everything that does not
+    // depend on U (V Kb, V Mka, the Y terms) is issued off the path: three dependent products per chunk instead of eight.
+    float rp[5][2][4];                                   // R = S0 At^T (four k-steps) + V Mka, as independent partials
     float y0[4] = {0, 0, 0, 0}, y1[4] = {0, 0, 0, 0};   // Y = S0 Qt^T + U Pb + V Pk
 #pragma unroll
+    for (int i = 0; i < 5; ++i)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) rp[i][0][e] = rp[i][1][e] = 0.f;
+#pragma unroll
     for (int kk = 0; kk < 4; ++kk) {
-      mma16816(r0, sa[kk], bAt[kk][0], bAt[kk][1]);
-      mma16816(r1, sa[kk], bAt[kk][2], bAt[kk][3]);
+      mma16816(rp[kk][0], sa[kk], bAt[kk][0], bAt[kk][1]);
+      mma16816(rp[kk][1], sa[kk], bAt[kk][2], bAt[kk][3]);
+    }
+    mma16816(rp[4][0], va, bMka[0], bMka[1]);
+    mma16816(rp[4][1], va, bMka[2], bMka[3]);
+    float tk[8][4];                                      // V Kb: the part of the state update that does not need U
+#pragma unroll
+    for (int n2 = 0; n2 < 4; ++n2) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) tk[2 * n2][e] = tk[2 * n2 + 1][e] = 0.f;
+      mma16816(tk[2 * n2], va, bKb[n2][0], bKb[n2][1]);
+      mma16816(tk[2 * n2 + 1], va, bKb[n2][2], bKb[n2][3]);
+    }
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {
       mma16816(y0, sa[kk], bQt[kk][0], bQt[kk][1]);
       mma16816(y1, sa[kk], bQt[kk][2], bQt[kk][3]);
     }
-    mma16816(r0, va, bMka[0], bMka[1]);
-    mma16816(r1, va, bMka[2], bMka[3]);
     mma16816(y0, va, bPk[0], bPk[1]);
     mma16816(y1, va, bPk[2], bPk[3]);
+    float r0[4], r1[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      r0[e] = (rp[0][0][e] + rp[1][0][e]) + (rp[2][0][e] + rp[3][0][e]) + rp[4][0][e];
+      r1[e] = (rp[0][1][e] + rp[1][1][e]) + (rp[2][1][e] + rp[3][1][e]) + rp[4][1][e];
+    }
     uint32_t ra[4], ua[4];
     float u0[4] = {0, 0, 0, 0}, u1[4] = {0, 0, 0, 0};
     acc_to_a(ra, r0, r1);
@@ -426,12 +450,12 @@ wkv7_tc_scan_kernel(const bf16* __restrict__ v_, const unsigned char* __restrict
       const int n = 2 * n2;
       const float2 g0 = *reinterpret_cast<const float2*>(&s.gL[n * 8 + tq * 2]);
       const float2 g1 = *reinterpret_cast<const float2*>(&s.gL[(n + 1) * 8 + tq * 2]);
-      S[n][0] *= g0.x; S[n][1] *= g0.y; S[n][2] *= g0.x; S[n][3] *= g0.y;
-      S[n + 1][0] *= g1.x; S[n + 1][1] *= g1.y; S[n + 1][2] *= g1.x; S[n + 1][3] *= g1.y;
+      S[n][0] = S[n][0] * g0.x + tk[n][0]; S[n][1] = S[n][1] * g0.y + tk[n][1];
+      S[n][2] = S[n][2] * g0.x + tk[n][2]; S[n][3] = S[n][3] * g0.y + tk[n][3];
+      S[n + 1][0] = S[n + 1][0] * g1.x + tk[n + 1][0]; S[n + 1][1] = S[n + 1][1] * g1.y + tk[n + 1][1];
+      S[n + 1][2] = S[n + 1][2] * g1.x + tk[n + 1][2]; S[n + 1][3] = S[n + 1][3] * g1.y + tk[n + 1][3];
       mma16816(S[n], ua, bBb[n2][0], bBb[n2][1]);
       mma16816(S[n + 1], ua, bBb[n2][2], bBb[n2][3]);
-      mma16816(S[n], va, bKb[n2][0], bKb[n2][1]);
-      mma16816(S[n + 1], va, bKb[n2][2], bKb[n2][3]);
     }
     // y of this warp's 16 value rows: transpose through the warp's own buffer, 16-byte stores
     __syncwarp();
@@ -533,14 +557,33 @@ wkv7_tc_bwd_scan_kernel(const bf16* __restrict__ dy_, const unsigned char* __res
     uint32_t dsa[4][4];
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk) acc_to_a(dsa[kk], S[2 * kk], S[2 * kk + 1]);
-    float u0[4] = {0, 0, 0, 0}, u1[4] = {0, 0, 0, 0};   // dU = dY Pb^T + dS Bb^T
+    // same latency argument as in the forward scan: independent accumulators on the dS -> dU -> dR -> dS path
+    float up[5][2][4];                                   // dU = dS Bb^T (four k-steps) + dY Pb^T
+#pragma unroll
+    for (int i = 0; i < 5; ++i)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) up[i][0][e] = up[i][1][e] = 0.f;
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk) {
-      mma16816(u0, dsa[kk], bBb[kk][0], bBb[kk][1]);
-      mma16816(u1, dsa[kk], bBb[kk][2], bBb[kk][3]);
+      mma16816(up[kk][0], dsa[kk], bBb[kk][0], bBb[kk][1]);
+      mma16816(up[kk][1], dsa[kk], bBb[kk][2], bBb[kk][3]);
     }
-    mma16816(u0, dya, bPb[0], bPb[1]);
-    mma16816(u1, dya, bPb[2], bPb[3]);
+    mma16816(up[4][0], dya, bPb[0], bPb[1]);
+    mma16816(up[4][1], dya, bPb[2], bPb[3]);
+    float tq_[8][4];                                     // dY Qt: independent of dR
+#pragma unroll
+    for (int n2 = 0; n2 < 4; ++n2) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) tq_[2 * n2][e] = tq_[2 * n2 + 1][e] = 0.f;
+      mma16816(tq_[2 * n2], dya, bQt[n2][0], bQt[n2][1]);
+      mma16816(tq_[2 * n2 + 1], dya, bQt[n2][2], bQt[n2][3]);
+    }
+    float u0[4], u1[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      u0[e] = (up[0][0][e] + up[1][0][e]) + (up[2][0][e] + up[3][0][e]) + up[4][0][e];
+      u1[e] = (up[0][1][e] + up[1][1][e]) + (up[2][1][e] + up[3][1][e]) + up[4][1][e];
+    }
     uint32_t dua[4], dra[4];
     acc_to_a(dua, u0, u1);
     float r0[4] = {0, 0, 0, 0}, r1[4] = {0, 0, 0, 0};   // dR = dU Tinv^T
@@ -553,10 +596,10 @@ wkv7_tc_bwd_scan_kernel(const bf16* __restrict__ dy_, const unsigned char* __res
       const int n = 2 * n2;
       const float2 g0 = *reinterpret_cast<const float2*>(&s.gL[n * 8 + tq * 2]);
       const float2 g1 = *reinterpret_cast<const float2*>(&s.gL[(n + 1) * 8 + tq * 2]);
-      S[n][0] *= g0.x; S[n][1] *= g0.y; S[n][2] *= g0.x; S[n][3] *= g0.y;
-      S[n + 1][0] *= g1.x; S[n + 1][1] *= g1.y; S[n + 1][2] *= g1.x; S[n + 1][3] *= g1.y;
-      mma16816(S[n], dya, bQt[n2][0], bQt[n2][1]);
-      mma16816(S[n + 1], dya, bQt[n2][2], bQt[n2][3]);
+      S[n][0] = S[n][0] * g0.x + tq_[n][0]; S[n][1] = S[n][1] * g0.y + tq_[n][1];
+      S[n][2] = S[n][2] * g0.x + tq_[n][2]; S[n][3] = S[n][3] * g0.y + tq_[n][3];
+      S[n + 1][0] = S[n + 1][0] * g1.x + tq_[n + 1][0]; S[n + 1][1] = S[n + 1][1] * g1.y + tq_[n + 1][1];
+      S[n + 1][2] = S[n + 1][2] * g1.x + tq_[n + 1][2]; S[n + 1][3] = S[n + 1][3] * g1.y + tq_[n + 1][3];
       mma16816(S[n], dra, bAt[n2][0], bAt[n2][1]);
       mma16816(S[n + 1], dra, bAt[n2][2], bAt[n2][3]);
     }
