@@ -508,6 +508,140 @@ ln_shift_mix_bwd_v4_kernel(const DOutPtrs dO, const bf16* __restrict__ dlast, co
   }
 }
 
+// K = 1 (channel mix): two rows per block reduction.  The single-output backward is bound by the round trip of one
+// row's tiles plus one barrier; handling rows t and t-1 together halves the barriers and doubles the bytes in flight.
+__global__ void __launch_bounds__(512, 2)
+ln_shift_mix_bwd1_pair_kernel(const bf16* __restrict__ dO, const bf16* __restrict__ dlast, const bf16* __restrict__ dres,
+                              const bf16* __restrict__ x, const float* __restrict__ mean_in,
+                              const float* __restrict__ rstd_in, const float* __restrict__ ln_w,
+                              const float* __restrict__ ln_b, const float* __restrict__ mix,
+                              const bf16* __restrict__ prev, bf16* __restrict__ dx, float* __restrict__ dprev,
+                              float* __restrict__ partials, int B, int T, int C, int strip) {
+  __shared__ float red[2 * EW_MAX_WARPS * 4];
+  int phase = 0;
+  const int b = blockIdx.y, t0 = blockIdx.x * strip, t1 = min(T, t0 + strip);
+  const int col = threadIdx.x * 4;
+  const bool active = col < C;
+  const size_t row0 = (size_t)b * T;
+  const float invC = 1.f / C;
+  auto ld4 = [](const bf16* p) { return *reinterpret_cast<const uint2*>(p); };
+  const uint2 z2 = make_uint2(0u, 0u);
+
+  float w[4] = {0, 0, 0, 0}, bb[4] = {0, 0, 0, 0}, mu[4] = {0, 0, 0, 0};
+  float acc_mu[4] = {0, 0, 0, 0}, acc_w[4] = {0, 0, 0, 0}, acc_b[4] = {0, 0, 0, 0}, carry[4] = {0, 0, 0, 0};
+  if (active) {
+    load4f(ln_w + col, w);
+    load4f(ln_b + col, bb);
+    load4f(mix + col, mu);
+    if (t1 < T) {
+      float g[4];
+      unpack4(ld4(dO + (row0 + t1) * C + col), g);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) carry[e] = g[e] * mu[e];
+    } else if (dlast) {
+      unpack4(ld4(dlast + (size_t)b * C + col), carry);
+    }
+  }
+  struct Raw { uint2 x; float m, r; };
+  auto fetch_row = [&](int t) {          // rows below t0 - 1 are never used
+    Raw q{z2, 0.f, 0.f};
+    if (t < t0 - 1) return q;
+    if (t >= 0) {
+      q.x = active ? ld4(x + (row0 + t) * C + col) : z2;
+      q.m = mean_in[row0 + t];
+      q.r = rstd_in[row0 + t];
+    } else if (prev && active) {
+      q.x = ld4(prev + (size_t)b * C + col);
+    }
+    return q;
+  };
+  auto h_of = [&](int t, const Raw& q, float* xh, float* h) {
+    float xf[4];
+    unpack4(q.x, xf);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      xh[e] = t < 0 ? 0.f : (xf[e] - q.m) * q.r;
+      h[e] = t < 0 ? xf[e] : round_bf16(xh[e] * w[e] + bb[e]);
+    }
+  };
+  auto fetch_g = [&](int t) { return (active && t >= t0) ? ld4(dO + (row0 + t) * C + col) : z2; };
+
+  uint2 gA = fetch_g(t1 - 1), gB = fetch_g(t1 - 2);
+  float xh_a[4], h_a[4];
+  h_of(t1 - 1, fetch_row(t1 - 1), xh_a, h_a);
+  Raw raw1 = fetch_row(t1 - 2), raw2 = fetch_row(t1 - 3);
+  for (int t = t1 - 1; t >= t0; t -= 2) {
+    const bool two = t - 1 >= t0;
+    float xh_b[4], h_b[4], xh_c[4], h_c[4];
+    h_of(t - 1, raw1, xh_b, h_b);
+    h_of(t - 2, raw2, xh_c, h_c);
+    const uint2 gA_c = gA, gB_c = gB;
+    if (t - 2 >= t0) {      // next pair's tiles are in flight during this pair's reduction
+      gA = fetch_g(t - 2);
+      gB = fetch_g(t - 3);
+      raw1 = fetch_row(t - 3);
+      raw2 = fetch_row(t - 4);
+    }
+    float ga[4], gb[4], dh_a[4], dh_b[4], nc[4];
+    unpack4(gA_c, ga);
+    unpack4(gB_c, gb);
+    float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float ca = ga[e] * mu[e];
+      dh_a[e] = carry[e] + ga[e] - ca;
+      acc_mu[e] += ga[e] * (h_b[e] - h_a[e]);
+      const float cb = gb[e] * mu[e];
+      dh_b[e] = ca + gb[e] - cb;
+      nc[e] = two ? cb : ca;
+      if (two) acc_mu[e] += gb[e] * (h_c[e] - h_b[e]);
+      const float wa = dh_a[e] * w[e];
+      c[0] += wa;
+      c[1] += wa * xh_a[e];
+      acc_w[e] += dh_a[e] * xh_a[e];
+      acc_b[e] += dh_a[e];
+      if (two) {
+        const float wb = dh_b[e] * w[e];
+        c[2] += wb;
+        c[3] += wb * xh_b[e];
+        acc_w[e] += dh_b[e] * xh_b[e];
+        acc_b[e] += dh_b[e];
+      }
+    }
+    block_sum<4>(c, red, phase);
+    if (active) {
+      auto emit = [&](int tt, const float* dh, const float* xh, float s0, float s1) {
+        const float r = rstd_in[row0 + tt];
+        float o[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[e] = r * (dh[e] * w[e] - s0 * invC - xh[e] * s1 * invC);
+        if (dres) {
+          float rr[4];
+          unpack4(ld4(dres + (row0 + tt) * C + col), rr);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) o[e] += rr[e];
+        }
+        *reinterpret_cast<uint2*>(dx + (row0 + tt) * C + col) = pack4(o);
+      };
+      emit(t, dh_a, xh_a, c[0], c[1]);
+      if (two) emit(t - 1, dh_b, xh_b, c[2], c[3]);
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      carry[e] = nc[e];
+      xh_a[e] = xh_c[e];
+      h_a[e] = h_c[e];
+    }
+  }
+  if (active) {
+    if (dprev && t0 == 0) store4f(dprev + (size_t)b * C + col, carry);
+    float* p = partials + ((size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 3) * C + col;
+    store4f(p, acc_mu);
+    store4f(p + (size_t)C, acc_w);
+    store4f(p + (size_t)2 * C, acc_b);
+  }
+}
+
 inline int threads_for(int C) { return ((C / 8 + 31) / 32) * 32; }
 
 }  // namespace
@@ -559,7 +693,11 @@ RWKV_EXPORT int rwkv_ln_shift_mix_backward(const void* const* dO, const void* dl
       (float*)partials, B, T, C, strip)
   if (C / 4 <= 512) {   // four channels per thread with row prefetch
     if (K == 6) LAUNCH_V4(6);
-    else LAUNCH_V4(1);
+    else
+      ln_shift_mix_bwd1_pair_kernel<<<grid, ((C / 4 + 31) / 32) * 32, 0, st>>>(
+          dptrs.p[0], (const bf16*)dlast, (const bf16*)dres, (const bf16*)x, (const float*)mean, (const float*)rstd,
+          (const float*)ln_w, (const float*)ln_b, (const float*)mix, (const bf16*)prev, (bf16*)dx, (float*)dprev,
+          (float*)partials, B, T, C, strip);
   } else if (K == 6) LAUNCH(6);
   else if (K == 1) LAUNCH(1);
   else return RWKV_ERR_BAD_SHAPE;
