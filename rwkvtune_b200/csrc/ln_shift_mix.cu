@@ -438,6 +438,7 @@ ln_shift_mix_bwd_v4_kernel(const DOutPtrs dO, const bf16* __restrict__ dlast, co
   float xh_cur[4], h_cur[4], xh_prev[4], h_prev[4];
   fetch_x(t1 - 1);
   h_from_fetched(t1 - 1, xh_cur, h_cur);
+  float r_cur = rq, r_prev = 0.f;     // rstd of the row being finished, kept in a register (no load after the barrier)
   fetch(t1 - 1);
   fetch_x(t1 - 2);
   for (int t = t1 - 1; t >= t0; --t) {
@@ -445,6 +446,7 @@ ln_shift_mix_bwd_v4_kernel(const DOutPtrs dO, const bf16* __restrict__ dlast, co
 #pragma unroll
     for (int k = 0; k < K; ++k) gc[k] = gq[k];
     h_from_fetched(t - 1, xh_prev, h_prev);
+    r_prev = rq;
     if (t - 1 >= t0) {   // next row's tiles are in flight during this row's reduction
       fetch(t - 1);
       fetch_x(t - 2);
@@ -479,7 +481,7 @@ ln_shift_mix_bwd_v4_kernel(const DOutPtrs dO, const bf16* __restrict__ dlast, co
     }
     block_sum<2>(c, red, phase);
     if (active) {
-      const float r = rstd_in[row0 + t];
+      const float r = r_cur;
       float o[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) o[e] = r * (dh[e] * w[e] - c[0] * invC - xh_cur[e] * c[1] * invC);
@@ -497,6 +499,7 @@ ln_shift_mix_bwd_v4_kernel(const DOutPtrs dO, const bf16* __restrict__ dlast, co
       xh_cur[e] = xh_prev[e];
       h_cur[e] = h_prev[e];
     }
+    r_cur = r_prev;
   }
   if (active) {
     if (dprev && t0 == 0) store4f(dprev + (size_t)b * C + col, carry);
