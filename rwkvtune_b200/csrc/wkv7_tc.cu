@@ -15,15 +15,17 @@
 // Kernels:
 //   prep        one CTA per chunk (full occupancy): everything that does not depend on the carried
 //               state - cumulative decays, scaled operands, the 16x16 matrices, the inverse - written
-//               to a workspace.
+//               to a workspace (10.5 KB per chunk) that the forward scan AND, if the caller keeps it,
+//               both backward kernels read.
 //   fwd scan    one CTA per (batch, head), warp w owns state rows [16w, 16w+16) as accumulator
 //               fragments; walks the chunks issuing only tensor-core products on operands prefetched
 //               with cp.async; stores the bf16 state at the start of every chunk for the backward.
 //   bwd scan    the same walk in reverse for dS:  dU = dY Pb^T + dS Bb^T,  dR = dU Tinv^T,
 //               dS0 = dY Qt + dS diag(gamma_L) + dR At;  stores dS at the end of every chunk (bf16).
-//   bwd chunk   one CTA per chunk (full occupancy): recomputes R, U from the saved chunk-start state
-//               and forms all six input gradients from the transposed products.  It never inverts the
-//               recurrence.  The decay gradient is the reverse cumulative sum over t of d(log gamma_t).
+//   bwd chunk   one CTA per chunk (three per SM): loads the workspace operands, recomputes R, U from the
+//               saved chunk-start state and forms all six input gradients from the transposed products
+//               (optionally adding them to gradients already in the output buffers).  It never inverts
+//               the recurrence.  The decay gradient is the reverse cumulative sum over t of d(log gamma_t).
 //
 // These small dependent products are issued with mma.sync from registers: tcgen05 needs operands in
 // shared memory and results read back from tensor memory between every dependent product, which costs
