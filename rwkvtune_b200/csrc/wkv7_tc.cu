@@ -323,7 +323,6 @@ struct ScanStage {
 };
 struct ScanSm {
   ScanStage st[STAGES];
-  float ybuf[4][L][L + 1];   // per warp: [t][v_local]
 };
 
 __global__ void __launch_bounds__(NT)
@@ -397,6 +396,9 @@ wkv7_tc_scan_kernel(const bf16* __restrict__ v_, const unsigned char* __restrict
       load_b_t(bBb[n2], &s.Bb[0][0], LDS_, 0, n2 * 16, lane);
       load_b_t(bKb[n2], &s.Kb[0][0], LDS_, 0, n2 * 16, lane);
     }
+    float2 gl[8];          // decay of this thread's state columns, read with the other operands (no load on the path)
+#pragma unroll
+    for (int n = 0; n < 8; ++n) gl[n] = *reinterpret_cast<const float2*>(&s.gL[n * 8 + tq * 2]);
     uint32_t sa[4][4];
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk) acc_to_a(sa[kk], S[2 * kk], S[2 * kk + 1]);
@@ -450,8 +452,7 @@ wkv7_tc_scan_kernel(const bf16* __restrict__ v_, const unsigned char* __restrict
 #pragma unroll
     for (int n2 = 0; n2 < 4; ++n2) {
       const int n = 2 * n2;
-      const float2 g0 = *reinterpret_cast<const float2*>(&s.gL[n * 8 + tq * 2]);
-      const float2 g1 = *reinterpret_cast<const float2*>(&s.gL[(n + 1) * 8 + tq * 2]);
+      const float2 g0 = gl[n], g1 = gl[n + 1];
       S[n][0] = S[n][0] * g0.x + tk[n][0]; S[n][1] = S[n][1] * g0.y + tk[n][1];
       S[n][2] = S[n][2] * g0.x + tk[n][2]; S[n][3] = S[n][3] * g0.y + tk[n][3];
       S[n + 1][0] = S[n + 1][0] * g1.x + tk[n + 1][0]; S[n + 1][1] = S[n + 1][1] * g1.y + tk[n + 1][1];
@@ -459,22 +460,15 @@ wkv7_tc_scan_kernel(const bf16* __restrict__ v_, const unsigned char* __restrict
       mma16816(S[n], ua, bBb[n2][0], bBb[n2][1]);
       mma16816(S[n + 1], ua, bBb[n2][2], bBb[n2][3]);
     }
-    // y of this warp's 16 value rows: transpose through the warp's own buffer, 16-byte stores
-    __syncwarp();
+    // y of this warp's 16 value rows: element (v, t) of the accumulator goes to y[t][v].  Sixteen lanes with the same t
+    // write one 32-byte sector between them, so the scattered 2-byte stores stay sector-efficient and nothing on the
+    // in-order instruction stream waits for a shared-memory round trip.
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      const int vl = g + (e >> 1) * 8;
-      sm.ybuf[warp][tq * 2 + (e & 1)][vl] = y0[e];
-      sm.ybuf[warp][8 + tq * 2 + (e & 1)][vl] = y1[e];
-    }
-    __syncwarp();
-    {
-      const int tl = lane >> 1, hf = lane & 1;
-      const int t = c * L + tl;
-      float f[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) f[i] = sm.ybuf[warp][tl][hf * 8 + i];
-      if (t < T) *reinterpret_cast<uint4*>(y_ + base + (size_t)t * tok_stride + m0 + hf * 8) = pack8(f);
+      const int vrow = m0 + g + (e >> 1) * 8;
+      const int ta = c * L + tq * 2 + (e & 1), tb = ta + 8;
+      if (ta < T) y_[base + (size_t)ta * tok_stride + vrow] = __float2bfloat16_rn(y0[e]);
+      if (tb < T) y_[base + (size_t)tb * tok_stride + vrow] = __float2bfloat16_rn(y1[e]);
     }
   }
   if (s_final) store_state_f32(S, s_final + ((size_t)bb * H + h) * N * N, m0, g, tq);
@@ -556,6 +550,9 @@ wkv7_tc_bwd_scan_kernel(const bf16* __restrict__ dy_, const unsigned char* __res
       load_b_t(bQt[n2], &s.Qt[0][0], LDS_, 0, n2 * 16, lane);
       load_b_t(bAt[n2], &s.At[0][0], LDS_, 0, n2 * 16, lane);
     }
+    float2 gl[8];
+#pragma unroll
+    for (int n = 0; n < 8; ++n) gl[n] = *reinterpret_cast<const float2*>(&s.gL[n * 8 + tq * 2]);
     uint32_t dsa[4][4];
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk) acc_to_a(dsa[kk], S[2 * kk], S[2 * kk + 1]);
@@ -596,8 +593,7 @@ wkv7_tc_bwd_scan_kernel(const bf16* __restrict__ dy_, const unsigned char* __res
 #pragma unroll
     for (int n2 = 0; n2 < 4; ++n2) {
       const int n = 2 * n2;
-      const float2 g0 = *reinterpret_cast<const float2*>(&s.gL[n * 8 + tq * 2]);
-      const float2 g1 = *reinterpret_cast<const float2*>(&s.gL[(n + 1) * 8 + tq * 2]);
+      const float2 g0 = gl[n], g1 = gl[n + 1];
       S[n][0] = S[n][0] * g0.x + tq_[n][0]; S[n][1] = S[n][1] * g0.y + tq_[n][1];
       S[n][2] = S[n][2] * g0.x + tq_[n][2]; S[n][3] = S[n][3] * g0.y + tq_[n][3];
       S[n + 1][0] = S[n + 1][0] * g1.x + tq_[n + 1][0]; S[n + 1][1] = S[n + 1][1] * g1.y + tq_[n + 1][1];
