@@ -27,13 +27,15 @@ def _c(t: torch.Tensor, dtype=None) -> torch.Tensor:
 # =============================================================================== WKV7
 class _WKV7(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, r, w, k, v, a, b, state, return_state: bool):
+    def forward(ctx, r, w, k, v, a, b, state, return_state: bool, track: bool = True):
         B, T, C = r.shape
         H = C // 64
         out_dtype = r.dtype
         r, w, k, v, a, b = (_c(t, BF16) for t in (r, w, k, v, a, b))
         s0 = None if state is None else _c(state, torch.float32)
-        need_grad = any(ctx.needs_input_grad[:7])
+        # `track` is the caller's grad mode (inside forward it is always off): under no_grad nothing is saved, even
+        # when the inputs derive from parameters that require grad (rollouts with the training model)
+        need_grad = track and any(ctx.needs_input_grad[:7])
         y = torch.empty(B, T, C, dtype=BF16, device=r.device)
         NC = (T + 15) // 16
         sa = torch.empty(B, T, C, dtype=torch.float32, device=r.device) if need_grad else None
@@ -66,7 +68,7 @@ class _WKV7(torch.autograd.Function):
              ptr(ds_T), *(ptr(g) for g in grads), ptr(ds0), i32(B), i32(T), i32(H), stream())
         if ctx.out_dtype != BF16:
             grads = [g.to(ctx.out_dtype) for g in grads]
-        return (*grads, ds0, None)
+        return (*grads, ds0, None, None)
 
 
 def _tc_ws(B, T, H, device):
@@ -79,13 +81,15 @@ class _WKV7TC(torch.autograd.Function):
     backward recomputes the intra-chunk quantities from the inputs and those states."""
 
     @staticmethod
-    def forward(ctx, r, w, k, v, a, b, state, return_state: bool):
+    def forward(ctx, r, w, k, v, a, b, state, return_state: bool, track: bool = True):
         B, T, C = r.shape
         H = C // 64
         out_dtype = r.dtype
         r, w, k, v, a, b = (_c(t, BF16) for t in (r, w, k, v, a, b))
         s0 = None if state is None else _c(state, torch.float32)
-        need_grad = any(ctx.needs_input_grad[:7])
+        # `track` is the caller's grad mode (inside forward it is always off): under no_grad nothing is saved, even
+        # when the inputs derive from parameters that require grad (rollouts with the training model)
+        need_grad = track and any(ctx.needs_input_grad[:7])
         NC = (T + 15) // 16
         y = torch.empty(B, T, C, dtype=BF16, device=r.device)
         cs = torch.empty(B, H, NC, 64, 64, dtype=BF16, device=r.device) if need_grad else None
@@ -118,7 +122,7 @@ class _WKV7TC(torch.autograd.Function):
              i32(H), stream())
         if ctx.out_dtype != BF16:
             grads = [g.to(ctx.out_dtype) for g in grads]
-        return (*grads, ds0, None)
+        return (*grads, ds0, None, None)
 
 
 # "auto": tensor-core chunked kernels from TC_MIN_T steps up, the step-by-step kernels below (decode, short
@@ -135,7 +139,7 @@ def wkv7(r, w, k, v, a, b, head_size: int = 64, state: Optional[torch.Tensor] = 
         raise ValueError("channel count must be a multiple of 64")
     use_tc = WKV7_IMPL == "tc" or (WKV7_IMPL == "auto" and r.shape[1] >= TC_MIN_T)
     fn = _WKV7TC if use_tc else _WKV7
-    y, s = fn.apply(r, w, k, v, a, b, state, return_state)
+    y, s = fn.apply(r, w, k, v, a, b, state, return_state, torch.is_grad_enabled())
     return y, s
 
 
