@@ -204,7 +204,8 @@ template <bool A_MN, bool B_MN, int EPI, bool AG>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const __grid_constant__ CUtensorMap map_c, int M, int N, int K, int* status,
-                    const bf16* __restrict__ c_in, long long ldc, const __grid_constant__ AgParams ag) {
+                    const bf16* __restrict__ c_in, long long ldc, int splits, float* __restrict__ partial,
+                    const __grid_constant__ AgParams ag) {
   if (AG && (int)blockIdx.x < ag.n_copy) {   // copy CTAs never touch barriers or tensor memory
     ag_copy_role(ag, N, K);
     return;
@@ -222,6 +223,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_n;
   const int num_kb = (K + BK - 1) / BK;
+  // split-K (splits > 1): a work item is (tile, K slice); the slice's fp32 tile goes to `partial[slice]` and a small
+  // kernel sums the slices.  For products with few output tiles and a long contraction (weight gradients of the
+  // low-rank maps: 16 tiles, K = tokens) this is what fills the SMs.  splits == 1 is the plain path.
+  const int num_items = num_tiles * splits;
+  auto kb_range = [&](int sp, int& lo, int& hi) {
+    lo = (int)((long long)num_kb * sp / splits);
+    hi = (int)((long long)num_kb * (sp + 1) / splits);
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&bars->full[s], 1); mbar_init(&bars->empty[s], 1); }
@@ -245,9 +254,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = cta; tile < num_tiles && ok; tile += n_cta) {
+      for (int item = cta; item < num_items && ok; item += n_cta) {
+        const int tile = item / splits;
         const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        int kb_lo, kb_hi;
+        kb_range(item - tile * splits, kb_lo, kb_hi);
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
           int k0 = kb * BK;
           if (AG) {   // contraction walked panel by panel, starting with the locally owned one
             const int kb_per_panel = ag.Kp / BK;
@@ -299,13 +311,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       uint32_t phase = 0;
       int local = 0;
       bool ok = true;
-      for (int tile = cta; tile < num_tiles && ok; tile += n_cta, ++local) {
+      for (int item = cta; item < num_items && ok; item += n_cta, ++local) {
         const int acc = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1;
         if (!mbar_wait(&bars->acc_empty[acc], acc_phase ^ 1, bars, status, 102)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        int kb_lo, kb_hi;
+        kb_range(item % splits, kb_lo, kb_hi);
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
           if (!mbar_wait(&bars->full[stage], phase, bars, status, 103)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = base + stage * STAGE_BYTES, sb = sa + A_BYTES;
@@ -313,7 +327,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           const uint64_t bdesc = make_smem_desc(sb, b_lbo, 1024 >> 4);
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k)
-            umma_f16(d_tmem, adesc + (uint64_t)(k * a_adv), bdesc + (uint64_t)(k * b_adv), idesc, (kb | k) ? 1u : 0u);
+            umma_f16(d_tmem, adesc + (uint64_t)(k * a_adv), bdesc + (uint64_t)(k * b_adv), idesc,
+                     ((kb - kb_lo) | k) ? 1u : 0u);
           umma_commit(&bars->empty[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -327,7 +342,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     int local = 0;
     int cbuf = 0;
     bool ok = true;
-    for (int tile = cta; tile < num_tiles && ok; tile += n_cta, ++local) {
+    for (int item = cta; item < num_items && ok; item += n_cta, ++local) {
+      const int tile = item / splits, sp = item - tile * splits;
       const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
@@ -354,6 +370,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           }
         }
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (splits > 1) {   // fp32 slice tile straight from the registers: 256 contiguous bytes per thread and chunk
+          const long long gm = m0 + row;
+          if (gm < M) {
+            float* dst = partial + ((size_t)sp * M + gm) * N + n0 + chunk * 64;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int col = j * 4;
+              if (n0 + chunk * 64 + col < N) {
+                const uint32_t* v = col < 32 ? &v0[col] : &v1[col - 32];
+                *reinterpret_cast<float4*>(dst + col) = make_float4(__uint_as_float(v[0]), __uint_as_float(v[1]),
+                                                                    __uint_as_float(v[2]), __uint_as_float(v[3]));
+              }
+            }
+          }
+          continue;
+        }
         // the staging buffer we are about to overwrite must have been read by its TMA store
         if (threadIdx.x == 64) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
         asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -449,7 +481,45 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, 
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int grid = tiles < sms ? tiles : sms;
   AgParams none = {};
-  kern<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(ma, mb, mc, M, N, K, status, c_in, ldc, none);
+  kern<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(ma, mb, mc, M, N, K, status, c_in, ldc, 1, nullptr, none);
+  return rwkv_launch_status();
+}
+
+// Sums the `splits` fp32 slice tiles of a split-K product and writes bf16 C.
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(const float* __restrict__ partial, bf16* __restrict__ c, int M, int N, long long ldc, int splits) {
+  const long long n4 = N / 4;
+  const long long total = (long long)M * n4;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long m = i / n4;
+    const int n = (int)(i - m * n4) * 4;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int sp = 0; sp < splits; ++sp) {
+      const float4 v = *reinterpret_cast<const float4*>(partial + ((size_t)sp * M + m) * N + n);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    *reinterpret_cast<uint2*>(c + m * ldc + n) = make_uint2(pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w));
+  }
+}
+
+template <bool A_MN, bool B_MN>
+int launch_splitk(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, int M, int N, int K, int* status,
+                  int sms, int splits, float* partial, bf16* c, long long ldc, cudaStream_t st) {
+  auto kern = gemm_tcgen05_kernel<A_MN, B_MN, 0, false>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return RWKV_ERR_CUDA_BASE + (int)e;
+    configured = true;
+  }
+  const int items = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * splits;
+  const int grid = items < sms ? items : sms;
+  AgParams none = {};
+  kern<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(ma, mb, mc, M, N, K, status, nullptr, 0, splits, partial, none);
+  const long long total = (long long)M * (N / 4);
+  long long blocks = (total + 255) / 256;
+  if (blocks > sms * 8) blocks = sms * 8;
+  splitk_reduce_kernel<<<(unsigned)blocks, 256, 0, st>>>(partial, c, M, N, ldc, splits);
   return rwkv_launch_status();
 }
 
@@ -469,7 +539,9 @@ int launch_ag(CUtensorMap ma, CUtensorMap mb, CUtensorMap mc, int M, int N, int 
   // GEMM CTAs wait for copy CTAs of the same grid: a cooperative launch guarantees they are co-resident
   const bf16* c_in = nullptr;
   long long ldc = 0;
-  void* args[] = {&ma, &mb, &mc, &M, &N, &K, &status, &c_in, &ldc, &ag};
+  int splits = 1;
+  float* partial = nullptr;
+  void* args[] = {&ma, &mb, &mc, &M, &N, &K, &status, &c_in, &ldc, &splits, &partial, &ag};
   cudaError_t e = cudaLaunchCooperativeKernel((void*)kern, dim3(grid), dim3(NUM_THREADS), args, SMEM_BYTES, st);
   return e == cudaSuccess ? rwkv_launch_status() : RWKV_ERR_CUDA_BASE + (int)e;
 }
@@ -518,6 +590,39 @@ RWKV_EXPORT int rwkv_gemm_bf16_tcgen05(const void* a, const void* b, void* c, in
   if (a_mn && b_mn) return DISPATCH(true, true);
   return DISPATCH(true, false);
 #undef DISPATCH
+}
+
+// Split-K variant of rwkv_gemm_bf16_tcgen05 (no epilogue): the contraction is cut into `splits` slices
+// (1 < splits <= ceil(K / 64)), each (tile, slice) is one work item; `workspace` holds splits * M * N floats.
+// N must be a multiple of 8.  For products with few output tiles and a long contraction.
+RWKV_EXPORT int rwkv_gemm_bf16_tcgen05_splitk(const void* a, const void* b, void* c, int M, int N, int K, long long lda,
+                                              long long ldb, long long ldc, int a_mn, int b_mn, int splits,
+                                              void* workspace, void* status, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || (N & 7) || splits < 2 || splits > (K + BK - 1) / BK || !workspace)
+    return RWKV_ERR_BAD_SHAPE;
+  if ((uintptr_t)workspace & 15) return RWKV_ERR_BAD_ALIGNMENT;
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  CUtensorMap ma, mb, mc;
+  int r;
+  r = a_mn ? make_map(&ma, a, K, M, lda, 64, BK) : make_map(&ma, a, M, K, lda, BK, BM);
+  if (r) return r;
+  r = b_mn ? make_map(&mb, b, K, N, ldb, 64, BK) : make_map(&mb, b, N, K, ldb, BK, BN);
+  if (r) return r;
+  r = make_map(&mc, c, M, N, ldc, 64, BM);
+  if (r) return r;
+  cudaStream_t st = (cudaStream_t)stream;
+  int* sp = (int*)status;
+  float* ws = (float*)workspace;
+  bf16* cp = (bf16*)c;
+  if (!a_mn && !b_mn) return launch_splitk<false, false>(ma, mb, mc, M, N, K, sp, sms, splits, ws, cp, ldc, st);
+  if (!a_mn && b_mn) return launch_splitk<false, true>(ma, mb, mc, M, N, K, sp, sms, splits, ws, cp, ldc, st);
+  if (a_mn && b_mn) return launch_splitk<true, true>(ma, mb, mc, M, N, K, sp, sms, splits, ws, cp, ldc, st);
+  return launch_splitk<true, false>(ma, mb, mc, M, N, K, sp, sms, splits, ws, cp, ldc, st);
 }
 
 // y[M,N] = x[M,K] @ W[N,K]^T where W is stored as `world` K-panels, panel p ([N, K/world], row-major) living at

@@ -93,8 +93,12 @@ def addmm_tn_(y: torch.Tensor, a: torch.Tensor, b: torch.Tensor) -> torch.Tensor
 
 def mm_tn(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     n = _native()
-    if n is not None and n.native_ok(a, b, "tn"):
-        return n.mm_tn(a, b)
+    if n is not None:
+        if n.native_ok(a, b, "tn"):
+            return n.mm_tn(a, b)
+        splits = n.splitk_plan(a, b)
+        if splits:
+            return n.mm_tn_splitk(a, b, splits)
     return a.t() @ b
 
 

@@ -92,6 +92,40 @@ def mm_tn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor = None) -> torch.T
     return _run(a, b, a.shape[1], b.shape[1], a.shape[0], 1, 1, 0, out)
 
 
+_SPLITK_WS = {}
+SPLITK_MIN_K = 8192
+
+
+def splitk_plan(a: torch.Tensor, b: torch.Tensor) -> int:
+    """Number of K slices for ``a[Kc,M]^T @ b[Kc,N]`` when it has few output tiles and a long contraction (the weight
+    gradients of the low-rank maps: 8-16 tiles, Kc = tokens); 0 when the product is not of that kind."""
+    if not (_rows_ok(a) and _rows_ok(b)) or not available() or not hasattr(_ext.lib(), "rwkv_gemm_bf16_tcgen05_splitk"):
+        return 0
+    Kc, M, N = a.shape[0], a.shape[1], b.shape[1]
+    if M < 64 or N < MIN_N or N % 8 or Kc < SPLITK_MIN_K:
+        return 0
+    tiles = -(-M // 128) * -(-N // 256)
+    if tiles >= 64:
+        return 0
+    splits = min(148 // tiles, -(-Kc // 64) // 8, 32)
+    return splits if splits >= 2 else 0
+
+
+def mm_tn_splitk(a: torch.Tensor, b: torch.Tensor, splits: int) -> torch.Tensor:
+    """``a[Kc,M]^T @ b[Kc,N]`` with the contraction cut into ``splits`` slices (fp32 slice tiles + one reduce)."""
+    Kc, M, N = a.shape[0], a.shape[1], b.shape[1]
+    key = a.device.index
+    ws = _SPLITK_WS.get(key)
+    need = splits * M * N
+    if ws is None or ws.numel() < need:
+        ws = _SPLITK_WS[key] = torch.empty(max(need, 1 << 22), dtype=torch.float32, device=a.device)
+    c = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+    _ext.call("rwkv_gemm_bf16_tcgen05_splitk", _ext.ptr(a), _ext.ptr(b), _ext.ptr(c), _ext.i32(M), _ext.i32(N),
+              _ext.i32(Kc), _ext.i64(a.stride(0)), _ext.i64(b.stride(0)), _ext.i64(c.stride(0)), _ext.i32(1), _ext.i32(1),
+              _ext.i32(splits), _ext.ptr(ws), _ext.ptr(_status(a.device)), _ext.stream())
+    return c
+
+
 class GatheredWeight:
     """A ``[N, K]`` weight stored as ``world`` K-panels (one per rank) plus the local staging matrix the
     all-gather-fused GEMM fills.  ``shard_ptrs`` are device addresses of every rank's ``[N, K/world]`` panel as

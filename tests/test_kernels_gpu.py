@@ -430,6 +430,25 @@ def test_gemm_accumulate_epilogue(layout):
     assert (y.float() - ref_y).abs().max().item() <= 2e-2 * ref_y.abs().max().item() + 1e-2
 
 
+@pytest.mark.parametrize("M,N,Kc", [(2048, 96, 16384), (96, 2048, 16384), (320, 264, 9000)])
+def test_gemm_split_k_weight_gradient(M, N, Kc):
+    """Few output tiles, long contraction (weight gradients of the low-rank maps): split-K on the tcgen05 kernel."""
+    from rwkvtune_b200.ops import gemm, gemm_native
+    torch.manual_seed(5)
+    a = (torch.randn(Kc, M, device="cuda") * 0.5).to(BF)
+    b = (torch.randn(Kc, N, device="cuda") * 0.5).to(BF)
+    splits = gemm_native.splitk_plan(a, b)
+    assert splits >= 2
+    out = gemm.mm_tn(a, b)
+    ref_y = a.float().t() @ b.float()
+    assert out.shape == (M, N) and out.dtype == BF
+    assert (out.float() - ref_y).abs().max().item() <= 1e-2 * ref_y.abs().max().item()
+    assert gemm_native.check_status() == 0
+    # a slice count that does not divide the K blocks evenly
+    out2 = gemm_native.mm_tn_splitk(a, b, 7)
+    assert (out2.float() - ref_y).abs().max().item() <= 1e-2 * ref_y.abs().max().item()
+
+
 @pytest.mark.parametrize("act", ["tanh", "sigmoid"])
 def test_gemm_activation_epilogue(act):
     torch.manual_seed(4)
