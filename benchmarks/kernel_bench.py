@@ -130,6 +130,19 @@ def bench_gemm(B, T, C, out, tf):
             out[f"gemm_nt_{name}_{tag}_ms"] = ms
             out[f"gemm_nt_{name}_{tag}_tflops"] = 2 * M * K * N / ms / 1e9
             out[f"gemm_nt_{name}_{tag}_frac_peak"] = 2 * M * K * N / ms / 1e9 / tf
+    # weight gradients of the low-rank maps: few output tiles, contraction over every token (split-K)
+    for D in (64, 96, 256):
+        x = torch.randn(M, C, device="cuda").to(BF)
+        h = torch.randn(M, D, device="cuda").to(BF)
+        for name, (a, b) in {f"tn_Cx{D}": (x, h), f"tn_{D}xC": (h, x)}.items():
+            for native in (False, True):
+                gemm.set_native(native)
+                try:
+                    ms = timeit(lambda: gemm.mm_tn(a, b))
+                finally:
+                    gemm.set_native(True)
+                tag = "native_splitk" if native else "cublas"
+                out[f"gemm_{name}_{tag}_us"] = ms * 1e3
 
 
 def bench_loss(C, out, hbm, M=8192, V=65536):
