@@ -10,6 +10,7 @@ from typing import Any
 
 __version__ = "0.1.0"
 __license__ = "Apache-2.0"
+__author__ = "rwkvtune_b200 contributors"
 
 _LAZY = {
     "RWKV7Model": "rwkvtune_b200.models", "RWKV7Config": "rwkvtune_b200.models",
@@ -25,7 +26,7 @@ _LAZY = {
     "RWKV7_DEFAULT_TARGET_MODULES": "rwkvtune_b200.peft",
     "create_model_hub": "rwkvtune_b200.utils",
 }
-__all__ = ["__version__"] + sorted(_LAZY)
+__all__ = ["__version__", "__author__", "__license__"] + sorted(_LAZY)
 
 
 def __getattr__(name: str) -> Any:

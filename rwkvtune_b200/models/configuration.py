@@ -90,6 +90,10 @@ class RWKVConfig:
     def to_json_string(self) -> str:
         return json.dumps(self.to_dict(), indent=2, ensure_ascii=False) + "\n"
 
+    def to_json_file(self, json_file: str) -> None:
+        with open(json_file, "w", encoding="utf-8") as fh:
+            fh.write(self.to_json_string())
+
     def save_pretrained(self, save_directory: str) -> str:
         os.makedirs(save_directory, exist_ok=True)
         target = os.path.join(save_directory, CONFIG_NAME)
@@ -145,6 +149,16 @@ class GenerationConfig:
 
     def to_dict(self) -> Dict[str, Any]:
         return {f.name: getattr(self, f.name) for f in fields(self)}
+
+    @classmethod
+    def from_json_file(cls, json_file: str) -> "GenerationConfig":
+        with open(json_file, "r", encoding="utf-8") as fh:
+            return cls.from_dict(json.load(fh))
+
+    def to_json_file(self, json_file: str) -> None:
+        with open(json_file, "w", encoding="utf-8") as fh:
+            json.dump(self.to_dict(), fh, indent=2)
+            fh.write("\n")
 
     def save_pretrained(self, save_directory: str) -> str:
         os.makedirs(save_directory, exist_ok=True)

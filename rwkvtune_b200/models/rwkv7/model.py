@@ -227,6 +227,15 @@ class RWKV7Block(nn.Module):
         x, ffn_last = self.ffn(x, self.ln2.weight, self.ln2.bias, ffn_prev, want_state)
         return x, v_first, att_last, new_wkv, ffn_last
 
+    def forward_with_state(self, x, v_first, layer_state: Dict[str, torch.Tensor]):
+        """Dictionary form of the stateful step (``rwkvtune/models/rwkv7/model.py:382-420``): ``layer_state`` holds
+        ``att_x_prev`` / ``att_kv`` / ``ffn_x_prev``; returns ``(x, v_first, new_layer_state)`` with fp32 states."""
+        dt = x.dtype
+        x, v_first, att_last, new_wkv, ffn_last = self.forward(
+            x, v_first, layer_state["att_x_prev"].to(dt), layer_state["att_kv"].float(),
+            layer_state["ffn_x_prev"].to(dt), True)
+        return x, v_first, {"att_x_prev": att_last.float(), "att_kv": new_wkv.float(), "ffn_x_prev": ffn_last.float()}
+
 
 def _block_plain(block, x, v_first):
     x, v_first, _, _, _ = block(x, v_first)

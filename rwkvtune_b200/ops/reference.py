@@ -129,6 +129,15 @@ class _L2Wrap(torch.autograd.Function):
         return grad_output, gy, None
 
 
+class L2Wrap:
+    """``L2Wrap.apply(loss, logits)`` with ``logits [B, T, V]``: the stand-alone form of the regulariser that the
+    fused head kernels apply in place (``rwkvtune/training/lightning_module.py:22-39``); factor ``1e-4 / (B * T)``."""
+
+    @staticmethod
+    def apply(loss: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
+        return _L2Wrap.apply(loss, logits, 1e-4 / (logits.shape[0] * logits.shape[1]))
+
+
 def linear_cross_entropy(x, weight, labels, l2wrap: bool = True, ignore_index: int = -100,
                          l2wrap_tokens: Optional[int] = None):
     """``CrossEntropy(x @ weight^T, labels)`` averaged over non-ignored targets, plus L2Wrap.

@@ -34,3 +34,14 @@ class SamplingParams:
     @property
     def greedy(self) -> bool:
         return self.temperature < 1e-6
+
+    @classmethod
+    def from_dict(cls, data: dict) -> "SamplingParams":
+        """Unknown keys are ignored."""
+        known = cls.__dataclass_fields__
+        return cls(**{key: value for key, value in data.items() if key in known})
+
+    def to_dict(self) -> dict:
+        from dataclasses import asdict
+
+        return asdict(self)

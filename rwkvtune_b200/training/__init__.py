@@ -4,7 +4,9 @@ from .pretrain_trainer import PretrainTrainer
 from .sft_config import SFTConfig
 from .sft_trainer import SFTTrainer
 
-__all__ = ["PretrainConfig", "PretrainTrainer", "SFTConfig", "SFTTrainer", "GRPOConfig", "GRPOTrainer"]
+from ..ops.reference import L2Wrap
+
+__all__ = ["PretrainConfig", "PretrainTrainer", "SFTConfig", "SFTTrainer", "GRPOConfig", "GRPOTrainer", "L2Wrap"]
 
 
 def __getattr__(name):

@@ -24,6 +24,11 @@ class RepeatBatchSampler:
     def set_epoch(self, epoch: int) -> None:
         self.epoch = epoch
 
+    @property
+    def sampler(self):
+        """The index source behind the batches: this object draws its own permutation."""
+        return self
+
     def _indices(self) -> List[int]:
         if self.shuffle:
             g = torch.Generator().manual_seed(self.seed + self.epoch)
@@ -82,21 +87,56 @@ def create_grpo_dataloader(dataset, batch_size: int, repeat_batch_count: int = 1
 
 
 class GRPODataBuffer:
-    """FIFO of rollout slices (kept for API parity; the trainer holds its slices in a plain list)."""
+    """Bounded FIFO of rollout samples (``rwkvtune/training/grpo/dataset.py:17-78``).
 
-    def __init__(self, capacity: int = 16):
-        self.capacity, self.items = capacity, []
+    ``add_batch`` splits a rollout of ``B*G`` completions into per-sample records, ``sample_batch`` draws a random
+    training batch of stacked tensors.  ``add`` / ``pop`` move whole slices (what the trainer itself uses)."""
+
+    _TENSOR_FIELDS = ("prompt_ids", "completion_ids", "completion_logps", "rewards", "advantages", "masks")
+
+    def __init__(self, buffer_size: int = 1000, capacity: Optional[int] = None):
+        from collections import deque
+
+        self.buffer_size = int(capacity if capacity is not None else buffer_size)
+        self.buffer = deque(maxlen=self.buffer_size)
+
+    # reference-style per-sample interface ---------------------------------------------------------------------
+    def add_batch(self, prompts, prompt_ids, completions, completion_ids, completion_logps, rewards, advantages,
+                  masks) -> None:
+        cols = (prompt_ids, completion_ids, completion_logps, rewards, advantages, masks)
+        for i, (prompt, completion) in enumerate(zip(prompts, completions)):
+            record = {"prompt": prompt, "completion": completion}
+            record.update({name: col[i] for name, col in zip(self._TENSOR_FIELDS, cols)})
+            self.buffer.append(record)
+
+    def sample_batch(self, batch_size: int, generator: Optional[torch.Generator] = None):
+        """Random batch without replacement (``None`` when the buffer is empty)."""
+        if not self.buffer:
+            return None
+        picks = torch.randperm(len(self.buffer), generator=generator)[:batch_size].tolist()
+        rows = [self.buffer[i] for i in picks]
+        return {name: torch.stack([row[name] for row in rows]) for name in self._TENSOR_FIELDS}
+
+    def is_full(self) -> bool:
+        return len(self.buffer) >= self.buffer_size
+
+    # slice interface ------------------------------------------------------------------------------------------
+    @property
+    def capacity(self) -> int:
+        return self.buffer_size
+
+    @property
+    def items(self):
+        return self.buffer
 
     def add(self, item) -> None:
-        self.items.append(item)
-        if len(self.items) > self.capacity:
-            self.items.pop(0)
+        self.buffer.append(item)
 
     def pop(self):
-        return self.items.pop(0) if self.items else None
+        return self.buffer.popleft() if self.buffer else None
 
     def __len__(self) -> int:
-        return len(self.items)
+        return len(self.buffer)
 
     def clear(self) -> None:
-        self.items.clear()
+        self.buffer.clear()

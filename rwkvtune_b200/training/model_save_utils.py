@@ -49,6 +49,16 @@ def save_model_with_config(model, output_dir: str, tokenizer=None, save_format: 
     return path
 
 
+def save_model_checkpoint(module, save_directory: str, checkpoint_name: str, tokenizer=None,
+                          model_path: Optional[str] = None) -> str:
+    """Weights + config (+ tokenizer) under ``save_directory/checkpoint_name``
+    (``rwkvtune/training/model_save_utils.py:116-140``).  ``module`` is a model or anything holding one as
+    ``.model`` (a trainer, an engine); ``model_path`` is accepted for signature parity and not needed."""
+    model = getattr(module, "model", module)
+    return save_model_with_config(model, os.path.join(save_directory, checkpoint_name), tokenizer=tokenizer,
+                                  save_format="pth")
+
+
 def get_lora_state_dict(model_or_sd) -> Dict[str, torch.Tensor]:
     sd = model_or_sd if isinstance(model_or_sd, dict) else model_or_sd.state_dict()
     out = {}

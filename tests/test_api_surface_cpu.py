@@ -1,0 +1,132 @@
+"""Small pieces of the public surface that have no other test: buffer, config files, parameter dictionaries,
+the dictionary-state block step and the stand-alone L2Wrap."""
+import json
+
+import torch
+
+from rwkvtune_b200.models import GenerationConfig, GenerationMixin, RWKV7Model, RWKVConfig
+from rwkvtune_b200.sampling_params import SamplingParams
+from rwkvtune_b200.training import L2Wrap
+from rwkvtune_b200.training.grpo import GRPODataBuffer, RepeatBatchSampler
+
+
+def test_grpo_data_buffer_per_sample_interface():
+    buf = GRPODataBuffer(buffer_size=6)
+    n, P, L = 4, 3, 5
+    for start in (0, 4):
+        buf.add_batch([f"p{start + i}" for i in range(n)], torch.arange(n * P).view(n, P) + start,
+                      [f"c{start + i}" for i in range(n)], torch.arange(n * L).view(n, L), torch.zeros(n, L),
+                      torch.arange(n, dtype=torch.float32) + start, torch.ones(n), torch.ones(n, L))
+    assert len(buf) == 6 and buf.is_full()                      # the two oldest samples were dropped
+    assert sorted(r["prompt"] for r in buf.items) == [f"p{i}" for i in range(2, 8)]
+    batch = buf.sample_batch(4, generator=torch.Generator().manual_seed(0))
+    assert batch["prompt_ids"].shape == (4, P) and batch["completion_ids"].shape == (4, L)
+    assert len(set(batch["rewards"].tolist())) == 4             # without replacement
+    buf.clear()
+    assert buf.sample_batch(2) is None and not buf.is_full()
+    buf.add("slice")
+    assert buf.pop() == "slice" and buf.pop() is None
+
+
+def test_repeat_batch_sampler_properties():
+    s = RepeatBatchSampler(10, 4, repeat_count=3, shuffle=False)
+    assert s.batch_size == 4 and s.sampler is s and isinstance(s.drop_last, bool)
+    batches = list(s)
+    assert batches[0] == batches[1] == batches[2]
+
+
+def test_config_json_files(tmp_path):
+    cfg = RWKVConfig(n_layer=2, n_embd=128, vocab_size=512)
+    cfg.to_json_file(str(tmp_path / "c.json"))
+    assert RWKVConfig.from_json_file(str(tmp_path / "c.json")).to_dict() == cfg.to_dict()
+    g = GenerationConfig(temperature=0.7, top_k=5)
+    g.to_json_file(str(tmp_path / "g.json"))
+    assert json.load(open(tmp_path / "g.json"))["top_k"] == 5
+    assert GenerationConfig.from_json_file(str(tmp_path / "g.json")) == g
+
+
+def test_sampling_params_dict_round_trip():
+    p = SamplingParams(max_tokens=7, temperature=0.5, stop="###", logit_bias={3: -1.0})
+    d = p.to_dict()
+    assert d["stop"] == ["###"] and d["max_tokens"] == 7
+    assert SamplingParams.from_dict({**d, "unknown_key": 1}) == p
+
+
+def test_l2wrap_gradient_at_argmax():
+    logits = torch.randn(2, 3, 11, requires_grad=True)
+    loss = L2Wrap.apply(logits.sum() * 0.0, logits)
+    loss.backward()
+    g = logits.grad
+    mx, ids = logits.detach().max(-1, keepdim=True)
+    expect = torch.zeros_like(g).scatter_(-1, ids, mx * 1e-4 / 6)
+    assert torch.allclose(g, expect, atol=1e-9)
+
+
+def test_block_forward_with_state_matches_model_state_step():
+    torch.manual_seed(0)
+    cfg = RWKVConfig(n_layer=2, n_embd=128, vocab_size=256)
+    model = RWKV7Model(cfg).eval()
+    assert isinstance(model, GenerationMixin)
+    idx = torch.randint(0, 256, (1, 6))
+    with torch.no_grad():
+        x = model.emb(idx)
+        H, N = cfg.n_embd // 64, 64
+        v_first = torch.empty_like(x)
+        for blk in model.blocks:
+            st = {"att_x_prev": torch.zeros(1, cfg.n_embd), "att_kv": torch.zeros(1, H, N, N),
+                  "ffn_x_prev": torch.zeros(1, cfg.n_embd)}
+            x, v_first, new = blk.forward_with_state(x, v_first, st)
+            assert new["att_kv"].shape == (1, H, N, N) and new["att_kv"].dtype == torch.float32
+        x = torch.nn.functional.layer_norm(x, (cfg.n_embd,), model.ln_out.weight, model.ln_out.bias)
+        ref = model.forward_hidden(idx)
+    assert torch.allclose(x, ref, atol=1e-4, rtol=1e-4)
+
+
+def test_operator_entry_points_follow_reference_conventions():
+    from rwkvtune_b200.models.rwkv7 import operators as O
+    from rwkvtune_b200.ops import reference
+    torch.manual_seed(1)
+    B, T, H, N = 2, 5, 2, 64
+    C = H * N
+    r, k, v = (torch.randn(B, T, C) * 0.5 for _ in range(3))
+    w = -torch.nn.functional.softplus(-torch.randn(B, T, C)) - 0.5
+    kk = torch.nn.functional.normalize(torch.randn(B, T, H, N), dim=-1).reshape(B, T, C)
+    a, b = -kk, kk * torch.sigmoid(torch.randn(B, T, C))
+    y_ref, s_ref = reference.wkv7(r, w, k, v, a, b, N)
+    op = O.load_wkv_operator(device="cpu")
+    assert torch.allclose(op(r, w, k, v, a, b), y_ref)
+    y, s = op(r, w, k, v, a, b, state=None, return_state=True)
+    assert torch.allclose(s, s_ref)
+    assert O.load_wkv7_operator is O.load_wkv_operator
+    y2, s2 = O.rwkv7_wkv(r, w, k, v, a, b, head_size=N, return_state=True)
+    assert torch.allclose(y2, y_ref, atol=1e-5) and torch.allclose(s2, s_ref, atol=1e-5)
+    y1, s1 = O.rwkv7_wkv_cpu(r[0], w[0], k[0], v[0], a[0], b[0], HEAD_SIZE=N)
+    assert y1.shape == (T, C) and torch.allclose(s1, s_ref[0], atol=1e-5)
+    # infctx form: [B, T, H, N], w first, two half chunks carry the state
+    f4 = lambda t: t.reshape(B, T, H, N)
+    ya, sa = O.rwkv7_wkv_infctx(f4(w)[:, :3], f4(r)[:, :3], f4(k)[:, :3], f4(v)[:, :3], f4(a)[:, :3], f4(b)[:, :3])
+    yb, sb = O.load_cuda_operator_infctx()(f4(w)[:, 3:], f4(r)[:, 3:], f4(k)[:, 3:], f4(v)[:, 3:], f4(a)[:, 3:],
+                                           f4(b)[:, 3:], state=sa)
+    assert torch.allclose(torch.cat([ya, yb], 1).reshape(B, T, C), y_ref, atol=1e-5)
+    assert torch.allclose(sb, s_ref, atol=1e-5)
+    yn, sn = O.rwkv7_wkv_infctx_naive(f4(w), f4(r), f4(k), f4(v), f4(a), f4(b), scale=0.5)
+    assert torch.allclose(yn.reshape(B, T, C), 0.5 * y_ref, atol=1e-5) and torch.allclose(sn, s_ref, atol=1e-5)
+    try:
+        O.load_wkv_operator(device="tpu")
+        raise AssertionError("expected ValueError")
+    except ValueError:
+        pass
+
+
+def test_save_model_checkpoint_layout(tmp_path):
+    from rwkvtune_b200.training.model_save_utils import save_model_checkpoint
+
+    class Holder:
+        pass
+
+    h = Holder()
+    h.model = RWKV7Model(RWKVConfig(n_layer=1, n_embd=64, vocab_size=128))
+    path = save_model_checkpoint(h, str(tmp_path), "step-10")
+    assert path == str(tmp_path / "step-10" / "model.pth") and (tmp_path / "step-10" / "config.json").exists()
+    sd = torch.load(path)
+    assert set(sd) == set(h.model.state_dict())
