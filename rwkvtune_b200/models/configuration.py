@@ -125,6 +125,7 @@ class GenerationConfig:
 
     eos_token_id: Optional[int] = 261
     pad_token_id: Optional[int] = 0
+    bos_token_id: Optional[int] = None
     do_sample: bool = True
     temperature: float = 1.0
     top_p: float = 0.85
