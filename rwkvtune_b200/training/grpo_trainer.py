@@ -151,6 +151,28 @@ class GRPOTrainer:
         total = (per_func_t * torch.tensor(self.reward_weights)[None, :]).sum(1)
         return total, per_func_t
 
+    def _postprocess(self, prompts, completions, comp_ids, masks, extra):
+        """Hook between rollout and rewards (``rwkvtune/training/grpo/lightning_module.py:876-905``): called with
+        ``prompts, completions, completion_ids [B*G, C], masks [B*G, C], tokenizer`` and the extra dataset columns as
+        keywords; returns a dict with ``completions``, ``completion_ids`` and ``masks`` of the same shapes (the hook
+        re-encodes what it edits).  The edited ids are what the policy is trained on."""
+        result = self.completion_postprocess_fn(prompts=prompts, completions=list(completions), completion_ids=comp_ids,
+                                                masks=masks, tokenizer=self.processing_class, **extra)
+        if not isinstance(result, dict):
+            raise TypeError("completion_postprocess_fn must return a dict with keys 'completions', 'completion_ids', "
+                            f"'masks'; got {type(result).__name__}")
+        for key in ("completions", "completion_ids", "masks"):
+            if key not in result:
+                raise KeyError(f"completion_postprocess_fn result lacks {key!r}; got {sorted(result)}")
+        new_text = list(result["completions"])
+        new_ids = torch.as_tensor(result["completion_ids"]).to(device=comp_ids.device, dtype=comp_ids.dtype)
+        new_masks = torch.as_tensor(result["masks"]).to(device=masks.device, dtype=masks.dtype)
+        if len(new_text) != len(prompts) or new_ids.shape != comp_ids.shape or new_masks.shape != masks.shape:
+            raise ValueError(f"completion_postprocess_fn must keep {len(prompts)} completions and the shape "
+                             f"{tuple(comp_ids.shape)}; got {len(new_text)}, {tuple(new_ids.shape)}, "
+                             f"{tuple(new_masks.shape)}")
+        return new_text, new_ids, new_masks
+
     def _generate_and_buffer(self, batch: Dict[str, Any]) -> None:
         a, ctx, eng = self.args, self.ctx, self.engine
         G = a.num_generations
@@ -165,9 +187,7 @@ class GRPOTrainer:
         ids_rep = [p for p in prompts_ids for _ in range(G)]
         extra = {k: [v for v in vals for _ in range(G)] for k, vals in batch.items() if k not in ("prompts", "input_ids")}
         if self.completion_postprocess_fn is not None:
-            completions = list(self.completion_postprocess_fn(prompts_rep, completions))
-            if len(completions) != len(prompts_rep):
-                raise ValueError("completion_postprocess_fn must return one completion per input")
+            completions, comp_ids, masks = self._postprocess(prompts_rep, completions, comp_ids, masks, extra)
         rewards, per_func = self._compute_rewards(prompts_rep, completions, extra)
         rewards, per_func = rewards.to(ctx.device), per_func.to(ctx.device)
         n_local = rewards.numel()

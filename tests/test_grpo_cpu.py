@@ -107,3 +107,46 @@ def test_grpo_trainer_end_to_end(tmp_path):
     assert {"adapter_model.bin", "adapter_config.json", "trainer_state"} <= set(os.listdir(final))
     moved = any(float(p.abs().sum()) > 0 for n, p in tr.engine.model.named_parameters() if "lora_B" in n)
     assert moved, "LoRA B matrices never received an update"
+
+
+def test_completion_postprocess_hook_contract(tmp_path):
+    """The hook gets texts, ids, masks, the tokenizer and the dataset columns, and what it returns is what gets
+    scored and trained on; a result of the wrong kind is rejected."""
+    torch.manual_seed(0)
+    model = RWKV7Model(RWKVConfig(n_layer=1, n_embd=64, vocab_size=128, dim_att_lora=16, dim_gate_lora=16, dim_mv_lora=16,
+                                  eos_token_id=7))
+    data = [{"prompt": f"p{i}", "input_ids": [10 + i, 11 + i], "tag": i} for i in range(2)]
+    args = GRPOConfig(micro_bsz=2, num_generations=2, steps_per_generation=1, max_prompt_length=4, max_completion_length=5,
+                      lr_init=1e-3, lr_final=1e-4, warmup_steps=0, accelerator="cpu", precision="fp32",
+                      proj_dir=str(tmp_path / "g"), epoch_count=1, log_steps=1)
+    calls = {}
+
+    def keep_two_tokens(prompts, completions, completion_ids, masks, tokenizer, **columns):
+        calls.update(n=len(prompts), shape=tuple(completion_ids.shape), tok=tokenizer, columns=sorted(columns))
+        ids = completion_ids.clone()
+        ids[:, 2:] = 0
+        new_masks = masks.clone()
+        new_masks[:, 2:] = False
+        return {"completions": ["cut"] * len(completions), "completion_ids": ids, "masks": new_masks}
+
+    scored = []
+
+    def reward(prompts, completions, **kw):
+        scored.extend(completions)
+        return [float(i % 2) for i in range(len(completions))]
+
+    tok = _Tok()
+    tr = GRPOTrainer(model, reward, args, data, processing_class=tok, peft_config=LoraConfig(r=4, lora_alpha=8),
+                     completion_postprocess_fn=keep_two_tokens)
+    tr.train()
+    assert calls["n"] == 4 and calls["shape"][0] == 4 and calls["tok"] is tok and calls["columns"] == ["tag"]
+    assert scored and set(scored) == {"cut"}
+    assert tr.last_metrics["completions/mean_length"] <= 2.0
+
+    tr2 = GRPOTrainer(model, reward, args, data, processing_class=tok,
+                      completion_postprocess_fn=lambda **kw: ["not", "a", "dict", "!"])
+    try:
+        tr2.train()
+        raise AssertionError("expected TypeError")
+    except TypeError as e:
+        assert "dict" in str(e)
