@@ -54,7 +54,14 @@ class GRPOTrainer:
         if train_dataset is None:
             raise ValueError("train_dataset is required")
         self.train_dataset, self.eval_dataset = train_dataset, eval_dataset
-        self.processing_class = processing_class
+        if processing_class is None:    # as in the reference (grpo_trainer.py:540-549): the default RWKV vocabulary,
+            from ..data.tokenizers import AutoTokenizer, get_tokenizer   # or the model directory's own tokenizer
+
+            if isinstance(model, str) and os.path.exists(os.path.join(model, "tokenizer_config.json")):
+                processing_class = AutoTokenizer.from_pretrained(model)
+            else:
+                processing_class = get_tokenizer()
+        self.processing_class = self.tokenizer = processing_class
         self.callbacks = list(callbacks or [])
         self.loss_mask_func = loss_mask_func
         self.completion_postprocess_fn = completion_postprocess_fn
