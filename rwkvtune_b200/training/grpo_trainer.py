@@ -270,7 +270,8 @@ class GRPOTrainer:
             raise RuntimeError("policy log-probabilities carry no gradient (no trainable parameters on the path)")
         ref = self._reference_logps(data["prompt_ids"], comp) if a.beta > 0 else None
         if self.loss_mask_func is not None:
-            custom = self.loss_mask_func(data["prompts"], data["completions"], comp, self.processing_class)
+            custom = self.loss_mask_func(prompts=data["prompts"], completions=data["completions"], completion_ids=comp,
+                                         tokenizer=self.processing_class)
             custom = torch.as_tensor(custom, dtype=mask.dtype, device=mask.device)
             if custom.shape == mask.shape and float((custom * mask).sum()) > 0:
                 mask = mask * custom

@@ -150,3 +150,26 @@ def test_completion_postprocess_hook_contract(tmp_path):
         raise AssertionError("expected TypeError")
     except TypeError as e:
         assert "dict" in str(e)
+
+
+def test_loss_mask_hook_is_called_with_keywords(tmp_path):
+    torch.manual_seed(0)
+    model = RWKV7Model(RWKVConfig(n_layer=1, n_embd=64, vocab_size=128, dim_att_lora=16, dim_gate_lora=16, dim_mv_lora=16,
+                                  eos_token_id=7))
+    data = [{"prompt": f"p{i}", "input_ids": [10 + i, 11 + i]} for i in range(2)]
+    args = GRPOConfig(micro_bsz=2, num_generations=2, steps_per_generation=1, max_prompt_length=4, max_completion_length=5,
+                      lr_init=1e-3, lr_final=1e-4, warmup_steps=0, accelerator="cpu", precision="fp32",
+                      proj_dir=str(tmp_path / "g"), epoch_count=1, log_steps=1)
+    seen = {}
+
+    def first_token_only(**kw):
+        seen.update({k: type(v).__name__ for k, v in kw.items()})
+        m = torch.zeros_like(kw["completion_ids"], dtype=torch.float32)
+        m[:, 0] = 1
+        return m
+
+    tr = GRPOTrainer(model, lambda prompts, completions, **k: [float(i % 2) for i in range(len(completions))], args, data,
+                     processing_class=_Tok(), peft_config=LoraConfig(r=4, lora_alpha=8), loss_mask_func=first_token_only)
+    tr.train()
+    assert set(seen) == {"prompts", "completions", "completion_ids", "tokenizer"}
+    assert tr.last_metrics["train_loss"] == tr.last_metrics["train_loss"]
