@@ -10,6 +10,7 @@ atomic checkpoints with rotation, and resume by seeking the sampler.
 from __future__ import annotations
 
 import copy
+import dataclasses
 import os
 import time
 from typing import Any, Dict, Optional
@@ -50,6 +51,9 @@ class SupervisedTrainer:
             model = AutoModel.from_pretrained(model, device="cpu")
         self.model = model
         if lora_config is not None and not is_peft_model(model):
+            if isinstance(lora_config, dict):   # the reference passes the adapter settings as a plain dict
+                known = {f.name for f in dataclasses.fields(LoraConfig)}
+                lora_config = LoraConfig(**{k: v for k, v in lora_config.items() if k in known})
             self.model = get_peft_model(model, lora_config)
         args.use_lora = is_peft_model(self.model)
         self._sync_arch_fields()

@@ -130,3 +130,12 @@ def test_save_model_checkpoint_layout(tmp_path):
     assert path == str(tmp_path / "step-10" / "model.pth") and (tmp_path / "step-10" / "config.json").exists()
     sd = torch.load(path)
     assert set(sd) == set(h.model.state_dict())
+
+
+def test_trainer_accepts_lora_settings_as_dict():
+    from rwkvtune_b200 import SFTConfig, SFTTrainer, is_peft_model
+    m = RWKV7Model(RWKVConfig(n_layer=1, n_embd=64, vocab_size=128))
+    tr = SFTTrainer(m, SFTConfig(accelerator="cpu", precision="fp32"), [{"input_ids": [1, 2, 3], "labels": [2, 3, 4]}],
+                    lora_config={"r": 4, "lora_alpha": 8, "not_a_field": 1})
+    assert is_peft_model(tr.model) and tr.args.use_lora
+    assert any("lora_A" in n for n, _ in tr.model.named_parameters())
