@@ -40,12 +40,12 @@ class TokenizerConfig:
         self._extra_config = kwargs
 
     @classmethod
-    def from_dict(cls, d: Dict[str, Any]) -> "TokenizerConfig":
-        return cls(**d)
+    def from_dict(cls, config_dict: Dict[str, Any]) -> "TokenizerConfig":
+        return cls(**config_dict)
 
     @classmethod
-    def from_json_file(cls, path: str) -> "TokenizerConfig":
-        with open(path, "r", encoding="utf-8") as fh:
+    def from_json_file(cls, json_file: str) -> "TokenizerConfig":
+        with open(json_file, "r", encoding="utf-8") as fh:
             return cls.from_dict(json.load(fh))
 
     def to_dict(self) -> Dict[str, Any]:
@@ -53,9 +53,9 @@ class TokenizerConfig:
         d.update(self._extra_config)
         return {k: v for k, v in d.items() if v is not None}
 
-    def to_json_file(self, path: str) -> None:
-        os.makedirs(os.path.dirname(path) or ".", exist_ok=True)
-        with open(path, "w", encoding="utf-8") as fh:
+    def to_json_file(self, json_file: str) -> None:
+        os.makedirs(os.path.dirname(json_file) or ".", exist_ok=True)
+        with open(json_file, "w", encoding="utf-8") as fh:
             json.dump(self.to_dict(), fh, indent=2, ensure_ascii=False)
 
     def save_pretrained(self, save_directory: str) -> None:

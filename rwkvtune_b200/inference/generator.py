@@ -42,8 +42,7 @@ class TextGenerator:
                 continue
             if not user:
                 continue
-            prefix = f"System: {system_prompt}\n\n" if system_prompt and not history else ""
-            reply = self.pipeline.chat(prefix + user, history)
+            reply = self.pipeline.chat(user, system_prompt=system_prompt, history=history)
             print(f"Assistant: {reply}")
             history.append((user, reply))
             turns += 1

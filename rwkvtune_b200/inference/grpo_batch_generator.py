@@ -74,7 +74,9 @@ class _DecodeGraph:
 class GRPOBatchGenerator:
     def __init__(self, model, tokenizer=None, device=None, eos_token_id=None, prefill_chunk_size: int = 2048,
                  max_prefill_batch_size: int = -1, max_decode_batch_size: int = -1, sync_every: int = 8,
-                 verbose: bool = False, use_cuda_graph: Optional[bool] = None):
+                 verbose: bool = False, use_cuda_graph: Optional[bool] = None, chunk_size: Optional[int] = None):
+        if chunk_size is not None:      # the reference's name for the prefill chunk (grpo_batch_generator.py:74-82)
+            prefill_chunk_size = chunk_size
         self.model = model
         self.tokenizer = tokenizer
         self.device = torch.device(device) if device is not None else next(model.parameters()).device
@@ -84,7 +86,7 @@ class GRPOBatchGenerator:
         if eos is None:
             eos = getattr(model.config, "eos_token_id", None)
         self.eos_ids = [] if eos is None else ([int(eos)] if isinstance(eos, int) else [int(e) for e in eos])
-        self.prefill_chunk_size = prefill_chunk_size
+        self.prefill_chunk_size = self.chunk_size = prefill_chunk_size
         self.max_prefill_batch_size = max_prefill_batch_size
         self.max_decode_batch_size = max_decode_batch_size
         self.sync_every = max(1, sync_every)

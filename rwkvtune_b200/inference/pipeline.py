@@ -4,7 +4,7 @@ tensor shapes or taken from a preset), then ``generate`` / ``chat``
 from __future__ import annotations
 
 import os
-from typing import List, Optional, Tuple
+from typing import List, Optional, Tuple, Union
 
 import torch
 
@@ -62,20 +62,33 @@ class InferencePipeline:
     def decode(self, tokens: List[int]) -> str:
         return self.tokenizer.decode(tokens)
 
-    def generate(self, prompt: str, max_tokens: int = 100, temperature: float = 1.0, top_p: float = 0.9,
-                 top_k: int = 0, num_generations: int = 1, **kwargs):
+    def generate(self, prompt: Union[str, List[str]], max_tokens: int = 100, temperature: float = 1.0,
+                 top_p: float = 0.9, top_k: int = 0, num_generations: int = 1, stream: bool = False, **kwargs):
+        """One prompt or a list of prompts (``rwkvtune/inference/pipeline.py:198-255``).  A single prompt with
+        ``num_generations=1`` returns a string; every other case returns a list, prompt-major
+        (``len(prompt) * num_generations`` entries).  ``stream`` only prints each finished completion."""
+        single = isinstance(prompt, str)
+        prompts = [prompt] if single else list(prompt)
         if top_p <= 0:          # the "greedy" preset
             temperature, top_p = 0.0, 1.0
         gc = GenerationConfig(max_length=max_tokens, temperature=temperature, top_p=top_p, top_k=top_k,
                               num_generations=num_generations)
-        out = self._generator.generate(prompts=[prompt], generation_config=gc)
+        out = self._generator.generate(prompts=prompts, generation_config=gc)
         if self.debug_output:
-            print(f"[pipeline] prompt tokens {len(self.encode(prompt))}, generated {out['masks'].sum(-1).tolist()}")
-        return out["completions"][0] if num_generations == 1 else out["completions"]
+            print(f"[pipeline] prompt tokens {[len(self.encode(p)) for p in prompts]}, "
+                  f"generated {out['masks'].sum(-1).tolist()}")
+        completions = out["completions"]
+        if stream:
+            for text in completions:
+                print(text, flush=True)
+        return completions[0] if single and num_generations == 1 else completions
 
-    def chat(self, user_input: str, history: Optional[List[Tuple[str, str]]] = None, max_tokens: int = 256,
-             temperature: float = 1.0, top_p: float = 0.9) -> str:
-        parts = [f"User: {u}\n\nAssistant: {a}\n\n" for u, a in (history or [])]
+    def chat(self, user_input: str, system_prompt: Optional[str] = None,
+             history: Optional[List[Tuple[str, str]]] = None, **kwargs) -> str:
+        """``history`` is a list of ``(user, assistant)`` turns; keyword arguments go to :meth:`generate`
+        (defaults: 256 new tokens)."""
+        parts = [f"System: {system_prompt}\n\n"] if system_prompt else []
+        parts += [f"User: {u}\n\nAssistant: {a}\n\n" for u, a in (history or [])]
         parts.append(f"User: {user_input}\n\nAssistant:")
-        text = self.generate("".join(parts), max_tokens=max_tokens, temperature=temperature, top_p=top_p)
-        return text.strip()
+        kwargs.setdefault("max_tokens", 256)
+        return self.generate("".join(parts), **kwargs).strip()

@@ -143,9 +143,11 @@ class AutoConfig:
         return cfg.n_layer * per_layer + cfg.vocab_size * 4
 
     @staticmethod
-    def calculate(max_cache_memory_gb: float, state_size_bytes: int) -> CacheConfig:
-        entries = max(1, int(max_cache_memory_gb * (1 << 30) // max(state_size_bytes, 1)))
-        return CacheConfig(max_cache_memory_gb=max_cache_memory_gb, max_cache_entries=entries)
+    def calculate(max_memory_gb: float, model_state_size_bytes: int, safety_factor: float = 0.9) -> CacheConfig:
+        """Entry count that fits ``safety_factor`` of the budget (``rwkvtune/inference/state_cache.py:231-259``)."""
+        budget = int(max_memory_gb * 1e9 * safety_factor)
+        entries = max(1, budget // max(int(model_state_size_bytes), 1))
+        return CacheConfig(max_cache_memory_gb=max_memory_gb, max_cache_entries=entries)
 
 
 @dataclass

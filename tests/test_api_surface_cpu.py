@@ -139,3 +139,20 @@ def test_trainer_accepts_lora_settings_as_dict():
                     lora_config={"r": 4, "lora_alpha": 8, "not_a_field": 1})
     assert is_peft_model(tr.model) and tr.args.use_lora
     assert any("lora_A" in n for n, _ in tr.model.named_parameters())
+
+
+def test_pipeline_generate_forms_and_chat_prompt():
+    from rwkvtune_b200.inference import InferencePipeline
+    torch.manual_seed(0)
+    model = RWKV7Model(RWKVConfig(n_layer=1, n_embd=64, vocab_size=65536))
+    pipe = InferencePipeline(model=model, device="cpu", precision="fp32")
+    one = pipe.generate("hello", max_tokens=3)
+    assert isinstance(one, str)
+    many = pipe.generate(["a b", "c"], max_tokens=2, num_generations=2)
+    assert isinstance(many, list) and len(many) == 4
+    assert isinstance(pipe.generate("x", max_tokens=2, num_generations=2), list)
+    seen = {}
+    pipe.generate = lambda prompt, **kw: seen.update(prompt=prompt, kw=kw) or " ok "
+    assert pipe.chat("How?", system_prompt="Be brief.", history=[("Hi", "Hello")], temperature=0.5) == "ok"
+    assert seen["prompt"] == "System: Be brief.\n\nUser: Hi\n\nAssistant: Hello\n\nUser: How?\n\nAssistant:"
+    assert seen["kw"] == {"temperature": 0.5, "max_tokens": 256}
