@@ -52,13 +52,14 @@ def list_available_models(config_dir: Optional[str] = None) -> Dict[str, str]:
     return {f[:-5]: os.path.join(d, f) for f in sorted(os.listdir(d)) if f.endswith(".json")} if os.path.isdir(d) else {}
 
 
-def load_model_config(config_identifier: str, config_dir: Optional[str] = None) -> ModelConfig:
+def load_model_config(config_identifier: str, config_dir: Optional[str] = None,
+                      default_arch: str = "rwkv7") -> ModelConfig:
     if os.path.isfile(config_identifier):
         path = config_identifier
     else:
         models = list_available_models(config_dir)
         key = config_identifier.lower()
-        key = key if key in models else f"rwkv7-{key}"
+        key = key if key in models else f"{default_arch}-{key}"
         if key not in models:
             raise ValueError(f"unknown model config {config_identifier!r}; available: {sorted(models)}")
         path = models[key]

@@ -22,17 +22,28 @@ class ChatFormatter:
         return self.template.render(messages=messages, add_generation_prompt=add_generation_prompt, **kwargs)
 
     @staticmethod
-    def convert_sharegpt_to_messages(conversations: List[Dict[str, str]], system: Optional[str] = None) -> List[Dict[str, str]]:
+    def convert_sharegpt_to_messages(conversations: List[Dict[str, str]], include_gpt_ignore: bool = True,
+                                     system: Optional[str] = None) -> List[Dict[str, str]]:
+        """``gpt_ignore`` turns (assistant text that takes no loss) are kept as assistant messages flagged
+        ``_ignore`` when ``include_gpt_ignore``, dropped otherwise (``rwkvtune/data/chat_formatter.py:73-112``)."""
         msgs = [{"role": "system", "content": system}] if system else []
         for turn in conversations:
-            role = _ROLE_MAP.get(turn.get("from", turn.get("role", "")))
+            src = turn.get("from", turn.get("role", ""))
+            content = turn.get("value", turn.get("content", ""))
+            if src == "gpt_ignore":
+                if include_gpt_ignore:
+                    msgs.append({"role": "assistant", "content": content, "_ignore": True})
+                continue
+            role = _ROLE_MAP.get(src)
             if role is None:
                 continue
-            msgs.append({"role": role, "content": turn.get("value", turn.get("content", ""))})
+            msgs.append({"role": role, "content": content})
         return msgs
 
-    def format_sharegpt(self, conversations, system: Optional[str] = None, add_generation_prompt: bool = False) -> str:
-        return self.format_messages(self.convert_sharegpt_to_messages(conversations, system), add_generation_prompt)
+    def format_sharegpt(self, conversations, add_generation_prompt: bool = False, include_gpt_ignore: bool = True,
+                        system: Optional[str] = None) -> str:
+        return self.format_messages(self.convert_sharegpt_to_messages(conversations, include_gpt_ignore, system),
+                                    add_generation_prompt)
 
     def __repr__(self) -> str:
         return f"ChatFormatter(template={self.template_path})"

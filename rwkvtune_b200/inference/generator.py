@@ -22,8 +22,10 @@ class TextGenerator:
             raise ValueError(f"unknown preset {preset!r}; available: {list(self.PRESETS)}")
         return self.pipeline.generate(prompt, max_tokens=max_tokens, **{**self.PRESETS[preset], **kwargs})
 
-    def complete(self, text: str, preset: str = "balanced", max_tokens: int = 100, **kwargs) -> str:
-        return text + self.generate(text, preset, max_tokens, **kwargs)
+    def complete(self, prompt: str, max_tokens: int = 50, n: int = 1, **kwargs) -> List[str]:
+        """``n`` independent completions of ``prompt`` (``rwkvtune/inference/generator.py:69-95``)."""
+        result = self.pipeline.generate(prompt, max_tokens=max_tokens, num_generations=n, **kwargs)
+        return result if isinstance(result, list) else [result]
 
     def interactive_chat(self, system_prompt: Optional[str] = None, input_fn=input, max_turns: Optional[int] = None) -> None:
         history: List[Tuple[str, str]] = []

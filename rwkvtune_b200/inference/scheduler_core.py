@@ -310,10 +310,11 @@ class SchedulerCore:
 
 
 def create_scheduler_core(model, tokenizer, max_batch_size: int = 64, max_batch_tokens: int = 8192,
-                          prefill_chunk_size: int = 512, use_state_cache: bool = False,
+                          prefill_chunk_size: int = 512, state_cache=None, use_state_cache: bool = False,
                           max_cache_memory_gb: float = 4.0) -> SchedulerCore:
-    cache = None
-    if use_state_cache:
+    """``state_cache``: a ready :class:`StateCache` (the reference's argument); ``use_state_cache=True`` builds one."""
+    cache = state_cache
+    if cache is None and use_state_cache:
         from .state_cache import create_state_cache
 
         cache = create_state_cache(model, max_cache_memory_gb)

@@ -62,7 +62,8 @@ class RWKVConfig:
 
     # ------------------------------------------------------------------ (de)serialise
     @classmethod
-    def from_dict(cls, data: Dict[str, Any]) -> "RWKVConfig":
+    def from_dict(cls, config_dict: Dict[str, Any]) -> "RWKVConfig":
+        data = config_dict
         known = {f.name for f in fields(cls)} - {"_extra_config"}
         kwargs = {k: v for k, v in data.items() if k in known}
         extra = {k: v for k, v in data.items() if k not in known}
@@ -76,7 +77,8 @@ class RWKVConfig:
             return cls.from_dict(json.load(fh))
 
     @classmethod
-    def from_pretrained(cls, path: str) -> "RWKVConfig":
+    def from_pretrained(cls, pretrained_model_name_or_path: str) -> "RWKVConfig":
+        path = pretrained_model_name_or_path
         cfg = _resolve_json(path, CONFIG_NAME)
         if not os.path.exists(cfg):
             raise FileNotFoundError(f"no {CONFIG_NAME} found at {path}")
@@ -136,12 +138,14 @@ class GenerationConfig:
     num_return_sequences: int = 1
 
     @classmethod
-    def from_dict(cls, data: Dict[str, Any]) -> "GenerationConfig":
+    def from_dict(cls, config_dict: Dict[str, Any]) -> "GenerationConfig":
+        data = config_dict
         known = {f.name for f in fields(cls)}
         return cls(**{k: v for k, v in data.items() if k in known})
 
     @classmethod
-    def from_pretrained(cls, path: str) -> "GenerationConfig":
+    def from_pretrained(cls, pretrained_model_name_or_path: str) -> "GenerationConfig":
+        path = pretrained_model_name_or_path
         target = _resolve_json(path, GENERATION_CONFIG_NAME)
         if not os.path.exists(target):
             return cls()

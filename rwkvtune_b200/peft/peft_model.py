@@ -33,7 +33,8 @@ def _lora_layers(model: nn.Module):
     return [(n, m) for n, m in model.named_modules() if isinstance(m, LoraLinear)]
 
 
-def get_peft_model(model: nn.Module, config: LoraConfig) -> nn.Module:
+def get_peft_model(model: nn.Module, peft_config: LoraConfig) -> nn.Module:
+    config = peft_config
     targets = list(config.target_modules)
     replaced = 0
     for name, module in list(model.named_modules()):

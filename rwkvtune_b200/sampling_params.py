@@ -36,8 +36,9 @@ class SamplingParams:
         return self.temperature < 1e-6
 
     @classmethod
-    def from_dict(cls, data: dict) -> "SamplingParams":
+    def from_dict(cls, d: dict) -> "SamplingParams":
         """Unknown keys are ignored."""
+        data = d
         known = cls.__dataclass_fields__
         return cls(**{key: value for key, value in data.items() if key in known})
 

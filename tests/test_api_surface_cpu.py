@@ -156,3 +156,23 @@ def test_pipeline_generate_forms_and_chat_prompt():
     assert pipe.chat("How?", system_prompt="Be brief.", history=[("Hi", "Hello")], temperature=0.5) == "ok"
     assert seen["prompt"] == "System: Be brief.\n\nUser: Hi\n\nAssistant: Hello\n\nUser: How?\n\nAssistant:"
     assert seen["kw"] == {"temperature": 0.5, "max_tokens": 256}
+
+
+def test_sharegpt_conversion_and_text_generator_complete():
+    from rwkvtune_b200.data.chat_formatter import ChatFormatter
+    conv = [{"from": "human", "value": "q"}, {"from": "gpt_ignore", "value": "draft"}, {"from": "gpt", "value": "a"}]
+    kept = ChatFormatter.convert_sharegpt_to_messages(conv)
+    assert [m["role"] for m in kept] == ["user", "assistant", "assistant"] and kept[1]["_ignore"] is True
+    dropped = ChatFormatter.convert_sharegpt_to_messages(conv, include_gpt_ignore=False)
+    assert [m["content"] for m in dropped] == ["q", "a"]
+    text = ChatFormatter().format_sharegpt(conv, add_generation_prompt=True, include_gpt_ignore=False)
+    assert "q" in text and "draft" not in text
+
+    from rwkvtune_b200.inference import TextGenerator
+
+    class _Pipe:
+        def generate(self, prompt, max_tokens=100, num_generations=1, **kw):
+            return "x" if num_generations == 1 else ["x"] * num_generations
+
+    g = TextGenerator(_Pipe())
+    assert g.complete("p") == ["x"] and g.complete("p", n=3) == ["x", "x", "x"]
