@@ -40,7 +40,7 @@ from .grpo.advantage import AdvantageCalculator
 from .grpo.dataset import create_grpo_dataloader
 from .grpo.loss import get_loss_function
 from .grpo_config import GRPOConfig
-from .model_save_utils import save_checkpoint_with_lora_support
+from .model_save_utils import save_model_or_adapter
 
 RewardFunc = Callable[..., Union[List[float], torch.Tensor]]
 
@@ -391,7 +391,7 @@ class GRPOTrainer:
 
         def write(tmp: str) -> None:
             if ctx.is_main:
-                save_checkpoint_with_lora_support(eng.model, tmp, self.processing_class, a.lora_save_mode, self.base_model_path)
+                save_model_or_adapter(eng.model, tmp, self.processing_class, a.lora_save_mode, self.base_model_path)
             ckpt.save_trainer_state(tmp, eng, ctx, meta, a.save_optimizer_state)
 
         ckpt.atomic_checkpoint(final, ctx, write)
@@ -417,6 +417,6 @@ class GRPOTrainer:
     def save_model(self, output_dir: Optional[str] = None) -> str:
         out = output_dir or os.path.join(self.args.proj_dir, "final")
         if self.ctx is None or self.ctx.is_main:
-            save_checkpoint_with_lora_support(self.model, out, self.processing_class, self.args.lora_save_mode,
+            save_model_or_adapter(self.model, out, self.processing_class, self.args.lora_save_mode,
                                               self.base_model_path)
         return out

@@ -29,21 +29,35 @@ def save_tokenizer(tokenizer, output_dir: str) -> None:
         tokenizer.save_pretrained(output_dir)
 
 
-def save_model_with_config(model, output_dir: str, tokenizer=None, save_format: str = "pth",
-                           state_dict: Optional[Dict[str, torch.Tensor]] = None, dtype: Optional[torch.dtype] = None) -> str:
+def save_model_with_config(model, save_directory: str, model_name: str = "model", tokenizer=None, model_config_obj=None,
+                           save_format: str = "pth", is_main_process: bool = True,
+                           state_dict: Optional[Dict[str, torch.Tensor]] = None,
+                           dtype: Optional[torch.dtype] = None) -> Optional[str]:
+    """``config.json`` + ``<model_name>.pth`` / ``.safetensors`` (+ tokenizer files) in ``save_directory``
+    (``rwkvtune/training/model_save_utils.py:26-113``).  ``model`` is a module or a state dict; the config comes from
+    ``model_config_obj`` or ``model.config``; ranks other than the main one do nothing."""
+    if not is_main_process:
+        return None
+    output_dir = save_directory
     os.makedirs(output_dir, exist_ok=True)
-    if hasattr(model, "config") and hasattr(model.config, "save_pretrained"):
-        model.config.save_pretrained(output_dir)
-    sd = state_dict if state_dict is not None else _cpu_state_dict(model)
+    cfg = model_config_obj if model_config_obj is not None else getattr(model, "config", None)
+    if cfg is not None and hasattr(cfg, "save_pretrained"):
+        cfg.save_pretrained(output_dir)
+    if state_dict is not None:
+        sd = state_dict
+    elif isinstance(model, dict):
+        sd = {k: v.detach().cpu() for k, v in model.items()}
+    else:
+        sd = _cpu_state_dict(model)
     if dtype is not None:
         sd = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in sd.items()}
     if save_format == "safetensors":
         from safetensors.torch import save_file
 
-        path = os.path.join(output_dir, "model.safetensors")
+        path = os.path.join(output_dir, f"{model_name}.safetensors")
         save_file({k: v.contiguous() for k, v in sd.items()}, path)
     else:
-        path = os.path.join(output_dir, WEIGHTS_NAME)
+        path = os.path.join(output_dir, WEIGHTS_NAME if model_name == "model" else f"{model_name}.pth")
         torch.save(sd, path)
     save_tokenizer(tokenizer, output_dir)
     return path
@@ -59,8 +73,9 @@ def save_model_checkpoint(module, save_directory: str, checkpoint_name: str, tok
                                   save_format="pth")
 
 
-def get_lora_state_dict(model_or_sd) -> Dict[str, torch.Tensor]:
-    sd = model_or_sd if isinstance(model_or_sd, dict) else model_or_sd.state_dict()
+def get_lora_state_dict(model) -> Dict[str, torch.Tensor]:
+    """The ``lora_`` entries of a module's (or a state dict's) parameters, on the CPU."""
+    sd = model if isinstance(model, dict) else model.state_dict()
     out = {}
     for k, v in sd.items():
         if "lora_" in k:
@@ -68,18 +83,34 @@ def get_lora_state_dict(model_or_sd) -> Dict[str, torch.Tensor]:
     return out
 
 
-def save_lora_checkpoint(model, output_dir: str, tokenizer=None, base_model_name_or_path: str = "") -> str:
+def save_lora_checkpoint(model, save_directory: str, lora_config: Optional[Dict[str, Any]] = None,
+                         base_model_path: Optional[str] = None, tokenizer=None, safe_serialization: bool = False,
+                         is_main_process: bool = True) -> Optional[str]:
+    """Adapter weights + ``adapter_config.json`` (``rwkvtune/training/model_save_utils.py:154-237``).  The adapter
+    settings come from ``model.peft_config``; entries of ``lora_config`` (a dict) override them.  With
+    ``safe_serialization`` the weights go to ``adapter_model.safetensors``."""
+    if not is_main_process:
+        return None
+    output_dir, base_model_name_or_path = save_directory, base_model_path or ""
     os.makedirs(output_dir, exist_ok=True)
     sd = get_lora_state_dict(model)
     if hasattr(model, "get_trainable_extra_state_dict"):
         sd.update(model.get_trainable_extra_state_dict())
-    path = os.path.join(output_dir, ADAPTER_WEIGHTS_NAME)
-    torch.save(sd, path)
+    if safe_serialization:
+        from safetensors.torch import save_file
+
+        path = os.path.join(output_dir, "adapter_model.safetensors")
+        save_file({k: v.contiguous() for k, v in sd.items()}, path)
+    else:
+        path = os.path.join(output_dir, ADAPTER_WEIGHTS_NAME)
+        torch.save(sd, path)
     cfg = getattr(model, "peft_config", None)
     body: Dict[str, Any] = {"peft_type": "LORA", "base_model_name_or_path": base_model_name_or_path,
                             "task_type": "CAUSAL_LM", "inference_mode": True}
     if cfg is not None:
         body.update(cfg.to_dict())
+    if lora_config:
+        body.update(lora_config)
     for name in ("adapter_config.json", "lora_config.json"):
         with open(os.path.join(output_dir, name), "w", encoding="utf-8") as fh:
             json.dump(body, fh, indent=2)
@@ -89,15 +120,32 @@ def save_lora_checkpoint(model, output_dir: str, tokenizer=None, base_model_name
     return path
 
 
-def save_checkpoint_with_lora_support(model, output_dir: str, tokenizer=None, lora_save_mode: str = "lora_only",
-                                      base_model_name_or_path: str = "", dtype: Optional[torch.dtype] = None) -> None:
-    """Plain models: full save.  LoRA models: ``lora_only`` -> adapter files, ``full`` -> merged weights,
-    ``both`` -> adapter files plus merged weights in ``<dir>/merged``."""
+def save_model_or_adapter(model, output_dir: str, tokenizer=None, lora_save_mode: str = "lora_only",
+                          base_model_name_or_path: str = "", dtype: Optional[torch.dtype] = None) -> None:
+    """What the trainers call.  Plain models: full save.  LoRA models: ``lora_only`` -> adapter files, ``full`` ->
+    merged weights, ``both`` -> adapter files plus merged weights in ``<dir>/merged``."""
     if not is_peft_model(model):
-        save_model_with_config(model, output_dir, tokenizer, dtype=dtype)
+        save_model_with_config(model, output_dir, tokenizer=tokenizer, dtype=dtype)
         return
     if lora_save_mode in ("lora_only", "both"):
-        save_lora_checkpoint(model, output_dir, tokenizer, base_model_name_or_path)
+        save_lora_checkpoint(model, output_dir, base_model_path=base_model_name_or_path, tokenizer=tokenizer)
     if lora_save_mode in ("full", "both"):
         target = output_dir if lora_save_mode == "full" else os.path.join(output_dir, "merged")
-        save_model_with_config(model, target, tokenizer, state_dict=model.get_merged_state_dict(), dtype=dtype)
+        save_model_with_config(model, target, tokenizer=tokenizer, state_dict=model.get_merged_state_dict(), dtype=dtype)
+
+
+def save_checkpoint_with_lora_support(lightning_module, save_directory: str, checkpoint_name: str, tokenizer=None,
+                                      model_path: Optional[str] = None, use_lora: bool = False,
+                                      lora_save_mode: str = "lora_only", lora_config: Optional[Dict[str, Any]] = None,
+                                      is_main_process: bool = True) -> Optional[str]:
+    """The reference's entry point (``rwkvtune/training/model_save_utils.py:240-330``): saves under
+    ``save_directory/checkpoint_name``; ``lightning_module`` is a model or an object holding one as ``.model``.
+    ``use_lora`` is implied by the model itself; ``lora_config`` entries override the stored adapter settings."""
+    if not is_main_process:
+        return None
+    model = getattr(lightning_module, "model", lightning_module)
+    target = os.path.join(save_directory, checkpoint_name)
+    save_model_or_adapter(model, target, tokenizer, lora_save_mode, model_path or "")
+    if lora_config and is_peft_model(model) and lora_save_mode in ("lora_only", "both"):
+        save_lora_checkpoint(model, target, lora_config=lora_config, base_model_path=model_path, tokenizer=None)
+    return target

@@ -24,7 +24,7 @@ from ..models import AutoModel
 from ..parallel import init_distributed
 from ..peft import LoraConfig, get_peft_model, is_peft_model
 from .data_loading import BatchLoader
-from .model_save_utils import save_checkpoint_with_lora_support
+from .model_save_utils import save_model_or_adapter
 
 _ARCH_FIELDS = ("n_layer", "n_embd", "vocab_size", "head_size_a", "dim_att_lora", "dim_gate_lora", "dim_mv_lora",
                 "dim_att", "dim_ffn")
@@ -114,7 +114,7 @@ class SupervisedTrainer:
     def save_model(self, output_dir: Optional[str] = None) -> str:
         out = output_dir or os.path.join(self.args.proj_dir, "final")
         if self.ctx is None or self.ctx.is_main:
-            save_checkpoint_with_lora_support(self.model, out, self.processing_class, self.args.lora_save_mode,
+            save_model_or_adapter(self.model, out, self.processing_class, self.args.lora_save_mode,
                                               self.base_model_path)
         return out
 
@@ -188,7 +188,7 @@ class SupervisedTrainer:
 
         def write(tmp: str) -> None:
             if ctx.is_main:
-                save_checkpoint_with_lora_support(self.model, tmp, self.processing_class, a.lora_save_mode,
+                save_model_or_adapter(self.model, tmp, self.processing_class, a.lora_save_mode,
                                                   self.base_model_path)
             ckpt.save_trainer_state(tmp, eng, ctx, meta, a.save_optimizer_state)
 

@@ -176,3 +176,32 @@ def test_sharegpt_conversion_and_text_generator_complete():
 
     g = TextGenerator(_Pipe())
     assert g.complete("p") == ["x"] and g.complete("p", n=3) == ["x", "x", "x"]
+
+
+def test_save_utilities_follow_reference_signatures(tmp_path):
+    from rwkvtune_b200 import LoraConfig, get_peft_model
+    from rwkvtune_b200.training.model_save_utils import (get_lora_state_dict, save_checkpoint_with_lora_support,
+                                                         save_lora_checkpoint, save_model_with_config)
+    base = RWKV7Model(RWKVConfig(n_layer=1, n_embd=64, vocab_size=128))
+    p = save_model_with_config(base, str(tmp_path / "a"), "weights")
+    assert p.endswith("weights.pth") and (tmp_path / "a" / "config.json").exists()
+    assert save_model_with_config(base, str(tmp_path / "skip"), is_main_process=False) is None
+    assert not (tmp_path / "skip").exists()
+    p = save_model_with_config(base.state_dict(), str(tmp_path / "b"), model_config_obj=base.config,
+                               save_format="safetensors")
+    assert p.endswith("model.safetensors") and (tmp_path / "b" / "config.json").exists()
+
+    lora = get_peft_model(base, peft_config=LoraConfig(r=4, lora_alpha=8))
+    assert get_lora_state_dict(model=lora)
+    save_lora_checkpoint(lora, str(tmp_path / "c"), lora_config={"note": "x"}, base_model_path="hub/x",
+                         safe_serialization=True)
+    cfg = json.load(open(tmp_path / "c" / "adapter_config.json"))
+    assert cfg["r"] == 4 and cfg["note"] == "x" and cfg["base_model_name_or_path"] == "hub/x"
+    assert (tmp_path / "c" / "adapter_model.safetensors").exists()
+
+    class Holder:
+        model = lora
+
+    out = save_checkpoint_with_lora_support(Holder(), str(tmp_path), "ckpt-1", use_lora=True, lora_save_mode="both")
+    assert out == str(tmp_path / "ckpt-1")
+    assert (tmp_path / "ckpt-1" / "adapter_model.bin").exists() and (tmp_path / "ckpt-1" / "merged" / "model.pth").exists()
