@@ -32,7 +32,9 @@ class BlockStateList:
         self.wkv_states = wkv_states
 
     @staticmethod
-    def create(n_layer: int, batch: int, n_embd: int, n_head: int, device, dtype, head_size: int = None):
+    def create(n_layer: int, batch_size: int, n_embd: int, n_head: int, device, dtype=torch.bfloat16,
+               head_size: int = None):
+        batch = batch_size
         N = head_size if head_size is not None else n_embd // n_head
         return BlockStateList(
             torch.zeros(n_layer, 2, batch, n_embd, device=device, dtype=dtype),
@@ -40,7 +42,9 @@ class BlockStateList:
         )
 
     @staticmethod
-    def empty(n_layer: int, batch: int, n_embd: int, n_head: int, device, dtype, head_size: int = None):
+    def empty(n_layer: int, batch_size: int, n_embd: int, n_head: int, device, dtype=torch.bfloat16,
+              head_size: int = None):
+        batch = batch_size
         N = head_size if head_size is not None else n_embd // n_head
         return BlockStateList(
             torch.empty(n_layer, 2, batch, n_embd, device=device, dtype=dtype),

@@ -27,11 +27,11 @@ class RWKV7Infctx(RWKV7Model):
         new_wkv = torch.stack(s_l, dim=0)
         return x, new_shift, new_wkv
 
-    def forward_infctx(self, idx: torch.Tensor, shift_states: torch.Tensor, wkv_states: torch.Tensor
+    def forward_infctx(self, idx: torch.Tensor, last_shift_states: torch.Tensor, last_wkv_states: torch.Tensor
                        ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
         """``idx [B, T]``, ``shift_states [L,2,B,C]``, ``wkv_states [L,B,H,N,N]`` ->
         ``(logits [B,T,V], new_shift_states, new_wkv_states)``."""
-        x, new_shift, new_wkv = self.forward_hidden_infctx(idx, shift_states, wkv_states)
+        x, new_shift, new_wkv = self.forward_hidden_infctx(idx, last_shift_states, last_wkv_states)
         return self.head(x), new_shift, new_wkv
 
 

@@ -13,21 +13,41 @@ import torch
 
 
 class RepeatBatchSampler:
-    """Yields each batch of indices ``repeat_count`` times in a row."""
+    """Yields each batch of indices ``repeat_count`` times in a row.
 
-    def __init__(self, n: int, batch_size: int, repeat_count: int = 1, shuffle: bool = True, seed: int = 42,
-                 rank: int = 0, world_size: int = 1, drop_last: bool = True):
-        self.n, self.batch_size, self.repeat_count = n, batch_size, max(1, repeat_count)
+    Two ways to build it: ``RepeatBatchSampler(n, batch_size, repeat_count, ...)`` draws its own (seeded, rank-sharded)
+    permutation of ``range(n)``; ``RepeatBatchSampler(batch_sampler, repeat_batch_count)`` wraps any iterable of index
+    batches, which is the reference's form (``rwkvtune/training/grpo/dataset.py:81-124``)."""
+
+    def __init__(self, n, batch_size: Optional[int] = None, repeat_count: int = 1, shuffle: bool = True, seed: int = 42,
+                 rank: int = 0, world_size: int = 1, drop_last: bool = True, repeat_batch_count: Optional[int] = None):
+        self._wrapped = None if isinstance(n, int) else n
+        if repeat_batch_count is not None:
+            repeat_count = repeat_batch_count
+        elif self._wrapped is not None and batch_size is not None:     # (batch_sampler, repeat_batch_count)
+            repeat_count, batch_size = batch_size, None
+        if repeat_count <= 0:
+            raise ValueError(f"repeat_batch_count must be > 0, got {repeat_count}")
+        if self._wrapped is not None:
+            batch_size = getattr(self._wrapped, "batch_size", batch_size)
+            drop_last = bool(getattr(self._wrapped, "drop_last", False))
+            n = 0
+        elif batch_size is None:
+            raise ValueError("batch_size is required")
+        self.n, self.batch_size, self.repeat_count = n, batch_size, repeat_count
         self.shuffle, self.seed, self.rank, self.world_size, self.drop_last = shuffle, seed, rank, world_size, drop_last
         self.epoch = 0
 
     def set_epoch(self, epoch: int) -> None:
         self.epoch = epoch
+        inner = getattr(self._wrapped, "sampler", None)
+        if inner is not None and hasattr(inner, "set_epoch"):
+            inner.set_epoch(epoch)
 
     @property
     def sampler(self):
-        """The index source behind the batches: this object draws its own permutation."""
-        return self
+        """The index source behind the batches (this object itself when it draws its own permutation)."""
+        return self if self._wrapped is None else getattr(self._wrapped, "sampler", None)
 
     def _indices(self) -> List[int]:
         if self.shuffle:
@@ -40,6 +60,8 @@ class RepeatBatchSampler:
         return order[self.rank:total:self.world_size]
 
     def num_batches(self) -> int:
+        if self._wrapped is not None:
+            return len(self._wrapped)
         per_rank = (self.n + self.world_size - 1) // self.world_size
         return per_rank // self.batch_size if self.drop_last else -(-per_rank // self.batch_size)
 
@@ -47,6 +69,11 @@ class RepeatBatchSampler:
         return self.num_batches() * self.repeat_count
 
     def __iter__(self) -> Iterator[List[int]]:
+        if self._wrapped is not None:
+            for batch in self._wrapped:
+                for _ in range(self.repeat_count):
+                    yield batch
+            return
         idx = self._indices()
         for b in range(self.num_batches()):
             batch = idx[b * self.batch_size:(b + 1) * self.batch_size]

@@ -205,3 +205,17 @@ def test_save_utilities_follow_reference_signatures(tmp_path):
     out = save_checkpoint_with_lora_support(Holder(), str(tmp_path), "ckpt-1", use_lora=True, lora_save_mode="both")
     assert out == str(tmp_path / "ckpt-1")
     assert (tmp_path / "ckpt-1" / "adapter_model.bin").exists() and (tmp_path / "ckpt-1" / "merged" / "model.pth").exists()
+
+
+def test_repeat_batch_sampler_wraps_a_batch_sampler():
+    from torch.utils.data import BatchSampler, SequentialSampler
+    inner = BatchSampler(SequentialSampler(range(7)), batch_size=3, drop_last=False)
+    s = RepeatBatchSampler(inner, 2)
+    assert list(s) == [[0, 1, 2], [0, 1, 2], [3, 4, 5], [3, 4, 5], [6], [6]] and len(s) == 6
+    assert s.batch_size == 3 and s.drop_last is False and s.sampler is inner.sampler
+    assert len(RepeatBatchSampler(batch_sampler := inner, repeat_batch_count=3)) == 9 and batch_sampler is inner
+    try:
+        RepeatBatchSampler(inner, 0)
+        raise AssertionError("expected ValueError")
+    except ValueError:
+        pass
