@@ -226,16 +226,24 @@ class StateCache:
             self._maybe_evict()
 
     @torch.no_grad()
-    def create_checkpoints(self, tokens: Sequence[int], system_prompt_len: Optional[int] = None,
+    def create_checkpoints(self, tokens: Sequence[int], messages=None,
                            state: Optional[List[Dict[str, torch.Tensor]]] = None, output: Optional[torch.Tensor] = None,
-                           chunk_size: int = 2048) -> int:
-        """Cache the state after the first message (``system_prompt_len`` tokens, when given and enabled) and
-        after the full prompt.  If ``state``/``output`` for the full prompt are supplied they are stored as
-        they are; otherwise the model is run."""
+                           chunk_size: int = 2048, system_prompt_len: Optional[int] = None) -> int:
+        """Cache the state after the first message and after the full prompt.  The first-message boundary is
+        ``system_prompt_len`` tokens when given (an int passed as ``messages`` means the same); with a message list
+        it is estimated from the share of characters in the first message, as the reference does
+        (``rwkvtune/inference/state_cache.py:458-589``).  If ``state`` / ``output`` for the full prompt are supplied
+        they are stored as they are; the prefix state is computed by running the model."""
         if self.config.cache_level == CacheLevel.NONE:
             return 0
         made = 0
         tokens = list(tokens)
+        if isinstance(messages, int):
+            system_prompt_len, messages = messages, None
+        if system_prompt_len is None and messages:
+            chars = [len(m.get("content", "")) for m in messages]
+            if sum(chars) > 0 and len(tokens) > 1:
+                system_prompt_len = max(1, min(int(len(tokens) * chars[0] / sum(chars)), len(tokens) - 1))
         cuts = []
         if self.config.cache_first_message and system_prompt_len and 0 < system_prompt_len < len(tokens):
             cuts.append((system_prompt_len, "system_prompt"))

@@ -129,3 +129,13 @@ def test_structured_output_masks_to_json():
             break
     import json
     assert json.loads(text)["ok"] in (True, False)
+
+
+def test_state_cache_checkpoints_from_messages(model):
+    cache = create_state_cache(model, max_cache_memory_gb=0.01, max_cache_entries=4)
+    tokens = list(range(3, 15))                         # 12 tokens
+    messages = [{"role": "system", "content": "x" * 30}, {"role": "user", "content": "y" * 10}]
+    assert cache.create_checkpoints(tokens, messages) == 2           # first message ~ 30/40 of the tokens
+    pos, state, _ = cache.lookup(tokens[:9] + [99, 98])
+    assert pos == 9 and state is not None
+    assert cache.create_checkpoints(tokens, messages) == 0           # both prefixes already cached
