@@ -24,7 +24,10 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--max-length", type=int, default=1024)
     p.add_argument("--eos-token", default="\n\n")
     p.add_argument("--model-max-length", type=int, default=4096)
-    p.add_argument("--no-copy", action="store_true", help="symlink the weight file instead of copying it")
+    p.add_argument("--copy-weights", action="store_true", default=True, help="copy the weight file (default)")
+    p.add_argument("--link-weights", "--no-copy", dest="link_weights", action="store_true",
+                   help="symlink the weight file instead of copying it")
+    p.add_argument("--verbose", action="store_true", help="print the resolved settings and full tracebacks")
     p.add_argument("--save-format", choices=["pth", "safetensors"], default="pth")
     p.add_argument("--overwrite", action="store_true")
     p.add_argument("--list-configs", action="store_true")
@@ -43,16 +46,31 @@ def main(argv=None) -> int:
     a = build_parser().parse_args(argv)
     from ..utils import create_model_hub
 
-    out = create_model_hub(
+    if a.verbose:
+        for key, value in sorted(vars(a).items()):
+            print(f"  {key}: {value}")
+    try:
+        out = _create(a, create_model_hub)
+    except Exception as err:      # the reference reports the error and exits 1 (cli/create_model_hub.py:255-261)
+        print(f"error: {err}", file=sys.stderr)
+        if a.verbose:
+            import traceback
+
+            traceback.print_exc()
+        return 1
+    print(f"model directory written to {out}")
+    return 0
+
+
+def _create(a, create_model_hub):
+    return create_model_hub(
         output_dir=a.output_dir, model_file=a.model_file, config_name=a.config_name, vocab_file=a.vocab_file,
         chat_template_file=a.chat_template, model_name=a.model_name, description=a.description, n_layer=a.n_layer,
         n_embd=a.n_embd, vocab_size=a.vocab_size, head_size_a=a.head_size_a, ctx_len=a.ctx_len,
         dim_att_lora=a.dim_att_lora, dim_gate_lora=a.dim_gate_lora, dim_mv_lora=a.dim_mv_lora,
         temperature=a.temperature, top_p=a.top_p, top_k=a.top_k, repetition_penalty=a.repetition_penalty,
         max_length=a.max_length, eos_token=a.eos_token, model_max_length=a.model_max_length,
-        copy_weights=not a.no_copy, save_format=a.save_format, overwrite=a.overwrite)
-    print(f"model directory written to {out}")
-    return 0
+        copy_weights=not a.link_weights, save_format=a.save_format, overwrite=a.overwrite)
 
 
 if __name__ == "__main__":
