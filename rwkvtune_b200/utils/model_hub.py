@@ -71,7 +71,6 @@ def create_model_hub(output_dir: str, model_file: Optional[str] = None, config_n
                      overwrite: bool = False) -> str:
     if os.path.exists(output_dir) and os.listdir(output_dir) and not overwrite:
         raise FileExistsError(f"{output_dir} exists and is not empty (pass overwrite=True)")
-    os.makedirs(output_dir, exist_ok=True)
     arch: Dict[str, Any] = {}
     if config_name:
         arch.update(load_model_config(config_name).to_train_config_dict())
@@ -85,6 +84,7 @@ def create_model_hub(output_dir: str, model_file: Optional[str] = None, config_n
     if "n_layer" not in arch or "n_embd" not in arch:
         raise ValueError("architecture unknown: give config_name, config_dict, n_layer/n_embd or a readable model_file")
     cfg = RWKVConfig.from_dict(arch)
+    os.makedirs(output_dir, exist_ok=True)      # only once the architecture is known: a failed call leaves nothing
     cfg.save_pretrained(output_dir)
     GenerationConfig(temperature=temperature, top_p=top_p, top_k=top_k, repetition_penalty=repetition_penalty,
                      max_length=max_length).save_pretrained(output_dir)
