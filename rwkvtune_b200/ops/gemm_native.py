@@ -2,7 +2,8 @@
 
 ``native_ok`` states which problems the kernel takes: bf16 CUDA tensors, 16-byte aligned rows
 (every leading dimension a multiple of 8 elements) and sizes large enough that a 128x256 tile is
-not mostly padding.  Everything else goes to the library GEMM.
+not mostly padding.  Weight-gradient products with few output tiles and a long contraction take the kernel's
+split-K path (``splitk_plan`` / ``mm_tn_splitk``).  Everything else goes to the library GEMM.
 """
 from __future__ import annotations
 
@@ -54,7 +55,7 @@ def native_ok(x: torch.Tensor, w: torch.Tensor, layout: str) -> bool:
     if not (M >= MIN_M and N >= MIN_N and K >= MIN_K and N % 8 == 0):
         return False
     tiles = -(-M // 128) * -(-N // 256)
-    # a long contraction spread over few output tiles needs split-K, which this kernel does not do
+    # a long contraction spread over few output tiles belongs to the split-K path (see splitk_plan)
     return tiles >= 64 or K <= 4096
 
 

@@ -71,3 +71,17 @@ def test_embedding_and_gather_rows():
     assert torch.equal(ops.embedding(idx, table), F.embedding(idx, table))
     sel = torch.tensor([4, 4, 0, 49])
     assert torch.equal(ops.gather_rows(table, sel), table.index_select(0, sel))
+
+
+def test_gemm_wrappers_fall_back_on_cpu():
+    """On CPU tensors the GEMM wrappers are the plain products and the split-K planner declines."""
+    import torch
+    from rwkvtune_b200.ops import gemm, gemm_native
+    torch.manual_seed(0)
+    a, b = torch.randn(40, 6), torch.randn(40, 10)
+    assert gemm_native.splitk_plan(a.bfloat16(), b.bfloat16()) == 0
+    assert torch.allclose(gemm.mm_tn(a, b), a.t() @ b)
+    y = torch.ones(6, 10)
+    assert gemm.addmm_tn_(y, a, b) is y and torch.allclose(y, 1 + a.t() @ b, atol=1e-5)
+    x, w = torch.randn(5, 6), torch.randn(7, 6)
+    assert torch.allclose(gemm.mm_nt(x, w), x @ w.t()) and torch.allclose(gemm.mm_nn(x, w.t().contiguous()), x @ w.t())
