@@ -219,3 +219,36 @@ def test_repeat_batch_sampler_wraps_a_batch_sampler():
         raise AssertionError("expected ValueError")
     except ValueError:
         pass
+
+
+def test_public_names_of_the_reference_are_importable():
+    import importlib
+    expected = {
+        "rwkvtune_b200": ["AutoModel", "AutoTokenizer", "GRPOConfig", "GRPOTrainer", "GenerationConfig", "LoraConfig",
+                          "PretrainConfig", "PretrainTrainer", "RWKV7Config", "RWKV7Model",
+                          "RWKV7_DEFAULT_TARGET_MODULES", "RWKVConfig", "RWKVTokenizer", "SFTConfig", "SFTTrainer",
+                          "TRIE_TOKENIZER", "__author__", "__license__", "__version__", "create_model_hub",
+                          "get_peft_model", "get_tokenizer", "is_peft_model", "load_peft_model"],
+        "rwkvtune_b200.inference": ["InferencePipeline", "TextGenerator", "BatchGenerator", "GenerationConfig",
+                                    "GRPOBatchGenerator", "TokenSampler", "SchedulerCore", "SequenceState", "SeqStatus",
+                                    "create_scheduler_core", "JsonSchemaEnforcer", "JsonObjectEnforcer",
+                                    "create_enforcer", "is_structured_output_available", "StateCache", "CacheConfig",
+                                    "CacheLevel", "create_state_cache"],
+        "rwkvtune_b200.training": ["PretrainConfig", "PretrainTrainer", "SFTConfig", "SFTTrainer", "GRPOConfig",
+                                   "GRPOTrainer"],
+        "rwkvtune_b200.peft": ["LoraConfig", "get_peft_model", "is_peft_model", "load_peft_model",
+                               "RWKV7_DEFAULT_TARGET_MODULES"],
+        "rwkvtune_b200.models": ["RWKVConfig", "GenerationConfig", "AutoModel", "RWKV7Model", "RWKV7Config",
+                                 "GenerationMixin"],
+        "rwkvtune_b200.models.rwkv7.operators": ["load_wkv_operator", "rwkv7_wkv", "load_wkv7_operator",
+                                                 "load_cpu_operator", "load_cuda_operator_train",
+                                                 "load_cuda_operator_inference", "load_cuda_operator_infctx"],
+        "rwkvtune_b200.configs": ["load_model_config", "list_available_models", "print_model_info", "ModelConfig"],
+        "rwkvtune_b200.training.model_save_utils": ["save_model_with_config", "save_model_checkpoint",
+                                                    "get_lora_state_dict", "save_lora_checkpoint",
+                                                    "save_checkpoint_with_lora_support"],
+    }
+    for module, names in expected.items():
+        mod = importlib.import_module(module)
+        missing = [n for n in names if not hasattr(mod, n)]
+        assert not missing, f"{module} lacks {missing}"
