@@ -63,7 +63,7 @@ def run_reference(a) -> None:
         return _unavailable("no CUDA device")
     import torch.distributed as dist
 
-    from bench import MODELS, PUBLISHED_TOK_S, ClockSampler
+    from bench import MODELS, ClockSampler, vs_baseline
 
     rank, local_rank, world = (int(os.environ.get(k, d)) for k, d in (("RANK", 0), ("LOCAL_RANK", 0), ("WORLD_SIZE", 1)))
     if world != a.gpus:
@@ -95,11 +95,21 @@ def run_reference(a) -> None:
     with torch.device(dev):
         model = RWKV7Model(cfg)
     model.train()
+    mode = getattr(a, "ref_mode", "autocast")
+    if mode == "bf16_master":   # bf16 module + fp32 master weights: the DeepSpeed stage-2 precision regime
+        model.to(torch.bfloat16)
     net = model
     if world > 1:
         net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local_rank], gradient_as_bucket_view=True)
-    decay = [p for n, p in model.named_parameters() if p.ndim >= 2 and ".weight" in n]
-    other = [p for n, p in model.named_parameters() if not (p.ndim >= 2 and ".weight" in n)]
+    named = list(model.named_parameters())
+    masters = None
+    if mode == "bf16_master":
+        masters = [torch.nn.Parameter(p.detach().float().clone()) for _, p in named]
+        opt_named = [(n, m) for (n, _), m in zip(named, masters)]
+    else:
+        opt_named = named
+    decay = [p for n, p in opt_named if p.ndim >= 2 and ".weight" in n]
+    other = [p for n, p in opt_named if not (p.ndim >= 2 and ".weight" in n)]
     opt = torch.optim.AdamW([{"params": other, "weight_decay": 0.0}, {"params": decay, "weight_decay": 0.01}],
                             lr=3e-4, betas=(0.9, 0.99), eps=1e-8, fused=True)
     crit = torch.nn.CrossEntropyLoss(ignore_index=-100)
@@ -115,6 +125,16 @@ def run_reference(a) -> None:
             loss = crit(logits.view(-1, logits.size(-1)), lab.view(-1))
             loss = L2Wrap.apply(loss, logits)
         loss.backward()
+        if masters is not None:
+            for (_, p), m in zip(named, masters):
+                m.grad = p.grad.float()
+                p.grad = None
+            torch.nn.utils.clip_grad_norm_(masters, 1.0)
+            opt.step()
+            opt.zero_grad(set_to_none=True)
+            with torch.no_grad():
+                torch._foreach_copy_([p for _, p in named], masters)
+            return loss.detach()
         torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
         opt.step()
         opt.zero_grad(set_to_none=True)
@@ -164,13 +184,15 @@ def run_reference(a) -> None:
         print(json.dumps({
             "metric": "train_tokens_per_sec", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": a.steps,
             "warmup": a.warmup, "ms_per_step": ms / a.steps, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": value / PUBLISHED_TOK_S[a.model], "dtype": "bf16", "data": "synthetic", "impl": "reference",
+            "vs_baseline": vs_baseline(a.model, value, world), "dtype": "bf16", "data": "synthetic", "impl": "reference",
             "final_loss": final_loss,
             "harness": "unmodified reference RWKV7Model + its JIT WKV7 CUDA kernels + CrossEntropy/L2Wrap step body; "
-                       "fp32 params under bf16 autocast, torch AdamW(fused), DDP for N>1 "
+                       + ("bf16 module with fp32 master weights, " if mode == "bf16_master" else "fp32 params under bf16 autocast, ")
+                       + "torch AdamW(fused), DDP for N>1 "
                        "(lightning and deepspeed are not installable offline)",
             "config": {"model": f"rwkv7-{a.model}", "global_batch": B * world, "seq_len": T,
-                       "parallelism": f"ddp{world}" if world > 1 else "single", "grad_cp": a.grad_cp},
+                       "parallelism": f"dp{world}", "grad_cp": a.grad_cp},
+            "details": {"sharding": "ddp" if world > 1 else "none", "ref_mode": mode},
             "clocks": clocks,
             "e2e": {"value": tokens / (ms_e2e / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": 2 * B * T * 8,
                     "d2h_bytes_per_step": 4},
