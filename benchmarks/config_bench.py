@@ -24,7 +24,8 @@ sys.path.insert(0, ROOT)
 
 from bench import MODELS  # noqa: E402
 
-NVLINK_GBS = 770.0    # measured peer copy bandwidth per direction per GPU on this machine class
+NVLINK_GBS = 770.0           # rate of a plain peer-to-peer copy, per direction per GPU, measured on this machine class
+NVLINK_NOMINAL_GBS = 900.0   # NVLink 5: 18 links, per direction per GPU
 
 
 def _ctx():
@@ -195,7 +196,10 @@ def bench_grpo(a):
 
 
 def bench_collectives(a):
-    """Fused ZeRO-2 kernels on the 1.5B flat parameter space: bytes that must cross NVLink / time vs 770 GB/s."""
+    """Fused ZeRO-2 kernels on the 1.5B flat parameter space: bytes that must cross NVLink per rank and direction over
+    the kernel's time, as a fraction of the link's nominal 900 GB/s and of the 770 GB/s a plain peer copy reaches on
+    this pool; then the same kernels inside real training steps, with the bucketed reduce-scatter overlapped with
+    backward and without, to show how much communication is left exposed after backward."""
     from rwkvtune_b200.engine import EngineConfig, TrainEngine
     from rwkvtune_b200.models import RWKVConfig, RWKV7Model
     from rwkvtune_b200.ops import _ext
@@ -207,11 +211,13 @@ def bench_collectives(a):
     torch.manual_seed(7)
     with torch.device(ctx.device):
         model = RWKV7Model(cfg)
-    eng = TrainEngine(model, EngineConfig(lr_init=1e-4, strategy="deepspeed_stage_2", precision="bf16", transport="p2p"), ctx)
+    eng = TrainEngine(model, EngineConfig(lr_init=1e-4, weight_decay=0.01, strategy="deepspeed_stage_2", precision="bf16",
+                                          transport="p2p", grad_cp=1), ctx)
     fz, opt, sp = eng.opt._p2p, eng.opt, eng.space
     sp.grads.normal_(0, 1e-3)
     W = ctx.world_size
     shard = opt.hi - opt.lo
+    scratch = torch.zeros(1024, dtype=torch.float32, device=ctx.device)
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
     acc = [0.0, 0.0, 0.0]
     iters = a.warmup + a.steps
@@ -220,7 +226,8 @@ def bench_collectives(a):
         fz._barrier()
         ev[0].record()
         _ext.call("rwkv_zero2_reduce_scatter", fz.grad_ptrs, fz.ctrl_ptrs, _ext.i32(fz.rank), _ext.i32(W), _ext.i64(opt.lo),
-                  _ext.i64(shard), _ext.f32(1.0 / W), _ext.ptr(fz.gred), _ext.ptr(fz.scratch), _ext.stream())
+                  _ext.i64(shard), _ext.f32(1.0 / W), _ext.ptr(fz.gred), _ext.ptr(scratch), _ext.ptr(fz.status),
+                  _ext.stream())
         ev[1].record()
         fz._barrier()
         ev[2].record()
@@ -231,7 +238,7 @@ def bench_collectives(a):
                       _ext.i64(e - s), _ext.ptr(opt.master[lo:hi]), _ext.ptr(opt.exp_avg[lo:hi]),
                       _ext.ptr(opt.exp_avg_sq[lo:hi]), _ext.ptr(fz.gred[lo:hi]), _ext.f32(1e-6 * grp.lr_scale),
                       _ext.f32(opt.beta1), _ext.f32(opt.beta2), _ext.f32(opt.eps), _ext.f32(grp.weight_decay),
-                      _ext.i32(opt.step_count), _ext.f32(opt.grad_clip), _ext.stream())
+                      _ext.i32(opt.step_count), _ext.f32(opt.grad_clip), _ext.ptr(fz.status), _ext.stream())
         ev[3].record()
         fz._barrier()
         torch.cuda.synchronize()
@@ -239,18 +246,48 @@ def bench_collectives(a):
             acc[0] += ev[0].elapsed_time(ev[1])
             acc[1] += ev[2].elapsed_time(ev[3])
             acc[2] += ev[0].elapsed_time(ev[3])
-    fz.check()
+    fz.check_now()
     rs_ms, ab_ms, all_ms = (_max_over_ranks(ctx, x / a.steps) for x in acc)
     link_bytes = (W - 1) * shard * 2          # bf16 shard pulled from / pushed to each of W-1 peers
     hbm_adam = shard * (3 * 4 * 2 + 4 + 2)     # master, m, v read+write (fp32), reduced grad read, bf16 param write
-    return ctx, {"metric": "fused_zero2_fraction_of_nvlink_roofline", "value": link_bytes / (rs_ms * 1e-3) / 1e9 / NVLINK_GBS,
-                 "reduce_scatter_ms": rs_ms, "reduce_scatter_gbs_in": link_bytes / (rs_ms * 1e-3) / 1e9,
-                 "reduce_scatter_frac_of_770": link_bytes / (rs_ms * 1e-3) / 1e9 / NVLINK_GBS,
-                 "adam_broadcast_ms": ab_ms, "adam_broadcast_gbs_out": link_bytes / (ab_ms * 1e-3) / 1e9,
-                 "adam_broadcast_frac_of_770": link_bytes / (ab_ms * 1e-3) / 1e9 / NVLINK_GBS,
+    rs_gbs, ab_gbs = link_bytes / (rs_ms * 1e-3) / 1e9, link_bytes / (ab_ms * 1e-3) / 1e9
+
+    # ---- inside training steps: time from "backward done" to "parameters published", overlap on and off
+    B, T = 8, 4096
+    ids = torch.randint(0, 65536, (B, T), device=ctx.device)
+    exposed = {}
+    for tag, overlap in (("overlap", True), ("serial", False)):
+        fz.overlap = overlap
+        for _ in range(2):
+            eng.train_step(ids, ids, 1e-6)
+        fz.timing = []
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ctx.barrier()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(a.steps):
+            eng.train_step(ids, ids, 1e-6)
+        e1.record()
+        torch.cuda.synchronize()
+        tail = sum(x.elapsed_time(y) for x, y in fz.timing) / max(len(fz.timing), 1)
+        fz.timing = None
+        exposed[f"step_ms_{tag}"] = _max_over_ranks(ctx, e0.elapsed_time(e1) / a.steps)
+        exposed[f"after_backward_ms_{tag}"] = _max_over_ranks(ctx, tail)
+    eng.check_health()
+    return ctx, {"metric": "fused_zero2_fraction_of_nvlink_roofline", "value": rs_gbs / NVLINK_NOMINAL_GBS,
+                 "reduce_scatter_ms": rs_ms, "reduce_scatter_gbs_in": rs_gbs,
+                 "reduce_scatter_frac_of_900_nominal": rs_gbs / NVLINK_NOMINAL_GBS,
+                 "reduce_scatter_frac_of_770_measured_peer_copy": rs_gbs / NVLINK_GBS,
+                 "adam_broadcast_ms": ab_ms, "adam_broadcast_gbs_out": ab_gbs,
+                 "adam_broadcast_frac_of_900_nominal": ab_gbs / NVLINK_NOMINAL_GBS,
+                 "adam_broadcast_frac_of_770_measured_peer_copy": ab_gbs / NVLINK_GBS,
+                 "adam_broadcast_hbm_floor_ms": hbm_adam / 6548.8e9 * 1e3,
                  "whole_step_ms": all_ms, "link_bytes_per_phase": link_bytes, "adam_hbm_bytes": hbm_adam,
+                 "buckets": fz.n_buckets, "reduce_launches_this_rank": len(fz.launch_of_bucket), **exposed,
                  "config": {"model": "rwkv7-1.5b", "elements": int(sp.padded), "shard_elements": int(shard),
-                            "parallelism": f"zero2-dp{W}", "roofline": "bytes over NVLink per direction / 770 GB/s measured"}}
+                            "parallelism": f"zero2-dp{W}", "global_batch": B * W, "seq_len": T,
+                            "roofline": "bytes over NVLink per rank and direction / 900 GB/s nominal; 770 GB/s is the "
+                                        "rate of a plain peer-to-peer copy measured on this pool"}}
 
 
 def main():

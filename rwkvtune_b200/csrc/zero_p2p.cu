@@ -4,9 +4,16 @@
 // (phase B).  Data moves by plain peer loads/stores issued from inside the kernels on buffers
 // that every rank has mapped (symmetric memory); no NCCL call is on this path.
 //
-// Cross-rank ordering uses flag words in a small symmetric control block:
-//   ctrl[r] (int32 [MAX_RANKS])  flags:  slot p of rank r's block is written by rank p
-//   ctrl[r] + 64 (float [MAX_RANKS])     slot p holds rank p's squared-norm partial
+// Cross-rank ordering uses flag words in a small symmetric control block (int32 words):
+//   ctrl[r][0 .. 16)             barrier flags: slot p of rank r's block is written by rank p
+//   ctrl[r][64 .. 80)  (float)   slot p holds rank p's squared-norm partial
+//   ctrl[r][128 + 16 b + p]      "bucket b of rank p's gradients is complete" (epoch value), b < MAX_BUCKETS
+// Gradient buckets make the reduce-scatter overlap with backward: as soon as the last gradient of a bucket has been
+// written, the rank raises the bucket's flag in every peer's block (rwkv_p2p_signal, on the compute stream) and the
+// owner of that range reduces it on a side stream after a bounded wait for all ranks' flags (rwkv_p2p_wait +
+// rwkv_zero2_reduce_bucket), while backward continues with the next layers.
+// Every data kernel reads the status word first and returns without writing when a wait has expired earlier in
+// the step, so a timed-out step changes neither gradients-in-flight nor parameters ("poisoned step").
 // A barrier stores a monotonically increasing epoch into slot `rank` of every peer's block with
 // release semantics at system scope and then waits, with a globaltimer deadline, until all slots
 // of its own block have reached the epoch.  A wait that expires records a code in `status` and
@@ -57,26 +64,68 @@ __global__ void p2p_barrier_kernel(PeerPtrs ctrl, int rank, int world, int epoch
   }
 }
 
-// Phase A.  out[i] = scale * sum_p grad_p[lo + i]  (fp32, fixed rank order); partial[b] = sum of out^2.
+// One block; thread t raises flag word `word + rank` in rank t's control block.
+__global__ void p2p_signal_kernel(PeerPtrs ctrl, int rank, int world, int word, int value) {
+  const int t = threadIdx.x;
+  if (t >= world) return;
+  __threadfence_system();
+  st_release_sys(reinterpret_cast<int*>(ctrl.p[t]) + word + rank, value);
+}
+
+// One block; thread t waits (bounded) until flag word `word + t` of this rank's block has reached `value`.
+__global__ void p2p_wait_kernel(PeerPtrs ctrl, int rank, int world, int word, int value, int* status,
+                                unsigned long long timeout_ns) {
+  const int t = threadIdx.x;
+  if (t >= world) return;
+  const int* mine = reinterpret_cast<const int*>(ctrl.p[rank]) + word + t;
+  const unsigned long long deadline = globaltimer_ns() + timeout_ns;
+  while (ld_acquire_sys(mine) < value) {
+    if (globaltimer_ns() > deadline) {
+      atomicCAS(status, 0, RWKV_ERR_WAIT_TIMEOUT * 100 + t);
+      return;
+    }
+    __nanosleep(64);
+  }
+}
+
+// Phase A.  out[i] (+)= scale * sum_p grad_p[lo + i]  (fp32, fixed rank order); partial[b] = sum of out^2.
+// With `accumulate` the reduced micro-batch gradient is added to what `out` holds (fp32 accumulation of
+// micro-batches on the owner) and the norm partial is taken of the accumulated value.
 __global__ void __launch_bounds__(256)
 zero2_reduce_kernel(PeerPtrs grads, int world, size_t lo, size_t n, float scale, float* __restrict__ out,
-                    float* __restrict__ partial) {
+                    float* __restrict__ partial, int accumulate, const int* __restrict__ status) {
   __shared__ float red[8];
+  if (status && *reinterpret_cast<const volatile int*>(status)) return;   // poisoned step: touch nothing
   float acc = 0.f;
   const size_t n8 = n / 8;
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
     float s[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    for (int p = 0; p < world; ++p) {
-      const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(grads.p[p]) + lo) + i);
-      float f[8];
-      unpack8(raw, f);
+    uint4 raw[MAX_RANKS];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) s[e] += f[e];
+    for (int p = 0; p < MAX_RANKS; ++p)    // all peers' loads in flight before the first add
+      if (p < world) raw[p] = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(grads.p[p]) + lo) + i);
+#pragma unroll
+    for (int p = 0; p < MAX_RANKS; ++p) {
+      if (p < world) {
+        float f[8];
+        unpack8(raw[p], f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) s[e] += f[e];
+      }
+    }
+    float4* o4 = reinterpret_cast<float4*>(out + i * 8);
+    if (accumulate) {
+      const float4 a0 = o4[0], a1 = o4[1];
+      s[0] = s[0] * scale + a0.x; s[1] = s[1] * scale + a0.y; s[2] = s[2] * scale + a0.z; s[3] = s[3] * scale + a0.w;
+      s[4] = s[4] * scale + a1.x; s[5] = s[5] * scale + a1.y; s[6] = s[6] * scale + a1.z; s[7] = s[7] * scale + a1.w;
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) s[e] *= scale;
     }
 #pragma unroll
-    for (int e = 0; e < 8; ++e) { s[e] *= scale; acc += s[e] * s[e]; }
-    reinterpret_cast<float4*>(out + i * 8)[0] = make_float4(s[0], s[1], s[2], s[3]);
-    reinterpret_cast<float4*>(out + i * 8)[1] = make_float4(s[4], s[5], s[6], s[7]);
+    for (int e = 0; e < 8; ++e) acc += s[e] * s[e];
+    o4[0] = make_float4(s[0], s[1], s[2], s[3]);
+    o4[1] = make_float4(s[4], s[5], s[6], s[7]);
   }
   acc = warp_sum(acc);
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
@@ -91,9 +140,10 @@ zero2_reduce_kernel(PeerPtrs grads, int world, size_t lo, size_t n, float scale,
 // Sums the block partials and publishes this rank's squared-norm partial into slot `rank` of every
 // rank's control block.
 __global__ void __launch_bounds__(256)
-zero2_publish_norm_kernel(const float* __restrict__ partial, int nblocks, PeerPtrs ctrl, int rank, int world) {
+zero2_publish_norm_kernel(const float* __restrict__ partial, int nblocks, PeerPtrs ctrl, int rank, int world,
+                          const float* __restrict__ extra) {
   __shared__ float red[8];
-  float acc = 0.f;
+  float acc = (extra && threadIdx.x == 0) ? extra[0] : 0.f;   // squared norm of gradients reduced elsewhere
   for (int i = threadIdx.x; i < nblocks; i += 256) acc += partial[i];
   acc = warp_sum(acc);
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
@@ -116,7 +166,8 @@ struct AdamArgs {
 __global__ void __launch_bounds__(256)
 zero2_adam_bcast_kernel(PeerPtrs params, int world, const float* __restrict__ my_norms, size_t flat0, size_t seg,
                         float* __restrict__ master, float* __restrict__ m, float* __restrict__ v,
-                        const float* __restrict__ gred, AdamArgs a) {
+                        const float* __restrict__ gred, AdamArgs a, const int* __restrict__ status) {
+  if (status && *reinterpret_cast<const volatile int*>(status)) return;   // poisoned step: parameters stay as they are
   float coef = 1.f;
   if (a.clip > 0.f) {
     float nsq = 0.f;
@@ -175,29 +226,74 @@ RWKV_EXPORT int rwkv_p2p_barrier(const unsigned long long* ctrl_ptrs, int rank, 
   return rwkv_launch_status();
 }
 
-// Phase A: reduced fp32 gradients of [lo, lo + n) into `out`, this rank's squared norm published to all ranks.
-// `scratch` needs 1024 floats.  n must be a multiple of 8 and lo a multiple of 8.
-RWKV_EXPORT int rwkv_zero2_reduce_scatter(const unsigned long long* grad_ptrs, const unsigned long long* ctrl_ptrs,
-                                          int rank, int world, long long lo, long long n, float scale, void* out,
-                                          void* scratch, void* stream) {
-  PeerPtrs g, c;
+// Raise flag word `word + rank` (0 <= word, word + world <= control block size) in every rank's control block.
+RWKV_EXPORT int rwkv_p2p_signal(const unsigned long long* ctrl_ptrs, int rank, int world, int word, int value,
+                                void* stream) {
+  PeerPtrs c;
+  int r = fill_ptrs(&c, ctrl_ptrs, world);
+  if (r) return r;
+  if (rank < 0 || rank >= world || word < 0) return RWKV_ERR_BAD_SHAPE;
+  p2p_signal_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(c, rank, world, word, value);
+  return rwkv_launch_status();
+}
+
+// Wait until flag words `word .. word + world` of this rank's block have all reached `value`; on expiry
+// `status` receives 500 + the rank that was missing.
+RWKV_EXPORT int rwkv_p2p_wait(const unsigned long long* ctrl_ptrs, int rank, int world, int word, int value,
+                              void* status, long long timeout_ns, void* stream) {
+  PeerPtrs c;
+  int r = fill_ptrs(&c, ctrl_ptrs, world);
+  if (r) return r;
+  if (rank < 0 || rank >= world || word < 0 || timeout_ns <= 0 || !status) return RWKV_ERR_BAD_SHAPE;
+  p2p_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(c, rank, world, word, value, (int*)status,
+                                                      (unsigned long long)timeout_ns);
+  return rwkv_launch_status();
+}
+
+// Phase A on one range: out[0 .. n) (+)= scale * sum over ranks of grads[lo .. lo + n); `partial` receives `blocks`
+// floats (block sums of out^2).  n and lo multiples of 8; 1 <= blocks <= 1024.  `status` (may be null): the step's
+// status word; when it is non-zero the kernel writes nothing.
+RWKV_EXPORT int rwkv_zero2_reduce_bucket(const unsigned long long* grad_ptrs, int world, long long lo, long long n,
+                                         float scale, void* out, void* partial, int blocks, int accumulate,
+                                         const void* status, void* stream) {
+  PeerPtrs g;
   int r = fill_ptrs(&g, grad_ptrs, world);
   if (r) return r;
-  r = fill_ptrs(&c, ctrl_ptrs, world);
-  if (r) return r;
   if (n <= 0 || (n & 7) || (lo & 7)) return RWKV_ERR_BAD_ALIGNMENT;
-  const int blocks = 1024;
-  cudaStream_t st = (cudaStream_t)stream;
-  zero2_reduce_kernel<<<blocks, 256, 0, st>>>(g, world, (size_t)lo, (size_t)n, scale, (float*)out, (float*)scratch);
-  zero2_publish_norm_kernel<<<1, 256, 0, st>>>((const float*)scratch, blocks, c, rank, world);
+  if (blocks <= 0 || blocks > 1024) return RWKV_ERR_BAD_SHAPE;
+  zero2_reduce_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(g, world, (size_t)lo, (size_t)n, scale, (float*)out,
+                                                                (float*)partial, accumulate, (const int*)status);
   return rwkv_launch_status();
+}
+
+// Sum `n_partials` block partials (+ `extra[0]` when given) and publish the result as this rank's squared-norm
+// share in every rank's control block.
+RWKV_EXPORT int rwkv_zero2_publish_norm(const void* partial, int n_partials, const void* extra,
+                                        const unsigned long long* ctrl_ptrs, int rank, int world, void* stream) {
+  PeerPtrs c;
+  int r = fill_ptrs(&c, ctrl_ptrs, world);
+  if (r) return r;
+  if (n_partials < 0 || rank < 0 || rank >= world) return RWKV_ERR_BAD_SHAPE;
+  zero2_publish_norm_kernel<<<1, 256, 0, (cudaStream_t)stream>>>((const float*)partial, n_partials, c, rank, world,
+                                                                 (const float*)extra);
+  return rwkv_launch_status();
+}
+
+// Phase A in one call (whole shard, no buckets): reduced fp32 gradients of [lo, lo + n) into `out`, this rank's
+// squared norm published to all ranks.  `scratch` needs 1024 floats.  n and lo must be multiples of 8.
+RWKV_EXPORT int rwkv_zero2_reduce_scatter(const unsigned long long* grad_ptrs, const unsigned long long* ctrl_ptrs,
+                                          int rank, int world, long long lo, long long n, float scale, void* out,
+                                          void* scratch, const void* status, void* stream) {
+  int r = rwkv_zero2_reduce_bucket(grad_ptrs, world, lo, n, scale, out, scratch, 1024, 0, status, stream);
+  if (r) return r;
+  return rwkv_zero2_publish_norm(scratch, 1024, nullptr, ctrl_ptrs, rank, world, stream);
 }
 
 // Phase B on one segment.  flat0: offset of the segment in the flat parameter space (multiple of 8).
 RWKV_EXPORT int rwkv_zero2_adam_broadcast(const unsigned long long* param_ptrs, const unsigned long long* ctrl_ptrs,
                                           int rank, int world, long long flat0, long long seg, void* master, void* m,
                                           void* v, const void* gred, float lr, float beta1, float beta2, float eps,
-                                          float weight_decay, int step, float clip, void* stream) {
+                                          float weight_decay, int step, float clip, const void* status, void* stream) {
   PeerPtrs p;
   int r = fill_ptrs(&p, param_ptrs, world);
   if (r) return r;
@@ -212,6 +308,6 @@ RWKV_EXPORT int rwkv_zero2_adam_broadcast(const unsigned long long* param_ptrs, 
   const int blocks = (int)((n8 + 255) / 256 < 148 * 8 ? (n8 + 255) / 256 : 148 * 8);
   zero2_adam_bcast_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(p, world, norms, (size_t)flat0, (size_t)seg,
                                                                     (float*)master, (float*)m, (float*)v,
-                                                                    (const float*)gred, a);
+                                                                    (const float*)gred, a, (const int*)status);
   return rwkv_launch_status();
 }

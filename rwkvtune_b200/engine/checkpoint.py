@@ -53,24 +53,39 @@ def save_trainer_state(dirpath: str, engine, ctx, extra_meta: Dict[str, Any], sa
 
 
 def atomic_checkpoint(final_dir: str, ctx, write_fn) -> None:
-    """Run ``write_fn(tmp_dir)`` on every rank, then publish ``tmp_dir`` as ``final_dir`` atomically."""
+    """Run ``write_fn(tmp_dir)`` on every rank, then publish ``tmp_dir`` as ``final_dir``.
+
+    The directory is published only if **every** rank wrote its part: the ranks agree on a success flag
+    (a host-side MIN-reduction) between the writes and the rename, so a rank that failed to write its optimiser
+    shard (disk full, I/O error) vetoes the checkpoint instead of leaving one with a missing shard.  An existing
+    ``final_dir`` is renamed aside first and deleted only after the new one is in place; on a veto the temporary
+    directory is removed, the old checkpoint stays, and every rank raises."""
     tmp = final_dir + ".tmp"
+    old = final_dir + ".old"
     if ctx.rank == 0:
         shutil.rmtree(tmp, ignore_errors=True)
         os.makedirs(tmp, exist_ok=True)
     _barrier(ctx)
-    ok = True
+    error: Optional[BaseException] = None
     try:
         write_fn(tmp)
-    except Exception:
-        ok = False
-        raise
-    finally:
-        _barrier(ctx)   # reached on failure too, so the other ranks do not hang
-        if ok and ctx.rank == 0:
-            shutil.rmtree(final_dir, ignore_errors=True)
+    except Exception as exc:   # the other ranks must still reach the agreement below
+        error = exc
+    everyone_ok = ctx.all_agree(error is None)
+    if ctx.rank == 0:
+        if everyone_ok:
+            shutil.rmtree(old, ignore_errors=True)
+            if os.path.exists(final_dir):
+                os.replace(final_dir, old)
             os.replace(tmp, final_dir)
-        _barrier(ctx)
+            shutil.rmtree(old, ignore_errors=True)
+        else:
+            shutil.rmtree(tmp, ignore_errors=True)
+    _barrier(ctx)
+    if error is not None:
+        raise error
+    if not everyone_ok:
+        raise RuntimeError(f"checkpoint {final_dir} was not published: another rank failed to write its part")
 
 
 def rotate_checkpoints(proj_dir: str, keep: int, pattern: str = "rwkv7-*") -> List[str]:
@@ -110,6 +125,22 @@ def read_meta(ckpt_dir: str) -> Dict[str, Any]:
         return json.load(fh)
 
 
+def check_shards(shards: List[Dict[str, Any]], where: str = "") -> None:
+    """A sharded optimiser state is usable only if every rank's file is there and the owned ranges tile the flat
+    space without gaps: one file per saved rank, ``lo`` of each shard equal to ``hi`` of the previous one."""
+    world = int(shards[0]["world_size"])
+    if len(shards) != world:
+        raise RuntimeError(f"{where}: optimiser state was saved by {world} ranks but {len(shards)} shard files exist")
+    ordered = sorted(shards, key=lambda s: s["lo"])
+    pos = 0
+    for s in ordered:
+        if int(s["lo"]) != pos:
+            raise RuntimeError(f"{where}: optimiser shards do not tile the parameter space (gap or overlap at {pos})")
+        pos = int(s["hi"])
+    if pos != int(ordered[0]["padded"]):
+        raise RuntimeError(f"{where}: optimiser shards end at {pos}, expected {ordered[0]['padded']}")
+
+
 def load_optimizer_state(ckpt_dir: str, engine, ctx) -> bool:
     """Restore master weights and Adam moments, re-sharding if the world size changed."""
     meta = read_meta(ckpt_dir)
@@ -124,6 +155,8 @@ def load_optimizer_state(ckpt_dir: str, engine, ctx) -> bool:
     shards = [torch.load(f, map_location="cpu", weights_only=False) for f in files]
     if shards[0]["stage"] == 0:
         shards = shards[:1]
+    else:
+        check_shards(shards, ckpt_dir)
     master, m, v, step = merge_shards(shards)
     dev = engine.space.device
     engine.opt.load_full_state(master.to(dev), m.to(dev), v.to(dev), step)

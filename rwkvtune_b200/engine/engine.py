@@ -102,6 +102,7 @@ class TrainEngine:
         self.optimizer_steps = 0
         self.tokens_seen = 0
         self._graphs: Dict[tuple, dict] = {}
+        self.guard = None
 
     # ------------------------------------------------------------------ memory-aware checkpointing
     SAVED_UNITS_PER_LAYER = 37.0   # [tokens, n_embd] bf16 tensors a block keeps for backward without checkpointing
@@ -253,17 +254,20 @@ class TrainEngine:
         ``accumulate_grad_batches`` calls.  Returns the detached loss (device tensor)."""
         acc = self.cfg.accumulate_grad_batches
         scale = 1.0 / acc
+        boundary = (self.micro_step + 1) % acc == 0
         if self.cfg.train_type == "infctx":
             loss = self._step_infctx(idx, labels, scale)
         elif self._graph_ok():
             loss = self._graph_step_normal(idx, labels, scale)
         else:
             loss = self._loss_normal(idx, labels)
+            self.opt.arm()          # gradient buckets are reduced while backward is still running
             (loss * scale if acc > 1 else loss).backward()
             loss = loss.detach()
+        self.opt.finish_micro(boundary)
         self.micro_step += 1
         self.tokens_seen += idx.numel()
-        if self.micro_step % acc == 0:
+        if boundary:
             self.opt.step(lr)
             self.opt.zero_grad()
             self.optimizer_steps += 1
@@ -274,9 +278,11 @@ class TrainEngine:
         """Back-propagate an externally computed loss (already a mean over the micro-batch) and run the
         optimiser on accumulation boundaries.  Returns True when an optimiser step happened."""
         acc = self.cfg.accumulate_grad_batches
+        boundary = (self.micro_step + 1) % acc == 0
         (loss / acc if acc > 1 else loss).backward()
+        self.opt.finish_micro(boundary)
         self.micro_step += 1
-        if self.micro_step % acc == 0:
+        if boundary:
             self.opt.step(lr)
             self.opt.zero_grad()
             self.optimizer_steps += 1
@@ -285,7 +291,49 @@ class TrainEngine:
         return False
 
     def train_step_from_host(self, idx_cpu: torch.Tensor, labels_cpu: torch.Tensor, lr: float) -> float:
-        """The call a trainer makes per batch: pinned host tensors in, Python float out."""
+        """The call a trainer makes per batch: pinned host tensors in, Python float out.  Reading the loss waits for
+        the step's kernels, so the device status words of the step are checked right after it at no extra cost."""
         idx = idx_cpu.to(self.ctx.device, non_blocking=True)
         labels = labels_cpu.to(self.ctx.device, non_blocking=True)
-        return float(self.train_step(idx, labels, lr))
+        if self.guard is not None:
+            self.guard.before_step()
+        loss = float(self.train_step(idx, labels, lr))
+        if self.guard is not None:
+            self.guard.after_step(self.health_ok())
+        self.check_health()
+        return loss
+
+    # ------------------------------------------------------------------ health
+    def start_guard(self, timeout_s: float = 60.0):
+        """Multi-rank runs: start this rank's heartbeat and return the :class:`StepGuard` that ``train_step_from_host``
+        consults around every step (peers alive before the step, all ranks' device status clean after it)."""
+        if self.ctx.world_size <= 1 or self.guard is not None:
+            return self.guard
+        from .watchdog import StepGuard
+
+        store = self.ctx.store()
+        if store is None:
+            return None
+        self.guard = StepGuard(store, self.ctx.rank, self.ctx.world_size, agree=self.ctx.all_agree, timeout_s=timeout_s)
+        self.guard.start()
+        self.ctx.barrier()    # every rank has published its first heartbeat before anyone checks
+        return self.guard
+
+    def health_ok(self) -> bool:
+        """False when a bounded wait inside one of the kernels expired during a finished step."""
+        try:
+            self.check_health()
+        except RuntimeError:
+            return False
+        return True
+
+    def check_health(self) -> None:
+        """Raises when a device-side wait (peer flag, panel arrival, mbarrier) expired during a finished step.  Reads
+        pinned host copies refreshed at the end of every step: no device synchronisation."""
+        self.opt.check_health()
+        if self.zero3 is not None:
+            from ..ops import gemm_native
+
+            code = gemm_native.check_status(self.ctx.device)
+            if code:
+                raise RuntimeError(f"rank {self.ctx.rank}: a wait inside the all-gather GEMM expired (code {code})")

@@ -2,7 +2,8 @@
 
 File names, record keys and metric names follow ``rwkvtune/training/callbacks.py:113-295``.  Only
 rank 0 writes.  Throughput counts the tokens actually processed (the reference assumes every sample
-is ``ctx_len`` long) and step time is measured with CUDA events when a GPU is in use.
+is ``ctx_len`` long); step time is the host wall-clock between two loss read-backs, each of which waits for
+the step's kernels, so it includes device time and host time of the step.
 """
 from __future__ import annotations
 

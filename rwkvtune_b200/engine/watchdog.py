@@ -101,3 +101,55 @@ def vote(store, rank: int, world_size: int, step: int, ok: bool, timeout_s: floa
             return all(store.get(k) == b"1" for k in keys)
         sleep(0.01)
     return False
+
+
+class StepAborted(RuntimeError):
+    """Some rank reported a failed step (an expired device-side wait, an exception) and all ranks stop together."""
+
+
+class StepGuard:
+    """What a trainer runs around every optimiser step when there is more than one rank.
+
+    * ``start()`` launches the heartbeat thread of this rank (store keys ``hb/<rank>``).
+    * ``before_step()`` checks the peers' heartbeats (at most once per ``interval_s``) and raises
+      :class:`RankFailure` *on the host, before the next kernel or collective is launched* when one has gone quiet.
+    * ``after_step(ok)`` is called once the step's result has been read back: ``ok`` says whether this rank's
+      device status words were clean; the ranks agree (a MIN-reduction over the host-side control group, falling back
+      to a vote through the store) and every rank raises :class:`StepAborted` if any of them was not.
+
+    ``store`` needs ``set`` / ``get`` / ``check`` (a ``torch.distributed.TCPStore`` or :class:`DictStore`);
+    ``agree`` is a callable ``bool -> bool`` (``DistContext.all_agree``) or None to vote through the store.
+    """
+
+    def __init__(self, store, rank: int, world_size: int, agree=None, timeout_s: float = 60.0, interval_s: float = 1.0,
+                 clock=time.time):
+        self.rank, self.world = rank, world_size
+        self.store, self.agree, self.clock = store, agree, clock
+        self.hb = Heartbeat(store, rank, world_size, timeout_s, interval_s, clock)
+        self.interval_s = interval_s
+        self._last_check = None
+        self._step = 0
+        self.vote_timeout_s = timeout_s
+
+    def start(self) -> None:
+        self.hb.start()
+
+    def stop(self) -> None:
+        self.hb.stop()
+
+    def before_step(self) -> None:
+        now = self.clock()
+        if self._last_check is not None and now - self._last_check < self.interval_s:
+            return
+        self._last_check = now
+        self.hb.assert_alive()
+
+    def after_step(self, ok: bool) -> None:
+        self._step += 1
+        if self.agree is not None:
+            everyone = self.agree(bool(ok))
+        else:
+            everyone = vote(self.store, self.rank, self.world, self._step, bool(ok), self.vote_timeout_s, self.clock)
+        if not everyone:
+            raise StepAborted(f"rank {self.rank}: step {self._step} failed on "
+                              f"{'this rank' if not ok else 'another rank'}; all ranks stop")

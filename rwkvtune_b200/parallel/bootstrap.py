@@ -33,6 +33,27 @@ class DistContext:
         if self.world_size > 1:
             dist.barrier()
 
+    def all_agree(self, ok: bool) -> bool:
+        """True only if every rank passed ``ok=True``.  A host-side MIN-reduction: it runs on the gloo control
+        group when there is one, so it neither launches a kernel nor waits for the GPU."""
+        if self.world_size <= 1:
+            return bool(ok)
+        if self.control_group is not None:
+            t = torch.tensor([1 if ok else 0], dtype=torch.int32)
+            dist.all_reduce(t, op=dist.ReduceOp.MIN, group=self.control_group)
+        else:
+            t = torch.tensor([1 if ok else 0], dtype=torch.int32, device=self.device)
+            dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        return bool(int(t.item()))
+
+    def store(self):
+        """The rendezvous key-value store of the default process group (None in single-process runs)."""
+        if self.world_size <= 1 or not dist.is_initialized():
+            return None
+        from torch.distributed import distributed_c10d
+
+        return distributed_c10d._get_default_store()
+
 
 def env_world() -> tuple:
     return (int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)),

@@ -124,6 +124,26 @@ class ZeroOptimizer:
             sp.params.copy_(torch.cat(parts))
 
     # ------------------------------------------------------------------ public
+    def arm(self) -> None:
+        """Before the backward pass of a micro-batch whose every parameter receives exactly one gradient: lets the
+        fused transport reduce gradient buckets while backward is still running.  No effect on other transports."""
+        if self._p2p is not None:
+            self._p2p.arm()
+
+    def finish_micro(self, boundary: bool) -> None:
+        """After the backward pass of a micro-batch.  Fused transport: whatever was not reduced during backward goes
+        out now, micro-batches are summed in fp32 on the owning rank, and on a non-boundary micro-batch the local
+        bf16 gradient buffer is cleared.  Library transports keep accumulating micro-batches in the flat bf16
+        gradient buffer and reduce once at the boundary (the gradient of one micro-batch is already a sum over
+        thousands of tokens; adding up to 16 of them in bf16 costs at most half an ulp each)."""
+        if self._p2p is not None:
+            self._p2p.finish_micro(boundary)
+
+    def check_health(self) -> None:
+        """Raise if a bounded device-side wait expired during a finished step (no device synchronisation)."""
+        if self._p2p is not None:
+            self._p2p.check()
+
     def step(self, lr: float, grad_scale: float = 1.0) -> None:
         """Reduce gradients, clip by global norm, AdamW on the owned range, publish new parameters.
 

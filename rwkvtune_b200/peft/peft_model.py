@@ -90,17 +90,26 @@ def _get_trainable_extra_state_dict(self) -> Dict[str, torch.Tensor]:
 
 
 def _get_merged_state_dict(self) -> Dict[str, torch.Tensor]:
-    """Plain state_dict with adapters folded in: ``.base_layer.`` stripped, ``lora_*`` dropped."""
-    layers = _lora_layers(self)
-    was_merged = [m.merged for _, m in layers]
-    for _, m in layers:
-        m.merge()
-    sd = {k.replace(".base_layer.", "."): v.detach().cpu().clone() for k, v in self.state_dict().items()
-          if "lora_A" not in k and "lora_B" not in k}
-    for (_, m), merged in zip(layers, was_merged):
-        if not merged:
-            m.unmerge()
-    return sd
+    """Plain state_dict with adapters folded in: ``.base_layer.`` stripped, ``lora_*`` dropped.
+
+    Nothing in the model is modified: each merged matrix ``W + s B A`` is formed on the side.  Base weights that are
+    sharded across ranks (ZeRO-3 keeps only a column panel of each frozen matrix per rank and leaves an empty tensor
+    in the module) are first reassembled from the panels."""
+    sd = {k: v for k, v in self.state_dict().items() if "lora_A" not in k and "lora_B" not in k}
+    for name, m in _lora_layers(self):
+        key = f"{name}.base_layer.weight"
+        sw = getattr(m, "_sharded", None)
+        base = sw.full_weight() if sw is not None else m.base_layer.weight
+        if m.merged:
+            sd[key] = base.detach()
+            continue
+        delta = (m.lora_B.detach().float() @ m.lora_A.detach().float()) * m.scaling
+        sd[key] = (base.detach().float() + delta.to(base.device)).to(base.dtype)
+    for name, m in self.named_modules():   # sharded matrices that carry no adapter
+        sw = getattr(m, "_sharded", None)
+        if sw is not None and not isinstance(m, LoraLinear):
+            sd[f"{name}.weight"] = sw.full_weight().detach()
+    return {k.replace(".base_layer.", "."): v.detach().cpu().clone() for k, v in sd.items()}
 
 
 def _save_lora_weights(self, path: str) -> None:

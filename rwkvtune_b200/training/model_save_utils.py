@@ -21,7 +21,16 @@ ADAPTER_WEIGHTS_NAME = "adapter_model.bin"
 
 
 def _cpu_state_dict(model) -> Dict[str, torch.Tensor]:
-    return {k: v.detach().cpu().contiguous() for k, v in model.state_dict().items()}
+    """``model.state_dict()`` on the CPU.  Matrices that ZeRO-3 holds as one column panel per rank are reassembled
+    (the reference consolidates a stage-3 run into one ``model.pth`` the same way,
+    ``rwkvtune/training/callbacks.py:385-426``)."""
+    sd = {k: v.detach().cpu().contiguous() for k, v in model.state_dict().items()}
+    for name, m in model.named_modules():
+        sw = getattr(m, "_sharded", None)
+        if sw is not None:
+            key = f"{name}.base_layer.weight" if hasattr(m, "base_layer") else f"{name}.weight"
+            sd[key] = sw.full_weight().detach().cpu().contiguous()
+    return sd
 
 
 def save_tokenizer(tokenizer, output_dir: str) -> None:

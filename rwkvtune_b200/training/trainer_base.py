@@ -142,7 +142,20 @@ class SupervisedTrainer:
         logger = MetricLogger(a.proj_dir, a.report_to, a.run_name, ctx.is_main, config=vars(a))
         start_epoch, skip = self._maybe_resume(per_epoch)
         samples_per_batch = a.micro_bsz * ctx.world_size
-        use_events = ctx.device.type == "cuda"
+        guard = eng.start_guard()
+        try:
+            self._run_epochs(start_epoch, skip, per_epoch, total_steps, loader, logger, samples_per_batch)
+        except Exception as exc:
+            self._emergency_save(exc)
+            raise
+        finally:
+            if guard is not None:
+                guard.stop()
+        logger.close()
+        ctx.barrier()
+
+    def _run_epochs(self, start_epoch, skip, per_epoch, total_steps, loader, logger, samples_per_batch) -> None:
+        a, ctx, eng = self.args, self.ctx, self.engine
         for epoch in range(start_epoch, a.epoch_count):
             self.state["epoch"] = epoch
             loss_sum, n_loss = 0.0, 0
@@ -175,12 +188,34 @@ class SupervisedTrainer:
             logger.log_epoch(epoch, loss_sum / max(n_loss, 1), self.state["global_batch"])
             if (a.epoch_save > 0 and (epoch + 1) % a.epoch_save == 0) or epoch == a.epoch_count - 1:
                 self._save_checkpoint(f"rwkv7-epoch{epoch + 1}")
-        logger.close()
-        ctx.barrier()
+
+    def _emergency_save(self, exc: BaseException) -> None:
+        """A peer stopped answering or a step was aborted: the lowest rank still known to be alive writes a
+        weights-only save point without any collective (the reference has no counterpart; its elastic resume reloads
+        weights only, ``rwkvtune/training/sft_trainer.py:705-723``).  Parameters are consistent: an aborted step's
+        kernels leave them untouched."""
+        from ..engine.watchdog import RankFailure, StepAborted
+        from ..parallel.p2p import PeerWaitTimeout
+
+        if not isinstance(exc, (RankFailure, StepAborted, PeerWaitTimeout)) or self.ctx is None:
+            return
+        dead = set(exc.ranks) if isinstance(exc, RankFailure) else set()
+        writer = min(r for r in range(self.ctx.world_size) if r not in dead)
+        if self.ctx.rank != writer:
+            return
+        out = os.path.join(self.args.proj_dir, "rwkv7-emergency")
+        try:
+            save_model_or_adapter(self.model, out, self.processing_class, self.args.lora_save_mode, self.base_model_path)
+            with open(os.path.join(out, "emergency.txt"), "w", encoding="utf-8") as fh:
+                fh.write(f"{type(exc).__name__}: {exc}\nsamples_seen={self.state['samples_seen']}\n")
+            print(f"[trainer] {type(exc).__name__}: weights saved to {out}", flush=True)
+        except Exception as save_exc:   # never mask the original failure
+            print(f"[trainer] emergency save failed: {save_exc}", flush=True)
 
     # ------------------------------------------------------------------ checkpoints
     def _save_checkpoint(self, name: str) -> None:
         a, ctx, eng = self.args, self.ctx, self.engine
+        eng.check_health()    # never write a save point from a step in which a device-side wait expired
         final = os.path.join(a.proj_dir, name)
         meta = {"samples_seen": self.state["samples_seen"], "devices": ctx.world_size, "micro_bsz": a.micro_bsz,
                 "accumulate_grad_batches": a.accumulate_grad_batches, "epoch": self.state["epoch"],

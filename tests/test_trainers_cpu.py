@@ -105,3 +105,50 @@ def test_pretrain_trainer_infctx_iterable(tmp_path):
     PretrainTrainer(_model(), args, Stream()).train()
     losses = _losses(proj)
     assert len(losses) == 6 and losses[-1] < losses[0]
+
+
+class _FakePanels:
+    """Stands in for a ZeRO-3 sharded weight: the module holds an empty tensor, the full matrix comes from here."""
+
+    def __init__(self, full):
+        self.full = full.clone()
+        self.calls = 0
+
+    def full_weight(self):
+        self.calls += 1
+        return self.full
+
+
+def test_full_and_merged_saves_reassemble_sharded_weights(tmp_path):
+    from rwkvtune_b200.peft import get_peft_model
+    from rwkvtune_b200.training.model_save_utils import save_model_or_adapter
+
+    model = get_peft_model(_model(), LoraConfig(r=4, lora_alpha=8))
+    with torch.no_grad():
+        for n, p in model.named_parameters():
+            if "lora_B" in n:
+                p.normal_(0, 0.05)
+    expected = model.get_merged_state_dict()
+    idx = torch.tensor([_dataset()[0]["input_ids"]])
+    want = model(idx)
+    # shard: every adapted projection loses its base weight, as Zero3ShardedLinears does on a multi-GPU stage-3 run
+    fakes = []
+    for name, m in model.named_modules():
+        if hasattr(m, "base_layer"):
+            m._sharded = _FakePanels(m.base_layer.weight.data)
+            m.base_layer.weight.data = torch.empty(0)
+            fakes.append(m._sharded)
+    assert fakes and all(f.calls == 0 for f in fakes)
+    got = model.get_merged_state_dict()
+    assert set(got) == set(expected)
+    for k in expected:
+        assert got[k].shape == expected[k].shape and torch.allclose(got[k], expected[k], atol=1e-6), k
+    assert all(m.base_layer.weight.numel() == 0 for _, m in model.named_modules() if hasattr(m, "base_layer"))
+    out = str(tmp_path / "both")
+    save_model_or_adapter(model, out, None, "both")
+    assert os.path.exists(os.path.join(out, "adapter_model.bin"))
+    merged = AutoModel.from_pretrained(os.path.join(out, "merged"))
+    assert torch.allclose(merged(idx), want, atol=1e-4)
+    full = str(tmp_path / "full")
+    save_model_or_adapter(model, full, None, "full")
+    assert torch.allclose(AutoModel.from_pretrained(full)(idx), want, atol=1e-4)

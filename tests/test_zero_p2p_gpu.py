@@ -39,12 +39,12 @@ def test_reduce_scatter_adam_broadcast_emulated_ranks():
     scale = 1.0 / W
     for r in range(W):
         _ext.call("rwkv_zero2_reduce_scatter", _arr(grads), _arr(ctrl), _ext.i32(r), _ext.i32(W), _ext.i64(r * shard),
-                  _ext.i64(shard), _ext.f32(scale), _ext.ptr(gred[r]), _ext.ptr(scratch), st)
+                  _ext.i64(shard), _ext.f32(scale), _ext.ptr(gred[r]), _ext.ptr(scratch), _ext.ptr(None), st)
     lr, b1, b2, eps, wd, clip = 1e-2, 0.9, 0.99, 1e-8, 0.01, 0.5
     for r in range(W):
         _ext.call("rwkv_zero2_adam_broadcast", _arr(params), _arr(ctrl), _ext.i32(r), _ext.i32(W), _ext.i64(r * shard),
                   _ext.i64(shard), _ext.ptr(master[r]), _ext.ptr(m[r]), _ext.ptr(v[r]), _ext.ptr(gred[r]), _ext.f32(lr),
-                  _ext.f32(b1), _ext.f32(b2), _ext.f32(eps), _ext.f32(wd), _ext.i32(1), _ext.f32(clip), st)
+                  _ext.f32(b1), _ext.f32(b2), _ext.f32(eps), _ext.f32(wd), _ext.i32(1), _ext.f32(clip), _ext.ptr(None), st)
     torch.cuda.synchronize()
     g_full = sum(g.float() for g in grads) * scale
     assert torch.allclose(torch.cat(gred), g_full, atol=1e-6)
@@ -81,6 +81,71 @@ def test_barrier_wait_expires_with_status():
     assert torch.ones(4, device="cuda").sum().item() == 4.0
 
 
+def test_bucket_reduce_accumulates_and_poisoned_step_writes_nothing():
+    """The per-bucket pieces on emulated ranks: two micro-batches summed in fp32 on the owner, the norm share with an
+    extra term, and a non-zero status word turning the data kernels into no-ops."""
+    from rwkvtune_b200.ops import _ext
+
+    torch.manual_seed(1)
+    W, n, lo = 2, 2048, 512
+    dev = "cuda"
+    st = _ext.stream()
+    ctrl = [torch.zeros(256, dtype=torch.int32, device=dev) for _ in range(W)]
+    out = torch.zeros(n, device=dev)
+    part = torch.zeros(1024, device=dev)
+    total = torch.zeros(n, device=dev)
+    for micro in range(2):
+        grads = [(torch.randn(4096, device=dev) * 0.1).to(torch.bfloat16) for _ in range(W)]
+        _ext.call("rwkv_zero2_reduce_bucket", _arr(grads), _ext.i32(W), _ext.i64(lo), _ext.i64(n), _ext.f32(0.5),
+                  _ext.ptr(out), _ext.ptr(part), _ext.i32(4), _ext.i32(micro), _ext.ptr(None), st)
+        total += sum(g[lo:lo + n].float() for g in grads) * 0.5
+    torch.cuda.synchronize()
+    assert torch.allclose(out, total, atol=1e-6)
+    assert torch.allclose(part.sum(), total.square().sum(), rtol=1e-5)
+    extra = torch.full((1,), 3.0, device=dev)
+    _ext.call("rwkv_zero2_publish_norm", _ext.ptr(part), _ext.i32(1024), _ext.ptr(extra), _arr(ctrl), _ext.i32(1),
+              _ext.i32(W), st)
+    torch.cuda.synchronize()
+    for c in ctrl:
+        assert torch.allclose(c.view(torch.float32)[64 + 1], total.square().sum() + 3.0, rtol=1e-5)
+    # poisoned: status != 0 -> neither the reduce nor the optimiser kernel writes
+    status = torch.full((1,), 502, dtype=torch.int32, device=dev)
+    before = out.clone()
+    _ext.call("rwkv_zero2_reduce_bucket", _arr(grads), _ext.i32(W), _ext.i64(lo), _ext.i64(n), _ext.f32(0.5),
+              _ext.ptr(out), _ext.ptr(part), _ext.i32(4), _ext.i32(0), _ext.ptr(status), st)
+    params = [torch.ones(4096, device=dev).to(torch.bfloat16) for _ in range(W)]
+    master, m, v = torch.ones(n, device=dev), torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+    _ext.call("rwkv_zero2_adam_broadcast", _arr(params), _arr(ctrl), _ext.i32(0), _ext.i32(W), _ext.i64(lo),
+              _ext.i64(n), _ext.ptr(master), _ext.ptr(m), _ext.ptr(v), _ext.ptr(out), _ext.f32(0.1), _ext.f32(0.9),
+              _ext.f32(0.99), _ext.f32(1e-8), _ext.f32(0.0), _ext.i32(1), _ext.f32(1.0), _ext.ptr(status), st)
+    torch.cuda.synchronize()
+    assert torch.equal(out, before) and torch.equal(master, torch.ones(n, device=dev))
+    assert all(torch.equal(p, torch.ones(4096, device=dev).to(torch.bfloat16)) for p in params)
+
+
+def test_bucket_flag_signal_and_bounded_wait():
+    """A bucket flag raised by one emulated rank reaches every control block; a wait for a flag that one rank never
+    raises gives up after its deadline with that rank's number in the status word."""
+    from rwkvtune_b200.ops import _ext
+
+    W, word = 2, 128 + 16 * 3
+    ctrl = [torch.zeros(128 + 16 * 8, dtype=torch.int32, device="cuda") for _ in range(W)]
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    _ext.call("rwkv_p2p_signal", _arr(ctrl), _ext.i32(0), _ext.i32(W), _ext.i32(word), _ext.i32(7), _ext.stream())
+    torch.cuda.synchronize()
+    assert int(ctrl[0][word]) == 7 and int(ctrl[1][word]) == 7 and int(ctrl[0][word + 1]) == 0
+    _ext.call("rwkv_p2p_wait", _arr(ctrl), _ext.i32(0), _ext.i32(W), _ext.i32(word), _ext.i32(7), _ext.ptr(status),
+              _ext.i64(50_000_000), _ext.stream())
+    torch.cuda.synchronize()
+    assert int(status.item()) == 501            # rank 1 never raised its flag
+    status.zero_()
+    _ext.call("rwkv_p2p_signal", _arr(ctrl), _ext.i32(1), _ext.i32(W), _ext.i32(word), _ext.i32(7), _ext.stream())
+    _ext.call("rwkv_p2p_wait", _arr(ctrl), _ext.i32(0), _ext.i32(W), _ext.i32(word), _ext.i32(7), _ext.ptr(status),
+              _ext.i64(50_000_000), _ext.stream())
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+
+
 _WORKER = r'''
 import os, sys, json, torch
 sys.path.insert(0, os.environ["RWKV_ROOT"])
@@ -89,26 +154,35 @@ from rwkvtune_b200.models import RWKVConfig, RWKV7Model
 from rwkvtune_b200.parallel import init_distributed
 ctx = init_distributed("gpu")
 out = {}
-for transport in ("nccl", "p2p"):
+for tag, transport, overlap, acc in (("nccl", "nccl", False, 1), ("p2p", "p2p", True, 1), ("p2p_serial", "p2p", False, 1),
+                                     ("nccl_acc2", "nccl", False, 2), ("p2p_acc2", "p2p", True, 2)):
     torch.manual_seed(0)
     cfg = RWKVConfig(n_layer=2, n_embd=256, vocab_size=1024, dim_att_lora=32, dim_gate_lora=64, dim_mv_lora=32)
     eng = TrainEngine(RWKV7Model(cfg), EngineConfig(lr_init=1e-3, weight_decay=0.01, strategy="deepspeed_stage_2",
-                                                   precision="bf16", transport=transport), ctx)
+                                                   precision="bf16", transport=transport,
+                                                   accumulate_grad_batches=acc), ctx)
+    if eng.opt._p2p is not None:
+        eng.opt._p2p.overlap = overlap
+        assert eng.opt._p2p.n_buckets >= 1
     g = torch.Generator().manual_seed(100 + ctx.rank)
     losses = []
-    for step in range(3):
+    for step in range(3 * acc):
         idx = torch.randint(0, 1024, (2, 64), generator=g).to(ctx.device)
         losses.append(float(eng.train_step(idx, idx.roll(-1, 1), 1e-3)))
+    eng.check_health()
     if eng.opt._p2p is not None:
-        eng.opt._p2p.check()
+        eng.opt._p2p.check_now()
     torch.cuda.synchronize()
-    out[transport] = (losses, eng.space.params.float().clone())
+    out[tag] = (losses, eng.space.params.float().clone())
 torch.distributed.barrier()
 if ctx.rank == 0:
     a, b = out["nccl"][1], out["p2p"][1]
     diff = (a - b).abs().max().item()
     print(json.dumps({"losses_nccl": out["nccl"][0], "losses_p2p": out["p2p"][0], "max_param_diff": diff,
-                      "param_scale": a.abs().max().item()}))
+                      "param_scale": a.abs().max().item(),
+                      "overlap_vs_serial_identical": bool(torch.equal(out["p2p"][1], out["p2p_serial"][1])),
+                      "acc2_param_diff": (out["nccl_acc2"][1] - out["p2p_acc2"][1]).abs().max().item(),
+                      "losses_nccl_acc2": out["nccl_acc2"][0], "losses_p2p_acc2": out["p2p_acc2"][0]}))
 torch.distributed.destroy_process_group()
 '''
 
@@ -127,6 +201,10 @@ def test_p2p_transport_matches_nccl_two_ranks(tmp_path):
     rec = json.loads(line)
     assert rec["max_param_diff"] <= 2e-2 * rec["param_scale"] + 1e-3, rec
     for x, y in zip(rec["losses_nccl"], rec["losses_p2p"]):
+        assert abs(x - y) < 5e-2, rec
+    assert rec["overlap_vs_serial_identical"], "reducing buckets during backward changed the result"
+    assert rec["acc2_param_diff"] <= 2e-2 * rec["param_scale"] + 1e-3, rec
+    for x, y in zip(rec["losses_nccl_acc2"], rec["losses_p2p_acc2"]):
         assert abs(x - y) < 5e-2, rec
 
 
