@@ -1,4 +1,5 @@
-"""GRPO rollout throughput: prompts x generations decoded in lock-step (BASELINE config 5 shape by default).
+"""GRPO rollout throughput: prompts x generations decoded in lock-step (by default the 1.5B model, 8 prompts of 512
+tokens x 8 generations x 512 new tokens).
 
     python benchmarks/rollout_bench.py [--model 1.5b] [--prompts 8] [--prompt-len 512] [--generations 8] [--new-tokens 512]
 

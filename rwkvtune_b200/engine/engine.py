@@ -8,6 +8,7 @@ of its Lightning modules (``rwkvtune/training/lightning_module.py:175-206``,
 """
 from __future__ import annotations
 
+import os
 import time
 from dataclasses import dataclass
 from typing import Callable, Dict, Optional, Sequence
@@ -103,6 +104,10 @@ class TrainEngine:
         self.tokens_seen = 0
         self._graphs: Dict[tuple, dict] = {}
         self.guard = None
+        from .profiling import PhaseMonitor
+
+        # phase timers + NVTX ranges; RWKVTUNE_PHASE_SYNC=1 synchronises at phase boundaries (exact device time per phase)
+        self.phases = PhaseMonitor(ctx.device, sync=os.environ.get("RWKVTUNE_PHASE_SYNC", "0") == "1")
 
     # ------------------------------------------------------------------ memory-aware checkpointing
     SAVED_UNITS_PER_LAYER = 37.0   # [tokens, n_embd] bf16 tensors a block keeps for backward without checkpointing
@@ -147,12 +152,13 @@ class TrainEngine:
         wkv = torch.zeros(L, B, H, N, N, device=idx.device, dtype=torch.float32)
         total = torch.zeros((), device=idx.device, dtype=torch.float32)
         pending = []
-        if cfg.truncated_bptt:
-            # which chunks have a supervised token: one device-to-host read for the whole sequence, so the chunk loop
-            # below never waits for the GPU and the host can run ahead of it
-            pad = n_chunks * chunk - T
-            lab_p = torch.nn.functional.pad(labels, (0, pad), value=-100) if pad else labels
-            chunk_valid = (lab_p.reshape(B, n_chunks, chunk) != -100).any(dim=2).any(dim=0).tolist()
+        # which chunks have a supervised token: one device-to-host read for the whole sequence, so the chunk loop
+        # below never waits for the GPU and the host can run ahead of it.  A chunk without one (a masked prompt)
+        # contributes neither cross-entropy nor L2Wrap, but the sum is still divided by the number of chunks
+        # (rwkvtune/training/lightning_module_infctx.py:246-262, :349-365).
+        pad = n_chunks * chunk - T
+        lab_p = torch.nn.functional.pad(labels, (0, pad), value=-100) if pad else labels
+        chunk_valid = (lab_p.reshape(B, n_chunks, chunk) != -100).any(dim=2).any(dim=0).tolist()
         use_graph = cfg.truncated_bptt and self._graph_ok() and T % chunk == 0 and all(chunk_valid)
         for i in range(n_chunks):
             ids_c, lab_c = idx[:, i * chunk:(i + 1) * chunk], labels[:, i * chunk:(i + 1) * chunk]
@@ -162,20 +168,21 @@ class TrainEngine:
                 continue
             x, shift, wkv = m.forward_hidden_infctx(ids_c, shift, wkv, checkpoint=bool(cfg.grad_cp))
             Bc, Tc, _ = x.shape
-            from .. import ops
-
+            if not cfg.truncated_bptt and not chunk_valid[i]:
+                continue      # full BPTT: the chunk only carries state (and its graph) forward
             loss_c = ops.linear_cross_entropy(x.reshape(Bc * Tc, C), m._head_weight(), lab_c.reshape(-1),
                                               l2wrap=cfg.l2wrap, l2wrap_tokens=Bc * Tc)
-            has_valid = chunk_valid[i] if cfg.truncated_bptt else True
             if cfg.truncated_bptt:
-                if has_valid:
+                if chunk_valid[i]:
                     (loss_c * (scale / n_chunks)).backward()
                     total += loss_c.detach()
                 shift, wkv = shift.detach(), wkv.detach()
             else:
                 pending.append(loss_c)
         if not cfg.truncated_bptt:
-            loss = torch.stack(pending).mean()
+            if not pending:       # nothing supervised in the whole sequence
+                return total
+            loss = torch.stack(pending).sum() / n_chunks
             (loss * scale).backward()
             return loss.detach()
         return total / n_chunks
@@ -255,23 +262,25 @@ class TrainEngine:
         acc = self.cfg.accumulate_grad_batches
         scale = 1.0 / acc
         boundary = (self.micro_step + 1) % acc == 0
-        if self.cfg.train_type == "infctx":
-            loss = self._step_infctx(idx, labels, scale)
-        elif self._graph_ok():
-            loss = self._graph_step_normal(idx, labels, scale)
-        else:
-            loss = self._loss_normal(idx, labels)
-            self.opt.arm()          # gradient buckets are reduced while backward is still running
-            (loss * scale if acc > 1 else loss).backward()
-            loss = loss.detach()
-        self.opt.finish_micro(boundary)
-        self.micro_step += 1
-        self.tokens_seen += idx.numel()
-        if boundary:
-            self.opt.step(lr)
-            self.opt.zero_grad()
-            self.optimizer_steps += 1
-            ops.bump_param_epoch()
+        with self.phases.phase("forward_backward"):
+            if self.cfg.train_type == "infctx":
+                loss = self._step_infctx(idx, labels, scale)
+            elif self._graph_ok():
+                loss = self._graph_step_normal(idx, labels, scale)
+            else:
+                loss = self._loss_normal(idx, labels)
+                self.opt.arm()          # gradient buckets are reduced while backward is still running
+                (loss * scale if acc > 1 else loss).backward()
+                loss = loss.detach()
+        with self.phases.phase("reduce_optimizer"):
+            self.opt.finish_micro(boundary)
+            self.micro_step += 1
+            self.tokens_seen += idx.numel()
+            if boundary:
+                self.opt.step(lr)
+                self.opt.zero_grad()
+                self.optimizer_steps += 1
+                ops.bump_param_epoch()
         return loss
 
     def backward_and_step(self, loss: torch.Tensor, lr: float) -> bool:
@@ -279,16 +288,17 @@ class TrainEngine:
         optimiser on accumulation boundaries.  Returns True when an optimiser step happened."""
         acc = self.cfg.accumulate_grad_batches
         boundary = (self.micro_step + 1) % acc == 0
-        (loss / acc if acc > 1 else loss).backward()
-        self.opt.finish_micro(boundary)
-        self.micro_step += 1
-        if boundary:
-            self.opt.step(lr)
-            self.opt.zero_grad()
-            self.optimizer_steps += 1
-            ops.bump_param_epoch()
-            return True
-        return False
+        with self.phases.phase("backward"):
+            (loss / acc if acc > 1 else loss).backward()
+        with self.phases.phase("reduce_optimizer"):
+            self.opt.finish_micro(boundary)
+            self.micro_step += 1
+            if boundary:
+                self.opt.step(lr)
+                self.opt.zero_grad()
+                self.optimizer_steps += 1
+                ops.bump_param_epoch()
+        return boundary
 
     def train_step_from_host(self, idx_cpu: torch.Tensor, labels_cpu: torch.Tensor, lr: float) -> float:
         """The call a trainer makes per batch: pinned host tensors in, Python float out.  Reading the loss waits for

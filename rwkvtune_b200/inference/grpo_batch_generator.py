@@ -172,7 +172,13 @@ class GRPOBatchGenerator:
         for p in prompts:
             owner.append(uniq.setdefault(tuple(p), len(uniq)))
         uniq_prompts = [list(k) for k in uniq.keys()]
+        nvtx = dev.type == "cuda"
+        if nvtx:
+            torch.cuda.nvtx.range_push("prefill")
         pre_logits, pre_state = self._chunked_prefill(uniq_prompts)
+        if nvtx:
+            torch.cuda.nvtx.range_pop()
+            torch.cuda.nvtx.range_push("decode")
         t_prefill = time.perf_counter()
         fan = torch.tensor(owner, dtype=torch.long, device=dev).repeat_interleave(G)
         state = self._select(pre_state, fan)
@@ -236,6 +242,8 @@ class GRPOBatchGenerator:
                 else:
                     logits, state = self._forward(tok[:, None], state)
         finally:
+            if nvtx:
+                torch.cuda.nvtx.range_pop()
             TokenSampler.set_max_valid_token_id(prev_max)
             if was_training:
                 self.model.train()

@@ -54,6 +54,13 @@ class GRPOTrainer:
         if train_dataset is None:
             raise ValueError("train_dataset is required")
         self.train_dataset, self.eval_dataset = train_dataset, eval_dataset
+        import warnings
+
+        if eval_dataset is not None:   # accepted for signature parity; the reference stores it and never evaluates either
+            warnings.warn("GRPOTrainer: eval_dataset is accepted but not used (no evaluation loop runs during GRPO)")
+        if optimizers is not None and tuple(optimizers) != (None, None):
+            warnings.warn("GRPOTrainer: `optimizers` is ignored; the engine builds its own sharded AdamW and schedule "
+                          "from lr_init / lr_final / warmup_steps / weight_decay")
         if processing_class is None:    # as in the reference (grpo_trainer.py:540-549): the default RWKV vocabulary,
             from ..data.tokenizers import AutoTokenizer, get_tokenizer   # or the model directory's own tokenizer
 
@@ -184,10 +191,12 @@ class GRPOTrainer:
         a, ctx, eng = self.args, self.ctx, self.engine
         G = a.num_generations
         prompts_ids = [list(p)[-a.max_prompt_length:] for p in batch["input_ids"]]
+        phases = eng.phases
         t0 = time.perf_counter()
-        out = self.generator.generate(prompts_ids, max_new_tokens=a.max_completion_length, num_generations=G,
-                                      temperature=a.temperature, top_p=a.top_p, top_k=a.top_k,
-                                      repetition_penalty=a.repetition_penalty, logit_bias=a.logit_bias)
+        with phases.phase("rollout"):
+            out = self.generator.generate(prompts_ids, max_new_tokens=a.max_completion_length, num_generations=G,
+                                          temperature=a.temperature, top_p=a.top_p, top_k=a.top_k,
+                                          repetition_penalty=a.repetition_penalty, logit_bias=a.logit_bias)
         t_roll = time.perf_counter() - t0
         completions, comp_ids, masks = out["completions"], out["completion_ids"], out["masks"]
         prompts_rep = [p for p in batch["prompts"] for _ in range(G)]
@@ -195,7 +204,8 @@ class GRPOTrainer:
         extra = {k: [v for v in vals for _ in range(G)] for k, vals in batch.items() if k not in ("prompts", "input_ids")}
         if self.completion_postprocess_fn is not None:
             completions, comp_ids, masks = self._postprocess(prompts_rep, completions, comp_ids, masks, extra)
-        rewards, per_func = self._compute_rewards(prompts_rep, completions, extra)
+        with phases.phase("rewards"):
+            rewards, per_func = self._compute_rewards(prompts_rep, completions, extra)
         rewards, per_func = rewards.to(ctx.device), per_func.to(ctx.device)
         n_local = rewards.numel()
         if ctx.world_size > 1:
@@ -208,14 +218,19 @@ class GRPOTrainer:
             gathered = [torch.zeros_like(rewards) for _ in range(ctx.world_size)]
             dist.all_gather(gathered, rewards)
             all_rewards = torch.cat(gathered)
+            # the per-function columns too, so that the logged train/rewards/<func>/* describe the whole job
+            # (rwkvtune/training/grpo/lightning_module.py:980-988 gathers both)
+            gathered_pf = [torch.zeros_like(per_func) for _ in range(ctx.world_size)]
+            dist.all_gather(gathered_pf, per_func.contiguous())
+            all_per_func = torch.cat(gathered_pf)
         else:
-            all_rewards = rewards
+            all_rewards, all_per_func = rewards, per_func
         adv_all = self.advantage.compute_advantages(all_rewards)
         adv = adv_all[ctx.rank * n_local:(ctx.rank + 1) * n_local]
         if comp_ids.shape[1] == 0:
             comp_ids = torch.zeros(n_local, 1, dtype=torch.long, device=ctx.device)
             masks = torch.zeros(n_local, 1, dtype=torch.bool, device=ctx.device)
-        with torch.no_grad():
+        with torch.no_grad(), phases.phase("old_logps"):
             old_logps, _ = self._per_token_logps(eng.model, ids_rep, comp_ids)
         order = torch.randperm(n_local, device=ctx.device) if a.shuffle_buffer else torch.arange(n_local, device=ctx.device)
         S = a.steps_per_generation
@@ -233,9 +248,11 @@ class GRPOTrainer:
                               "completions/mean_length": float(lengths.mean()), "completions/min_length": float(lengths.min()),
                               "completions/max_length": float(lengths.max()), "rollout/seconds": t_roll,
                               "rollout/tokens_per_sec": float(lengths.sum()) / max(t_roll, 1e-9),
-                              "mean_advantage": float(adv.mean())}
+                              "mean_advantage": float(adv.mean()),
+                              "phase/prefill/seconds": float(self.generator.last_stats.get("prefill_s", 0.0)),
+                              "phase/decode/seconds": float(self.generator.last_stats.get("decode_s", 0.0))}
         for j, name in enumerate(self.reward_names):
-            col = per_func[:, j]
+            col = all_per_func[:, j]
             self.rollout_stats.update({f"train/rewards/{name}/mean": float(col.mean()), f"train/rewards/{name}/std": float(col.std(unbiased=False)),
                                        f"train/rewards/{name}/min": float(col.min()), f"train/rewards/{name}/max": float(col.max())})
         self.state["rollouts"] += 1
@@ -340,6 +357,9 @@ class GRPOTrainer:
         logger = MetricLogger(a.proj_dir, a.report_to or "", a.run_name or "", ctx.is_main, "grpo_loss_data.jsonl",
                               "grpo_train_log.txt", vars(a))
         self._maybe_resume()
+        from ..engine.profiling import StepProfiler, profile_steps_requested
+
+        profiler = StepProfiler(profile_steps_requested(a), a.proj_dir, is_main=ctx.is_main)
         done = False
         for epoch in range(a.epoch_count):
             loader.sampler.set_epoch(epoch)
@@ -354,8 +374,13 @@ class GRPOTrainer:
                 lr = a.lr_init * grpo_lr_scale(eng.optimizer_steps, a.lr_init, a.lr_final, a.warmup_steps, total_opt,
                                                a.accumulate_grad_batches)
                 t0 = time.perf_counter()
-                metrics = self._training_step(data, lr)
+                profiler.step_begin()
+                with eng.phases.phase("policy_step"):
+                    metrics = self._training_step(data, lr)
+                profiler.step_end()
+                eng.check_health()
                 metrics.update(self.rollout_stats)
+                metrics.update(eng.phases.scalars())
                 self.state["global_step"] += 1
                 self.state["samples_seen"] += a.micro_bsz * ctx.world_size
                 self.last_metrics = metrics

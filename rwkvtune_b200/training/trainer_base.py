@@ -155,7 +155,10 @@ class SupervisedTrainer:
         ctx.barrier()
 
     def _run_epochs(self, start_epoch, skip, per_epoch, total_steps, loader, logger, samples_per_batch) -> None:
+        from ..engine.profiling import StepProfiler, profile_steps_requested
+
         a, ctx, eng = self.args, self.ctx, self.engine
+        profiler = StepProfiler(profile_steps_requested(a), a.proj_dir, is_main=ctx.is_main)
         for epoch in range(start_epoch, a.epoch_count):
             self.state["epoch"] = epoch
             loss_sum, n_loss = 0.0, 0
@@ -165,7 +168,9 @@ class SupervisedTrainer:
                     break
                 real_step = (epoch + a.epoch_begin) * per_epoch + (b + 1)
                 lr = sft_lr(real_step, a.lr_init, a.lr_final, a.warmup_steps, total_steps, a.epoch_count)
+                profiler.step_begin()
                 loss = eng.train_step_from_host(batch["input_ids"], batch["labels"], lr)
+                profiler.step_end()
                 self.state["samples_seen"] += samples_per_batch
                 self.state["global_batch"] += 1
                 if ctx.world_size > 1 and (b + 1) % a.log_every_n_steps == 0:
@@ -177,7 +182,8 @@ class SupervisedTrainer:
                 now = time.perf_counter()
                 if (b + 1) % a.log_every_n_steps == 0:
                     tokens = batch["input_ids"].numel() * ctx.world_size
-                    rec = logger.log_step(self.state["global_batch"], loss, lr, tokens, now - t_last)
+                    rec = logger.log_step(self.state["global_batch"], loss, lr, tokens, now - t_last,
+                                          eng.phases.scalars())
                     if ctx.is_main:
                         print(f"epoch {epoch} step {b + 1}/{per_epoch} loss {loss:.4f} lr {lr:.3e} "
                               f"{rec['kt_s']:.1f} Kt/s", flush=True)

@@ -1,0 +1,79 @@
+"""Engine-level behaviour on CPU: infinite-context steps with masked chunks, phase timers, bucket planning."""
+import torch
+
+from rwkvtune_b200.engine import EngineConfig, TrainEngine
+from rwkvtune_b200.models import RWKVConfig, RWKV7Model
+from rwkvtune_b200.parallel import DistContext
+
+
+def _engine(**kw):
+    torch.manual_seed(0)
+    cfg = RWKVConfig(n_layer=2, n_embd=64, vocab_size=128, dim_att_lora=16, dim_gate_lora=16, dim_mv_lora=16)
+    return TrainEngine(RWKV7Model(cfg), EngineConfig(lr_init=1e-3, precision="fp32", train_type="infctx", chunk_ctx=16,
+                                                     **kw), DistContext())
+
+
+def _batch():
+    g = torch.Generator().manual_seed(3)
+    idx = torch.randint(1, 128, (2, 48), generator=g)
+    labels = idx.roll(-1, 1).clone()
+    labels[:, :16] = -100            # the whole first chunk is prompt
+    return idx, labels
+
+
+def test_full_bptt_skips_fully_masked_chunks_and_divides_by_all_chunks():
+    idx, labels = _batch()
+    eng = _engine(truncated_bptt=False)
+    loss = eng.train_step(idx, labels, 1e-3)
+    assert torch.isfinite(loss)
+    # the same number from the plain statements: two supervised chunks, each a mean over its own tokens, over 3 chunks
+    ref = _engine(truncated_bptt=False)
+    m = ref.model
+    with torch.no_grad():
+        logits = m(idx)
+    per_chunk = []
+    for c in (1, 2):
+        sl = slice(16 * c, 16 * (c + 1))
+        per_chunk.append(torch.nn.functional.cross_entropy(logits[:, sl].reshape(-1, 128), labels[:, sl].reshape(-1)))
+    assert abs(float(loss) - float(sum(per_chunk) / 3)) < 1e-4
+    truncated = _engine(truncated_bptt=True).train_step(idx, labels, 1e-3)
+    assert abs(float(truncated) - float(loss)) < 1e-4
+
+
+def test_nothing_supervised_is_a_zero_loss_step_not_a_nan():
+    idx, labels = _batch()
+    labels[:] = -100
+    for truncated in (True, False):
+        loss = _engine(truncated_bptt=truncated).train_step(idx, labels, 1e-3)
+        assert float(loss) == 0.0
+
+
+def test_phase_monitor_collects_engine_phases():
+    idx, labels = _batch()
+    eng = _engine()
+    eng.train_step(idx, labels, 1e-3)
+    sc = eng.phases.scalars()
+    assert sc["phase/forward_backward/seconds"] > 0 and "phase/reduce_optimizer/seconds" in sc
+    assert eng.phases.scalars() == {}          # reset after reading
+
+
+def test_bucket_plan_covers_the_space_with_whole_parameters():
+    from rwkvtune_b200.parallel.p2p import plan_buckets
+
+    segs, off = [], 0
+    for n in (100, 4000, 128, 9000, 256, 256, 12000, 64):
+        segs.append((off, n))
+        off += (n + 127) // 128 * 128
+    padded = (off + 1023) // 1024 * 1024
+    bounds, seg_bucket = plan_buckets(segs, padded, 8000)
+    assert bounds[0] == 0 and bounds[-1] == padded and bounds == sorted(bounds)
+    assert len(seg_bucket) == len(segs) and seg_bucket == sorted(seg_bucket)
+    starts = {s for s, _ in segs} | {padded}
+    assert all(b in starts for b in bounds)                      # buckets start at parameter boundaries
+    for (start, n), b in zip(segs, seg_bucket):
+        assert bounds[b] <= start and start + n <= bounds[b + 1]
+    assert len(bounds) - 1 >= 3
+    one, sb = plan_buckets(segs, padded, 10**9)
+    assert one == [0, padded] and set(sb) == {0}
+    many, _ = plan_buckets(segs, padded, 1, max_buckets=4)       # capped
+    assert len(many) - 1 <= 4

@@ -218,6 +218,39 @@ def test_linear_cross_entropy_matches_reference():
     _close(wk.grad, wr.grad, 5e-2, 5e-2 * wr.grad.abs().mean().item() + 1e-5, "dw")
 
 
+def test_linear_cross_entropy_over_several_slabs():
+    """The head loss walks the rows in slabs of 4096 and sums the head-weight gradient over the slabs in the GEMM
+    epilogue (a bf16 running sum, rounded once per slab).  3 slabs + a ragged tail against the fp32 statement, with a
+    bound on what the per-slab rounding costs."""
+    from rwkvtune_b200.ops import cuda_ops
+    torch.manual_seed(0)
+    slab = cuda_ops._LinearCrossEntropy.SLAB
+    M, C, V = 3 * slab + 17, 256, 4096
+    x = (torch.randn(M, C, device="cuda") * 0.5).to(BF)
+    w = (torch.randn(V, C, device="cuda") * 0.05).to(BF)
+    labels = torch.randint(0, V, (M,), device="cuda")
+    labels[torch.rand(M, device="cuda") < 0.2] = -100
+    xk, wk = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    xr, wr = x.float().clone().requires_grad_(True), w.float().clone().requires_grad_(True)
+    loss = ops.linear_cross_entropy(xk, wk, labels, True, -100, M)
+    loss_r = ref.linear_cross_entropy(xr, wr, labels, True, -100, M)
+    assert abs(loss.item() - loss_r.item()) < 2e-2
+    loss.backward(); loss_r.backward()
+    assert _relnorm(xk.grad, xr.grad) < 2e-2
+    # head gradient: bf16 logits-gradient operands (~0.4 % each) plus one bf16 rounding of the running sum per slab
+    err = _relnorm(wk.grad, wr.grad)
+    assert err < 1.2e-2, err
+    # one-slab evaluation of the same problem (no running sum): the slab accumulation may not add more than 0.4 %
+    cuda_ops._LinearCrossEntropy.SLAB = 1 << 20
+    try:
+        x1, w1 = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+        ops.linear_cross_entropy(x1, w1, labels, True, -100, M).backward()
+    finally:
+        cuda_ops._LinearCrossEntropy.SLAB = slab
+    assert abs(err - _relnorm(w1.grad, wr.grad)) < 4e-3
+    assert _relnorm(wk.grad, w1.grad) < 8e-3
+
+
 @pytest.mark.parametrize("temperature,with_entropy", [(1.0, True), (0.7, True), (1.3, False)])
 def test_linear_logprob_entropy_matches_reference(temperature, with_entropy):
     torch.manual_seed(1)
@@ -239,6 +272,91 @@ def test_linear_logprob_entropy_matches_reference(temperature, with_entropy):
     total.backward(); total_r.backward()
     _close(xk.grad, xr.grad, 5e-2, 5e-2 * xr.grad.abs().mean().item() + 1e-4, "dx")
     _close(wk.grad, wr.grad, 5e-2, 5e-2 * wr.grad.abs().mean().item() + 1e-4, "dw")
+
+
+@pytest.mark.parametrize("with_state", [False, True])
+def test_wkv7_tensor_core_long_sequence(with_state, wkv_impl):
+    """Training length: 4096 steps = 256 chunk steps of carried state (bf16 chunk-boundary states in backward)."""
+    wkv_impl("tc")
+    B, T, H = 1, 4096, 2
+    ins = _wkv_inputs(B, T, H, seed=3)
+    s0 = (torch.randn(B, H, 64, 64, device="cuda") * 0.1) if with_state else None
+    ins_k = [t.clone().requires_grad_(True) for t in ins]
+    ins_r = [t.float().clone().requires_grad_(True) for t in ins]
+    s0_k = s0.clone().requires_grad_(True) if with_state else None
+    s0_r = s0.clone().requires_grad_(True) if with_state else None
+    y, sT = ops.wkv7(*ins_k, 64, state=s0_k, return_state=True)
+    y_ref, sT_ref = ref.wkv7(*ins_r, 64, s0_r)
+    gy = torch.randn_like(y_ref)
+    gs = torch.randn_like(sT_ref) * 0.1
+    (y.float() * gy).sum().add((sT * gs).sum()).backward()
+    (y_ref * gy).sum().add((sT_ref * gs).sum()).backward()
+    assert _relnorm(y, y_ref) < 1.5e-2 and _relnorm(sT, sT_ref) < 1.5e-2
+    for name, a, b in zip("rwkvab", ins_k, ins_r):
+        assert _relnorm(a.grad, b.grad) < 3e-2, (name, _relnorm(a.grad, b.grad))
+    # no drift along the sequence: the last quarter is as accurate as the first
+    q = T // 4
+    assert _relnorm(y[:, -q:], y_ref[:, -q:]) < 1.5e-2
+    assert _relnorm(ins_k[0].grad[:, :q], ins_r[0].grad[:, :q]) < 3e-2
+
+
+def test_wkv7_tensor_core_decay_at_its_bound(wkv_impl):
+    """``w = -0.5`` everywhere is the strongest decay the model can produce (``w = -softplus(.) - 0.5``): the
+    per-chunk rescaling by the inverse cumulative decay is then at its largest."""
+    wkv_impl("tc")
+    B, T, H = 1, 256, 2
+    ins = _wkv_inputs(B, T, H, seed=5)
+    ins[1] = torch.full_like(ins[1], -0.5)
+    ins_k = [t.clone().requires_grad_(True) for t in ins]
+    ins_r = [t.float().clone().requires_grad_(True) for t in ins]
+    y, _ = ops.wkv7(*ins_k, 64)
+    y_ref, _ = ref.wkv7(*ins_r, 64, None)
+    gy = torch.randn_like(y_ref)
+    (y.float() * gy).sum().backward()
+    (y_ref * gy).sum().backward()
+    assert torch.isfinite(y.float()).all()
+    assert _relnorm(y, y_ref) < 1.5e-2
+    for name, a, b in zip("rwkvab", ins_k, ins_r):
+        assert torch.isfinite(a.grad.float()).all()
+        assert _relnorm(a.grad, b.grad) < 3e-2, (name, _relnorm(a.grad, b.grad))
+    # and the weakest decay the bf16 input can express (w strongly negative -> exp(-exp(w)) ~ 1)
+    ins[1] = torch.full_like(ins[1], -8.0)
+    ins_k = [t.clone().requires_grad_(True) for t in ins]
+    ins_r = [t.float().clone().requires_grad_(True) for t in ins]
+    y, _ = ops.wkv7(*ins_k, 64)
+    y_ref, _ = ref.wkv7(*ins_r, 64, None)
+    assert _relnorm(y, y_ref) < 1.5e-2
+
+
+def test_training_step_is_bit_reproducible():
+    """Same seed, same data, twice: split-K weight gradients, the sorted embedding gradient and the two-stage norm
+    all use fixed orders, so parameters after two optimiser steps are bit-identical."""
+    from rwkvtune_b200.engine import EngineConfig, TrainEngine
+    from rwkvtune_b200.models import RWKVConfig, RWKV7Model
+    from rwkvtune_b200.parallel import DistContext
+
+    def run():
+        torch.manual_seed(0)
+        cfg = RWKVConfig(n_layer=2, n_embd=256, vocab_size=2048, dim_att_lora=32, dim_gate_lora=64, dim_mv_lora=32)
+        m = RWKV7Model(cfg)
+        with torch.no_grad():
+            for n, p in m.named_parameters():
+                if n.endswith(("output.weight", "ffn.value.weight", "w1", "a1", "v1", "g1")):
+                    p.copy_(torch.randn_like(p) * 0.05)
+        eng = TrainEngine(m, EngineConfig(lr_init=1e-3, weight_decay=0.01, precision="bf16"),
+                          DistContext(device=torch.device("cuda", 0)))
+        g = torch.Generator().manual_seed(5)
+        losses = []
+        for _ in range(2):
+            idx = torch.randint(0, 2048, (4, 2304), generator=g).cuda()     # 9216 rows: split-K and multi-slab paths
+            losses.append(eng.train_step(idx, idx.roll(-1, 1), 1e-3).item())
+        torch.cuda.synchronize()
+        return losses, eng.space.params.clone()
+
+    l1, p1 = run()
+    l2, p2 = run()
+    assert l1 == l2
+    assert torch.equal(p1, p2)
 
 
 def test_model_step_on_gpu_matches_cpu_reference():
@@ -265,9 +383,14 @@ def test_model_step_on_gpu_matches_cpu_reference():
     bad = []
     for n, p in mg.named_parameters():
         a, b = p.grad.float().cpu(), g_cpu[n]
+        if b.abs().max() <= 1e-6:
+            continue
+        # per-parameter relative error in norm: the bf16 model against the fp32 one (weights, activations and
+        # gradients each rounded to 8 bits of mantissa through two blocks)
+        rel = ((a - b).norm() / b.norm()).item()
         cos = torch.nn.functional.cosine_similarity(a.flatten(), b.flatten(), dim=0).item()
-        if cos < 0.98 and b.abs().max() > 1e-6:
-            bad.append((n, cos))
+        if rel > 0.08 or cos < 0.997:
+            bad.append((n, round(rel, 4), round(cos, 5)))
     assert not bad, bad
 
 

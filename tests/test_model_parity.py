@@ -119,3 +119,50 @@ def test_block_recompute_matches_plain_backward():
     assert abs(l0 - l1) < 1e-6 and g0.keys() == g1.keys() and len(g0) > 10
     for n in g0:
         assert torch.allclose(g0[n], g1[n], atol=1e-6, rtol=1e-5), n
+
+
+def test_tokenizer_matches_reference_trie_on_mixed_text(reference_pkg):
+    """Encode / decode parity with the reference's ``TRIE_TOKENIZER`` (``rwkvtune/data/tokenizers/rwkv_tokenizer.py``)
+    on ASCII, CJK, emoji, control characters and raw bytes that are not valid UTF-8."""
+    from rwkvtune.data.tokenizers.rwkv_tokenizer import TRIE_TOKENIZER as RefTok
+
+    from rwkvtune_b200.data.tokenizers import get_tokenizer
+    from rwkvtune_b200.data.tokenizers.rwkv_tokenizer import TRIE_TOKENIZER
+
+    import rwkvtune.data.tokenizers as ref_tok_pkg
+    import os
+
+    vocab = os.path.join(os.path.dirname(ref_tok_pkg.__file__), "vocab", "rwkv_vocab_v20230424.txt")
+    ref = RefTok(vocab)
+    ours = get_tokenizer()
+    assert isinstance(ours, TRIE_TOKENIZER)
+    texts = [
+        "Hello, world!\n\nUser: hi\n\nAssistant: hello",
+        "The quick brown fox jumps over the lazy dog 1234567890 times.",
+        "中文分词测试：今天天气很好，我们去公园散步吧。",
+        "日本語のテキストと한국어 텍스트 mixed with English",
+        "emoji 🎉🚀👩‍💻 and symbols ∑∫√≠≈ ©®™",
+        "tabs\tand\r\nnewlines\n\n\nand    spaces",
+        "def f(x):\n    return x ** 2  # comment\n",
+        "<|im_start|>system\nYou are helpful.<|im_end|>",
+        "",
+        " ",
+        "a" * 300,
+    ]
+    for t in texts:
+        a, b = ref.encode(t), ours.encode(t)
+        assert a == b, t
+        assert ref.decode(a) == ours.decode(b) == t
+    raw = [bytes([0xff, 0xfe, 0x41, 0x00, 0x80]), bytes(range(256)), "héllo".encode("latin-1")]
+    for bts in raw:
+        a, b = ref.encodeBytes(bts), ours.encodeBytes(bts)
+        assert a == b
+        assert ref.decodeBytes(a) == ours.decodeBytes(b) == bts
+        assert ref.decode(a) == ours.decode(b)      # tolerant decoding of invalid UTF-8
+    import random
+
+    rng = random.Random(0)
+    for _ in range(50):
+        ids = [rng.randrange(1, 65530) for _ in range(40)]
+        assert ref.decode(ids) == ours.decode(ids)
+        assert ref.decodeBytes(ids) == ours.decodeBytes(ids)
