@@ -311,3 +311,122 @@ RWKV_EXPORT int rwkv_zero2_adam_broadcast(const unsigned long long* param_ptrs, 
                                                                     (const float*)gred, a, (const int*)status);
   return rwkv_launch_status();
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// ZeRO-3 helpers for weights stored as K-panels (rank p owns columns [p*Kp, (p+1)*Kp) of a [N, K] matrix as a
+// contiguous [N, Kp] array).
+namespace {
+
+// Gather: staged[n][p*Kp + c] = panel_p[n][c] for every rank p, starting with the local panel.  Plain peer loads,
+// eight 16-byte loads in flight per thread (a peer load takes microseconds: throughput = bytes in flight / latency).
+__global__ void __launch_bounds__(256)
+ag_gather_kernel(PeerPtrs panels, int rank, int world, int N, int K, int Kp, bf16* __restrict__ staged) {
+  constexpr int UNROLL = 8;
+  const int vec_per_row = Kp / 8;
+  const long long total = (long long)N * vec_per_row;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (int s = 0; s < world; ++s) {
+    const int p = (rank + s) % world;
+    const uint4* src = reinterpret_cast<const uint4*>(panels.p[p]);
+    bf16* dst = staged + (long long)p * Kp;
+    for (long long v0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; v0 < total; v0 += stride * UNROLL) {
+      uint4 val[UNROLL];
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const long long v = v0 + u * stride;
+        if (v < total) val[u] = __ldcg(src + v);
+      }
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const long long v = v0 + u * stride;
+        if (v < total) {
+          const long long row = v / vec_per_row;
+          const int c = (int)(v - row * vec_per_row);
+          *reinterpret_cast<uint4*>(dst + row * K + c * 8) = val[u];
+        }
+      }
+    }
+  }
+}
+
+// Reduce-scatter of a full [N, K] weight gradient held by every rank: this rank sums columns [col0, col0 + Kp) of all
+// ranks' matrices (fixed rank order, fp32) into its panel gradient out[N][Kp] (+= when `accumulate`).
+__global__ void __launch_bounds__(256)
+zero3_reduce_panel_kernel(PeerPtrs dw, int world, int N, int K, int Kp, int col0, float scale, float* __restrict__ out,
+                          float* __restrict__ partial, int accumulate, const int* __restrict__ status) {
+  __shared__ float red[8];
+  if (status && *reinterpret_cast<const volatile int*>(status)) return;
+  float acc = 0.f;
+  const int vec_per_row = Kp / 8;
+  const long long total = (long long)N * vec_per_row;
+  for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < total; v += (long long)gridDim.x * blockDim.x) {
+    const long long row = v / vec_per_row;
+    const int c = (int)(v - row * vec_per_row);
+    const long long src_off = row * K + col0 + c * 8;
+    uint4 raw[MAX_RANKS];
+#pragma unroll
+    for (int p = 0; p < MAX_RANKS; ++p)
+      if (p < world) raw[p] = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(dw.p[p]) + src_off));
+    float s[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+    for (int p = 0; p < MAX_RANKS; ++p) {
+      if (p < world) {
+        float f[8];
+        unpack8(raw[p], f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) s[e] += f[e];
+      }
+    }
+    float4* o4 = reinterpret_cast<float4*>(out + v * 8);
+    if (accumulate) {
+      const float4 a0 = o4[0], a1 = o4[1];
+      s[0] = s[0] * scale + a0.x; s[1] = s[1] * scale + a0.y; s[2] = s[2] * scale + a0.z; s[3] = s[3] * scale + a0.w;
+      s[4] = s[4] * scale + a1.x; s[5] = s[5] * scale + a1.y; s[6] = s[6] * scale + a1.z; s[7] = s[7] * scale + a1.w;
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) s[e] *= scale;
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc += s[e] * s[e];
+    o4[0] = make_float4(s[0], s[1], s[2], s[3]);
+    o4[1] = make_float4(s[4], s[5], s[6], s[7]);
+  }
+  acc = warp_sum(acc);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0 && partial) {
+    float t = 0.f;
+    for (int i = 0; i < 8; ++i) t += red[i];
+    partial[blockIdx.x] = t;
+  }
+}
+
+}  // namespace
+
+// staged ([N, K] bf16, local) <- the `world` K-panels ([N, K/world] each) at panel_ptrs (peer-mapped addresses).
+RWKV_EXPORT int rwkv_ag_gather(const unsigned long long* panel_ptrs, int rank, int world, int N, int K, void* staged,
+                               int blocks, void* stream) {
+  PeerPtrs p;
+  int r = fill_ptrs(&p, panel_ptrs, world);
+  if (r) return r;
+  if (N <= 0 || K <= 0 || K % world || (K / world) % 8 || rank < 0 || rank >= world || blocks <= 0) return RWKV_ERR_BAD_SHAPE;
+  if ((uintptr_t)staged & 15) return RWKV_ERR_BAD_ALIGNMENT;
+  ag_gather_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(p, rank, world, N, K, K / world, (bf16*)staged);
+  return rwkv_launch_status();
+}
+
+// out[N][Kp] (+)= scale * sum over ranks of dw_r[:, rank*Kp : (rank+1)*Kp]; dw_ptrs: every rank's [N, K] bf16 gradient.
+// `partial` (may be null) receives `blocks` block sums of out^2.
+RWKV_EXPORT int rwkv_zero3_reduce_panel(const unsigned long long* dw_ptrs, int rank, int world, int N, int K,
+                                        float scale, void* out, void* partial, int blocks, int accumulate,
+                                        const void* status, void* stream) {
+  PeerPtrs p;
+  int r = fill_ptrs(&p, dw_ptrs, world);
+  if (r) return r;
+  if (N <= 0 || K <= 0 || K % world || (K / world) % 8 || rank < 0 || rank >= world || blocks <= 0 || blocks > 1024)
+    return RWKV_ERR_BAD_SHAPE;
+  const int Kp = K / world;
+  zero3_reduce_panel_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(p, world, N, K, Kp, rank * Kp, scale, (float*)out,
+                                                                      (float*)partial, accumulate, (const int*)status);
+  return rwkv_launch_status();
+}

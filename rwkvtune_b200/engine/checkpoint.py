@@ -42,6 +42,9 @@ def save_trainer_state(dirpath: str, engine, ctx, extra_meta: Dict[str, Any], sa
     opt = engine.opt
     if save_optimizer and (opt.stage >= 1 or ctx.rank == 0):
         torch.save(opt.state_dict(), os.path.join(sdir, f"rank{ctx.rank}.pt"))
+    zero3 = getattr(engine, "zero3", None)
+    if save_optimizer and zero3 is not None and zero3.trainable:   # optimiser state of the K-panels this rank owns
+        torch.save(zero3.state_dict(), os.path.join(sdir, f"panels{ctx.rank}.pt"))
     if ctx.rank == 0:
         meta = {"format": 1, "time": time.time(), "world_size": ctx.world_size, "stage": opt.stage,
                 "optimizer_steps": engine.optimizer_steps, "micro_step": engine.micro_step,
@@ -160,6 +163,11 @@ def load_optimizer_state(ckpt_dir: str, engine, ctx) -> bool:
     master, m, v, step = merge_shards(shards)
     dev = engine.space.device
     engine.opt.load_full_state(master.to(dev), m.to(dev), v.to(dev), step)
+    zero3 = getattr(engine, "zero3", None)
+    if zero3 is not None and zero3.trainable:
+        pfiles = sorted(glob.glob(os.path.join(ckpt_dir, STATE_DIR, "panels*.pt")))
+        if pfiles:
+            zero3.load_state([torch.load(f, map_location="cpu", weights_only=False) for f in pfiles])
     engine.optimizer_steps = int(meta.get("optimizer_steps", step))
     engine.micro_step = int(meta.get("micro_step", 0))
     engine.tokens_seen = int(meta.get("tokens_seen", 0))

@@ -71,7 +71,9 @@ class TrainEngine:
         if stage == 3 and ctx.world_size > 1 and ctx.device.type == "cuda" and dtype == torch.bfloat16:
             from ..parallel.zero3 import Zero3ShardedLinears
 
-            self.zero3 = Zero3ShardedLinears(self.model, ctx)
+            # trainable matrices are sharded too when the fused peer-memory transport carries their gradients;
+            # on the library transport they stay replicated with sharded optimiser state (stage-2 behaviour)
+            self.zero3 = Zero3ShardedLinears(self.model, ctx, shard_trainable=cfg.transport in ("p2p", "auto"))
         groups = build_param_groups(self.model.named_parameters(), cfg.weight_decay, cfg.lr_2x_patterns)
         if not groups:
             raise RuntimeError("the model has no trainable parameters")
@@ -99,6 +101,15 @@ class TrainEngine:
         self.stage = stage
         self.opt = ZeroOptimizer(self.space, ctx, min(stage, 2), (cfg.beta1, cfg.beta2), cfg.adam_eps, cfg.grad_clip,
                                  transport)
+        if self.zero3 is not None and self.zero3.trainable:
+            if self.opt._p2p is None:
+                raise RuntimeError("ZeRO-3 with trainable sharded matrices needs the fused peer-memory transport")
+            self.zero3.attach(self.opt._p2p, cfg.weight_decay, (cfg.beta1, cfg.beta2), cfg.adam_eps, cfg.grad_clip)
+        if self.zero3 is not None:
+            n_cp = self.model.config.n_layer if cfg.grad_cp else 0
+            if cfg.grad_cp and isinstance(cfg.grad_cp_layers, int):
+                n_cp = cfg.grad_cp_layers
+            self.zero3.recompute_below = n_cp
         self.micro_step = 0
         self.optimizer_steps = 0
         self.tokens_seen = 0
@@ -132,6 +143,8 @@ class TrainEngine:
             torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
             n_cp = int(t)
         cfg.grad_cp_layers = n_cp
+        if self.zero3 is not None:
+            self.zero3.recompute_below = n_cp
         return n_cp
 
     # ------------------------------------------------------------------ losses
@@ -274,6 +287,8 @@ class TrainEngine:
                 loss = loss.detach()
         with self.phases.phase("reduce_optimizer"):
             self.opt.finish_micro(boundary)
+            if self.zero3 is not None:
+                self.zero3.finish_micro()
             self.micro_step += 1
             self.tokens_seen += idx.numel()
             if boundary:
@@ -292,6 +307,8 @@ class TrainEngine:
             (loss / acc if acc > 1 else loss).backward()
         with self.phases.phase("reduce_optimizer"):
             self.opt.finish_micro(boundary)
+            if self.zero3 is not None:
+                self.zero3.finish_micro()
             self.micro_step += 1
             if boundary:
                 self.opt.step(lr)
@@ -344,6 +361,7 @@ class TrainEngine:
         if self.zero3 is not None:
             from ..ops import gemm_native
 
-            code = gemm_native.check_status(self.ctx.device)
+            self.zero3.check()
+            code = gemm_native.check_status_nosync(self.ctx.device)
             if code:
                 raise RuntimeError(f"rank {self.ctx.rank}: a wait inside the all-gather GEMM expired (code {code})")

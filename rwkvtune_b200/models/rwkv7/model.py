@@ -198,9 +198,9 @@ class RWKV7ChannelMix(nn.Module):
         plain = all(type(m) is Linear and getattr(m, "_sharded", None) is None for m in (self.key, self.value))
         if plain:
             return ops.channel_mix_ffn(xk, self.key.weight, self.value.weight, x), (last if want_state else None)
-        if type(self.key) is Linear:
+        if type(self.key) is Linear and getattr(self.key, "_sharded", None) is None:
             hidden = ops.linear_relu_sq(xk, self.key.weight)
-        else:   # wrapped (e.g. LoRA): activation applied separately
+        else:   # wrapped (LoRA) or sharded (ZeRO-3): activation applied separately
             hidden = ops.relu_squared(self.key(xk))
         return _project_add(self.value, hidden, x), (last if want_state else None)
 

@@ -91,6 +91,15 @@ def addmm_tn_(y: torch.Tensor, a: torch.Tensor, b: torch.Tensor) -> torch.Tensor
     return y.add_((a.t() @ b).to(y.dtype))
 
 
+def mm_tn_into(out: torch.Tensor, a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """``out = a^T @ b`` written into an existing bf16 ``[M, N]`` buffer (a weight gradient formed directly in a
+    communication staging buffer)."""
+    n = _native()
+    if _acc_ok(n, out) and n.native_ok(a, b, "tn"):
+        return n.mm_tn(a, b, out=out, accumulate=False)
+    return out.copy_((a.t() @ b).to(out.dtype))
+
+
 def mm_tn(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     n = _native()
     if n is not None:

@@ -28,6 +28,26 @@ def check_status(device=None) -> int:
     return int(_status(dev).item())
 
 
+_STATUS_HOST = {}
+
+
+def check_status_nosync(device=None) -> int:
+    """Status word as of the last :func:`snapshot_status` (a pinned host copy: no device synchronisation)."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    host = _STATUS_HOST.get(key)
+    return 0 if host is None else int(host[0])
+
+
+def snapshot_status(device=None) -> None:
+    """Queue an asynchronous copy of the status word to pinned host memory (call at the end of a step)."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    if key not in _STATUS_HOST:
+        _STATUS_HOST[key] = torch.zeros(1, dtype=torch.int32).pin_memory()
+    _STATUS_HOST[key].copy_(_status(dev), non_blocking=True)
+
+
 _HAS_GEMM = None
 
 
@@ -60,11 +80,12 @@ def native_ok(x: torch.Tensor, w: torch.Tensor, layout: str) -> bool:
 
 
 def _run(a, b, M, N, K, a_mn: int, b_mn: int, epilogue: int = 0, out: torch.Tensor = None,
-         residual: torch.Tensor = None) -> torch.Tensor:
-    """``out`` given: accumulate into it (epilogue 2, ``out += op(a) op(b)``).  ``residual`` given: return
-    ``residual + op(a) op(b)`` in a new tensor.  Both must be bf16 ``[M, N]`` with unit inner stride."""
+         residual: torch.Tensor = None, accumulate: bool = True) -> torch.Tensor:
+    """``out`` given: accumulate into it (epilogue 2, ``out += op(a) op(b)``) or, with ``accumulate=False``, store
+    into it.  ``residual`` given: return ``residual + op(a) op(b)`` in a new tensor.  Both must be bf16 ``[M, N]``
+    with unit inner stride."""
     if out is not None:
-        c, epilogue = out, 2
+        c, epilogue = out, (2 if accumulate else epilogue)
     else:
         c = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
         if residual is not None and epilogue == 0:
@@ -88,9 +109,9 @@ def mm_nn(x: torch.Tensor, w: torch.Tensor, epilogue: int = 0, out: torch.Tensor
     return _run(x, w, x.shape[0], w.shape[1], x.shape[1], 0, 1, epilogue, out, residual)
 
 
-def mm_tn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor = None) -> torch.Tensor:
+def mm_tn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor = None, accumulate: bool = True) -> torch.Tensor:
     """``a[Kc,M]^T @ b[Kc,N]`` (weight gradients: contraction over the token dimension)"""
-    return _run(a, b, a.shape[1], b.shape[1], a.shape[0], 1, 1, 0, out)
+    return _run(a, b, a.shape[1], b.shape[1], a.shape[0], 1, 1, 0, out, None, accumulate)
 
 
 _SPLITK_WS = {}

@@ -124,6 +124,8 @@ class FusedZero2:
                 self.launch_of_bucket[b] = (len(self.launch_of_bucket), lo, hi - lo)
         self.partials = torch.zeros(max(1, len(self.launch_of_bucket)) * REDUCE_BLOCKS, dtype=torch.float32, device=dev)
         self.extra_sumsq: Optional[torch.Tensor] = None   # squared norm of gradients reduced elsewhere (ZeRO-3 panels)
+        self.before_publish = None    # callable(): runs before this rank's norm share is published
+        self.after_norm = None        # callable(lr): runs once every rank's norm share has arrived
         self.comm = torch.cuda.Stream(device=dev)
         self._events = [torch.cuda.Event() for _ in range(self.n_buckets)]
         self._joined = torch.cuda.Event()
@@ -238,9 +240,13 @@ class FusedZero2:
             self.finish_micro(True, grad_scale)
         opt.step_count += 1
         n_part = len(self.launch_of_bucket) * REDUCE_BLOCKS
+        if self.before_publish is not None:
+            self.before_publish()
         _ext.call("rwkv_zero2_publish_norm", _ext.ptr(self.partials), _ext.i32(n_part), _ext.ptr(self.extra_sumsq),
                   self.ctrl_ptrs, _ext.i32(self.rank), _ext.i32(self.W), _ext.stream())
         self._barrier()                      # all norm shares published; all peers done reading my gradients
+        if self.after_norm is not None:
+            self.after_norm(lr)
         for gi, s, e in sp.group_segments_in(opt.lo, opt.hi):
             grp = sp.groups[gi]
             a, b = s - opt.lo, e - opt.lo

@@ -146,6 +146,37 @@ def test_bucket_flag_signal_and_bounded_wait():
     assert int(status.item()) == 0
 
 
+def test_panel_gather_and_panel_reduce_emulated_ranks():
+    """ZeRO-3 helpers on one device: the gather reassembles a matrix from column panels; the panel reduce sums one
+    column panel of every rank's full weight gradient in fp32, accumulating across calls."""
+    from rwkvtune_b200.ops import _ext
+
+    torch.manual_seed(2)
+    W, N, K = 4, 96, 256
+    Kp = K // W
+    full = torch.randn(N, K, device="cuda").to(torch.bfloat16)
+    panels = [full[:, p * Kp:(p + 1) * Kp].contiguous() for p in range(W)]
+    st = _ext.stream()
+    for rank in (0, 3):
+        staged = torch.zeros(N, K, dtype=torch.bfloat16, device="cuda")
+        _ext.call("rwkv_ag_gather", _arr(panels), _ext.i32(rank), _ext.i32(W), _ext.i32(N), _ext.i32(K),
+                  _ext.ptr(staged), _ext.i32(8), st)
+        torch.cuda.synchronize()
+        assert torch.equal(staged, full)
+    dws = [(torch.randn(N, K, device="cuda") * 0.1).to(torch.bfloat16) for _ in range(W)]
+    ref_sum = sum(d.float() for d in dws) / W
+    part = torch.zeros(512, device="cuda")
+    for rank in range(W):
+        out = torch.zeros(N, Kp, device="cuda")
+        for rep in range(2):      # second call accumulates
+            _ext.call("rwkv_zero3_reduce_panel", _arr(dws), _ext.i32(rank), _ext.i32(W), _ext.i32(N), _ext.i32(K),
+                      _ext.f32(1.0 / W), _ext.ptr(out), _ext.ptr(part), _ext.i32(4), _ext.i32(rep), _ext.ptr(None), st)
+        torch.cuda.synchronize()
+        want = ref_sum[:, rank * Kp:(rank + 1) * Kp] * 2
+        assert torch.allclose(out, want, atol=1e-5)
+        assert torch.allclose(part.sum(), want.square().sum(), rtol=1e-4)
+
+
 _WORKER = r'''
 import os, sys, json, torch
 sys.path.insert(0, os.environ["RWKV_ROOT"])
@@ -238,6 +269,24 @@ for strategy in ("deepspeed_stage_2", "deepspeed_stage_3"):
     torch.cuda.synchronize()
     out[strategy] = losses
     assert gemm_native.check_status() == 0
+    eng.check_health()
+    if strategy.endswith("3"):
+        # full / merged saves under stage 3 reassemble the sharded base weights (rank 0 only, no collective)
+        from rwkvtune_b200.training.model_save_utils import save_model_or_adapter
+        from rwkvtune_b200 import AutoModel
+        idx = torch.randint(0, 1024, (1, 64), generator=torch.Generator().manual_seed(5)).to(ctx.device)
+        with torch.no_grad():
+            want = eng.model(idx).float()
+        torch.distributed.barrier()
+        if ctx.rank == 0:
+            save_dir = os.environ["RWKV_SAVE_DIR"]
+            save_model_or_adapter(eng.model, save_dir, None, "both")
+            merged = AutoModel.from_pretrained(os.path.join(save_dir, "merged")).to(ctx.device).to(torch.bfloat16)
+            with torch.no_grad():
+                got = merged(idx).float()
+            out["merged_rel_err"] = ((got - want).norm() / want.norm()).item()
+            out["adapter_saved"] = os.path.exists(os.path.join(save_dir, "adapter_model.bin"))
+        torch.distributed.barrier()
 torch.distributed.barrier()
 if ctx.rank == 0:
     print(json.dumps(out))
@@ -249,7 +298,7 @@ torch.distributed.destroy_process_group()
 def test_zero3_lora_fused_allgather_gemm_matches_stage2(tmp_path):
     script = tmp_path / "worker_z3.py"
     script.write_text(_WORKER_Z3)
-    env = dict(os.environ, RWKV_ROOT=ROOT, NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, RWKV_ROOT=ROOT, NCCL_NVLS_ENABLE="0", RWKV_SAVE_DIR=str(tmp_path / "saved"))
     res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
                           "--master-addr", "127.0.0.1", "--master-port", "29534", str(script)],
                          capture_output=True, text=True, env=env, timeout=300)
@@ -259,3 +308,72 @@ def test_zero3_lora_fused_allgather_gemm_matches_stage2(tmp_path):
     for x, y in zip(rec["deepspeed_stage_2"], rec["deepspeed_stage_3"]):
         assert abs(x - y) < 5e-2, rec
     assert rec["deepspeed_stage_3"][-1] < rec["deepspeed_stage_3"][0]
+    assert rec["adapter_saved"] and rec["merged_rel_err"] < 2e-2, rec
+
+
+_WORKER_Z3_FULL = r'''
+import os, sys, json, torch
+sys.path.insert(0, os.environ["RWKV_ROOT"])
+from rwkvtune_b200.engine import EngineConfig, TrainEngine
+from rwkvtune_b200.models import RWKVConfig, RWKV7Model
+from rwkvtune_b200.parallel import init_distributed
+ctx = init_distributed("gpu")
+out = {}
+weights = {}
+for tag, strategy, cp, acc in (("s2", "deepspeed_stage_2", 0, 1), ("s3", "deepspeed_stage_3", 0, 1),
+                               ("s3_cp", "deepspeed_stage_3", 1, 1), ("s2_acc", "deepspeed_stage_2", 0, 2),
+                               ("s3_acc", "deepspeed_stage_3", 0, 2)):
+    torch.manual_seed(0)
+    cfg = RWKVConfig(n_layer=3, n_embd=256, vocab_size=1024, dim_att_lora=32, dim_gate_lora=64, dim_mv_lora=32)
+    model = RWKV7Model(cfg)
+    with torch.no_grad():
+        for n, p in model.named_parameters():
+            if n.endswith(("output.weight", "ffn.value.weight")):
+                p.normal_(0, 0.05)
+    eng = TrainEngine(model, EngineConfig(lr_init=2e-3, weight_decay=0.01, strategy=strategy, precision="bf16", grad_cp=cp,
+                                          transport="p2p", accumulate_grad_batches=acc), ctx)
+    if strategy.endswith("3"):
+        z = eng.zero3
+        assert z is not None and len(z.trainable) == 18, "stage 3 did not shard the trainable projection weights"
+        assert all(m.weight.numel() == 0 for m in eng.model.modules() if getattr(m, "_sharded", None) is not None)
+    g = torch.Generator().manual_seed(100 + ctx.rank)
+    losses = []
+    for step in range(4 * acc):
+        idx = torch.randint(0, 1024, (2, 128), generator=g).to(ctx.device)
+        losses.append(float(eng.train_step(idx, idx.roll(-1, 1), 2e-3)))
+    torch.cuda.synchronize()
+    eng.check_health()
+    out[tag] = losses
+    blk = eng.model.blocks[1]
+    if strategy.endswith("3"):
+        weights[tag] = torch.cat([blk.att.key._sharded.full_weight().float().flatten(),
+                                  blk.ffn.value._sharded.full_weight().float().flatten()]).clone()
+    else:
+        weights[tag] = torch.cat([blk.att.key.weight.float().flatten(), blk.ffn.value.weight.float().flatten()]).clone()
+    torch.distributed.barrier()
+rel = lambda a, b: ((weights[a] - weights[b]).norm() / weights[b].norm()).item()
+if ctx.rank == 0:
+    out["rel_s3"], out["rel_s3_cp"], out["rel_s3_acc"] = rel("s3", "s2"), rel("s3_cp", "s2"), rel("s3_acc", "s2_acc")
+    print(json.dumps(out))
+torch.distributed.destroy_process_group()
+'''
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_zero3_full_parameter_training_matches_stage2(tmp_path):
+    """Every projection matrix sharded and trained through its panel: same losses and weights as the replicated
+    stage-2 run, with and without activation checkpointing and with gradient accumulation."""
+    script = tmp_path / "worker_z3_full.py"
+    script.write_text(_WORKER_Z3_FULL)
+    env = dict(os.environ, RWKV_ROOT=ROOT, NCCL_NVLS_ENABLE="0")
+    res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                          "--master-addr", "127.0.0.1", "--master-port", "29535", str(script)],
+                         capture_output=True, text=True, env=env, timeout=300)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-3000:]
+    import json
+    rec = json.loads([l for l in res.stdout.splitlines() if l.startswith("{")][-1])
+    for a, b in (("s3", "s2"), ("s3_cp", "s2"), ("s3_acc", "s2_acc")):
+        for x, y in zip(rec[a], rec[b]):
+            assert abs(x - y) < 5e-2, rec
+    assert rec["s3"][-1] < rec["s3"][0]
+    assert rec["rel_s3"] < 2e-2 and rec["rel_s3_cp"] < 2e-2 and rec["rel_s3_acc"] < 2e-2, rec
