@@ -4,6 +4,8 @@
     python benchmarks/config_bench.py --config infctx       # 0.4B, 65536-token sequences in 4096-token chunks
     python benchmarks/config_bench.py --config grpo         # 1.5B GRPO (dapo, beta 0.04), LoRA r=64, G=8
     python benchmarks/config_bench.py --config collectives  # fused reduce-scatter / AdamW+broadcast vs NVLink roofline
+    python benchmarks/config_bench.py --config ag_gemm      # all-gather-fused GEMM vs plain GEMM at the 2.9B shapes
+    python benchmarks/config_bench.py --config full_zero3   # full-parameter stage 3 vs stage 2 step time
 
 Multi-GPU: ``python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 benchmarks/config_bench.py ...``.
 Synthetic uniform-random tokens, random-init weights, bf16; timed on the device with CUDA events after warm-up,
@@ -290,18 +292,140 @@ def bench_collectives(a):
                                         "rate of a plain peer-to-peer copy measured on this pool"}}
 
 
+def bench_ag_gemm(a):
+    """The all-gather-fused GEMM in isolation at the 2.9B projection shapes (tokens = 2 x 8192): the fused kernel
+    (panels pulled over NVLink by copy CTAs while the MMA CTAs run) against the plain tcgen05 GEMM on a weight that
+    is already gathered, and the stand-alone gather kernel.  Roofline: the slower of FLOPs / measured bf16 peak and
+    remote panel bytes / link bandwidth."""
+    from rwkvtune_b200.ops import gemm_native
+    from rwkvtune_b200.parallel.zero3 import Zero3ShardedLinears
+    import torch.nn as nn
+
+    ctx = _ctx()
+    W = ctx.world_size
+    if W < 2:
+        raise SystemExit("--config ag_gemm needs at least 2 ranks")
+    C, M = 2560, (a.micro_bsz or 2) * (a.ctx_len or 8192)
+
+    class Holder(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.blocks = nn.ModuleList([nn.ModuleDict({"att": nn.ModuleDict({"receptance": nn.Linear(C, C, bias=False)}),
+                                                        "ffn": nn.ModuleDict({"key": nn.Linear(C, 4 * C, bias=False),
+                                                                              "value": nn.Linear(4 * C, C, bias=False)})})
+                                         for _ in range(2)])
+
+    torch.manual_seed(3)
+    with torch.device(ctx.device):
+        holder = Holder().to(torch.bfloat16)
+    for p in holder.parameters():
+        p.requires_grad_(False)
+    full = {n: m.weight.data.clone() for n, m in holder.named_modules() if isinstance(m, nn.Linear)}
+    z3 = Zero3ShardedLinears(holder, ctx)
+    rows = {}
+    peak = 1615.2
+    if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")):
+        peak = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"]
+    for sw in z3.sharded:
+        if sw.layer != 0:
+            continue
+        x = torch.randn(M, sw.K, device=ctx.device).to(torch.bfloat16)
+        wfull = full[sw.name]
+        other = [o for o in z3.sharded if o.slot == sw.slot and o is not sw][0]
+
+        def timed(fn, flush):
+            ts = []
+            for it in range(a.warmup + a.steps):
+                flush()
+                if W > 1:
+                    torch.distributed.barrier()
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                fn()
+                e1.record()
+                torch.cuda.synchronize()
+                if it >= a.warmup:
+                    ts.append(e0.elapsed_time(e1))
+            ts.sort()
+            return _max_over_ranks(ctx, ts[len(ts) // 2])
+
+        nothing = lambda: None
+        plain = timed(lambda: gemm_native.mm_nt(x, wfull), nothing)
+        fused = timed(lambda: z3.forward_gemm(x, sw), nothing)
+        gw = sw.gathered()
+        gather = timed(lambda: z3.gather_into(sw, gw, __import__("rwkvtune_b200.ops._ext", fromlist=["x"]).stream()), nothing)
+        flops = 2.0 * M * sw.N * sw.K
+        remote = sw.N * sw.K * 2 * (W - 1) / W
+        floor_ms = max(flops / (peak * 1e12), remote / (NVLINK_NOMINAL_GBS * 1e9)) * 1e3
+        y = z3.forward_gemm(x, sw)
+        ref = gemm_native.mm_nt(x, wfull)
+        rows[sw.slot] = {"N": sw.N, "K": sw.K, "plain_gemm_ms": plain, "fused_ag_gemm_ms": fused, "gather_only_ms": gather,
+                         "fused_over_plain": fused / plain, "roofline_floor_ms": floor_ms,
+                         "fused_fraction_of_roofline": floor_ms / fused, "remote_bytes": remote,
+                         "gather_gbs": remote / (gather * 1e-3) / 1e9,
+                         "max_abs_diff_vs_plain": float((y.float() - ref.float()).abs().max())}
+        del other
+    worst = max(r["fused_over_plain"] for r in rows.values())
+    return ctx, {"metric": "ag_gemm_time_over_plain_gemm_time", "value": worst, "shapes": rows,
+                 "config": {"model": "rwkv7-2.9b projection shapes", "tokens": M, "parallelism": f"zero3-dp{W}",
+                            "roofline": f"max(FLOPs / {peak} TFLOP/s measured, remote panel bytes / 900 GB/s)"}}
+
+
+def bench_full_zero3(a):
+    """Full-parameter training with every projection matrix sharded (stage 3) against the replicated stage-2 run of
+    the same model and batch."""
+    from rwkvtune_b200.engine import EngineConfig, TrainEngine
+    from rwkvtune_b200.models import RWKVConfig, RWKV7Model
+
+    ctx = _ctx()
+    B, T = a.micro_bsz or 8, a.ctx_len or 4096
+    out = {}
+    for strategy in ("deepspeed_stage_2", "deepspeed_stage_3"):
+        cfg = RWKVConfig(vocab_size=65536, ctx_len=T, **MODELS[a.model or "1.5b"])
+        torch.manual_seed(7)
+        with torch.device(ctx.device):
+            model = RWKV7Model(cfg)
+        eng = TrainEngine(model, EngineConfig(lr_init=1e-4, weight_decay=0.01, grad_clip=1.0, strategy=strategy,
+                                              precision="bf16", grad_cp=1, transport="p2p"), ctx)
+        g = torch.Generator().manual_seed(100 + ctx.rank)
+        ids = torch.randint(0, 65536, (B, T), generator=g).to(ctx.device)
+        state = {}
+
+        def step(i):
+            eng.train_step(ids, ids, 1e-4)
+            if i == 0:
+                torch.cuda.synchronize()
+                state["cp"] = eng.autotune_checkpointing(B, T)
+
+        torch.cuda.reset_peak_memory_stats()
+        ms = _time_steps(ctx, step, a.warmup, a.steps)
+        eng.check_health()
+        out[strategy] = {"ms_per_step": ms, "tokens_per_sec": B * T * ctx.world_size / ms * 1e3,
+                         "checkpointed_layers": state.get("cp"),
+                         "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2**30, 1)}
+        del eng, model
+        torch.cuda.empty_cache()
+    s2, s3 = out["deepspeed_stage_2"]["ms_per_step"], out["deepspeed_stage_3"]["ms_per_step"]
+    return ctx, {"metric": "zero3_step_time_over_zero2_step_time", "value": s3 / s2, **out,
+                 "config": {"model": f"rwkv7-{a.model or '1.5b'}", "seq_len": T, "micro_bsz": B,
+                            "parallelism": f"dp{ctx.world_size}"}}
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--config", required=True, choices=["lora_zero3", "infctx", "grpo", "collectives"])
+    ap.add_argument("--config", required=True, choices=["lora_zero3", "infctx", "grpo", "collectives", "ag_gemm", "full_zero3"])
     ap.add_argument("--steps", type=int, default=4)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--micro-bsz", type=int, default=0)
     ap.add_argument("--ctx-len", type=int, default=0)
     ap.add_argument("--new-tokens", type=int, default=512)
+    ap.add_argument("--model", default="", help="full_zero3: model size (default 1.5b)")
     ap.add_argument("--no-graph", action="store_true", help="infctx: issue every chunk eagerly instead of replaying a CUDA graph")
     a = ap.parse_args()
     ctx, out = {"lora_zero3": bench_lora_zero3, "infctx": bench_infctx, "grpo": bench_grpo,
-                "collectives": bench_collectives}[a.config](a)
+                "collectives": bench_collectives, "ag_gemm": bench_ag_gemm,
+                "full_zero3": bench_full_zero3}[a.config](a)
     out.update({"n_gpus": ctx.world_size, "steps": a.steps, "warmup": a.warmup, "dtype": "bf16", "data": "synthetic"})
     if ctx.is_main:
         print(json.dumps(out))

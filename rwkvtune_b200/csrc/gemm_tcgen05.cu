@@ -36,6 +36,7 @@ constexpr int C_CHUNK_BYTES = BM * 64 * 2;    // 128 rows x 64 bf16
 constexpr int NUM_THREADS = 192;
 constexpr int TMEM_COLS = 512;
 constexpr uint32_t WAIT_LIMIT = 1u << 28;
+constexpr int MAX_RANKS = 16;
 
 struct Barriers {
   uint64_t full[STAGES];
@@ -133,66 +134,70 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-constexpr int MAX_RANKS = 16;
-
 // All-gather fused into the GEMM (ZeRO-3): the weight is stored as K-panels, rank p owning columns
-// [p*Kp, (p+1)*Kp) as a contiguous [N, Kp] matrix.  A few CTAs of the same grid copy the panels from
-// the owners' memory (plain peer loads over NVLink) into a local [N, K] staging matrix and raise one
-// flag per panel; the GEMM CTAs walk the contraction panel by panel in arrival order (own panel first)
-// and TMA-load B from the staging matrix as soon as the panel's flag is up.  Each remote byte crosses
-// NVLink once; the transfer of panel p+1 overlaps the MMAs on panel p.
+// [p*Kp, (p+1)*Kp) as a contiguous [N, Kp] matrix.  Every CTA of the GEMM carries four extra "copy" warps.
+// Copy warp q of every CTA works on the row blocks j = q, q + 4, ... of the weight (a row block = 256 weight
+// rows = one output-column tile, all panels): the 148 warps with the same q pull that row block from the owners'
+// memory - plain peer loads over NVLink, eight 16-byte loads in flight per thread, all peers at once - into a
+// local [N, K] staging matrix and each adds one arrival to the row block's counter.  Four row blocks are in
+// flight at any time and they complete in order.  The tiles are walked in groups of column tiles, and the TMA
+// producer of a tile waits only for the row block it is about to load: the MMAs of the first column tiles run
+// while the rest of the weight is still crossing NVLink, no SM is set aside for copying, and each remote byte
+// crosses the link once.
 struct AgParams {
   const bf16* shard[MAX_RANKS];
   bf16* staged;
-  int* panel_flag;     // [world], equals `epoch` once the panel has landed
-  int* panel_count;    // [world], monotonically increasing arrival counters
-  int rank, world, epoch, n_copy, Kp;
+  int* blk_count;      // [n_rb] arrival counters, monotonically increasing over calls
+  int rank, world, Kp, n_rb;
+  int target;          // a row block has landed when its counter has reached this value
+  int group;           // column tiles per tile group (see the tile order below)
 };
+constexpr int AG_COPY_WARPS = 4;
 
 __device__ __forceinline__ int ld_acquire_gpu(const int* p) {
   int v;
   asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ void st_release_gpu(int* p, int v) {
-  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
 
-__device__ void ag_copy_role(const AgParams& ag, int N, int K) {
-  // A peer load takes a couple of microseconds to come back, so throughput is bytes in flight / latency:
-  // every thread keeps AG_UNROLL independent 16-byte loads outstanding before it stores any of them.
-  constexpr int AG_UNROLL = 8;
-  const int vec_per_row = ag.Kp / 8;
-  const long long total = (long long)N * vec_per_row;
-  const long long stride = (long long)ag.n_copy * blockDim.x;
-  for (int s = 0; s < ag.world; ++s) {
-    const int p = (ag.rank + s) % ag.world;
-    const uint4* src = reinterpret_cast<const uint4*>(ag.shard[p]);
-    bf16* dst = ag.staged + (long long)p * ag.Kp;
-    for (long long v0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; v0 < total; v0 += stride * AG_UNROLL) {
-      uint4 val[AG_UNROLL];
+// Runs in warps NUM_THREADS/32 .. NUM_THREADS/32 + AG_COPY_WARPS - 1 of every CTA.
+__device__ void ag_copy_role(const AgParams& ag, int N, int K, int cta, int n_cta) {
+  constexpr int UNROLL = 8;
+  const int wq = ((int)threadIdx.x - NUM_THREADS) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long g = (long long)cta * 32 + lane;          // this thread among the threads that share a row block
+  const long long G = (long long)n_cta * 32;
+  const int vec_per_prow = ag.Kp / 8;                      // 16-byte vectors per panel row
+  const int vec_per_row = K / 8;
+  for (int j = wq; j < ag.n_rb; j += AG_COPY_WARPS) {
+    const int r0 = j * BN;
+    const int rows = min(BN, N - r0);
+    const long long total = (long long)rows * vec_per_row;
+    for (long long v0 = g; v0 < total; v0 += G * UNROLL) {
+      uint4 val[UNROLL];
+      long long dst_off[UNROLL];
 #pragma unroll
-      for (int u = 0; u < AG_UNROLL; ++u) {
-        const long long v = v0 + u * stride;
-        if (v < total) val[u] = __ldcg(src + v);
+      for (int u = 0; u < UNROLL; ++u) {
+        const long long v = v0 + u * G;
+        if (v < total) {
+          const int row = (int)(v / vec_per_row);
+          const int cv = (int)(v - (long long)row * vec_per_row);
+          const int p = cv / vec_per_prow;
+          const int c = cv - p * vec_per_prow;
+          val[u] = __ldcg(reinterpret_cast<const uint4*>(ag.shard[p]) + (long long)(r0 + row) * vec_per_prow + c);
+          dst_off[u] = (long long)(r0 + row) * K + (long long)cv * 8;
+        }
       }
 #pragma unroll
-      for (int u = 0; u < AG_UNROLL; ++u) {
-        const long long v = v0 + u * stride;
-        if (v < total) {
-          const long long row = v / vec_per_row;
-          const int c = (int)(v - row * vec_per_row);
-          *reinterpret_cast<uint4*>(dst + row * K + c * 8) = val[u];
-        }
+      for (int u = 0; u < UNROLL; ++u) {
+        const long long v = v0 + u * G;
+        if (v < total) *reinterpret_cast<uint4*>(ag.staged + dst_off[u]) = val[u];
       }
     }
     __threadfence();
     asm volatile("fence.proxy.async;" ::: "memory");
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      const int old = atomicAdd(&ag.panel_count[p], 1);
-      if (old + 1 == ag.epoch * ag.n_copy) st_release_gpu(&ag.panel_flag[p], ag.epoch);
-    }
+    __syncwarp();
+    if (lane == 0) atomicAdd(&ag.blk_count[j], 1);
   }
 }
 
@@ -201,17 +206,13 @@ __device__ void ag_copy_role(const AgParams& ag, int N, int K) {
 //      5 = x * 2 sqrt(Y) with Y a bf16 [M,N] matrix: the derivative of relu(p)^2 expressed through its output Y,
 //          applied to the dgrad of the channel-mix value projection (no separate activation-backward pass)
 template <bool A_MN, bool B_MN, int EPI, bool AG>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(AG ? NUM_THREADS + AG_COPY_WARPS * 32 : NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const __grid_constant__ CUtensorMap map_c, int M, int N, int K, int* status,
                     const bf16* __restrict__ c_in, long long ldc, int splits, float* __restrict__ partial,
                     const __grid_constant__ AgParams ag) {
-  if (AG && (int)blockIdx.x < ag.n_copy) {   // copy CTAs never touch barriers or tensor memory
-    ag_copy_role(ag, N, K);
-    return;
-  }
-  const int cta = AG ? (int)blockIdx.x - ag.n_copy : (int)blockIdx.x;
-  const int n_cta = AG ? (int)gridDim.x - ag.n_copy : (int)gridDim.x;
+  const int cta = (int)blockIdx.x;
+  const int n_cta = (int)gridDim.x;
   extern __shared__ unsigned char smem_dyn[];
   const uint32_t raw = smem_u32(smem_dyn);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -227,6 +228,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   // kernel sums the slices.  For products with few output tiles and a long contraction (weight gradients of the
   // low-rank maps: 16 tiles, K = tokens) this is what fills the SMs.  splits == 1 is the plain path.
   const int num_items = num_tiles * splits;
+  // plain GEMM: row-tile-major (consecutive CTAs share the A tile's row panel and sweep B, which stays in L2).
+  // All-gather variant: the column tiles are taken in groups of `ag.group`, group after group in the order in which
+  // their weight rows arrive, and row-tile-major inside a group: early tiles need only the first row blocks of the
+  // weight, while A is re-read once per group instead of once per column tile.
+  auto tile_m0 = [&](int tile) {
+    if (!AG) return (tile / tiles_n) * BM;
+    const int per_group = tiles_m * ag.group;
+    const int g = tile / per_group;
+    const int gn = min(ag.group, tiles_n - g * ag.group);
+    return ((tile - g * per_group) / gn) * BM;
+  };
+  auto tile_n0 = [&](int tile) {
+    if (!AG) return (tile % tiles_n) * BN;
+    const int per_group = tiles_m * ag.group;
+    const int g = tile / per_group;
+    const int gn = min(ag.group, tiles_n - g * ag.group);
+    return (g * ag.group + (tile - g * per_group) % gn) * BN;
+  };
   auto kb_range = [&](int sp, int& lo, int& hi) {
     lo = (int)((long long)num_kb * sp / splits);
     hi = (int)((long long)num_kb * (sp + 1) / splits);
@@ -256,30 +275,26 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       bool ok = true;
       for (int item = cta; item < num_items && ok; item += n_cta) {
         const int tile = item / splits;
-        const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+        const int m0 = tile_m0(tile), n0 = tile_n0(tile);
         int kb_lo, kb_hi;
         kb_range(item - tile * splits, kb_lo, kb_hi);
         for (int kb = kb_lo; kb < kb_hi; ++kb) {
-          int k0 = kb * BK;
-          if (AG) {   // contraction walked panel by panel, starting with the locally owned one
-            const int kb_per_panel = ag.Kp / BK;
-            const int s_idx = kb / kb_per_panel;
-            const int p = (ag.rank + s_idx) % ag.world;
-            k0 = p * ag.Kp + (kb - s_idx * kb_per_panel) * BK;
-            if (kb % kb_per_panel == 0) {
-              bool landed = false;
-              for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
-                if (ld_acquire_gpu(&ag.panel_flag[p]) >= ag.epoch) { landed = true; break; }
-                if ((it & 0xfff) == 0xfff && *reinterpret_cast<volatile int*>(&bars->abort_flag)) break;
-              }
-              if (!landed) {
-                *reinterpret_cast<volatile int*>(&bars->abort_flag) = 1;
-                if (status) atomicCAS(status, 0, 105);
-                ok = false;
-                break;
-              }
-              asm volatile("fence.proxy.async;" ::: "memory");
+          const int k0 = kb * BK;
+          if (AG && kb == kb_lo) {   // the row block of the weight that this column tile reads must have landed
+            const int* cnt = &ag.blk_count[n0 / BN];
+            bool landed = false;
+            for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
+              if (ld_acquire_gpu(cnt) >= ag.target) { landed = true; break; }
+              if ((it & 0xfff) == 0xfff && *reinterpret_cast<volatile int*>(&bars->abort_flag)) break;
+              __nanosleep(32);
             }
+            if (!landed) {
+              *reinterpret_cast<volatile int*>(&bars->abort_flag) = 1;
+              if (status) atomicCAS(status, 0, 105);
+              ok = false;
+              break;
+            }
+            asm volatile("fence.proxy.async;" ::: "memory");
           }
           if (!mbar_wait(&bars->empty[stage], phase ^ 1, bars, status, 101)) { ok = false; break; }
           mbar_expect_tx(&bars->full[stage], STAGE_BYTES);
@@ -335,6 +350,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (ok) umma_commit(&bars->acc_full[acc]);
       }
     }
+  } else if (AG && warp >= NUM_THREADS / 32) {
+    // ------------------------------------------------------------------ panel copy (all-gather variant only)
+    ag_copy_role(ag, N, K, cta, n_cta);
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
     const int quarter = warp & 3;                 // tensor-memory lanes [32q, 32q+32)
@@ -344,7 +362,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     bool ok = true;
     for (int item = cta; item < num_items && ok; item += n_cta, ++local) {
       const int tile = item / splits, sp = item - tile * splits;
-      const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+      const int m0 = tile_m0(tile), n0 = tile_n0(tile);
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
       mbar_wait(&bars->acc_full[acc], acc_phase, bars, status, 104);
@@ -524,7 +542,7 @@ int launch_splitk(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMa
 }
 
 int launch_ag(CUtensorMap ma, CUtensorMap mb, CUtensorMap mc, int M, int N, int K, int* status, int sms,
-              AgParams ag, cudaStream_t st) {
+              AgParams ag, int* arrivals_io, cudaStream_t st) {
   auto kern = gemm_tcgen05_kernel<false, false, 0, true>;
   static bool configured = false;
   if (!configured) {
@@ -533,16 +551,19 @@ int launch_ag(CUtensorMap ma, CUtensorMap mb, CUtensorMap mc, int M, int N, int 
     configured = true;
   }
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-  int n_gemm = sms - ag.n_copy;
-  if (tiles < n_gemm) n_gemm = tiles;
-  const int grid = n_gemm + ag.n_copy;
-  // GEMM CTAs wait for copy CTAs of the same grid: a cooperative launch guarantees they are co-resident
+  const int grid = tiles < sms ? tiles : sms;
+  // every row block receives one arrival per CTA of the grid
+  *arrivals_io += grid;
+  ag.target = *arrivals_io;
+  // tile producers wait for copy warps of other CTAs of the same grid: a cooperative launch guarantees that all
+  // CTAs are resident together
   const bf16* c_in = nullptr;
   long long ldc = 0;
   int splits = 1;
   float* partial = nullptr;
   void* args[] = {&ma, &mb, &mc, &M, &N, &K, &status, &c_in, &ldc, &splits, &partial, &ag};
-  cudaError_t e = cudaLaunchCooperativeKernel((void*)kern, dim3(grid), dim3(NUM_THREADS), args, SMEM_BYTES, st);
+  cudaError_t e = cudaLaunchCooperativeKernel((void*)kern, dim3(grid), dim3(NUM_THREADS + AG_COPY_WARPS * 32), args,
+                                              SMEM_BYTES, st);
   return e == cudaSuccess ? rwkv_launch_status() : RWKV_ERR_CUDA_BASE + (int)e;
 }
 
@@ -627,20 +648,21 @@ RWKV_EXPORT int rwkv_gemm_bf16_tcgen05_splitk(const void* a, const void* b, void
 
 // y[M,N] = x[M,K] @ W[N,K]^T where W is stored as `world` K-panels, panel p ([N, K/world], row-major) living at
 // shard_ptrs[p] (peer-mapped addresses; shard_ptrs[rank] is local).  `staged` ([N,K] bf16, local) receives the
-// gathered weight and can be reused afterwards (e.g. by the backward pass).  panel_flag / panel_count: `world`
-// device ints each, zero-initialised once; `epoch` must increase by one per call on the same buffers.
+// gathered weight and can be reused afterwards (e.g. by the backward pass).  blk_count: ceil(N / 256)
+// device ints, zero-initialised once; *arrivals_io: host-side running total of arrivals per counter (0 before the
+// first call on these buffers), advanced by this call.
 RWKV_EXPORT int rwkv_ag_gemm_bf16_tcgen05(const void* x, const unsigned long long* shard_ptrs, void* staged, void* y,
-                                          int M, int N, int K, int rank, int world, void* panel_flag,
-                                          void* panel_count, int epoch, int n_copy, void* status, void* stream) {
+                                          int M, int N, int K, int rank, int world, void* blk_count,
+                                          int* arrivals_io, void* status, void* stream) {
   if (M <= 0 || N <= 0 || K <= 0 || world <= 0 || world > MAX_RANKS || rank < 0 || rank >= world) return RWKV_ERR_BAD_SHAPE;
-  if (K % world || (K / world) % BK || n_copy <= 0 || epoch <= 0) return RWKV_ERR_BAD_SHAPE;
+  if (K % world || (K / world) % BK || !arrivals_io || !blk_count) return RWKV_ERR_BAD_SHAPE;
+  if (*arrivals_io > 0x70000000) return RWKV_ERR_TOO_LARGE;
   static int sms = 0;
   if (!sms) {
     int dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   }
-  if (n_copy >= sms) return RWKV_ERR_BAD_SHAPE;
   CUtensorMap ma, mb, mc;
   int r = make_map(&ma, x, M, K, K, BK, BM);
   if (r) return r;
@@ -651,8 +673,8 @@ RWKV_EXPORT int rwkv_ag_gemm_bf16_tcgen05(const void* x, const unsigned long lon
   AgParams ag = {};
   for (int i = 0; i < world; ++i) ag.shard[i] = reinterpret_cast<const bf16*>(shard_ptrs[i]);
   ag.staged = (bf16*)staged;
-  ag.panel_flag = (int*)panel_flag;
-  ag.panel_count = (int*)panel_count;
-  ag.rank = rank; ag.world = world; ag.epoch = epoch; ag.n_copy = n_copy; ag.Kp = K / world;
-  return launch_ag(ma, mb, mc, M, N, K, (int*)status, sms, ag, (cudaStream_t)stream);
+  ag.blk_count = (int*)blk_count;
+  ag.rank = rank; ag.world = world; ag.Kp = K / world; ag.n_rb = (N + BN - 1) / BN;
+  ag.group = ag.n_rb >= 16 ? 8 : 4;
+  return launch_ag(ma, mb, mc, M, N, K, (int*)status, sms, ag, arrivals_io, (cudaStream_t)stream);
 }

@@ -91,41 +91,56 @@ __global__ void p2p_wait_kernel(PeerPtrs ctrl, int rank, int world, int word, in
 // Phase A.  out[i] (+)= scale * sum_p grad_p[lo + i]  (fp32, fixed rank order); partial[b] = sum of out^2.
 // With `accumulate` the reduced micro-batch gradient is added to what `out` holds (fp32 accumulation of
 // micro-batches on the owner) and the norm partial is taken of the accumulated value.
+// WMAX: compile-time bound on the rank count (2, 4, 8, 16).  A peer load takes microseconds, so throughput is bytes
+// in flight over latency: every thread issues the loads of all ranks for ITER consecutive vectors before it adds.
+template <int WMAX>
 __global__ void __launch_bounds__(256)
 zero2_reduce_kernel(PeerPtrs grads, int world, size_t lo, size_t n, float scale, float* __restrict__ out,
                     float* __restrict__ partial, int accumulate, const int* __restrict__ status) {
+  constexpr int ITER = WMAX >= 8 ? 1 : (WMAX == 4 ? 2 : 4);
   __shared__ float red[8];
   if (status && *reinterpret_cast<const volatile int*>(status)) return;   // poisoned step: touch nothing
   float acc = 0.f;
   const size_t n8 = n / 8;
-  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
-    float s[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    uint4 raw[MAX_RANKS];
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i0 = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i0 < n8; i0 += stride * ITER) {
+    uint4 raw[ITER][WMAX];
 #pragma unroll
-    for (int p = 0; p < MAX_RANKS; ++p)    // all peers' loads in flight before the first add
-      if (p < world) raw[p] = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(grads.p[p]) + lo) + i);
+    for (int u = 0; u < ITER; ++u) {
+      const size_t i = i0 + u * stride;
 #pragma unroll
-    for (int p = 0; p < MAX_RANKS; ++p) {
-      if (p < world) {
-        float f[8];
-        unpack8(raw[p], f);
+      for (int p = 0; p < WMAX; ++p)
+        if (p < world && i < n8)
+          raw[u][p] = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(grads.p[p]) + lo) + i);
+    }
 #pragma unroll
-        for (int e = 0; e < 8; ++e) s[e] += f[e];
+    for (int u = 0; u < ITER; ++u) {
+      const size_t i = i0 + u * stride;
+      if (i >= n8) break;
+      float s[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+      for (int p = 0; p < WMAX; ++p) {
+        if (p < world) {
+          float f[8];
+          unpack8(raw[u][p], f);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) s[e] += f[e];
+        }
       }
-    }
-    float4* o4 = reinterpret_cast<float4*>(out + i * 8);
-    if (accumulate) {
-      const float4 a0 = o4[0], a1 = o4[1];
-      s[0] = s[0] * scale + a0.x; s[1] = s[1] * scale + a0.y; s[2] = s[2] * scale + a0.z; s[3] = s[3] * scale + a0.w;
-      s[4] = s[4] * scale + a1.x; s[5] = s[5] * scale + a1.y; s[6] = s[6] * scale + a1.z; s[7] = s[7] * scale + a1.w;
-    } else {
+      float4* o4 = reinterpret_cast<float4*>(out + i * 8);
+      if (accumulate) {
+        const float4 a0 = o4[0], a1 = o4[1];
+        s[0] = s[0] * scale + a0.x; s[1] = s[1] * scale + a0.y; s[2] = s[2] * scale + a0.z; s[3] = s[3] * scale + a0.w;
+        s[4] = s[4] * scale + a1.x; s[5] = s[5] * scale + a1.y; s[6] = s[6] * scale + a1.z; s[7] = s[7] * scale + a1.w;
+      } else {
 #pragma unroll
-      for (int e = 0; e < 8; ++e) s[e] *= scale;
-    }
+        for (int e = 0; e < 8; ++e) s[e] *= scale;
+      }
 #pragma unroll
-    for (int e = 0; e < 8; ++e) acc += s[e] * s[e];
-    o4[0] = make_float4(s[0], s[1], s[2], s[3]);
-    o4[1] = make_float4(s[4], s[5], s[6], s[7]);
+      for (int e = 0; e < 8; ++e) acc += s[e] * s[e];
+      o4[0] = make_float4(s[0], s[1], s[2], s[3]);
+      o4[1] = make_float4(s[4], s[5], s[6], s[7]);
+    }
   }
   acc = warp_sum(acc);
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
@@ -261,8 +276,15 @@ RWKV_EXPORT int rwkv_zero2_reduce_bucket(const unsigned long long* grad_ptrs, in
   if (r) return r;
   if (n <= 0 || (n & 7) || (lo & 7)) return RWKV_ERR_BAD_ALIGNMENT;
   if (blocks <= 0 || blocks > 1024) return RWKV_ERR_BAD_SHAPE;
-  zero2_reduce_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(g, world, (size_t)lo, (size_t)n, scale, (float*)out,
-                                                                (float*)partial, accumulate, (const int*)status);
+  cudaStream_t st = (cudaStream_t)stream;
+#define RWKV_REDUCE(WM)                                                                                              \
+  zero2_reduce_kernel<WM><<<blocks, 256, 0, st>>>(g, world, (size_t)lo, (size_t)n, scale, (float*)out, (float*)partial, \
+                                                  accumulate, (const int*)status)
+  if (world <= 2) RWKV_REDUCE(2);
+  else if (world <= 4) RWKV_REDUCE(4);
+  else if (world <= 8) RWKV_REDUCE(8);
+  else RWKV_REDUCE(16);
+#undef RWKV_REDUCE
   return rwkv_launch_status();
 }
 

@@ -159,20 +159,23 @@ class GatheredWeight:
         self.rank, self.world, self.N, self.K = rank, world, N, K
         self.ptrs = (ctypes.c_ulonglong * world)(*[int(p) for p in shard_ptrs])
         self.staged = torch.empty(N, K, dtype=torch.bfloat16, device=device)
-        self.flags = torch.zeros(world, dtype=torch.int32, device=device)
-        self.counts = torch.zeros(world, dtype=torch.int32, device=device)
-        self.epoch = 0
-        self.n_copy = n_copy
+        self.counts = torch.zeros(world * (-(-N // 256)), dtype=torch.int32, device=device)   # per (panel, 256-row block)
+        self.arrivals = ctypes.c_int(0)      # running arrival total per counter, advanced by every call
 
 
 def ag_mm_nt(x: torch.Tensor, gw: GatheredWeight) -> torch.Tensor:
     """``x [M,K] @ W^T`` with the all-gather of ``W`` fused into the GEMM; afterwards ``gw.staged`` holds ``W``."""
+    import ctypes
+
     M = x.shape[0]
     y = torch.empty(M, gw.N, dtype=torch.bfloat16, device=x.device)
-    gw.epoch += 1
+    if gw.arrivals.value > 0x60000000:       # counters are 32-bit: start over long before they wrap
+        torch.cuda.current_stream().synchronize()
+        gw.counts.zero_()
+        gw.arrivals.value = 0
     _ext.call("rwkv_ag_gemm_bf16_tcgen05", _ext.ptr(x), gw.ptrs, _ext.ptr(gw.staged), _ext.ptr(y), _ext.i32(M),
-              _ext.i32(gw.N), _ext.i32(gw.K), _ext.i32(gw.rank), _ext.i32(gw.world), _ext.ptr(gw.flags),
-              _ext.ptr(gw.counts), _ext.i32(gw.epoch), _ext.i32(gw.n_copy), _ext.ptr(_status(x.device)), _ext.stream())
+              _ext.i32(gw.N), _ext.i32(gw.K), _ext.i32(gw.rank), _ext.i32(gw.world), _ext.ptr(gw.counts),
+              ctypes.byref(gw.arrivals), _ext.ptr(_status(x.device)), _ext.stream())
     return y
 
 

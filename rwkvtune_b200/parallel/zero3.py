@@ -8,8 +8,9 @@ matrix: ``att.receptance/key/value/output`` and ``ffn.key/value`` (99 % of a blo
 ``world`` column panels, rank ``p`` keeping ``W[:, p*K/W:(p+1)*K/W]``.  All panels of a rank live in one
 symmetric-memory buffer, so every rank holds device pointers to every peer's panels.
 
-* **Forward**: :func:`gemm_native.ag_mm_nt` - copy CTAs of the GEMM's own grid pull the panels over NVLink into a
-  local staging matrix while its MMA CTAs already multiply the panels that have landed.
+* **Forward**: :func:`gemm_native.ag_mm_nt` - four copy warps in every CTA of the GEMM pull the panels over NVLink
+  into a local staging matrix, 256 weight rows at a time, while the tensor-core warps already multiply the column
+  tiles whose weight rows have landed.
 * **Backward, data gradient**: ``dy @ W`` needs the full matrix again.  With activation checkpointing the recompute
   forward has just staged it.  Otherwise the staging slot of that role holds the next layer's matrix, and this
   layer's is brought in by :func:`prefetch`: a gather kernel of this repository on a side stream, issued as soon as

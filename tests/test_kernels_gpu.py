@@ -458,7 +458,7 @@ def test_tcgen05_gemm_relu_sq_epilogue():
 @pytest.mark.parametrize("M,N,K,W,rank", [(512, 512, 512, 4, 1), (1024, 2560, 2560, 8, 5), (384, 320, 256, 2, 0)])
 def test_ag_fused_gemm_emulated_panels(M, N, K, W, rank):
     """K-panels of the weight held in separate buffers (as if on W ranks); the fused kernel must gather them into
-    the staging matrix and produce x @ W^T.  Called twice to check the epoch-based panel flags."""
+    the staging matrix and produce x @ W^T.  Called repeatedly to check the running arrival counters."""
     from rwkvtune_b200.ops import gemm_native
     torch.manual_seed(K)
     x = torch.randn(M, K, device="cuda").to(BF)
@@ -474,6 +474,12 @@ def test_ag_fused_gemm_emulated_panels(M, N, K, W, rank):
         assert gemm_native.check_status() == 0
         assert torch.equal(gw.staged, w)
         assert (y.float() - ref_out).abs().max().item() <= 2e-2 * ref_out.abs().max().item() + 1e-2
+    # a different row count on the same buffers: another grid size, so another number of arrivals per counter
+    gw.staged.zero_()
+    y = gemm_native.ag_mm_nt(x[:256].contiguous(), gw)
+    torch.cuda.synchronize()
+    assert gemm_native.check_status() == 0 and torch.equal(gw.staged, w)
+    assert (y.float() - ref_out[:256]).abs().max().item() <= 2e-2 * ref_out.abs().max().item() + 1e-2
 
 
 @pytest.mark.parametrize("B,T,H,with_state", [(2, 64, 2, False), (1, 37, 3, True), (2, 256, 1, True)])
