@@ -130,6 +130,12 @@ def bench_gemm(B, T, C, out, tf):
             out[f"gemm_nt_{name}_{tag}_ms"] = ms
             out[f"gemm_nt_{name}_{tag}_tflops"] = 2 * M * K * N / ms / 1e9
             out[f"gemm_nt_{name}_{tag}_frac_peak"] = 2 * M * K * N / ms / 1e9 / tf
+        from rwkvtune_b200.ops import gemm_native
+        if hasattr(gemm_native, "mm_nt_2cta"):
+            ms = timeit(lambda: gemm_native.mm_nt_2cta(x, w))
+            out[f"gemm_nt_{name}_native_2cta_ms"] = ms
+            out[f"gemm_nt_{name}_native_2cta_tflops"] = 2 * M * K * N / ms / 1e9
+            out[f"gemm_nt_{name}_native_2cta_over_cublas"] = out[f"gemm_nt_{name}_cublas_ms"] / ms
     # weight gradients of the low-rank maps: few output tiles, contraction over every token (split-K)
     for D in (64, 96, 256):
         x = torch.randn(M, C, device="cuda").to(BF)

@@ -24,6 +24,7 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "tensormap_cache.cuh"
 
 namespace {
 
@@ -453,38 +454,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 }
 
 // ------------------------------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn get_encode() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-  }
-  return fn;
-}
-
-// 2-D bf16 tensor map over a row-major [rows, cols] matrix with leading dimension `ld` (elements),
-// box = {box_cols, box_rows}, 128-byte swizzle.
-int make_map(CUtensorMap* map, const void* ptr, long long rows, long long cols, long long ld, int box_cols,
-             int box_rows) {
-  EncodeTiledFn enc = get_encode();
-  if (!enc) return RWKV_ERR_NOT_INITIALISED;
-  if (((uintptr_t)ptr & 15) || (ld * 2) % 16) return RWKV_ERR_BAD_ALIGNMENT;
-  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? RWKV_OK : RWKV_ERR_CUDA_BASE + 900 + (int)r;
-}
+using rwkv_tmap::make_map;   // encoded maps are cached per (address, shape, stride, box)
 
 template <bool A_MN, bool B_MN, int EPI>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, int M, int N, int K, int* status,

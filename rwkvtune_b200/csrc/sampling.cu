@@ -1,4 +1,6 @@
-// Temperature + top-p sampling over a full vocabulary row without sorting it.
+// Token sampling over a full vocabulary row without sorting it: repetition penalty (from a bitmap of tokens already
+// seen), banned ids, temperature, additive logit bias, top-k, top-p, the draw (or the arg-max when greedy), the
+// token's log-probability and the update of the seen-bitmap, in one kernel.
 //
 // One 1024-thread CTA per row; each thread keeps up to 64 probabilities in registers
 // (V <= 65536).  The nucleus is "the sorted prefix whose cumulative mass is <= top_p, plus
@@ -8,7 +10,10 @@
 // scatter is needed.  The draw is an inverse-CDF walk over the kept tokens in index order with a
 // Philox4x32-10 uniform keyed by (seed, row).  Replaces the full 65536-way sort + cumsum +
 // unsort + softmax + multinomial sequence of the reference
-// (rwkvtune/inference/core.py:165-238).
+// (rwkvtune/inference/core.py:165-238) and its per-sequence Python repetition penalty
+// (rwkvtune/inference/grpo_batch_generator.py:25-42).  Top-k keeps every value >= the k-th largest (ties kept, as
+// `logits < kth` masking does); the k-th largest is found exactly by a 32-step radix descent over the
+// order-preserving integer image of the floats (one count reduction per bit).
 #include "common.cuh"
 
 namespace {
@@ -59,16 +64,37 @@ __device__ __forceinline__ float block_reduce_max(float v, float* red) {
   return red[32];
 }
 
+struct SampleArgs {
+  const float* bias;            // [V] additive bias applied after temperature scaling, or null
+  unsigned char* seen;          // [*, V] bitmap of tokens already in each sequence's history, or null
+  const long long* seen_rows;   // [n] row of `seen` that belongs to batch row i (null: row i)
+  float penalty;                // repetition penalty (> 0, != 1 to have an effect)
+  int top_k;                    // 0 = off
+  int greedy;                   // 1: arg-max of the penalised, biased logits (no temperature)
+  int update_seen;              // 1: mark the sampled token in `seen`
+};
+
+__device__ __forceinline__ uint32_t order_key(float v) {
+  const uint32_t u = __float_as_uint(v);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(ST)
 sample_top_p_kernel(const T* __restrict__ logits, int V, int n_valid, float inv_temp, float top_p,
-                    unsigned long long seed, long long* __restrict__ tokens, float* __restrict__ logps) {
+                    unsigned long long seed, long long* __restrict__ tokens, float* __restrict__ logps,
+                    const SampleArgs sa) {
   __shared__ float red[33];
   __shared__ float scan[ST / 32];
   __shared__ int winner;
   __shared__ int amax;
   const int row = blockIdx.x, tid = threadIdx.x;
   const T* x = logits + (size_t)row * V;
+  unsigned char* seen_row = nullptr;
+  if (sa.seen) seen_row = sa.seen + (size_t)(sa.seen_rows ? sa.seen_rows[row] : row) * V;
+  const bool penalise = seen_row && sa.penalty > 0.f && sa.penalty != 1.f;
+  const float inv_pen = penalise ? 1.f / sa.penalty : 1.f;
+  const float scale = sa.greedy ? 1.f : inv_temp;
 
   float p[SPT];
   float mx = -INFINITY;
@@ -77,14 +103,48 @@ sample_top_p_kernel(const T* __restrict__ logits, int V, int n_valid, float inv_
     const int i = tid + j * ST;
     float v = -INFINITY;
     if (i < n_valid) {
-      if constexpr (sizeof(T) == 2) v = __bfloat162float(x[i]) * inv_temp;
-      else v = x[i] * inv_temp;
+      if constexpr (sizeof(T) == 2) v = __bfloat162float(x[i]);
+      else v = x[i];
+      if (penalise && seen_row[i]) v = v > 0.f ? v * inv_pen : v * sa.penalty;
+      v *= scale;
+      if (sa.bias) v += sa.bias[i];
       if (!(v == v)) v = -INFINITY;   // NaN logits are never sampled
     }
     p[j] = v;
     mx = fmaxf(mx, v);
   }
   mx = block_reduce_max(mx, red);
+  if (sa.greedy) {   // first index of the maximum; log-probability under the plain softmax of the same logits
+    if (tid == 0) amax = 0x7fffffff;
+    __syncthreads();
+    float zg = 0.f;
+#pragma unroll
+    for (int j = 0; j < SPT; ++j) {
+      if (p[j] == mx) atomicMin(&amax, tid + j * ST);
+      zg += (p[j] == -INFINITY) ? 0.f : __expf(p[j] - mx);
+    }
+    zg = block_reduce_sum(zg, red);
+    if (tid == 0) {
+      tokens[row] = amax;
+      logps[row] = -__logf(zg);
+      if (sa.update_seen && seen_row) seen_row[amax] = 1;
+    }
+    return;
+  }
+  if (sa.top_k > 0 && sa.top_k < n_valid) {   // radix descent for the key of the k-th largest value
+    uint32_t prefix = 0u;
+    for (int bit = 31; bit >= 0; --bit) {
+      const uint32_t cand = prefix | (1u << bit);
+      float cnt = 0.f;
+#pragma unroll
+      for (int j = 0; j < SPT; ++j) cnt += (order_key(p[j]) >= cand) ? 1.f : 0.f;
+      cnt = block_reduce_sum(cnt, red);
+      if (cnt >= (float)sa.top_k) prefix = cand;
+    }
+#pragma unroll
+    for (int j = 0; j < SPT; ++j)
+      if (order_key(p[j]) < prefix) p[j] = -INFINITY;
+  }
   float z = 0.f;
 #pragma unroll
   for (int j = 0; j < SPT; ++j) {
@@ -180,21 +240,42 @@ sample_top_p_kernel(const T* __restrict__ logits, int V, int n_valid, float inv_
       logps[row] = __logf(pmax / total);
     }
     tokens[row] = winner;
+    if (sa.update_seen && seen_row) seen_row[winner] = 1;
   }
 }
 
 }  // namespace
 
-// logits: [n, V] fp32 (is_bf16 = 0) or bf16 (1); ids >= n_valid are banned; tokens int64 [n], logps fp32 [n]
-RWKV_EXPORT int rwkv_sample_top_p(const void* logits, int is_bf16, int n, int V, int n_valid, float inv_temp,
-                                  float top_p, long long seed, void* tokens, void* logps, void* stream) {
-  if (n <= 0 || V <= 0 || V > ST * SPT || n_valid <= 0 || n_valid > V) return RWKV_ERR_BAD_SHAPE;
+// logits: [n, V] fp32 (is_bf16 = 0) or bf16 (1); ids >= n_valid are banned; tokens int64 [n], logps fp32 [n].
+// bias: fp32 [V] or null.  seen: uint8 [rows, V] or null, seen_rows: int64 [n] or null (row i of the batch uses
+// seen[seen_rows[i]]); penalty <= 0 or == 1 disables the repetition penalty; top_k = 0 disables top-k; greedy = 1
+// takes the arg-max (temperature ignored); update_seen = 1 marks the sampled token in the bitmap.
+RWKV_EXPORT int rwkv_sample_tokens(const void* logits, int is_bf16, int n, int V, int n_valid, float inv_temp,
+                                   float top_p, int top_k, int greedy, const void* bias, void* seen,
+                                   const void* seen_rows, float penalty, int update_seen, long long seed,
+                                   void* tokens, void* logps, void* stream) {
+  if (n <= 0 || V <= 0 || V > ST * SPT || n_valid <= 0 || n_valid > V || top_k < 0) return RWKV_ERR_BAD_SHAPE;
+  SampleArgs sa;
+  sa.bias = (const float*)bias;
+  sa.seen = (unsigned char*)seen;
+  sa.seen_rows = (const long long*)seen_rows;
+  sa.penalty = penalty;
+  sa.top_k = top_k;
+  sa.greedy = greedy;
+  sa.update_seen = update_seen;
   cudaStream_t st = (cudaStream_t)stream;
   if (is_bf16)
     sample_top_p_kernel<bf16><<<n, ST, 0, st>>>((const bf16*)logits, V, n_valid, inv_temp, top_p,
-                                                (unsigned long long)seed, (long long*)tokens, (float*)logps);
+                                                (unsigned long long)seed, (long long*)tokens, (float*)logps, sa);
   else
     sample_top_p_kernel<float><<<n, ST, 0, st>>>((const float*)logits, V, n_valid, inv_temp, top_p,
-                                                 (unsigned long long)seed, (long long*)tokens, (float*)logps);
+                                                 (unsigned long long)seed, (long long*)tokens, (float*)logps, sa);
   return rwkv_launch_status();
+}
+
+// Temperature + top-p only (the call above with every other feature off).
+RWKV_EXPORT int rwkv_sample_top_p(const void* logits, int is_bf16, int n, int V, int n_valid, float inv_temp,
+                                  float top_p, long long seed, void* tokens, void* logps, void* stream) {
+  return rwkv_sample_tokens(logits, is_bf16, n, V, n_valid, inv_temp, top_p, 0, 0, nullptr, nullptr, nullptr, 1.f, 0,
+                            seed, tokens, logps, stream);
 }

@@ -7,9 +7,10 @@ the tokenizer's largest id are banned; ``temperature < 1e-6`` is greedy; then te
 sorted prefix with ``cumsum <= top_p`` plus always the most likely token.  Returns the sampled ids
 and their log-probabilities under the filtered distribution.
 
-On CUDA the filter-and-draw step runs in the ``rwkv_sample_top_p`` kernel (threshold search over the
-row instead of a full 65536-way sort) when no ``logits_processor`` is given; everything stays on the
-device.  A ``torch.Generator`` or an explicit ``seed`` makes draws reproducible.
+On CUDA the whole rule - repetition penalty from a seen-token bitmap, ban, temperature or greedy, bias, top-k,
+top-p, draw, log-probability - runs in one launch of the ``rwkv_sample_tokens`` kernel (threshold searches over the
+row instead of a full 65536-way sort) unless a ``logits_processor`` is given; everything stays on the device.  A
+``torch.Generator`` or an explicit ``seed`` makes draws reproducible.
 """
 from __future__ import annotations
 
@@ -79,13 +80,12 @@ class TokenSampler:
                      ) -> Tuple[torch.Tensor, torch.Tensor]:
         if logits_batch.dim() != 2:
             raise ValueError(f"batch sampling needs 2-D logits, got shape {tuple(logits_batch.shape)}")
-        if (logits_batch.is_cuda and TokenSampler.use_native_kernel and logits_processor is None and not logit_bias
-                and temperature >= 1e-6 and not top_k):
+        if logits_batch.is_cuda and TokenSampler.use_native_kernel and logits_processor is None:
             from . import sampling_native
 
-            if sampling_native.available():
-                return sampling_native.sample_top_p(logits_batch, temperature, top_p,
-                                                    TokenSampler._max_valid_token_id, seed, generator)
+            if sampling_native.full_available() and logits_batch.shape[1] <= 65536:
+                return sampling_native.sample_tokens(logits_batch, temperature, top_p, top_k, logit_bias,
+                                                     TokenSampler._max_valid_token_id, seed=seed, generator=generator)
         filtered = TokenSampler.filter_logits(logits_batch, temperature, top_p, top_k, logit_bias, logits_processor)
         logp = F.log_softmax(filtered, dim=-1)
         if temperature < 1e-6:

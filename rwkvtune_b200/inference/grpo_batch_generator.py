@@ -20,6 +20,7 @@ from typing import Any, Dict, List, Optional, Sequence
 import torch
 
 from .. import ops
+from . import sampling_native
 from .core import TokenSampler, apply_repetition_penalty
 
 
@@ -205,16 +206,24 @@ class GRPOBatchGenerator:
             graph = self._graph_for(n)
             graph.load_state(state)
         try:
+            fused_sampler = (dev.type == "cuda" and TokenSampler.use_native_kernel and sampling_native.full_available()
+                             and V <= 65536)
             for step in range(max_new_tokens):
-                lg = logits.float()
-                if use_pen:
-                    lg = apply_repetition_penalty(lg, seen.index_select(0, rows), repetition_penalty)
                 step_seed = None if seed is None else int(seed) * 1000003 + step
-                tok, _ = TokenSampler.sample_batch(lg, temperature, top_p, top_k, logit_bias, seed=step_seed)
+                if fused_sampler:   # penalty, ban, temperature, bias, top-k, top-p, draw and bitmap update: one launch
+                    tok, _ = sampling_native.sample_tokens(
+                        logits, temperature, top_p, top_k, logit_bias, self.max_valid_token_id,
+                        seen=seen if use_pen else None, seen_rows=rows if use_pen else None,
+                        repetition_penalty=repetition_penalty if use_pen else 1.0, update_seen=use_pen, seed=step_seed)
+                else:
+                    lg = logits.float()
+                    if use_pen:
+                        lg = apply_repetition_penalty(lg, seen.index_select(0, rows), repetition_penalty)
+                    tok, _ = TokenSampler.sample_batch(lg, temperature, top_p, top_k, logit_bias, seed=step_seed)
                 live = ~finished.index_select(0, rows)
                 out_ids[rows, step] = torch.where(live, tok, torch.zeros_like(tok))
                 lengths[rows] += live.long()
-                if use_pen:
+                if use_pen and not fused_sampler:
                     seen[rows, tok] = True
                 done_now = torch.zeros_like(live)
                 if eos is not None:

@@ -100,7 +100,37 @@ def _run(a, b, M, N, K, a_mn: int, b_mn: int, epilogue: int = 0, out: torch.Tens
 def mm_nt(x: torch.Tensor, w: torch.Tensor, epilogue: int = 0, out: torch.Tensor = None,
           residual: torch.Tensor = None) -> torch.Tensor:
     """``x [M,K] @ w[N,K]^T``"""
+    if two_cta_ok(x.shape[0], w.shape[0], x.shape[1], 2 if (out is not None or residual is not None) else epilogue):
+        return mm_nt_2cta(x, w, epilogue, out, residual)
     return _run(x, w, x.shape[0], w.shape[0], x.shape[1], 0, 0, epilogue, out, residual)
+
+
+# The pair-of-SMs kernel (``gemm_tcgen05_2cta.cu``: 256x256 tiles, tcgen05.mma.cta_group::2) serves K-major x K-major
+# products (nn.Linear forward) with epilogues 0, 1, 2 when the output has at least one 256x256 tile per SM pair.
+TWO_CTA = __import__("os").environ.get("RWKVTUNE_GEMM_2CTA", "0") == "1"
+
+
+def two_cta_ok(M: int, N: int, K: int, epilogue: int) -> bool:
+    return (TWO_CTA and epilogue in (0, 1, 2) and M >= 256 and N >= 256 and -(-M // 256) * -(-N // 256) >= 74
+            and hasattr(_ext.lib(), "rwkv_gemm_bf16_tcgen05_2cta"))
+
+
+def mm_nt_2cta(x: torch.Tensor, w: torch.Tensor, epilogue: int = 0, out: torch.Tensor = None,
+               residual: torch.Tensor = None) -> torch.Tensor:
+    """``x [M,K] @ w[N,K]^T`` on pairs of SMs.  ``out`` given: ``out += x w^T``; ``residual`` given: returns
+    ``residual + x w^T``."""
+    M, K, N = x.shape[0], x.shape[1], w.shape[0]
+    if out is not None:
+        c, epilogue = out, 2
+    else:
+        c = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+        if residual is not None:
+            epilogue = 2
+    _ext.call("rwkv_gemm_bf16_tcgen05_2cta", _ext.ptr(x), _ext.ptr(w), _ext.ptr(c), _ext.i32(M), _ext.i32(N), _ext.i32(K),
+              _ext.i64(x.stride(0)), _ext.i64(w.stride(0)), _ext.i64(c.stride(0)), _ext.i32(epilogue),
+              _ext.ptr(_status(x.device)), _ext.ptr(residual), _ext.i64(0 if residual is None else residual.stride(0)),
+              _ext.stream())
+    return c
 
 
 def mm_nn(x: torch.Tensor, w: torch.Tensor, epilogue: int = 0, out: torch.Tensor = None,

@@ -419,6 +419,107 @@ def test_sampler_kernel_matches_filtered_distribution():
     assert bf.min() >= 0 and bf.max() < V
 
 
+@pytest.mark.parametrize("M,N,K", [(512, 512, 128), (2048, 1024, 512), (1000, 776, 200), (256, 256, 64), (4096, 2048, 2048)])
+@pytest.mark.parametrize("epilogue", [0, 1, 2])
+def test_gemm_on_sm_pairs_matches_reference(M, N, K, epilogue):
+    """The cta_group::2 kernel (256x256 tiles over two SMs) against fp32 matmul, with ragged edges and every epilogue."""
+    from rwkvtune_b200.ops import gemm_native
+    torch.manual_seed(M + N + K)
+    x = torch.randn(M, K, device="cuda").to(BF)
+    w = (torch.randn(N, K, device="cuda") * 0.2).to(BF)
+    ref_out = x.float() @ w.float().t()
+    if epilogue == 1:
+        ref_out = torch.relu(ref_out) ** 2
+        y = gemm_native.mm_nt_2cta(x, w, epilogue=1)
+    elif epilogue == 2:
+        res = torch.randn(M, N, device="cuda").to(BF)
+        ref_out = ref_out + res.float()
+        y = gemm_native.mm_nt_2cta(x, w, residual=res)
+        acc = res.clone()
+        y2 = gemm_native.mm_nt_2cta(x, w, out=acc)
+        assert y2.data_ptr() == acc.data_ptr()
+        assert (acc.float() - ref_out).abs().max().item() <= 2e-2 * ref_out.abs().max().item() + 1e-2
+    else:
+        y = gemm_native.mm_nt_2cta(x, w)
+    torch.cuda.synchronize()
+    assert gemm_native.check_status() == 0
+    assert (y.float() - ref_out).abs().max().item() <= 2e-2 * ref_out.abs().max().item() + 1e-2
+
+
+def _chi_square_ok(toks, probs, n):
+    V = probs.numel()
+    counts = torch.bincount(toks, minlength=V).float()
+    kept = probs > 0
+    assert (probs[toks] > 0).all(), "sampled a token outside the allowed set"
+    expected = probs[kept] * n
+    chi2 = ((counts[kept] - expected) ** 2 / expected.clamp(min=1e-9)).sum().item()
+    dof = max(int(kept.sum()) - 1, 1)
+    assert chi2 < dof + 6 * (2 * dof) ** 0.5 + 10, (chi2, dof)
+
+
+@pytest.mark.parametrize("top_k,top_p", [(50, 1.0), (20, 0.8), (0, 0.6)])
+def test_sampler_kernel_topk_bias_and_penalty_match_the_filter(top_k, top_p):
+    """The fused sampler against the statement-by-statement rule (penalty from the seen bitmap, ban, temperature,
+    bias, top-k, top-p) on the distribution of many draws from one row."""
+    from rwkvtune_b200.inference.core import TokenSampler, apply_repetition_penalty
+    from rwkvtune_b200.inference import sampling_native
+    torch.manual_seed(1)
+    V, n = 1200, 4096
+    base = torch.randn(1, V, device="cuda") * 2.0
+    logits = base.expand(n, V).contiguous()
+    bias = {3: 4.0, 17: -150.0, 900: 2.5, 5000: 1.0}
+    seen1 = torch.zeros(1, V, dtype=torch.bool, device="cuda")
+    seen1[0, torch.randperm(V, device="cuda")[:200]] = True
+    seen = seen1.expand(n, V).contiguous()
+    temp, pen = 0.9, 1.3
+    ref_logits = apply_repetition_penalty(base.clone(), seen1, pen)
+    filt = TokenSampler.filter_logits(ref_logits, temp, top_p, top_k, bias, max_valid_token_id=1100)
+    probs = torch.softmax(filt, -1)[0]
+    toks, lps = sampling_native.sample_tokens(logits, temp, top_p, top_k, bias, 1100, seen=seen,
+                                              repetition_penalty=pen, update_seen=True, seed=11)
+    _chi_square_ok(toks, probs, n)
+    assert torch.allclose(lps, torch.log(probs[toks]), atol=3e-3)
+    if top_k:
+        assert int((probs > 0).sum()) <= top_k
+    # the drawn token was marked in each row's bitmap, nothing else changed
+    after = seen.clone()
+    expect = seen1.expand(n, V).clone()
+    expect[torch.arange(n, device="cuda"), toks] = True
+    assert torch.equal(after, expect)
+    # rows indexed through seen_rows: batch row i uses bitmap row perm[i]
+    perm = torch.randperm(n, device="cuda")
+    seen2 = torch.zeros(n, V, dtype=torch.bool, device="cuda")
+    t2, _ = sampling_native.sample_tokens(logits, temp, top_p, top_k, None, None, seen=seen2, seen_rows=perm,
+                                          repetition_penalty=pen, update_seen=True, seed=5)
+    assert torch.equal(seen2[perm, t2], torch.ones(n, dtype=torch.bool, device="cuda")) and int(seen2.sum()) == n
+
+
+def test_sampler_kernel_greedy_and_sample_batch_routing():
+    from rwkvtune_b200.inference.core import TokenSampler
+    from rwkvtune_b200.inference import sampling_native
+    torch.manual_seed(2)
+    n, V = 64, 65536
+    logits = (torch.randn(n, V, device="cuda") * 3).to(BF)
+    bias = {7: 50.0}
+    tok, lp = sampling_native.sample_tokens(logits, 0.0, 0.5, 10, bias, 65529, seed=1)
+    ref = logits.float().clone()
+    ref[:, 65530:] = float("-inf")
+    ref[:, 7] += 50.0
+    assert torch.equal(tok, ref.argmax(-1))
+    assert torch.allclose(lp, torch.log_softmax(ref, -1).gather(1, tok[:, None]).squeeze(1), atol=2e-3)
+    # TokenSampler.sample_batch goes through the kernel for every combination without a logits_processor
+    prev = TokenSampler._max_valid_token_id
+    TokenSampler.set_max_valid_token_id(65529)
+    try:
+        t1, l1 = TokenSampler.sample_batch(logits, 0.8, 0.9, 40, bias, seed=9)
+        t2, l2 = sampling_native.sample_tokens(logits, 0.8, 0.9, 40, bias, 65529, seed=9)
+        assert torch.equal(t1, t2) and torch.equal(l1, l2)
+        filt = TokenSampler.filter_logits(logits, 0.8, 0.9, 40, bias)
+        assert torch.isfinite(filt.gather(1, t1[:, None])).all()
+    finally:
+        TokenSampler.set_max_valid_token_id(prev)
+
+
 @pytest.mark.parametrize("M,N,K", [(256, 512, 128), (200, 320, 96), (1024, 2048, 2048), (384, 64, 32)])
 @pytest.mark.parametrize("layout", ["nt", "nn", "tn"])
 def test_tcgen05_gemm_layouts(M, N, K, layout):
