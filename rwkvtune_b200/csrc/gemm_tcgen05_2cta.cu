@@ -1,8 +1,10 @@
-// bf16 GEMM on pairs of SMs: C[M,N] = A[M,K] * B[N,K]^T (both operands K-major), one 256x256 output tile per
-// cluster of two CTAs, issued as tcgen05.mma.cta_group::2.
+// bf16 GEMM on pairs of SMs: C[M,N] = op(A) * op(B), one 256x256 output tile per cluster of two CTAs, issued as
+// tcgen05.mma.cta_group::2.  Operands may be K-major (contraction index contiguous) or MN-major, as in the
+// single-CTA kernel, so x@W^T (NT), x@W (NN) and dy^T@x (TN) all run here without transposing anything.
 //
 // Each CTA of a pair stages ITS OWN halves of the operands with TMA - 128 rows of A and 128 rows of B per
-// 64-wide K block (no multicast: every load reads this GPU's memory into the issuing CTA's shared memory) - and
+// 64-wide K block (every load reads this GPU's memory into the issuing CTA's own shared memory; nothing is
+// broadcast across the cluster) - and
 // both CTAs' loads complete on the leader CTA's "full" mbarrier (cp.async.bulk.tensor ... .cta_group::2).  One
 // elected thread of the leader issues the MMAs: the tensor cores of both SMs read A from their own shared
 // memory and the two B halves from both, so each SM fills 32 KB of shared memory per 256x256x64 step instead
@@ -125,10 +127,12 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t sr
                : "memory");
 }
 
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr) {   // K-major, 128-byte swizzle, 8-row groups 1024 B apart
+// 128-byte swizzle, 8-row groups 1024 B apart.  lbo_16: leading-dimension byte offset >> 4 (1 for K-major, where it
+// is unused; for MN-major the distance between two 64-element chunks of the M/N dimension).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_16) {
   uint64_t d = 0;
   d |= (uint64_t)((addr >> 4) & 0x3fff);
-  d |= (uint64_t)1 << 16;                  // leading-dimension byte offset (unused for swizzled K-major), encoded >> 4
+  d |= (uint64_t)(lbo_16 & 0x3fff) << 16;
   d |= (uint64_t)(1024 >> 4) << 32;        // stride between 8-row groups
   d |= (uint64_t)1 << 46;                  // descriptor version for sm_100
   d |= (uint64_t)2 << 61;                  // 128-byte swizzle
@@ -166,8 +170,9 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-// EPI: 0 = plain store, 1 = relu(x)^2, 2 = add the bf16 [M,N] matrix c_in (row stride ldc; may be C itself)
-template <int EPI>
+// EPI: 0 = plain store, 1 = relu(x)^2, 2 = add the bf16 [M,N] matrix c_in (row stride ldc; may be C itself),
+//      5 = x * 2 sqrt(c_in): the derivative of relu(p)^2 expressed through its output, applied to a data gradient
+template <bool A_MN, bool B_MN, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                          const __grid_constant__ CUtensorMap map_c, int M, int N, int K, int* status,
@@ -217,8 +222,18 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           if (rank == 0) mbar_expect_tx(&bars->full[stage], 2 * STAGE_BYTES);
           const uint32_t full_leader = map_to_cta(smem_u32(&bars->full[stage]), 0);
           const uint32_t sa = base + stage * STAGE_BYTES, sb = sa + A_BYTES;
-          tma_load_2d_pair(sa, &map_a, full_leader, kb * BK, m0);
-          tma_load_2d_pair(sb, &map_b, full_leader, kb * BK, n0);
+          if (A_MN) {   // A stored [K, M]: two boxes of 64 m-columns x 64 k-rows
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c) tma_load_2d_pair(sa + c * (BK * 128), &map_a, full_leader, m0 + c * 64, kb * BK);
+          } else {
+            tma_load_2d_pair(sa, &map_a, full_leader, kb * BK, m0);
+          }
+          if (B_MN) {   // B stored [K, N]: this CTA's 128 n-columns as two boxes
+#pragma unroll
+            for (int c = 0; c < BNH / 64; ++c) tma_load_2d_pair(sb + c * (BK * 128), &map_b, full_leader, n0 + c * 64, kb * BK);
+          } else {
+            tma_load_2d_pair(sb, &map_b, full_leader, kb * BK, n0);
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -227,8 +242,11 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     // ------------------------------------------------------------------ MMA issuer (leader CTA only)
     if (lane == 0 && rank == 0) {
       // kind::f16: D fp32 (bit 4), A bf16 (bit 7), B bf16 (bit 10), both K-major, N = 256, M = 256 across the pair
-      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
+      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((A_MN ? 1u : 0u) << 15) |
+                                 ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) |
                                  ((uint32_t)((2 * BM) >> 4) << 24);
+      constexpr uint32_t a_lbo = A_MN ? (BK * 128) >> 4 : 1, b_lbo = B_MN ? (BK * 128) >> 4 : 1;
+      constexpr uint32_t a_adv = A_MN ? (2 * 1024) >> 4 : 32 >> 4, b_adv = B_MN ? (2 * 1024) >> 4 : 32 >> 4;
       int stage = 0;
       uint32_t phase = 0;
       int local = 0;
@@ -243,10 +261,10 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           if (!mbar_wait(&bars->full[stage], phase, bars, status, 203)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = base + stage * STAGE_BYTES, sb = sa + A_BYTES;
-          const uint64_t adesc = make_smem_desc(sa), bdesc = make_smem_desc(sb);
+          const uint64_t adesc = make_smem_desc(sa, a_lbo), bdesc = make_smem_desc(sb, b_lbo);
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k)
-            umma_f16_pair(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (kb | k) ? 1u : 0u);
+            umma_f16_pair(d_tmem, adesc + (uint64_t)(k * a_adv), bdesc + (uint64_t)(k * b_adv), idesc, (kb | k) ? 1u : 0u);
           umma_commit_pair(&bars->empty[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -274,8 +292,8 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         uint32_t v0[32], v1[32];
         tmem_ld32(t_row + chunk * 64, v0);
         tmem_ld32(t_row + chunk * 64 + 32, v1);
-        uint4 cin[EPI == 2 ? 8 : 1];
-        if (EPI == 2) {
+        uint4 cin[(EPI == 2 || EPI == 5) ? 8 : 1];
+        if (EPI == 2 || EPI == 5) {
           const long long gm = m0 + row;
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
@@ -291,13 +309,14 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           float f[8], prev[8];
-          if (EPI == 2) unpack8(cin[j], prev);
+          if (EPI == 2 || EPI == 5) unpack8(cin[j], prev);
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
             const int col = j * 8 + e;
             float x = __uint_as_float(col < 32 ? v0[col] : v1[col - 32]);
             if (EPI == 1) { x = fmaxf(x, 0.f); x = x * x; }
             if (EPI == 2) x += prev[e];
+            if (EPI == 5) x *= 2.f * sqrtf(prev[e]);
             f[e] = x;
           }
           const uint4 packed = pack8(f);
@@ -332,10 +351,10 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 
 using rwkv_tmap::make_map;   // encoded maps are cached per (address, shape, stride, box)
 
-template <int EPI>
+template <bool A_MN, bool B_MN, int EPI>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, int M, int N, int K, int* status,
            int sms, const bf16* c_in, long long ldc, cudaStream_t st) {
-  auto kern = gemm_tcgen05_2cta_kernel<EPI>;
+  auto kern = gemm_tcgen05_2cta_kernel<A_MN, B_MN, EPI>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
@@ -351,14 +370,20 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, 
 
 }  // namespace
 
-// C[M,N] (row-major, ldc) = A[M,K] (row-major, lda) * B[N,K]^T (row-major, ldb), bf16 in/out, fp32 accumulation,
-// on pairs of SMs.  epilogue: 0 none, 1 relu(x)^2, 2 add a bf16 [M,N] matrix: `residual` (row stride ldr) or, when
-// that is null, the values already in C (in place).  status: device int, set non-zero if a device-side wait expired.
+// C[M,N] (row-major, ldc) = op(A) op(B), bf16 in/out, fp32 accumulation, on pairs of SMs.
+//   a_mn = 0: A is [M,K] row-major (lda);  a_mn = 1: A is stored [K,M] row-major (lda)
+//   b_mn = 0: B is [N,K] row-major (ldb);  b_mn = 1: B is stored [K,N] row-major (ldb)
+//   epilogue: 0 none, 1 relu(x)^2, 5 multiply by 2 sqrt(residual), 2 add a bf16 [M,N] matrix: `residual` (row stride
+//   ldr) or, when that is null, the values already in C (in place).
+//   status: device int, set non-zero if a device-side wait expired.
 RWKV_EXPORT int rwkv_gemm_bf16_tcgen05_2cta(const void* a, const void* b, void* c, int M, int N, int K, long long lda,
-                                            long long ldb, long long ldc, int epilogue, void* status,
-                                            const void* residual, long long ldr, void* stream) {
-  if (M <= 0 || N <= 0 || K <= 0 || epilogue < 0 || epilogue > 2) return RWKV_ERR_BAD_SHAPE;
-  if (epilogue == 2 && residual && (((uintptr_t)residual & 15) || (ldr * 2) % 16)) return RWKV_ERR_BAD_ALIGNMENT;
+                                            long long ldb, long long ldc, int a_mn, int b_mn, int epilogue,
+                                            void* status, const void* residual, long long ldr, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || !(epilogue == 0 || epilogue == 1 || epilogue == 2 || epilogue == 5))
+    return RWKV_ERR_BAD_SHAPE;
+  if ((epilogue == 2 || epilogue == 5) && residual && (((uintptr_t)residual & 15) || (ldr * 2) % 16))
+    return RWKV_ERR_BAD_ALIGNMENT;
+  if (epilogue == 5 && !residual) return RWKV_ERR_BAD_SHAPE;
   static int sms = 0;
   if (!sms) {
     int dev = 0;
@@ -366,16 +391,24 @@ RWKV_EXPORT int rwkv_gemm_bf16_tcgen05_2cta(const void* a, const void* b, void* 
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   }
   CUtensorMap ma, mb, mc;
-  int r = make_map(&ma, a, M, K, lda, BK, BM);
+  int r = a_mn ? make_map(&ma, a, K, M, lda, 64, BK) : make_map(&ma, a, M, K, lda, BK, BM);
   if (r) return r;
-  r = make_map(&mb, b, N, K, ldb, BK, BNH);
+  r = b_mn ? make_map(&mb, b, K, N, ldb, 64, BK) : make_map(&mb, b, N, K, ldb, BK, BNH);
   if (r) return r;
   r = make_map(&mc, c, M, N, ldc, 64, BM);
   if (r) return r;
   cudaStream_t st = (cudaStream_t)stream;
+  int* sp = (int*)status;
   const bf16* cp = residual ? (const bf16*)residual : (const bf16*)c;
   if (residual) ldc = ldr;
-  if (epilogue == 1) return launch<1>(ma, mb, mc, M, N, K, (int*)status, sms, cp, ldc, st);
-  if (epilogue == 2) return launch<2>(ma, mb, mc, M, N, K, (int*)status, sms, cp, ldc, st);
-  return launch<0>(ma, mb, mc, M, N, K, (int*)status, sms, cp, ldc, st);
+#define DISPATCH(AM, BMN)                                                                 \
+  (epilogue == 1   ? launch<AM, BMN, 1>(ma, mb, mc, M, N, K, sp, sms, cp, ldc, st)         \
+   : epilogue == 2 ? launch<AM, BMN, 2>(ma, mb, mc, M, N, K, sp, sms, cp, ldc, st)         \
+   : epilogue == 5 ? launch<AM, BMN, 5>(ma, mb, mc, M, N, K, sp, sms, cp, ldc, st)         \
+                   : launch<AM, BMN, 0>(ma, mb, mc, M, N, K, sp, sms, cp, ldc, st))
+  if (!a_mn && !b_mn) return DISPATCH(false, false);
+  if (!a_mn && b_mn) return DISPATCH(false, true);
+  if (a_mn && b_mn) return DISPATCH(true, true);
+  return DISPATCH(true, false);
+#undef DISPATCH
 }

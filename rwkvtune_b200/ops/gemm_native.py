@@ -84,6 +84,9 @@ def _run(a, b, M, N, K, a_mn: int, b_mn: int, epilogue: int = 0, out: torch.Tens
     """``out`` given: accumulate into it (epilogue 2, ``out += op(a) op(b)``) or, with ``accumulate=False``, store
     into it.  ``residual`` given: return ``residual + op(a) op(b)`` in a new tensor.  Both must be bf16 ``[M, N]``
     with unit inner stride."""
+    eff = (2 if accumulate else epilogue) if out is not None else (2 if (residual is not None and epilogue == 0) else epilogue)
+    if two_cta_ok(M, N, K, eff):
+        return _run_2cta(a, b, M, N, K, a_mn, b_mn, epilogue, out, residual, accumulate)
     if out is not None:
         c, epilogue = out, (2 if accumulate else epilogue)
     else:
@@ -100,37 +103,52 @@ def _run(a, b, M, N, K, a_mn: int, b_mn: int, epilogue: int = 0, out: torch.Tens
 def mm_nt(x: torch.Tensor, w: torch.Tensor, epilogue: int = 0, out: torch.Tensor = None,
           residual: torch.Tensor = None) -> torch.Tensor:
     """``x [M,K] @ w[N,K]^T``"""
-    if two_cta_ok(x.shape[0], w.shape[0], x.shape[1], 2 if (out is not None or residual is not None) else epilogue):
-        return mm_nt_2cta(x, w, epilogue, out, residual)
     return _run(x, w, x.shape[0], w.shape[0], x.shape[1], 0, 0, epilogue, out, residual)
 
 
-# The pair-of-SMs kernel (``gemm_tcgen05_2cta.cu``: 256x256 tiles, tcgen05.mma.cta_group::2) serves K-major x K-major
-# products (nn.Linear forward) with epilogues 0, 1, 2 when the output has at least one 256x256 tile per SM pair.
-TWO_CTA = __import__("os").environ.get("RWKVTUNE_GEMM_2CTA", "0") == "1"
+# The pair-of-SMs kernel (``gemm_tcgen05_2cta.cu``: 256x256 tiles, tcgen05.mma.cta_group::2) serves every layout with
+# epilogues 0, 1, 2, 5 when the output has at least one 256x256 tile per SM pair; smaller products, the tanh / sigmoid
+# epilogues and split-K stay on the single-CTA kernel.  Measured on the 1.5B step: 386-388 -> 367-369 ms.
+TWO_CTA = __import__("os").environ.get("RWKVTUNE_GEMM_2CTA", "1") == "1"    # RWKVTUNE_GEMM_2CTA=0: single-CTA kernel only
 
 
 def two_cta_ok(M: int, N: int, K: int, epilogue: int) -> bool:
-    return (TWO_CTA and epilogue in (0, 1, 2) and M >= 256 and N >= 256 and -(-M // 256) * -(-N // 256) >= 74
+    return (TWO_CTA and epilogue in (0, 1, 2, 5) and M >= 256 and N >= 256 and -(-M // 256) * -(-N // 256) >= 74
             and hasattr(_ext.lib(), "rwkv_gemm_bf16_tcgen05_2cta"))
+
+
+def _run_2cta(a, b, M, N, K, a_mn: int, b_mn: int, epilogue: int = 0, out: torch.Tensor = None,
+              residual: torch.Tensor = None, accumulate: bool = True) -> torch.Tensor:
+    """Same contract as :func:`_run`, on the pair-of-SMs kernel."""
+    if out is not None:
+        c, epilogue = out, (2 if accumulate else epilogue)
+    else:
+        c = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+        if residual is not None and epilogue == 0:
+            epilogue = 2
+    _ext.call("rwkv_gemm_bf16_tcgen05_2cta", _ext.ptr(a), _ext.ptr(b), _ext.ptr(c), _ext.i32(M), _ext.i32(N), _ext.i32(K),
+              _ext.i64(a.stride(0)), _ext.i64(b.stride(0)), _ext.i64(c.stride(0)), _ext.i32(a_mn), _ext.i32(b_mn),
+              _ext.i32(epilogue), _ext.ptr(_status(a.device)), _ext.ptr(residual),
+              _ext.i64(0 if residual is None else residual.stride(0)), _ext.stream())
+    return c
 
 
 def mm_nt_2cta(x: torch.Tensor, w: torch.Tensor, epilogue: int = 0, out: torch.Tensor = None,
                residual: torch.Tensor = None) -> torch.Tensor:
     """``x [M,K] @ w[N,K]^T`` on pairs of SMs.  ``out`` given: ``out += x w^T``; ``residual`` given: returns
     ``residual + x w^T``."""
-    M, K, N = x.shape[0], x.shape[1], w.shape[0]
-    if out is not None:
-        c, epilogue = out, 2
-    else:
-        c = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
-        if residual is not None:
-            epilogue = 2
-    _ext.call("rwkv_gemm_bf16_tcgen05_2cta", _ext.ptr(x), _ext.ptr(w), _ext.ptr(c), _ext.i32(M), _ext.i32(N), _ext.i32(K),
-              _ext.i64(x.stride(0)), _ext.i64(w.stride(0)), _ext.i64(c.stride(0)), _ext.i32(epilogue),
-              _ext.ptr(_status(x.device)), _ext.ptr(residual), _ext.i64(0 if residual is None else residual.stride(0)),
-              _ext.stream())
-    return c
+    return _run_2cta(x, w, x.shape[0], w.shape[0], x.shape[1], 0, 0, epilogue, out, residual)
+
+
+def mm_nn_2cta(x: torch.Tensor, w: torch.Tensor, epilogue: int = 0, out: torch.Tensor = None,
+               residual: torch.Tensor = None) -> torch.Tensor:
+    """``x [M,K] @ w[K,N]`` on pairs of SMs."""
+    return _run_2cta(x, w, x.shape[0], w.shape[1], x.shape[1], 0, 1, epilogue, out, residual)
+
+
+def mm_tn_2cta(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor = None, accumulate: bool = True) -> torch.Tensor:
+    """``a[Kc,M]^T @ b[Kc,N]`` on pairs of SMs."""
+    return _run_2cta(a, b, a.shape[1], b.shape[1], a.shape[0], 1, 1, 0, out, None, accumulate)
 
 
 def mm_nn(x: torch.Tensor, w: torch.Tensor, epilogue: int = 0, out: torch.Tensor = None,

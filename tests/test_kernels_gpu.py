@@ -446,6 +446,37 @@ def test_gemm_on_sm_pairs_matches_reference(M, N, K, epilogue):
     assert (y.float() - ref_out).abs().max().item() <= 2e-2 * ref_out.abs().max().item() + 1e-2
 
 
+@pytest.mark.parametrize("M,N,K", [(512, 512, 128), (1000, 776, 200), (2048, 1024, 512), (4096, 2048, 2048)])
+@pytest.mark.parametrize("layout", ["nn", "tn"])
+def test_gemm_on_sm_pairs_mn_major_operands(M, N, K, layout):
+    """The pair-of-SMs kernel with MN-major operands: x @ W (data gradients) and a^T @ b (weight gradients), plus the
+    relu^2-derivative epilogue and store / accumulate into an existing buffer."""
+    from rwkvtune_b200.ops import gemm_native
+    torch.manual_seed(M * 3 + N + K)
+    if layout == "nn":
+        x = torch.randn(M, K, device="cuda").to(BF)
+        w = (torch.randn(K, N, device="cuda") * 0.2).to(BF)
+        ref_out = x.float() @ w.float()
+        y = gemm_native.mm_nn_2cta(x, w)
+        hidden = (torch.rand(M, N, device="cuda") * 2).to(BF)
+        y5 = gemm_native.mm_nn_2cta(x, w, epilogue=5, residual=hidden)
+        ref5 = ref_out * 2 * hidden.float().sqrt()
+        assert (y5.float() - ref5).abs().max().item() <= 2e-2 * ref5.abs().max().item() + 1e-2
+    else:
+        a = torch.randn(K, M, device="cuda").to(BF)
+        b = (torch.randn(K, N, device="cuda") * 0.2).to(BF)
+        ref_out = a.float().t() @ b.float()
+        y = gemm_native.mm_tn_2cta(a, b)
+        buf = torch.full((M, N), 7.0, device="cuda").to(BF)
+        gemm_native.mm_tn_2cta(a, b, out=buf, accumulate=False)
+        assert (buf.float() - ref_out).abs().max().item() <= 2e-2 * ref_out.abs().max().item() + 1e-2
+        gemm_native.mm_tn_2cta(a, b, out=buf)
+        assert (buf.float() - 2 * ref_out).abs().max().item() <= 4e-2 * ref_out.abs().max().item() + 2e-2
+    torch.cuda.synchronize()
+    assert gemm_native.check_status() == 0
+    assert (y.float() - ref_out).abs().max().item() <= 2e-2 * ref_out.abs().max().item() + 1e-2
+
+
 def _chi_square_ok(toks, probs, n):
     V = probs.numel()
     counts = torch.bincount(toks, minlength=V).float()
