@@ -112,8 +112,11 @@ def mm_nt(x: torch.Tensor, w: torch.Tensor, epilogue: int = 0, out: torch.Tensor
 TWO_CTA = __import__("os").environ.get("RWKVTUNE_GEMM_2CTA", "1") == "1"    # RWKVTUNE_GEMM_2CTA=0: single-CTA kernel only
 
 
+TWO_CTA_MIN_TILES = int(__import__("os").environ.get("RWKVTUNE_GEMM_2CTA_MIN_TILES", "48"))   # of 74 SM pairs
+
+
 def two_cta_ok(M: int, N: int, K: int, epilogue: int) -> bool:
-    return (TWO_CTA and epilogue in (0, 1, 2, 5) and M >= 256 and N >= 256 and -(-M // 256) * -(-N // 256) >= 74
+    return (TWO_CTA and epilogue in (0, 1, 2, 5) and M >= 256 and N >= 256 and -(-M // 256) * -(-N // 256) >= TWO_CTA_MIN_TILES
             and hasattr(_ext.lib(), "rwkv_gemm_bf16_tcgen05_2cta"))
 
 
