@@ -7,6 +7,8 @@
 // each a separate pass over [B,T,C] (model.py:138-144, :305-306, :373).  Here x is read once
 // and the K outputs are written once.  h is rounded to bf16 before it is mixed, so a
 // sequence processed in chunks with the carried row gives bit-identical results.
+#include <stdlib.h>
+
 #include "elementwise.cuh"
 
 namespace {
@@ -645,6 +647,243 @@ ln_shift_mix_bwd1_pair_kernel(const bf16* __restrict__ dO, const bf16* __restric
   }
 }
 
+// ------------------------------------------------------------------------------------------------------------
+// Backward, pipelined version (K = 1 or 6, up to 2048 channels): four channels per thread held as two float2 pairs
+// (packed fp32x2 arithmetic), two rows per block reduction, and the tiles of the next two rows (K gradients, x of the
+// row before, the residual gradient) fetched with 8-byte cp.async into a per-thread slot of a double-buffered
+// shared-memory ring while the current two rows are processed.  The per-channel state (K mix coefficients, K + 2
+// parameter-gradient accumulators, the LayerNorm weight and bias, the carry) fills the register file of one CTA per
+// SM, so loads in flight cannot come from other CTAs or from more registers: the ring supplies them.
+// Same `partials` layout and the same arithmetic order per channel as the kernels above.
+constexpr int V5_MAX_THREADS = 512;
+// HBM latency under load is several thousand cycles; one row pair is 8 KB per tensor per CTA, so keeping the memory
+// system busy from a single resident CTA takes two (K = 6: 3 x 64 KB of ring) or three (K = 1) row pairs in flight.
+__host__ __device__ constexpr int V5_NBUF(int K) { return K >= 4 ? 3 : 4; }
+
+__device__ __forceinline__ float2 bf2_to_f2(uint32_t u) { return make_float2(bf16_lo(u), bf16_hi(u)); }
+__device__ __forceinline__ float2 f2_fma(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+__device__ __forceinline__ float2 f2_add(float2 a, float2 b) { return __fadd2_rn(a, b); }
+__device__ __forceinline__ float2 f2_mul(float2 a, float2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ float2 f2_sub(float2 a, float2 b) { return __fadd2_rn(a, make_float2(-b.x, -b.y)); }
+__device__ __forceinline__ float2 f2_set(float v) { return make_float2(v, v); }
+__device__ __forceinline__ void cp8(void* dst, const void* src, bool pred) {
+  const int sz = pred ? 8 : 0;     // size 0: the 8 bytes are zero-filled, nothing is read
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src),
+               "r"(sz)
+               : "memory");
+}
+
+template <int K>
+__global__ void __launch_bounds__(V5_MAX_THREADS, 1)
+ln_shift_mix_bwd_v5_kernel(const DOutPtrs dO, const bf16* __restrict__ dlast, const bf16* __restrict__ dres,
+                           const bf16* __restrict__ x, const float* __restrict__ mean_in,
+                           const float* __restrict__ rstd_in, const float* __restrict__ ln_w,
+                           const float* __restrict__ ln_b, const float* __restrict__ mix,
+                           const bf16* __restrict__ prev, bf16* __restrict__ dx, float* __restrict__ dprev,
+                           float* __restrict__ partials, int B, int T, int C, int strip) {
+  constexpr int NTEN = K + 2;                       // per row slot: K gradient tiles, x of the row before, dres
+  constexpr int NBUF = V5_NBUF(K);                  // ring depth: NBUF - 1 row pairs in flight ahead of the one in work
+  extern __shared__ __align__(16) unsigned char v5_smem[];
+  uint2* ring = reinterpret_cast<uint2*>(v5_smem);  // [NBUF buffers][2 rows][NTEN][blockDim.x]
+  __shared__ float red[2 * EW_MAX_WARPS * 4];
+  int phase = 0;
+  const int nt = blockDim.x;
+  const int b = blockIdx.y, t0 = blockIdx.x * strip, t1 = min(T, t0 + strip);
+  const int tid = threadIdx.x, col = tid * 4;
+  const bool active = col < C;
+  const size_t row0 = (size_t)b * T;
+  const float invC = 1.f / C;
+  auto slot = [&](int bf_, int r, int ten) { return ring + ((size_t)((bf_ * 2 + r) * NTEN + ten)) * nt + tid; };
+
+  float2 w2[2], b2[2], mu2[K][2], accmu2[K][2], accw2[2], accb2[2], carry2[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    w2[i] = b2[i] = accw2[i] = accb2[i] = carry2[i] = f2_set(0.f);
+#pragma unroll
+    for (int k = 0; k < K; ++k) mu2[k][i] = accmu2[k][i] = f2_set(0.f);
+  }
+  if (active) {
+    const float4 w4 = *reinterpret_cast<const float4*>(ln_w + col), b4 = *reinterpret_cast<const float4*>(ln_b + col);
+    w2[0] = make_float2(w4.x, w4.y); w2[1] = make_float2(w4.z, w4.w);
+    b2[0] = make_float2(b4.x, b4.y); b2[1] = make_float2(b4.z, b4.w);
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const float4 m4 = *reinterpret_cast<const float4*>(mix + (size_t)k * C + col);
+      mu2[k][0] = make_float2(m4.x, m4.y); mu2[k][1] = make_float2(m4.z, m4.w);
+    }
+    if (t1 < T) {   // halo: contribution of the row after the strip
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+        const uint2 g = *reinterpret_cast<const uint2*>(dO.p[k] + (row0 + t1) * C + col);
+        carry2[0] = f2_fma(bf2_to_f2(g.x), mu2[k][0], carry2[0]);
+        carry2[1] = f2_fma(bf2_to_f2(g.y), mu2[k][1], carry2[1]);
+      }
+    } else if (dlast) {
+      const uint2 g = *reinterpret_cast<const uint2*>(dlast + (size_t)b * C + col);
+      carry2[0] = bf2_to_f2(g.x); carry2[1] = bf2_to_f2(g.y);
+    }
+  }
+
+  // Row slot r of a buffer describes output row tt: gradients of row tt, x of row tt - 1 (to rebuild h of the row
+  // before), dres of row tt.  Rows below t0 are never processed; x of row t0 - 1 is a halo read (the carried row
+  // `prev` stands in for row -1).
+  auto issue = [&](int buf, int t_hi) {
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int tt = t_hi - r;
+      const bool live = active && tt >= t0;
+      const size_t off = (row0 + (live ? tt : t0)) * C + (active ? col : 0);   // always an address inside the tensors
+#pragma unroll
+      for (int k = 0; k < K; ++k) cp8(slot(buf, r, k), dO.p[k] + off, live);
+      const bool has_x = live && tt - 1 >= 0;
+      const bool has_prev = live && tt - 1 < 0 && prev != nullptr;
+      const bf16* xsrc = has_x ? x + (row0 + tt - 1) * C + col : (has_prev ? prev + (size_t)b * C + col : x + off);
+      cp8(slot(buf, r, K), xsrc, has_x || has_prev);
+      cp8(slot(buf, r, K + 1), dres ? dres + off : x + off, live && dres != nullptr);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  // h and xhat of a row from its raw x tile; row -1 is the carried row (already h), rows without data are zero
+  auto rebuild = [&](const uint2& raw, int t, float2* xh, float2* h) {
+    const float2 x0 = bf2_to_f2(raw.x), x1 = bf2_to_f2(raw.y);
+    if (t < 0) {
+      xh[0] = xh[1] = f2_set(0.f);
+      h[0] = x0; h[1] = x1;
+      return;
+    }
+    const float m = mean_in[row0 + t], r = rstd_in[row0 + t];
+    const float2 r2 = f2_set(r), nmr = f2_set(-m * r);
+    xh[0] = f2_fma(x0, r2, nmr);
+    xh[1] = f2_fma(x1, r2, nmr);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const float2 hv = f2_fma(xh[i], w2[i], b2[i]);
+      h[i] = bf2_to_f2(pack_bf16(hv.x, hv.y));      // rounded exactly as the forward stored it
+    }
+  };
+
+  float2 xh_a[2], h_a[2];
+  {
+    uint2 raw = make_uint2(0u, 0u);
+    if (active) raw = *reinterpret_cast<const uint2*>(x + (row0 + t1 - 1) * C + col);
+    rebuild(raw, t1 - 1, xh_a, h_a);
+  }
+  // prologue: NBUF - 1 row pairs in flight (empty groups keep the group count uniform past the end of the strip)
+#pragma unroll
+  for (int i = 0; i < NBUF - 1; ++i) {
+    if (t1 - 1 - 2 * i >= t0) issue(i, t1 - 1 - 2 * i);
+    else asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+  int buf = 0;
+  for (int t = t1 - 1; t >= t0; t -= 2) {
+    const bool two = t - 1 >= t0;
+    {
+      const int ahead = t - 2 * (NBUF - 1);
+      int nb = buf + NBUF - 1;
+      if (nb >= NBUF) nb -= NBUF;
+      if (ahead >= t0) issue(nb, ahead);
+      else asm volatile("cp.async.commit_group;" ::: "memory");
+      asm volatile("cp.async.wait_group %0;" ::"n"(NBUF - 1) : "memory");
+    }
+    float2 xh_b[2], h_b[2], xh_c[2], h_c[2];
+    rebuild(*slot(buf, 0, K), t - 1, xh_b, h_b);
+    rebuild(*slot(buf, 1, K), t - 2, xh_c, h_c);
+    float2 dh_a[2], dh_b[2], nc_a[2], nc_b[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) { dh_a[i] = carry2[i]; nc_a[i] = nc_b[i] = dh_b[i] = f2_set(0.f); }
+    const float2 dlt_a[2] = {f2_sub(h_b[0], h_a[0]), f2_sub(h_b[1], h_a[1])};
+    const float2 dlt_b[2] = {f2_sub(h_c[0], h_b[0]), f2_sub(h_c[1], h_b[1])};
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const uint2 ga = *slot(buf, 0, k), gb = *slot(buf, 1, k);     // zero for rows that are not processed
+      const float2 ga2[2] = {bf2_to_f2(ga.x), bf2_to_f2(ga.y)}, gb2[2] = {bf2_to_f2(gb.x), bf2_to_f2(gb.y)};
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        dh_a[i] = f2_add(dh_a[i], ga2[i]);
+        nc_a[i] = f2_fma(ga2[i], mu2[k][i], nc_a[i]);
+        accmu2[k][i] = f2_fma(ga2[i], dlt_a[i], accmu2[k][i]);
+        dh_b[i] = f2_add(dh_b[i], gb2[i]);
+        nc_b[i] = f2_fma(gb2[i], mu2[k][i], nc_b[i]);
+        accmu2[k][i] = f2_fma(gb2[i], dlt_b[i], accmu2[k][i]);
+      }
+    }
+    float c[4] = {0.f, 0.f, 0.f, 0.f};
+    float2 gw_a[2], gw_b[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      dh_a[i] = f2_sub(dh_a[i], nc_a[i]);                   // sum_k g_k (1 - mu_k) + carry
+      dh_b[i] = f2_add(f2_sub(dh_b[i], nc_b[i]), nc_a[i]);  // row t-1 receives row t's shifted share
+      gw_a[i] = f2_mul(dh_a[i], w2[i]);
+      gw_b[i] = f2_mul(dh_b[i], w2[i]);
+      const float2 pa = f2_mul(gw_a[i], xh_a[i]), pb = f2_mul(gw_b[i], xh_b[i]);
+      c[0] += gw_a[i].x + gw_a[i].y;
+      c[1] += pa.x + pa.y;
+      accw2[i] = f2_fma(dh_a[i], xh_a[i], accw2[i]);
+      accb2[i] = f2_add(accb2[i], dh_a[i]);
+      if (two) {
+        c[2] += gw_b[i].x + gw_b[i].y;
+        c[3] += pb.x + pb.y;
+        accw2[i] = f2_fma(dh_b[i], xh_b[i], accw2[i]);
+        accb2[i] = f2_add(accb2[i], dh_b[i]);
+      }
+    }
+    block_sum<4>(c, red, phase);
+    if (active) {
+      auto emit = [&](int tt, const float2* gw, const float2* xh, float s0, float s1, const uint2& rres) {
+        const float2 r2 = f2_set(rstd_in[row0 + tt]);
+        const float2 n0 = f2_set(-s0 * invC), n1 = f2_set(-s1 * invC);
+        float2 o[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) o[i] = f2_mul(r2, f2_fma(xh[i], n1, f2_add(gw[i], n0)));
+        if (dres) {
+          o[0] = f2_add(o[0], bf2_to_f2(rres.x));
+          o[1] = f2_add(o[1], bf2_to_f2(rres.y));
+        }
+        *reinterpret_cast<uint2*>(dx + (row0 + tt) * C + col) = make_uint2(pack_bf16(o[0].x, o[0].y), pack_bf16(o[1].x, o[1].y));
+      };
+      emit(t, gw_a, xh_a, c[0], c[1], *slot(buf, 0, K + 1));
+      if (two) emit(t - 1, gw_b, xh_b, c[2], c[3], *slot(buf, 1, K + 1));
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      carry2[i] = two ? nc_b[i] : nc_a[i];
+      xh_a[i] = two ? xh_c[i] : xh_b[i];
+      h_a[i] = two ? h_c[i] : h_b[i];
+    }
+    if (++buf == NBUF) buf = 0;
+  }
+  if (active) {
+    if (dprev && t0 == 0) *reinterpret_cast<float4*>(dprev + (size_t)b * C + col) = make_float4(carry2[0].x, carry2[0].y, carry2[1].x, carry2[1].y);
+    float* p = partials + ((size_t)(blockIdx.y * gridDim.x + blockIdx.x) * (K + 2)) * C + col;
+#pragma unroll
+    for (int k = 0; k < K; ++k)
+      *reinterpret_cast<float4*>(p + (size_t)k * C) = make_float4(accmu2[k][0].x, accmu2[k][0].y, accmu2[k][1].x, accmu2[k][1].y);
+    *reinterpret_cast<float4*>(p + (size_t)K * C) = make_float4(accw2[0].x, accw2[0].y, accw2[1].x, accw2[1].y);
+    *reinterpret_cast<float4*>(p + (size_t)(K + 1) * C) = make_float4(accb2[0].x, accb2[0].y, accb2[1].x, accb2[1].y);
+  }
+}
+
+template <int K>
+int launch_bwd_v5(const DOutPtrs& dptrs, const void* dlast, const void* dres, const void* x, const void* mean,
+                  const void* rstd, const void* ln_w, const void* ln_b, const void* mix, const void* prev, void* dx,
+                  void* dprev, void* partials, int B, int T, int C, int strip, cudaStream_t st) {
+  const int nt = ((C / 4 + 31) / 32) * 32;
+  const int smem = V5_NBUF(K) * 2 * (K + 2) * nt * (int)sizeof(uint2);
+  auto kern = ln_shift_mix_bwd_v5_kernel<K>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, V5_NBUF(K) * 2 * (K + 2) * V5_MAX_THREADS * (int)sizeof(uint2));
+    if (e != cudaSuccess) return RWKV_ERR_CUDA_BASE + (int)e;
+    configured = true;
+  }
+  dim3 grid((T + strip - 1) / strip, B);
+  kern<<<grid, nt, smem, st>>>(dptrs, (const bf16*)dlast, (const bf16*)dres, (const bf16*)x, (const float*)mean,
+                               (const float*)rstd, (const float*)ln_w, (const float*)ln_b, (const float*)mix,
+                               (const bf16*)prev, (bf16*)dx, (float*)dprev, (float*)partials, B, T, C, strip);
+  return rwkv_launch_status();
+}
+
 inline int threads_for(int C) { return ((C / 8 + 31) / 32) * 32; }
 
 }  // namespace
@@ -694,6 +933,16 @@ RWKV_EXPORT int rwkv_ln_shift_mix_backward(const void* const* dO, const void* dl
       dptrs, (const bf16*)dlast, (const bf16*)dres, (const bf16*)x, (const float*)mean, (const float*)rstd,      \
       (const float*)ln_w, (const float*)ln_b, (const float*)mix, (const bf16*)prev, (bf16*)dx, (float*)dprev,    \
       (float*)partials, B, T, C, strip)
+  static int use_v5 = -1;
+  if (use_v5 < 0) {
+    const char* e = getenv("RWKVTUNE_LN_BWD_V5");
+    use_v5 = (e && e[0] == '0') ? 0 : 1;
+  }
+  if (use_v5 && C % 4 == 0 && C / 4 <= V5_MAX_THREADS) {   // pipelined kernel: packed arithmetic, two rows per reduction
+    if (K == 6)
+      return launch_bwd_v5<6>(dptrs, dlast, dres, x, mean, rstd, ln_w, ln_b, mix, prev, dx, dprev, partials, B, T, C, strip, st);
+    return launch_bwd_v5<1>(dptrs, dlast, dres, x, mean, rstd, ln_w, ln_b, mix, prev, dx, dprev, partials, B, T, C, strip, st);
+  }
   if (C / 4 <= 512) {   // four channels per thread with row prefetch
     if (K == 6) LAUNCH_V4(6);
     else
