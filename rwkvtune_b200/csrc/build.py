@@ -47,15 +47,20 @@ def _digest(path: str) -> str:
     return h.hexdigest()
 
 
-def _compile_one(src: str, verbose: bool) -> str:
-    obj_dir = os.path.join(HERE, "build")
+DEBUG_LIB_NAME = "librwkvtune_b200_debug.so"
+DEBUG_FLAGS = ["-DRWKV_DEBUG_BOUNDS"]
+
+
+def _compile_one(src: str, verbose: bool, debug: bool = False) -> str:
+    obj_dir = os.path.join(HERE, "build_debug" if debug else "build")
     os.makedirs(obj_dir, exist_ok=True)
     obj = os.path.join(obj_dir, src[:-3] + ".o")
     stamp = obj + ".sha"
-    digest = _digest(os.path.join(HERE, src))
+    digest = _digest(os.path.join(HERE, src)) + ("-debug" if debug else "")
     if os.path.exists(obj) and os.path.exists(stamp) and open(stamp).read() == digest:
         return obj
-    cmd = [nvcc_path()] + ARCH_FLAGS + COMMON_FLAGS + ["-Xptxas", "-v", "-c", os.path.join(HERE, src), "-o", obj]
+    cmd = ([nvcc_path()] + ARCH_FLAGS + COMMON_FLAGS + (DEBUG_FLAGS if debug else [])
+           + ["-Xptxas", "-v", "-c", os.path.join(HERE, src), "-o", obj])
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError(f"nvcc failed for {src}:\n{res.stdout}\n{res.stderr}")
@@ -68,14 +73,16 @@ def _compile_one(src: str, verbose: bool) -> str:
     return obj
 
 
-def build(verbose: bool = True, force: bool = False) -> str:
-    """Compile and link; returns the path of the shared library."""
+def build(verbose: bool = True, force: bool = False, debug: bool = False) -> str:
+    """Compile and link; returns the path of the shared library.  ``debug=True`` builds the bounds-recording variant
+    (``librwkvtune_b200_debug.so``: data-dependent indices are range-checked, violations are recorded in a device
+    word and skipped, nothing traps); ``RWKVTUNE_DEBUG_LIB=1`` makes the package load it."""
     if force:
-        shutil.rmtree(os.path.join(HERE, "build"), ignore_errors=True)
+        shutil.rmtree(os.path.join(HERE, "build_debug" if debug else "build"), ignore_errors=True)
     srcs = sources()
     with cf.ThreadPoolExecutor(max_workers=min(8, len(srcs) or 1)) as pool:
-        objs = list(pool.map(lambda s: _compile_one(s, verbose), srcs))
-    lib = os.path.join(HERE, LIB_NAME)
+        objs = list(pool.map(lambda s: _compile_one(s, verbose, debug), srcs))
+    lib = os.path.join(HERE, DEBUG_LIB_NAME if debug else LIB_NAME)
     newest = max(os.path.getmtime(o) for o in objs)
     if force or not os.path.exists(lib) or os.path.getmtime(lib) < newest:
         cmd = [nvcc_path(), "-shared", "-o", lib] + objs
@@ -88,4 +95,4 @@ def build(verbose: bool = True, force: bool = False) -> str:
 
 
 if __name__ == "__main__":
-    build(verbose=True, force="--force" in sys.argv)
+    build(verbose=True, force="--force" in sys.argv, debug="--debug" in sys.argv)

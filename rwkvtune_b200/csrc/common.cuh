@@ -65,3 +65,35 @@ __device__ __forceinline__ float warp_max(float v) {
 }
 
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
+
+
+// ------------------------------------------------------------------------------------------------------------------
+// Debug build (`python -m rwkvtune_b200.csrc.build --debug`, -DRWKV_DEBUG_BOUNDS): data-dependent indices (token ids,
+// labels, gather indices, row permutations) are range-checked where they are used.  An index out of range is
+// *recorded* - event count, kernel tag, the index and its limit - and the access is skipped; nothing traps, asserts or
+// faults, so the context stays usable and the host reads the record afterwards (`rwkv_debug_read_<file>`).  In the
+// release build the same call is the plain range test the kernels rely on anyway.
+// Each translation unit that uses the check instantiates its own record with RWKV_DEFINE_DEBUG_EVENTS(tag).
+#ifdef RWKV_DEBUG_BOUNDS
+#define RWKV_DEFINE_DEBUG_EVENTS(tag)                                                                     \
+  static __device__ long long rwkv_debug_events_[4];   /* count, kernel tag of the first event, index, limit */ \
+  RWKV_EXPORT int rwkv_debug_read_##tag(long long* out4, int reset) {                                     \
+    cudaError_t e = cudaMemcpyFromSymbol(out4, rwkv_debug_events_, 4 * sizeof(long long));                \
+    if (e == cudaSuccess && reset) {                                                                      \
+      const long long zero[4] = {0, 0, 0, 0};                                                             \
+      e = cudaMemcpyToSymbol(rwkv_debug_events_, zero, sizeof(zero));                                     \
+    }                                                                                                     \
+    return e == cudaSuccess ? RWKV_OK : RWKV_ERR_CUDA_BASE + (int)e;                                      \
+  }
+#define RWKV_IN_RANGE(i, n, kernel_tag) rwkv_in_range_dbg_((long long)(i), (long long)(n), (kernel_tag), rwkv_debug_events_)
+__device__ __forceinline__ bool rwkv_in_range_dbg_(long long i, long long n, int kernel_tag, long long* ev) {
+  if (i >= 0 && i < n) return true;
+  if (atomicAdd(reinterpret_cast<unsigned long long*>(&ev[0]), 1ull) == 0ull) {
+    ev[1] = kernel_tag; ev[2] = i; ev[3] = n;
+  }
+  return false;
+}
+#else
+#define RWKV_DEFINE_DEBUG_EVENTS(tag)
+#define RWKV_IN_RANGE(i, n, kernel_tag) ((long long)(i) >= 0 && (long long)(i) < (long long)(n))
+#endif

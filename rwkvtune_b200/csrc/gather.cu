@@ -9,6 +9,8 @@
 //                           order (positions sorted by index), so the result is deterministic.
 #include "common.cuh"
 
+RWKV_DEFINE_DEBUG_EVENTS(gather)
+
 namespace {
 
 __global__ void __launch_bounds__(256)
@@ -20,7 +22,7 @@ gather_rows_kernel(const uint4* __restrict__ src, const long long* __restrict__ 
     const long long r = i / vec_per_row;
     const int c = (int)(i - r * vec_per_row);
     const long long s = index[r];
-    dst[i] = (s >= 0 && s < n_src) ? src[s * vec_per_row + c] : make_uint4(0u, 0u, 0u, 0u);
+    dst[i] = RWKV_IN_RANGE(s, n_src, 1) ? src[s * vec_per_row + c] : make_uint4(0u, 0u, 0u, 0u);
   }
 }
 
@@ -30,12 +32,13 @@ embedding_bwd_kernel(const bf16* __restrict__ dy, const long long* __restrict__ 
                      const long long* __restrict__ order, bf16* __restrict__ dW, long long M, long long V, int C) {
   const long long i = blockIdx.x;
   const long long tok = sorted_idx[i];
-  if (tok < 0 || tok >= V) return;
+  if (!RWKV_IN_RANGE(tok, V, 2)) return;
   if (i > 0 && sorted_idx[i - 1] == tok) return;
   for (int c = threadIdx.x * 8; c < C; c += blockDim.x * 8) {
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     for (long long j = i; j < M && sorted_idx[j] == tok; ++j) {
       float f[8];
+      if (!RWKV_IN_RANGE(order[j], M, 3)) continue;
       unpack8(*reinterpret_cast<const uint4*>(dy + order[j] * C + c), f);
 #pragma unroll
       for (int e = 0; e < 8; ++e) acc[e] += f[e];

@@ -11,6 +11,8 @@
 //                                (rwkvtune/training/grpo/utils.py:13-152)
 #include "common.cuh"
 
+RWKV_DEFINE_DEBUG_EVENTS(loss_rows)
+
 namespace {
 
 constexpr int LNT = 256;
@@ -92,7 +94,7 @@ ce_rows_kernel(bf16* __restrict__ logits, const long long* __restrict__ labels, 
   const int row = blockIdx.x;
   bf16* p = logits + (size_t)row * V;
   const long long label = labels[row];
-  const bool valid = label != ignore_index && label >= 0 && label < V;
+  const bool valid = label != ignore_index && RWKV_IN_RANGE(label, V, 11);
   if (threadIdx.x == 0) tgt_s = valid ? __bfloat162float(p[label]) : 0.f;   // before the row is overwritten
   const RowStats st = row_stats<false>(p, V, 1.f, red);
   const float lse = st.m + __logf(st.s);
@@ -126,7 +128,7 @@ logprob_entropy_fwd_kernel(const bf16* __restrict__ logits, const long long* __r
   if (threadIdx.x == 0) {
     const float lse = st.m + __logf(st.s);
     const long long t = targets[row];
-    const float zt = (t >= 0 && t < V) ? __bfloat162float(p[t]) * inv_t : 0.f;
+    const float zt = RWKV_IN_RANGE(t, V, 12) ? __bfloat162float(p[t]) * inv_t : 0.f;
     logp[row] = zt - lse;
     if (ent) ent[row] = lse - st.sx / st.s;
   }

@@ -14,7 +14,9 @@ from typing import Optional
 import torch
 
 _LIB: Optional[ctypes.CDLL] = None
-_LIB_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "csrc", "librwkvtune_b200.so")
+DEBUG_BUILD = os.environ.get("RWKVTUNE_DEBUG_LIB", "0") == "1"      # load the bounds-recording build of the library
+_LIB_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "csrc",
+                         "librwkvtune_b200_debug.so" if DEBUG_BUILD else "librwkvtune_b200.so")
 
 
 class NativeLibraryMissing(RuntimeError):
@@ -115,3 +117,25 @@ def i64(v: int) -> ctypes.c_longlong:
 
 def f32(v: float) -> ctypes.c_float:
     return ctypes.c_float(float(v))
+
+
+DEBUG_EVENT_SOURCES = ("gather", "loss_rows")
+
+
+def debug_events(reset: bool = False):
+    """Bounds violations recorded by the debug build since the last reset: ``{source file: (count, kernel tag, index,
+    limit)}`` for every source that saw one.  Empty in the release build."""
+    out = {}
+    if not DEBUG_BUILD:
+        return out
+    torch.cuda.synchronize()
+    for tag in DEBUG_EVENT_SOURCES:
+        fn = getattr(lib(), f"rwkv_debug_read_{tag}", None)
+        if fn is None:
+            continue
+        buf = (ctypes.c_longlong * 4)()
+        fn.restype = ctypes.c_int
+        check(fn(buf, ctypes.c_int(1 if reset else 0)), f"rwkv_debug_read_{tag}")
+        if buf[0]:
+            out[tag] = tuple(int(v) for v in buf)
+    return out
