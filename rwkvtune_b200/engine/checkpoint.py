@@ -155,7 +155,13 @@ def load_optimizer_state(ckpt_dir: str, engine, ctx) -> bool:
                    key=lambda f: int(os.path.basename(f)[4:-3]))
     if not files:
         return False
-    shards = [torch.load(f, map_location="cpu", weights_only=False) for f in files]
+    try:
+        shards = [torch.load(f, map_location="cpu", weights_only=False) for f in files]
+    except Exception as exc:   # truncated or corrupt shard: fall back to a weights-only resume, loudly
+        if ctx.is_main:
+            print(f"[checkpoint] optimiser state under {ckpt_dir} is unreadable ({type(exc).__name__}: {exc}); "
+                  "resuming from the weights only")
+        return False
     if shards[0]["stage"] == 0:
         shards = shards[:1]
     else:

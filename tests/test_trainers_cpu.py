@@ -152,3 +152,26 @@ def test_full_and_merged_saves_reassemble_sharded_weights(tmp_path):
     full = str(tmp_path / "full")
     save_model_or_adapter(model, full, None, "full")
     assert torch.allclose(AutoModel.from_pretrained(full)(idx), want, atol=1e-4)
+
+
+def test_truncated_optimizer_shard_falls_back_to_weights_only_resume(tmp_path, capsys):
+    common = dict(ctx_len=32, micro_bsz=4, lr_init=3e-3, lr_final=1e-3, warmup_steps=0, accelerator="cpu",
+                  precision="fp32", grad_cp=0, epoch_save=1, save_total_limit=0)
+    first = str(tmp_path / "first")
+    SFTTrainer(_model(), SFTConfig(epoch_count=1, proj_dir=first, **common), _dataset()).train()
+    ck = os.path.join(first, "rwkv7-epoch1")
+    shard = os.path.join(ck, "trainer_state", "rank0.pt")
+    raw = open(shard, "rb").read()
+    open(shard, "wb").write(raw[:len(raw) // 3])          # the file was cut short
+    resumed = str(tmp_path / "resumed")
+    args = SFTConfig(epoch_count=2, proj_dir=resumed, resume_from_checkpoint=ck, **common)
+    SFTTrainer(_model(), args, _dataset()).train()
+    out = capsys.readouterr().out
+    assert "unreadable" in out and "weights only" in out
+    losses = _losses(resumed)
+    assert len(losses) == 6 and all(l == l for l in losses)      # the second epoch ran from the saved weights
+    # a missing meta file means "no trainer state": also a clean weights-only resume
+    os.remove(os.path.join(ck, "trainer_state", "meta.json"))
+    again = str(tmp_path / "again")
+    SFTTrainer(_model(), SFTConfig(epoch_count=1, proj_dir=again, resume_from_checkpoint=ck, **common), _dataset()).train()
+    assert len(_losses(again)) == 6
