@@ -183,7 +183,7 @@ def run_ours(a):
                        "parallelism": f"dp{ctx.world_size}", "grad_cp": a.grad_cp},
             "details": {"sharding": "zero2" if ctx.world_size > 1 else "none", "checkpointed_layers": cp_layers,
                         "cuda_graph": bool(a.cuda_graph),
-                        "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2**30, 1),
+                        "peak_mem_gb": round(eng.phases.peak_bytes() / 2**30, 1),
                         "transport": a.transport if ctx.world_size > 1 else "none",
                         "optimizer": "AdamW fp32 master, clip 1.0",
                         "l2_flush": "inputs larger than L2: per-step activations and weights (>3 GB) exceed the 126 MB L2",

@@ -97,7 +97,7 @@ def bench_lora_zero3(a):
                  "config": {"model": "rwkv7-2.9b", "lora_r": 64, "seq_len": T, "micro_bsz": B,
                             "parallelism": f"zero3-dp{ctx.world_size}" if ctx.world_size > 1 else "single",
                             "fused_allgather_gemm": eng.zero3 is not None, "checkpointed_layers": state["cp"],
-                            "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2**30, 1)}}
+                            "peak_mem_gb": round(eng.phases.peak_bytes() / 2**30, 1)}}
 
 
 def bench_infctx(a):
@@ -124,7 +124,7 @@ def bench_infctx(a):
                  "config": {"model": "rwkv7-0.4b", "seq_len": T, "chunk_ctx": chunk, "micro_bsz": B, "bptt": "truncated",
                             "cuda_graph_chunk_step": not a.no_graph,
                             "parallelism": f"zero2-dp{ctx.world_size}" if ctx.world_size > 1 else "single",
-                            "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2**30, 1)}}
+                            "peak_mem_gb": round(eng.phases.peak_bytes() / 2**30, 1)}}
 
 
 class _IdTokenizer:
@@ -403,7 +403,7 @@ def bench_full_zero3(a):
         eng.check_health()
         out[strategy] = {"ms_per_step": ms, "tokens_per_sec": B * T * ctx.world_size / ms * 1e3,
                          "checkpointed_layers": state.get("cp"),
-                         "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2**30, 1)}
+                         "peak_mem_gb": round(eng.phases.peak_bytes() / 2**30, 1)}
         del eng, model
         torch.cuda.empty_cache()
     s2, s3 = out["deepspeed_stage_2"]["ms_per_step"], out["deepspeed_stage_3"]["ms_per_step"]

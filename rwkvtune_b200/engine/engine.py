@@ -133,7 +133,7 @@ class TrainEngine:
         if self.ctx.device.type != "cuda" or not self.cfg.grad_cp:
             return L
         total = torch.cuda.get_device_properties(self.ctx.device).total_memory
-        peak = torch.cuda.max_memory_allocated(self.ctx.device)
+        peak = self.phases.peak_bytes()
         per_layer = self.SAVED_UNITS_PER_LAYER * batch * seq_len * cfg.n_embd * 2
         budget = total * (1.0 - reserve_fraction) - peak
         free_layers = int(max(0, budget) // per_layer)

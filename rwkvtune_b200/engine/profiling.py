@@ -33,6 +33,14 @@ class PhaseMonitor:
         self.seconds: Dict[str, float] = defaultdict(float)
         self.calls: Dict[str, int] = defaultdict(int)
         self.peak_gb: Dict[str, float] = defaultdict(float)
+        self._run_peak = 0          # bytes: peak over the whole run, kept across the per-phase resets below
+
+    def peak_bytes(self) -> int:
+        """Peak allocated bytes since this monitor was created.  Phases reset the allocator's own peak counter to
+        get a per-phase figure, so the run-wide peak has to be read here, not from ``torch.cuda.max_memory_allocated``."""
+        if self.cuda:
+            self._run_peak = max(self._run_peak, torch.cuda.max_memory_allocated(self.device))
+        return self._run_peak
 
     @contextlib.contextmanager
     def phase(self, name: str):
@@ -40,6 +48,7 @@ class PhaseMonitor:
             torch.cuda.nvtx.range_push(name)
             if self.sync:
                 torch.cuda.synchronize(self.device)
+            self.peak_bytes()
             torch.cuda.reset_peak_memory_stats(self.device)
             before = torch.cuda.memory_allocated(self.device)
         t0 = time.perf_counter()
@@ -53,6 +62,7 @@ class PhaseMonitor:
             self.calls[name] += 1
             if self.cuda:
                 peak = torch.cuda.max_memory_allocated(self.device) / 2**30
+                self.peak_bytes()
                 self.peak_gb[name] = max(self.peak_gb[name], peak)
                 torch.cuda.nvtx.range_pop()
                 if self.verbose:

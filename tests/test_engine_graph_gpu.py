@@ -37,3 +37,20 @@ def test_graph_replay_trains_like_eager(train_type):
     assert n0 == 0 and n1 == 1            # one shape captured after the warm-up steps
     for a, b in zip(eager, graph):
         assert abs(a - b) <= 2e-3 * abs(a) + 1e-4, (eager, graph)
+
+
+def test_run_wide_peak_survives_phase_resets():
+    """Phases reset the allocator's peak counter for their own figure; the run-wide peak must still be the largest."""
+    from rwkvtune_b200.engine.profiling import PhaseMonitor
+
+    dev = torch.device("cuda", 0)
+    mon = PhaseMonitor(dev)
+    with mon.phase("big"):
+        big = torch.empty(64 << 20, dtype=torch.uint8, device=dev)
+        del big
+    with mon.phase("small"):
+        small = torch.empty(1 << 20, dtype=torch.uint8, device=dev)
+        del small
+    assert mon.peak_gb["big"] > mon.peak_gb["small"]
+    assert mon.peak_bytes() >= 64 << 20
+    assert mon.peak_bytes() / 2**30 >= mon.peak_gb["big"] - 1e-6
