@@ -27,6 +27,45 @@ static inline int rwkv_launch_status() {
   return e == cudaSuccess ? RWKV_OK : RWKV_ERR_CUDA_BASE + (int)e;
 }
 
+// ------------------------------------------------------------------------------------------------------------------
+// Chained launches (programmatic dependent launch).  A decode step is ~250 kernels of a few microseconds each, so the
+// gap between two kernels of the stream costs as much as the kernels.  When chaining is on (`rwkv_set_launch_chaining`,
+// switched on by the inference engine around its decode loop), the kernels of the decode path are launched with the
+// programmatic-stream-serialisation attribute: a kernel may be scheduled while its predecessor is still running, does
+// whatever does not depend on it, and `rwkv_chain_wait()` then blocks until the predecessor has completed and its
+// writes are visible.  Every chained kernel calls `rwkv_chain_begin()` (or `rwkv_chain_trigger()` then, later,
+// `rwkv_chain_wait()`) before its first global access, so the order of the stream is kept transitively.  Launched
+// the ordinary way the two instructions do nothing.
+__device__ __forceinline__ void rwkv_chain_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void rwkv_chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void rwkv_chain_begin() {
+  rwkv_chain_trigger();
+  rwkv_chain_wait();
+}
+inline int& rwkv_chain_flag() {
+  static int flag = 0;
+  return flag;
+}
+template <typename... KArgs, typename... Args>
+static inline void rwkv_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                               Args... args) {
+  if (!rwkv_chain_flag()) {
+    kernel<<<grid, block, smem, st>>>(args...);
+    return;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 __device__ __forceinline__ float bf16_lo(uint32_t packed) { return __uint_as_float(packed << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t packed) { return __uint_as_float(packed & 0xffff0000u); }
 

@@ -20,6 +20,7 @@ ln_shift_mix_fwd_kernel(const bf16* __restrict__ x, const float* __restrict__ ln
                         bf16* __restrict__ last, float* __restrict__ mean_out, float* __restrict__ rstd_out,
                         int B, int T, int C, int strip, float eps) {
   __shared__ float red[2 * EW_MAX_WARPS * 4];
+  rwkv_chain_begin();
   int phase = 0;
   const RowCtx rc = make_row_ctx(T, C, strip);
   const size_t row0 = (size_t)rc.b * T;
@@ -250,6 +251,7 @@ layer_norm_fwd_kernel(const bf16* __restrict__ x, const float* __restrict__ ln_w
                       bf16* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows,
                       int C, int strip, float eps) {
   __shared__ float red[2 * EW_MAX_WARPS * 4];
+  rwkv_chain_begin();
   int phase = 0;
   const int col = threadIdx.x * 8;
   const bool active = col < C;
@@ -896,9 +898,9 @@ RWKV_EXPORT int rwkv_ln_shift_mix_forward(const void* x, const void* ln_w, const
   const int nt = threads_for(C);
   cudaStream_t st = (cudaStream_t)stream;
 #define LAUNCH(KK)                                                                                              \
-  ln_shift_mix_fwd_kernel<KK><<<grid, nt, 0, st>>>((const bf16*)x, (const float*)ln_w, (const float*)ln_b,      \
-                                                   (const float*)mix, (const bf16*)prev, (bf16*)outs,           \
-                                                   (bf16*)last, (float*)mean, (float*)rstd, B, T, C, strip, eps)
+  rwkv_launch(ln_shift_mix_fwd_kernel<KK>, grid, dim3(nt), 0, st, (const bf16*)x, (const float*)ln_w,          \
+              (const float*)ln_b, (const float*)mix, (const bf16*)prev, (bf16*)outs, (bf16*)last, (float*)mean,  \
+              (float*)rstd, B, T, C, strip, eps)
   if (K == 6) LAUNCH(6);
   else if (K == 1) LAUNCH(1);
   else return RWKV_ERR_BAD_SHAPE;
@@ -961,9 +963,9 @@ RWKV_EXPORT int rwkv_ln_shift_mix_backward(const void* const* dO, const void* dl
 RWKV_EXPORT int rwkv_layer_norm_forward(const void* x, const void* ln_w, const void* ln_b, void* y, void* mean,
                                         void* rstd, int rows, int C, int strip, float eps, void* stream) {
   if (C % 8 || C / 8 > 512 || strip <= 0) return RWKV_ERR_BAD_SHAPE;
-  layer_norm_fwd_kernel<<<(rows + strip - 1) / strip, threads_for(C), 0, (cudaStream_t)stream>>>(
-      (const bf16*)x, (const float*)ln_w, (const float*)ln_b, (bf16*)y, (float*)mean, (float*)rstd, rows, C, strip,
-      eps);
+  rwkv_launch(layer_norm_fwd_kernel, dim3((rows + strip - 1) / strip), dim3(threads_for(C)), 0, (cudaStream_t)stream,
+              (const bf16*)x, (const float*)ln_w, (const float*)ln_b, (bf16*)y, (float*)mean, (float*)rstd, rows, C,
+              strip, eps);
   return rwkv_launch_status();
 }
 

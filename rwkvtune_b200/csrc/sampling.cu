@@ -88,6 +88,7 @@ sample_top_p_kernel(const T* __restrict__ logits, int V, int n_valid, float inv_
   __shared__ float scan[ST / 32];
   __shared__ int winner;
   __shared__ int amax;
+  rwkv_chain_begin();
   const int row = blockIdx.x, tid = threadIdx.x;
   const T* x = logits + (size_t)row * V;
   unsigned char* seen_row = nullptr;
@@ -265,11 +266,11 @@ RWKV_EXPORT int rwkv_sample_tokens(const void* logits, int is_bf16, int n, int V
   sa.update_seen = update_seen;
   cudaStream_t st = (cudaStream_t)stream;
   if (is_bf16)
-    sample_top_p_kernel<bf16><<<n, ST, 0, st>>>((const bf16*)logits, V, n_valid, inv_temp, top_p,
-                                                (unsigned long long)seed, (long long*)tokens, (float*)logps, sa);
+    rwkv_launch(sample_top_p_kernel<bf16>, dim3(n), dim3(ST), 0, st, (const bf16*)logits, V, n_valid, inv_temp, top_p,
+                (unsigned long long)seed, (long long*)tokens, (float*)logps, sa);
   else
-    sample_top_p_kernel<float><<<n, ST, 0, st>>>((const float*)logits, V, n_valid, inv_temp, top_p,
-                                                 (unsigned long long)seed, (long long*)tokens, (float*)logps, sa);
+    rwkv_launch(sample_top_p_kernel<float>, dim3(n), dim3(ST), 0, st, (const float*)logits, V, n_valid, inv_temp,
+                top_p, (unsigned long long)seed, (long long*)tokens, (float*)logps, sa);
   return rwkv_launch_status();
 }
 

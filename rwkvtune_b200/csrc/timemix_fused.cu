@@ -30,6 +30,7 @@ timemix_prep_fwd_kernel(const bf16* __restrict__ k, const bf16* __restrict__ v, 
                         const float* __restrict__ k_k, const float* __restrict__ k_a, bf16* __restrict__ w_out,
                         bf16* __restrict__ k_out, bf16* __restrict__ v_out, bf16* __restrict__ an_out,
                         bf16* __restrict__ b_out, int T, int C, int strip) {
+  rwkv_chain_begin();
   const RowCtx rc = make_row_ctx(T, C, strip);
   PrepParams p;
 #pragma unroll
@@ -196,6 +197,7 @@ gn_bonus_gate_fwd_kernel(const bf16* __restrict__ y, const bf16* __restrict__ r,
                          const bf16* __restrict__ v, const bf16* __restrict__ g, const float* __restrict__ gn_w,
                          const float* __restrict__ gn_b, const float* __restrict__ r_k, bf16* __restrict__ z, int T,
                          int C, int strip, float eps) {
+  rwkv_chain_begin();
   const RowCtx rc = make_row_ctx(T, C, strip);
   float gw[8] = {0, 0, 0, 0, 0, 0, 0, 0}, gb[8] = {0, 0, 0, 0, 0, 0, 0, 0}, rk[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   if (rc.active) { load8f(gn_w + rc.col, gw); load8f(gn_b + rc.col, gb); load8f(r_k + rc.col, rk); }
@@ -347,7 +349,7 @@ RWKV_EXPORT int rwkv_timemix_prep_forward(const void* k, const void* v, const vo
                                           int strip, void* stream) {
   if (!shape_ok(B, T, C, strip)) return RWKV_ERR_BAD_SHAPE;
   dim3 grid((T + strip - 1) / strip, B);
-  timemix_prep_fwd_kernel<<<grid, threads_for(C), 0, (cudaStream_t)stream>>>(
+  rwkv_launch(timemix_prep_fwd_kernel, grid, dim3(threads_for(C)), 0, (cudaStream_t)stream,
       (const bf16*)k, (const bf16*)v, (const bf16*)vfirst, (const bf16*)wlin, (const bf16*)alin, (const bf16*)vlin,
       (const float*)w0, (const float*)a0, (const float*)v0, (const float*)k_k, (const float*)k_a, (bf16*)w_out,
       (bf16*)k_out, (bf16*)v_out, (bf16*)an_out, (bf16*)b_out, T, C, strip);
@@ -375,7 +377,7 @@ RWKV_EXPORT int rwkv_gn_bonus_gate_forward(const void* y, const void* r, const v
                                            void* z, int B, int T, int C, int strip, float eps, void* stream) {
   if (!shape_ok(B, T, C, strip)) return RWKV_ERR_BAD_SHAPE;
   dim3 grid((T + strip - 1) / strip, B);
-  gn_bonus_gate_fwd_kernel<<<grid, threads_for(C), 0, (cudaStream_t)stream>>>(
+  rwkv_launch(gn_bonus_gate_fwd_kernel, grid, dim3(threads_for(C)), 0, (cudaStream_t)stream,
       (const bf16*)y, (const bf16*)r, (const bf16*)k, (const bf16*)v, (const bf16*)g, (const float*)gn_w,
       (const float*)gn_b, (const float*)r_k, (bf16*)z, T, C, strip, eps);
   return rwkv_launch_status();

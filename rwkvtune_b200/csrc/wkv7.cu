@@ -95,6 +95,7 @@ wkv7_fwd_kernel(const bf16* __restrict__ q_, const bf16* __restrict__ w_, const 
                 int T, int H) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   FwdSmem& sm = *reinterpret_cast<FwdSmem*>(smem_raw);
+  rwkv_chain_begin();
 
   const int h = blockIdx.x, bb = blockIdx.y;
   // state row of this sequence: its batch index, or its slot in a state pool (continuous batching keeps the
@@ -560,7 +561,7 @@ RWKV_EXPORT int rwkv_wkv7_forward(const void* q, const void* w, const void* k, c
     configured = true;
   }
   dim3 grid(H, B);
-  wkv7_fwd_kernel<<<grid, NTHREADS, sizeof(FwdSmem), (cudaStream_t)stream>>>(
+  rwkv_launch(wkv7_fwd_kernel, grid, dim3(NTHREADS), sizeof(FwdSmem), (cudaStream_t)stream,
       (const bf16*)q, (const bf16*)w, (const bf16*)k, (const bf16*)v, (const bf16*)a, (const bf16*)b,
       (const float*)s0, (bf16*)y, (float*)sa, (float*)ckpt, (float*)s_final, nullptr, T, H);
   return rwkv_launch_status();
@@ -580,7 +581,7 @@ RWKV_EXPORT int rwkv_wkv7_forward_slots(const void* q, const void* w, const void
     configured = true;
   }
   dim3 grid(H, B);
-  wkv7_fwd_kernel<<<grid, NTHREADS, sizeof(FwdSmem), (cudaStream_t)stream>>>(
+  rwkv_launch(wkv7_fwd_kernel, grid, dim3(NTHREADS), sizeof(FwdSmem), (cudaStream_t)stream,
       (const bf16*)q, (const bf16*)w, (const bf16*)k, (const bf16*)v, (const bf16*)a, (const bf16*)b,
       (const float*)pool, (bf16*)y, nullptr, nullptr, (float*)pool, (const long long*)slots, T, H);
   return rwkv_launch_status();

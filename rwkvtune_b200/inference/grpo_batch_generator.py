@@ -14,6 +14,7 @@ batch when more than half of the paths are done.
 """
 from __future__ import annotations
 
+import contextlib
 import time
 from typing import Any, Dict, List, Optional, Sequence
 
@@ -122,9 +123,13 @@ class GRPOBatchGenerator:
         return tuple([ops.gather_rows(t, index) for t in part] for part in state)
 
     def _forward(self, ids: torch.Tensor, state):
+        from ..ops import _ext
+
         att, wkv, ffn = state
-        x, a, s, f = self.model.forward_states(ids, att, wkv, ffn)
-        logits = self.model.head(x[:, -1, :])
+        # weights are constant for the whole rollout: the step's kernels can be launched as a dependent chain
+        with (_ext.launch_chaining() if ids.is_cuda and ids.shape[1] == 1 else contextlib.nullcontext()):
+            x, a, s, f = self.model.forward_states(ids, att, wkv, ffn)
+            logits = self.model.head(x[:, -1, :])
         return logits, (a, s, f)
 
     # ------------------------------------------------------------------ prefill

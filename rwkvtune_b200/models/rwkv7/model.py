@@ -149,22 +149,32 @@ class RWKV7TimeMix(nn.Module):
         """
         (xr, xw, xk, xv, xa, xg), last, x = ops.ln_shift_mix_unbound(x, ln_w, ln_b, self.mix_matrix(), x_prev)
 
+        v_lin = None
         if self._plain_projections() and x.is_cuda and not torch.is_grad_enabled():
-            r, k, v = ops.linear_group([xr, xk, xv], [self.receptance.weight, self.key.weight, self.value.weight])
+            # inference: the three projections and the first stages of the low-rank chains go out together
+            first = self.layer_id == 0
+            (r, k, v), low = ops.projections_with_lowrank(
+                [xr, xk, xv], [self.receptance.weight, self.key.weight, self.value.weight],
+                [xw, xa, xg] + ([] if first else [xv]), [self.w1, self.a1, self.g1] + ([] if first else [self.v1]),
+                ["tanh", None, "sigmoid"] + ([] if first else [None]),
+                [self.w2, self.a2, self.g2] + ([] if first else [self.v2]))
+            w_lin, a_lin, g = low[:3]
+            if not first:
+                v_lin = low[3]
         else:
             r = self.receptance(xr)
             k = self.key(xk)
             v = self.value(xv)
-        w_lin = ops.matmul(ops.matmul_act(xw, self.w1, "tanh"), self.w2)
-        a_lin = ops.matmul(ops.matmul(xa, self.a1), self.a2)
-        g = ops.matmul(ops.matmul_act(xg, self.g1, "sigmoid"), self.g2)
+            w_lin = ops.matmul(ops.matmul_act(xw, self.w1, "tanh"), self.w2)
+            a_lin = ops.matmul(ops.matmul(xa, self.a1), self.a2)
+            g = ops.matmul(ops.matmul_act(xg, self.g1, "sigmoid"), self.g2)
+            if self.layer_id != 0:
+                v_lin = ops.matmul(ops.matmul(xv, self.v1), self.v2)
         if self.layer_id == 0:
-            v_lin = None
             w, k, v, a_, b_ = ops.timemix_prep(k, v, None, w_lin, a_lin, None, self.w0, self.a0, None,
                                                self.k_k, self.k_a, self.head_size)
             v_first = v
         else:
-            v_lin = ops.matmul(ops.matmul(xv, self.v1), self.v2)
             w, k, v, a_, b_ = ops.timemix_prep(k, v, v_first, w_lin, a_lin, v_lin, self.w0, self.a0, self.v0,
                                                self.k_k, self.k_a, self.head_size)
 

@@ -126,6 +126,19 @@ def linear_group(xs, weights):
     return [torch.nn.functional.linear(x, w) for x, w in zip(xs, weights)]
 
 
+def projections_with_lowrank(lin_xs, lin_ws, lr_xs, lr_w1, lr_acts, lr_w2):
+    """``([x @ W^T ...], [act(x @ w1) @ w2 ...])``: the ``nn.Linear`` projections and the low-rank chains of a
+    time-mix block (``rwkvtune/models/rwkv7/model.py:146-160``).  ``lr_acts[i]`` is ``None``, ``"tanh"`` or
+    ``"sigmoid"``.  While decoding on CUDA the whole set is two grouped launches."""
+    if _native(lin_xs[0], "gemm"):
+        from . import gemm
+
+        return gemm.projections_with_lowrank(lin_xs, lin_ws, lr_xs, lr_w1, lr_acts, lr_w2)
+    act = {None: lambda t: t, "tanh": torch.tanh, "sigmoid": torch.sigmoid}
+    return ([torch.nn.functional.linear(x, w) for x, w in zip(lin_xs, lin_ws)],
+            [act[a](x @ w1) @ w2 for x, w1, a, w2 in zip(lr_xs, lr_w1, lr_acts, lr_w2)])
+
+
 def linear_relu_sq(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     """``relu(x @ weight^T) ** 2`` (channel-mix key projection); fused into the GEMM epilogue on CUDA."""
     if _native(x, "gemm") and _native(x, "relu_squared"):

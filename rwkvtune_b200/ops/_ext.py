@@ -107,6 +107,37 @@ def launch_count() -> int:
     return LAUNCH_COUNT
 
 
+# ------------------------------------------------------------------------------- chained launches
+import contextlib as _contextlib
+import os as _os
+
+_CHAINING = False
+CHAINING_ALLOWED = _os.environ.get("RWKVTUNE_CHAINED_LAUNCH", "1") == "1"
+
+
+def chaining() -> bool:
+    return _CHAINING
+
+
+@_contextlib.contextmanager
+def launch_chaining():
+    """Inside this context the kernels of the decode path are launched as a programmatic dependent chain: each may be
+    scheduled while its predecessor still runs and waits on the device for it before touching activations (see
+    ``csrc/common.cuh``).  The decode GEMM additionally streams its first weight tiles before that wait, so the
+    context must not enclose anything that writes model weights.  ``RWKVTUNE_CHAINED_LAUNCH=0`` turns it off."""
+    global _CHAINING
+    if not (CHAINING_ALLOWED and available() and hasattr(lib(), "rwkv_set_launch_chaining")) or _CHAINING:
+        yield
+        return
+    lib().rwkv_set_launch_chaining(ctypes.c_int(1))
+    _CHAINING = True
+    try:
+        yield
+    finally:
+        lib().rwkv_set_launch_chaining(ctypes.c_int(0))
+        _CHAINING = False
+
+
 def i32(v: int) -> ctypes.c_int:
     return ctypes.c_int(int(v))
 

@@ -690,6 +690,12 @@ def linear_relu_sq(x, weight):
     from . import gemm_native
 
     x2 = x.reshape(-1, x.shape[-1])
+    if not torch.is_grad_enabled():
+        from . import gemm
+
+        ys = gemm.decode_products([x], [weight], acts=["relu_sq"])
+        if ys is not None:
+            return ys[0]
     if x.dtype == BF16 and weight.dtype == BF16 and gemm_native.native_ok(x2 if x2.is_contiguous() else x2.contiguous(), weight, "nt"):
         return _LinearReluSq.apply(x, weight)
     return relu_squared(linear(x, weight))

@@ -32,11 +32,37 @@ def _native():
     return gemm_native
 
 
+def _decode(n) -> bool:
+    return n is not None and n.DECODE_DISPATCH
+
+
+def decode_products(xs, ws, acts=None, kn=None, residuals=None):
+    """``[act_i(x_i @ W_i) (+ residual_i)]`` as ONE launch of the decode GEMM, or ``None`` when the problems do not
+    qualify (more than 128 rows, autograd recording, CPU tensors, odd shapes): the caller then takes its usual path.
+    ``kn[i]`` marks a weight stored ``[in, out]``; ``acts[i]`` is ``None``, ``"relu_sq"``, ``"tanh"`` or ``"sigmoid"``."""
+    n = _native()
+    if not _decode(n) or torch.is_grad_enabled() or not 0 < len(xs) <= 8:
+        return None
+    kn = list(kn) if kn is not None else [False] * len(xs)
+    x2 = [x.reshape(-1, x.shape[-1]) for x in xs]
+    if any(a.shape[0] != x2[0].shape[0] for a in x2) or not all(n.decode_ok(a, w, t) for a, w, t in zip(x2, ws, kn)):
+        return None
+    r2 = None
+    if residuals is not None:
+        r2 = [None if r is None else r.reshape(-1, r.shape[-1]) for r in residuals]
+        for r, w, t in zip(r2, ws, kn):
+            if r is not None and not (r.dtype == torch.bfloat16 and r.is_contiguous() and r.data_ptr() % 8 == 0
+                                      and r.shape == (x2[0].shape[0], w.shape[1] if t else w.shape[0])):
+                return None
+    ys = n.decode_group(x2, list(ws), epis=acts, kn=kn, residuals=r2)
+    return [y.reshape(*x.shape[:-1], y.shape[-1]) for y, x in zip(ys, xs)]
+
+
 def mm_nt(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     n = _native()
     if n is not None:
-        if n.SMALL_M_DISPATCH and n.small_m_ok(x, w):
-            return n.small_m_group([x], [w])[0]
+        if n.DECODE_DISPATCH and n.decode_ok(x, w):
+            return n.decode_group([x], [w])[0]
         if n.native_ok(x, w, "nt"):
             return n.mm_nt(x, w)
     return x @ w.t()
@@ -45,20 +71,36 @@ def mm_nt(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
 def linear_group(xs, ws):
     """``[x_i @ w_i^T]`` for several independent projections with the same row count.  During decoding
     (few rows, no autograd) they go out as one grouped launch; otherwise one ``linear`` each."""
-    n = _native()
-    if (n is not None and n.SMALL_M_DISPATCH and not torch.is_grad_enabled() and len(xs) <= 8
-            and all(x.shape[:-1] == xs[0].shape[:-1] for x in xs)):
-        x2 = [x.reshape(-1, x.shape[-1]) for x in xs]
-        if all(n.small_m_ok(a, w) for a, w in zip(x2, ws)):
-            ys = n.small_m_group(x2, list(ws))
-            return [y.reshape(*x.shape[:-1], w.shape[0]) for y, x, w in zip(ys, xs, ws)]
+    ys = decode_products(xs, ws)
+    if ys is not None:
+        return ys
     return [linear(x, w) for x, w in zip(xs, ws)]
+
+
+def projections_with_lowrank(lin_xs, lin_ws, lr_xs, lr_w1, lr_acts, lr_w2):
+    """The projections of a time-mix block: ``[x @ W^T]`` for the ``nn.Linear`` weights ``lin_ws`` and
+    ``[act(x @ w1) @ w2]`` for the low-rank chains.  While decoding (few rows, no autograd) the linear maps and all
+    first stages are one grouped launch and all second stages another; otherwise one GEMM each."""
+    k = len(lin_xs)
+    first = decode_products(list(lin_xs) + list(lr_xs), list(lin_ws) + list(lr_w1),
+                            acts=[None] * k + list(lr_acts), kn=[False] * k + [True] * len(lr_xs))
+    if first is not None:
+        second = decode_products(first[k:], list(lr_w2), kn=[True] * len(lr_xs))
+        if second is not None:
+            return first[:k], second
+    lins = [linear(x, w) for x, w in zip(lin_xs, lin_ws)]
+    lows = [matmul(matmul_act(x, a, act) if act else matmul(x, a), b)
+            for x, a, act, b in zip(lr_xs, lr_w1, lr_acts, lr_w2)]
+    return lins, lows
 
 
 def mm_nn(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     n = _native()
-    if n is not None and n.native_ok(x, w, "nn"):
-        return n.mm_nn(x, w)
+    if n is not None:
+        if n.DECODE_DISPATCH and n.decode_ok(x, w, True):
+            return n.decode_group([x], [w], kn=[True])[0]
+        if n.native_ok(x, w, "nn"):
+            return n.mm_nn(x, w)
     return x @ w
 
 
@@ -139,7 +181,9 @@ class _LinearAdd(torch.autograd.Function):
         x2 = x.reshape(-1, x.shape[-1])
         r2 = residual.reshape(-1, residual.shape[-1])
         n = _native()
-        if _acc_ok(n, r2) and n.native_ok(x2, w, "nt"):
+        if _decode(n) and n.decode_ok(x2, w) and r2.dtype == torch.bfloat16 and r2.is_contiguous():
+            y = n.decode_group([x2], [w], residuals=[r2])[0]
+        elif _acc_ok(n, r2) and n.native_ok(x2, w, "nt"):
             y = n.mm_nt(x2, w, residual=r2)
         else:
             y = r2 + mm_nt(x2, w)
@@ -188,7 +232,9 @@ class _MatMulAct(torch.autograd.Function):
     def forward(ctx, x, w, act: str):
         x2 = x.reshape(-1, x.shape[-1])
         n = _native()
-        if n is not None and n.native_ok(x2, w, "nn"):
+        if _decode(n) and n.decode_ok(x2, w, True):
+            y = n.decode_group([x2], [w], epis=[act], kn=[True])[0]
+        elif n is not None and n.native_ok(x2, w, "nn"):
             y = n.mm_nn(x2, w, epilogue=3 if act == "tanh" else 4)
         else:
             y = torch.tanh(x2 @ w) if act == "tanh" else torch.sigmoid(x2 @ w)

@@ -279,3 +279,57 @@ def small_m_group(xs, ws, split_k=None):
               vp(*[t.data_ptr() for t in ys]), ip(*[w.shape[0] for w in ws]), ip(*[w.shape[1] for w in ws]),
               _ext.i32(n), _ext.i32(M), _ext.i32(split_k), _ext.ptr(scratch), _ext.ptr(ctr), _ext.stream())
     return ys
+
+
+# ------------------------------------------------------------------------------- decode GEMM (tcgen05, clusters)
+import os as _os
+
+DECODE_MAX_M = 128
+# The rollout path sends its projections here (``gemm_decode_tcgen05.cu``); RWKVTUNE_DECODE_GEMM=0 leaves them on
+# the library GEMM.
+DECODE_DISPATCH = _os.environ.get("RWKVTUNE_DECODE_GEMM", "1") == "1"
+DECODE_EPI = {None: 0, "none": 0, "relu_sq": 1, "tanh": 3, "sigmoid": 4}
+_HAS_DECODE = None
+
+
+def decode_available() -> bool:
+    global _HAS_DECODE
+    if _HAS_DECODE is None:
+        _HAS_DECODE = _ext.available() and hasattr(_ext.lib(), "rwkv_gemm_decode_tcgen05")
+    return _HAS_DECODE
+
+
+def decode_ok(x: torch.Tensor, w: torch.Tensor, kn: bool = False) -> bool:
+    """``x [M, K]`` times ``w`` (``[N, K]``, or ``[K, N]`` with ``kn``) with at most 128 rows: one grouped
+    weight-streaming launch (see ``gemm_decode_tcgen05.cu``)."""
+    if not (decode_available() and x.is_cuda and x.dim() == 2 and w.dim() == 2 and x.dtype == torch.bfloat16
+            and w.dtype == torch.bfloat16 and 0 < x.shape[0] <= DECODE_MAX_M and x.is_contiguous()
+            and w.is_contiguous() and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):
+        return False
+    K, N = (w.shape[0], w.shape[1]) if kn else (w.shape[1], w.shape[0])
+    return x.shape[1] == K and K % 8 == 0 and N % 8 == 0
+
+
+def decode_group(xs, ws, epis=None, kn=None, residuals=None, split: int = 0):
+    """``[act_i(x_i @ W_i) (+ residual_i)]`` for up to 8 problems sharing the row count, in one launch.
+    ``kn[i]`` marks a weight stored ``[K, N]``; ``epis[i]`` is one of ``DECODE_EPI``; a residual is a contiguous
+    ``[M, N_i]`` bf16 tensor."""
+    import ctypes
+
+    n = len(xs)
+    M = xs[0].shape[0]
+    kn = list(kn) if kn is not None else [False] * n
+    Ns = [w.shape[1] if t else w.shape[0] for w, t in zip(ws, kn)]
+    Ks = [w.shape[0] if t else w.shape[1] for w, t in zip(ws, kn)]
+    ys = [torch.empty(M, N, dtype=torch.bfloat16, device=xs[0].device) for N in Ns]
+    vp = ctypes.c_void_p * n
+    ip = ctypes.c_int * n
+    res = None
+    if residuals is not None and any(r is not None for r in residuals):
+        res = vp(*[(r.data_ptr() if r is not None else None) for r in residuals])
+    codes = ip(*[DECODE_EPI[e] for e in (epis if epis is not None else [None] * n)])
+    _ext.call("rwkv_gemm_decode_tcgen05", vp(*[t.data_ptr() for t in xs]), vp(*[t.data_ptr() for t in ws]),
+              vp(*[t.data_ptr() for t in ys]), res, ip(*Ns), ip(*Ks), codes, ip(*[int(t) for t in kn]), _ext.i32(n),
+              _ext.i32(M), _ext.i32(split), _ext.i32(1 if _ext.chaining() else 0), _ext.ptr(_status(xs[0].device)),
+              _ext.stream())
+    return ys

@@ -673,6 +673,50 @@ def test_small_m_grouped_gemm(M):
         assert torch.allclose(o.float(), y.float(), atol=2e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("M", [1, 7, 64, 100, 128])
+def test_decode_grouped_gemm(M):
+    """Cluster split-K decode GEMM: both weight layouts, ragged N and K, every epilogue, residual add, every split."""
+    from rwkvtune_b200.ops import gemm_native
+    torch.manual_seed(M)
+    # (N, K, weight stored [K, N], epilogue, residual)
+    probs = [(256, 512, False, None, False), (1024, 512, False, "relu_sq", True), (72, 2048, True, "tanh", False),
+             (512, 96, True, None, True), (200, 264, False, "sigmoid", False), (2048, 64, True, None, False)]
+    xs = [(torch.randn(M, K, device="cuda") * 0.5).to(BF) for _, K, *_ in probs]
+    ws = [((torch.randn(K, N, device="cuda") if kn else torch.randn(N, K, device="cuda")) * 0.05).to(BF)
+          for N, K, kn, _, _ in probs]
+    res = [torch.randn(M, N, device="cuda").to(BF) if r else None for N, _, _, _, r in probs]
+    kn = [p[2] for p in probs]
+    epis = [p[3] for p in probs]
+    assert all(gemm_native.decode_ok(x, w, t) for x, w, t in zip(xs, ws, kn))
+    act = {None: lambda t: t, "relu_sq": lambda t: torch.relu(t) ** 2, "tanh": torch.tanh, "sigmoid": torch.sigmoid}
+    refs = []
+    for x, w, t, e, r in zip(xs, ws, kn, epis, res):
+        y = act[e](x.float() @ (w.float() if t else w.float().t()))
+        refs.append(y + r.float() if r is not None else y)
+    first = None
+    for split in (0, 1, 2, 4, 8):
+        ys = gemm_native.decode_group(xs, ws, epis=epis, kn=kn, residuals=res, split=split)
+        for y, ref_y in zip(ys, refs):
+            assert (y.float() - ref_y).abs().max().item() <= 1e-2 * ref_y.abs().max().item() + 1e-2, split
+        if split == 0:
+            first = ys
+    again = gemm_native.decode_group(xs, ws, epis=epis, kn=kn, residuals=res)
+    for a, b in zip(first, again):
+        assert torch.equal(a, b)          # fixed summation order: bit-reproducible
+    assert gemm_native.check_status() == 0
+
+
+def test_decode_gemm_residual_in_place():
+    from rwkvtune_b200.ops import gemm_native
+    torch.manual_seed(5)
+    x = (torch.randn(64, 2048, device="cuda") * 0.5).to(BF)
+    w = (torch.randn(2048, 2048, device="cuda") * 0.03).to(BF)
+    r = torch.randn(64, 2048, device="cuda").to(BF)
+    (y,) = gemm_native.decode_group([x], [w], residuals=[r])
+    ref_y = x.float() @ w.float().t() + r.float()
+    assert (y.float() - ref_y).abs().max().item() <= 1e-2 * ref_y.abs().max().item() + 1e-2
+
+
 @pytest.mark.parametrize("layout", ["nt", "nn"])
 def test_gemm_accumulate_epilogue(layout):
     from rwkvtune_b200.ops import gemm
