@@ -416,14 +416,21 @@ RWKV_EXPORT int rwkv_gemm_decode_tcgen05(const void* const* xs, const void* cons
   cfg.dynamicSmemBytes = smem;
   cfg.stream = (cudaStream_t)stream;
   cudaLaunchAttribute attr[2];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 1;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = split;
-  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  int n_attr = 0;
+  if (split > 1) {   // a single K slice needs no cluster (the kernel's cluster barriers are then CTA-local)
+    attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+    attr[n_attr].val.clusterDim.x = 1;
+    attr[n_attr].val.clusterDim.y = 1;
+    attr[n_attr].val.clusterDim.z = split;
+    ++n_attr;
+  }
+  if (rwkv_chain_flag()) {
+    attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+    ++n_attr;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = rwkv_chain_flag() ? 2 : 1;
+  cfg.numAttrs = n_attr;
   cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_decode_kernel, prm);
   return e == cudaSuccess ? rwkv_launch_status() : RWKV_ERR_CUDA_BASE + (int)e;
 }

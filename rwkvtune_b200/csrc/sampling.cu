@@ -2,11 +2,11 @@
 // seen), banned ids, temperature, additive logit bias, top-k, top-p, the draw (or the arg-max when greedy), the
 // token's log-probability and the update of the seen-bitmap, in one kernel.
 //
-// One 1024-thread CTA per row; each thread keeps up to 64 probabilities in registers
+// One 1024-thread CTA per row; each thread keeps up to 64 probabilities, 24 in registers and 40 in shared memory
 // (V <= 65536).  The nucleus is "the sorted prefix whose cumulative mass is <= top_p, plus
 // always the most likely token" -- i.e. token i is kept iff the mass of all tokens at least as
 // likely as i is <= top_p.  That set is {p >= theta*} for a threshold found by bisection on
-// theta (each probe is one register pass + one block reduction), so no sort, no cumsum and no
+// theta (each probe is one pass over registers and shared memory + one block reduction), so no sort, no cumsum and no
 // scatter is needed.  The draw is an inverse-CDF walk over the kept tokens in index order with a
 // Philox4x32-10 uniform keyed by (seed, row).  Replaces the full 65536-way sort + cumsum +
 // unsort + softmax + multinomial sequence of the reference
@@ -20,6 +20,8 @@ namespace {
 
 constexpr int ST = 1024;       // threads per row
 constexpr int SPT = 64;        // values per thread
+constexpr int SPT_REG = 24;    // of which in registers; the rest in shared memory (160 KB)
+constexpr int SAMPLE_SMEM = (SPT - SPT_REG) * ST * 4;
 
 __device__ __forceinline__ uint2 mulhilo(uint32_t a, uint32_t b) {
   const unsigned long long p = (unsigned long long)a * b;
@@ -79,6 +81,14 @@ __device__ __forceinline__ uint32_t order_key(float v) {
   return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
+#define PGET(j) ((j) < SPT_REG ? p_reg[(j) < SPT_REG ? (j) : 0] : p_sh[((j) - SPT_REG) * ST + tid])
+#define PSET(j, v)                                         \
+  do {                                                     \
+    const float pset_v_ = (v);                             \
+    if ((j) < SPT_REG) p_reg[(j) < SPT_REG ? (j) : 0] = pset_v_; \
+    else p_sh[((j) - SPT_REG) * ST + tid] = pset_v_;       \
+  } while (0)
+
 template <typename T>
 __global__ void __launch_bounds__(ST)
 sample_top_p_kernel(const T* __restrict__ logits, int V, int n_valid, float inv_temp, float top_p,
@@ -97,7 +107,11 @@ sample_top_p_kernel(const T* __restrict__ logits, int V, int n_valid, float inv_
   const float inv_pen = penalise ? 1.f / sa.penalty : 1.f;
   const float scale = sa.greedy ? 1.f : inv_temp;
 
-  float p[SPT];
+  // half of the row's values live in registers, half in shared memory (column j of thread tid at [j][tid]: conflict-
+  // free): 64 registers per thread are all a 1024-thread CTA can have, and values spilled to local memory made
+  // every pass of the searches below a trip through L1/L2
+  extern __shared__ float p_sh[];
+  float p_reg[SPT_REG];
   float mx = -INFINITY;
 #pragma unroll
   for (int j = 0; j < SPT; ++j) {
@@ -111,7 +125,7 @@ sample_top_p_kernel(const T* __restrict__ logits, int V, int n_valid, float inv_
       if (sa.bias) v += sa.bias[i];
       if (!(v == v)) v = -INFINITY;   // NaN logits are never sampled
     }
-    p[j] = v;
+    PSET(j, v);
     mx = fmaxf(mx, v);
   }
   mx = block_reduce_max(mx, red);
@@ -121,8 +135,8 @@ sample_top_p_kernel(const T* __restrict__ logits, int V, int n_valid, float inv_
     float zg = 0.f;
 #pragma unroll
     for (int j = 0; j < SPT; ++j) {
-      if (p[j] == mx) atomicMin(&amax, tid + j * ST);
-      zg += (p[j] == -INFINITY) ? 0.f : __expf(p[j] - mx);
+      if (PGET(j) == mx) atomicMin(&amax, tid + j * ST);
+      zg += (PGET(j) == -INFINITY) ? 0.f : __expf(PGET(j) - mx);
     }
     zg = block_reduce_sum(zg, red);
     if (tid == 0) {
@@ -138,33 +152,33 @@ sample_top_p_kernel(const T* __restrict__ logits, int V, int n_valid, float inv_
       const uint32_t cand = prefix | (1u << bit);
       float cnt = 0.f;
 #pragma unroll
-      for (int j = 0; j < SPT; ++j) cnt += (order_key(p[j]) >= cand) ? 1.f : 0.f;
+      for (int j = 0; j < SPT; ++j) cnt += (order_key(PGET(j)) >= cand) ? 1.f : 0.f;
       cnt = block_reduce_sum(cnt, red);
       if (cnt >= (float)sa.top_k) prefix = cand;
     }
 #pragma unroll
     for (int j = 0; j < SPT; ++j)
-      if (order_key(p[j]) < prefix) p[j] = -INFINITY;
+      if (order_key(PGET(j)) < prefix) PSET(j, -INFINITY);
   }
   float z = 0.f;
 #pragma unroll
   for (int j = 0; j < SPT; ++j) {
-    p[j] = (p[j] == -INFINITY) ? 0.f : __expf(p[j] - mx);
-    z += p[j];
+    PSET(j, (PGET(j) == -INFINITY) ? 0.f : __expf(PGET(j) - mx));
+    z += PGET(j);
   }
   z = block_reduce_sum(z, red);
   const float inv_z = 1.f / z;
   float pmax = 0.f;
 #pragma unroll
   for (int j = 0; j < SPT; ++j) {
-    p[j] *= inv_z;
-    pmax = fmaxf(pmax, p[j]);
+    PSET(j, PGET(j) * (inv_z));
+    pmax = fmaxf(pmax, PGET(j));
   }
   if (tid == 0) amax = 0x7fffffff;
   pmax = block_reduce_max(pmax, red);
 #pragma unroll
   for (int j = 0; j < SPT; ++j)
-    if (p[j] == pmax) atomicMin(&amax, tid + j * ST);
+    if (PGET(j) == pmax) atomicMin(&amax, tid + j * ST);
 
   // bisection for the smallest theta with mass({p >= theta}) <= top_p
   float theta = 0.f;
@@ -172,7 +186,7 @@ sample_top_p_kernel(const T* __restrict__ logits, int V, int n_valid, float inv_
     float lo = 0.f, hi = pmax;          // mass(lo) > top_p (or lo == 0), mass(hi) may or may not qualify
     float m_hi = 0.f;
 #pragma unroll
-    for (int j = 0; j < SPT; ++j) m_hi += (p[j] >= hi) ? p[j] : 0.f;
+    for (int j = 0; j < SPT; ++j) m_hi += (PGET(j) >= hi) ? PGET(j) : 0.f;
     m_hi = block_reduce_sum(m_hi, red);
     if (m_hi > top_p) {
       theta = pmax;                      // even the top token alone exceeds top_p: keep just it
@@ -181,7 +195,7 @@ sample_top_p_kernel(const T* __restrict__ logits, int V, int n_valid, float inv_
         const float mid = 0.5f * (lo + hi);
         float m = 0.f;
 #pragma unroll
-        for (int j = 0; j < SPT; ++j) m += (p[j] >= mid) ? p[j] : 0.f;
+        for (int j = 0; j < SPT; ++j) m += (PGET(j) >= mid) ? PGET(j) : 0.f;
         m = block_reduce_sum(m, red);
         if (m <= top_p) hi = mid; else lo = mid;
       }
@@ -191,7 +205,7 @@ sample_top_p_kernel(const T* __restrict__ logits, int V, int n_valid, float inv_
 
   float kept = 0.f;
 #pragma unroll
-  for (int j = 0; j < SPT; ++j) kept += (p[j] >= theta && p[j] > 0.f) ? p[j] : 0.f;
+  for (int j = 0; j < SPT; ++j) kept += (PGET(j) >= theta && PGET(j) > 0.f) ? PGET(j) : 0.f;
   // block-wide exclusive scan of the per-thread kept mass
   const int lane = tid & 31, warp = tid >> 5;
   float incl = kept;
@@ -221,17 +235,17 @@ sample_top_p_kernel(const T* __restrict__ logits, int V, int n_valid, float inv_
     int pick = -1;
 #pragma unroll
     for (int j = 0; j < SPT; ++j) {
-      if (p[j] >= theta && p[j] > 0.f) {
+      if (PGET(j) >= theta && PGET(j) > 0.f) {
         if (pick < 0) pick = j;          // first kept value as a floor
         if (u >= acc) pick = j;
-        acc += p[j];
+        acc += PGET(j);
       }
     }
     atomicMax(&winner, tid + pick * ST);
     // the token's log-probability under the renormalised nucleus
     float pv = 0.f;
 #pragma unroll
-    for (int j = 0; j < SPT; ++j) if (j == pick) pv = p[j];
+    for (int j = 0; j < SPT; ++j) if (j == pick) pv = PGET(j);
     logps[row] = __logf(pv / total);
   }
   __syncthreads();
@@ -244,6 +258,9 @@ sample_top_p_kernel(const T* __restrict__ logits, int V, int n_valid, float inv_
     if (sa.update_seen && seen_row) seen_row[winner] = 1;
   }
 }
+
+#undef PGET
+#undef PSET
 
 }  // namespace
 
@@ -265,11 +282,18 @@ RWKV_EXPORT int rwkv_sample_tokens(const void* logits, int is_bf16, int n, int V
   sa.greedy = greedy;
   sa.update_seen = update_seen;
   cudaStream_t st = (cudaStream_t)stream;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e1 = cudaFuncSetAttribute(sample_top_p_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, SAMPLE_SMEM);
+    cudaError_t e2 = cudaFuncSetAttribute(sample_top_p_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, SAMPLE_SMEM);
+    if (e1 != cudaSuccess || e2 != cudaSuccess) return RWKV_ERR_CUDA_BASE + (int)(e1 != cudaSuccess ? e1 : e2);
+    configured = true;
+  }
   if (is_bf16)
-    rwkv_launch(sample_top_p_kernel<bf16>, dim3(n), dim3(ST), 0, st, (const bf16*)logits, V, n_valid, inv_temp, top_p,
+    rwkv_launch(sample_top_p_kernel<bf16>, dim3(n), dim3(ST), SAMPLE_SMEM, st, (const bf16*)logits, V, n_valid, inv_temp, top_p,
                 (unsigned long long)seed, (long long*)tokens, (float*)logps, sa);
   else
-    rwkv_launch(sample_top_p_kernel<float>, dim3(n), dim3(ST), 0, st, (const float*)logits, V, n_valid, inv_temp,
+    rwkv_launch(sample_top_p_kernel<float>, dim3(n), dim3(ST), SAMPLE_SMEM, st, (const float*)logits, V, n_valid, inv_temp,
                 top_p, (unsigned long long)seed, (long long*)tokens, (float*)logps, sa);
   return rwkv_launch_status();
 }
