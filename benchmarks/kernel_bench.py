@@ -182,24 +182,20 @@ def _graph_time(fn):
 
 
 def bench_decode_gemm(C, out, hbm, M=64):
-    """Weight-streaming projections at decode batch sizes: small-M kernel vs the library GEMM.  Each timed replay
+    """Weight-streaming projections at decode batch sizes: the decode GEMM vs the library GEMM.  Each timed replay
     cycles through enough distinct weight matrices (> L2) that weights come from HBM as in a decode step."""
     from rwkvtune_b200.ops import gemm_native
     for name, (K, N) in {"CxC": (C, C), "Cx4C": (C, 4 * C), "4CxC": (4 * C, C)}.items():
         n_w = max(4, int(256e6 // (N * K * 2)) + 1)
         ws = [torch.randn(N, K, device="cuda").to(BF) for _ in range(n_w)]
         x = torch.randn(M, K, device="cuda").to(BF)
-        for tag, fn in (("small_m", lambda w: gemm_native.small_m_group([x], [w])),
-                        ("tcgen05_cluster", lambda w: gemm_native.decode_group([x], [w])),
+        for tag, fn in (("tcgen05_cluster", lambda w: gemm_native.decode_group([x], [w])),
                         ("cublas", lambda w: x @ w.t())):
             ms = _graph_time(lambda: [fn(w) for w in ws]) / n_w
             out[f"decode_gemm_M{M}_{name}_{tag}_us"] = ms * 1e3
             out[f"decode_gemm_M{M}_{name}_{tag}_frac_hbm"] = N * K * 2 / ms / 1e6 / hbm
     ws = [torch.randn(C, C, device="cuda").to(BF) for _ in range(48)]
     xs = [torch.randn(M, C, device="cuda").to(BF) for _ in range(3)]
-    ms = _graph_time(lambda: [gemm_native.small_m_group(xs, ws[i:i + 3]) for i in range(0, 48, 3)]) / 16
-    out[f"decode_gemm_M{M}_3xCxC_grouped_us"] = ms * 1e3
-    out[f"decode_gemm_M{M}_3xCxC_grouped_frac_hbm"] = 3 * C * C * 2 / ms / 1e6 / hbm
     ms = _graph_time(lambda: [gemm_native.decode_group(xs, ws[i:i + 3]) for i in range(0, 48, 3)]) / 16
     out[f"decode_gemm_M{M}_3xCxC_tcgen05_cluster_us"] = ms * 1e3
     out[f"decode_gemm_M{M}_3xCxC_tcgen05_cluster_frac_hbm"] = 3 * C * C * 2 / ms / 1e6 / hbm

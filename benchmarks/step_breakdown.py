@@ -29,7 +29,7 @@ sys.path.insert(0, ROOT)
 
 FAMILIES = [
     ("gemm (tcgen05)", r"gemm_tcgen05|splitk_reduce"),
-    ("gemm (small-M)", r"gemm_small_m"),
+    ("gemm (decode)", r"gemm_decode"),
     ("gemm (library)", r"nvjet|cutlass|cublas|gemm|xmma|sm100_|sm90_"),
     ("wkv7 prep", r"wkv7_tc_prep"),
     ("wkv7 scan fwd", r"wkv7_tc_scan"),

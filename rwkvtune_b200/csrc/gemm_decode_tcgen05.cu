@@ -53,6 +53,7 @@ struct alignas(64) DecodeParams {
   int count, M, Mpad, stages, tmem_cols;
   int prefetch;     // weights are not written by any kernel of the chain: stream them before the chain wait
   int* status;
+  unsigned long long* trace;   // optional [CTAs][16] globaltimer stamps of the phases of every CTA (null: off)
 };
 
 struct DBarriers {
@@ -165,6 +166,15 @@ __device__ __forceinline__ float d_act(float x, int epi) {
   return x;
 }
 
+// phase stamps for `benchmarks/decode_gemm_timeline.py`: 0 CTA started, 1 barriers armed and tensor memory allocated,
+// 2 predecessor kernel complete (chain wait returned), 3 first ring stage landed, 4 last ring stage landed,
+// 5 accumulator complete, 6 partial tile in shared memory, 7 cluster barrier passed, 8 rows summed and stored,
+// 9 tensor memory released
+#define D_STAMP(i)                                                                                              \
+  do {                                                                                                          \
+    if (prm.trace) prm.trace[((size_t)blockIdx.z * gridDim.x + blockIdx.x) * 16 + (i)] = d_globaltimer_ns();    \
+  } while (0)
+
 __global__ void __launch_bounds__(D_THREADS)
 gemm_decode_kernel(const __grid_constant__ DecodeParams prm) {
   extern __shared__ unsigned char smem_dyn[];
@@ -174,6 +184,7 @@ gemm_decode_kernel(const __grid_constant__ DecodeParams prm) {
   unsigned char* base_ptr = smem_dyn + (base - raw);
 
   rwkv_chain_trigger();
+  if (threadIdx.x == 0) D_STAMP(0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int S = (int)gridDim.z, z = (int)blockIdx.z;       // cluster = the S CTAs with the same blockIdx.x
   int pi = 0;
@@ -204,6 +215,7 @@ gemm_decode_kernel(const __grid_constant__ DecodeParams prm) {
   __syncthreads();
   d_fence_after();
   const uint32_t tmem_base = bars.tmem_base;
+  if (threadIdx.x == 0) D_STAMP(1);
   // everything that reads activations or writes results comes after the predecessor kernel has completed; the
   // producer thread decides for itself (it may start the weight stream first)
   if (threadIdx.x != 0) rwkv_chain_wait();
@@ -226,6 +238,7 @@ gemm_decode_kernel(const __grid_constant__ DecodeParams prm) {
         }
       }
       rwkv_chain_wait();
+      D_STAMP(2);
       for (int i = 0; i < pre; ++i)
         d_tma_load_2d(base + i * stage_bytes + W_BYTES, &P.map_x, &bars.full[i], (kb_lo + i) * DK, 0);
       int stage = pre == stages ? 0 : pre;
@@ -255,6 +268,8 @@ gemm_decode_kernel(const __grid_constant__ DecodeParams prm) {
       bool ok = true;
       for (int kb = kb_lo; kb < kb_hi; ++kb) {
         if (!d_mbar_wait(&bars.full[stage], phase, &bars, status, 203)) { ok = false; break; }
+        if (kb == kb_lo) D_STAMP(3);
+        if (kb == kb_hi - 1) D_STAMP(4);
         d_fence_after();
         const uint32_t sw = base + stage * stage_bytes, sx = sw + W_BYTES;
         const uint64_t adesc = d_smem_desc(sw, a_lbo);
@@ -276,6 +291,7 @@ gemm_decode_kernel(const __grid_constant__ DecodeParams prm) {
     bool have = kb_hi > kb_lo;
     if (have) have = d_mbar_wait(&bars.acc_full, 0, &bars, status, 204);
     have = __all_sync(0xffffffffu, have);
+    if (threadIdx.x == 64) D_STAMP(5);
     // the four warps start overwriting the ring only when all of them know the MMAs are done (or that none ran)
     asm volatile("bar.sync 1, 128;" ::: "memory");
     d_fence_after();
@@ -293,9 +309,11 @@ gemm_decode_kernel(const __grid_constant__ DecodeParams prm) {
       for (int i = 0; i < 16; ++i) Pm[(c + i) * DN + n] = __uint_as_float(v[i]);
     }
     d_fence_before();
+    if (threadIdx.x == 64) D_STAMP(6);
   }
 
   d_cluster_sync();   // every CTA's partial tile is in its shared memory
+  if (threadIdx.x == 64) D_STAMP(7);
 
   if (warp >= 2) {
     // ---------------------------------------------------------------------------------- cluster reduction + store
@@ -328,11 +346,13 @@ gemm_decode_kernel(const __grid_constant__ DecodeParams prm) {
     }
   }
 
+  if (threadIdx.x == 64) D_STAMP(8);
   d_cluster_sync();   // nobody leaves while a peer may still read its partial tile
   __syncthreads();
   if (warp == 1) {
     d_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(prm.tmem_cols));
+    if (lane == 0) D_STAMP(9);
   }
 }
 
@@ -344,10 +364,12 @@ gemm_decode_kernel(const __grid_constant__ DecodeParams prm) {
 // Every N_i a multiple of 8, every K_i a multiple of 8, all pointers 16-byte aligned.  split: K slices per column
 // tile (1, 2, 4 or 8), 0 = choose.  prefetch_weights: with chained launches, request weight tiles before the
 // predecessor kernel has finished (only when no kernel in flight writes any of the weights).  status: device int, set non-zero if a device-side wait ran out.
-RWKV_EXPORT int rwkv_gemm_decode_tcgen05(const void* const* xs, const void* const* ws, void* const* ys,
-                                         const void* const* residuals, const int* Ns, const int* Ks, const int* epis,
-                                         const int* w_kn, int count, int M, int split, int prefetch_weights, void* status,
-                                         void* stream) {
+// trace: optional device buffer of 16 x (number of CTAs) uint64, zeroed by the caller: globaltimer stamps of the phases of
+// every CTA (see D_STAMP), for benchmarks/decode_gemm_timeline.py.
+RWKV_EXPORT int rwkv_gemm_decode_tcgen05_traced(const void* const* xs, const void* const* ws, void* const* ys,
+                                                const void* const* residuals, const int* Ns, const int* Ks,
+                                                const int* epis, const int* w_kn, int count, int M, int split,
+                                                int prefetch_weights, void* status, void* stream, void* trace) {
   if (count <= 0 || count > D_MAX_PROBLEMS || M <= 0 || M > D_MAX_M) return RWKV_ERR_BAD_SHAPE;
   if (split != 0 && split != 1 && split != 2 && split != 4 && split != 8) return RWKV_ERR_BAD_SHAPE;
   DecodeParams prm;
@@ -357,6 +379,7 @@ RWKV_EXPORT int rwkv_gemm_decode_tcgen05(const void* const* xs, const void* cons
   prm.M = M;
   prm.Mpad = Mpad;
   prm.status = (int*)status;
+  prm.trace = (unsigned long long*)trace;
   prm.prefetch = prefetch_weights ? 1 : 0;
   int cols = 32;
   while (cols < Mpad) cols *= 2;
@@ -433,6 +456,14 @@ RWKV_EXPORT int rwkv_gemm_decode_tcgen05(const void* const* xs, const void* cons
   cfg.numAttrs = n_attr;
   cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_decode_kernel, prm);
   return e == cudaSuccess ? rwkv_launch_status() : RWKV_ERR_CUDA_BASE + (int)e;
+}
+
+RWKV_EXPORT int rwkv_gemm_decode_tcgen05(const void* const* xs, const void* const* ws, void* const* ys,
+                                         const void* const* residuals, const int* Ns, const int* Ks, const int* epis,
+                                         const int* w_kn, int count, int M, int split, int prefetch_weights, void* status,
+                                         void* stream) {
+  return rwkv_gemm_decode_tcgen05_traced(xs, ws, ys, residuals, Ns, Ks, epis, w_kn, count, M, split, prefetch_weights,
+                                         status, stream, nullptr);
 }
 
 // Chained launches for the kernels of the decode path (see common.cuh): 1 = on, 0 = off.  Returns the previous value.

@@ -230,57 +230,6 @@ def ag_mm_nt(x: torch.Tensor, gw: GatheredWeight) -> torch.Tensor:
     return y
 
 
-# ------------------------------------------------------------------------------- small-M (decode) GEMM
-SMALL_M_MAX = 256
-# Measured on B200 at M = 64 (CUDA-graph replay, weights from HBM): 14.8 / 25.0 / 30.5 us for the CxC / Cx4C /
-# 4CxC projections of the 1.5B model against 5.4 / 9.3 / 13.9 us for the library GEMM, so the dispatcher leaves
-# decode-sized products on the library until this kernel wins; ``small_m_group`` stays callable for tests and
-# benchmarks.
-SMALL_M_DISPATCH = False
-_SMALL_WS = {}
-
-
-def small_m_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
-    """``x [M,K] @ w[N,K]^T`` with few rows: one grouped weight-streaming launch (see ``gemm_small_m.cu``)."""
-    return (available() and x.is_cuda and x.dim() == 2 and w.dim() == 2 and x.dtype == torch.bfloat16
-            and w.dtype == torch.bfloat16 and 0 < x.shape[0] <= SMALL_M_MAX and w.shape[0] % 2 == 0
-            and x.shape[1] % 8 == 0 and x.is_contiguous() and w.is_contiguous()
-            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
-
-
-def _small_workspace(device, floats: int, counters: int):
-    """Persistent split-K scratch per device.  The kernel leaves it zeroed, so it is cleared only when (re)allocated."""
-    key = (device.type, device.index)
-    ws, ctr = _SMALL_WS.get(key, (None, None))
-    if ws is None or ws.numel() < floats or ctr.numel() < counters:
-        ws = torch.zeros(max(floats, 1 << 22), dtype=torch.float32, device=device)
-        ctr = torch.zeros(max(counters, 4096), dtype=torch.int32, device=device)
-        _SMALL_WS[key] = (ws, ctr)
-    return ws, ctr
-
-
-def small_m_group(xs, ws, split_k=None):
-    """``[x_i @ w_i^T]`` for up to 8 ``(x_i [M,K_i], w_i [N_i,K_i])`` pairs sharing ``M``, in one launch."""
-    import ctypes
-
-    n = len(xs)
-    M = xs[0].shape[0]
-    ys = [torch.empty(M, w.shape[0], dtype=torch.bfloat16, device=x.device) for x, w in zip(xs, ws)]
-    tiles = sum(-(-w.shape[0] // 64) for w in ws) * -(-M // 64)
-    if split_k is None:   # enough CTAs for the 148 SMs, at least two 128-wide K blocks each
-        kmin = min(w.shape[1] for w in ws)
-        split_k = max(1, min(-(-148 // tiles), kmin // 256, 16))
-    scratch = ctr = None
-    if split_k > 1:
-        scratch, ctr = _small_workspace(xs[0].device, sum(M * w.shape[0] for w in ws), tiles)
-    vp = ctypes.c_void_p * n
-    ip = ctypes.c_int * n
-    _ext.call("rwkv_gemm_small_m", vp(*[t.data_ptr() for t in xs]), vp(*[t.data_ptr() for t in ws]),
-              vp(*[t.data_ptr() for t in ys]), ip(*[w.shape[0] for w in ws]), ip(*[w.shape[1] for w in ws]),
-              _ext.i32(n), _ext.i32(M), _ext.i32(split_k), _ext.ptr(scratch), _ext.ptr(ctr), _ext.stream())
-    return ys
-
-
 # ------------------------------------------------------------------------------- decode GEMM (tcgen05, clusters)
 import os as _os
 
@@ -310,10 +259,11 @@ def decode_ok(x: torch.Tensor, w: torch.Tensor, kn: bool = False) -> bool:
     return x.shape[1] == K and K % 8 == 0 and N % 8 == 0
 
 
-def decode_group(xs, ws, epis=None, kn=None, residuals=None, split: int = 0):
+def decode_group(xs, ws, epis=None, kn=None, residuals=None, split: int = 0, trace=None):
     """``[act_i(x_i @ W_i) (+ residual_i)]`` for up to 8 problems sharing the row count, in one launch.
     ``kn[i]`` marks a weight stored ``[K, N]``; ``epis[i]`` is one of ``DECODE_EPI``; a residual is a contiguous
-    ``[M, N_i]`` bf16 tensor."""
+    ``[M, N_i]`` bf16 tensor.  ``trace``: optional zeroed int64 CUDA tensor of at least 16 x (number of CTAs) entries that
+    receives the per-CTA phase time stamps (``benchmarks/decode_gemm_timeline.py``)."""
     import ctypes
 
     n = len(xs)
@@ -328,8 +278,11 @@ def decode_group(xs, ws, epis=None, kn=None, residuals=None, split: int = 0):
     if residuals is not None and any(r is not None for r in residuals):
         res = vp(*[(r.data_ptr() if r is not None else None) for r in residuals])
     codes = ip(*[DECODE_EPI[e] for e in (epis if epis is not None else [None] * n)])
-    _ext.call("rwkv_gemm_decode_tcgen05", vp(*[t.data_ptr() for t in xs]), vp(*[t.data_ptr() for t in ws]),
-              vp(*[t.data_ptr() for t in ys]), res, ip(*Ns), ip(*Ks), codes, ip(*[int(t) for t in kn]), _ext.i32(n),
-              _ext.i32(M), _ext.i32(split), _ext.i32(1 if _ext.chaining() else 0), _ext.ptr(_status(xs[0].device)),
-              _ext.stream())
+    args = (vp(*[t.data_ptr() for t in xs]), vp(*[t.data_ptr() for t in ws]), vp(*[t.data_ptr() for t in ys]), res,
+            ip(*Ns), ip(*Ks), codes, ip(*[int(t) for t in kn]), _ext.i32(n), _ext.i32(M), _ext.i32(split),
+            _ext.i32(1 if _ext.chaining() else 0), _ext.ptr(_status(xs[0].device)), _ext.stream())
+    if trace is None:
+        _ext.call("rwkv_gemm_decode_tcgen05", *args)
+    else:
+        _ext.call("rwkv_gemm_decode_tcgen05_traced", *args, _ext.ptr(trace))
     return ys
