@@ -1,5 +1,6 @@
 // Decode-sized grouped GEMM on the 5th-generation tensor cores:
-//   y_i[M, N_i] = act_i(x_i[M, K_i] @ W_i) (+ residual_i)     for up to 8 problems in ONE launch, M <= 128.
+//   y_i[M, N_i] = act_i(alpha_i * x_i[M, K_i] @ W_i) + residual_i   (or act_i(alpha_i * x_i W_i + residual_i))
+// for up to 12 problems in ONE launch, M <= 128.
 //
 // With M = number of sequences being decoded, every projection is bound by streaming its weight matrix once,
 // and a 24-layer step issues some 330 of them, so both the launch count and the bytes in flight per SM matter.
@@ -30,7 +31,7 @@ namespace {
 constexpr int DN = 128;                      // weight rows (output columns) per CTA = rows of the MMA
 constexpr int DK = 64;                       // contraction elements per ring stage (one 128-byte swizzled row)
 constexpr int D_THREADS = 192;
-constexpr int D_MAX_PROBLEMS = 8;
+constexpr int D_MAX_PROBLEMS = 12;
 constexpr int D_MAX_STAGES = 8;
 constexpr int D_MAX_M = 128;
 constexpr int D_MAX_SPLIT = 8;               // portable cluster size
@@ -46,7 +47,9 @@ struct alignas(64) DecodeProblem {
   int epi;          // 0 none, 1 relu(x)^2, 3 tanh, 4 sigmoid
   int w_kn;         // weight stored [K, N] (N contiguous) instead of [N, K]
   int tile_start;   // first blockIdx.x of this problem
-  int pad_[3];
+  float alpha;      // scale of the product (a LoRA adapter's alpha / r; 1 otherwise)
+  int res_first;    // 1: y = act(alpha * acc + residual)   0: y = act(alpha * acc) + residual
+  int pad_[1];
 };
 struct alignas(64) DecodeParams {
   DecodeProblem p[D_MAX_PROBLEMS];
@@ -322,6 +325,8 @@ gemm_decode_kernel(const __grid_constant__ DecodeParams prm) {
     const int m_lo = z * rp, m_hi = min(M, m_lo + rp);
     const int n4 = (t & 31) * 4;
     const int epi = P.epi;
+    const float alpha = P.alpha;
+    const bool res_first = P.res_first != 0;
     if (n0 + n4 < N) {
       const float* Pm = reinterpret_cast<const float*>(base_ptr);
       for (int m = m_lo + (t >> 5); m < m_hi; m += 4) {
@@ -334,13 +339,17 @@ gemm_decode_kernel(const __grid_constant__ DecodeParams prm) {
 #pragma unroll
         for (int zz = 1; zz < D_MAX_SPLIT; ++zz)
           if (zz < S) { acc.x += part[zz].x; acc.y += part[zz].y; acc.z += part[zz].z; acc.w += part[zz].w; }
-        acc.x = d_act(acc.x, epi); acc.y = d_act(acc.y, epi); acc.z = d_act(acc.z, epi); acc.w = d_act(acc.w, epi);
         const size_t off = (size_t)m * N + n0 + n4;
-        if (P.residual) {
-          const uint2 r = __ldg(reinterpret_cast<const uint2*>(P.residual + off));
-          acc.x += __uint_as_float(r.x << 16); acc.y += __uint_as_float(r.x & 0xffff0000u);
-          acc.z += __uint_as_float(r.y << 16); acc.w += __uint_as_float(r.y & 0xffff0000u);
+        float4 res = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (P.residual) {   // plain load: the residual may be the output buffer itself (in-place accumulation)
+          const uint2 r = *reinterpret_cast<const uint2*>(P.residual + off);
+          res = make_float4(__uint_as_float(r.x << 16), __uint_as_float(r.x & 0xffff0000u),
+                            __uint_as_float(r.y << 16), __uint_as_float(r.y & 0xffff0000u));
         }
+        acc.x *= alpha; acc.y *= alpha; acc.z *= alpha; acc.w *= alpha;
+        if (res_first) { acc.x += res.x; acc.y += res.y; acc.z += res.z; acc.w += res.w; }
+        acc.x = d_act(acc.x, epi); acc.y = d_act(acc.y, epi); acc.z = d_act(acc.z, epi); acc.w = d_act(acc.w, epi);
+        if (!res_first) { acc.x += res.x; acc.y += res.y; acc.z += res.z; acc.w += res.w; }
         *reinterpret_cast<uint2*>(P.y + off) = make_uint2(pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w));
       }
     }
@@ -358,9 +367,10 @@ gemm_decode_kernel(const __grid_constant__ DecodeParams prm) {
 
 }  // namespace
 
-// count <= 8 problems sharing M <= 128.  xs: [M, K_i] bf16 row-major contiguous; ws: [N_i, K_i] (w_kn[i] = 0) or
+// count <= 12 problems sharing M <= 128.  xs: [M, K_i] bf16 row-major contiguous; ws: [N_i, K_i] (w_kn[i] = 0) or
 // [K_i, N_i] (w_kn[i] = 1) bf16 row-major contiguous; ys: [M, N_i] bf16 contiguous; residuals[i] may be null, else
-// [M, N_i] bf16 added after the activation (may alias ys[i]); epis[i]: 0 none, 1 relu^2, 3 tanh, 4 sigmoid.
+// [M, N_i] bf16 added after the activation, or before it where res_first[i] (may be ys[i] itself: accumulation in place);
+// epis[i]: 0 none, 1 relu^2, 3 tanh, 4 sigmoid; alphas[i] scales the product (null: 1).
 // Every N_i a multiple of 8, every K_i a multiple of 8, all pointers 16-byte aligned.  split: K slices per column
 // tile (1, 2, 4 or 8), 0 = choose.  prefetch_weights: with chained launches, request weight tiles before the
 // predecessor kernel has finished (only when no kernel in flight writes any of the weights).  status: device int, set non-zero if a device-side wait ran out.
@@ -368,7 +378,8 @@ gemm_decode_kernel(const __grid_constant__ DecodeParams prm) {
 // every CTA (see D_STAMP), for benchmarks/decode_gemm_timeline.py.
 RWKV_EXPORT int rwkv_gemm_decode_tcgen05_traced(const void* const* xs, const void* const* ws, void* const* ys,
                                                 const void* const* residuals, const int* Ns, const int* Ks,
-                                                const int* epis, const int* w_kn, int count, int M, int split,
+                                                const int* epis, const int* w_kn, const float* alphas,
+                                                const int* res_first, int count, int M, int split,
                                                 int prefetch_weights, void* status, void* stream, void* trace) {
   if (count <= 0 || count > D_MAX_PROBLEMS || M <= 0 || M > D_MAX_M) return RWKV_ERR_BAD_SHAPE;
   if (split != 0 && split != 1 && split != 2 && split != 4 && split != 8) return RWKV_ERR_BAD_SHAPE;
@@ -402,6 +413,8 @@ RWKV_EXPORT int rwkv_gemm_decode_tcgen05_traced(const void* const* xs, const voi
     p.K = K;
     p.epi = epis ? epis[i] : 0;
     p.w_kn = (w_kn && w_kn[i]) ? 1 : 0;
+    p.alpha = alphas ? alphas[i] : 1.f;
+    p.res_first = (res_first && res_first[i]) ? 1 : 0;
     p.tile_start = tiles;
     tiles += (N + DN - 1) / DN;
     const int kb = (K + DK - 1) / DK;
@@ -460,10 +473,10 @@ RWKV_EXPORT int rwkv_gemm_decode_tcgen05_traced(const void* const* xs, const voi
 
 RWKV_EXPORT int rwkv_gemm_decode_tcgen05(const void* const* xs, const void* const* ws, void* const* ys,
                                          const void* const* residuals, const int* Ns, const int* Ks, const int* epis,
-                                         const int* w_kn, int count, int M, int split, int prefetch_weights, void* status,
-                                         void* stream) {
-  return rwkv_gemm_decode_tcgen05_traced(xs, ws, ys, residuals, Ns, Ks, epis, w_kn, count, M, split, prefetch_weights,
-                                         status, stream, nullptr);
+                                         const int* w_kn, const float* alphas, const int* res_first, int count, int M,
+                                         int split, int prefetch_weights, void* status, void* stream) {
+  return rwkv_gemm_decode_tcgen05_traced(xs, ws, ys, residuals, Ns, Ks, epis, w_kn, alphas, res_first, count, M, split,
+                                         prefetch_weights, status, stream, nullptr);
 }
 
 // Chained launches for the kernels of the decode path (see common.cuh): 1 = on, 0 = off.  Returns the previous value.

@@ -39,10 +39,35 @@ class Linear(nn.Linear):
         return ops.linear(x, self.weight)
 
 
+def _decode_spec(layer: nn.Module, x: torch.Tensor, act: Optional[str] = None, residual: Optional[torch.Tensor] = None):
+    """Entry of :func:`ops.decode_projection_set` for a projection layer: a plain unsharded :class:`Linear`, or a wrapper
+    that describes itself through ``decode_spec()`` (the LoRA layer: base weight + adapter factors).  ``None`` for
+    anything else (ZeRO-3 panels, adapters with active dropout)."""
+    if getattr(layer, "_sharded", None) is not None:
+        return None
+    if type(layer) is Linear:
+        return (x, layer.weight, act, residual, None)
+    describe = getattr(layer, "decode_spec", None)
+    spec = describe() if describe is not None else None
+    if spec is None:
+        return None
+    return (x, spec[0], act, residual, spec[1])
+
+
+def _decoding(x: torch.Tensor) -> bool:
+    """Few rows, no autograd, on the GPU: the grouped decode GEMM applies."""
+    return x.is_cuda and not torch.is_grad_enabled() and x.numel() // x.shape[-1] <= 128
+
+
 def _project_add(layer: nn.Module, h: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
     """``residual + layer(h)``; a plain, unsharded :class:`Linear` adds the residual in its GEMM epilogue."""
     if type(layer) is Linear and getattr(layer, "_sharded", None) is None:
         return ops.linear_add(h, layer.weight, residual)
+    if _decoding(h):
+        spec = _decode_spec(layer, h, None, residual)
+        out = ops.decode_projection_set([spec]) if spec is not None else None
+        if out is not None:
+            return out[0][0]
     return residual + layer(h)
 
 
@@ -150,25 +175,40 @@ class RWKV7TimeMix(nn.Module):
         (xr, xw, xk, xv, xa, xg), last, x = ops.ln_shift_mix_unbound(x, ln_w, ln_b, self.mix_matrix(), x_prev)
 
         v_lin = None
-        if self._plain_projections() and x.is_cuda and not torch.is_grad_enabled():
-            # inference: the three projections and the first stages of the low-rank chains go out together
-            first = self.layer_id == 0
-            (r, k, v), low = ops.projections_with_lowrank(
-                [xr, xk, xv], [self.receptance.weight, self.key.weight, self.value.weight],
-                [xw, xa, xg] + ([] if first else [xv]), [self.w1, self.a1, self.g1] + ([] if first else [self.v1]),
-                ["tanh", None, "sigmoid"] + ([] if first else [None]),
-                [self.w2, self.a2, self.g2] + ([] if first else [self.v2]))
+        first = self.layer_id == 0
+        done = False
+        if x.is_cuda and not torch.is_grad_enabled():
+            # inference: r/k/v (with their adapters, if any) and the first stages of the low-rank chains go out as one
+            # grouped launch while decoding, the second stages as another
+            chains = [(xw, self.w1, "tanh", self.w2), (xa, self.a1, None, self.a2), (xg, self.g1, "sigmoid", self.g2)]
+            if not first:
+                chains.append((xv, self.v1, None, self.v2))
+            specs = [_decode_spec(m, t) for m, t in ((self.receptance, xr), (self.key, xk), (self.value, xv))]
+            out = None
+            if _decoding(x) and all(sp is not None for sp in specs):
+                out = ops.decode_projection_set(specs, chains)
+            if out is not None:
+                (r, k, v), low = out
+            elif self._plain_projections():
+                (r, k, v), low = ops.projections_with_lowrank(
+                    [xr, xk, xv], [self.receptance.weight, self.key.weight, self.value.weight],
+                    [c[0] for c in chains], [c[1] for c in chains], [c[2] for c in chains], [c[3] for c in chains])
+            else:
+                r, k, v = self.receptance(xr), self.key(xk), self.value(xv)
+                _, low = ops.projections_with_lowrank([], [], [c[0] for c in chains], [c[1] for c in chains],
+                                                      [c[2] for c in chains], [c[3] for c in chains])
             w_lin, a_lin, g = low[:3]
             if not first:
                 v_lin = low[3]
-        else:
+            done = True
+        if not done:
             r = self.receptance(xr)
             k = self.key(xk)
             v = self.value(xv)
             w_lin = ops.matmul(ops.matmul_act(xw, self.w1, "tanh"), self.w2)
             a_lin = ops.matmul(ops.matmul(xa, self.a1), self.a2)
             g = ops.matmul(ops.matmul_act(xg, self.g1, "sigmoid"), self.g2)
-            if self.layer_id != 0:
+            if not first:
                 v_lin = ops.matmul(ops.matmul(xv, self.v1), self.v2)
         if self.layer_id == 0:
             w, k, v, a_, b_ = ops.timemix_prep(k, v, None, w_lin, a_lin, None, self.w0, self.a0, None,
@@ -208,6 +248,11 @@ class RWKV7ChannelMix(nn.Module):
         plain = all(type(m) is Linear and getattr(m, "_sharded", None) is None for m in (self.key, self.value))
         if plain:
             return ops.channel_mix_ffn(xk, self.key.weight, self.value.weight, x), (last if want_state else None)
+        if _decoding(xk):
+            spec = _decode_spec(self.key, xk, "relu_sq")
+            out = ops.decode_projection_set([spec]) if spec is not None else None
+            if out is not None:
+                return _project_add(self.value, out[0][0], x), (last if want_state else None)
         if type(self.key) is Linear and getattr(self.key, "_sharded", None) is None:
             hidden = ops.linear_relu_sq(xk, self.key.weight)
         else:   # wrapped (LoRA) or sharded (ZeRO-3): activation applied separately

@@ -130,13 +130,24 @@ def projections_with_lowrank(lin_xs, lin_ws, lr_xs, lr_w1, lr_acts, lr_w2):
     """``([x @ W^T ...], [act(x @ w1) @ w2 ...])``: the ``nn.Linear`` projections and the low-rank chains of a
     time-mix block (``rwkvtune/models/rwkv7/model.py:146-160``).  ``lr_acts[i]`` is ``None``, ``"tanh"`` or
     ``"sigmoid"``.  While decoding on CUDA the whole set is two grouped launches."""
-    if _native(lin_xs[0], "gemm"):
+    if _native((list(lin_xs) + list(lr_xs))[0], "gemm"):
         from . import gemm
 
         return gemm.projections_with_lowrank(lin_xs, lin_ws, lr_xs, lr_w1, lr_acts, lr_w2)
     act = {None: lambda t: t, "tanh": torch.tanh, "sigmoid": torch.sigmoid}
     return ([torch.nn.functional.linear(x, w) for x, w in zip(lin_xs, lin_ws)],
             [act[a](x @ w1) @ w2 for x, w1, a, w2 in zip(lr_xs, lr_w1, lr_acts, lr_w2)])
+
+
+def decode_projection_set(lin, lowrank=()):
+    """Independent projections of the same few rows (a decode step) in at most two grouped launches, or ``None`` when
+    the set does not qualify (CPU tensors, autograd recording, more than 128 rows, odd shapes): see
+    ``ops/gemm.py::decode_projection_set`` for the argument format."""
+    if lin and _native(lin[0][0], "gemm") or (not lin and lowrank and _native(lowrank[0][0], "gemm")):
+        from . import gemm
+
+        return gemm.decode_projection_set(list(lin), list(lowrank))
+    return None
 
 
 def linear_relu_sq(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:

@@ -41,7 +41,7 @@ def decode_products(xs, ws, acts=None, kn=None, residuals=None):
     qualify (more than 128 rows, autograd recording, CPU tensors, odd shapes): the caller then takes its usual path.
     ``kn[i]`` marks a weight stored ``[in, out]``; ``acts[i]`` is ``None``, ``"relu_sq"``, ``"tanh"`` or ``"sigmoid"``."""
     n = _native()
-    if not _decode(n) or torch.is_grad_enabled() or not 0 < len(xs) <= 8:
+    if not _decode(n) or torch.is_grad_enabled() or not 0 < len(xs) <= n.DECODE_MAX_PROBLEMS:
         return None
     kn = list(kn) if kn is not None else [False] * len(xs)
     x2 = [x.reshape(-1, x.shape[-1]) for x in xs]
@@ -56,6 +56,67 @@ def decode_products(xs, ws, acts=None, kn=None, residuals=None):
                 return None
     ys = n.decode_group(x2, list(ws), epis=acts, kn=kn, residuals=r2)
     return [y.reshape(*x.shape[:-1], y.shape[-1]) for y, x in zip(ys, xs)]
+
+
+def decode_projection_set(lin, lowrank=()):
+    """A set of independent projections of the same few rows, in at most two launches of the decode GEMM.
+
+    ``lin``: ``(x, weight [out, in], act, residual, lora)`` per ``nn.Linear``-like map, ``lora`` being ``None`` or
+    ``(A [r, in], B [out, r], scaling)``; the result is ``act(x W^T + scaling * (x A^T) B^T) + residual`` (a residual
+    together with an activation is supported without an adapter only).  ``lowrank``: ``(x, w1 [in, d], act, w2 [d, out])``
+    per chain, result ``act(x w1) w2``.  First launch: every base product, every ``x A^T`` and every chain's first stage;
+    second launch: every adapter's ``B`` product accumulated in place (activation applied there) and every chain's second
+    stage.  Returns ``(lin_outs, lowrank_outs)`` or ``None`` when the set does not qualify."""
+    n = _native()
+    if not _decode(n) or torch.is_grad_enabled():
+        return None
+    xs, ws, acts, kn, res = [], [], [], [], []
+    for x, w, act, residual, lora in lin:
+        if lora is not None and act is not None and residual is not None:
+            return None
+        xs.append(x); ws.append(w); kn.append(False)
+        acts.append(act if lora is None else None)
+        res.append(residual if (lora is None or act is None) else None)
+    for x, w, act, residual, lora in lin:
+        if lora is not None:
+            xs.append(x); ws.append(lora[0]); kn.append(False); acts.append(None); res.append(None)
+    for x, w1, act, w2 in lowrank:
+        xs.append(x); ws.append(w1); kn.append(True); acts.append(act); res.append(None)
+    if not xs or len(xs) > n.DECODE_MAX_PROBLEMS:
+        return None
+    first = decode_products(xs, ws, acts=acts, kn=kn, residuals=res)
+    if first is None:
+        return None
+    n_lin = len(lin)
+    lin_out = first[:n_lin]
+    adapters = [i for i, item in enumerate(lin) if item[4] is not None]
+    xa = first[n_lin:n_lin + len(adapters)]
+    hidden = first[n_lin + len(adapters):]
+    if not adapters and not lowrank:
+        return lin_out, []
+    x2, w2s, act2, kn2, res2, alpha2, rf2, outs2 = [], [], [], [], [], [], [], []
+    for a_out, i in zip(xa, adapters):
+        y = lin_out[i].reshape(-1, lin_out[i].shape[-1])
+        x2.append(a_out.reshape(-1, a_out.shape[-1])); w2s.append(lin[i][4][1]); kn2.append(False)
+        act2.append(lin[i][2]); res2.append(y); alpha2.append(lin[i][4][2]); rf2.append(True); outs2.append(y)
+    for h, item in zip(hidden, lowrank):
+        x2.append(h.reshape(-1, h.shape[-1])); w2s.append(item[3]); kn2.append(True)
+        act2.append(None); res2.append(None); alpha2.append(1.0); rf2.append(False); outs2.append(None)
+    if not all(n.decode_ok(a, w, t) for a, w, t in zip(x2, w2s, kn2)):
+        # the first launch has run; finish the set with ordinary products
+        for a_out, i in zip(xa, adapters):
+            y = lin_out[i] + (a_out @ lin[i][4][1].t()) * lin[i][4][2]
+            lin_out[i] = y if lin[i][2] is None else _apply_act(y, lin[i][2])
+        return lin_out, [h @ item[3] for h, item in zip(hidden, lowrank)]
+    second = n.decode_group(x2, w2s, epis=act2, kn=kn2, residuals=res2, alphas=alpha2, res_first=rf2, outs=outs2)
+    lows = [y.reshape(*item[0].shape[:-1], y.shape[-1]) for y, item in zip(second[len(adapters):], lowrank)]
+    return lin_out, lows
+
+
+def _apply_act(y: torch.Tensor, act: str) -> torch.Tensor:
+    if act == "relu_sq":
+        return torch.relu(y) ** 2
+    return torch.tanh(y) if act == "tanh" else torch.sigmoid(y)
 
 
 def mm_nt(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
@@ -81,13 +142,10 @@ def projections_with_lowrank(lin_xs, lin_ws, lr_xs, lr_w1, lr_acts, lr_w2):
     """The projections of a time-mix block: ``[x @ W^T]`` for the ``nn.Linear`` weights ``lin_ws`` and
     ``[act(x @ w1) @ w2]`` for the low-rank chains.  While decoding (few rows, no autograd) the linear maps and all
     first stages are one grouped launch and all second stages another; otherwise one GEMM each."""
-    k = len(lin_xs)
-    first = decode_products(list(lin_xs) + list(lr_xs), list(lin_ws) + list(lr_w1),
-                            acts=[None] * k + list(lr_acts), kn=[False] * k + [True] * len(lr_xs))
-    if first is not None:
-        second = decode_products(first[k:], list(lr_w2), kn=[True] * len(lr_xs))
-        if second is not None:
-            return first[:k], second
+    out = decode_projection_set([(x, w, None, None, None) for x, w in zip(lin_xs, lin_ws)],
+                                list(zip(lr_xs, lr_w1, lr_acts, lr_w2)))
+    if out is not None:
+        return out
     lins = [linear(x, w) for x, w in zip(lin_xs, lin_ws)]
     lows = [matmul(matmul_act(x, a, act) if act else matmul(x, a), b)
             for x, a, act, b in zip(lr_xs, lr_w1, lr_acts, lr_w2)]

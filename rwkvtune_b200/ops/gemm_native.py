@@ -259,11 +259,16 @@ def decode_ok(x: torch.Tensor, w: torch.Tensor, kn: bool = False) -> bool:
     return x.shape[1] == K and K % 8 == 0 and N % 8 == 0
 
 
-def decode_group(xs, ws, epis=None, kn=None, residuals=None, split: int = 0, trace=None):
-    """``[act_i(x_i @ W_i) (+ residual_i)]`` for up to 8 problems sharing the row count, in one launch.
-    ``kn[i]`` marks a weight stored ``[K, N]``; ``epis[i]`` is one of ``DECODE_EPI``; a residual is a contiguous
-    ``[M, N_i]`` bf16 tensor.  ``trace``: optional zeroed int64 CUDA tensor of at least 16 x (number of CTAs) entries that
-    receives the per-CTA phase time stamps (``benchmarks/decode_gemm_timeline.py``)."""
+DECODE_MAX_PROBLEMS = 12
+
+
+def decode_group(xs, ws, epis=None, kn=None, residuals=None, split: int = 0, trace=None, alphas=None, res_first=None,
+                 outs=None):
+    """``[act_i(alpha_i * x_i @ W_i) + residual_i]`` (or ``act_i(alpha_i * x_i @ W_i + residual_i)`` where
+    ``res_first[i]``) for up to 12 problems sharing the row count, in one launch.  ``kn[i]`` marks a weight stored
+    ``[K, N]``; ``epis[i]`` is one of ``DECODE_EPI``; a residual is a contiguous ``[M, N_i]`` bf16 tensor and may be the
+    output itself (``outs[i]``: accumulate in place).  ``trace``: optional zeroed int64 CUDA tensor of at least
+    16 x (number of CTAs) entries that receives the per-CTA phase time stamps (``benchmarks/decode_gemm_timeline.py``)."""
     import ctypes
 
     n = len(xs)
@@ -271,15 +276,18 @@ def decode_group(xs, ws, epis=None, kn=None, residuals=None, split: int = 0, tra
     kn = list(kn) if kn is not None else [False] * n
     Ns = [w.shape[1] if t else w.shape[0] for w, t in zip(ws, kn)]
     Ks = [w.shape[0] if t else w.shape[1] for w, t in zip(ws, kn)]
-    ys = [torch.empty(M, N, dtype=torch.bfloat16, device=xs[0].device) for N in Ns]
+    ys = [o if (outs is not None and (o := outs[i]) is not None)
+          else torch.empty(M, N, dtype=torch.bfloat16, device=xs[0].device) for i, N in enumerate(Ns)]
     vp = ctypes.c_void_p * n
     ip = ctypes.c_int * n
     res = None
     if residuals is not None and any(r is not None for r in residuals):
         res = vp(*[(r.data_ptr() if r is not None else None) for r in residuals])
     codes = ip(*[DECODE_EPI[e] for e in (epis if epis is not None else [None] * n)])
+    al = None if alphas is None else (ctypes.c_float * n)(*[1.0 if v is None else float(v) for v in alphas])
+    rf = None if res_first is None else ip(*[int(bool(v)) for v in res_first])
     args = (vp(*[t.data_ptr() for t in xs]), vp(*[t.data_ptr() for t in ws]), vp(*[t.data_ptr() for t in ys]), res,
-            ip(*Ns), ip(*Ks), codes, ip(*[int(t) for t in kn]), _ext.i32(n), _ext.i32(M), _ext.i32(split),
+            ip(*Ns), ip(*Ks), codes, ip(*[int(t) for t in kn]), al, rf, _ext.i32(n), _ext.i32(M), _ext.i32(split),
             _ext.i32(1 if _ext.chaining() else 0), _ext.ptr(_status(xs[0].device)), _ext.stream())
     if trace is None:
         _ext.call("rwkv_gemm_decode_tcgen05", *args)

@@ -103,6 +103,17 @@ class LoraLinear(nn.Module):
         return _LoraLinearFn.apply(x, self.base_layer.weight, self.lora_A, self.lora_B, self.scaling,
                                    self.base_layer.weight.requires_grad)
 
+    def decode_spec(self):
+        """``(weight, adapter)`` for the grouped decode path: ``adapter`` is ``None`` (merged or disabled) or
+        ``(lora_A, lora_B, scaling)``.  ``None`` when the layer cannot take that path (sharded base, active dropout)."""
+        if getattr(self, "_sharded", None) is not None:
+            return None
+        if self.merged or self.disabled:
+            return self.base_layer.weight, None
+        if isinstance(self.lora_dropout, nn.Dropout) and self.training:
+            return None
+        return self.base_layer.weight, (self.lora_A, self.lora_B, self.scaling)
+
     @torch.no_grad()
     def merge(self) -> None:
         if not self.merged:

@@ -78,3 +78,45 @@ def test_decode_step_logits_match_library_gemm():
             gemm_native.DECODE_DISPATCH = prev
     scale = outs[1].abs().max().item()
     assert (outs[0] - outs[1]).abs().max().item() <= 3e-2 * scale + 1e-2
+
+
+def test_lora_decode_step_matches_ungrouped_adapter_path():
+    """With LoRA adapters on all six projections the decode step runs as grouped launches (base products and x A^T
+    together, B products accumulated in place); it must agree with the layer-by-layer adapter path."""
+    from rwkvtune_b200 import LoraConfig
+    from rwkvtune_b200.peft import get_peft_model
+    from rwkvtune_b200.inference import GRPOBatchGenerator
+    from rwkvtune_b200.ops import gemm_native
+    from rwkvtune_b200.peft.lora.layer import LoraLinear
+
+    model = get_peft_model(_model(), LoraConfig(r=16, lora_alpha=32))
+    torch.manual_seed(3)
+    n_lora = 0
+    with torch.no_grad():
+        for m in model.modules():
+            if isinstance(m, LoraLinear):
+                m.lora_B.normal_(0, 0.05)
+                n_lora += 1
+    assert n_lora >= 6 * 3
+    model.eval()
+    gen = GRPOBatchGenerator(model, _Tok(), use_cuda_graph=False)
+    tok = torch.randint(10, 2000, (16, 1), device="cuda")
+    outs, launches = [], []
+    from rwkvtune_b200.ops import _ext
+    for dispatch in (True, False):
+        prev = gemm_native.DECODE_DISPATCH
+        gemm_native.DECODE_DISPATCH = dispatch
+        try:
+            state = gen._zero_state(16)
+            with torch.no_grad():
+                logits = None
+                for _ in range(3):
+                    before = _ext.launch_count()
+                    logits, state = gen._forward(tok, state)
+                    launches.append(_ext.launch_count() - before)
+            outs.append(logits.float())
+        finally:
+            gemm_native.DECODE_DISPATCH = prev
+    scale = outs[1].abs().max().item()
+    assert (outs[0] - outs[1]).abs().max().item() <= 3e-2 * scale + 1e-2
+    assert gemm_native.check_status() == 0
