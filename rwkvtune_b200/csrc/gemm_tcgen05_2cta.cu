@@ -15,6 +15,11 @@
 // swizzled staging, TMA store) and report back to the leader's "accumulator empty" mbarrier.  Two accumulators
 // per CTA let the epilogue of tile i overlap the MMAs of tile i+1.
 //
+// A second operand pair (A2 [M, K2], B2 [N, K2], same layouts as the first) may be appended to the contraction:
+// C = op(A) op(B) + op(A2) op(B2), its K blocks simply following the first pair's in the ring.  That is the LoRA
+// linear in one launch - x W^T + (s x A^T) B^T with the rank-r factor as one extra 64-wide K block - instead of a
+// base GEMM followed by a second GEMM that re-reads and re-writes the whole output to accumulate into it.
+//
 // Every mbarrier wait is bounded: on expiry the waiter records a code in `status`, all roles leave their
 // loops, the two CTAs meet at the cluster barrier, tensor memory is released and the kernel returns.
 //
@@ -176,7 +181,8 @@ template <bool A_MN, bool B_MN, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                          const __grid_constant__ CUtensorMap map_c, int M, int N, int K, int* status,
-                         const bf16* __restrict__ c_in, long long ldc) {
+                         const bf16* __restrict__ c_in, long long ldc, const __grid_constant__ CUtensorMap map_a2,
+                         const __grid_constant__ CUtensorMap map_b2, int K2) {
   extern __shared__ unsigned char smem_dyn[];
   const uint32_t raw = smem_u32(smem_dyn);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -189,7 +195,8 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   const int pair = (int)blockIdx.x >> 1, n_pairs = (int)gridDim.x >> 1;
   const int tiles_m = (M + 2 * BM - 1) / (2 * BM), tiles_n = (N + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_n;
-  const int num_kb = (K + BK - 1) / BK;
+  const int num_kb1 = (K + BK - 1) / BK;                    // K blocks of the first operand pair
+  const int num_kb = num_kb1 + (K2 + BK - 1) / BK;          // ... followed by those of the second (K2 = 0: none)
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&bars->full[s], 1); mbar_init(&bars->empty[s], 1); }
@@ -222,17 +229,21 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           if (rank == 0) mbar_expect_tx(&bars->full[stage], 2 * STAGE_BYTES);
           const uint32_t full_leader = map_to_cta(smem_u32(&bars->full[stage]), 0);
           const uint32_t sa = base + stage * STAGE_BYTES, sb = sa + A_BYTES;
+          const bool second = kb >= num_kb1;
+          const CUtensorMap* ma = second ? &map_a2 : &map_a;
+          const CUtensorMap* mb = second ? &map_b2 : &map_b;
+          const int k0 = (second ? kb - num_kb1 : kb) * BK;
           if (A_MN) {   // A stored [K, M]: two boxes of 64 m-columns x 64 k-rows
 #pragma unroll
-            for (int c = 0; c < BM / 64; ++c) tma_load_2d_pair(sa + c * (BK * 128), &map_a, full_leader, m0 + c * 64, kb * BK);
+            for (int c = 0; c < BM / 64; ++c) tma_load_2d_pair(sa + c * (BK * 128), ma, full_leader, m0 + c * 64, k0);
           } else {
-            tma_load_2d_pair(sa, &map_a, full_leader, kb * BK, m0);
+            tma_load_2d_pair(sa, ma, full_leader, k0, m0);
           }
           if (B_MN) {   // B stored [K, N]: this CTA's 128 n-columns as two boxes
 #pragma unroll
-            for (int c = 0; c < BNH / 64; ++c) tma_load_2d_pair(sb + c * (BK * 128), &map_b, full_leader, n0 + c * 64, kb * BK);
+            for (int c = 0; c < BNH / 64; ++c) tma_load_2d_pair(sb + c * (BK * 128), mb, full_leader, n0 + c * 64, k0);
           } else {
-            tma_load_2d_pair(sb, &map_b, full_leader, kb * BK, n0);
+            tma_load_2d_pair(sb, mb, full_leader, k0, n0);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -353,7 +364,8 @@ using rwkv_tmap::make_map;   // encoded maps are cached per (address, shape, str
 
 template <bool A_MN, bool B_MN, int EPI>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, int M, int N, int K, int* status,
-           int sms, const bf16* c_in, long long ldc, cudaStream_t st) {
+           int sms, const bf16* c_in, long long ldc, cudaStream_t st, const CUtensorMap& ma2, const CUtensorMap& mb2,
+           int K2) {
   auto kern = gemm_tcgen05_2cta_kernel<A_MN, B_MN, EPI>;
   static bool configured = false;
   if (!configured) {
@@ -364,7 +376,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, 
   const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
   int pairs = sms / 2;
   if (tiles < pairs) pairs = tiles;
-  kern<<<2 * pairs, NUM_THREADS, SMEM_BYTES, st>>>(ma, mb, mc, M, N, K, status, c_in, ldc);
+  kern<<<2 * pairs, NUM_THREADS, SMEM_BYTES, st>>>(ma, mb, mc, M, N, K, status, c_in, ldc, ma2, mb2, K2);
   return rwkv_launch_status();
 }
 
@@ -376,11 +388,16 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, 
 //   epilogue: 0 none, 1 relu(x)^2, 5 multiply by 2 sqrt(residual), 2 add a bf16 [M,N] matrix: `residual` (row stride
 //   ldr) or, when that is null, the values already in C (in place).
 //   status: device int, set non-zero if a device-side wait expired.
-RWKV_EXPORT int rwkv_gemm_bf16_tcgen05_2cta(const void* a, const void* b, void* c, int M, int N, int K, long long lda,
-                                            long long ldb, long long ldc, int a_mn, int b_mn, int epilogue,
-                                            void* status, const void* residual, long long ldr, void* stream) {
-  if (M <= 0 || N <= 0 || K <= 0 || !(epilogue == 0 || epilogue == 1 || epilogue == 2 || epilogue == 5))
+//   a2 / b2 (optional, K2 > 0): a second operand pair in the same layouts, appended to the contraction:
+//   C = op(A) op(B) + op(A2) op(B2)   (A2 is [M,K2] or stored [K2,M]; B2 is [N,K2] or stored [K2,N])
+RWKV_EXPORT int rwkv_gemm_bf16_tcgen05_2cta_dual(const void* a, const void* b, void* c, int M, int N, int K,
+                                                 long long lda, long long ldb, long long ldc, int a_mn, int b_mn,
+                                                 int epilogue, void* status, const void* residual, long long ldr,
+                                                 const void* a2, const void* b2, int K2, long long lda2, long long ldb2,
+                                                 void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || K2 < 0 || !(epilogue == 0 || epilogue == 1 || epilogue == 2 || epilogue == 5))
     return RWKV_ERR_BAD_SHAPE;
+  if (K2 > 0 && (!a2 || !b2)) return RWKV_ERR_BAD_SHAPE;
   if ((epilogue == 2 || epilogue == 5) && residual && (((uintptr_t)residual & 15) || (ldr * 2) % 16))
     return RWKV_ERR_BAD_ALIGNMENT;
   if (epilogue == 5 && !residual) return RWKV_ERR_BAD_SHAPE;
@@ -397,18 +414,32 @@ RWKV_EXPORT int rwkv_gemm_bf16_tcgen05_2cta(const void* a, const void* b, void* 
   if (r) return r;
   r = make_map(&mc, c, M, N, ldc, 64, BM);
   if (r) return r;
+  CUtensorMap ma2 = ma, mb2 = mb;     // placeholders when there is no second pair (never dereferenced: K2 = 0)
+  if (K2 > 0) {
+    r = a_mn ? make_map(&ma2, a2, K2, M, lda2, 64, BK) : make_map(&ma2, a2, M, K2, lda2, BK, BM);
+    if (r) return r;
+    r = b_mn ? make_map(&mb2, b2, K2, N, ldb2, 64, BK) : make_map(&mb2, b2, N, K2, ldb2, BK, BNH);
+    if (r) return r;
+  }
   cudaStream_t st = (cudaStream_t)stream;
   int* sp = (int*)status;
   const bf16* cp = residual ? (const bf16*)residual : (const bf16*)c;
   if (residual) ldc = ldr;
 #define DISPATCH(AM, BMN)                                                                 \
-  (epilogue == 1   ? launch<AM, BMN, 1>(ma, mb, mc, M, N, K, sp, sms, cp, ldc, st)         \
-   : epilogue == 2 ? launch<AM, BMN, 2>(ma, mb, mc, M, N, K, sp, sms, cp, ldc, st)         \
-   : epilogue == 5 ? launch<AM, BMN, 5>(ma, mb, mc, M, N, K, sp, sms, cp, ldc, st)         \
-                   : launch<AM, BMN, 0>(ma, mb, mc, M, N, K, sp, sms, cp, ldc, st))
+  (epilogue == 1   ? launch<AM, BMN, 1>(ma, mb, mc, M, N, K, sp, sms, cp, ldc, st, ma2, mb2, K2)         \
+   : epilogue == 2 ? launch<AM, BMN, 2>(ma, mb, mc, M, N, K, sp, sms, cp, ldc, st, ma2, mb2, K2)         \
+   : epilogue == 5 ? launch<AM, BMN, 5>(ma, mb, mc, M, N, K, sp, sms, cp, ldc, st, ma2, mb2, K2)         \
+                   : launch<AM, BMN, 0>(ma, mb, mc, M, N, K, sp, sms, cp, ldc, st, ma2, mb2, K2))
   if (!a_mn && !b_mn) return DISPATCH(false, false);
   if (!a_mn && b_mn) return DISPATCH(false, true);
   if (a_mn && b_mn) return DISPATCH(true, true);
   return DISPATCH(true, false);
 #undef DISPATCH
+}
+
+RWKV_EXPORT int rwkv_gemm_bf16_tcgen05_2cta(const void* a, const void* b, void* c, int M, int N, int K, long long lda,
+                                            long long ldb, long long ldc, int a_mn, int b_mn, int epilogue,
+                                            void* status, const void* residual, long long ldr, void* stream) {
+  return rwkv_gemm_bf16_tcgen05_2cta_dual(a, b, c, M, N, K, lda, ldb, ldc, a_mn, b_mn, epilogue, status, residual, ldr,
+                                          nullptr, nullptr, 0, 0, 0, stream);
 }

@@ -12,6 +12,7 @@ and writes them back with one ``index_copy_``; the reference copies per sequence
 from __future__ import annotations
 
 import collections
+import contextlib
 import os
 import time
 from dataclasses import dataclass, field
@@ -20,6 +21,7 @@ from typing import Any, Dict, Iterator, List, Optional, Tuple, Union
 
 import torch
 
+from ..ops import _ext
 from .core import TokenSampler
 
 
@@ -166,7 +168,10 @@ class SchedulerCore:
             wkv = [(kv_pool[l], idx) for l in range(self.n_layer)]
         else:
             wkv = list(kv_pool.index_select(1, idx).unbind(0))
-        x, a, s, f = self.model.forward_states(ids, list(att.unbind(0)), wkv, list(ffn.unbind(0)))
+        # single-token steps of a serving loop (weights constant): the kernels are launched as a dependent chain
+        chain = _ext.launch_chaining() if (ids.is_cuda and ids.shape[1] == 1) else contextlib.nullcontext()
+        with chain:
+            x, a, s, f = self.model.forward_states(ids, list(att.unbind(0)), wkv, list(ffn.unbind(0)))
         self.state_pool["att_x_prev"].index_copy_(1, idx, torch.stack(a).to(self.dtype))
         self.state_pool["ffn_x_prev"].index_copy_(1, idx, torch.stack(f).to(self.dtype))
         if not isinstance(s[0], tuple):

@@ -167,6 +167,23 @@ def _acc_ok(n, y: torch.Tensor) -> bool:
             and y.data_ptr() % 16 == 0 and (y.stride(0) * 2) % 16 == 0)
 
 
+def mm_nt_plus(x: torch.Tensor, w: torch.Tensor, x2: torch.Tensor, w2: torch.Tensor) -> torch.Tensor:
+    """``x @ w^T + x2 @ w2^T`` (``w [N, K]``, ``w2 [N, K2]``).  On the native path ONE GEMM launch whose contraction
+    runs over ``K`` then ``K2`` (the LoRA linear: ``x2 = s x A^T``, ``w2 = B``); otherwise a GEMM and an accumulate."""
+    n = _native()
+    if n is not None and n.dual_ok(x, w, x2, w2, "nt"):
+        return n.mm_nt_dual(x, w, x2, w2)
+    return addmm_nt_(mm_nt(x, w), x2, w2)
+
+
+def mm_nn_plus(x: torch.Tensor, w: torch.Tensor, x2: torch.Tensor, w2: torch.Tensor) -> torch.Tensor:
+    """``x @ w + x2 @ w2`` (``w [K, N]``, ``w2 [K2, N]``); see :func:`mm_nt_plus`."""
+    n = _native()
+    if n is not None and n.dual_ok(x, w, x2, w2, "nn"):
+        return n.mm_nn_dual(x, w, x2, w2)
+    return addmm_nn_(mm_nn(x, w), x2, w2)
+
+
 def addmm_nt_(y: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     """``y += x @ w^T`` in place; on the native path the sum happens in the GEMM epilogue (no temporary)."""
     n = _native()

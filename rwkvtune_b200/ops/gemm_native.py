@@ -121,19 +121,51 @@ def two_cta_ok(M: int, N: int, K: int, epilogue: int) -> bool:
 
 
 def _run_2cta(a, b, M, N, K, a_mn: int, b_mn: int, epilogue: int = 0, out: torch.Tensor = None,
-              residual: torch.Tensor = None, accumulate: bool = True) -> torch.Tensor:
-    """Same contract as :func:`_run`, on the pair-of-SMs kernel."""
+              residual: torch.Tensor = None, accumulate: bool = True, a2: torch.Tensor = None,
+              b2: torch.Tensor = None, K2: int = 0) -> torch.Tensor:
+    """Same contract as :func:`_run`, on the pair-of-SMs kernel.  ``a2`` / ``b2`` (same layouts as ``a`` / ``b``,
+    contraction length ``K2``) are appended to the contraction: ``op(a) op(b) + op(a2) op(b2)`` in one launch."""
     if out is not None:
         c, epilogue = out, (2 if accumulate else epilogue)
     else:
         c = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
         if residual is not None and epilogue == 0:
             epilogue = 2
-    _ext.call("rwkv_gemm_bf16_tcgen05_2cta", _ext.ptr(a), _ext.ptr(b), _ext.ptr(c), _ext.i32(M), _ext.i32(N), _ext.i32(K),
-              _ext.i64(a.stride(0)), _ext.i64(b.stride(0)), _ext.i64(c.stride(0)), _ext.i32(a_mn), _ext.i32(b_mn),
-              _ext.i32(epilogue), _ext.ptr(_status(a.device)), _ext.ptr(residual),
-              _ext.i64(0 if residual is None else residual.stride(0)), _ext.stream())
+    if a2 is None:
+        _ext.call("rwkv_gemm_bf16_tcgen05_2cta", _ext.ptr(a), _ext.ptr(b), _ext.ptr(c), _ext.i32(M), _ext.i32(N),
+                  _ext.i32(K), _ext.i64(a.stride(0)), _ext.i64(b.stride(0)), _ext.i64(c.stride(0)), _ext.i32(a_mn),
+                  _ext.i32(b_mn), _ext.i32(epilogue), _ext.ptr(_status(a.device)), _ext.ptr(residual),
+                  _ext.i64(0 if residual is None else residual.stride(0)), _ext.stream())
+    else:
+        _ext.call("rwkv_gemm_bf16_tcgen05_2cta_dual", _ext.ptr(a), _ext.ptr(b), _ext.ptr(c), _ext.i32(M), _ext.i32(N),
+                  _ext.i32(K), _ext.i64(a.stride(0)), _ext.i64(b.stride(0)), _ext.i64(c.stride(0)), _ext.i32(a_mn),
+                  _ext.i32(b_mn), _ext.i32(epilogue), _ext.ptr(_status(a.device)), _ext.ptr(residual),
+                  _ext.i64(0 if residual is None else residual.stride(0)), _ext.ptr(a2), _ext.ptr(b2), _ext.i32(K2),
+                  _ext.i64(a2.stride(0)), _ext.i64(b2.stride(0)), _ext.stream())
     return c
+
+
+def dual_ok(x: torch.Tensor, w: torch.Tensor, x2: torch.Tensor, w2: torch.Tensor, layout: str) -> bool:
+    """``x w^T + x2 w2^T`` (``layout="nt"``) or ``x w + x2 w2`` (``"nn"``) as one launch of the pair-of-SMs kernel."""
+    if not (available() and hasattr(_ext.lib(), "rwkv_gemm_bf16_tcgen05_2cta_dual")):
+        return False
+    if not all(t.is_cuda and t.dtype == torch.bfloat16 and t.dim() == 2 and _rows_ok(t) for t in (x, w, x2, w2)):
+        return False
+    M, K = x.shape
+    N = w.shape[0] if layout == "nt" else w.shape[1]
+    K2 = x2.shape[1]
+    shapes = (w.shape == (N, K) and w2.shape == (N, K2)) if layout == "nt" else (w.shape == (K, N) and w2.shape == (K2, N))
+    return shapes and x2.shape[0] == M and K2 > 0 and two_cta_ok(M, N, K, 0)
+
+
+def mm_nt_dual(x, w, x2, w2) -> torch.Tensor:
+    """``x [M,K] @ w[N,K]^T + x2 [M,K2] @ w2[N,K2]^T``: the second product rides as extra K blocks of the first."""
+    return _run_2cta(x, w, x.shape[0], w.shape[0], x.shape[1], 0, 0, a2=x2, b2=w2, K2=x2.shape[1])
+
+
+def mm_nn_dual(x, w, x2, w2) -> torch.Tensor:
+    """``x [M,K] @ w[K,N] + x2 [M,K2] @ w2[K2,N]``."""
+    return _run_2cta(x, w, x.shape[0], w.shape[1], x.shape[1], 0, 1, a2=x2, b2=w2, K2=x2.shape[1])
 
 
 def mm_nt_2cta(x: torch.Tensor, w: torch.Tensor, epilogue: int = 0, out: torch.Tensor = None,

@@ -134,7 +134,7 @@ class _LoraAGLinearFn(torch.autograd.Function):
         dyb = gemm.mm_nn(dy2, b)
         dx = None
         if ctx.needs_input_grad[0]:
-            dx = gemm.addmm_nn_(gemm.mm_nn(dy2, sw.full_weight()), dyb * s, a).reshape(ctx.shape)
+            dx = gemm.mm_nn_plus(dy2, sw.full_weight(), dyb * s, a).reshape(ctx.shape)
         sw.owner.after_dgrad(sw)
         da = gemm.mm_tn(dyb, x2) * s if ctx.needs_input_grad[2] else None
         db = gemm.mm_tn(dy2, xa) * s if ctx.needs_input_grad[3] else None

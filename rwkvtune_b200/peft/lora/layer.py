@@ -3,7 +3,9 @@
 ``y = x W^T + s (x A^T) B^T`` with the base weight frozen.  The reference evaluates this as three
 ``F.linear`` calls and lets autograd also differentiate through the base layer
 (``rwkvtune/peft/lora/layer.py:92-130``).  Here one autograd node does it: the backward produces
-``dx = dy W + s (dy B) A``, ``dA`` and ``dB`` and never forms the (unused) base weight gradient.
+``dx = dy W + s (dy B) A``, ``dA`` and ``dB`` and never forms the (unused) base weight gradient.  Both ``y`` and ``dx``
+are single GEMM launches: the rank-``r`` term is appended to the contraction of the base product (``[x | s x A^T]`` against
+``[W | B]``), the second operand pair being fetched through its own TMA tensor maps.
 """
 from __future__ import annotations
 
@@ -20,7 +22,9 @@ class _LoraLinearFn(torch.autograd.Function):
     def forward(ctx, x, w, a, b, scaling: float, w_needs_grad: bool):
         x2 = x.reshape(-1, x.shape[-1])
         xa = gemm.mm_nt(x2, a)                       # [M, r]
-        y = gemm.addmm_nt_(gemm.mm_nt(x2, w), xa * scaling, b)     # scale the [M, r] factor, add in the GEMM epilogue
+        # scale the [M, r] factor; its product with B rides as the last K block of the base GEMM (one launch, no
+        # read-modify-write of y)
+        y = gemm.mm_nt_plus(x2, w, xa * scaling, b)
         ctx.save_for_backward(x2, w, a, b, xa)
         ctx.scaling, ctx.shape = scaling, x.shape
         return y.reshape(*x.shape[:-1], w.shape[0])
@@ -33,7 +37,7 @@ class _LoraLinearFn(torch.autograd.Function):
         dyb = gemm.mm_nn(dy2, b)                     # [M, r]
         dx = dw = da = db = None
         if ctx.needs_input_grad[0]:
-            dx = gemm.addmm_nn_(gemm.mm_nn(dy2, w), dyb * s, a).reshape(ctx.shape)
+            dx = gemm.mm_nn_plus(dy2, w, dyb * s, a).reshape(ctx.shape)
         if ctx.needs_input_grad[1]:
             dw = gemm.mm_tn(dy2, x2)
         if ctx.needs_input_grad[2]:

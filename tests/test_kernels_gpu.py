@@ -698,6 +698,58 @@ def test_decode_gemm_residual_in_place():
 
 
 @pytest.mark.parametrize("layout", ["nt", "nn"])
+@pytest.mark.parametrize("K2", [64, 16, 136])
+def test_gemm_second_operand_pair_along_k(layout, K2):
+    """x W^T + x2 W2^T (and the NN form) as one launch: the second pair's K blocks follow the first pair's in the ring."""
+    from rwkvtune_b200.ops import gemm, gemm_native
+    torch.manual_seed(K2)
+    M, K, N = 4096, 328, 3200          # ragged last K block of the first pair; enough 256x256 tiles for the pair kernel
+    x = (torch.randn(M, K, device="cuda") * 0.5).to(BF)
+    x2 = (torch.randn(M, K2, device="cuda") * 0.5).to(BF)
+    w = (torch.randn(N, K, device="cuda") * 0.1).to(BF)
+    w2 = (torch.randn(N, K2, device="cuda") * 0.1).to(BF)
+    ref_y = x.float() @ w.float().t() + x2.float() @ w2.float().t()
+    if layout == "nt":
+        assert gemm_native.dual_ok(x, w, x2, w2, "nt")
+        y = gemm.mm_nt_plus(x, w, x2, w2)
+    else:
+        wt, w2t = w.t().contiguous(), w2.t().contiguous()
+        assert gemm_native.dual_ok(x, wt, x2, w2t, "nn")
+        y = gemm.mm_nn_plus(x, wt, x2, w2t)
+    assert (y.float() - ref_y).abs().max().item() <= 1e-2 * ref_y.abs().max().item() + 1e-2
+    assert gemm_native.check_status() == 0
+
+
+def test_lora_linear_single_launch_forward_and_dgrad():
+    """LoRA linear at a training shape: y and dx each come from one GEMM launch with the rank-r term appended to the
+    contraction; values and all gradients against the fp32 statement of the same layer."""
+    from rwkvtune_b200.ops import _ext
+    from rwkvtune_b200.peft.lora.layer import LoraLinear
+    torch.manual_seed(11)
+    M, Cin, Cout, r = 4096, 2048, 3072, 64
+    base = torch.nn.Linear(Cin, Cout, bias=False, device="cuda", dtype=BF)
+    base.weight.requires_grad_(False)
+    layer = LoraLinear(base, r=r, lora_alpha=2 * r)
+    with torch.no_grad():
+        layer.lora_B.normal_(0, 0.02)
+    x = (torch.randn(M, Cin, device="cuda") * 0.5).to(BF).requires_grad_(True)
+    dy = (torch.randn(M, Cout, device="cuda") * 0.1).to(BF)
+    before = _ext.launch_count()
+    y = layer(x)
+    fwd_launches = _ext.launch_count() - before
+    y.backward(dy)
+    assert fwd_launches == 2            # x A^T, then the base product with the adapter term as its last K block
+    xf, W, A, B = x.detach().float(), base.weight.float(), layer.lora_A.float(), layer.lora_B.float()
+    s = layer.scaling
+    ref_y = xf @ W.t() + s * (xf @ A.t()) @ B.t()
+    ref_dx = dy.float() @ W + s * (dy.float() @ B) @ A
+    ref_da = s * (dy.float() @ B).t() @ xf
+    ref_db = s * dy.float().t() @ (xf @ A.t())
+    for got, want in ((y, ref_y), (x.grad, ref_dx), (layer.lora_A.grad, ref_da), (layer.lora_B.grad, ref_db)):
+        assert (got.float() - want).abs().max().item() <= 2e-2 * want.abs().max().item() + 1e-2
+
+
+@pytest.mark.parametrize("layout", ["nt", "nn"])
 def test_gemm_accumulate_epilogue(layout):
     from rwkvtune_b200.ops import gemm
     torch.manual_seed(3)
