@@ -152,6 +152,10 @@ struct AgParams {
   int rank, world, Kp, n_rb;
   int target;          // a row block has landed when its counter has reached this value
   int group;           // column tiles per tile group (see the tile order below)
+  // optional second operand pair (local memory, K-major), appended to the contraction: y = x W^T + x2 W2^T.  The LoRA
+  // term of a sharded frozen weight rides here as one extra K block instead of a second, accumulating GEMM.
+  int K2;
+  CUtensorMap map_a2, map_b2;
 };
 constexpr int AG_COPY_WARPS = 4;
 
@@ -247,9 +251,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int gn = min(ag.group, tiles_n - g * ag.group);
     return (g * ag.group + (tile - g * per_group) % gn) * BN;
   };
+  const int num_kb2 = AG ? (ag.K2 + BK - 1) / BK : 0;      // K blocks of the appended operand pair (all-gather variant)
   auto kb_range = [&](int sp, int& lo, int& hi) {
     lo = (int)((long long)num_kb * sp / splits);
-    hi = (int)((long long)num_kb * (sp + 1) / splits);
+    hi = (int)((long long)num_kb * (sp + 1) / splits) + (sp == splits - 1 ? num_kb2 : 0);
   };
 
   if (threadIdx.x == 0) {
@@ -300,6 +305,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           if (!mbar_wait(&bars->empty[stage], phase ^ 1, bars, status, 101)) { ok = false; break; }
           mbar_expect_tx(&bars->full[stage], STAGE_BYTES);
           const uint32_t sa = base + stage * STAGE_BYTES, sb = sa + A_BYTES;
+          if (AG && kb >= num_kb) {   // appended pair: both operands K-major, from this GPU's memory
+            tma_load_2d(sa, &ag.map_a2, &bars->full[stage], (kb - num_kb) * BK, m0);
+            tma_load_2d(sb, &ag.map_b2, &bars->full[stage], (kb - num_kb) * BK, n0);
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            continue;
+          }
           if (A_MN) {
 #pragma unroll
             for (int c = 0; c < BM / 64; ++c) tma_load_2d(sa + c * (BK * 128), &map_a, &bars->full[stage], m0 + c * 64, k0);
@@ -621,9 +632,13 @@ RWKV_EXPORT int rwkv_gemm_bf16_tcgen05_splitk(const void* a, const void* b, void
 // gathered weight and can be reused afterwards (e.g. by the backward pass).  blk_count: ceil(N / 256)
 // device ints, zero-initialised once; *arrivals_io: host-side running total of arrivals per counter (0 before the
 // first call on these buffers), advanced by this call.
-RWKV_EXPORT int rwkv_ag_gemm_bf16_tcgen05(const void* x, const unsigned long long* shard_ptrs, void* staged, void* y,
-                                          int M, int N, int K, int rank, int world, void* blk_count,
-                                          int* arrivals_io, void* status, void* stream) {
+// x2 / w2 (optional): a second, local operand pair ([M, K2] and [N, K2], row-major contiguous) appended to the
+// contraction: y = x W^T + x2 w2^T.
+RWKV_EXPORT int rwkv_ag_gemm_bf16_tcgen05_dual(const void* x, const unsigned long long* shard_ptrs, void* staged, void* y,
+                                               int M, int N, int K, int rank, int world, void* blk_count,
+                                               int* arrivals_io, void* status, const void* x2, const void* w2, int K2,
+                                               void* stream) {
+  if (K2 < 0 || (K2 > 0 && (!x2 || !w2))) return RWKV_ERR_BAD_SHAPE;
   if (M <= 0 || N <= 0 || K <= 0 || world <= 0 || world > MAX_RANKS || rank < 0 || rank >= world) return RWKV_ERR_BAD_SHAPE;
   if (K % world || (K / world) % BK || !arrivals_io || !blk_count) return RWKV_ERR_BAD_SHAPE;
   if (*arrivals_io > 0x70000000) return RWKV_ERR_TOO_LARGE;
@@ -646,5 +661,19 @@ RWKV_EXPORT int rwkv_ag_gemm_bf16_tcgen05(const void* x, const unsigned long lon
   ag.blk_count = (int*)blk_count;
   ag.rank = rank; ag.world = world; ag.Kp = K / world; ag.n_rb = (N + BN - 1) / BN;
   ag.group = ag.n_rb >= 16 ? 8 : 4;
+  ag.K2 = K2;
+  if (K2 > 0) {
+    r = make_map(&ag.map_a2, x2, M, K2, K2, BK, BM);
+    if (r) return r;
+    r = make_map(&ag.map_b2, w2, N, K2, K2, BK, BN);
+    if (r) return r;
+  }
   return launch_ag(ma, mb, mc, M, N, K, (int*)status, sms, ag, arrivals_io, (cudaStream_t)stream);
+}
+
+RWKV_EXPORT int rwkv_ag_gemm_bf16_tcgen05(const void* x, const unsigned long long* shard_ptrs, void* staged, void* y,
+                                          int M, int N, int K, int rank, int world, void* blk_count,
+                                          int* arrivals_io, void* status, void* stream) {
+  return rwkv_ag_gemm_bf16_tcgen05_dual(x, shard_ptrs, staged, y, M, N, K, rank, world, blk_count, arrivals_io, status,
+                                        nullptr, nullptr, 0, stream);
 }

@@ -79,6 +79,15 @@ inline int make_map(CUtensorMap* map, const void* ptr, long long rows, long long
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r == CUDA_ERROR_INVALID_CONTEXT) {
+    // The encoder is a driver entry point and wants a current context.  A thread whose first CUDA work is this call
+    // (an autograd worker starting a backward pass with a GEMM) has none yet: a runtime call binds the device's
+    // primary context.  (Never reached while a stream is being captured: the capturing thread has a context.)
+    cudaFree(nullptr);
+    r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
   if (r != CUDA_SUCCESS) return RWKV_ERR_CUDA_BASE + 900 + (int)r;
   std::lock_guard<std::mutex> lock(mu);
   if (table.size() >= MAX_ENTRIES) table.clear();

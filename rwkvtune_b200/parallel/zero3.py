@@ -118,9 +118,13 @@ class _LoraAGLinearFn(torch.autograd.Function):
     def forward(ctx, x, sw: ShardedWeight, a, b, scaling: float):
         x2 = x.reshape(-1, x.shape[-1])
         x2 = x2 if x2.is_contiguous() else x2.contiguous()
-        base = sw.owner.forward_gemm(x2, sw)
         xa = gemm.mm_nt(x2, a)
-        y = gemm.addmm_nt_(base, xa * scaling, b)
+        b_c = b if b.is_contiguous() else b.contiguous()
+        if xa.shape[1] % 8 == 0 and b_c.dtype == torch.bfloat16:
+            # the adapter term is the last K block of the all-gather GEMM (no second pass over y)
+            y = sw.owner.forward_gemm(x2, sw, extra=((xa * scaling).contiguous(), b_c))
+        else:
+            y = gemm.addmm_nt_(sw.owner.forward_gemm(x2, sw), xa * scaling, b)
         ctx.save_for_backward(x2, a, b, xa)
         ctx.sw, ctx.shape, ctx.scaling = sw, x.shape, scaling
         return y.reshape(*x.shape[:-1], sw.N)
@@ -266,13 +270,14 @@ class Zero3ShardedLinears:
             self._slots[key] = _Slot(self.ctx.rank, self.ctx.world_size, sw.N, sw.K, self.ctx.device, self.n_copy)
         return self._slots[key]
 
-    def forward_gemm(self, x2: torch.Tensor, sw: ShardedWeight) -> torch.Tensor:
+    def forward_gemm(self, x2: torch.Tensor, sw: ShardedWeight, extra=None) -> torch.Tensor:
+        """``x2 @ W^T`` with the gather fused in; ``extra = (u [M, r], v [N, r])`` adds ``u @ v^T`` inside the same launch."""
         gw = sw.gathered()
         if gw.pending is not None:      # a prefetch may still be writing the slot
             torch.cuda.current_stream().wait_event(gw.pending)
             gw.pending = None
         gw.ptrs_for(sw)
-        y = gemm_native.ag_mm_nt(x2, gw)
+        y = gemm_native.ag_mm_nt(x2, gw) if extra is None else gemm_native.ag_mm_nt(x2, gw, extra[0], extra[1])
         gw.current_owner = sw
         return y
 

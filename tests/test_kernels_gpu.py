@@ -612,6 +612,15 @@ def test_ag_fused_gemm_emulated_panels(M, N, K, W, rank):
     torch.cuda.synchronize()
     assert gemm_native.check_status() == 0 and torch.equal(gw.staged, w)
     assert (y.float() - ref_out[:256]).abs().max().item() <= 2e-2 * ref_out.abs().max().item() + 1e-2
+    # an appended local operand pair (the LoRA term of a sharded weight): y = x W^T + u v^T in the same launch
+    u = (torch.randn(M, 64, device="cuda") * 0.5).to(BF)
+    v = (torch.randn(N, 64, device="cuda") * 0.1).to(BF)
+    gw.staged.zero_()
+    y = gemm_native.ag_mm_nt(x, gw, u, v)
+    torch.cuda.synchronize()
+    ref2 = ref_out + u.float() @ v.float().t()
+    assert gemm_native.check_status() == 0 and torch.equal(gw.staged, w)
+    assert (y.float() - ref2).abs().max().item() <= 2e-2 * ref2.abs().max().item() + 1e-2
 
 
 @pytest.mark.parametrize("B,T,H,with_state", [(2, 64, 2, False), (1, 37, 3, True), (2, 256, 1, True)])
