@@ -34,8 +34,9 @@ static inline int rwkv_launch_status() {
 // programmatic-stream-serialisation attribute: a kernel may be scheduled while its predecessor is still running, does
 // whatever does not depend on it, and `rwkv_chain_wait()` then blocks until the predecessor has completed and its
 // writes are visible.  Every chained kernel calls `rwkv_chain_begin()` (or `rwkv_chain_trigger()` then, later,
-// `rwkv_chain_wait()`) before its first global access, so the order of the stream is kept transitively.  Launched
-// the ordinary way the two instructions do nothing.
+// `rwkv_chain_wait()`) before its first access to anything another kernel of the chain writes, so the order of the
+// stream is kept transitively; model parameters - constant while chaining is on - may be requested before the wait.
+// Launched the ordinary way the two instructions do nothing.
 __device__ __forceinline__ void rwkv_chain_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void rwkv_chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void rwkv_chain_begin() {

@@ -20,7 +20,7 @@ ln_shift_mix_fwd_kernel(const bf16* __restrict__ x, const float* __restrict__ ln
                         bf16* __restrict__ last, float* __restrict__ mean_out, float* __restrict__ rstd_out,
                         int B, int T, int C, int strip, float eps) {
   __shared__ float red[2 * EW_MAX_WARPS * 4];
-  rwkv_chain_begin();
+  rwkv_chain_trigger();
   int phase = 0;
   const RowCtx rc = make_row_ctx(T, C, strip);
   const size_t row0 = (size_t)rc.b * T;
@@ -34,6 +34,9 @@ ln_shift_mix_fwd_kernel(const bf16* __restrict__ x, const float* __restrict__ ln
 #pragma unroll
     for (int k = 0; k < K; ++k) load8f(mix + (size_t)k * C + rc.col, mu[k]);
   }
+  // parameters (constant while launches are chained) are requested before the predecessor kernel has finished,
+  // activations after
+  rwkv_chain_wait();
 #pragma unroll
   for (int e = 0; e < 8; ++e) hprev[e] = 0.f;
 

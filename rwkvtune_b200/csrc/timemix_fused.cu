@@ -30,7 +30,7 @@ timemix_prep_fwd_kernel(const bf16* __restrict__ k, const bf16* __restrict__ v, 
                         const float* __restrict__ k_k, const float* __restrict__ k_a, bf16* __restrict__ w_out,
                         bf16* __restrict__ k_out, bf16* __restrict__ v_out, bf16* __restrict__ an_out,
                         bf16* __restrict__ b_out, int T, int C, int strip) {
-  rwkv_chain_begin();
+  rwkv_chain_trigger();
   const RowCtx rc = make_row_ctx(T, C, strip);
   PrepParams p;
 #pragma unroll
@@ -42,6 +42,7 @@ timemix_prep_fwd_kernel(const bf16* __restrict__ k, const bf16* __restrict__ v, 
     load8f(k_k + rc.col, p.kk);
     load8f(k_a + rc.col, p.ka);
   }
+  rwkv_chain_wait();   // parameters before, activations after (see common.cuh)
   for (int t = rc.t0; t < rc.t1; ++t) {
     const size_t off = ((size_t)rc.b * T + t) * C + rc.col;
     float kf[8] = {0, 0, 0, 0, 0, 0, 0, 0}, vf[8], wl[8], al[8];
@@ -197,10 +198,11 @@ gn_bonus_gate_fwd_kernel(const bf16* __restrict__ y, const bf16* __restrict__ r,
                          const bf16* __restrict__ v, const bf16* __restrict__ g, const float* __restrict__ gn_w,
                          const float* __restrict__ gn_b, const float* __restrict__ r_k, bf16* __restrict__ z, int T,
                          int C, int strip, float eps) {
-  rwkv_chain_begin();
+  rwkv_chain_trigger();
   const RowCtx rc = make_row_ctx(T, C, strip);
   float gw[8] = {0, 0, 0, 0, 0, 0, 0, 0}, gb[8] = {0, 0, 0, 0, 0, 0, 0, 0}, rk[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   if (rc.active) { load8f(gn_w + rc.col, gw); load8f(gn_b + rc.col, gb); load8f(r_k + rc.col, rk); }
+  rwkv_chain_wait();   // parameters before, activations after (see common.cuh)
   for (int t = rc.t0; t < rc.t1; ++t) {
     const size_t off = ((size_t)rc.b * T + t) * C + rc.col;
     float yf[8] = {0, 0, 0, 0, 0, 0, 0, 0}, rf[8] = {0, 0, 0, 0, 0, 0, 0, 0}, kf[8] = {0, 0, 0, 0, 0, 0, 0, 0};
