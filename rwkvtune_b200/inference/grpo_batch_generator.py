@@ -261,7 +261,13 @@ class GRPOBatchGenerator:
             TokenSampler.set_max_valid_token_id(prev_max)
             if was_training:
                 self.model.train()
-        max_len = int(lengths.max()) if n else 0
+        max_len = int(lengths.max()) if n else 0          # host read: everything queued above has completed
+        if dev.type == "cuda":
+            from ..ops import gemm_native
+
+            code = gemm_native.check_status(dev) if gemm_native.available() else 0
+            if code:      # a bounded device-side wait of a GEMM ran out during the rollout: the tokens are not trustworthy
+                raise RuntimeError(f"rollout aborted: a device-side wait expired inside a GEMM kernel (status {code})")
         comp = out_ids[:, :max_len]
         masks = torch.arange(max_len, device=dev)[None, :] < lengths[:, None]
         comp = comp * masks
