@@ -210,6 +210,15 @@ class RWKV7TimeMix(nn.Module):
             g = ops.matmul(ops.matmul_act(xg, self.g1, "sigmoid"), self.g2)
             if not first:
                 v_lin = ops.matmul(ops.matmul(xv, self.v1), self.v2)
+        if ops.timemix_decode_core_ok(r, g, wkv_state, self.head_size):
+            # one token per sequence: preparation, state update and GroupNorm + bonus + gate are one kernel
+            z, new_state = ops.timemix_decode_core(r, k, v, None if first else v_first, w_lin, a_lin, v_lin, g, self.w0,
+                                                   self.a0, None if first else self.v0, self.k_k, self.k_a, self.r_k,
+                                                   self.ln_x.weight, self.ln_x.bias, wkv_state)
+            if first:
+                v_first = v
+            out = _project_add(self.output, z, x)
+            return out, v_first, (last if want_state else None), (new_state if want_state else None)
         if self.layer_id == 0:
             w, k, v, a_, b_ = ops.timemix_prep(k, v, None, w_lin, a_lin, None, self.w0, self.a0, None,
                                                self.k_k, self.k_a, self.head_size)

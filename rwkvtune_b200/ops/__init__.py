@@ -220,6 +220,22 @@ def wkv7_pool_step(r, w, k, v, a, b, pool: torch.Tensor, slots: torch.Tensor, he
     return y.to(r.dtype)
 
 
+def timemix_decode_core_ok(r, g, state, head_size: int = 64) -> bool:
+    """True when :func:`timemix_decode_core` applies: CUDA, one token per sequence, bf16, head size 64, an existing fp32
+    state, no autograd, and none of the three kernels it replaces switched off."""
+    if not (_native(r, "wkv7") and _native(r, "timemix_prep") and _native(r, "gn_bonus_gate")):
+        return False
+    return _cuda().timemix_decode_core_ok(r, g, state, head_size)
+
+
+def timemix_decode_core(r, k, v, v_first, w_lin, a_lin, v_lin, g, w0, a0, v0, k_k, k_a, r_k, gn_w, gn_b, state,
+                        eps: float = GROUPNORM_EPS):
+    """One decoding step of a block's recurrent core - ``timemix_prep``, the WKV7 update and ``gn_bonus_gate`` - as a
+    single kernel (check :func:`timemix_decode_core_ok` first).  Returns ``(z, new_state)``."""
+    return _cuda().timemix_decode_core(r, k, v, v_first, w_lin, a_lin, v_lin, g, w0, a0, v0, k_k, k_a, r_k, gn_w, gn_b,
+                                       state, eps)
+
+
 def wkv7_gn(r, w, k, v, a, b, g, gn_w, gn_b, r_k, head_size: int = 64, state: Optional[torch.Tensor] = None,
             return_state: bool = False, eps: float = GROUPNORM_EPS):
     """The recurrence followed by GroupNorm + bonus + gate; returns ``(z, final_state or None)``.  On CUDA the two

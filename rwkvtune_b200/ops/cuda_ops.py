@@ -733,6 +733,50 @@ def wkv7_pool_step(r, w, k, v, a, b, pool: torch.Tensor, slots: torch.Tensor) ->
     return y
 
 
+def timemix_decode_core_ok(r, g, state, head_size: int) -> bool:
+    """One token per sequence, bf16, head size 64, an existing fp32 state (tensor, or ``(pool, slots)``), no autograd,
+    and the fused kernel present in the library."""
+    if not (r.is_cuda and r.dim() == 3 and r.shape[1] == 1 and r.dtype == BF16 and g.dtype == BF16 and head_size == 64
+            and r.shape[-1] % 64 == 0 and not torch.is_grad_enabled() and state is not None):
+        return False
+    from . import _ext
+
+    if not hasattr(_ext.lib(), "rwkv_wkv7_decode_core"):
+        return False
+    st = state[0] if isinstance(state, tuple) else state
+    return st.dtype == torch.float32 and st.is_contiguous() and tuple(st.shape[1:]) == (r.shape[-1] // 64, 64, 64)
+
+
+def timemix_decode_core(r, k, v, v_first, w_lin, a_lin, v_lin, g, w0, a0, v0, k_k, k_a, r_k, gn_w, gn_b, state,
+                        eps: float = ref.GROUPNORM_EPS):
+    """Key/decay/value preparation, WKV7 state update + read-out and GroupNorm + bonus + gate of one decoding step as
+    ONE kernel (``csrc/wkv7_decode.cu``); same roundings and summation order as ``timemix_prep`` -> ``wkv7`` ->
+    ``gn_bonus_gate``.
+    ``state``: fp32 ``[B, H, 64, 64]`` (a new tensor is returned, or the same one while ``INPLACE_STATE``) or
+    ``(pool, slots)`` (updated in place).  ``v_first`` / ``v_lin`` are ``None`` in the first block.
+    Returns ``(z [B, 1, C] bf16, new state)``."""
+    B, _, C = r.shape
+    H = C // 64
+    r, k, v, w_lin, a_lin, g = (_c(t, BF16) for t in (r, k, v, w_lin, a_lin, g))
+    if v_first is not None:
+        v_first, v_lin = _c(v_first, BF16), _c(v_lin, BF16)
+    slots = None
+    if isinstance(state, tuple):
+        s_in = s_out = state[0]
+        slots = _c(state[1], torch.int64)
+        new_state = state
+    else:
+        s_in = state
+        s_out = state if INPLACE_STATE else torch.empty_like(state)
+        new_state = s_out
+    z = torch.empty(B, 1, C, dtype=BF16, device=r.device)
+    call("rwkv_wkv7_decode_core", ptr(r), ptr(k), ptr(v), ptr(w_lin), ptr(a_lin), ptr(v_lin), ptr(v_first), ptr(g),
+         ptr(_f32(w0)), ptr(_f32(a0)), ptr(_f32(v0)) if v_first is not None else ptr(None), ptr(_f32(k_k)), ptr(_f32(k_a)),
+         ptr(_f32(r_k)), ptr(_f32(gn_w)), ptr(_f32(gn_b)), ptr(s_in), ptr(s_out), ptr(slots), ptr(z), i32(B), i32(H),
+         f32(eps), stream())
+    return z, new_state
+
+
 # =============================================================================== gathers
 def gather_rows(src: torch.Tensor, index: torch.Tensor) -> torch.Tensor:
     """``src.index_select(0, index)`` for a contiguous tensor whose rows are a multiple of 16 bytes."""

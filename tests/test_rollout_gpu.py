@@ -120,3 +120,54 @@ def test_lora_decode_step_matches_ungrouped_adapter_path():
     scale = outs[1].abs().max().item()
     assert (outs[0] - outs[1]).abs().max().item() <= 3e-2 * scale + 1e-2
     assert gemm_native.check_status() == 0
+
+
+@pytest.mark.parametrize("first_block", [True, False])
+@pytest.mark.parametrize("pooled", [False, True])
+def test_fused_decode_core_reproduces_the_three_kernel_path(first_block, pooled):
+    """timemix_prep -> wkv7 -> gn_bonus_gate against the single decode-core kernel: the same values in z and in the state."""
+    from rwkvtune_b200 import ops
+
+    torch.manual_seed(7 + first_block + 2 * pooled)
+    B, H = 24, 5
+    C = H * 64
+    dev = "cuda"
+    bf = lambda s=1.0: (torch.randn(B, 1, C, device=dev) * s).to(torch.bfloat16)
+    r, k, v, w_lin, a_lin, v_lin, v_first, g = bf(), bf(), bf(), bf(0.5), bf(0.5), bf(0.5), bf(), bf()
+    par = lambda s=0.5: torch.nn.Parameter(torch.randn(1, 1, C, device=dev) * s)
+    w0, a0, v0, k_k, k_a = par(), par(), par(), par(0.3) + 0.8, par(0.3) + 0.8
+    r_k = torch.nn.Parameter(torch.randn(H, 64, device=dev) * 0.3)
+    gn_w = torch.nn.Parameter(1 + 0.1 * torch.randn(C, device=dev))
+    gn_b = torch.nn.Parameter(0.1 * torch.randn(C, device=dev))
+    vf, vl, v0_ = (None, None, None) if first_block else (v_first, v_lin, v0)
+    n_slots = 40
+    pool0 = torch.randn(n_slots, H, 64, 64, device=dev) * 0.3
+    slots = torch.randperm(n_slots, device=dev)[:B]
+    with torch.no_grad():
+        if pooled:
+            pool_a, pool_b = pool0.clone(), pool0.clone()
+            state_a, state_b = (pool_a, slots), (pool_b, slots)
+        else:
+            s0 = pool0[:B].contiguous()
+            state_a, state_b = s0.clone(), s0.clone()
+        w, k2, v2, a_, b_ = ops.timemix_prep(k, v, vf, w_lin, a_lin, vl, w0, a0, v0_, k_k, k_a, 64)
+        z_ref, s_ref = ops.wkv7_gn(r, w, k2, v2, a_, b_, g, gn_w, gn_b, r_k, 64, state=state_a, return_state=True)
+        assert ops.timemix_decode_core_ok(r, g, state_b, 64)
+        z, s_new = ops.timemix_decode_core(r, k, v, vf, w_lin, a_lin, vl, g, w0, a0, v0_, k_k, k_a, r_k, gn_w, gn_b, state_b)
+    torch.cuda.synchronize()
+
+    def same(got, want, what):
+        # same roundings and the same order of sums; what may differ is where the compiler contracts a multiply and an
+        # add into one fused operation: a last-bit difference in an occasional element
+        diff = (got.float() - want.float()).abs()
+        bad = diff > 0
+        assert bad.float().mean().item() < 2e-3, (what, bad.float().mean().item())
+        assert (diff <= 2 ** -7 * want.float().abs() + 1e-6).all(), (what, diff.max().item())
+
+    same(z, z_ref.to(z.dtype), "z")
+    if pooled:
+        same(pool_b, pool_a, "state")
+        assert not torch.equal(pool_b, pool0)
+    else:
+        same(s_new, s_ref, "state")
+        assert torch.equal(state_b, s0)      # functional: the input state is untouched
