@@ -10,14 +10,19 @@ import pytest
 import torch
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-_PORT = [29610]
+def _free_port() -> int:
+    """A port nobody listens on right now (a fixed port can still be held by a rendezvous that has just ended)."""
+    import socket
+
+    with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
 
 
 def _launch(script_path, nproc, *args, timeout=420, expect_fail=False):
-    _PORT[0] += 1
     env = dict(os.environ, RWKV_ROOT=ROOT, OMP_NUM_THREADS="1", PYTHONPATH=ROOT)
     res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(nproc),
-                          "--master-addr", "127.0.0.1", "--master-port", str(_PORT[0]), str(script_path), *map(str, args)],
+                          "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), str(script_path), *map(str, args)],
                          capture_output=True, text=True, env=env, timeout=timeout, cwd=ROOT)
     if not expect_fail:
         assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]

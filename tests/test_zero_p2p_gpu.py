@@ -8,6 +8,15 @@ import sys
 import pytest
 import torch
 
+
+def _free_port() -> int:
+    import socket
+
+    with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
@@ -224,7 +233,7 @@ def test_p2p_transport_matches_nccl_two_ranks(tmp_path):
     script.write_text(_WORKER)
     env = dict(os.environ, RWKV_ROOT=ROOT, NCCL_NVLS_ENABLE="0")
     res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
-                          "--master-addr", "127.0.0.1", "--master-port", "29533", str(script)],
+                          "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), str(script)],
                          capture_output=True, text=True, env=env, timeout=300)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
     import json
@@ -300,7 +309,7 @@ def test_zero3_lora_fused_allgather_gemm_matches_stage2(tmp_path):
     script.write_text(_WORKER_Z3)
     env = dict(os.environ, RWKV_ROOT=ROOT, NCCL_NVLS_ENABLE="0", RWKV_SAVE_DIR=str(tmp_path / "saved"))
     res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
-                          "--master-addr", "127.0.0.1", "--master-port", "29534", str(script)],
+                          "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), str(script)],
                          capture_output=True, text=True, env=env, timeout=300)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-3000:]
     import json
@@ -367,7 +376,7 @@ def test_zero3_full_parameter_training_matches_stage2(tmp_path):
     script.write_text(_WORKER_Z3_FULL)
     env = dict(os.environ, RWKV_ROOT=ROOT, NCCL_NVLS_ENABLE="0")
     res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
-                          "--master-addr", "127.0.0.1", "--master-port", "29535", str(script)],
+                          "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), str(script)],
                          capture_output=True, text=True, env=env, timeout=300)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-3000:]
     import json
