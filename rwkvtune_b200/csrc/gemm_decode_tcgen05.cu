@@ -35,6 +35,7 @@ constexpr int D_MAX_PROBLEMS = 12;
 constexpr int D_MAX_STAGES = 8;
 constexpr int D_MAX_M = 128;
 constexpr int D_MAX_SPLIT = 8;               // portable cluster size
+constexpr int D_MAX_NEXT = 4;                // weight matrices of later launches to prefetch into L2
 constexpr int W_BYTES = DN * DK * 2;         // 16 KiB
 constexpr unsigned long long D_WAIT_NS = 2000000000ull;
 
@@ -57,6 +58,11 @@ struct alignas(64) DecodeParams {
   int prefetch;     // weights are not written by any kernel of the chain: stream them before the chain wait
   int* status;
   unsigned long long* trace;   // optional [CTAs][16] globaltimer stamps of the phases of every CTA (null: off)
+  // Weights of the products that follow this launch in the step (null / 0: none).  Once a CTA has requested all of its own
+  // tiles it asks for its share of these to be brought into L2, so that HBM keeps streaming during this launch's
+  // epilogue and the next launch's prologue instead of idling through both.
+  const void* next_w[D_MAX_NEXT];
+  unsigned next_bytes[D_MAX_NEXT];
 };
 
 struct DBarriers {
@@ -259,6 +265,21 @@ gemm_decode_kernel(const __grid_constant__ DecodeParams prm) {
         d_tma_load_2d(sx, &P.map_x, &bars.full[stage], kb * DK, 0);
         if (++stage == stages) { stage = 0; phase ^= 1; }
       }
+      // this CTA's share of the following launches' weights: L2 prefetch, 16-byte granules, at most 32 KB per request
+      const unsigned cta = blockIdx.z * gridDim.x + blockIdx.x, n_cta = gridDim.x * gridDim.z;
+#pragma unroll
+      for (int j = 0; j < D_MAX_NEXT; ++j) {
+        const unsigned total = prm.next_bytes[j];
+        if (!prm.next_w[j] || !total) continue;
+        const unsigned share = ((total / n_cta) + 15u) & ~15u;
+        const unsigned lo = cta * share;
+        const unsigned hi = min(total, lo + share);
+        const char* basep = reinterpret_cast<const char*>(prm.next_w[j]);
+        for (unsigned off = lo; off < hi; off += 32768u) {
+          const unsigned sz = min(32768u, hi - off) & ~15u;
+          if (sz) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(basep + off), "r"(sz) : "memory");
+        }
+      }
     }
   } else if (warp == 1) {
     if (lane == 0 && kb_hi > kb_lo) {   // --------------------------------------------- MMA issuer
@@ -374,13 +395,17 @@ gemm_decode_kernel(const __grid_constant__ DecodeParams prm) {
 // Every N_i a multiple of 8, every K_i a multiple of 8, all pointers 16-byte aligned.  split: K slices per column
 // tile (1, 2, 4 or 8), 0 = choose.  prefetch_weights: with chained launches, request weight tiles before the
 // predecessor kernel has finished (only when no kernel in flight writes any of the weights).  status: device int, set non-zero if a device-side wait ran out.
+// next_ws / next_bytes (next_count <= 4, may be null): device pointers (16-byte aligned) and sizes (below 4 GB) of weight
+// matrices that later launches of the same stream will read; they are prefetched into L2.
 // trace: optional device buffer of 16 x (number of CTAs) uint64, zeroed by the caller: globaltimer stamps of the phases of
 // every CTA (see D_STAMP), for benchmarks/decode_gemm_timeline.py.
 RWKV_EXPORT int rwkv_gemm_decode_tcgen05_traced(const void* const* xs, const void* const* ws, void* const* ys,
                                                 const void* const* residuals, const int* Ns, const int* Ks,
                                                 const int* epis, const int* w_kn, const float* alphas,
                                                 const int* res_first, int count, int M, int split,
-                                                int prefetch_weights, void* status, void* stream, void* trace) {
+                                                int prefetch_weights, void* status, void* stream, void* trace,
+                                                const void* const* next_ws, const long long* next_bytes,
+                                                int next_count) {
   if (count <= 0 || count > D_MAX_PROBLEMS || M <= 0 || M > D_MAX_M) return RWKV_ERR_BAD_SHAPE;
   if (split != 0 && split != 1 && split != 2 && split != 4 && split != 8) return RWKV_ERR_BAD_SHAPE;
   DecodeParams prm;
@@ -391,6 +416,12 @@ RWKV_EXPORT int rwkv_gemm_decode_tcgen05_traced(const void* const* xs, const voi
   prm.Mpad = Mpad;
   prm.status = (int*)status;
   prm.trace = (unsigned long long*)trace;
+  for (int j = 0; j < D_MAX_NEXT; ++j) {
+    const bool on = next_ws && next_bytes && j < next_count && next_ws[j] && !((uintptr_t)next_ws[j] & 15) &&
+                    next_bytes[j] > 0 && next_bytes[j] < 0xffff0000ll;
+    prm.next_w[j] = on ? next_ws[j] : nullptr;
+    prm.next_bytes[j] = on ? (unsigned)next_bytes[j] : 0u;
+  }
   prm.prefetch = prefetch_weights ? 1 : 0;
   int cols = 32;
   while (cols < Mpad) cols *= 2;
@@ -476,7 +507,7 @@ RWKV_EXPORT int rwkv_gemm_decode_tcgen05(const void* const* xs, const void* cons
                                          const int* w_kn, const float* alphas, const int* res_first, int count, int M,
                                          int split, int prefetch_weights, void* status, void* stream) {
   return rwkv_gemm_decode_tcgen05_traced(xs, ws, ys, residuals, Ns, Ks, epis, w_kn, alphas, res_first, count, M, split,
-                                         prefetch_weights, status, stream, nullptr);
+                                         prefetch_weights, status, stream, nullptr, nullptr, nullptr, 0);
 }
 
 // Chained launches for the kernels of the decode path (see common.cuh): 1 = on, 0 = off.  Returns the previous value.

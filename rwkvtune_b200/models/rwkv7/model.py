@@ -59,15 +59,26 @@ def _decoding(x: torch.Tensor) -> bool:
     return x.is_cuda and not torch.is_grad_enabled() and x.numel() // x.shape[-1] <= 128
 
 
-def _project_add(layer: nn.Module, h: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
-    """``residual + layer(h)``; a plain, unsharded :class:`Linear` adds the residual in its GEMM epilogue."""
-    if type(layer) is Linear and getattr(layer, "_sharded", None) is None:
-        return ops.linear_add(h, layer.weight, residual)
+def _weights_of(*layers) -> list:
+    """Weight tensors of projection layers, as an L2 prefetch hint for the decode GEMM (sharded or absent ones skipped)."""
+    out = []
+    for m in layers:
+        w = getattr(m, "weight", None) if m is not None else None
+        if isinstance(w, torch.Tensor) and w.is_cuda and w.numel() > 0:
+            out.append(w)
+    return out
+
+
+def _project_add(layer: nn.Module, h: torch.Tensor, residual: torch.Tensor, prefetch=None) -> torch.Tensor:
+    """``residual + layer(h)``; a plain, unsharded :class:`Linear` adds the residual in its GEMM epilogue.  ``prefetch``:
+    weights that the step reads next (decode only)."""
     if _decoding(h):
         spec = _decode_spec(layer, h, None, residual)
-        out = ops.decode_projection_set([spec]) if spec is not None else None
+        out = ops.decode_projection_set([spec], (), prefetch) if spec is not None else None
         if out is not None:
             return out[0][0]
+    if type(layer) is Linear and getattr(layer, "_sharded", None) is None:
+        return ops.linear_add(h, layer.weight, residual)
     return residual + layer(h)
 
 
@@ -186,7 +197,7 @@ class RWKV7TimeMix(nn.Module):
             specs = [_decode_spec(m, t) for m, t in ((self.receptance, xr), (self.key, xk), (self.value, xv))]
             out = None
             if _decoding(x) and all(sp is not None for sp in specs):
-                out = ops.decode_projection_set(specs, chains)
+                out = ops.decode_projection_set(specs, chains, _weights_of(self.output))
             if out is not None:
                 (r, k, v), low = out
             elif self._plain_projections():
@@ -217,7 +228,8 @@ class RWKV7TimeMix(nn.Module):
                                                    self.ln_x.weight, self.ln_x.bias, wkv_state)
             if first:
                 v_first = v
-            out = _project_add(self.output, z, x)
+            nxt = getattr(self, "_decode_next", None)          # the channel-mix half of this block
+            out = _project_add(self.output, z, x, _weights_of(getattr(nxt, "key", None)))
             return out, v_first, (last if want_state else None), (new_state if want_state else None)
         if self.layer_id == 0:
             w, k, v, a_, b_ = ops.timemix_prep(k, v, None, w_lin, a_lin, None, self.w0, self.a0, None,
@@ -254,14 +266,16 @@ class RWKV7ChannelMix(nn.Module):
 
     def forward(self, x, ln_w, ln_b, x_prev=None, want_state: bool = False):
         (xk,), last, x = ops.ln_shift_mix_unbound(x, ln_w, ln_b, self.x_k, x_prev)
+        if _decoding(xk):
+            spec = _decode_spec(self.key, xk, "relu_sq")
+            out = ops.decode_projection_set([spec], (), _weights_of(self.value)) if spec is not None else None
+            if out is not None:
+                nxt = getattr(self, "_decode_next", None)      # the time-mix half of the next block
+                hint = _weights_of(*(getattr(nxt, n, None) for n in ("receptance", "key", "value"))) if nxt is not None else None
+                return _project_add(self.value, out[0][0], x, hint), (last if want_state else None)
         plain = all(type(m) is Linear and getattr(m, "_sharded", None) is None for m in (self.key, self.value))
         if plain:
             return ops.channel_mix_ffn(xk, self.key.weight, self.value.weight, x), (last if want_state else None)
-        if _decoding(xk):
-            spec = _decode_spec(self.key, xk, "relu_sq")
-            out = ops.decode_projection_set([spec]) if spec is not None else None
-            if out is not None:
-                return _project_add(self.value, out[0][0], x), (last if want_state else None)
         if type(self.key) is Linear and getattr(self.key, "_sharded", None) is None:
             hidden = ops.linear_relu_sq(xk, self.key.weight)
         else:   # wrapped (LoRA) or sharded (ZeRO-3): activation applied separately
@@ -361,6 +375,11 @@ class RWKV7Model(GenerationMixin, nn.Module):
         self.config = config
         self.emb = nn.Embedding(config.vocab_size, config.n_embd)
         self.blocks = nn.ModuleList([RWKV7Block(config, i) for i in range(config.n_layer)])
+        # who runs after whom in a decode step (plain attributes, not sub-modules): each half tells its last GEMM whose
+        # weights to bring into L2 next
+        for i, blk in enumerate(self.blocks):
+            object.__setattr__(blk.att, "_decode_next", blk.ffn)
+            object.__setattr__(blk.ffn, "_decode_next", self.blocks[i + 1].att if i + 1 < config.n_layer else None)
         self.ln_out = nn.LayerNorm(config.n_embd)
         self.head = Linear(config.n_embd, config.vocab_size)
         self._emb_preprocessed = False

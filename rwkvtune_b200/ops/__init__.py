@@ -139,14 +139,14 @@ def projections_with_lowrank(lin_xs, lin_ws, lr_xs, lr_w1, lr_acts, lr_w2):
             [act[a](x @ w1) @ w2 for x, w1, a, w2 in zip(lr_xs, lr_w1, lr_acts, lr_w2)])
 
 
-def decode_projection_set(lin, lowrank=()):
+def decode_projection_set(lin, lowrank=(), prefetch=None):
     """Independent projections of the same few rows (a decode step) in at most two grouped launches, or ``None`` when
     the set does not qualify (CPU tensors, autograd recording, more than 128 rows, odd shapes): see
     ``ops/gemm.py::decode_projection_set`` for the argument format."""
     if lin and _native(lin[0][0], "gemm") or (not lin and lowrank and _native(lowrank[0][0], "gemm")):
         from . import gemm
 
-        return gemm.decode_projection_set(list(lin), list(lowrank))
+        return gemm.decode_projection_set(list(lin), list(lowrank), prefetch)
     return None
 
 

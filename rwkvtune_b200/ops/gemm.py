@@ -36,7 +36,7 @@ def _decode(n) -> bool:
     return n is not None and n.DECODE_DISPATCH
 
 
-def decode_products(xs, ws, acts=None, kn=None, residuals=None):
+def decode_products(xs, ws, acts=None, kn=None, residuals=None, prefetch=None):
     """``[act_i(x_i @ W_i) (+ residual_i)]`` as ONE launch of the decode GEMM, or ``None`` when the problems do not
     qualify (more than 128 rows, autograd recording, CPU tensors, odd shapes): the caller then takes its usual path.
     ``kn[i]`` marks a weight stored ``[in, out]``; ``acts[i]`` is ``None``, ``"relu_sq"``, ``"tanh"`` or ``"sigmoid"``."""
@@ -54,12 +54,13 @@ def decode_products(xs, ws, acts=None, kn=None, residuals=None):
             if r is not None and not (r.dtype == torch.bfloat16 and r.is_contiguous() and r.data_ptr() % 8 == 0
                                       and r.shape == (x2[0].shape[0], w.shape[1] if t else w.shape[0])):
                 return None
-    ys = n.decode_group(x2, list(ws), epis=acts, kn=kn, residuals=r2)
+    ys = n.decode_group(x2, list(ws), epis=acts, kn=kn, residuals=r2, prefetch=prefetch)
     return [y.reshape(*x.shape[:-1], y.shape[-1]) for y, x in zip(ys, xs)]
 
 
-def decode_projection_set(lin, lowrank=()):
+def decode_projection_set(lin, lowrank=(), prefetch=None):
     """A set of independent projections of the same few rows, in at most two launches of the decode GEMM.
+    ``prefetch``: weight tensors of the products that come next in the step (L2 prefetch hint, see ``decode_group``).
 
     ``lin``: ``(x, weight [out, in], act, residual, lora)`` per ``nn.Linear``-like map, ``lora`` being ``None`` or
     ``(A [r, in], B [out, r], scaling)``; the result is ``act(x W^T + scaling * (x A^T) B^T) + residual`` (a residual
@@ -84,7 +85,7 @@ def decode_projection_set(lin, lowrank=()):
         xs.append(x); ws.append(w1); kn.append(True); acts.append(act); res.append(None)
     if not xs or len(xs) > n.DECODE_MAX_PROBLEMS:
         return None
-    first = decode_products(xs, ws, acts=acts, kn=kn, residuals=res)
+    first = decode_products(xs, ws, acts=acts, kn=kn, residuals=res, prefetch=prefetch)
     if first is None:
         return None
     n_lin = len(lin)

@@ -308,12 +308,14 @@ DECODE_MAX_PROBLEMS = 12
 
 
 def decode_group(xs, ws, epis=None, kn=None, residuals=None, split: int = 0, trace=None, alphas=None, res_first=None,
-                 outs=None):
+                 outs=None, prefetch=None):
     """``[act_i(alpha_i * x_i @ W_i) + residual_i]`` (or ``act_i(alpha_i * x_i @ W_i + residual_i)`` where
     ``res_first[i]``) for up to 12 problems sharing the row count, in one launch.  ``kn[i]`` marks a weight stored
     ``[K, N]``; ``epis[i]`` is one of ``DECODE_EPI``; a residual is a contiguous ``[M, N_i]`` bf16 tensor and may be the
     output itself (``outs[i]``: accumulate in place).  ``trace``: optional zeroed int64 CUDA tensor of at least
-    16 x (number of CTAs) entries that receives the per-CTA phase time stamps (``benchmarks/decode_gemm_timeline.py``)."""
+    16 x (number of CTAs) entries that receives the per-CTA phase time stamps (``benchmarks/decode_gemm_timeline.py``).
+    ``prefetch``: weight tensors that later launches of the step will read (the four largest are used): the kernel asks
+    for them to be brought into L2 once its own tiles are requested."""
     import ctypes
 
     n = len(xs)
@@ -334,8 +336,13 @@ def decode_group(xs, ws, epis=None, kn=None, residuals=None, split: int = 0, tra
     args = (vp(*[t.data_ptr() for t in xs]), vp(*[t.data_ptr() for t in ws]), vp(*[t.data_ptr() for t in ys]), res,
             ip(*Ns), ip(*Ks), codes, ip(*[int(t) for t in kn]), al, rf, _ext.i32(n), _ext.i32(M), _ext.i32(split),
             _ext.i32(1 if _ext.chaining() else 0), _ext.ptr(_status(xs[0].device)), _ext.stream())
-    if trace is None:
+    nxt = [t for t in (prefetch or ()) if t is not None and t.is_cuda and t.numel() > 0 and t.data_ptr() % 16 == 0]
+    if trace is None and not nxt:
         _ext.call("rwkv_gemm_decode_tcgen05", *args)
     else:
-        _ext.call("rwkv_gemm_decode_tcgen05_traced", *args, _ext.ptr(trace))
+        nxt = sorted(nxt, key=lambda t: -t.numel())[:4]
+        k = len(nxt)
+        np_ = (ctypes.c_void_p * max(k, 1))(*[t.data_ptr() for t in nxt]) if k else None
+        nb_ = (ctypes.c_longlong * max(k, 1))(*[t.numel() * t.element_size() for t in nxt]) if k else None
+        _ext.call("rwkv_gemm_decode_tcgen05_traced", *args, _ext.ptr(trace), np_, nb_, _ext.i32(k))
     return ys
