@@ -304,3 +304,43 @@ RWKV_EXPORT int rwkv_sample_top_p(const void* logits, int is_bf16, int n, int V,
   return rwkv_sample_tokens(logits, is_bf16, n, V, n_valid, inv_temp, top_p, 0, 0, nullptr, nullptr, nullptr, 1.f, 0,
                             seed, tokens, logps, stream);
 }
+
+namespace {
+
+// Per-step bookkeeping of a lock-step rollout, for the live paths i = 0 .. n_live-1 (path i is row rows[i] of the
+// rollout): store the sampled token (0 once the row has finished), count it, mark the row finished on an end-of-sequence
+// id or at the last step, and hand the token to the next decode step's input buffer.
+__global__ void __launch_bounds__(256)
+rollout_advance_kernel(const long long* __restrict__ tok, const long long* __restrict__ rows,
+                       unsigned char* __restrict__ finished, long long* __restrict__ out_ids,
+                       long long* __restrict__ lengths, const long long* __restrict__ eos, int n_eos, int step,
+                       int max_new, int n_live, long long* __restrict__ next_tok) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_live) return;
+  const long long r = rows[i];
+  const long long t = tok[i];
+  const bool live = finished[r] == 0;
+  out_ids[r * max_new + step] = live ? t : 0;
+  if (live) {
+    lengths[r] += 1;
+    bool done = step + 1 >= max_new;
+    for (int e = 0; e < n_eos; ++e) done = done || (t == eos[e]);
+    if (done) finished[r] = 1;
+  }
+  if (next_tok) next_tok[i] = t;
+}
+
+}  // namespace
+
+// tok, rows: int64 [n_live] (rows distinct); finished: bool [n]; out_ids: int64 [n, max_new]; lengths: int64 [n];
+// eos: int64 [n_eos] or null; next_tok: int64 [n_live] or null.
+RWKV_EXPORT int rwkv_rollout_advance(const void* tok, const void* rows, void* finished, void* out_ids, void* lengths,
+                                     const void* eos, int n_eos, int step, int max_new, int n_live, void* next_tok,
+                                     void* stream) {
+  if (n_live <= 0) return RWKV_OK;
+  if (step < 0 || step >= max_new || n_eos < 0 || (n_eos > 0 && !eos)) return RWKV_ERR_BAD_SHAPE;
+  rollout_advance_kernel<<<(n_live + 255) / 256, 256, 0, (cudaStream_t)stream>>>(
+      (const long long*)tok, (const long long*)rows, (unsigned char*)finished, (long long*)out_ids, (long long*)lengths,
+      (const long long*)eos, n_eos, step, max_new, n_live, (long long*)next_tok);
+  return rwkv_launch_status();
+}

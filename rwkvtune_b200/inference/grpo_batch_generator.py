@@ -67,8 +67,10 @@ class _DecodeGraph:
             for dst, src in zip(part_dst, part_src):
                 dst.copy_(src)
 
-    def step(self, tok: torch.Tensor) -> torch.Tensor:
-        self.tok.copy_(tok[:, None])
+    def step(self, tok: Optional[torch.Tensor]) -> torch.Tensor:
+        """Replay the captured step on ``tok``; ``None`` when the caller has already written ``self.tok``."""
+        if tok is not None:
+            self.tok.copy_(tok[:, None])
         self.graph.replay()
         return self.logits
 
@@ -213,6 +215,7 @@ class GRPOBatchGenerator:
         try:
             fused_sampler = (dev.type == "cuda" and TokenSampler.use_native_kernel and sampling_native.full_available()
                              and V <= 65536)
+            fused_advance = dev.type == "cuda" and sampling_native.advance_available()
             for step in range(max_new_tokens):
                 step_seed = None if seed is None else int(seed) * 1000003 + step
                 if fused_sampler:   # penalty, ban, temperature, bias, top-k, top-p, draw and bitmap update: one launch
@@ -225,16 +228,22 @@ class GRPOBatchGenerator:
                     if use_pen:
                         lg = apply_repetition_penalty(lg, seen.index_select(0, rows), repetition_penalty)
                     tok, _ = TokenSampler.sample_batch(lg, temperature, top_p, top_k, logit_bias, seed=step_seed)
-                live = ~finished.index_select(0, rows)
-                out_ids[rows, step] = torch.where(live, tok, torch.zeros_like(tok))
-                lengths[rows] += live.long()
                 if use_pen and not fused_sampler:
                     seen[rows, tok] = True
-                done_now = torch.zeros_like(live)
-                if eos is not None:
-                    done_now = torch.isin(tok, eos)
-                done_now |= (step + 1) >= max_new_tokens
-                finished[rows] |= done_now & live | ~live
+                fed = False
+                if fused_advance:   # token store, length count, end-of-sequence check, next step's input: one launch
+                    fed = graph is not None
+                    sampling_native.rollout_advance(tok, rows, finished, out_ids, lengths, eos, step,
+                                                    graph.tok if fed else None)
+                else:
+                    live = ~finished.index_select(0, rows)
+                    out_ids[rows, step] = torch.where(live, tok, torch.zeros_like(tok))
+                    lengths[rows] += live.long()
+                    done_now = torch.zeros_like(live)
+                    if eos is not None:
+                        done_now = torch.isin(tok, eos)
+                    done_now |= (step + 1) >= max_new_tokens
+                    finished[rows] |= done_now & live | ~live
                 steps = step + 1
                 if steps == max_new_tokens:
                     break
@@ -248,11 +257,12 @@ class GRPOBatchGenerator:
                         rows = rows.index_select(0, keep)
                         state = self._select(graph.state if graph is not None else state, keep)
                         tok = tok.index_select(0, keep)
+                        fed = False                  # another batch size: the next step's input buffer changes
                         if graph is not None:
                             graph = self._graph_for(int(keep.numel()))
                             graph.load_state(state)
                 if graph is not None:
-                    logits = graph.step(tok)
+                    logits = graph.step(None if fed else tok)
                 else:
                     logits, state = self._forward(tok[:, None], state)
         finally:

@@ -99,3 +99,18 @@ def sample_tokens(logits: torch.Tensor, temperature: float = 1.0, top_p: float =
               _ext.f32(float(repetition_penalty or 1.0)), _ext.i32(1 if (update_seen and seen_u8 is not None) else 0),
               _ext.i64(seed), _ext.ptr(tokens), _ext.ptr(logp), _ext.stream())
     return tokens, logp
+
+
+def advance_available() -> bool:
+    return _ext.available() and hasattr(_ext.lib(), "rwkv_rollout_advance")
+
+
+def rollout_advance(tok: torch.Tensor, rows: torch.Tensor, finished: torch.Tensor, out_ids: torch.Tensor,
+                    lengths: torch.Tensor, eos: Optional[torch.Tensor], step: int,
+                    next_tok: Optional[torch.Tensor] = None) -> None:
+    """One launch for the per-step bookkeeping of a lock-step rollout: ``out_ids[rows, step] = tok`` (0 for finished rows),
+    ``lengths[rows] += live``, ``finished[rows] |= tok in eos or last step``, and ``next_tok[:] = tok`` (the static input
+    of a captured decode step).  Replaces about a dozen indexing kernels per step."""
+    _ext.call("rwkv_rollout_advance", _ext.ptr(tok), _ext.ptr(rows), _ext.ptr(finished), _ext.ptr(out_ids),
+              _ext.ptr(lengths), _ext.ptr(eos), _ext.i32(0 if eos is None else eos.numel()), _ext.i32(step),
+              _ext.i32(out_ids.shape[1]), _ext.i32(tok.numel()), _ext.ptr(next_tok), _ext.stream())

@@ -171,3 +171,24 @@ def test_fused_decode_core_reproduces_the_three_kernel_path(first_block, pooled)
     else:
         same(s_new, s_ref, "state")
         assert torch.equal(state_b, s0)      # functional: the input state is untouched
+
+
+def test_fused_step_bookkeeping_equals_indexing_ops(monkeypatch):
+    """Token store, length count and end-of-sequence handling in one kernel against the same statements as tensor
+    indexing; many end-of-sequence ids, so that paths finish early and the batch is compacted on the way."""
+    from rwkvtune_b200.inference import GRPOBatchGenerator, sampling_native
+
+    model = _model()
+    prompts = [[3, 4, 5, 6], [9, 8, 11], [100, 200, 300, 400, 500], [42]]
+    outs = []
+    for fused in (True, False):
+        if not fused:
+            monkeypatch.setattr(sampling_native, "advance_available", lambda: False)
+        gen = GRPOBatchGenerator(model, _Tok(), eos_token_id=list(range(7, 160)), sync_every=2)
+        out = gen.generate(prompts, max_new_tokens=40, num_generations=6, temperature=1.0, top_p=0.95, seed=1234)
+        torch.cuda.synchronize()
+        outs.append((out["completion_ids"].cpu(), out["masks"].cpu(), out["lengths"].cpu()))
+    assert torch.equal(outs[0][2], outs[1][2])
+    assert torch.equal(outs[0][1], outs[1][1]) and torch.equal(outs[0][0], outs[1][0])
+    lengths = outs[0][2]
+    assert (lengths < 40).any() and (lengths > 1).any()       # some paths ended on an end-of-sequence id, not all at once
