@@ -204,6 +204,43 @@ def bench_decode_gemm(C, out, hbm, M=64):
     out[f"decode_gemm_M{M}_3xCxC_cublas_frac_hbm"] = 3 * C * C * 2 / ms / 1e6 / hbm
 
 
+def bench_decode_core(C, out, hbm, paths=64, layers=8):
+    """One decoding step of the recurrent core (preparation + WKV7 update + GroupNorm/bonus/gate) as one kernel against
+    the three kernels it replaces; `layers` independent state tensors (> L2 together) are walked per timed replay, as
+    the layers of a decode step are.  The floor is the state: 2 x paths x H x 64 x 64 x 4 bytes per layer."""
+    from rwkvtune_b200 import ops
+    from rwkvtune_b200.ops import cuda_ops
+    H = C // 64
+    bf = lambda s=1.0: (torch.randn(paths, 1, C, device="cuda") * s).to(BF)
+    r, k, v, w_lin, a_lin, v_lin, v_first, g = bf(), bf(), bf(), bf(0.5), bf(0.5), bf(0.5), bf(), bf()
+    par = lambda s=0.5: torch.nn.Parameter(torch.randn(1, 1, C, device="cuda") * s)
+    w0, a0, v0, k_k, k_a = par(), par(), par(), torch.nn.Parameter(par(0.3) + 0.8), torch.nn.Parameter(par(0.3) + 0.8)
+    r_k = torch.nn.Parameter(torch.randn(H, 64, device="cuda") * 0.3)
+    gn_w = torch.nn.Parameter(1 + 0.1 * torch.randn(C, device="cuda"))
+    gn_b = torch.nn.Parameter(0.1 * torch.randn(C, device="cuda"))
+    states = [torch.randn(paths, H, 64, 64, device="cuda") * 0.1 for _ in range(layers)]
+    floor_bytes = 2 * paths * H * 64 * 64 * 4
+
+    def fused():
+        for s in states:
+            ops.timemix_decode_core(r, k, v, v_first, w_lin, a_lin, v_lin, g, w0, a0, v0, k_k, k_a, r_k, gn_w, gn_b, s)
+
+    def three():
+        for s in states:
+            w, k2, v2, a_, b_ = ops.timemix_prep(k, v, v_first, w_lin, a_lin, v_lin, w0, a0, v0, k_k, k_a, 64)
+            ops.wkv7_gn(r, w, k2, v2, a_, b_, g, gn_w, gn_b, r_k, 64, state=s, return_state=True)
+
+    cuda_ops.INPLACE_STATE = True
+    try:
+        with torch.no_grad():
+            for tag, fn in (("fused", fused), ("three_kernels", three)):
+                ms = _graph_time(fn) / layers
+                out[f"decode_core_{paths}paths_{tag}_us"] = ms * 1e3
+                out[f"decode_core_{paths}paths_{tag}_frac_hbm"] = floor_bytes / ms / 1e6 / hbm
+    finally:
+        cuda_ops.INPLACE_STATE = False
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--only", default="")
@@ -225,6 +262,8 @@ def main():
         bench_loss(a.C, out, hbm)
     if not only or "decode" in only:
         bench_decode_gemm(a.C, out, hbm)
+    if not only or "decode_core" in only:
+        bench_decode_core(a.C, out, hbm)
     for k, v in out.items():
         print(f"{k}: {v:.4g}" if isinstance(v, float) else f"{k}: {v}")
     if a.json:

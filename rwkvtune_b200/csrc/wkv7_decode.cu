@@ -106,7 +106,7 @@ __device__ __forceinline__ float dc_head_total(float mine, float* vals, float* s
   return *slot;
 }
 
-__global__ void __launch_bounds__(DC_THREADS, 8)
+__global__ void __launch_bounds__(DC_THREADS, 7)
 wkv7_decode_core_kernel(const DecodeCoreArgs A) {
   __shared__ __align__(16) float in[DC_NIN][DC_N];   // r, decay, k', v', -kk, kk a of this head
   __shared__ __align__(16) float sabuf[DC_N];
@@ -121,13 +121,16 @@ wkv7_decode_core_kernel(const DecodeCoreArgs A) {
   const int ch = h * DC_N + (prep ? tid : 0);
 
   // parameters do not depend on the predecessor kernel
-  float w0 = 0.f, a0 = 0.f, v0 = 0.f, kk_p = 0.f, ka_p = 0.f;
+  float w0 = 0.f, a0 = 0.f, v0 = 0.f, kk_p = 0.f, ka_p = 0.f, gw = 0.f, gb = 0.f, rk = 0.f;
   if (prep) {
     w0 = A.w0[ch];
     a0 = A.a0[ch];
     if (A.vfirst) v0 = A.v0[ch];
     kk_p = A.k_k[ch];
     ka_p = A.k_a[ch];
+    gw = A.gn_w[ch];     // needed last, requested first: no memory round trip left in the GroupNorm phase
+    gb = A.gn_b[ch];
+    rk = A.r_k[ch];
   }
   rwkv_chain_wait();
 
@@ -209,7 +212,6 @@ wkv7_decode_core_kernel(const DecodeCoreArgs A) {
   __syncthreads();
 
   if (prep) {   // GroupNorm over the head, bonus, gate
-    const float gw = A.gn_w[ch], gb = A.gn_b[ch], rk = A.r_k[ch];
     const float yf = round_bf16(ybuf[tid]);
     const float s = dc_head_total(yf, scratch[0], &totals[1], tid);
     const float bonus = dc_head_total(in[DQ][tid] * in[DK_][tid] * rk, scratch[1], &totals[2], tid);
