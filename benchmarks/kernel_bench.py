@@ -175,8 +175,10 @@ def _graph_time(fn):
     microsecond kernels would measure the host)."""
     fn()
     torch.cuda.synchronize()
+    from rwkvtune_b200.ops import _ext
+
     g = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(g):
+    with _ext.capture_safe_gc(), torch.cuda.graph(g):
         fn()
     return timeit(g.replay)
 

@@ -117,3 +117,35 @@ RWKV_EXPORT int rwkv_adamw_step(void* master, void* m, void* v, const void* grad
                                                (bf16*)param_out, (size_t)n, (const float*)norm_sq, a);
   return rwkv_launch_status();
 }
+
+namespace {
+
+// out[w] = sum_r partials[r][w]: the per-CTA partial sums of a parameter gradient ([rows, W] fp32, rows = CTAs of the
+// backward kernel, W = a few thousand) into the gradient.  A block owns 32 columns: 8 row groups of 32 lanes read
+// 128 contiguous bytes each and stride over the rows, then the 8 groups meet in shared memory (fixed order).
+__global__ void __launch_bounds__(256)
+colsum_kernel(const float* __restrict__ partials, int rows, long long W, float* __restrict__ out) {
+  __shared__ float part[8][32];
+  const int lane = threadIdx.x & 31, grp = threadIdx.x >> 5;
+  const long long col = (long long)blockIdx.x * 32 + lane;
+  float acc = 0.f;
+  if (col < W)
+    for (int r = grp; r < rows; r += 8) acc += partials[(long long)r * W + col];
+  part[grp][lane] = acc;
+  __syncthreads();
+  if (grp == 0 && col < W) {
+    float s = 0.f;
+#pragma unroll
+    for (int g = 0; g < 8; ++g) s += part[g][lane];
+    out[col] = s;
+  }
+}
+
+}  // namespace
+
+// partials: fp32 [rows, W] contiguous; out: fp32 [W].
+RWKV_EXPORT int rwkv_colsum_f32(const void* partials, int rows, long long W, void* out, void* stream) {
+  if (rows <= 0 || W <= 0) return RWKV_ERR_BAD_SHAPE;
+  colsum_kernel<<<(unsigned)((W + 31) / 32), 256, 0, (cudaStream_t)stream>>>((const float*)partials, rows, W, (float*)out);
+  return rwkv_launch_status();
+}

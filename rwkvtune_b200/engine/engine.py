@@ -217,8 +217,10 @@ class TrainEngine:
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         entry = {"graph": torch.cuda.CUDAGraph()}
+        from ..ops import _ext
+
         with torch.cuda.stream(side):
-            with torch.cuda.graph(entry["graph"], stream=side):
+            with _ext.capture_safe_gc(), torch.cuda.graph(entry["graph"], stream=side):
                 entry.update(build())
         torch.cuda.current_stream().wait_stream(side)
         self._graphs[key] = entry

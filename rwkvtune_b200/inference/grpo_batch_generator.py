@@ -16,11 +16,13 @@ from __future__ import annotations
 
 import contextlib
 import time
+import weakref
 from typing import Any, Dict, List, Optional, Sequence
 
 import torch
 
 from .. import ops
+from ..ops import _ext as _ext_mod
 from . import sampling_native
 from .core import TokenSampler, apply_repetition_penalty
 
@@ -33,7 +35,7 @@ class _DecodeGraph:
     def __init__(self, gen: "GRPOBatchGenerator", n: int):
         from ..ops import cuda_ops
 
-        self.gen, self.n = gen, n
+        self.gen, self.n = weakref.proxy(gen), n      # no cycle generator <-> graph: both die by reference count
         dev = gen.device
         self.tok = torch.zeros(n, 1, dtype=torch.long, device=dev)
         self.state = gen._zero_state(n)
@@ -46,7 +48,7 @@ class _DecodeGraph:
                     self._body()
             torch.cuda.current_stream(dev).wait_stream(side)
             self.graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(self.graph):
+            with _ext_mod.capture_safe_gc(), torch.cuda.graph(self.graph):
                 self.logits = self._body()
         finally:
             cuda_ops.INPLACE_STATE = False

@@ -107,9 +107,30 @@ def launch_count() -> int:
     return LAUNCH_COUNT
 
 
-# ------------------------------------------------------------------------------- chained launches
 import contextlib as _contextlib
 import os as _os
+
+
+# ------------------------------------------------------------------------------- graph capture hygiene
+@_contextlib.contextmanager
+def capture_safe_gc():
+    """Wrap a CUDA-graph capture.  Collects cyclic garbage first and keeps the collector off while capturing: an old
+    ``CUDAGraph`` (or anything else whose finaliser frees device memory) that the cycle collector happens to reclaim in
+    the middle of a capture makes a CUDA call that is illegal there and invalidates the capture - at a point that
+    depends on allocation counts, i.e. not reproducibly."""
+    import gc
+
+    gc.collect()
+    was_enabled = gc.isenabled()
+    gc.disable()
+    try:
+        yield
+    finally:
+        if was_enabled:
+            gc.enable()
+
+
+# ------------------------------------------------------------------------------- chained launches
 
 _CHAINING = False
 CHAINING_ALLOWED = _os.environ.get("RWKVTUNE_CHAINED_LAUNCH", "1") == "1"
