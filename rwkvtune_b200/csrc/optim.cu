@@ -123,8 +123,9 @@ namespace {
 // out[w] = sum_r partials[r][w]: the per-CTA partial sums of a parameter gradient ([rows, W] fp32, rows = CTAs of the
 // backward kernel, W = a few thousand) into the gradient.  A block owns 32 columns: 8 row groups of 32 lanes read
 // 128 contiguous bytes each and stride over the rows, then the 8 groups meet in shared memory (fixed order).
+template <typename OutT>
 __global__ void __launch_bounds__(256)
-colsum_kernel(const float* __restrict__ partials, int rows, long long W, float* __restrict__ out) {
+colsum_kernel(const float* __restrict__ partials, int rows, long long W, OutT* __restrict__ out) {
   __shared__ float part[8][32];
   const int lane = threadIdx.x & 31, grp = threadIdx.x >> 5;
   const long long col = (long long)blockIdx.x * 32 + lane;
@@ -137,15 +138,20 @@ colsum_kernel(const float* __restrict__ partials, int rows, long long W, float* 
     float s = 0.f;
 #pragma unroll
     for (int g = 0; g < 8; ++g) s += part[g][lane];
-    out[col] = s;
+    if constexpr (sizeof(OutT) == 2) out[col] = __float2bfloat16_rn(s);
+    else out[col] = s;
   }
 }
 
 }  // namespace
 
-// partials: fp32 [rows, W] contiguous; out: fp32 [W].
-RWKV_EXPORT int rwkv_colsum_f32(const void* partials, int rows, long long W, void* out, void* stream) {
+// partials: fp32 [rows, W] contiguous; out: [W], fp32 (out_bf16 = 0) or bf16 (1: the sum is rounded once, at the end).
+RWKV_EXPORT int rwkv_colsum_f32(const void* partials, int rows, long long W, void* out, int out_bf16, void* stream) {
   if (rows <= 0 || W <= 0) return RWKV_ERR_BAD_SHAPE;
-  colsum_kernel<<<(unsigned)((W + 31) / 32), 256, 0, (cudaStream_t)stream>>>((const float*)partials, rows, W, (float*)out);
+  const unsigned blocks = (unsigned)((W + 31) / 32);
+  if (out_bf16)
+    colsum_kernel<bf16><<<blocks, 256, 0, (cudaStream_t)stream>>>((const float*)partials, rows, W, (bf16*)out);
+  else
+    colsum_kernel<float><<<blocks, 256, 0, (cudaStream_t)stream>>>((const float*)partials, rows, W, (float*)out);
   return rwkv_launch_status();
 }

@@ -208,14 +208,16 @@ def _f32(t: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def _colsum(partials: torch.Tensor) -> torch.Tensor:
-    """``partials.sum(0)`` for the fp32 per-CTA partial sums ``[n_cta, ...]`` of a backward kernel: one small kernel
-    with coalesced column reads (the framework's reduction takes 28 us for 592 x 6144, this one a few)."""
+def _colsum(partials: torch.Tensor, dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """``partials.sum(0)`` for the fp32 per-CTA partial sums ``[n_cta, ...]`` of a backward kernel, delivered in the
+    parameters' ``dtype``: one small kernel with coalesced column reads (the framework's reduction takes 28 us for
+    592 x 6144 and each bf16 parameter gradient then needs a conversion launch of its own)."""
     if not (partials.is_cuda and partials.dtype == torch.float32 and partials.is_contiguous()
-            and hasattr(_ext.lib(), "rwkv_colsum_f32")):
-        return partials.sum(0)
-    out = torch.empty(partials.shape[1:], dtype=torch.float32, device=partials.device)
-    call("rwkv_colsum_f32", ptr(partials), i32(partials.shape[0]), i64(out.numel()), ptr(out), stream())
+            and dtype in (torch.float32, BF16) and hasattr(_ext.lib(), "rwkv_colsum_f32")):
+        return partials.sum(0).to(dtype)
+    out = torch.empty(partials.shape[1:], dtype=dtype, device=partials.device)
+    call("rwkv_colsum_f32", ptr(partials), i32(partials.shape[0]), i64(out.numel()), ptr(out), i32(1 if dtype == BF16 else 0),
+         stream())
     return out
 
 
@@ -267,7 +269,7 @@ def _ln_shift_mix_backward(ctx, d_list, d_last, d_res=None):
     call("rwkv_ln_shift_mix_backward", dptrs, ptr(dl), ptr(dr), ptr(xb), ptr(mean), ptr(rstd), ptr(w32), ptr(b32),
          ptr(m32), ptr(pv), ptr(dx), ptr(dprev), ptr(partials), i32(K), i32(B), i32(T), i32(C), i32(strip),
          stream())
-    sums = _colsum(partials)
+    sums = _colsum(partials, mix.dtype if mix.dtype == ln_w.dtype == ln_b.dtype else torch.float32)
     dmix = sums[:K].reshape(mix.shape).to(mix.dtype)
     dw = sums[K].reshape(ln_w.shape).to(ln_w.dtype)
     db = sums[K + 1].reshape(ln_b.shape).to(ln_b.dtype)
@@ -344,7 +346,7 @@ class _LayerNorm(torch.autograd.Function):
         partials = torch.empty(-(-rows // strip), 2, C, dtype=torch.float32, device=xb.device)
         call("rwkv_layer_norm_backward", ptr(dyb), ptr(xb), ptr(mean), ptr(rstd), ptr(w32), ptr(dx), ptr(partials),
              i32(rows), i32(C), i32(strip), stream())
-        sums = _colsum(partials)
+        sums = _colsum(partials, w.dtype if w.dtype == b.dtype else torch.float32)
         return dx.reshape(shape).to(xdt), sums[0].reshape(w.shape).to(w.dtype), sums[1].reshape(b.shape).to(b.dtype), None
 
 
@@ -401,7 +403,7 @@ class _TimemixPrep(torch.autograd.Function):
         call("rwkv_timemix_prep_backward", ptr(gw), ptr(gk), ptr(gv), ptr(gan), ptr(gb), ptr(kb), ptr(vb), ptr(vf),
              ptr(wl), ptr(al), ptr(vl), ptr(w0), ptr(a0), ptr(v0), ptr(k_k), ptr(k_a), ptr(dk), ptr(dv), ptr(dvf),
              ptr(dwl), ptr(dal), ptr(dvl), ptr(partials), i32(B), i32(T), i32(C), i32(strip), stream())
-        s = _colsum(partials)
+        s = _colsum(partials, pdtypes[0] if len(set(pdtypes)) == 1 else torch.float32)
         cast = (lambda t: t.to(dt)) if dt != BF16 else (lambda t: t)
         dw0 = s[0].reshape(pshapes[0]).to(pdtypes[0])
         da0 = s[1].reshape(pshapes[1]).to(pdtypes[1])
@@ -445,7 +447,7 @@ class _GnBonusGate(torch.autograd.Function):
         call("rwkv_gn_bonus_gate_backward", ptr(dzb), ptr(yb), ptr(rb), ptr(kb), ptr(vb), ptr(gb_), ptr(gw), ptr(gb),
              ptr(rk), ptr(dy), ptr(dr), ptr(dk), ptr(dv), ptr(dg), ptr(partials), i32(B), i32(T), i32(C), i32(strip),
              f32(eps), stream())
-        s = _colsum(partials)
+        s = _colsum(partials, dts[0] if len(set(dts)) == 1 else torch.float32)
         cast = (lambda t: t.to(dt)) if dt != BF16 else (lambda t: t)
         return (cast(dy), cast(dr), cast(dk), cast(dv), cast(dg), s[0].reshape(shp[0]).to(dts[0]),
                 s[1].reshape(shp[1]).to(dts[1]), s[2].reshape(shp[2]).to(dts[2]), None)
@@ -508,7 +510,7 @@ class _WKV7GN(torch.autograd.Function):
         call("rwkv_wkv7_tc_backward", ptr(r), ptr(w), ptr(k), ptr(v), ptr(a), ptr(b), ptr(dy), ptr(cs), ptr(ds_T),
              ptr(dstates), ptr(ws), i32(1 if kept else 0), ptr(dr), ptr(dw), ptr(dk), ptr(dv), ptr(da), ptr(db),
              ptr(ds0), i32(1), i32(B), i32(T), i32(H), stream())
-        s = _colsum(partials)
+        s = _colsum(partials, dts[0] if len(set(dts)) == 1 else torch.float32)
         return (dr, dw, dk, dv, da, db, dg, s[0].reshape(shp[0]).to(dts[0]), s[1].reshape(shp[1]).to(dts[1]),
                 s[2].reshape(shp[2]).to(dts[2]), ds0, None, None)
 
