@@ -19,11 +19,21 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
+_RENDEZVOUS_TROUBLE = ("address already in use", "eaddrinuse", "connection refused", "connection reset",
+                       "failed to connect", "rendezvous", "socket timeout")
+
+
 def _launch(script_path, nproc, *args, timeout=420, expect_fail=False):
     env = dict(os.environ, RWKV_ROOT=ROOT, OMP_NUM_THREADS="1", PYTHONPATH=ROOT)
-    res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(nproc),
-                          "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), str(script_path), *map(str, args)],
-                         capture_output=True, text=True, env=env, timeout=timeout, cwd=ROOT)
+    res = None
+    for attempt in range(2):
+        res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(nproc),
+                              "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), str(script_path),
+                              *map(str, args)], capture_output=True, text=True, env=env, timeout=timeout, cwd=ROOT)
+        # a port that was free a moment ago can be taken before the launcher binds it: that, and only that, is retried
+        trouble = res.returncode != 0 and any(t in (res.stdout + res.stderr).lower() for t in _RENDEZVOUS_TROUBLE)
+        if not (trouble and attempt == 0 and not expect_fail):
+            break
     if not expect_fail:
         assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
     return res
