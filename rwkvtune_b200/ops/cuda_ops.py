@@ -776,7 +776,7 @@ def timemix_decode_core_ok(r, g, state, head_size: int) -> bool:
     """One token per sequence, bf16, head size 64, an existing fp32 state (tensor, or ``(pool, slots)``), no autograd,
     and the fused kernel present in the library."""
     if not (r.is_cuda and r.dim() == 3 and r.shape[1] == 1 and r.dtype == BF16 and g.dtype == BF16 and head_size == 64
-            and r.shape[-1] % 64 == 0 and not torch.is_grad_enabled() and state is not None):
+            and r.shape[-1] % 64 == 0 and 0 < r.shape[0] <= 65535 and not torch.is_grad_enabled() and state is not None):
         return False
     from . import _ext
 
