@@ -194,7 +194,7 @@ def _f32(t: torch.Tensor) -> torch.Tensor:
     if hit is not None and hit[0] == stamp:
         return hit[1]
     if hit is not None:
-        if hit[0][0] != _PARAM_EPOCH and not torch.cuda.is_current_stream_capturing():
+        if hit[0][0] != _PARAM_EPOCH and not (t.is_cuda and torch.cuda.is_current_stream_capturing()):
             _refresh_f32_cache()          # an optimiser step has passed: refresh all copies together
             hit = _F32_CACHE.get(key)
             if hit is not None and hit[0] == stamp:

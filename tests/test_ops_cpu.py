@@ -85,3 +85,37 @@ def test_gemm_wrappers_fall_back_on_cpu():
     assert gemm.addmm_tn_(y, a, b) is y and torch.allclose(y, 1 + a.t() @ b, atol=1e-5)
     x, w = torch.randn(5, 6), torch.randn(7, 6)
     assert torch.allclose(gemm.mm_nt(x, w), x @ w.t()) and torch.allclose(gemm.mm_nn(x, w.t().contiguous()), x @ w.t())
+
+
+def test_cached_fp32_parameter_copies_refresh_together_after_an_optimiser_step():
+    """The fp32 copies of small parameters are cached; after the parameters were rewritten behind autograd's back
+    (the optimiser kernels write through raw pointers) one multi-tensor copy brings every cached copy up to date."""
+    import torch
+
+    from rwkvtune_b200.ops import cuda_ops
+
+    params = [torch.nn.Parameter(torch.randn(1, 1, 16).to(torch.bfloat16)) for _ in range(5)]
+    first = [cuda_ops._f32(p) for p in params]
+    assert all(c.dtype == torch.float32 and torch.equal(c, p.detach().reshape(-1).float()) for c, p in zip(first, params))
+    assert all(cuda_ops._f32(p) is c for p, c in zip(params, first))          # cached: same storage
+    with torch.no_grad():
+        for p in params:
+            p.data.add_(1.0)            # .data: no version bump, as with a raw-pointer write
+    assert torch.equal(cuda_ops._f32(params[0]), first[0])                     # stale until told
+    cuda_ops.bump_param_epoch()
+    again = cuda_ops._f32(params[0])                                           # refreshes all five at once
+    assert again is first[0]
+    for p, c in zip(params, first):
+        assert torch.equal(c, p.detach().reshape(-1).float())
+        key = (p.data_ptr(), p.numel(), p.dtype)
+        assert cuda_ops._F32_CACHE[key][0] == (cuda_ops._PARAM_EPOCH, p._version)
+    del params, first, again
+    import gc
+
+    gc.collect()
+    cuda_ops.bump_param_epoch()
+    live = torch.nn.Parameter(torch.randn(8).to(torch.bfloat16))
+    cuda_ops._f32(live)
+    cuda_ops.bump_param_epoch()
+    cuda_ops._f32(live)                                                        # dead entries are dropped on refresh
+    assert all(ref_() is not None for _, _, ref_ in cuda_ops._F32_CACHE.values())
