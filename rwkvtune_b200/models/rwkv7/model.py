@@ -79,6 +79,8 @@ def _project_add(layer: nn.Module, h: torch.Tensor, residual: torch.Tensor, pref
             return out[0][0]
     if type(layer) is Linear and getattr(layer, "_sharded", None) is None:
         return ops.linear_add(h, layer.weight, residual)
+    if getattr(layer, "lora_A", None) is not None:      # adapter layer: the residual sum rides in its fused GEMM
+        return layer(h, residual=residual)
     return residual + layer(h)
 
 
@@ -278,7 +280,9 @@ class RWKV7ChannelMix(nn.Module):
             return ops.channel_mix_ffn(xk, self.key.weight, self.value.weight, x), (last if want_state else None)
         if type(self.key) is Linear and getattr(self.key, "_sharded", None) is None:
             hidden = ops.linear_relu_sq(xk, self.key.weight)
-        else:   # wrapped (LoRA) or sharded (ZeRO-3): activation applied separately
+        elif getattr(self.key, "lora_A", None) is not None:     # adapter layer: relu^2 in the epilogue of its fused GEMM
+            hidden = self.key(xk, act="relu_sq")
+        else:   # sharded (ZeRO-3): activation applied separately
             hidden = ops.relu_squared(self.key(xk))
         return _project_add(self.value, hidden, x), (last if want_state else None)
 

@@ -168,13 +168,21 @@ def _acc_ok(n, y: torch.Tensor) -> bool:
             and y.data_ptr() % 16 == 0 and (y.stride(0) * 2) % 16 == 0)
 
 
-def mm_nt_plus(x: torch.Tensor, w: torch.Tensor, x2: torch.Tensor, w2: torch.Tensor) -> torch.Tensor:
-    """``x @ w^T + x2 @ w2^T`` (``w [N, K]``, ``w2 [N, K2]``).  On the native path ONE GEMM launch whose contraction
-    runs over ``K`` then ``K2`` (the LoRA linear: ``x2 = s x A^T``, ``w2 = B``); otherwise a GEMM and an accumulate."""
+def mm_nt_plus(x: torch.Tensor, w: torch.Tensor, x2: torch.Tensor, w2: torch.Tensor, act: str = None,
+               residual: torch.Tensor = None) -> torch.Tensor:
+    """``x @ w^T + x2 @ w2^T`` (``w [N, K]``, ``w2 [N, K2]``), optionally ``relu(.)^2`` (``act="relu_sq"``) or plus a
+    ``residual [M, N]`` (not both).  On the native path ONE GEMM launch whose contraction runs over ``K`` then ``K2`` (the
+    LoRA linear: ``x2 = s x A^T``, ``w2 = B``) with the activation / residual sum in its epilogue; otherwise a GEMM, an
+    accumulate and a separate element-wise pass."""
+    if act not in (None, "relu_sq") or (act is not None and residual is not None):
+        raise ValueError("mm_nt_plus: act is None or 'relu_sq', and never together with a residual")
     n = _native()
-    if n is not None and n.dual_ok(x, w, x2, w2, "nt"):
-        return n.mm_nt_dual(x, w, x2, w2)
-    return addmm_nt_(mm_nt(x, w), x2, w2)
+    if n is not None and n.dual_ok(x, w, x2, w2, "nt") and (residual is None or _acc_ok(n, residual)):
+        return n.mm_nt_dual(x, w, x2, w2, epilogue=1 if act else 0, residual=residual)
+    y = addmm_nt_(mm_nt(x, w), x2, w2)
+    if act:
+        y = torch.relu(y) ** 2
+    return y if residual is None else y + residual
 
 
 def mm_nn_plus(x: torch.Tensor, w: torch.Tensor, x2: torch.Tensor, w2: torch.Tensor) -> torch.Tensor:

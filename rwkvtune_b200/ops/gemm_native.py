@@ -158,9 +158,11 @@ def dual_ok(x: torch.Tensor, w: torch.Tensor, x2: torch.Tensor, w2: torch.Tensor
     return shapes and x2.shape[0] == M and K2 > 0 and two_cta_ok(M, N, K, 0)
 
 
-def mm_nt_dual(x, w, x2, w2) -> torch.Tensor:
-    """``x [M,K] @ w[N,K]^T + x2 [M,K2] @ w2[N,K2]^T``: the second product rides as extra K blocks of the first."""
-    return _run_2cta(x, w, x.shape[0], w.shape[0], x.shape[1], 0, 0, a2=x2, b2=w2, K2=x2.shape[1])
+def mm_nt_dual(x, w, x2, w2, epilogue: int = 0, residual: torch.Tensor = None) -> torch.Tensor:
+    """``x [M,K] @ w[N,K]^T + x2 [M,K2] @ w2[N,K2]^T``: the second product rides as extra K blocks of the first.
+    ``epilogue=1``: relu(.)^2 of the sum; ``residual`` ([M,N] bf16): added in the epilogue."""
+    return _run_2cta(x, w, x.shape[0], w.shape[0], x.shape[1], 0, 0, epilogue=epilogue, residual=residual, a2=x2, b2=w2,
+                     K2=x2.shape[1])
 
 
 def mm_nn_dual(x, w, x2, w2) -> torch.Tensor:

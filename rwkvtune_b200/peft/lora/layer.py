@@ -17,34 +17,53 @@ import torch.nn as nn
 from ...ops import gemm
 
 
+def _relu_sq_grad(y: torch.Tensor, dy: torch.Tensor) -> torch.Tensor:
+    """Gradient of ``relu(p)^2`` with respect to ``p`` expressed through its output ``y``: ``dy * 2 sqrt(y)``."""
+    if y.is_cuda and y.dtype == torch.bfloat16 and y.numel() % 8 == 0:
+        from ...ops import _ext
+
+        if _ext.available():
+            dyc = dy if dy.is_contiguous() else dy.contiguous()
+            out = torch.empty_like(y)
+            _ext.call("rwkv_relu_sq_backward", _ext.ptr(y), _ext.ptr(dyc), _ext.ptr(out), _ext.i64(y.numel()), _ext.i32(1),
+                      _ext.stream())
+            return out
+    return (dy.float() * 2.0 * y.float().sqrt()).to(dy.dtype)
+
+
 class _LoraLinearFn(torch.autograd.Function):
+    """``act(x W^T + s (x A^T) B^T) + residual`` (``act`` = identity or relu^2; a residual only without activation)."""
+
     @staticmethod
-    def forward(ctx, x, w, a, b, scaling: float, w_needs_grad: bool):
+    def forward(ctx, x, w, a, b, scaling: float, w_needs_grad: bool, residual=None, act=None):
         x2 = x.reshape(-1, x.shape[-1])
-        xa = gemm.mm_nt(x2, a)                       # [M, r]
-        # scale the [M, r] factor; its product with B rides as the last K block of the base GEMM (one launch, no
-        # read-modify-write of y)
-        y = gemm.mm_nt_plus(x2, w, xa * scaling, b)
-        ctx.save_for_backward(x2, w, a, b, xa)
-        ctx.scaling, ctx.shape = scaling, x.shape
+        xa_s = gemm.mm_nt(x2, a) * scaling           # [M, r], scaled once: used by the forward and by dB
+        r2 = None if residual is None else residual.reshape(-1, residual.shape[-1])
+        # the product with B rides as the last K block of the base GEMM (one launch, no read-modify-write of y);
+        # activation or residual sum in the same launch's epilogue
+        y = gemm.mm_nt_plus(x2, w, xa_s, b, act=act, residual=r2)
+        ctx.save_for_backward(x2, w, a, b, xa_s, y if act else None)
+        ctx.scaling, ctx.shape, ctx.act = scaling, x.shape, act
         return y.reshape(*x.shape[:-1], w.shape[0])
 
     @staticmethod
     def backward(ctx, dy):
-        x2, w, a, b, xa = ctx.saved_tensors
+        x2, w, a, b, xa_s, y = ctx.saved_tensors
         s = ctx.scaling
         dy2 = dy.reshape(-1, dy.shape[-1])
-        dyb = gemm.mm_nn(dy2, b)                     # [M, r]
+        dpre = _relu_sq_grad(y, dy2) if ctx.act else dy2
+        dyb_s = gemm.mm_nn(dpre, b) * s              # [M, r], scaled once: used by dx and by dA
         dx = dw = da = db = None
         if ctx.needs_input_grad[0]:
-            dx = gemm.mm_nn_plus(dy2, w, dyb * s, a).reshape(ctx.shape)
+            dx = gemm.mm_nn_plus(dpre, w, dyb_s, a).reshape(ctx.shape)
         if ctx.needs_input_grad[1]:
-            dw = gemm.mm_tn(dy2, x2)
+            dw = gemm.mm_tn(dpre, x2)
         if ctx.needs_input_grad[2]:
-            da = gemm.mm_tn(dyb, x2) * s
+            da = gemm.mm_tn(dyb_s, x2)
         if ctx.needs_input_grad[3]:
-            db = gemm.mm_tn(dy2, xa) * s
-        return dx, dw, da, db, None, None
+            db = gemm.mm_tn(dpre, xa_s)
+        d_res = dy if (len(ctx.needs_input_grad) > 6 and ctx.needs_input_grad[6]) else None
+        return dx, dw, da, db, None, None, d_res, None
 
 
 class LoraLinear(nn.Module):
@@ -85,7 +104,25 @@ class LoraLinear(nn.Module):
             return self.base_layer.weight
         return self.base_layer.weight + (self.lora_B @ self.lora_A) * self.scaling
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, residual: torch.Tensor = None, act: str = None) -> torch.Tensor:
+        """``act(base(x) + adapter(x)) + residual``; ``act`` is ``None`` or ``"relu_sq"`` (never with a residual).  On
+        the training path both ride in the epilogue of the single fused GEMM launch."""
+        if act is not None and residual is not None:
+            raise ValueError("LoraLinear: an activation and a residual cannot be combined")
+        fused = (getattr(self, "_sharded", None) is None and not (self.disabled or self.merged)
+                 and not (not torch.is_grad_enabled() and x.is_cuda and x.numel() // x.shape[-1] <= 256)
+                 and not (isinstance(self.lora_dropout, nn.Dropout) and self.training))
+        if fused:
+            return _LoraLinearFn.apply(x, self.base_layer.weight, self.lora_A, self.lora_B, self.scaling,
+                                       self.base_layer.weight.requires_grad, residual, act)
+        y = self._plain_forward(x)
+        if act == "relu_sq":
+            from ... import ops
+
+            y = ops.relu_squared(y)
+        return y if residual is None else residual + y
+
+    def _plain_forward(self, x: torch.Tensor) -> torch.Tensor:
         sw = getattr(self, "_sharded", None)
         if sw is not None:   # ZeRO-3 sharded frozen base weight
             from ...parallel.zero3 import ag_linear, lora_ag_linear
@@ -96,16 +133,13 @@ class LoraLinear(nn.Module):
         if self.disabled or self.merged:
             return self.base_layer(x)
         if not torch.is_grad_enabled() and x.is_cuda and x.numel() // x.shape[-1] <= 256:
-            # decode-sized batch: three library GEMMs, the adapter product added by the last one (beta = 1, alpha = scaling)
+            # decode-sized batch outside the grouped path: three library GEMMs, the adapter product added by the last one
             x2 = x.reshape(-1, x.shape[-1])
             y = torch.addmm(x2 @ self.base_layer.weight.t(), x2 @ self.lora_A.t(), self.lora_B.t(), alpha=self.scaling)
             return y.reshape(*x.shape[:-1], self.out_features)
-        if isinstance(self.lora_dropout, nn.Dropout) and self.training:
-            base = self.base_layer(x)
-            xd = self.lora_dropout(x)
-            return base + gemm.linear(gemm.linear(xd, self.lora_A), self.lora_B) * self.scaling
-        return _LoraLinearFn.apply(x, self.base_layer.weight, self.lora_A, self.lora_B, self.scaling,
-                                   self.base_layer.weight.requires_grad)
+        base = self.base_layer(x)
+        xd = self.lora_dropout(x)
+        return base + gemm.linear(gemm.linear(xd, self.lora_A), self.lora_B) * self.scaling
 
     def decode_spec(self):
         """``(weight, adapter)`` for the grouped decode path: ``adapter`` is ``None`` (merged or disabled) or

@@ -729,9 +729,11 @@ def test_gemm_second_operand_pair_along_k(layout, K2):
     assert gemm_native.check_status() == 0
 
 
-def test_lora_linear_single_launch_forward_and_dgrad():
+@pytest.mark.parametrize("mode", ["plain", "residual", "relu_sq"])
+def test_lora_linear_single_launch_forward_and_dgrad(mode):
     """LoRA linear at a training shape: y and dx each come from one GEMM launch with the rank-r term appended to the
-    contraction; values and all gradients against the fp32 statement of the same layer."""
+    contraction, the residual sum or relu^2 in that launch's epilogue; values and all gradients against the fp32
+    statement of the same layer."""
     from rwkvtune_b200.ops import _ext
     from rwkvtune_b200.peft.lora.layer import LoraLinear
     torch.manual_seed(11)
@@ -742,20 +744,29 @@ def test_lora_linear_single_launch_forward_and_dgrad():
     with torch.no_grad():
         layer.lora_B.normal_(0, 0.02)
     x = (torch.randn(M, Cin, device="cuda") * 0.5).to(BF).requires_grad_(True)
+    res = torch.randn(M, Cout, device="cuda").to(BF).requires_grad_(True) if mode == "residual" else None
     dy = (torch.randn(M, Cout, device="cuda") * 0.1).to(BF)
     before = _ext.launch_count()
-    y = layer(x)
+    y = layer(x, residual=res, act="relu_sq" if mode == "relu_sq" else None)
     fwd_launches = _ext.launch_count() - before
     y.backward(dy)
     assert fwd_launches == 2            # x A^T, then the base product with the adapter term as its last K block
     xf, W, A, B = x.detach().float(), base.weight.float(), layer.lora_A.float(), layer.lora_B.float()
     s = layer.scaling
-    ref_y = xf @ W.t() + s * (xf @ A.t()) @ B.t()
-    ref_dx = dy.float() @ W + s * (dy.float() @ B) @ A
-    ref_da = s * (dy.float() @ B).t() @ xf
-    ref_db = s * dy.float().t() @ (xf @ A.t())
+    pre = xf @ W.t() + s * (xf @ A.t()) @ B.t()
+    if mode == "relu_sq":
+        ref_y = torch.relu(pre) ** 2
+        dpre = dy.float() * 2 * torch.relu(pre)
+    else:
+        ref_y = pre + (res.detach().float() if res is not None else 0)
+        dpre = dy.float()
+    ref_dx = dpre @ W + s * (dpre @ B) @ A
+    ref_da = s * (dpre @ B).t() @ xf
+    ref_db = s * dpre.t() @ (xf @ A.t())
     for got, want in ((y, ref_y), (x.grad, ref_dx), (layer.lora_A.grad, ref_da), (layer.lora_B.grad, ref_db)):
         assert (got.float() - want).abs().max().item() <= 2e-2 * want.abs().max().item() + 1e-2
+    if res is not None:
+        assert torch.equal(res.grad, dy)
 
 
 @pytest.mark.parametrize("layout", ["nt", "nn"])
