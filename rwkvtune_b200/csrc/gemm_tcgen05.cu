@@ -522,9 +522,10 @@ int launch_splitk(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMa
   return rwkv_launch_status();
 }
 
+template <int EPI>
 int launch_ag(CUtensorMap ma, CUtensorMap mb, CUtensorMap mc, int M, int N, int K, int* status, int sms,
-              AgParams ag, int* arrivals_io, cudaStream_t st) {
-  auto kern = gemm_tcgen05_kernel<false, false, 0, true>;
+              AgParams ag, int* arrivals_io, const bf16* c_in, long long ldc, cudaStream_t st) {
+  auto kern = gemm_tcgen05_kernel<false, false, EPI, true>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
@@ -538,8 +539,6 @@ int launch_ag(CUtensorMap ma, CUtensorMap mb, CUtensorMap mc, int M, int N, int 
   ag.target = *arrivals_io;
   // tile producers wait for copy warps of other CTAs of the same grid: a cooperative launch guarantees that all
   // CTAs are resident together
-  const bf16* c_in = nullptr;
-  long long ldc = 0;
   int splits = 1;
   float* partial = nullptr;
   void* args[] = {&ma, &mb, &mc, &M, &N, &K, &status, &c_in, &ldc, &splits, &partial, &ag};
@@ -633,12 +632,14 @@ RWKV_EXPORT int rwkv_gemm_bf16_tcgen05_splitk(const void* a, const void* b, void
 // device ints, zero-initialised once; *arrivals_io: host-side running total of arrivals per counter (0 before the
 // first call on these buffers), advanced by this call.
 // x2 / w2 (optional): a second, local operand pair ([M, K2] and [N, K2], row-major contiguous) appended to the
-// contraction: y = x W^T + x2 w2^T.
-RWKV_EXPORT int rwkv_ag_gemm_bf16_tcgen05_dual(const void* x, const unsigned long long* shard_ptrs, void* staged, void* y,
-                                               int M, int N, int K, int rank, int world, void* blk_count,
-                                               int* arrivals_io, void* status, const void* x2, const void* w2, int K2,
-                                               void* stream) {
+// contraction: y = x W^T + x2 w2^T.  epilogue: 0 none, 1 relu(.)^2, 2 add `residual` ([M, N] bf16, row stride ldr).
+RWKV_EXPORT int rwkv_ag_gemm_bf16_tcgen05_fused(const void* x, const unsigned long long* shard_ptrs, void* staged,
+                                                void* y, int M, int N, int K, int rank, int world, void* blk_count,
+                                                int* arrivals_io, void* status, const void* x2, const void* w2, int K2,
+                                                int epilogue, const void* residual, long long ldr, void* stream) {
   if (K2 < 0 || (K2 > 0 && (!x2 || !w2))) return RWKV_ERR_BAD_SHAPE;
+  if (epilogue < 0 || epilogue > 2 || (epilogue == 2 && (!residual || ((uintptr_t)residual & 15) || (ldr * 2) % 16)))
+    return RWKV_ERR_BAD_SHAPE;
   if (M <= 0 || N <= 0 || K <= 0 || world <= 0 || world > MAX_RANKS || rank < 0 || rank >= world) return RWKV_ERR_BAD_SHAPE;
   if (K % world || (K / world) % BK || !arrivals_io || !blk_count) return RWKV_ERR_BAD_SHAPE;
   if (*arrivals_io > 0x70000000) return RWKV_ERR_TOO_LARGE;
@@ -668,7 +669,19 @@ RWKV_EXPORT int rwkv_ag_gemm_bf16_tcgen05_dual(const void* x, const unsigned lon
     r = make_map(&ag.map_b2, w2, N, K2, K2, BK, BN);
     if (r) return r;
   }
-  return launch_ag(ma, mb, mc, M, N, K, (int*)status, sms, ag, arrivals_io, (cudaStream_t)stream);
+  const bf16* c_in = (const bf16*)residual;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (epilogue == 1) return launch_ag<1>(ma, mb, mc, M, N, K, (int*)status, sms, ag, arrivals_io, nullptr, 0, st);
+  if (epilogue == 2) return launch_ag<2>(ma, mb, mc, M, N, K, (int*)status, sms, ag, arrivals_io, c_in, ldr, st);
+  return launch_ag<0>(ma, mb, mc, M, N, K, (int*)status, sms, ag, arrivals_io, nullptr, 0, st);
+}
+
+RWKV_EXPORT int rwkv_ag_gemm_bf16_tcgen05_dual(const void* x, const unsigned long long* shard_ptrs, void* staged, void* y,
+                                               int M, int N, int K, int rank, int world, void* blk_count,
+                                               int* arrivals_io, void* status, const void* x2, const void* w2, int K2,
+                                               void* stream) {
+  return rwkv_ag_gemm_bf16_tcgen05_fused(x, shard_ptrs, staged, y, M, N, K, rank, world, blk_count, arrivals_io, status,
+                                         x2, w2, K2, 0, nullptr, 0, stream);
 }
 
 RWKV_EXPORT int rwkv_ag_gemm_bf16_tcgen05(const void* x, const unsigned long long* shard_ptrs, void* staged, void* y,

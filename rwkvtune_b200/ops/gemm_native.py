@@ -248,9 +248,11 @@ class GatheredWeight:
         self.arrivals = ctypes.c_int(0)      # running arrival total per counter, advanced by every call
 
 
-def ag_mm_nt(x: torch.Tensor, gw: GatheredWeight, x2: torch.Tensor = None, w2: torch.Tensor = None) -> torch.Tensor:
+def ag_mm_nt(x: torch.Tensor, gw: GatheredWeight, x2: torch.Tensor = None, w2: torch.Tensor = None, epilogue: int = 0,
+             residual: torch.Tensor = None) -> torch.Tensor:
     """``x [M,K] @ W^T`` with the all-gather of ``W`` fused into the GEMM; afterwards ``gw.staged`` holds ``W``.
-    ``x2 [M,K2]`` / ``w2 [N,K2]`` (local, contiguous): ``+ x2 @ w2^T``, appended to the contraction of the same launch."""
+    ``x2 [M,K2]`` / ``w2 [N,K2]`` (local, contiguous): ``+ x2 @ w2^T``, appended to the contraction of the same launch.
+    ``epilogue=1``: relu(.)^2; ``residual [M,N]`` (bf16, local): added in the epilogue."""
     import ctypes
 
     M = x.shape[0]
@@ -259,17 +261,27 @@ def ag_mm_nt(x: torch.Tensor, gw: GatheredWeight, x2: torch.Tensor = None, w2: t
         torch.cuda.current_stream().synchronize()
         gw.counts.zero_()
         gw.arrivals.value = 0
-    dual = x2 is not None and hasattr(_ext.lib(), "rwkv_ag_gemm_bf16_tcgen05_dual")
-    if x2 is not None and not dual:
-        raise RuntimeError("this build of the native library has no appended operand pair in the all-gather GEMM")
-    if dual:
+    if residual is not None:
+        epilogue = 2
+    fused = (x2 is not None or epilogue) and hasattr(_ext.lib(), "rwkv_ag_gemm_bf16_tcgen05_fused")
+    if (x2 is not None or epilogue) and not fused:
+        raise RuntimeError("this build of the native library has no fused variant of the all-gather GEMM")
+    if fused and x2 is None:
+        _ext.call("rwkv_ag_gemm_bf16_tcgen05_fused", _ext.ptr(x), gw.ptrs, _ext.ptr(gw.staged), _ext.ptr(y), _ext.i32(M),
+                  _ext.i32(gw.N), _ext.i32(gw.K), _ext.i32(gw.rank), _ext.i32(gw.world), _ext.ptr(gw.counts),
+                  ctypes.byref(gw.arrivals), _ext.ptr(_status(x.device)), _ext.ptr(None), _ext.ptr(None), _ext.i32(0),
+                  _ext.i32(epilogue), _ext.ptr(residual), _ext.i64(0 if residual is None else residual.stride(0)),
+                  _ext.stream())
+        return y
+    if fused:
         if not (x2.is_contiguous() and w2.is_contiguous() and x2.shape == (M, w2.shape[1]) and w2.shape[0] == gw.N
                 and x2.shape[1] % 8 == 0 and x2.dtype == torch.bfloat16 and w2.dtype == torch.bfloat16):
             raise ValueError("appended operand pair must be contiguous bf16 [M, K2] and [N, K2] with K2 a multiple of 8")
-        _ext.call("rwkv_ag_gemm_bf16_tcgen05_dual", _ext.ptr(x), gw.ptrs, _ext.ptr(gw.staged), _ext.ptr(y), _ext.i32(M),
+        _ext.call("rwkv_ag_gemm_bf16_tcgen05_fused", _ext.ptr(x), gw.ptrs, _ext.ptr(gw.staged), _ext.ptr(y), _ext.i32(M),
                   _ext.i32(gw.N), _ext.i32(gw.K), _ext.i32(gw.rank), _ext.i32(gw.world), _ext.ptr(gw.counts),
                   ctypes.byref(gw.arrivals), _ext.ptr(_status(x.device)), _ext.ptr(x2), _ext.ptr(w2),
-                  _ext.i32(x2.shape[1]), _ext.stream())
+                  _ext.i32(x2.shape[1]), _ext.i32(epilogue), _ext.ptr(residual),
+                  _ext.i64(0 if residual is None else residual.stride(0)), _ext.stream())
         return y
     _ext.call("rwkv_ag_gemm_bf16_tcgen05", _ext.ptr(x), gw.ptrs, _ext.ptr(gw.staged), _ext.ptr(y), _ext.i32(M),
               _ext.i32(gw.N), _ext.i32(gw.K), _ext.i32(gw.rank), _ext.i32(gw.world), _ext.ptr(gw.counts),

@@ -115,34 +115,45 @@ class _LoraAGLinearFn(torch.autograd.Function):
     """``x W^T + s (x A^T) B^T`` with ``W`` sharded and frozen."""
 
     @staticmethod
-    def forward(ctx, x, sw: ShardedWeight, a, b, scaling: float):
+    def forward(ctx, x, sw: ShardedWeight, a, b, scaling: float, residual=None, act=None):
         x2 = x.reshape(-1, x.shape[-1])
         x2 = x2 if x2.is_contiguous() else x2.contiguous()
-        xa = gemm.mm_nt(x2, a)
+        xa_s = (gemm.mm_nt(x2, a) * scaling).contiguous()        # scaled once: used here and by dB
         b_c = b if b.is_contiguous() else b.contiguous()
-        if xa.shape[1] % 8 == 0 and b_c.dtype == torch.bfloat16:
-            # the adapter term is the last K block of the all-gather GEMM (no second pass over y)
-            y = sw.owner.forward_gemm(x2, sw, extra=((xa * scaling).contiguous(), b_c))
+        r2 = None if residual is None else residual.reshape(-1, residual.shape[-1])
+        if xa_s.shape[1] % 8 == 0 and b_c.dtype == torch.bfloat16 and (r2 is None or (
+                r2.dtype == torch.bfloat16 and r2.stride(1) == 1 and r2.data_ptr() % 16 == 0 and r2.stride(0) % 8 == 0)):
+            # the adapter term is the last K block of the all-gather GEMM (no second pass over y); relu^2 or the
+            # residual sum in the same launch's epilogue
+            y = sw.owner.forward_gemm(x2, sw, extra=(xa_s, b_c), epilogue=1 if act else 0, residual=r2)
         else:
-            y = gemm.addmm_nt_(sw.owner.forward_gemm(x2, sw), xa * scaling, b)
-        ctx.save_for_backward(x2, a, b, xa)
-        ctx.sw, ctx.shape, ctx.scaling = sw, x.shape, scaling
+            y = gemm.addmm_nt_(sw.owner.forward_gemm(x2, sw), xa_s, b)
+            if act:
+                y = torch.relu(y) ** 2
+            if r2 is not None:
+                y = y + r2
+        ctx.save_for_backward(x2, a, b, xa_s, y if act else None)
+        ctx.sw, ctx.shape, ctx.scaling, ctx.act = sw, x.shape, scaling, act
         return y.reshape(*x.shape[:-1], sw.N)
 
     @staticmethod
     def backward(ctx, dy):
-        x2, a, b, xa = ctx.saved_tensors
+        from ..peft.lora.layer import _relu_sq_grad
+
+        x2, a, b, xa_s, y = ctx.saved_tensors
         s, sw = ctx.scaling, ctx.sw
         dy2 = dy.reshape(-1, dy.shape[-1])
         dy2 = dy2 if dy2.is_contiguous() else dy2.contiguous()
-        dyb = gemm.mm_nn(dy2, b)
+        dpre = _relu_sq_grad(y, dy2) if ctx.act else dy2
+        dyb_s = gemm.mm_nn(dpre, b) * s                          # scaled once: used by dx and by dA
         dx = None
         if ctx.needs_input_grad[0]:
-            dx = gemm.mm_nn_plus(dy2, sw.full_weight(), dyb * s, a).reshape(ctx.shape)
+            dx = gemm.mm_nn_plus(dpre, sw.full_weight(), dyb_s, a).reshape(ctx.shape)
         sw.owner.after_dgrad(sw)
-        da = gemm.mm_tn(dyb, x2) * s if ctx.needs_input_grad[2] else None
-        db = gemm.mm_tn(dy2, xa) * s if ctx.needs_input_grad[3] else None
-        return dx, None, da, db, None
+        da = gemm.mm_tn(dyb_s, x2) if ctx.needs_input_grad[2] else None
+        db = gemm.mm_tn(dpre, xa_s) if ctx.needs_input_grad[3] else None
+        d_res = dy if (len(ctx.needs_input_grad) > 5 and ctx.needs_input_grad[5]) else None
+        return dx, None, da, db, None, d_res, None
 
 
 class _Slot(gemm_native.GatheredWeight):
@@ -270,14 +281,19 @@ class Zero3ShardedLinears:
             self._slots[key] = _Slot(self.ctx.rank, self.ctx.world_size, sw.N, sw.K, self.ctx.device, self.n_copy)
         return self._slots[key]
 
-    def forward_gemm(self, x2: torch.Tensor, sw: ShardedWeight, extra=None) -> torch.Tensor:
-        """``x2 @ W^T`` with the gather fused in; ``extra = (u [M, r], v [N, r])`` adds ``u @ v^T`` inside the same launch."""
+    def forward_gemm(self, x2: torch.Tensor, sw: ShardedWeight, extra=None, epilogue: int = 0, residual=None) -> torch.Tensor:
+        """``x2 @ W^T`` with the gather fused in; ``extra = (u [M, r], v [N, r])`` adds ``u @ v^T`` inside the same launch;
+        ``epilogue=1`` applies relu(.)^2, ``residual [M, N]`` is added, both in that launch's epilogue."""
         gw = sw.gathered()
         if gw.pending is not None:      # a prefetch may still be writing the slot
             torch.cuda.current_stream().wait_event(gw.pending)
             gw.pending = None
         gw.ptrs_for(sw)
-        y = gemm_native.ag_mm_nt(x2, gw) if extra is None else gemm_native.ag_mm_nt(x2, gw, extra[0], extra[1])
+        if extra is None and not epilogue and residual is None:
+            y = gemm_native.ag_mm_nt(x2, gw)
+        else:
+            u, v = extra if extra is not None else (None, None)
+            y = gemm_native.ag_mm_nt(x2, gw, u, v, epilogue=epilogue, residual=residual)
         gw.current_owner = sw
         return y
 
@@ -432,5 +448,8 @@ def ag_linear(x: torch.Tensor, sw: ShardedWeight) -> torch.Tensor:
     return _AGLinearFn.apply(x, sw, sw.anchor)
 
 
-def lora_ag_linear(x: torch.Tensor, sw: ShardedWeight, a: torch.Tensor, b: torch.Tensor, scaling: float) -> torch.Tensor:
-    return _LoraAGLinearFn.apply(x, sw, a, b, scaling)
+def lora_ag_linear(x: torch.Tensor, sw: ShardedWeight, a: torch.Tensor, b: torch.Tensor, scaling: float,
+                   residual: torch.Tensor = None, act: str = None) -> torch.Tensor:
+    """``act(x W^T + s (x A^T) B^T) + residual`` with ``W`` sharded (``act``: ``None`` or ``"relu_sq"``, never with a
+    residual)."""
+    return _LoraAGLinearFn.apply(x, sw, a, b, scaling, residual, act)

@@ -109,7 +109,12 @@ class LoraLinear(nn.Module):
         the training path both ride in the epilogue of the single fused GEMM launch."""
         if act is not None and residual is not None:
             raise ValueError("LoraLinear: an activation and a residual cannot be combined")
-        fused = (getattr(self, "_sharded", None) is None and not (self.disabled or self.merged)
+        sw = getattr(self, "_sharded", None)
+        if sw is not None and not self.disabled and not (isinstance(self.lora_dropout, nn.Dropout) and self.training):
+            from ...parallel.zero3 import lora_ag_linear     # ZeRO-3: the same fusion inside the all-gather GEMM
+
+            return lora_ag_linear(x, sw, self.lora_A, self.lora_B, self.scaling, residual, act)
+        fused = (sw is None and not (self.disabled or self.merged)
                  and not (not torch.is_grad_enabled() and x.is_cuda and x.numel() // x.shape[-1] <= 256)
                  and not (isinstance(self.lora_dropout, nn.Dropout) and self.training))
         if fused:

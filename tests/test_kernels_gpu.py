@@ -621,6 +621,16 @@ def test_ag_fused_gemm_emulated_panels(M, N, K, W, rank):
     ref2 = ref_out + u.float() @ v.float().t()
     assert gemm_native.check_status() == 0 and torch.equal(gw.staged, w)
     assert (y.float() - ref2).abs().max().item() <= 2e-2 * ref2.abs().max().item() + 1e-2
+    # ... with relu^2, and with a residual, in the same launch's epilogue
+    y = gemm_native.ag_mm_nt(x, gw, u, v, epilogue=1)
+    res = torch.randn(M, N, device="cuda").to(BF)
+    y2 = gemm_native.ag_mm_nt(x, gw, u, v, residual=res)
+    torch.cuda.synchronize()
+    assert gemm_native.check_status() == 0
+    want = torch.relu(ref2) ** 2
+    assert (y.float() - want).abs().max().item() <= 2e-2 * want.abs().max().item() + 1e-2
+    want = ref2 + res.float()
+    assert (y2.float() - want).abs().max().item() <= 2e-2 * want.abs().max().item() + 1e-2
 
 
 @pytest.mark.parametrize("B,T,H,with_state", [(2, 64, 2, False), (1, 37, 3, True), (2, 256, 1, True)])
