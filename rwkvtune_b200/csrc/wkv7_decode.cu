@@ -9,7 +9,7 @@
 // wkv7.cu / wkv7_tc.cu); at one token per sequence each of them is a launch plus a memory round trip, and the
 // general WKV7 kernel carries 58 KB of chunk staging per CTA that limits it to three CTAs per SM.  Here a CTA
 // owns one (sequence, head): 64 threads prepare one channel of the head each while all 128 threads are already
-// loading their 8 x 4 slice of the 64 x 64 fp32 state; 2.5 KB of shared memory and at most 64 registers, so that the
+// loading their 8 x 4 slice of the 64 x 64 fp32 state; 2.5 KB of shared memory and 72 registers (seven CTAs per SM), so that the
 // 32 KB of state traffic per CTA is spread over many resident CTAs.  The new state goes to a second tensor or back
 // into the first (in place), which may be a [B, H, 64, 64] tensor or a slot-indexed pool (continuous batching).
 //
