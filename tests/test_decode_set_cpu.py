@@ -123,3 +123,38 @@ def test_set_does_not_apply_while_autograd_records_or_with_too_many_problems(fak
         # an activation together with a residual cannot be combined with an adapter in two launches
         assert gemm.decode_projection_set([(x, w, "relu_sq", _rand(3, 8), (_rand(4, 8), _rand(8, 4), 1.0))]) is None
     assert fake.calls == []
+
+
+def test_decode_order_links_are_plain_attributes_not_submodules():
+    """Each half of a block knows which half runs next (for the L2 prefetch hints of the decode path); the links must
+    not show up as sub-modules, parameters or state-dict entries, and the model must still deep-copy."""
+    import copy
+
+    from rwkvtune_b200.models import RWKVConfig, RWKV7Model
+    from rwkvtune_b200.models.rwkv7.model import _weights_of
+
+    m = RWKV7Model(RWKVConfig(n_layer=3, n_embd=64, vocab_size=128))
+    for i, blk in enumerate(m.blocks):
+        assert blk.att._decode_next is blk.ffn
+        assert blk.ffn._decode_next is (m.blocks[i + 1].att if i + 1 < 3 else None)
+    names = [n for n, _ in m.named_modules()]
+    assert not any("_decode_next" in n for n in names) and len(names) == len(set(names))
+    assert not any("_decode_next" in k for k in m.state_dict())
+    n_params = sum(1 for _ in m.parameters())
+    m2 = copy.deepcopy(m)
+    assert sum(1 for _ in m2.parameters()) == n_params
+    assert m2.blocks[0].att._decode_next is m2.blocks[0].ffn          # the copy links to its own halves
+    assert _weights_of(m.blocks[0].ffn.key, None) == []                # CPU weights give no hint
+
+
+def test_launch_chaining_and_capture_guard_are_inert_without_a_gpu():
+    import gc
+
+    from rwkvtune_b200.ops import _ext
+
+    with _ext.launch_chaining():
+        assert _ext.chaining() is False or _ext.available()
+    was = gc.isenabled()
+    with _ext.capture_safe_gc():
+        assert not gc.isenabled()
+    assert gc.isenabled() == was
