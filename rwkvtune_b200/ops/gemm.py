@@ -71,44 +71,42 @@ def decode_projection_set(lin, lowrank=(), prefetch=None):
     n = _native()
     if not _decode(n) or torch.is_grad_enabled():
         return None
-    xs, ws, acts, kn, res = [], [], [], [], []
-    for x, w, act, residual, lora in lin:
-        if lora is not None and act is not None and residual is not None:
-            return None
-        xs.append(x); ws.append(w); kn.append(False)
-        acts.append(act if lora is None else None)
-        res.append(residual if (lora is None or act is None) else None)
-    for x, w, act, residual, lora in lin:
-        if lora is not None:
-            xs.append(x); ws.append(lora[0]); kn.append(False); acts.append(None); res.append(None)
-    for x, w1, act, w2 in lowrank:
-        xs.append(x); ws.append(w1); kn.append(True); acts.append(act); res.append(None)
-    if not xs or len(xs) > n.DECODE_MAX_PROBLEMS:
+    if any(lora is not None and act is not None and residual is not None for _, _, act, residual, lora in lin):
         return None
+    adapters = [i for i, item in enumerate(lin) if item[4] is not None]
+    # first launch, one row per problem: (x, weight, weight stored [in, out], activation, residual)
+    first_rows = [(x, w, False, act if lora is None else None, residual if (lora is None or act is None) else None)
+                  for x, w, act, residual, lora in lin]
+    first_rows += [(lin[i][0], lin[i][4][0], False, None, None) for i in adapters]
+    first_rows += [(x, w1, True, act, None) for x, w1, act, _ in lowrank]
+    if not first_rows or len(first_rows) > n.DECODE_MAX_PROBLEMS:
+        return None
+    xs, ws, kn, acts, res = (list(col) for col in zip(*first_rows))
     first = decode_products(xs, ws, acts=acts, kn=kn, residuals=res, prefetch=prefetch)
     if first is None:
         return None
     n_lin = len(lin)
     lin_out = first[:n_lin]
-    adapters = [i for i, item in enumerate(lin) if item[4] is not None]
     xa = first[n_lin:n_lin + len(adapters)]
     hidden = first[n_lin + len(adapters):]
     if not adapters and not lowrank:
         return lin_out, []
-    x2, w2s, act2, kn2, res2, alpha2, rf2, outs2 = [], [], [], [], [], [], [], []
+    # second launch: (x, weight, stored [in, out], activation, residual, scale, residual before activation, output)
+    second_rows = []
     for a_out, i in zip(xa, adapters):
-        y = lin_out[i].reshape(-1, lin_out[i].shape[-1])
-        x2.append(a_out.reshape(-1, a_out.shape[-1])); w2s.append(lin[i][4][1]); kn2.append(False)
-        act2.append(lin[i][2]); res2.append(y); alpha2.append(lin[i][4][2]); rf2.append(True); outs2.append(y)
-    for h, item in zip(hidden, lowrank):
-        x2.append(h.reshape(-1, h.shape[-1])); w2s.append(item[3]); kn2.append(True)
-        act2.append(None); res2.append(None); alpha2.append(1.0); rf2.append(False); outs2.append(None)
+        y = lin_out[i].reshape(-1, lin_out[i].shape[-1])          # accumulated in place
+        _, lora_b, scaling = lin[i][4]
+        second_rows.append((a_out.reshape(-1, a_out.shape[-1]), lora_b, False, lin[i][2], y, scaling, True, y))
+    for h, (_, _, _, w2) in zip(hidden, lowrank):
+        second_rows.append((h.reshape(-1, h.shape[-1]), w2, True, None, None, 1.0, False, None))
+    x2, w2s, kn2, act2, res2, alpha2, rf2, outs2 = (list(col) for col in zip(*second_rows))
     if not all(n.decode_ok(a, w, t) for a, w, t in zip(x2, w2s, kn2)):
         # the first launch has run; finish the set with ordinary products
         for a_out, i in zip(xa, adapters):
-            y = lin_out[i] + (a_out @ lin[i][4][1].t()) * lin[i][4][2]
+            _, lora_b, scaling = lin[i][4]
+            y = lin_out[i] + (a_out @ lora_b.t()) * scaling
             lin_out[i] = y if lin[i][2] is None else _apply_act(y, lin[i][2])
-        return lin_out, [h @ item[3] for h, item in zip(hidden, lowrank)]
+        return lin_out, [h @ w2 for h, (_, _, _, w2) in zip(hidden, lowrank)]
     second = n.decode_group(x2, w2s, epis=act2, kn=kn2, residuals=res2, alphas=alpha2, res_first=rf2, outs=outs2)
     lows = [y.reshape(*item[0].shape[:-1], y.shape[-1]) for y, item in zip(second[len(adapters):], lowrank)]
     return lin_out, lows
