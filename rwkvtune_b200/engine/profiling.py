@@ -132,3 +132,44 @@ class StepProfiler:
             print(f"[profile] kernel table of {self.n} steps written to {self.path}", flush=True)
         self.prof = None
         self.n = 0
+
+
+def get_gpu_memory_info(device=None) -> Optional[Dict[str, float]]:
+    """Allocator figures of one device in GiB (``allocated``, ``reserved``, ``max_allocated``, ``total``,
+    ``free`` = total - reserved, ``usage_percent``); ``None`` without CUDA.  Same keys as the reference's
+    helper of this name (``rwkvtune/training/grpo/lightning_module.py:34-62``)."""
+    if not torch.cuda.is_available():
+        return None
+    device = torch.cuda.current_device() if device is None else device
+    torch.cuda.synchronize(device)
+    gib = float(1 << 30)
+    total = torch.cuda.get_device_properties(device).total_memory / gib
+    reserved = torch.cuda.memory_reserved(device) / gib
+    return {"allocated": torch.cuda.memory_allocated(device) / gib, "reserved": reserved,
+            "max_allocated": torch.cuda.max_memory_allocated(device) / gib, "total": total, "free": total - reserved,
+            "usage_percent": 100.0 * reserved / total if total > 0 else 0.0}
+
+
+@contextlib.contextmanager
+def monitor_memory_and_time(rank, stage_name: str, device=None, sink=print):
+    """``with monitor_memory_and_time(rank, "rollout"):`` — one line per use with the wall-clock seconds of the
+    block and, on CUDA, the change in allocated memory and the peak inside the block (call convention of
+    ``rwkvtune/training/grpo/lightning_module.py:65-107``).  Built on :class:`PhaseMonitor`, so the block also
+    shows up as an NVTX range; the monitor is yielded for callers that want the figures instead of the line."""
+    dev = None
+    if torch.cuda.is_available():
+        dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    mon = PhaseMonitor(dev, sync=True)
+    before = get_gpu_memory_info(dev)
+    try:
+        with mon.phase(stage_name):
+            yield mon
+    finally:
+        stats = mon.scalars(reset=False)
+        line = f"[Rank {rank}] {stage_name}: {stats.get(f'phase/{stage_name}/seconds', 0.0):.2f} s"
+        after = get_gpu_memory_info(dev)
+        if before and after:
+            line += (f", allocated {before['allocated']:.2f} -> {after['allocated']:.2f} GiB, "
+                     f"peak {stats.get(f'phase/{stage_name}/peak_mem_gb', 0.0):.2f} GiB, "
+                     f"reserved {after['reserved']:.2f} of {after['total']:.2f} GiB ({after['usage_percent']:.1f}%)")
+        sink(line)

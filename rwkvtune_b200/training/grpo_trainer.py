@@ -36,6 +36,7 @@ from ..inference.grpo_batch_generator import GRPOBatchGenerator
 from ..models import AutoModel
 from ..parallel import init_distributed
 from ..peft import get_peft_model, is_peft_model
+from .callbacks import CallbackList
 from .grpo.advantage import AdvantageCalculator
 from .grpo.dataset import create_grpo_dataloader
 from .grpo.loss import get_loss_function
@@ -69,7 +70,7 @@ class GRPOTrainer:
             else:
                 processing_class = get_tokenizer()
         self.processing_class = self.tokenizer = processing_class
-        self.callbacks = list(callbacks or [])
+        self.callbacks = CallbackList(callbacks)
         self.loss_mask_func = loss_mask_func
         self.completion_postprocess_fn = completion_postprocess_fn
         self.reward_funcs = [reward_funcs] if callable(reward_funcs) else list(reward_funcs)
@@ -361,6 +362,7 @@ class GRPOTrainer:
 
         profiler = StepProfiler(profile_steps_requested(a), a.proj_dir, is_main=ctx.is_main)
         done = False
+        self.callbacks.fire("on_train_start", self)
         for epoch in range(a.epoch_count):
             loader.sampler.set_epoch(epoch)
             for b, batch in enumerate(loader):
@@ -374,6 +376,7 @@ class GRPOTrainer:
                 lr = a.lr_init * grpo_lr_scale(eng.optimizer_steps, a.lr_init, a.lr_final, a.warmup_steps, total_opt,
                                                a.accumulate_grad_batches)
                 t0 = time.perf_counter()
+                self.callbacks.fire("on_train_batch_start", self, batch, b)
                 profiler.step_begin()
                 with eng.phases.phase("policy_step"):
                     metrics = self._training_step(data, lr)
@@ -395,14 +398,15 @@ class GRPOTrainer:
                     print(f"step {self.state['global_step']}/{total_steps} loss {metrics['train_loss']:.5f} "
                           f"reward {metrics['train/reward/mean']:.4f} len {metrics['completions/mean_length']:.1f} "
                           f"lr {lr:.2e}", flush=True)
-                for cb in self.callbacks:
-                    if hasattr(cb, "on_step_end"):
-                        cb.on_step_end(self, metrics)
+                self.callbacks.fire("on_train_batch_end", self, {"loss": metrics["train_loss"], **metrics}, batch, b)
+                self.callbacks.fire("on_step_end", self, metrics)
                 if a.save_every_n_batches > 0 and self.state["global_step"] % a.save_every_n_batches == 0:
                     self._save_checkpoint(f"rwkv7-batch{self.state['global_step']}")
+            self.callbacks.fire("on_train_epoch_end", self, epoch)
             if done:
                 break
         self._save_checkpoint(f"checkpoint_epoch_{a.epoch_count}")
+        self.callbacks.fire("on_train_end", self)
         logger.close()
         ctx.barrier()
 
@@ -422,6 +426,7 @@ class GRPOTrainer:
         ckpt.atomic_checkpoint(final, ctx, write)
         if ctx.is_main and a.save_total_limit > 0:
             ckpt.rotate_checkpoints(a.proj_dir, a.save_total_limit, "rwkv7-batch*")
+        self.callbacks.fire("on_save_checkpoint", self, final)
 
     def _maybe_resume(self) -> None:
         a, ctx, eng = self.args, self.ctx, self.engine

@@ -15,5 +15,6 @@ class PretrainTrainer(SupervisedTrainer):
     config_name = "pretrain"
     accepts_iterable = True
 
-    def __init__(self, model, args: PretrainConfig = None, train_dataset=None, processing_class=None, lora_config=None):
-        super().__init__(model, args or PretrainConfig(), train_dataset, processing_class, lora_config)
+    def __init__(self, model, args: PretrainConfig = None, train_dataset=None, processing_class=None, lora_config=None,
+                 callbacks=None):
+        super().__init__(model, args or PretrainConfig(), train_dataset, processing_class, lora_config, callbacks)

@@ -10,5 +10,6 @@ class SFTTrainer(SupervisedTrainer):
     config_name = "sft"
     accepts_iterable = False
 
-    def __init__(self, model, args: SFTConfig = None, train_dataset=None, processing_class=None, lora_config=None):
-        super().__init__(model, args or SFTConfig(), train_dataset, processing_class, lora_config)
+    def __init__(self, model, args: SFTConfig = None, train_dataset=None, processing_class=None, lora_config=None,
+                 callbacks=None):
+        super().__init__(model, args or SFTConfig(), train_dataset, processing_class, lora_config, callbacks)

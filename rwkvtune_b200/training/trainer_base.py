@@ -23,6 +23,7 @@ from ..engine.metrics import MetricLogger
 from ..models import AutoModel
 from ..parallel import init_distributed
 from ..peft import LoraConfig, get_peft_model, is_peft_model
+from .callbacks import CallbackList
 from .data_loading import BatchLoader
 from .model_save_utils import save_model_or_adapter
 
@@ -40,8 +41,10 @@ class SupervisedTrainer:
     config_name = "sft"
     accepts_iterable = False
 
-    def __init__(self, model, args, train_dataset, processing_class=None, lora_config: Optional[LoraConfig] = None):
+    def __init__(self, model, args, train_dataset, processing_class=None, lora_config: Optional[LoraConfig] = None,
+                 callbacks=None):
         self.args = args
+        self.callbacks = CallbackList(callbacks)
         self.train_dataset = train_dataset
         self.processing_class = processing_class
         self.lora_config = lora_config
@@ -143,6 +146,7 @@ class SupervisedTrainer:
         start_epoch, skip = self._maybe_resume(per_epoch)
         samples_per_batch = a.micro_bsz * ctx.world_size
         guard = eng.start_guard()
+        self.callbacks.fire("on_train_start", self)
         try:
             self._run_epochs(start_epoch, skip, per_epoch, total_steps, loader, logger, samples_per_batch)
         except Exception as exc:
@@ -151,6 +155,7 @@ class SupervisedTrainer:
         finally:
             if guard is not None:
                 guard.stop()
+        self.callbacks.fire("on_train_end", self)
         logger.close()
         ctx.barrier()
 
@@ -168,6 +173,7 @@ class SupervisedTrainer:
                     break
                 real_step = (epoch + a.epoch_begin) * per_epoch + (b + 1)
                 lr = sft_lr(real_step, a.lr_init, a.lr_final, a.warmup_steps, total_steps, a.epoch_count)
+                self.callbacks.fire("on_train_batch_start", self, batch, b)
                 profiler.step_begin()
                 loss = eng.train_step_from_host(batch["input_ids"], batch["labels"], lr)
                 profiler.step_end()
@@ -188,10 +194,15 @@ class SupervisedTrainer:
                         print(f"epoch {epoch} step {b + 1}/{per_epoch} loss {loss:.4f} lr {lr:.3e} "
                               f"{rec['kt_s']:.1f} Kt/s", flush=True)
                 t_last = now
+                if len(self.callbacks):
+                    outputs = {"loss": loss, "lr": lr}
+                    self.callbacks.fire("on_train_batch_end", self, outputs, batch, b)
+                    self.callbacks.fire("on_step_end", self, outputs)
                 if a.save_every_n_batches > 0 and self.state["global_batch"] % a.save_every_n_batches == 0:
                     self._save_checkpoint(f"rwkv7-batch{self.state['global_batch']}")
             skip = 0
             logger.log_epoch(epoch, loss_sum / max(n_loss, 1), self.state["global_batch"])
+            self.callbacks.fire("on_train_epoch_end", self, epoch)
             if (a.epoch_save > 0 and (epoch + 1) % a.epoch_save == 0) or epoch == a.epoch_count - 1:
                 self._save_checkpoint(f"rwkv7-epoch{epoch + 1}")
 
@@ -237,6 +248,7 @@ class SupervisedTrainer:
         if ctx.is_main and a.save_total_limit > 0:
             ckpt.rotate_checkpoints(a.proj_dir, a.save_total_limit)
         ctx.barrier()
+        self.callbacks.fire("on_save_checkpoint", self, final)
 
     def _maybe_resume(self, per_epoch: int):
         a, ctx, eng = self.args, self.ctx, self.engine
