@@ -13,10 +13,13 @@ import torch
 
 from .... import ops
 from ....ops import reference as _reference
+from .infctx_oracle import (RWKV7InfctxNaiveFunction, WKV7InfctxFunction, naive_recurrent_rwkv7_bwd,
+                            naive_recurrent_rwkv7_fwd)
 
 __all__ = ["load_wkv_operator", "rwkv7_wkv", "load_wkv7_operator", "load_cpu_operator", "load_cuda_operator_train",
            "load_cuda_operator_inference", "load_cuda_operator_infctx", "rwkv7_wkv_cpu", "rwkv7_wkv_infctx",
-           "rwkv7_wkv_infctx_naive"]
+           "rwkv7_wkv_infctx_naive", "naive_recurrent_rwkv7_fwd", "naive_recurrent_rwkv7_bwd",
+           "RWKV7InfctxNaiveFunction", "WKV7InfctxFunction"]
 
 
 def _stateful(head_size: int) -> Callable:
@@ -92,10 +95,12 @@ def rwkv7_wkv_infctx(w, q, k, v, a, b, state: Optional[torch.Tensor] = None,
     return _infctx(lambda *args: ops.wkv7(*args, True), w, q, k, v, a, b, state, scale)
 
 
-def rwkv7_wkv_infctx_naive(w, q, k, v, a, b, state: Optional[torch.Tensor] = None,
+def rwkv7_wkv_infctx_naive(q, k, v, w, a, b, state: Optional[torch.Tensor] = None,
                            scale: float = 1.0) -> Tuple[torch.Tensor, torch.Tensor]:
-    """Same contract on the step-by-step fp32 PyTorch recurrence (the oracle; autograd does the backward)."""
-    return _infctx(_reference.wkv7, w, q, k, v, a, b, state, scale)
+    """The oracle of the chunk step: fp32 step-by-step recurrence with a closed-form backward (no autograd tape).
+    Note the argument order, ``q, k, v, w`` — that of ``wkv_infctx_naive.py:228-250``, not of
+    :func:`rwkv7_wkv_infctx`.  Returns fp32 ``(output [B, T, H, N], final_state [B, H, N, N])``."""
+    return RWKV7InfctxNaiveFunction.apply(q, k, v, w, a, b, scale, state)
 
 
 def load_cuda_operator_infctx():

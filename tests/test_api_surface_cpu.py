@@ -109,7 +109,8 @@ def test_operator_entry_points_follow_reference_conventions():
                                            f4(b)[:, 3:], state=sa)
     assert torch.allclose(torch.cat([ya, yb], 1).reshape(B, T, C), y_ref, atol=1e-5)
     assert torch.allclose(sb, s_ref, atol=1e-5)
-    yn, sn = O.rwkv7_wkv_infctx_naive(f4(w), f4(r), f4(k), f4(v), f4(a), f4(b), scale=0.5)
+    # the oracle takes q, k, v, w (the order of the reference's naive operator), unlike the chunk step above
+    yn, sn = O.rwkv7_wkv_infctx_naive(f4(r), f4(k), f4(v), f4(w), f4(a), f4(b), scale=0.5)
     assert torch.allclose(yn.reshape(B, T, C), 0.5 * y_ref, atol=1e-5) and torch.allclose(sn, s_ref, atol=1e-5)
     try:
         O.load_wkv_operator(device="tpu")
