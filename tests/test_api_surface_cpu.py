@@ -243,7 +243,13 @@ def test_public_names_of_the_reference_are_importable():
                                  "GenerationMixin"],
         "rwkvtune_b200.models.rwkv7.operators": ["load_wkv_operator", "rwkv7_wkv", "load_wkv7_operator",
                                                  "load_cpu_operator", "load_cuda_operator_train",
-                                                 "load_cuda_operator_inference", "load_cuda_operator_infctx"],
+                                                 "load_cuda_operator_inference", "load_cuda_operator_infctx",
+                                                 "rwkv7_wkv_infctx", "rwkv7_wkv_infctx_naive", "rwkv7_wkv_cpu",
+                                                 "naive_recurrent_rwkv7_fwd", "naive_recurrent_rwkv7_bwd",
+                                                 "RWKV7InfctxNaiveFunction", "WKV7InfctxFunction"],
+        "rwkvtune_b200.training.callbacks": ["TrainingCallback"],
+        "rwkvtune_b200.training.grpo": ["get_gpu_memory_info", "monitor_memory_and_time", "AdvantageCalculator",
+                                        "get_loss_function", "create_grpo_dataloader", "RepeatBatchSampler"],
         "rwkvtune_b200.configs": ["load_model_config", "list_available_models", "print_model_info", "ModelConfig"],
         "rwkvtune_b200.training.model_save_utils": ["save_model_with_config", "save_model_checkpoint",
                                                     "get_lora_state_dict", "save_lora_checkpoint",
