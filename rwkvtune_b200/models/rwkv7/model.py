@@ -248,6 +248,33 @@ class RWKV7TimeMix(nn.Module):
         return out, v_first, (last if want_state else None), new_state
 
 
+    def forward_with_state(self, x, v_first, x_prev, att_kv):
+        """The half-block step with the reference's module-level contract (``model.py:174-278``): ``x`` is the
+        *normalised* input ``[B, T, C]``, ``x_prev`` the last normalised row of the previous call ``[B, C]``,
+        ``att_kv`` the state ``[B, H, N, N]``.  Returns the bare projection ``(y, v_first, new_x_prev fp32,
+        new_att_kv)`` - no residual sum.  A composition of the unfused ops for callers that drive the halves
+        themselves; the model's own paths go through :meth:`forward`."""
+        from ...ops import reference as _ref
+
+        xx = _ref.token_shift(x, x_prev) - x
+        xr, xw, xk, xv, xa, xg = (x + xx * m for m in (self.x_r, self.x_w, self.x_k, self.x_v, self.x_a, self.x_g))
+        r, k, v = self.receptance(xr), self.key(xk), self.value(xv)
+        w_lin = ops.matmul(ops.matmul_act(xw, self.w1, "tanh"), self.w2)
+        a_lin = ops.matmul(ops.matmul(xa, self.a1), self.a2)
+        g = ops.matmul(ops.matmul_act(xg, self.g1, "sigmoid"), self.g2)
+        if self.layer_id == 0:
+            w, k, v, a_, b_ = ops.timemix_prep(k, v, None, w_lin, a_lin, None, self.w0, self.a0, None, self.k_k, self.k_a,
+                                               self.head_size)
+            v_first = v
+        else:
+            v_lin = ops.matmul(ops.matmul(xv, self.v1), self.v2)
+            w, k, v, a_, b_ = ops.timemix_prep(k, v, v_first, w_lin, a_lin, v_lin, self.w0, self.a0, self.v0, self.k_k,
+                                               self.k_a, self.head_size)
+        z, new_state = ops.wkv7_gn(r, w, k, v, a_, b_, g, self.ln_x.weight, self.ln_x.bias, self.r_k, self.head_size,
+                                   state=att_kv.float(), return_state=True)
+        return self.output(z), v_first, x[:, -1].float(), new_state
+
+
 class RWKV7ChannelMix(nn.Module):
     """Squared-ReLU feed-forward half of a block (``model.py:281-343``); width is ``4 * n_embd``."""
 
@@ -285,6 +312,15 @@ class RWKV7ChannelMix(nn.Module):
         else:   # sharded (ZeRO-3): activation applied separately
             hidden = ops.relu_squared(self.key(xk))
         return _project_add(self.value, hidden, x), (last if want_state else None)
+
+
+    def forward_with_state(self, x, x_prev):
+        """Reference contract of the half-block step (``model.py:310-343``): ``x`` normalised ``[B, T, C]``, ``x_prev``
+        ``[B, C]``; returns ``(y, new_x_prev fp32)`` without the residual sum."""
+        from ...ops import reference as _ref
+
+        xk = x + (_ref.token_shift(x, x_prev) - x) * self.x_k
+        return self.value(ops.relu_squared(self.key(xk))), x[:, -1].float()
 
 
 class RWKV7Block(nn.Module):

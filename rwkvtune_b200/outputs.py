@@ -23,7 +23,7 @@ class RequestOutput:
     prompt: Optional[str]
     prompt_token_ids: List[int]
     outputs: List[CompletionOutput] = field(default_factory=list)
-    finished: bool = False
+    finished: bool = True
 
     def __repr__(self) -> str:
         return (f"RequestOutput(request_id={self.request_id!r}, prompt={self.prompt!r}, "

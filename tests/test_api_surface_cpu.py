@@ -82,6 +82,44 @@ def test_block_forward_with_state_matches_model_state_step():
     assert torch.allclose(x, ref, atol=1e-4, rtol=1e-4)
 
 
+def test_half_block_steps_follow_the_reference_contract():
+    """``att.forward_with_state`` / ``ffn.forward_with_state`` take the normalised input and return the bare
+    projection; composed by hand with the residual sums they reproduce the block's own stateful step, over two
+    calls that carry the state."""
+    torch.manual_seed(0)
+    cfg = RWKVConfig(n_layer=2, n_embd=128, vocab_size=256)
+    model = RWKV7Model(cfg).eval()
+    with torch.no_grad():
+        for p in model.parameters():        # zero-initialised projections would make the comparison vacuous
+            if p.dim() >= 2 and float(p.abs().sum()) == 0:
+                p.normal_(0, 0.02)
+    H, N, C = cfg.n_embd // 64, 64, cfg.n_embd
+    ln = lambda m, t: torch.nn.functional.layer_norm(t, (C,), m.weight, m.bias)
+    with torch.no_grad():
+        x_all = model.emb(torch.randint(0, 256, (2, 7)))
+        for blk in model.blocks:
+            st = {"att_x_prev": torch.zeros(2, C), "att_kv": torch.zeros(2, H, N, N), "ffn_x_prev": torch.zeros(2, C)}
+            a_prev, kv, f_prev = st["att_x_prev"], st["att_kv"], st["ffn_x_prev"]
+            v_in = torch.randn_like(x_all)      # stands for layer 0's value rows when the block is not layer 0
+            t0 = 0
+            outs = []
+            for part in (x_all[:, :4], x_all[:, 4:]):
+                vf = v_in[:, t0:t0 + part.shape[1]]
+                t0 += part.shape[1]
+                want, vf_a, st = blk.forward_with_state(part, vf, st)
+                h = ln(blk.ln0, part) if blk.layer_id == 0 else part
+                y, vf_b, a_prev, kv = blk.att.forward_with_state(ln(blk.ln1, h), vf, a_prev, kv)
+                assert torch.allclose(vf_a, vf_b, atol=1e-5)
+                h = h + y
+                y, f_prev = blk.ffn.forward_with_state(ln(blk.ln2, h), f_prev)
+                got = h + y
+                assert a_prev.dtype == f_prev.dtype == kv.dtype == torch.float32 and a_prev.shape == (2, C)
+                assert torch.allclose(got, want, atol=1e-4, rtol=1e-4)
+                assert torch.allclose(kv, st["att_kv"], atol=1e-4) and torch.allclose(f_prev, st["ffn_x_prev"], atol=1e-5)
+                outs.append(want)
+            x_all = torch.cat(outs, 1)
+
+
 def test_operator_entry_points_follow_reference_conventions():
     from rwkvtune_b200.models.rwkv7 import operators as O
     from rwkvtune_b200.ops import reference
