@@ -7,7 +7,7 @@ replaces the reference's character trie; the longest special token starting at a
 """
 from __future__ import annotations
 
-from typing import Callable, Dict, List, Sequence
+from typing import Callable, Dict, List, Optional, Sequence, Tuple, Union
 
 
 class SpecialTokenTrie:
@@ -47,35 +47,66 @@ class SpecialTokenTrie:
         return out
 
 
-def encode_with_special_tokens(text: str, base_encode: Callable[[str], List[int]], special_tokens: Dict[str, int],
-                               trie: SpecialTokenTrie = None) -> List[int]:
+def _codec(tokenizer, name: str) -> Callable:
+    """``tokenizer.encode`` / ``tokenizer.decode``, or ``tokenizer`` itself when a bare function is passed."""
+    return getattr(tokenizer, name) if hasattr(tokenizer, name) else tokenizer
+
+
+def encode_with_special_tokens(text: str, tokenizer, additional_special_tokens: Dict[str, Union[int, List[int]]],
+                               trie: Optional[SpecialTokenTrie] = None) -> List[int]:
+    """Encode ``text`` with every special token mapped to its reserved id - or id sequence, when the mapping's value
+    is a list - and everything between them encoded by ``tokenizer`` (an object with ``encode`` or the function
+    itself).  Call convention of ``special_token_handler.py:118-159``; ``trie`` lets a caller reuse a prepared
+    splitter."""
+    encode = _codec(tokenizer, "encode")
+    if not additional_special_tokens:
+        return list(encode(text))
     if trie is None:
         trie = SpecialTokenTrie()
-        for tok in special_tokens:
+        for tok in additional_special_tokens:
             trie.add(tok)
     ids: List[int] = []
     for piece in trie.split(text):
-        if piece in special_tokens:
-            ids.append(special_tokens[piece])
+        hit = additional_special_tokens.get(piece)
+        if hit is None:
+            ids.extend(encode(piece))
+        elif isinstance(hit, (list, tuple)):
+            ids.extend(int(t) for t in hit)
         else:
-            ids.extend(base_encode(piece))
+            ids.append(int(hit))
     return ids
 
 
-def decode_with_special_tokens(token_ids: Sequence[int], base_decode: Callable[[List[int]], str],
-                               id_to_special: Dict[int, str], skip_special_tokens: bool = False) -> str:
+def decode_with_special_tokens(token_ids: Sequence[int], tokenizer, additional_special_tokens: Dict[str, Union[int, List[int]]],
+                               reverse_mapping: Optional[Dict[Tuple[int, ...], str]] = None,
+                               skip_special_tokens: bool = False) -> str:
+    """Inverse of :func:`encode_with_special_tokens` (``special_token_handler.py:162-216``): id sequences of special
+    tokens (longest first, up to 10 ids) turn back into their strings, everything else goes through ``tokenizer``.
+    Unlike the reference, which decodes unmatched ids one at a time, the ids between two special tokens are decoded
+    as one run, so a character whose bytes span several tokens survives."""
+    decode = _codec(tokenizer, "decode")
+    ids = [int(t) for t in token_ids]
+    if not additional_special_tokens:
+        return decode(ids)
+    if reverse_mapping is None:
+        reverse_mapping = {(tuple(int(t) for t in v) if isinstance(v, (list, tuple)) else (int(v),)): k
+                           for k, v in additional_special_tokens.items()}
+    longest = min(10, max((len(k) for k in reverse_mapping), default=1))
     parts: List[str] = []
     run: List[int] = []
-    for t in token_ids:
-        t = int(t)
-        if t in id_to_special:
+    i = 0
+    while i < len(ids):
+        hit = next((n for n in range(min(longest, len(ids) - i), 0, -1) if tuple(ids[i:i + n]) in reverse_mapping), 0)
+        if hit:
             if run:
-                parts.append(base_decode(run))
+                parts.append(decode(run))
                 run = []
             if not skip_special_tokens:
-                parts.append(id_to_special[t])
+                parts.append(reverse_mapping[tuple(ids[i:i + hit])])
+            i += hit
         else:
-            run.append(t)
+            run.append(ids[i])
+            i += 1
     if run:
-        parts.append(base_decode(run))
+        parts.append(decode(run))
     return "".join(parts)

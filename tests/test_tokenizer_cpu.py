@@ -1,0 +1,133 @@
+"""Tokenizer behaviour on CPU: round trips over the shipped vocabulary, special tokens, chat templates, ChatML
+set-up, files on disk, pickling, and the text-level special-token helpers."""
+import json
+import os
+import pickle
+
+import pytest
+import torch
+
+from rwkvtune_b200.data.tokenizers import AutoTokenizer, RWKVTokenizer, get_tokenizer, get_vocab_path
+from rwkvtune_b200.data.tokenizers import chatml_utils
+from rwkvtune_b200.data.tokenizers.special_token_handler import (SpecialTokenTrie, decode_with_special_tokens,
+                                                                 encode_with_special_tokens)
+
+
+@pytest.fixture(scope="module")
+def base():
+    return get_tokenizer()
+
+
+def _fresh():
+    return RWKVTokenizer(get_vocab_path())
+
+
+@pytest.mark.parametrize("text", ["Hello, world!", "多语言 テキスト 한국어 🙂🚀", "tabs\tand\nnewlines\n\nUser: hi", "\x00\x01 raw",
+                                  "a" * 300 + " " * 17, ""])
+def test_round_trip_and_greedy_longest_match(base, text):
+    ids = base.encode(text)
+    assert base.decode(ids) == text
+    assert all(0 < i < 65530 for i in ids)
+    if text:
+        # greedy longest match: no two neighbouring tokens whose concatenation is itself the longest match at that point
+        first = base.idx2token[ids[0]]
+        longer = [t for t in (text.encode("utf-8")[:len(first) + k] for k in range(1, 4)) if len(t) > len(first)]
+        assert not any(t in base.token2idx for t in longer)
+
+
+def test_eos_is_the_double_newline_and_bytes_decode_tolerantly(base):
+    assert base.eos_token_id == 261 and base.encode("\n\n") == [261]
+    euro = "€".encode("utf-8")
+    ids = [base.token2idx[euro[:1]], base.token2idx[euro[1:2]]]        # a character cut in the middle
+    out = base.decode(ids)
+    assert isinstance(out, str)                                          # no exception, replacement character or partial
+    assert base.decode(ids + [base.token2idx[euro[2:3]]]) == "€"
+
+
+def test_special_tokens_get_reserved_ids_and_split_the_text():
+    tok = _fresh()
+    assert tok.pad_token_id == tok.eos_token_id == 261 and len(tok) == 65530
+    assert tok.add_special_tokens({"additional_special_tokens": ["<|im_start|>", "<|im_end|>"]}) == 2
+    assert tok.add_special_tokens({"additional_special_tokens": ["<|im_start|>"]}) == 0       # already there
+    a, b = tok.additional_special_tokens["<|im_start|>"], tok.additional_special_tokens["<|im_end|>"]
+    assert (a, b) == (65530, 65531) and len(tok) == 65532 and tok.get_added_vocab()["<|im_end|>"] == b
+    ids = tok.encode("<|im_start|>user\nhi<|im_end|>")
+    assert ids[0] == a and ids[-1] == b and a not in ids[1:-1]
+    assert tok.decode(ids) == "<|im_start|>user\nhi<|im_end|>"
+    assert tok.decode(ids, skip_special_tokens=True) == "user\nhi"
+    assert tok.batch_decode([ids, ids[1:-1]], skip_special_tokens=True) == ["user\nhi", "user\nhi"]
+    # a token planted on an existing id takes that id over and can become a role token
+    assert tok.add_special_token_with_id("<|stop|>", 0, set_as="eos_token")
+    assert tok.eos_token == "<|stop|>" and tok.eos_token_id == 0 and tok.encode("x<|stop|>")[-1] == 0
+
+
+def test_call_pads_and_returns_tensors():
+    tok = _fresh()
+    out = tok(["a", "hello world"], return_tensors="pt")
+    assert out["input_ids"].shape == out["attention_mask"].shape == (2, 2)
+    assert out["attention_mask"].tolist() == [[1, 0], [1, 1]] and out["input_ids"][0, 1] == tok.pad_token_id
+    single = tok("hello world")
+    assert single["input_ids"] == tok.encode("hello world")
+    assert isinstance(tok("hi", return_tensors="pt")["input_ids"], torch.Tensor)
+
+
+def test_default_and_chatml_templates():
+    tok = _fresh()
+    msgs = [{"role": "user", "content": "hi"}, {"role": "assistant", "content": "hello"}]
+    plain = tok.apply_chat_template(msgs[:1], tokenize=False, add_generation_prompt=True)
+    assert plain == "User: hi\n\nAssistant:"
+    assert tok.apply_chat_template(msgs[:1], tokenize=True, add_generation_prompt=True) == tok.encode(plain)
+    res = chatml_utils.setup_chatml_tokenizer(tok)
+    assert res["success"] and res["template_set"] and not res["errors"]
+    ok, errors = chatml_utils.validate_chatml_tokenizer(tok)
+    assert ok and errors == []
+    assert tok.eos_token == "<|im_end|>" and tok.eos_token_id == 0          # re-mapped to the unused id 0
+    text = tok.apply_chat_template(msgs, tokenize=False, add_generation_prompt=True)
+    assert text.count("<|im_start|>") == 3 and text.count("<|im_end|>") == 2 and text.endswith("<|im_start|>assistant\n")
+    ids = tok.encode(text)
+    assert ids.count(tok.additional_special_tokens["<|im_start|>"]) == 3 and ids.count(0) == 2
+    good, diag = chatml_utils.verify_chatml_formatting(tok)
+    assert good and diag["num_tokens"] > 0 and not diag["errors"]
+    bare = _fresh()
+    assert chatml_utils.validate_chatml_tokenizer(bare) == (False, ["tokenizer.chat_template is not set"])
+
+
+def test_save_and_reload_keep_special_tokens_and_template(tmp_path):
+    tok = _fresh()
+    chatml_utils.setup_chatml_tokenizer(tok)
+    tok.save_pretrained(str(tmp_path))
+    assert {"vocab.txt", "tokenizer_config.json"} <= set(os.listdir(tmp_path))
+    cfg = json.load(open(tmp_path / "tokenizer_config.json"))
+    assert cfg["eos_token"] == "<|im_end|>" and "<|im_start|>" in json.dumps(cfg)
+    again = AutoTokenizer.from_pretrained(str(tmp_path))
+    sample = "<|im_start|>user\n你好<|im_end|>\n"
+    assert again.encode(sample) == tok.encode(sample) and again.eos_token_id == tok.eos_token_id == 0
+    assert again.chat_template == tok.chat_template
+    assert again.decode(again.encode(sample)) == sample
+
+
+def test_tokenizers_survive_pickling(base):
+    tok = _fresh()
+    tok.add_special_tokens({"additional_special_tokens": ["<|tool|>"]})
+    for t in (base, tok):
+        clone = pickle.loads(pickle.dumps(t))
+        s = "abc <|tool|> 数据"
+        assert clone.encode(s) == t.encode(s) and clone.decode(t.encode(s)) == s
+
+
+def test_text_level_helpers_accept_ids_and_id_sequences(base):
+    mapping = {"<|a|>": 65530, "<|think|>": [65531, 65532], "<|a|><": 65533}      # the longest special token wins
+    ids = encode_with_special_tokens("x<|a|>-<|think|>y<|a|><z", base, mapping)
+    assert ids == (base.encode("x") + [65530] + base.encode("-") + [65531, 65532] + base.encode("y") + [65533]
+                   + base.encode("z"))
+    assert encode_with_special_tokens("plain", base.encode, {}) == base.encode("plain")
+    back = decode_with_special_tokens(ids, base, mapping)
+    assert back == "x<|a|>-<|think|>y<|a|><z"
+    assert decode_with_special_tokens(ids, base.decode, mapping, skip_special_tokens=True) == "x-yz"
+    # a character split over several byte tokens between two special tokens is decoded as one run
+    euro = [base.token2idx[bytes([b])] for b in "€".encode("utf-8")]
+    assert decode_with_special_tokens([65530] + euro + [65530], base, mapping) == "<|a|>€<|a|>"
+    trie = SpecialTokenTrie()
+    for t in mapping:
+        trie.add(t)
+    assert trie.split("<|a|>x<|a|><") == ["<|a|>", "x", "<|a|><"] and trie.split("") == [] and len(trie) == 3
