@@ -7,6 +7,7 @@ A second, gloo-backed group is created next to NCCL for host-side votes and time
 """
 from __future__ import annotations
 
+import atexit
 import datetime
 import os
 from dataclasses import dataclass
@@ -78,6 +79,11 @@ def init_distributed(accelerator: str = "auto", timeout_s: float = 600.0) -> Dis
             kwargs = {"device_id": device} if use_cuda else {}
             dist.init_process_group(backend, rank=rank, world_size=world,
                                     timeout=datetime.timedelta(seconds=timeout_s), **kwargs)
+            if backend == "gloo":
+                # A process that exits with a live gloo group can die in its C++ teardown ("terminate called without
+                # an active exception": about one 8-rank run in four here), which turns a finished run into a failed
+                # one.  Destroying a gloo group is local - no peer takes part - so it is safe on every way out.
+                atexit.register(_shutdown_quietly)
         ctx.backend = dist.get_backend()
         if ctx.backend == "nccl":
             ctx.control_group = dist.new_group(backend="gloo", timeout=datetime.timedelta(seconds=timeout_s))
@@ -87,3 +93,10 @@ def init_distributed(accelerator: str = "auto", timeout_s: float = 600.0) -> Dis
 def shutdown() -> None:
     if dist.is_initialized():
         dist.destroy_process_group()
+
+
+def _shutdown_quietly() -> None:
+    try:
+        shutdown()
+    except Exception:      # interpreter is going down; a failed teardown must not replace the real exit status
+        pass
