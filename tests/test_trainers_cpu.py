@@ -175,3 +175,23 @@ def test_truncated_optimizer_shard_falls_back_to_weights_only_resume(tmp_path, c
     again = str(tmp_path / "again")
     SFTTrainer(_model(), SFTConfig(epoch_count=1, proj_dir=again, resume_from_checkpoint=ck, **common), _dataset()).train()
     assert len(_losses(again)) == 6
+
+
+def test_resume_latest_picks_the_newest_save_point_under_proj_dir(tmp_path, capsys):
+    proj = str(tmp_path / "run")
+    common = dict(ctx_len=32, micro_bsz=4, lr_init=3e-3, warmup_steps=0, accelerator="cpu", precision="fp32", grad_cp=0,
+                  epoch_save=1, save_total_limit=0, proj_dir=proj)
+    PretrainTrainer(_model(), PretrainConfig(epoch_count=2, **common), _dataset()).train()
+    assert {"rwkv7-epoch1", "rwkv7-epoch2"} <= set(os.listdir(proj))
+    capsys.readouterr()
+    tr = PretrainTrainer(_model(), PretrainConfig(epoch_count=3, resume_from_checkpoint="latest", **common), _dataset())
+    tr.train()
+    out = capsys.readouterr().out
+    assert "rwkv7-epoch2" in out and "with optimizer state" in out and "samples_seen=48" in out
+    assert tr.state["samples_seen"] == 72 and len(_losses(proj)) == 18          # 12 records of the first run + 6 new
+    # a parent directory resolves the same way; a path without any save point is an error, not a fresh start
+    from rwkvtune_b200.engine import checkpoint as ckpt
+    assert ckpt.find_checkpoint(proj).endswith("rwkv7-epoch3")
+    with pytest.raises(FileNotFoundError):
+        PretrainTrainer(_model(), PretrainConfig(epoch_count=1, resume_from_checkpoint=str(tmp_path / "nowhere"),
+                                                 **{**common, "proj_dir": str(tmp_path / "other")}), _dataset()).train()
