@@ -92,3 +92,46 @@ def test_sft_example_runs_end_to_end_on_cpu(tmp_path, monkeypatch):
     script.main()
     saved = [d for d in os.listdir(out) if os.path.isdir(os.path.join(out, d))]
     assert any("adapter_model.bin" in os.listdir(os.path.join(out, d)) for d in saved)
+
+
+def _tiny_hub(tmp_path):
+    from rwkvtune_b200.models import RWKVConfig, RWKV7Model
+    from rwkvtune_b200.utils import create_model_hub
+
+    torch.manual_seed(0)
+    cfg = RWKVConfig(n_layer=2, n_embd=64, vocab_size=65536, dim_att_lora=8, dim_gate_lora=8, dim_mv_lora=8, ctx_len=128)
+    raw = str(tmp_path / "raw.pth")
+    torch.save(RWKV7Model(cfg).state_dict(), raw)
+    return create_model_hub(str(tmp_path / "hub"), model_file=raw)
+
+
+def test_grpo_and_generation_examples_run_on_cpu(tmp_path, monkeypatch):
+    """``train_grpo_single_gpu.py`` trains adapters against the seven reward functions and dumps its rollouts;
+    ``test_generation.py`` then loads the adapter directory it saved and writes its JSON report."""
+    import test_generation as gen_script
+    import train_grpo_single_gpu as grpo_script
+
+    hub = _tiny_hub(tmp_path)
+    data = os.path.join(EXAMPLES, "data", "sharegpt_sample.jsonl")
+    out = str(tmp_path / "grpo")
+    monkeypatch.setattr(sys, "argv", [
+        "train_grpo_single_gpu.py", "--model_path", hub, "--data_file", data, "--output_dir", out, "--max_samples", "4",
+        "--micro_bsz", "2", "--num_generations", "2", "--steps_per_generation", "2", "--max_prompt_length", "48",
+        "--max_completion_length", "6", "--lora_r", "4", "--lora_alpha", "8", "--warmup_steps", "0", "--precision", "fp32",
+        "--accelerator", "cpu", "--save_rollout_steps", "1", "--beta", "0.02"])
+    grpo_script.main()
+    recs = [json.loads(l) for l in open(os.path.join(out, "grpo_loss_data.jsonl"))]
+    assert len(recs) == 4 and all(r["loss"] == r["loss"] for r in recs)
+    rollouts = os.listdir(os.path.join(out, "rollouts"))
+    first = json.loads(open(os.path.join(out, "rollouts", sorted(rollouts)[0])).readline())
+    assert {"prompt", "completion", "reward", "advantage"} <= set(first)
+    final = os.path.join(out, "checkpoint_epoch_1")
+    assert {"adapter_model.bin", "adapter_config.json"} <= set(os.listdir(final))
+
+    report = str(tmp_path / "gen.json")
+    monkeypatch.setattr(sys, "argv", [
+        "test_generation.py", "--model_path", hub, "--lora_path", final, "--data_file", data, "--num_samples", "2",
+        "--max_new_tokens", "5", "--device", "cpu", "--output_json", report])
+    gen_script.main()
+    rows = json.load(open(report))
+    assert len(rows) == 2 and all(isinstance(r, dict) and r for r in rows)
