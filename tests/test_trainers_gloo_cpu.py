@@ -26,7 +26,8 @@ def _launch(script, nproc, *args, timeout=420):
         cmd = [sys.executable, str(script), *map(str, args)]
     res = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=timeout, cwd=ROOT)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
-    return [json.loads(m) for m in re.findall(r"^REC (\{.*\})$", res.stdout, flags=re.M)]
+    # two ranks can share an output line: pick the flat JSON objects out, wherever they sit
+    return [json.loads(m) for m in re.findall(r"REC (\{[^{}]*\})", res.stdout)]
 
 
 _PRELUDE = r'''
