@@ -131,3 +131,71 @@ def test_text_level_helpers_accept_ids_and_id_sequences(base):
     for t in mapping:
         trie.add(t)
     assert trie.split("<|a|>x<|a|><") == ["<|a|>", "x", "<|a|><"] and trie.split("") == [] and len(trie) == 3
+
+
+def _native_or_skip(tok):
+    if getattr(tok, "_native", None) is None:
+        pytest.skip("native library not built")
+    return tok
+
+
+def test_native_trie_agrees_with_the_python_walk_on_text_and_raw_bytes(base):
+    import random
+
+    tok = _native_or_skip(base)
+    rng = random.Random(0)
+    alphabet = "abc XYZ,.\n\t的是不了人我在有他这為なにをはが한국어éüß🙂🚀"
+    samples = ["".join(rng.choice(alphabet) for _ in range(rng.randint(0, 400))) for _ in range(60)]
+    for s in samples:
+        b = s.encode("utf-8")
+        assert tok.encodeBytes(b) == tok._encode_python(b)
+    for _ in range(40):                                   # arbitrary bytes, including invalid UTF-8
+        b = bytes(rng.randrange(256) for _ in range(rng.randint(1, 300)))
+        ids = tok.encodeBytes(b)
+        assert ids == tok._encode_python(b) and tok.decodeBytes(ids) == b
+    assert tok.encodeBytes(b"") == []
+
+
+def test_native_batch_encoding_lists_arrays_and_threads(base):
+    import numpy as np
+
+    tok = _native_or_skip(base)
+    texts = ["", "hello world", "多语言 🙂" * 50, "x" * 1000, "\n\n"] * 7
+    want = [tok._encode_python(t.encode("utf-8")) for t in texts]
+    for threads in (1, 3, 0):
+        assert tok.encode_batch(texts, num_threads=threads) == want
+    arrays = tok.encode_batch(texts, return_arrays=True)
+    assert all(isinstance(a, np.ndarray) and a.dtype == np.int32 for a in arrays) and [a.tolist() for a in arrays] == want
+    assert tok.encode_batch([]) == []
+
+
+def test_native_trie_sees_tokens_added_later_and_survives_pickling():
+    tok = _native_or_skip(_fresh())
+    tok.add_special_tokens({"additional_special_tokens": ["<|late|>"]})
+    late = tok.additional_special_tokens["<|late|>"]
+    # the raw byte path too: the new token is part of the trie, not only of the text-level splitter
+    assert tok.encodeBytes("a<|late|>b".encode()) == tok._encode_python("a<|late|>b".encode())
+    assert late in tok.encodeBytes("a<|late|>b".encode())
+    clone = pickle.loads(pickle.dumps(tok))
+    assert clone._native is not None and clone._native is not tok._native
+    assert clone.encodeBytes("a<|late|>b".encode()) == tok.encodeBytes("a<|late|>b".encode())
+
+
+def test_python_fallback_is_complete_and_reports_uncovered_bytes(tmp_path, monkeypatch):
+    from rwkvtune_b200.data.tokenizers import rwkv_tokenizer as mod
+
+    vocab = tmp_path / "tiny_vocab.txt"
+    vocab.write_text("1 'a' 1\n2 'b' 1\n3 'ab' 2\n4 'abc' 3\n5 b'\\xff' 1\n")
+    for native in (True, False):
+        monkeypatch.setattr(mod._NativeTrie, "_tried", not native)
+        monkeypatch.setattr(mod._NativeTrie, "_lib", None)
+        tok = mod.TRIE_TOKENIZER(str(vocab), eos_token="a")
+        if not native:
+            assert tok._native is None and tok._next is not None
+        assert tok.encode("abab") == [3, 3] and tok.encode("abca") == [4, 1] and tok.encodeBytes(b"a\xffb") == [1, 5, 2]
+        assert tok.encode_batch(["ab", "ba"]) == [[3], [2, 1]]
+        with pytest.raises(ValueError, match="offset 2"):
+            tok.encode("abz")
+        with pytest.raises(ValueError, match="text 1"):
+            tok.encode_batch(["ab", "zz"])
+    monkeypatch.setattr(mod._NativeTrie, "_tried", False)
