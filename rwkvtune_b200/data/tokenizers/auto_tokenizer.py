@@ -192,6 +192,20 @@ class RWKVTokenizer(TRIE_TOKENIZER):
                 ids = ids + [self.eos_token_id]
         return ids
 
+    def encode_batch(self, texts: Sequence[str], num_threads: int = 0, return_arrays: bool = False,
+                     add_special_tokens: bool = True):
+        """:meth:`encode` of every text.  Plain configurations go to the native batch call; with registered special
+        tokens or BOS / EOS insertion every text takes the :meth:`encode` route, so the ids are the same either way."""
+        plain = not len(self._special_token_trie) and not (add_special_tokens and (self.add_bos_token or self.add_eos_token))
+        if plain:
+            return super().encode_batch(texts, num_threads, return_arrays)
+        out = [self.encode(t, add_special_tokens=add_special_tokens) for t in texts]
+        if return_arrays:
+            import numpy as np
+
+            return [np.asarray(o, dtype=np.int32) for o in out]
+        return out
+
     def decode(self, token_ids, skip_special_tokens: bool = False, **kwargs: Any) -> str:
         if hasattr(token_ids, "tolist"):
             token_ids = token_ids.tolist()
@@ -214,7 +228,8 @@ class RWKVTokenizer(TRIE_TOKENIZER):
     def __call__(self, text: Union[str, Sequence[str]], return_tensors: Optional[str] = None, padding: bool = True,
                  **kwargs: Any):
         single = isinstance(text, str)
-        seqs = [self.encode(t) for t in ([text] if single else text)]
+        texts = [text] if single else list(text)
+        seqs = self.encode_batch(texts) if len(texts) > 1 else [self.encode(texts[0])]
         if return_tensors == "pt":
             import torch
 

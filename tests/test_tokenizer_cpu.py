@@ -199,3 +199,19 @@ def test_python_fallback_is_complete_and_reports_uncovered_bytes(tmp_path, monke
         with pytest.raises(ValueError, match="text 1"):
             tok.encode_batch(["ab", "zz"])
     monkeypatch.setattr(mod._NativeTrie, "_tried", False)
+
+
+def test_batch_encoding_of_the_full_tokenizer_matches_encode_in_every_configuration():
+    texts = ["hello <|im_start|>user", "plain text", "<|im_end|>", ""]
+    plain = _fresh()
+    assert plain.encode_batch(texts) == [plain.encode(t) for t in texts]
+    assert plain(texts)["input_ids"] == [plain.encode(t) for t in texts]
+    special = _fresh()
+    special.add_special_tokens({"additional_special_tokens": ["<|im_start|>", "<|im_end|>"]})
+    assert special.encode_batch(texts) == [special.encode(t) for t in texts]
+    assert special.encode_batch(texts)[2] == [special.additional_special_tokens["<|im_end|>"]]
+    framed = RWKVTokenizer(get_vocab_path(), add_eos_token=True)
+    assert framed.encode_batch(texts) == [framed.encode(t) for t in texts] and framed.encode_batch(texts)[1][-1] == 261
+    assert framed.encode_batch(texts, add_special_tokens=False) == [framed.encode(t, add_special_tokens=False) for t in texts]
+    arrays = special.encode_batch(texts, return_arrays=True)
+    assert [a.tolist() for a in arrays] == special.encode_batch(texts)
