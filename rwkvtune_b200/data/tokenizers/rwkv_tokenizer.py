@@ -115,20 +115,36 @@ class _NativeTrie:
             pass
 
 
+_VOCAB_CACHE: Dict[str, tuple] = {}
+
+
+def _read_vocab(file_name: str) -> Dict[int, bytes]:
+    """Parsed vocabulary file, kept per (path, size, mtime): a process usually builds several tokenizers over the same
+    file (trainer, generator, pipeline), and parsing 65 k literals takes longer than everything else in the constructor."""
+    st = os.stat(file_name)
+    key = (st.st_size, st.st_mtime_ns)
+    hit = _VOCAB_CACHE.get(file_name)
+    if hit is not None and hit[0] == key:
+        return hit[1]
+    table: Dict[int, bytes] = {}
+    with open(file_name, "r", encoding="utf-8") as fh:
+        for line in fh:
+            sp1 = line.index(" ")
+            sp2 = line.rindex(" ")
+            idx = int(line[:sp1])
+            tok = ast.literal_eval(line[sp1 + 1:sp2])
+            tok = tok.encode("utf-8") if isinstance(tok, str) else tok
+            if len(tok) != int(line[sp2 + 1:]):
+                raise ValueError(f"vocabulary line for id {idx} has inconsistent byte length")
+            table[idx] = tok
+    _VOCAB_CACHE[file_name] = (key, table)
+    return table
+
+
 class TRIE_TOKENIZER:
     def __init__(self, file_name: str, eos_token: Optional[Union[str, int]] = None):
         self.file_name = file_name
-        self.idx2token: Dict[int, bytes] = {}
-        with open(file_name, "r", encoding="utf-8") as fh:
-            for line in fh:
-                sp1 = line.index(" ")
-                sp2 = line.rindex(" ")
-                idx = int(line[:sp1])
-                tok = ast.literal_eval(line[sp1 + 1:sp2])
-                tok = tok.encode("utf-8") if isinstance(tok, str) else tok
-                if len(tok) != int(line[sp2 + 1:]):
-                    raise ValueError(f"vocabulary line for id {idx} has inconsistent byte length")
-                self.idx2token[idx] = tok
+        self.idx2token: Dict[int, bytes] = dict(_read_vocab(file_name))
         self.token2idx: Dict[bytes, int] = {t: i for i, t in self.idx2token.items()}
         self._build_trie()
         self.vocab_size = max(self.idx2token) + 1
