@@ -25,6 +25,11 @@ def _launch(script, nproc, *args, timeout=420):
     if nproc == 1:
         cmd = [sys.executable, str(script), *map(str, args)]
     res = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=timeout, cwd=ROOT)
+    trouble = ("address already in use", "eaddrinuse", "connection refused", "failed to connect", "socket timeout")
+    if res.returncode != 0 and nproc > 1 and any(t in (res.stdout + res.stderr).lower() for t in trouble):
+        # the port that was free a moment ago was taken before the launcher bound it: once more on another one
+        cmd[cmd.index("--master-port") + 1] = str(_free_port())
+        res = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=timeout, cwd=ROOT)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
     # two ranks can share an output line: pick the flat JSON objects out, wherever they sit
     return [json.loads(m) for m in re.findall(r"REC (\{[^{}]*\})", res.stdout)]
