@@ -77,3 +77,56 @@ def test_bucket_plan_covers_the_space_with_whole_parameters():
     assert one == [0, padded] and set(sb) == {0}
     many, _ = plan_buckets(segs, padded, 1, max_buckets=4)       # capped
     assert len(many) - 1 <= 4
+
+
+def test_step_profiler_writes_a_table_for_the_requested_steps(tmp_path, monkeypatch):
+    import os
+
+    from rwkvtune_b200.engine.profiling import StepProfiler, profile_steps_requested
+
+    class Args:
+        profile_steps = 2
+
+    monkeypatch.delenv("RWKVTUNE_PROFILE", raising=False)
+    assert profile_steps_requested(Args()) == 2 and profile_steps_requested(object()) == 0
+    monkeypatch.setenv("RWKVTUNE_PROFILE", "5")
+    assert profile_steps_requested(Args()) == 5                     # the environment wins
+    monkeypatch.setenv("RWKVTUNE_PROFILE", "off")
+    assert profile_steps_requested(Args()) == 2
+
+    prof = StepProfiler(2, str(tmp_path / "run"), skip=1)
+    a = torch.randn(64, 64)
+    for step in range(5):
+        prof.step_begin()
+        (a @ a).sum()
+        prof.step_end()
+        # recording spans exactly steps 1 and 2
+        assert (prof.prof is not None) == (step == 1)
+    text = open(os.path.join(str(tmp_path / "run"), "profile_kernels.txt")).read()
+    assert text.startswith("2 training steps after 1 warm-up steps") and "aten::mm" in text
+    quiet = StepProfiler(1, str(tmp_path / "other"), skip=0, is_main=False)
+    quiet.step_begin()
+    quiet.step_end()
+    assert not os.path.exists(str(tmp_path / "other"))
+    off = StepProfiler(0, str(tmp_path / "off"))
+    off.step_begin()
+    off.step_end()
+    assert off.prof is None and not os.path.exists(str(tmp_path / "off"))
+
+
+def test_trainer_profile_steps_switch(tmp_path, monkeypatch):
+    import os
+
+    from rwkvtune_b200 import SFTConfig, SFTTrainer
+    from rwkvtune_b200.models import RWKVConfig, RWKV7Model
+
+    monkeypatch.delenv("RWKVTUNE_PROFILE", raising=False)
+    torch.manual_seed(0)
+    model = RWKV7Model(RWKVConfig(n_layer=1, n_embd=64, vocab_size=64, dim_att_lora=8, dim_gate_lora=8, dim_mv_lora=8))
+    rows = [{"input_ids": list(range(1, 17)), "labels": list(range(2, 18))} for _ in range(12)]
+    proj = str(tmp_path / "p")
+    args = SFTConfig(ctx_len=16, micro_bsz=2, epoch_count=1, accelerator="cpu", precision="fp32", proj_dir=proj, grad_cp=0,
+                     profile_steps=1)
+    SFTTrainer(model, args, rows).train()
+    text = open(os.path.join(proj, "profile_kernels.txt")).read()
+    assert text.startswith("1 training steps after 3 warm-up steps") and "aten::" in text
