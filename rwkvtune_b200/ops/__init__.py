@@ -205,7 +205,12 @@ def wkv7(r, w, k, v, a, b, head_size: int = 64, state: Optional[torch.Tensor] = 
     """WKV7 recurrence.  Returns ``(y, final_state or None)``; ``y`` has the dtype of ``r``."""
     if _native(r, "wkv7"):
         return _cuda().wkv7(r, w, k, v, a, b, head_size, state, return_state)
-    y, s = reference.wkv7(r, w, k, v, a, b, head_size, state)
+    if r.device.type == "cpu":      # one autograd node with a closed-form backward instead of the traced statement
+        from . import cpu_ops
+
+        y, s = cpu_ops.wkv7(r, w, k, v, a, b, head_size, state)
+    else:
+        y, s = reference.wkv7(r, w, k, v, a, b, head_size, state)
     return y.to(r.dtype), (s if return_state else None)
 
 

@@ -82,7 +82,9 @@ class ZeroOptimizer:
                       _ext.ptr(g if g.dtype == torch.bfloat16 else g.to(torch.bfloat16)), _ext.i64(g.numel()),
                       _ext.f32(scale), _ext.ptr(self._scratch), _ext.ptr(self.norm_sq), _ext.i32(0), _ext.stream())
         else:
-            self.norm_sq.copy_((g.float() * scale).square().sum().reshape(1))
+            from ..ops import cpu_ops
+
+            self.norm_sq.copy_(cpu_ops.grad_norm_sq(g, scale).reshape(1))
         if self.stage >= 1:
             dist.all_reduce(self.norm_sq)
 
@@ -108,8 +110,17 @@ class ZeroOptimizer:
                 if self.grad_clip > 0:
                     nrm = float(self.norm_sq.sqrt())
                     coef *= min(1.0, self.grad_clip / (nrm + 1e-6))
-                ref.adamw_step(self.master[a:b], g[a:b], self.exp_avg[a:b], self.exp_avg_sq[a:b], lr * grp.lr_scale,
-                               self.beta1, self.beta2, self.eps, grp.weight_decay, self.step_count, coef)
+                if g.is_cuda:
+                    ref.adamw_step(self.master[a:b], g[a:b], self.exp_avg[a:b], self.exp_avg_sq[a:b], lr * grp.lr_scale,
+                                   self.beta1, self.beta2, self.eps, grp.weight_decay, self.step_count, coef)
+                else:
+                    from ..ops import cpu_ops
+
+                    if getattr(self, "_cpu_scratch", None) is None or self._cpu_scratch.numel() < b - a:
+                        self._cpu_scratch = torch.empty(self.hi - self.lo, dtype=torch.float32)
+                    cpu_ops.adamw_step(self.master[a:b], g[a:b], self.exp_avg[a:b], self.exp_avg_sq[a:b],
+                                       lr * grp.lr_scale, self.beta1, self.beta2, self.eps, grp.weight_decay,
+                                       self.step_count, coef, self._cpu_scratch[:b - a])
                 p_out.copy_(self.master[a:b])
 
     def _gather_params(self) -> None:
