@@ -1,7 +1,7 @@
 """Ahead-of-time build of the native library for sm_100a.
 
 ``python -m rwkvtune_b200.csrc.build`` compiles every ``*.cu`` in this directory with
-``nvcc -gencode arch=compute_100a,code=sm_100a`` and links them into
+``nvcc -gencode arch=compute_100a,code=sm_100a`` (and the host-only ``*.cpp`` files with the host compiler) and links them into
 ``librwkvtune_b200.so`` next to the sources.  The kernels depend on the CUDA runtime
 only (no libtorch), so nvcc cross-compiles them on a machine without a GPU in a few
 seconds per file.  The reference instead JIT-compiles its kernels on the user's
@@ -34,8 +34,19 @@ def nvcc_path() -> str:
     return found
 
 
+HOST_FLAGS = ["-O3", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-fno-math-errno"]
+
+
 def sources() -> List[str]:
-    return sorted(f for f in os.listdir(HERE) if f.endswith(".cu"))
+    """Every ``*.cu`` (nvcc, sm_100a) and every ``*.cpp`` (host-only code, the host compiler) in this directory."""
+    return sorted(f for f in os.listdir(HERE) if f.endswith((".cu", ".cpp")))
+
+
+def host_compiler() -> str:
+    found = shutil.which(os.environ.get("CXX", "g++")) or shutil.which("c++")
+    if not found:
+        raise RuntimeError("no host C++ compiler found; set CXX")
+    return found
 
 
 def _digest(path: str) -> str:
@@ -43,7 +54,7 @@ def _digest(path: str) -> str:
     for dep in [path] + sorted(os.path.join(HERE, f) for f in os.listdir(HERE) if f.endswith(".cuh")):
         with open(dep, "rb") as fh:
             h.update(fh.read())
-    h.update(" ".join(ARCH_FLAGS + COMMON_FLAGS).encode())
+    h.update(" ".join(HOST_FLAGS if path.endswith(".cpp") else ARCH_FLAGS + COMMON_FLAGS).encode())
     return h.hexdigest()
 
 
@@ -54,18 +65,23 @@ DEBUG_FLAGS = ["-DRWKV_DEBUG_BOUNDS"]
 def _compile_one(src: str, verbose: bool, debug: bool = False) -> str:
     obj_dir = os.path.join(HERE, "build_debug" if debug else "build")
     os.makedirs(obj_dir, exist_ok=True)
-    obj = os.path.join(obj_dir, src[:-3] + ".o")
+    stem = os.path.splitext(src)[0]
+    obj = os.path.join(obj_dir, stem + ".o")
     stamp = obj + ".sha"
     digest = _digest(os.path.join(HERE, src)) + ("-debug" if debug else "")
     if os.path.exists(obj) and os.path.exists(stamp) and open(stamp).read() == digest:
         return obj
-    cmd = ([nvcc_path()] + ARCH_FLAGS + COMMON_FLAGS + (DEBUG_FLAGS if debug else [])
-           + ["-Xptxas", "-v", "-c", os.path.join(HERE, src), "-o", obj])
+    if src.endswith(".cpp"):
+        cmd = [host_compiler()] + HOST_FLAGS + (DEBUG_FLAGS if debug else []) + ["-c", os.path.join(HERE, src), "-o", obj]
+    else:
+        cmd = ([nvcc_path()] + ARCH_FLAGS + COMMON_FLAGS + (DEBUG_FLAGS if debug else [])
+               + ["-Xptxas", "-v", "-c", os.path.join(HERE, src), "-o", obj])
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
-        raise RuntimeError(f"nvcc failed for {src}:\n{res.stdout}\n{res.stderr}")
-    with open(os.path.join(obj_dir, src[:-3] + ".ptxas.txt"), "w") as fh:
-        fh.write(res.stderr)
+        raise RuntimeError(f"compilation failed for {src}:\n{res.stdout}\n{res.stderr}")
+    if src.endswith(".cu"):
+        with open(os.path.join(obj_dir, stem + ".ptxas.txt"), "w") as fh:
+            fh.write(res.stderr)
     if verbose:
         print(f"[build] {src} ok")
     with open(stamp, "w") as fh:

@@ -6,15 +6,110 @@ state ``S_0 .. S_T`` in one buffer, the backward is the closed-form reverse recu
 time (the outer products ``v k^T``, the read-out ``S_t r_t``, ``u_t = S_{t-1} a_t``, the gradients of ``r`` and ``a``);
 what is left in the Python loops is three small batched operations per step forward and seven backward, against the
 several dozen that autograd records for the traced statement (each ``x[:, t]`` alone costs a full-size zero fill in
-its backward).  On the 0.1B model at 2 x 256 tokens that takes a CPU training step from 6.8 s to about 2 s; the
-reference's CPU operator (``rwkvtune/models/rwkv7/operators/wkv_cpu.py:9-80``, traced by autograd) needs 5.9 s on the
-same machine.  The traced statement stays the oracle of the tests.
+its backward).  On the 0.1B model at 2 x 256 tokens that takes a CPU training step from 6.8 s to 3.0 s; the reference's
+CPU operator (``rwkvtune/models/rwkv7/operators/wkv_cpu.py:9-80``, traced by autograd) needs 5.9 s on the same
+machine.  When the native library is built the same algebra runs there (``csrc/wkv7_cpu.cpp``: one (batch, head)
+problem per thread, vectorised rows, one kept state per 16 steps and the rest rebuilt in the backward); the PyTorch form remains the fallback, and the traced statement stays the
+oracle of the tests.
 """
 from __future__ import annotations
 
+import ctypes
+import os
 from typing import Optional, Tuple
 
 import torch
+
+_NATIVE = None
+_NATIVE_TRIED = False
+
+
+def _native_lib():
+    """The package's native library when it carries the host WKV7 functions (``csrc/wkv7_cpu.cpp``); ``None`` when it
+    is not built or ``RWKVTUNE_NATIVE_CPU=0``.  The pure-PyTorch forms below are the fallback."""
+    global _NATIVE, _NATIVE_TRIED
+    if not _NATIVE_TRIED:
+        _NATIVE_TRIED = True
+        if os.environ.get("RWKVTUNE_NATIVE_CPU", "1") != "0":
+            path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "csrc", "librwkvtune_b200.so")
+            try:
+                lib = ctypes.CDLL(path)
+                lib.rwkv_wkv7_cpu_forward.argtypes = [ctypes.c_void_p] * 11 + [ctypes.c_int] * 5
+                lib.rwkv_wkv7_cpu_backward.argtypes = [ctypes.c_void_p] * 17 + [ctypes.c_int] * 5
+                lib.rwkv_wkv7_cpu_history_states.argtypes = [ctypes.c_int]
+                _NATIVE = lib
+            except (OSError, AttributeError):
+                _NATIVE = None
+    return _NATIVE
+
+
+def _p(t: Optional[torch.Tensor]):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _threads(work_items: int) -> int:
+    return max(1, min(torch.get_num_threads(), work_items))
+
+
+def _flat32(t: torch.Tensor) -> torch.Tensor:
+    return t.detach().float().contiguous()
+
+
+class _WKV7Native(torch.autograd.Function):
+    """The recurrence in the native library: one (batch, head) problem per thread, state history kept for the backward."""
+
+    @staticmethod
+    def forward(ctx, r, w, k, v, a, b, state, head_size: int):
+        lib = _native_lib()
+        B, T, C = r.shape
+        N = head_size
+        H = C // N
+        ins = [_flat32(t) for t in (r, w, k, v, a, b)]
+        s0 = None if state is None else _flat32(state)
+        history = torch.empty(B * H, lib.rwkv_wkv7_cpu_history_states(T), N, N, dtype=torch.float32)
+        decay = torch.empty(B, T, C, dtype=torch.float32)
+        y = torch.empty(B, T, C, dtype=torch.float32)
+        final = torch.empty(B, H, N, N, dtype=torch.float32)
+        rc = lib.rwkv_wkv7_cpu_forward(*[_p(t) for t in ins], _p(s0), _p(history), _p(final), _p(y), _p(decay), B, T, H, N,
+                                       _threads(B * H))
+        if rc != 0:
+            raise RuntimeError(f"rwkv_wkv7_cpu_forward refused the shapes (status {rc})")
+        ctx.save_for_backward(*ins, decay, history)
+        ctx.dims = (B, T, H, N)
+        ctx.dtypes = tuple(t.dtype for t in (r, w, k, v, a, b))
+        ctx.state_dtype = None if state is None else state.dtype
+        return y, final
+
+    @staticmethod
+    def backward(ctx, dy, dstate):
+        lib = _native_lib()
+        r, w, k, v, a, b, decay, history = ctx.saved_tensors
+        B, T, H, N = ctx.dims
+        dy = _flat32(dy)
+        ds = None if dstate is None else _flat32(dstate)
+        grads = [torch.empty(B, T, H * N, dtype=torch.float32) for _ in range(6)]
+        ds0 = torch.empty(B, H, N, N, dtype=torch.float32) if ctx.state_dtype is not None else None
+        rc = lib.rwkv_wkv7_cpu_backward(_p(r), _p(w), _p(k), _p(v), _p(a), _p(b), _p(decay), _p(history), _p(dy), _p(ds),
+                                        *[_p(g) for g in grads], _p(ds0), B, T, H, N, _threads(B * H))
+        if rc != 0:
+            raise RuntimeError(f"rwkv_wkv7_cpu_backward refused the shapes (status {rc})")
+        out = [g.to(dt) for g, dt in zip(grads, ctx.dtypes)]
+        return (*out, None if ds0 is None else ds0.to(ctx.state_dtype), None)
+
+
+def _wkv7_native_nograd(r, w, k, v, a, b, head_size: int, state):
+    lib = _native_lib()
+    B, T, C = r.shape
+    N = head_size
+    H = C // N
+    ins = [_flat32(t) for t in (r, w, k, v, a, b)]
+    s0 = None if state is None else _flat32(state)
+    y = torch.empty(B, T, C, dtype=torch.float32)
+    final = torch.empty(B, H, N, N, dtype=torch.float32)
+    rc = lib.rwkv_wkv7_cpu_forward(*[_p(t) for t in ins], _p(s0), None, _p(final), _p(y), None, B, T, H, N, _threads(B * H))
+    if rc != 0:
+        raise RuntimeError(f"rwkv_wkv7_cpu_forward refused the shapes (status {rc})")
+    return y, final
 
 
 def _time_major(t: torch.Tensor, B: int, T: int, H: int, N: int) -> torch.Tensor:
@@ -104,8 +199,11 @@ def wkv7(r, w, k, v, a, b, head_size: int = 64, state: Optional[torch.Tensor] = 
     ``[B, H, N, N]``; returns ``(y [B, T, C] fp32, final_state [B, H, N, N] fp32)``.  With autograd off nothing but
     the running state is kept."""
     needs_grad = torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (r, w, k, v, a, b, state))
+    native = r.device.type == "cpu" and head_size <= 256 and r.shape[1] > 0 and _native_lib() is not None
     if needs_grad:
-        return _WKV7.apply(r, w, k, v, a, b, state, head_size)
+        return (_WKV7Native if native else _WKV7).apply(r, w, k, v, a, b, state, head_size)
+    if native:
+        return _wkv7_native_nograd(r, w, k, v, a, b, head_size, state)
     B, T, C = r.shape
     N = head_size
     H = C // N

@@ -17,9 +17,20 @@ def _inputs(B, T, H, N, seed=0, dtype=torch.float32):
     return [t.to(dtype) for t in (r, w, k, v, a, b)], state
 
 
+@pytest.fixture(params=["native", "torch"])
+def form(request, monkeypatch):
+    """Both forms of the fast recurrence: inside the native library, and the pure-PyTorch one it falls back to."""
+    if request.param == "torch":
+        monkeypatch.setattr(cpu_ops, "_NATIVE", None)
+        monkeypatch.setattr(cpu_ops, "_NATIVE_TRIED", True)
+    elif cpu_ops._native_lib() is None:
+        pytest.skip("native library not built")
+    return request.param
+
+
 @pytest.mark.parametrize("shape,with_state", [((2, 9, 2, 8), True), ((1, 17, 3, 16), False), ((2, 33, 2, 64), True),
-                                              ((1, 1, 1, 64), True)])
-def test_recurrence_node_matches_the_traced_statement(shape, with_state):
+                                              ((1, 1, 1, 64), True), ((1, 16, 1, 8), True), ((2, 48, 1, 8), False)])
+def test_recurrence_node_matches_the_traced_statement(form, shape, with_state):
     B, T, H, N = shape
     ins, s0 = _inputs(B, T, H, N)
     s0 = s0 if with_state else None
@@ -34,15 +45,15 @@ def test_recurrence_node_matches_the_traced_statement(shape, with_state):
         got.append((y.detach(), s.detach()) + grads)
     for name, want, have in zip("y s dr dw dk dv da db ds0".split(), *got):
         assert have.dtype == want.dtype and have.shape == want.shape
-        assert float((want - have).abs().max()) <= 2e-6 * float(want.abs().max()) + 1e-7, name
+        assert float((want - have).abs().max()) <= 3e-6 * float(want.abs().max()) + 1e-7, name
     with torch.no_grad():
         y, s = cpu_ops.wkv7(*ins, N, s0)
-    assert torch.allclose(y, got[0][0], atol=1e-6) and torch.allclose(s, got[0][1], atol=1e-6)
+    assert torch.allclose(y, got[0][0], atol=5e-6) and torch.allclose(s, got[0][1], atol=5e-6)
     if s0 is not None:
         assert not torch.equal(s, s0) and s.data_ptr() != s0.data_ptr()              # the caller's state is left alone
 
 
-def test_low_precision_inputs_get_gradients_of_their_own_dtype_and_partial_requires_grad():
+def test_low_precision_inputs_get_gradients_of_their_own_dtype_and_partial_requires_grad(form):
     ins, s0 = _inputs(1, 6, 2, 8, dtype=torch.bfloat16)
     leaves = [t.clone().requires_grad_(i % 2 == 0) for i, t in enumerate(ins)]
     y, s = cpu_ops.wkv7(*leaves, 8, s0)
@@ -51,11 +62,12 @@ def test_low_precision_inputs_get_gradients_of_their_own_dtype_and_partial_requi
     assert all((t.grad is not None and t.grad.dtype == torch.bfloat16) == (i % 2 == 0) for i, t in enumerate(leaves))
 
 
-def test_dispatch_uses_the_node_for_cpu_tensors_and_keeps_the_contract():
+def test_dispatch_uses_the_node_for_cpu_tensors_and_keeps_the_contract(form):
     ins, s0 = _inputs(2, 5, 2, 8)
     leaves = [t.clone().requires_grad_(True) for t in ins]
     y, s = ops.wkv7(*leaves, 8, s0, True)
-    assert type(y.grad_fn).__name__ == "_WKV7Backward" and s.shape == (2, 2, 8, 8)
+    assert type(y.grad_fn).__name__ == ("_WKV7NativeBackward" if form == "native" else "_WKV7Backward")
+    assert s.shape == (2, 2, 8, 8)
     y2, none = ops.wkv7(*ins, 8)
     assert none is None and torch.allclose(y2, reference.wkv7(*ins, 8)[0], atol=1e-6)
 
