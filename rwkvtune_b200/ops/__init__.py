@@ -220,7 +220,12 @@ def wkv7_pool_step(r, w, k, v, a, b, pool: torch.Tensor, slots: torch.Tensor, he
     if _native(r, "wkv7") and head_size == 64:
         return _cuda().wkv7_pool_step(r, w, k, v, a, b, pool, slots)
     with torch.no_grad():
-        y, s = reference.wkv7(r, w, k, v, a, b, head_size, pool.index_select(0, slots))
+        if r.device.type == "cpu":
+            from . import cpu_ops
+
+            y, s = cpu_ops.wkv7(r, w, k, v, a, b, head_size, pool.index_select(0, slots))
+        else:
+            y, s = reference.wkv7(r, w, k, v, a, b, head_size, pool.index_select(0, slots))
         pool.index_copy_(0, slots, s.to(pool.dtype))
     return y.to(r.dtype)
 
