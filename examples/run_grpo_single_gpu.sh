@@ -25,5 +25,6 @@ ARGS=(--model_path "$MODEL_PATH"
       --save_rollout_steps "${SAVE_ROLLOUT_STEPS:-0}")
 [[ -n "${REWARD_WEIGHTS:-}" ]] && ARGS+=(--reward_weights "$REWARD_WEIGHTS")
 [[ -n "${SAVE_ROLLOUT_PATH:-}" ]] && ARGS+=(--save_rollout_path "$SAVE_ROLLOUT_PATH")
+[[ -n "${ACCELERATOR:-}" ]] && ARGS+=(--accelerator "$ACCELERATOR")      # ACCELERATOR=cpu PRECISION=fp32 runs on the host
 [[ -n "${REPORT_TO:-}" ]] && ARGS+=(--report_to "$REPORT_TO" --run_name "${RUN_NAME:-grpo}")
 CUDA_VISIBLE_DEVICES="${GPU_ID:-0}" exec python train_grpo_single_gpu.py "${ARGS[@]}"

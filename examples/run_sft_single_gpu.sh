@@ -21,5 +21,6 @@ if [[ "${USE_LORA:-0}" == "1" ]]; then
   ARGS+=(--use_lora --lora_r "${LORA_R:-64}" --lora_alpha "${LORA_ALPHA:-128}" --lora_dropout "${LORA_DROPOUT:-0.0}")
 fi
 [[ "${LAST_REPLY_ONLY:-0}" == "1" ]] && ARGS+=(--last_reply_only)
+[[ -n "${ACCELERATOR:-}" ]] && ARGS+=(--accelerator "$ACCELERATOR")      # ACCELERATOR=cpu PRECISION=fp32 runs on the host
 [[ -n "${REPORT_TO:-}" ]] && ARGS+=(--report_to "$REPORT_TO" --run_name "${RUN_NAME:-sft}")
 CUDA_VISIBLE_DEVICES="${GPU_ID:-0}" exec python train_sft_single_gpu.py "${ARGS[@]}"
