@@ -110,5 +110,34 @@ def build(verbose: bool = True, force: bool = False, debug: bool = False) -> str
     return lib
 
 
+def ptxas_table(debug: bool = False) -> str:
+    """Markdown table of what ``ptxas -v`` reported for every kernel of the last build: registers, stack frame,
+    spill stores / loads and static shared memory (dynamic shared memory is a launch parameter and not listed)."""
+    import re
+
+    obj_dir = os.path.join(HERE, "build_debug" if debug else "build")
+    lines = ["| source | kernel | registers | stack frame (B) | spill stores / loads (B) | static shared memory (B) |",
+             "|---|---|---|---|---|---|"]
+    demangle = shutil.which("c++filt")
+    for src in sources():
+        path = os.path.join(obj_dir, os.path.splitext(src)[0] + ".ptxas.txt")
+        if not src.endswith(".cu") or not os.path.exists(path):
+            continue
+        for block in re.split(r"ptxas info\s+: Compiling entry function '", open(path).read())[1:]:
+            name = block.split("'")[0]
+            if demangle:
+                name = subprocess.run([demangle, name], capture_output=True, text=True).stdout.strip() or name
+            name = re.sub(r"^void ", "", name.replace("(anonymous namespace)::", "").split("(")[0])
+            regs = re.search(r"Used (\d+) registers", block)
+            frame = re.search(r"(\d+) bytes stack frame, (\d+) bytes spill stores, (\d+) bytes spill loads", block)
+            smem = re.search(r"(\d+) bytes smem", block)
+            lines.append(f"| `{src}` | `{name}` | {regs.group(1) if regs else '?'} | {frame.group(1) if frame else '?'} | "
+                         f"{frame.group(2) if frame else '?'} / {frame.group(3) if frame else '?'} | "
+                         f"{smem.group(1) if smem else 0} |")
+    return "\n".join(lines)
+
+
 if __name__ == "__main__":
     build(verbose=True, force="--force" in sys.argv, debug="--debug" in sys.argv)
+    if "--ptxas" in sys.argv:
+        print(ptxas_table(debug="--debug" in sys.argv))
