@@ -164,6 +164,7 @@ class SupervisedTrainer:
 
         a, ctx, eng = self.args, self.ctx, self.engine
         profiler = StepProfiler(profile_steps_requested(a), a.proj_dir, is_main=ctx.is_main)
+        tuned = False
         for epoch in range(start_epoch, a.epoch_count):
             self.state["epoch"] = epoch
             loss_sum, n_loss = 0.0, 0
@@ -179,6 +180,9 @@ class SupervisedTrainer:
                 profiler.step_end()
                 self.state["samples_seen"] += samples_per_batch
                 self.state["global_batch"] += 1
+                if not tuned:
+                    tuned = True
+                    self._tune_checkpointing(batch["input_ids"].shape[1])
                 if ctx.world_size > 1 and (b + 1) % a.log_every_n_steps == 0:
                     t = torch.tensor([loss], device=ctx.device)
                     torch.distributed.all_reduce(t)
@@ -205,6 +209,24 @@ class SupervisedTrainer:
             self.callbacks.fire("on_train_epoch_end", self, epoch)
             if (a.epoch_save > 0 and (epoch + 1) % a.epoch_save == 0) or epoch == a.epoch_count - 1:
                 self._save_checkpoint(f"rwkv7-epoch{epoch + 1}")
+
+    def _tune_checkpointing(self, first_len: int) -> None:
+        """After the first step (every block recomputed, memory peak known): keep the activations of as many blocks as
+        fit and recompute only the rest (``TrainEngine.autotune_checkpointing``).  Only for ``grad_cp=1`` in normal mode
+        on a GPU, and only when the first batch of every rank was ``ctx_len`` long - with shorter first batches the
+        measured peak says nothing about the longest one, and every block stays recomputed as in the reference.
+        ``RWKVTUNE_GRAD_CP_AUTO=0`` switches it off."""
+        a, ctx, eng = self.args, self.ctx, self.engine
+        if not a.grad_cp or a.train_type != "normal" or ctx.device.type != "cuda":
+            return
+        if os.environ.get("RWKVTUNE_GRAD_CP_AUTO", "1") == "0":
+            return
+        full = ctx.all_agree(first_len >= a.ctx_len)          # one host-side agreement: every rank takes the same branch
+        if not full:
+            return
+        n_cp = eng.autotune_checkpointing(a.micro_bsz, a.ctx_len)
+        if ctx.is_main:
+            print(f"activation checkpointing: {n_cp} of {eng.model.config.n_layer} blocks recomputed", flush=True)
 
     def _emergency_save(self, exc: BaseException) -> None:
         """A peer stopped answering or a step was aborted: the lowest rank still known to be alive writes a

@@ -195,3 +195,32 @@ def test_resume_latest_picks_the_newest_save_point_under_proj_dir(tmp_path, caps
     with pytest.raises(FileNotFoundError):
         PretrainTrainer(_model(), PretrainConfig(epoch_count=1, resume_from_checkpoint=str(tmp_path / "nowhere"),
                                                  **{**common, "proj_dir": str(tmp_path / "other")}), _dataset()).train()
+
+
+def test_checkpoint_tuning_is_asked_for_only_when_it_is_safe(monkeypatch, capsys):
+    """The trainers hand the choice of recomputed blocks to the engine after the first step - on a GPU, in normal mode,
+    with ``grad_cp=1``, and only if every rank's first batch had the full length."""
+    import types
+
+    calls = []
+
+    def trainer(agree=True, device="cuda", **cfg):
+        args = SFTConfig(ctx_len=64, micro_bsz=4, accelerator="cpu", precision="fp32", **cfg)
+        tr = SFTTrainer(_model(), args, _dataset())
+        tr.ctx = types.SimpleNamespace(device=types.SimpleNamespace(type=device), is_main=True,
+                                       all_agree=lambda ok: bool(ok) and agree)
+        tr.engine = types.SimpleNamespace(model=types.SimpleNamespace(config=types.SimpleNamespace(n_layer=2)),
+                                          autotune_checkpointing=lambda b, t: calls.append((b, t)) or 1)
+        return tr
+
+    monkeypatch.delenv("RWKVTUNE_GRAD_CP_AUTO", raising=False)
+    trainer(grad_cp=1)._tune_checkpointing(64)
+    assert calls == [(4, 64)] and "1 of 2 blocks recomputed" in capsys.readouterr().out
+    trainer(grad_cp=0)._tune_checkpointing(64)
+    trainer(grad_cp=1, train_type="infctx", chunk_ctx=32)._tune_checkpointing(64)
+    trainer(grad_cp=1, device="cpu")._tune_checkpointing(64)
+    trainer(grad_cp=1)._tune_checkpointing(48)                  # a short first batch says nothing about the longest one
+    trainer(grad_cp=1, agree=False)._tune_checkpointing(64)     # another rank's first batch was short
+    monkeypatch.setenv("RWKVTUNE_GRAD_CP_AUTO", "0")
+    trainer(grad_cp=1)._tune_checkpointing(64)
+    assert calls == [(4, 64)]
