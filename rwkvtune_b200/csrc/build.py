@@ -96,6 +96,12 @@ def build(verbose: bool = True, force: bool = False, debug: bool = False) -> str
     if force:
         shutil.rmtree(os.path.join(HERE, "build_debug" if debug else "build"), ignore_errors=True)
     srcs = sources()
+    obj_dir = os.path.join(HERE, "build_debug" if debug else "build")
+    if os.path.isdir(obj_dir):      # objects of sources that no longer exist
+        stems = {os.path.splitext(s)[0] for s in srcs}
+        for f in os.listdir(obj_dir):
+            if f.split(".")[0] not in stems:
+                os.remove(os.path.join(obj_dir, f))
     with cf.ThreadPoolExecutor(max_workers=min(8, len(srcs) or 1)) as pool:
         objs = list(pool.map(lambda s: _compile_one(s, verbose, debug), srcs))
     lib = os.path.join(HERE, DEBUG_LIB_NAME if debug else LIB_NAME)
