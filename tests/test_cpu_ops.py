@@ -91,3 +91,24 @@ def test_norm_and_adamw_match_the_plain_statements():
         assert torch.allclose(x, y, rtol=1e-5, atol=1e-7)
     cpu_ops.adamw_step(state_b[0], grad, state_b[1], state_b[2], 1e-2, 0.9, 0.99, 1e-8, 0.01, 4, 0.5, None)      # no scratch
     assert torch.isfinite(state_b[0]).all()
+
+
+def test_cpu_training_is_bit_reproducible(form):
+    """Heads are independent work items, so the thread schedule cannot change a sum: same seed, same bits."""
+    from rwkvtune_b200.engine import EngineConfig, TrainEngine
+    from rwkvtune_b200.models import RWKVConfig, RWKV7Model
+    from rwkvtune_b200.parallel import DistContext
+
+    def run():
+        torch.manual_seed(0)
+        model = RWKV7Model(RWKVConfig(n_layer=2, n_embd=128, vocab_size=256, dim_att_lora=16, dim_gate_lora=16, dim_mv_lora=16))
+        eng = TrainEngine(model, EngineConfig(lr_init=1e-3, precision="fp32"), DistContext())
+        g = torch.Generator().manual_seed(1)
+        losses = []
+        for _ in range(3):
+            idx = torch.randint(0, 256, (2, 40), generator=g)
+            losses.append(float(eng.train_step(idx, idx.roll(-1, 1), 1e-3)))
+        return losses, eng.space.params.clone()
+
+    (la, pa), (lb, pb) = run(), run()
+    assert la == lb and torch.equal(pa, pb)
