@@ -173,3 +173,33 @@ def test_loss_mask_hook_is_called_with_keywords(tmp_path):
     tr.train()
     assert set(seen) == {"prompts", "completions", "completion_ids", "tokenizer"}
     assert tr.last_metrics["train_loss"] == tr.last_metrics["train_loss"]
+
+
+def test_reward_functions_are_weighted_named_and_checked():
+    """Several reward functions: weights from the config, names from the functions, lists or tensors as results, and a
+    result of the wrong length is an error that names the function."""
+    model = RWKV7Model(RWKVConfig(n_layer=1, n_embd=64, vocab_size=128, dim_att_lora=8, dim_gate_lora=8, dim_mv_lora=8))
+    data = [{"prompt": "p", "input_ids": [5, 6, 7]}]
+
+    def fmt(prompts, completions, **kw):
+        return [1.0, 0.0, 1.0]
+
+    def quality(prompts, completions, **kw):
+        return torch.tensor([0.5, 2.0, -1.0])
+
+    args = GRPOConfig(micro_bsz=1, num_generations=3, steps_per_generation=1, max_prompt_length=8, max_completion_length=4,
+                      accelerator="cpu", precision="fp32", reward_weights=[0.5, 2.0])
+    tr = GRPOTrainer(model, [fmt, quality], args, data, processing_class=_Tok(), peft_config=LoraConfig(r=4, lora_alpha=8))
+    assert tr.reward_names == ["fmt", "quality"] and tr.reward_weights == [0.5, 2.0]
+    total, per_func = tr._compute_rewards(["p"] * 3, ["a", "b", "c"], {})
+    assert per_func.shape == (3, 2) and per_func[:, 0].tolist() == [1.0, 0.0, 1.0]
+    assert torch.allclose(total, torch.tensor([0.5 + 1.0, 0.0 + 4.0, 0.5 - 2.0]))
+    single = GRPOTrainer(model, fmt, GRPOConfig(micro_bsz=1, num_generations=3, steps_per_generation=1, accelerator="cpu",
+                                                precision="fp32"), data, processing_class=_Tok())
+    assert single.reward_weights == [1.0] and len(single.reward_funcs) == 1          # a bare callable is one function
+    with pytest.raises(ValueError, match="reward_weights has 1 entries for 2"):
+        GRPOTrainer(model, [fmt, quality], GRPOConfig(micro_bsz=1, num_generations=3, steps_per_generation=1,
+                                                     accelerator="cpu", precision="fp32", reward_weights=[1.0]),
+                    data, processing_class=_Tok())
+    with pytest.raises(ValueError, match="fmt returned 3 values for 2 completions"):
+        tr._compute_rewards(["p"] * 2, ["a", "b"], {})
