@@ -151,3 +151,45 @@ def test_hub_directory_layout_and_link_mode(tmp_path):
     st = create_model_hub(str(tmp_path / "st"), model_file=str(raw), save_format="safetensors")
     assert os.path.exists(os.path.join(st, "model.safetensors"))
     assert torch.allclose(AutoModel.from_pretrained(st)(IDX), m(IDX), atol=1e-6)
+
+
+def test_merge_cli_syncs_eos_prefers_adapter_tokenizer_files_and_records_provenance(tmp_path, capsys):
+    from rwkvtune_b200.cli import merge_lora
+    from rwkvtune_b200.data.tokenizers import RWKVTokenizer, chatml_utils, get_vocab_path
+    from rwkvtune_b200.training.model_save_utils import save_lora_checkpoint
+    from rwkvtune_b200.utils import create_model_hub
+
+    torch.manual_seed(0)
+    base = RWKV7Model(RWKVConfig(n_layer=2, n_embd=64, vocab_size=65536, dim_att_lora=16, dim_gate_lora=16, dim_mv_lora=16))
+    raw = tmp_path / "raw.pth"
+    torch.save(base.state_dict(), str(raw))
+    hub = create_model_hub(str(tmp_path / "hub"), model_file=str(raw))
+    assert json.load(open(os.path.join(hub, "config.json")))["eos_token_id"] == 261
+
+    adapted = get_peft_model(AutoModel.from_pretrained(hub), LoraConfig(r=4, lora_alpha=8))
+    with torch.no_grad():
+        for n, p in adapted.named_parameters():
+            if "lora_B" in n:
+                p.normal_(0, 0.05)
+    tok = RWKVTokenizer(get_vocab_path())
+    chatml_utils.setup_chatml_tokenizer(tok)                   # <|im_end|> becomes the EOS, on id 0
+    adapter_dir = str(tmp_path / "adapter")
+    save_lora_checkpoint(adapted, adapter_dir, base_model_path=hub, tokenizer=tok)
+    idx = torch.tensor([[11, 12, 13, 14]])
+    want = adapted(idx)
+
+    out = str(tmp_path / "merged")
+    assert merge_lora.main(["--base-model", hub, "--lora-model", adapter_dir, "--output", out, "--precision", "fp32",
+                            "--save-format", "safetensors"]) == 0
+    files = set(os.listdir(out))
+    assert {"model.safetensors", "config.json", "tokenizer_config.json", "vocab.txt", "merge_info.json"} <= files
+    assert json.load(open(os.path.join(out, "config.json")))["eos_token_id"] == 0           # synced from the adapter side
+    merged_tok_cfg = json.load(open(os.path.join(out, "tokenizer_config.json")))
+    assert merged_tok_cfg["eos_token"] == "<|im_end|>"                                       # the adapter's tokenizer wins
+    info = json.load(open(os.path.join(out, "merge_info.json")))
+    assert info["weights_file"] == "model.safetensors" and info["precision"] == "fp32"
+    assert info["base_model"].endswith("hub") and info["lora_model"].endswith("adapter")
+    merged = AutoModel.from_pretrained(out)
+    assert not any("lora" in k for k in merged.state_dict()) and torch.allclose(merged(idx), want, atol=1e-5)
+    assert merge_lora.main(["-b", str(tmp_path / "nowhere"), "-l", adapter_dir, "-o", out]) == 1
+    assert "merge failed" in capsys.readouterr().err
