@@ -139,3 +139,46 @@ def test_state_cache_checkpoints_from_messages(model):
     pos, state, _ = cache.lookup(tokens[:9] + [99, 98])
     assert pos == 9 and state is not None
     assert cache.create_checkpoints(tokens, messages) == 0           # both prefixes already cached
+
+
+def test_scheduler_retries_after_out_of_memory_and_stops_runaway_loops(model, monkeypatch):
+    """An out-of-memory error inside a step is retried after the allocator cache is emptied; a loop that keeps
+    scheduling without finishing anything ends with an error that carries the scheduler's counters."""
+    tok = _Tok()
+    sched = SchedulerCore(model, tok, max_batch_size=2, max_batch_tokens=16, prefill_chunk_size=8)
+    seq = SequenceState(0, [3, 4, 5], max_new_tokens=3, temperature=0.0, eos_token_id=7)
+    sched.add_sequences([seq])
+    real = sched._execute_prefill
+    failures = {"left": 2}
+
+    def flaky(batch):
+        if failures["left"] > 0:
+            failures["left"] -= 1
+            raise torch.cuda.OutOfMemoryError("synthetic")
+        return real(batch)
+
+    emptied = []
+    monkeypatch.setattr(sched, "_execute_prefill", flaky)
+    monkeypatch.setattr(torch.cuda, "empty_cache", lambda: emptied.append(1))
+    monkeypatch.setattr("time.sleep", lambda s: None)
+    for _ in sched.run_to_completion_sync():
+        pass
+    assert seq.is_finished and len(emptied) == 2 and failures["left"] == 0
+    want = model.generate(torch.tensor([[3, 4, 5]]), max_new_tokens=3, do_sample=False, eos_token_id=7)[0, 3:].tolist()
+    assert seq.generated_tokens == want[:len(seq.generated_tokens)]
+
+    always = SchedulerCore(model, tok, max_batch_size=2, max_batch_tokens=16, prefill_chunk_size=8)
+    always.add_sequences([SequenceState(1, [3, 4], max_new_tokens=2, temperature=0.0, eos_token_id=7)])
+    monkeypatch.setattr(always, "_execute_prefill", lambda batch: (_ for _ in ()).throw(torch.cuda.OutOfMemoryError("again")))
+    with pytest.raises(torch.cuda.OutOfMemoryError):
+        always.step_sync()                                              # ten attempts, then the error is the caller's
+
+    stuck = SchedulerCore(model, tok, max_batch_size=2, max_batch_tokens=16, prefill_chunk_size=8)
+    stuck.add_sequences([SequenceState(2, [3, 4], max_new_tokens=2, temperature=0.0, eos_token_id=7)])
+    monkeypatch.setattr(stuck, "step_sync", lambda: [])
+    with pytest.raises(RuntimeError, match="exceeded 5 steps"):
+        for _ in stuck.run_to_completion_sync(max_steps=5):
+            pass
+    with pytest.raises(RuntimeError, match="no progress for 3 steps"):
+        for _ in stuck.run_to_completion_sync(stall_steps=3, stall_seconds=0.0):
+            pass
