@@ -182,3 +182,53 @@ def test_scheduler_retries_after_out_of_memory_and_stops_runaway_loops(model, mo
     with pytest.raises(RuntimeError, match="no progress for 3 steps"):
         for _ in stuck.run_to_completion_sync(stall_steps=3, stall_seconds=0.0):
             pass
+
+
+def test_sampler_rules_one_by_one():
+    """Greedy below the temperature threshold, bias clamping, the processor hook, top-k, seeds, the single-row form,
+    rows that went non-finite, and the shape check."""
+    TokenSampler.set_max_valid_token_id(None)
+    logits = torch.tensor([[0.0, 1.0, 3.0, 2.0, -1.0]])
+    tok, lp = TokenSampler.sample_batch(logits, temperature=0.0)
+    assert tok.tolist() == [2] and float(lp) == pytest.approx(float(torch.log_softmax(logits, -1)[0, 2]))
+    # a bias beyond +-100 is clamped: +1e9 on id 0 still loses to nothing, -1e9 on the arg-max removes it
+    tok, _ = TokenSampler.sample_batch(logits, temperature=0.0, logit_bias={2: -1e9, "3": 0.5})
+    assert tok.tolist() == [3]
+    filtered = TokenSampler.filter_logits(logits, 1.0, 1.0, 0, logit_bias={0: 1e9, 99: 5.0})
+    assert float(filtered[0, 0]) == 100.0 and filtered.shape == logits.shape             # clamped; id 99 is out of range
+    # the processor sees the logits after temperature and bias and before top-k / top-p
+    seen = {}
+
+    def processor(x):
+        seen["x"] = x.clone()
+        x = x.clone()
+        x[..., 2] = float("-inf")
+        return x
+
+    out = TokenSampler.filter_logits(logits, 0.5, 1.0, 2, logits_processor=processor)
+    assert torch.allclose(seen["x"], logits / 0.5) and torch.isinf(out[0, 2])
+    assert torch.isfinite(out[0]).sum() == 2 and torch.isfinite(out[0, [1, 3]]).all()    # top-2 of what the processor left
+    # top-p keeps the sorted prefix whose mass stays within p, and always the most likely id
+    sharp = torch.tensor([[10.0, 0.0, 0.0, 0.0]])
+    assert torch.isfinite(TokenSampler.filter_logits(sharp, 1.0, 0.5, 0)[0]).tolist() == [True, False, False, False]
+    # seeds and generators reproduce a draw
+    flat = torch.zeros(3, 50)
+    a, _ = TokenSampler.sample_batch(flat, seed=11)
+    b, _ = TokenSampler.sample_batch(flat, seed=11)
+    c, _ = TokenSampler.sample_batch(flat, generator=torch.Generator().manual_seed(11))
+    assert a.tolist() == b.tolist() == c.tolist()
+    tok, lp = TokenSampler.sample(torch.tensor([0.0, 5.0, 1.0]), temperature=0.0)
+    assert (tok, lp) == (1, pytest.approx(float(torch.log_softmax(torch.tensor([0.0, 5.0, 1.0]), -1)[1])))
+    # a row of NaNs falls back to a uniform draw instead of raising
+    broken = torch.tensor([[float("nan")] * 4, [0.0, 1.0, 2.0, 3.0]])
+    tok, _ = TokenSampler.sample_batch(broken, seed=0)
+    assert 0 <= int(tok[0]) < 4 and 0 <= int(tok[1]) < 4
+    with pytest.raises(ValueError):
+        TokenSampler.sample_batch(torch.zeros(5))
+    # ids above the tokenizer's range are never drawn
+    TokenSampler.set_max_valid_token_id(2)
+    try:
+        draws, _ = TokenSampler.sample_batch(torch.zeros(200, 6), seed=1)
+        assert int(draws.max()) <= 2
+    finally:
+        TokenSampler.set_max_valid_token_id(None)
