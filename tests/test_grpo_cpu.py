@@ -203,3 +203,55 @@ def test_reward_functions_are_weighted_named_and_checked():
                     data, processing_class=_Tok())
     with pytest.raises(ValueError, match="fmt returned 3 values for 2 completions"):
         tr._compute_rewards(["p"] * 2, ["a", "b"], {})
+
+
+def test_full_parameter_grpo_keeps_a_frozen_reference_saves_per_batch_and_resumes(tmp_path):
+    """Without an adapter and with ``beta > 0`` the KL reference is a frozen copy of the starting weights; save points
+    every n batches; a second trainer picks the run up from one of them; ``save_model`` writes the final directory."""
+    def make():
+        torch.manual_seed(0)
+        m = RWKV7Model(RWKVConfig(n_layer=2, n_embd=64, vocab_size=128, dim_att_lora=16, dim_gate_lora=16, dim_mv_lora=16,
+                                  eos_token_id=7))
+        with torch.no_grad():
+            for n, p in m.named_parameters():
+                if n.endswith(("output.weight", "ffn.value.weight")):
+                    p.normal_(0, 0.05)
+        return m
+
+    data = [{"prompt": f"p{i}", "input_ids": [10 + i, 11 + i, 12 + i]} for i in range(4)]
+    proj = str(tmp_path / "full")
+    common = dict(micro_bsz=2, num_generations=2, steps_per_generation=1, max_prompt_length=8, max_completion_length=5,
+                  beta=0.1, lr_init=5e-3, lr_final=1e-3, warmup_steps=0, accelerator="cpu", precision="fp32", epoch_count=1,
+                  log_steps=1, save_every_n_batches=1, save_total_limit=0)
+    with pytest.warns(UserWarning) as caught:
+        tr = GRPOTrainer(make(), _low_id_reward, GRPOConfig(proj_dir=proj, **common), data, eval_dataset=data,
+                         processing_class=_Tok(), optimizers=(object(), None))
+    msgs = " ".join(str(w.message) for w in caught)
+    assert "eval_dataset is accepted but not used" in msgs and "`optimizers` is ignored" in msgs
+    start = {n: p.detach().clone() for n, p in tr.model.named_parameters()}
+    tr.train()
+    assert tr.ref_model is not None and not any(p.requires_grad for p in tr.ref_model.parameters())
+    for n, p in tr.ref_model.named_parameters():                       # the reference did not move, the policy did
+        assert torch.equal(p, start[n])
+    assert any(not torch.equal(p, start[n]) for n, p in tr.engine.model.named_parameters())
+    assert tr.last_metrics["kl_div"] >= 0
+    saved = sorted(d for d in os.listdir(proj) if d.startswith("rwkv7-batch"))
+    assert saved == ["rwkv7-batch1", "rwkv7-batch2"]
+    assert {"model.pth", "config.json", "trainer_state"} <= set(os.listdir(os.path.join(proj, "rwkv7-batch1")))
+    final = tr.save_model()
+    assert final.endswith("final") and os.path.exists(os.path.join(final, "model.pth"))
+
+    again = GRPOTrainer(make(), _low_id_reward,
+                        GRPOConfig(proj_dir=str(tmp_path / "again"), resume_from_checkpoint=os.path.join(proj, "rwkv7-batch1"),
+                                   **common), data, processing_class=_Tok())
+    again.train()
+    assert again.state["global_step"] == 2                               # one step was already done
+    recs = [json.loads(l) for l in open(os.path.join(str(tmp_path / "again"), "grpo_loss_data.jsonl"))]
+    assert len(recs) == 1
+    with pytest.raises(FileNotFoundError):
+        GRPOTrainer(make(), _low_id_reward, GRPOConfig(proj_dir=str(tmp_path / "x"), resume_from_checkpoint=str(tmp_path / "none"),
+                                                       **common), data, processing_class=_Tok()).train()
+    with pytest.raises(ValueError):
+        GRPOTrainer(make(), _low_id_reward, GRPOConfig(proj_dir=str(tmp_path / "y"), **common), None, processing_class=_Tok())
+    with pytest.raises(ValueError):
+        GRPOTrainer(make(), [], GRPOConfig(proj_dir=str(tmp_path / "z"), **common), data, processing_class=_Tok())
