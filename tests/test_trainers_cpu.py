@@ -224,3 +224,70 @@ def test_checkpoint_tuning_is_asked_for_only_when_it_is_safe(monkeypatch, capsys
     monkeypatch.setenv("RWKVTUNE_GRAD_CP_AUTO", "0")
     trainer(grad_cp=1)._tune_checkpointing(64)
     assert calls == [(4, 64)]
+
+
+def test_dataset_and_mode_validation_errors(tmp_path):
+    cfg = dict(ctx_len=32, micro_bsz=4, accelerator="cpu", precision="fp32", proj_dir=str(tmp_path / "v"))
+    with pytest.raises(ValueError, match="train_dataset is required"):
+        SFTTrainer(_model(), SFTConfig(**cfg), None)
+    with pytest.raises(ValueError, match="empty"):
+        SFTTrainer(_model(), SFTConfig(**cfg), [])
+    with pytest.raises(TypeError, match="map-style"):
+        SFTTrainer(_model(), SFTConfig(**cfg), iter(_dataset()))
+
+    class Columns(list):
+        column_names = ["input_ids", "text"]
+
+    with pytest.raises(ValueError, match="lacks columns"):
+        SFTTrainer(_model(), SFTConfig(**cfg), Columns(_dataset()))
+
+    class Stream:
+        def __iter__(self):
+            return iter(_dataset())
+
+    with pytest.raises(ValueError, match="epoch_steps"):
+        PretrainTrainer(_model(), PretrainConfig(**cfg), Stream()).train()
+    with pytest.raises(ValueError, match="too small"):
+        SFTTrainer(_model(), SFTConfig(**cfg), _dataset(3)).train()
+    with pytest.raises(ValueError, match="accumulate_grad_batches"):
+        PretrainTrainer(_model(), PretrainConfig(train_type="infctx", chunk_ctx=16, accumulate_grad_batches=2, **cfg),
+                        _dataset()).train()
+
+
+def test_adapter_runs_save_per_batch_and_resume_from_directory_file_or_full_weights(tmp_path, capsys):
+    common = dict(ctx_len=32, micro_bsz=4, lr_init=5e-3, warmup_steps=0, accelerator="cpu", precision="fp32", grad_cp=0,
+                  save_total_limit=0)
+    first = str(tmp_path / "first")
+    tr = SFTTrainer(_model(), SFTConfig(epoch_count=1, proj_dir=first, save_every_n_batches=2, **common), _dataset(),
+                    lora_config=LoraConfig(r=4, lora_alpha=8))
+    tr.train()
+    assert {"rwkv7-batch2", "rwkv7-batch4", "rwkv7-batch6", "rwkv7-epoch1"} <= set(os.listdir(first))
+    ck = os.path.join(first, "rwkv7-epoch1")
+    idx = torch.tensor([_dataset()[0]["input_ids"]])
+    want = tr.model(idx)
+
+    def resumed(source, epochs=1):
+        t = SFTTrainer(_model(), SFTConfig(epoch_count=epochs, proj_dir=str(tmp_path / f"r{abs(hash(source)) % 9999}"),
+                                           resume_from_checkpoint=source, **common), _dataset(),
+                       lora_config=LoraConfig(r=4, lora_alpha=8))
+        t.train()
+        return t
+
+    a = resumed(ck)                                                     # the checkpoint directory (adapter inside)
+    assert a.state["samples_seen"] == 24 and torch.allclose(a.model(idx), want, atol=1e-5)
+    capsys.readouterr()
+    b = resumed(os.path.join(ck, "adapter_model.bin"))                  # the bare adapter file: weights only, a fresh epoch
+    out = capsys.readouterr().out
+    assert "adapter_model.bin (weights only); samples_seen=0" in out and "step 6/6" in out
+    assert not torch.allclose(b.model(idx), want, atol=1e-5)            # it trained on from the loaded adapter
+    full = str(tmp_path / "plain.pth")                                  # a plain full-weight file into an adapter model
+    torch.save(_model().state_dict(), full)
+    c = SFTTrainer(_model(), SFTConfig(epoch_count=1, proj_dir=str(tmp_path / "c"), resume_from_checkpoint=full, **common),
+                   _dataset(), lora_config=LoraConfig(r=4, lora_alpha=8))
+    c.train()
+    assert any("lora_A" in n for n, _ in c.model.named_parameters())
+    empty = tmp_path / "emptyck"
+    (empty / "trainer_state").mkdir(parents=True)
+    with pytest.raises(FileNotFoundError, match="neither model weights nor adapter"):
+        SFTTrainer(_model(), SFTConfig(epoch_count=1, proj_dir=str(tmp_path / "d"), resume_from_checkpoint=str(empty), **common),
+                   _dataset()).train()
