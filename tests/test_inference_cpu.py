@@ -232,3 +232,69 @@ def test_sampler_rules_one_by_one():
         assert int(draws.max()) <= 2
     finally:
         TokenSampler.set_max_valid_token_id(None)
+
+
+def test_scheduler_stop_strings_token_queue_enforcer_and_fully_cached_prompts(model):
+    import queue
+
+    from rwkvtune_b200.inference import CacheConfig, CacheLevel, StateCache
+
+    tok = _Tok()
+    greedy = model.generate(torch.tensor([[3, 4, 5]]), max_new_tokens=6, do_sample=False, eos_token_id=999)[0, 3:].tolist()
+    text = tok.decode(greedy)
+
+    # a stop string ends the sequence as soon as the decoded text contains it; tokens also arrive on the queue
+    q = queue.Queue()
+    sched = SchedulerCore(model, tok, max_batch_size=2, max_batch_tokens=16, prefill_chunk_size=8)
+    seq = SequenceState("s", [3, 4, 5], max_new_tokens=6, temperature=0.0, eos_token_id=999, stop=[text[1:3]], output_queue=q)
+    sched.add_sequences([seq])
+    for _ in sched.run_to_completion_sync():
+        pass
+    assert seq.finish_reason == "stop" and seq.generated_tokens == greedy[:3] and text[1:3] in seq.generated_text
+    drained = []
+    while not q.empty():
+        drained.append(q.get())
+    assert drained == greedy[:3] + [None]                                # the end marker follows the last token
+
+    # an enforcer masks the logits, is told every token, and ends the sequence when it is satisfied
+    class TwoTokens:
+        def __init__(self):
+            self.seen = []
+
+        def mask_logits(self, logits):
+            out = torch.full_like(logits, float("-inf"))
+            out[..., 20 + len(self.seen)] = 0.0
+            return out
+
+        def update(self, token):
+            self.seen.append(token)
+
+        def is_finished(self):
+            return len(self.seen) == 2
+
+    enf = TwoTokens()
+    sched2 = SchedulerCore(model, tok, max_batch_size=2, max_batch_tokens=16, prefill_chunk_size=8)
+    forced = SequenceState(1, [3, 4, 5], max_new_tokens=6, temperature=1.0, eos_token_id=999, enforcer=enf)
+    sched2.add_sequences([forced])
+    for _ in sched2.run_to_completion_sync():
+        pass
+    assert forced.generated_tokens == [20, 21] == enf.seen and forced.finish_reason == "schema_complete"
+
+    # a prompt that is in the cache to its last token needs no prefill at all: its stored logits seed the first draw
+    cache = StateCache(model, CacheConfig(max_cache_memory_gb=0.01, cache_level=CacheLevel.EXACT), auto_config=False)
+    cache.create_checkpoints([3, 4, 5])
+    pos, state, output = cache.lookup([3, 4, 5])
+    assert pos == 3 and state is not None and cache.lookup([3, 4])[0] == 0          # exact level: no prefix hits
+    assert cache.get_stats()["exact_hits"] >= 1
+    sched3 = SchedulerCore(model, tok, max_batch_size=2, max_batch_tokens=16, prefill_chunk_size=8, state_cache=cache)
+    hit = SequenceState(2, [3, 4, 5], max_new_tokens=6, temperature=0.0, eos_token_id=999)
+    sched3.add_sequences([hit])
+    for _ in sched3.run_to_completion_sync():
+        pass
+    assert hit.cached_prefix_len == 3 and hit.generated_tokens == greedy
+    off = StateCache(model, CacheConfig(max_cache_memory_gb=0.01, cache_level=CacheLevel.NONE), auto_config=False)
+    assert off.lookup([3, 4, 5]) == (0, None, None) and off.get_stats()["total_misses"] == 1
+    with pytest.raises(ValueError):
+        CacheConfig(max_cache_memory_gb=0.0)
+    with pytest.raises(ValueError):
+        sched3.add_sequences([SequenceState(3, [], max_new_tokens=1)])
