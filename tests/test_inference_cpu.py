@@ -298,3 +298,26 @@ def test_scheduler_stop_strings_token_queue_enforcer_and_fully_cached_prompts(mo
         CacheConfig(max_cache_memory_gb=0.0)
     with pytest.raises(ValueError):
         sched3.add_sequences([SequenceState(3, [], max_new_tokens=1)])
+
+
+def test_batch_generator_token_inputs_eos_stripping_and_mode_restore(model, capsys):
+    from rwkvtune_b200.inference import BatchGenerator, GenerationConfig
+
+    class Tok(_Tok):
+        pass
+
+    tok = Tok()
+    first = int(model.generate(torch.tensor([[3, 4, 5]]), max_new_tokens=1, do_sample=False)[0, -1])
+    tok.eos_token_id = first                       # the very first greedy token ends the sequence
+    gen = BatchGenerator(model, tok, max_batch_size=4, verbose=True)
+    model.train()
+    out = gen.generate(input_ids=[[3, 4, 5], [9, 8]], generation_config=GenerationConfig(max_length=4, temperature=0.0,
+                                                                                        num_generations=2))
+    assert model.training                                                  # the caller's mode is put back
+    model.eval()
+    assert out["completion_ids"].shape[0] == 4 and out["masks"].dtype == torch.float32
+    assert out["masks"][0].sum() == 0 and out["completions"][0] == ""      # only an EOS was produced, and it is stripped
+    assert out["masks"][0].tolist() == out["masks"][1].tolist()            # both generations of a prompt, prompt-major
+    assert "eos 2" in capsys.readouterr().out
+    with pytest.raises(ValueError):
+        gen.generate()
