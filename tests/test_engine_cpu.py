@@ -1,4 +1,5 @@
 """Engine-level behaviour on CPU: infinite-context steps with masked chunks, phase timers, bucket planning."""
+import pytest
 import torch
 
 from rwkvtune_b200.engine import EngineConfig, TrainEngine
@@ -130,3 +131,49 @@ def test_trainer_profile_steps_switch(tmp_path, monkeypatch):
     SFTTrainer(model, args, rows).train()
     text = open(os.path.join(proj, "profile_kernels.txt")).read()
     assert text.startswith("1 training steps after 3 warm-up steps") and "aten::" in text
+
+
+def test_checkpoint_publication_replacement_rotation_and_lookup(tmp_path):
+    import os
+    import time
+
+    from rwkvtune_b200.engine import checkpoint as ckpt
+    from rwkvtune_b200.parallel import DistContext
+
+    ctx = DistContext()
+    final = str(tmp_path / "rwkv7-batch1")
+
+    def writer(text):
+        def write(tmp):
+            with open(os.path.join(tmp, "model.pth"), "w") as fh:
+                fh.write(text)
+        return write
+
+    ckpt.atomic_checkpoint(final, ctx, writer("first"))
+    ckpt.atomic_checkpoint(final, ctx, writer("second"))                       # same name again: replaced, nothing left over
+    assert open(os.path.join(final, "model.pth")).read() == "second"
+    assert sorted(os.listdir(tmp_path)) == ["rwkv7-batch1"]
+
+    def failing(tmp):
+        raise OSError("disk full")
+
+    with pytest.raises(OSError, match="disk full"):
+        ckpt.atomic_checkpoint(final, ctx, failing)
+    assert open(os.path.join(final, "model.pth")).read() == "second" and sorted(os.listdir(tmp_path)) == ["rwkv7-batch1"]
+
+    for i in (2, 3, 4):
+        d = tmp_path / f"rwkv7-batch{i}"
+        (d / ckpt.STATE_DIR).mkdir(parents=True)
+        now = time.time() + i
+        os.utime(d, (now, now))
+    (tmp_path / "rwkv7-batch9.tmp").mkdir()                                    # an unfinished save is not a candidate
+    assert ckpt.rotate_checkpoints(str(tmp_path), 0) == []
+    removed = ckpt.rotate_checkpoints(str(tmp_path), 2)
+    assert sorted(os.path.basename(r) for r in removed) == ["rwkv7-batch1", "rwkv7-batch2"]
+    assert ckpt.find_checkpoint(str(tmp_path)).endswith("rwkv7-batch4")        # a parent directory: the newest child
+    assert ckpt.find_checkpoint(str(tmp_path / "rwkv7-batch3")).endswith("rwkv7-batch3")
+    weights = tmp_path / "plain.pth"
+    weights.write_text("x")
+    assert ckpt.find_checkpoint(str(weights)) == str(weights)                  # a bare file is taken as it is
+    assert ckpt.find_checkpoint(str(tmp_path / "nowhere")) is None and ckpt.find_checkpoint(None) is None
+    assert ckpt.read_meta(str(tmp_path / "rwkv7-batch3")) == {}
