@@ -1,4 +1,5 @@
-"""Engine-level behaviour on CPU: infinite-context steps with masked chunks, phase timers, bucket planning."""
+"""Engine-level behaviour on CPU: infinite-context steps with masked chunks, phase timers, bucket planning, the N-step
+profiler, checkpoint publication / rotation / lookup."""
 import pytest
 import torch
 

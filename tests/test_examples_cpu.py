@@ -1,5 +1,5 @@
-"""The example scripts' data preparation and reward functions, and one tiny end-to-end SFT run through
-``examples/train_sft_single_gpu.py`` on CPU."""
+"""The example scripts' data preparation and reward functions, and tiny end-to-end runs of all three scripts on CPU:
+SFT with an adapter, GRPO, and generation with the adapter GRPO saved."""
 import json
 import os
 import sys

@@ -1,4 +1,5 @@
-"""Sampler rules, rollout generator, scheduler, state cache on a tiny CPU model."""
+"""Sampler rules, rollout generator, scheduler (stop strings, token queue, enforcer hook, out-of-memory retry, runaway
+guards), batch generator and state cache on a tiny CPU model."""
 import pytest
 import torch
 

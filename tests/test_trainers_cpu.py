@@ -1,4 +1,5 @@
-"""SFT/Pretrain trainers end to end on CPU: loss goes down, checkpoint layout, resume, LoRA, CLI round trip."""
+"""SFT/Pretrain trainers end to end on CPU: loss goes down, checkpoint layout, resume (exact, "latest", from adapter or
+full-weight files), LoRA, CLI round trip, argument validation, the checkpoint-tuning decision."""
 import json
 import os
 
